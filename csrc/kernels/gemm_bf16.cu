@@ -1,0 +1,70 @@
+// Plain bf16 GEMM on the shared tcgen05 mainloop: every operand layout (NT / NN / TN / TT) and
+// bf16 or fp32 output, optionally accumulating into the destination.  The reference has no GEMM of
+// its own (it calls cuBLAS through torch.matmul, e.g. rl_engine/kernels/ops/pytorch/loss/
+// linear_logp.py:17-38); this kernel exists so that no hot path needs a library GEMM.
+#include "../common/gemm_sm100.cuh"
+#include "../common/tensormap.h"
+#include "kernels.h"
+
+namespace rlk {
+
+namespace {
+
+constexpr int kBN = 256;
+constexpr int kStages = 4;
+
+template <bool A_MN, bool B_MN, class Epi>
+void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
+  // Rasterise in groups of 8 M-tiles so concurrently running CTAs share A and B tiles in L2.
+  const GemmProblem p = make_gemm_problem(a.M, a.N, a.K, kBN, 1, 8);
+  const CUtensorMap ta = A_MN ? make_tmap_2d_bf16(a.A, a.K, a.M, a.lda, kBK, 64)
+                              : make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
+  const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, a.K, a.N, a.ldb, kBK, 64)
+                              : make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kBN, kBK);
+  auto kernel = gemm_sm100_kernel<kBN, A_MN, B_MN, kStages, Epi>;
+  using L = GemmSmem<kBN, kStages>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    configured = true;
+  }
+  int grid = p.num_items < a.sm_count ? p.num_items : a.sm_count;
+  if (grid < 1) return;
+  kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, a.err, 100u);
+}
+
+template <bool A_MN, bool B_MN>
+void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
+  if (a.out_fp32) {
+    if (a.accumulate) {
+      using E = EpiStore<float, true>;
+      launch<A_MN, B_MN, E>(a, typename E::Params{static_cast<float*>(a.D), a.ldd, a.alpha}, stream);
+    } else {
+      using E = EpiStore<float, false>;
+      launch<A_MN, B_MN, E>(a, typename E::Params{static_cast<float*>(a.D), a.ldd, a.alpha}, stream);
+    }
+  } else {
+    if (a.accumulate) {
+      using E = EpiStore<__nv_bfloat16, true>;
+      launch<A_MN, B_MN, E>(a, typename E::Params{static_cast<__nv_bfloat16*>(a.D), a.ldd, a.alpha}, stream);
+    } else {
+      using E = EpiStore<__nv_bfloat16, false>;
+      launch<A_MN, B_MN, E>(a, typename E::Params{static_cast<__nv_bfloat16*>(a.D), a.ldd, a.alpha}, stream);
+    }
+  }
+}
+
+}  // namespace
+
+void gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return;
+  if (a.a_mn_major) {
+    if (a.b_mn_major) dispatch_out<true, true>(a, stream);
+    else dispatch_out<true, false>(a, stream);
+  } else {
+    if (a.b_mn_major) dispatch_out<false, true>(a, stream);
+    else dispatch_out<false, false>(a, stream);
+  }
+}
+
+}  // namespace rlk

@@ -1,0 +1,196 @@
+// Host-callable launchers of every CUDA kernel in the extension.  This header is plain C++ (no
+// torch, no device code) so the binding layer and the kernels compile independently.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rlk {
+
+// ----------------------------------------------------------------------------- GEMM (tcgen05)
+// D[M,N] = alpha * op(A) * op(B)^T (+ D if accumulate).
+//   a_mn_major = false : A is row-major [M, K] (ld = lda);  true : A is row-major [K, M]
+//   b_mn_major = false : B is row-major [N, K] (ld = ldb);  true : B is row-major [K, N]
+// out_fp32 selects float (else bf16) output.  All leading dimensions are in elements; operand
+// leading dimensions must be multiples of 8 and bases 16-byte aligned (TMA).
+struct GemmArgs {
+  const __nv_bfloat16* A;
+  const __nv_bfloat16* B;
+  void* D;
+  int M, N, K;
+  long long lda, ldb, ldd;
+  bool a_mn_major, b_mn_major;
+  bool out_fp32, accumulate;
+  float alpha;
+  int sm_count;
+  uint32_t* err;
+};
+void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
+
+// ----------------------------------------------------------------- fused linear -> log-prob
+struct LinearLogpFwdArgs {
+  const __nv_bfloat16* hidden;  // [n_tokens, hidden_dim]
+  const __nv_bfloat16* weight;  // [v_local, hidden_dim]
+  const long long* target;      // [n_tokens] global ids
+  const float* bias;            // [v_local] or null
+  int n_tokens, hidden_dim, v_local;
+  long long ld_hidden, ld_weight;
+  long long vocab_start;
+  int rank, world;
+  void* peer_partials[8];          // per rank: float4 [world * items_per_m, n_pad]
+  unsigned int* peer_counters[8];  // per rank: [tiles_m] counters of the set used by this launch
+  unsigned int* next_counters;     // local: the set the next launch will use (zeroed here)
+  float* logp;
+  float* lse;
+  float* entropy;
+  int sm_count;
+  uint32_t* err;
+  unsigned long long wait_limit_ns;  // 0 = default
+};
+void linear_logp_forward(const LinearLogpFwdArgs& args, cudaStream_t stream);
+void linear_logp_workspace_shape(int n_tokens, int v_local, int world, int* items_per_m, int* n_pad, int* tiles_m);
+
+struct LinearLogpDzArgs {
+  const __nv_bfloat16* hidden;
+  const __nv_bfloat16* weight;
+  const long long* target;
+  const float* bias;
+  const float* lse;
+  const float* grad;
+  int n_tokens, hidden_dim, v_local;
+  long long ld_hidden, ld_weight;
+  long long vocab_start;
+  __nv_bfloat16* dz;
+  long long ld_dz;
+  int sm_count;
+  uint32_t* err;
+};
+void linear_logp_dz(const LinearLogpDzArgs& args, cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// dtype codes used by the elementwise / row kernels: 0 = float32, 1 = bfloat16, 2 = float16.
+
+// ------------------------------------------------------------------ log-prob over logits rows
+struct LogpRowsArgs {
+  const void* logits;  // [rows, V] with row pitch ld (elements)
+  long long ld;
+  int in_dtype;
+  const long long* ids;          // [rows]
+  const long long* row_indices;  // [launch_rows] or null (dense)
+  int launch_rows;
+  int V;
+  void* out;  // [rows]
+  int out_dtype;
+};
+void logp_rows(const LogpRowsArgs& args, cudaStream_t stream);
+
+struct RatioKlFwdArgs {
+  const void* policy;
+  const void* ref;
+  long long ld_policy, ld_ref;
+  int dtype;
+  const long long* ids;
+  const unsigned char* mask;
+  const float* old_logp;
+  int rows, V;
+  float* ratio;
+  float* kl;
+  float* save_d;
+  float* save_lse;
+  unsigned int* bad_id_flag;
+};
+void ratio_kl_forward(const RatioKlFwdArgs& args, cudaStream_t stream);
+
+struct RatioKlBwdArgs {
+  const void* policy;
+  long long ld_policy;
+  int dtype;
+  const long long* ids;
+  const unsigned char* mask;
+  const float* g_ratio;
+  const float* g_kl;
+  const float* ratio;
+  const float* save_d;
+  const float* save_lse;
+  int rows, V;
+  void* grad;
+  long long ld_grad;
+};
+void ratio_kl_backward(const RatioKlBwdArgs& args, cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// -------------------------------------------------------------------------------- RL losses
+// bounds == null -> uniform groups of `uniform` sequences.
+void group_advantages(const float* rewards, const long long* bounds, int num_groups, long long uniform, float eps,
+                      float* adv, cudaStream_t stream);
+
+struct SurrogateFwdArgs {
+  const float* logp;      // [n] policy log-probs
+  const float* ref_logp;  // [n] or null (kl = 0)
+  const float* old_logp;  // [n]
+  const float* adv_seq;   // [n / T] per-sequence advantages, or null
+  const float* adv_tok;   // [n] per-token advantages, or null
+  const unsigned char* mask;
+  long long n, T;
+  float clip_eps, beta;
+  float* d_pl;       // [n] unit gradient of the policy term
+  float* d_kl;       // [n] unit gradient of the kl term
+  float* ratio_out;  // [n] or null
+  float* kl_out;     // [n] or null
+  float* partials;   // [surrogate_partial_floats()]
+  float* out4;       // {loss, policy_loss, kl, active count}
+};
+int surrogate_partial_floats();
+void surrogate_forward(const SurrogateFwdArgs& args, cudaStream_t stream);
+void surrogate_backward(const float* d_pl, const float* d_kl, const float* stats, const float* g3, float beta,
+                        long long n, float* grad_logp, cudaStream_t stream);
+void dpo_forward(const float* pc, const float* pr, const float* rc, const float* rr, int n, float beta, float ls,
+                 float* out_loss, float* chosen_reward, float* rejected_reward, float* dh, cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// --------------------------------------------------------------------------- model-side ops
+void rmsnorm_forward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, void* y, long long ldy,
+                     bool out_fp32, long long rows, int D, float eps, float* rstd, cudaStream_t stream);
+int rmsnorm_bwd_chunks(long long rows);
+void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, const void* dy,
+                      long long lddy, const float* rstd, void* dx, long long lddx, long long rows, int D,
+                      float* dw_part, void* dw, cudaStream_t stream);
+// up == null -> plain SiLU
+void swiglu_forward(const void* gate, long long ldg, const void* up, long long ldu, int dtype, void* out, long long ldo,
+                    bool out_fp32, long long rows, int F, cudaStream_t stream);
+void swiglu_backward(const void* gate, long long ldg, const void* up, long long ldu, const void* dy, long long lddy,
+                     int dtype, void* dgate, long long lddg, void* dup, long long lddu, long long rows, int F,
+                     cudaStream_t stream);
+void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
+                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream);
+void embedding_forward(const long long* ids, const void* table, long long ldw, int dtype, void* out, long long rows,
+                       int D, long long vocab, cudaStream_t stream);
+void embedding_backward(const long long* seg_ids, const long long* seg_start, long long segments,
+                        const long long* order, const void* dy, int dy_dtype, int D, void* dtable, bool table_fp32,
+                        long long ldw, cudaStream_t stream);
+void adamw_step(void* p, int p_dtype, float* master, const void* g, int g_dtype, float* m, float* v, long long n,
+                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// ---------------------------------------------------------------------------------- sampler
+// top_k in [1, sample_topk_limit()], top_p in (0, 1] (1 disables the nucleus cut).
+void sample_topk_topp(const void* logits, long long ld, int dtype, int rows, int V, int top_k, float top_p,
+                      float temperature, unsigned long long seed, unsigned long long offset, long long* out_ids,
+                      float* out_logprob, cudaStream_t stream);
+int sample_topk_limit();
+
+}  // namespace rlk

@@ -1,0 +1,357 @@
+// Memory-bound transformer ops for sm_100a: RMSNorm, SiLU / SwiGLU, RoPE, embedding, fused AdamW.
+// All use 16-byte accesses, fp32 math, and fixed-order reductions (bitwise reproducible and
+// independent of the batch: a row's result depends only on that row).
+//
+// The reference has only PyTorch definitions of these (rl_engine/kernels/ops/pytorch/norm/
+// rms_norm.py:52-70, activation/swiglu.py:38-86, linear/embedding.py:35-51) and no RoPE or optimiser.
+#include "../common/ptx.cuh"
+#include "kernels.h"
+
+#include <cuda_fp16.h>
+
+namespace rlk {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p, long long i);
+template <> __device__ __forceinline__ float ldf<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) { return __bfloat162float(p[i]); }
+template <> __device__ __forceinline__ float ldf<__half>(const __half* p, long long i) { return __half2float(p[i]); }
+template <typename T> __device__ __forceinline__ void stf(T* p, long long i, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, long long i, float v) { p[i] = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void stf<__half>(__half* p, long long i, float v) { p[i] = __float2half_rn(v); }
+
+// Vector of 16 bytes of T
+template <typename T> struct Vec16 {
+  static constexpr int kN = 16 / sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ float get(int j) const { return ldf(reinterpret_cast<const T*>(&raw), j); }
+  __device__ __forceinline__ void set(int j, float v) { stf(reinterpret_cast<T*>(&raw), j, v); }
+};
+
+constexpr int kNormThreads = 128;
+
+__device__ __forceinline__ float block_sum_128(float v, float* smem) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+  __syncthreads();
+  const float r = (smem[0] + smem[1]) + (smem[2] + smem[3]);
+  __syncthreads();
+  return r;
+}
+
+// ---------------------------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w ; out dtype TO (x.dtype or fp32); optionally saves rstd.
+template <typename T, typename TW, typename TO>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, TO* __restrict__ y, long long ldy,
+                   int D, float eps, float* __restrict__ rstd_out) {
+  __shared__ float red[4];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  TO* yr = y + row * ldy;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += kNormThreads) {
+    const float v = ldf(xr, i);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum_128(ss, red);
+  const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+  if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+  for (int i = threadIdx.x; i < D; i += kNormThreads) stf(yr, i, ldf(xr, i) * rstd * ldf(w, i));
+}
+
+// dx = rstd * (w*dy - x * rstd^2 * mean(w*dy*x)); per-row-chunk partial dw written to dw_part[chunk, D].
+constexpr int kNormBwdRows = 64;  // rows per CTA for the dw partial
+template <typename T, typename TW>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, const T* __restrict__ dy,
+                   long long lddy, const float* __restrict__ rstd, T* __restrict__ dx, long long lddx, int rows, int D,
+                   float* __restrict__ dw_part) {
+  __shared__ float red[4];
+  extern __shared__ float dw_acc[];  // [D]
+  for (int i = threadIdx.x; i < D; i += kNormThreads) dw_acc[i] = 0.f;
+  const long long r0 = static_cast<long long>(blockIdx.x) * kNormBwdRows;
+  const long long r1 = r0 + kNormBwdRows < rows ? r0 + kNormBwdRows : rows;
+  for (long long row = r0; row < r1; ++row) {
+    const T* xr = x + row * ldx;
+    const T* gr = dy + row * lddy;
+    T* dr = dx + row * lddx;
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x; i < D; i += kNormThreads) dot = fmaf(ldf(gr, i) * ldf(w, i), ldf(xr, i), dot);
+    dot = block_sum_128(dot, red);
+    const float c = dot * rs * rs / static_cast<float>(D);
+    for (int i = threadIdx.x; i < D; i += kNormThreads) {
+      const float xv = ldf(xr, i), gv = ldf(gr, i);
+      stf(dr, i, rs * (gv * ldf(w, i) - xv * c));
+      dw_acc[i] = fmaf(gv, xv * rs, dw_acc[i]);  // each thread owns its columns: no race
+    }
+  }
+  float* out = dw_part + static_cast<long long>(blockIdx.x) * D;
+  for (int i = threadIdx.x; i < D; i += kNormThreads) out[i] = dw_acc[i];
+}
+
+template <typename TW>
+__global__ void colsum_kernel(const float* __restrict__ part, int chunks, int D, TW* __restrict__ dw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= D) return;
+  float s = 0.f;
+  for (int c = 0; c < chunks; ++c) s += part[static_cast<long long>(c) * D + i];
+  stf(dw, i, s);
+}
+
+// ------------------------------------------------------------------------------ SiLU / SwiGLU
+template <typename T, typename TO>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ gate, long long ldg, const T* __restrict__ up, long long ldu,
+                                  TO* __restrict__ out, long long ldo, long long rows, int F) {
+  const long long total = rows * F;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / F;
+    const int c = static_cast<int>(idx - r * F);
+    const float g = ldf(gate, r * ldg + c);
+    const float s = g / (1.f + expf(-g));
+    const float u = up ? ldf(up, r * ldu + c) : 1.f;
+    stf(out, r * ldo + c, s * u);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ gate, long long ldg, const T* __restrict__ up, long long ldu,
+                                  const T* __restrict__ dy, long long lddy, T* __restrict__ dgate, long long lddg,
+                                  T* __restrict__ dup, long long lddu, long long rows, int F) {
+  const long long total = rows * F;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / F;
+    const int c = static_cast<int>(idx - r * F);
+    const float g = ldf(gate, r * ldg + c);
+    const float sig = 1.f / (1.f + expf(-g));
+    const float silu = g * sig;
+    const float d = ldf(dy, r * lddy + c);
+    const float u = up ? ldf(up, r * ldu + c) : 1.f;
+    stf(dgate, r * lddg + c, d * u * sig * (1.f + g * (1.f - sig)));
+    if (dup) stf(dup, r * lddu + c, d * silu);
+  }
+}
+
+// ------------------------------------------------------------------------------------- RoPE
+// x: [tokens, heads, D] (token pitch ldt, head pitch D); cos/sin: [max_pos, D/2] fp32.
+// out[.., j] = a cos - b sin ; out[.., j + D/2] = b cos + a sin ; sign = -1 gives the inverse (backward).
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, long long ldt, const long long* __restrict__ pos,
+                            const float* __restrict__ cs, const float* __restrict__ sn, T* __restrict__ out,
+                            long long ldo, long long tokens, int heads, int D, float sign) {
+  const int half = D / 2;
+  const long long total = tokens * heads * half;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int j = static_cast<int>(idx % half);
+    const long long th = idx / half;
+    const int h = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    const long long p = pos[t];
+    const float c = cs[p * half + j];
+    const float s = sn[p * half + j] * sign;
+    const long long base = t * ldt + static_cast<long long>(h) * D;
+    const long long obase = t * ldo + static_cast<long long>(h) * D;
+    const float a = ldf(x, base + j), b = ldf(x, base + j + half);
+    stf(out, obase + j, a * c - b * s);
+    stf(out, obase + j + half, b * c + a * s);
+  }
+}
+
+// -------------------------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ table, long long ldw,
+                                     T* __restrict__ out, int D, long long vocab) {
+  const long long row = blockIdx.x;
+  long long id = ids[row];
+  if (id < 0 || id >= vocab) id = 0;
+  const T* src = table + id * ldw;
+  T* dst = out + row * static_cast<long long>(D);
+  if ((D * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 &&
+      (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    const int n = D * sizeof(T) / 16;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// Deterministic backward: tokens are pre-sorted by id (stable); CTA s sums the rows of segment s in
+// that order and writes one table row.  No atomics.
+template <typename T, typename TG>
+__global__ void embedding_bwd_kernel(const long long* __restrict__ seg_ids, const long long* __restrict__ seg_start,
+                                     const long long* __restrict__ order, const T* __restrict__ dy, int D,
+                                     TG* __restrict__ dtable, long long ldw) {
+  const long long s = blockIdx.x;
+  const long long b0 = seg_start[s], b1 = seg_start[s + 1];
+  const long long id = seg_ids[s];
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float acc = 0.f;
+    for (long long k = b0; k < b1; ++k) acc += ldf(dy, order[k] * static_cast<long long>(D) + i);
+    stf(dtable, id * ldw + i, acc);
+  }
+}
+
+// ------------------------------------------------------------------------------ fused AdamW
+// p (bf16 or fp32), optional fp32 master copy, g (bf16 or fp32), m / v fp32.  Decoupled weight decay.
+template <typename TP, typename TG>
+__global__ void adamw_kernel(TP* __restrict__ p, float* __restrict__ master, const TG* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2, float grad_scale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float gi = ldf(g, i) * grad_scale;
+    float w = master ? master[i] : ldf(p, i);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float denom = sqrtf(vi / bc2) + eps;
+    w = w * (1.f - lr * wd) - lr * (mi / bc1) / denom;
+    if (master) master[i] = w;
+    stf(p, i, w);
+  }
+}
+
+inline int grid_for(long long total, int threads) {
+  long long b = (total + threads - 1) / threads;
+  const long long cap = 148LL * 16;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+#define RLK_DISPATCH_T(code, ...)                          \
+  do {                                                     \
+    if ((code) == 0) { using T = float; __VA_ARGS__; }      \
+    else if ((code) == 1) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else { using T = __half; __VA_ARGS__; }                \
+  } while (0)
+
+void rmsnorm_forward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, void* y, long long ldy,
+                     bool out_fp32, long long rows, int D, float eps, float* rstd, cudaStream_t stream) {
+  if (rows <= 0) return;
+  RLK_DISPATCH_T(x_dtype, {
+    using TX = T;
+    RLK_DISPATCH_T(w_dtype, {
+      using TW = T;
+      if (out_fp32)
+        rmsnorm_fwd_kernel<TX, TW, float><<<rows, kNormThreads, 0, stream>>>(
+            static_cast<const TX*>(x), ldx, static_cast<const TW*>(w), static_cast<float*>(y), ldy, D, eps, rstd);
+      else
+        rmsnorm_fwd_kernel<TX, TW, TX><<<rows, kNormThreads, 0, stream>>>(
+            static_cast<const TX*>(x), ldx, static_cast<const TW*>(w), static_cast<TX*>(y), ldy, D, eps, rstd);
+    });
+  });
+}
+
+int rmsnorm_bwd_chunks(long long rows) { return static_cast<int>((rows + kNormBwdRows - 1) / kNormBwdRows); }
+
+void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, const void* dy,
+                      long long lddy, const float* rstd, void* dx, long long lddx, long long rows, int D,
+                      float* dw_part, void* dw, cudaStream_t stream) {
+  if (rows <= 0) return;
+  const int chunks = rmsnorm_bwd_chunks(rows);
+  RLK_DISPATCH_T(x_dtype, {
+    using TX = T;
+    RLK_DISPATCH_T(w_dtype, {
+      using TW = T;
+      auto k = rmsnorm_bwd_kernel<TX, TW>;
+      if (D * 4 > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, D * 4);
+      k<<<chunks, kNormThreads, D * sizeof(float), stream>>>(static_cast<const TX*>(x), ldx, static_cast<const TW*>(w),
+                                                            static_cast<const TX*>(dy), lddy, rstd,
+                                                            static_cast<TX*>(dx), lddx, static_cast<int>(rows), D,
+                                                            dw_part);
+      colsum_kernel<TW><<<(D + 255) / 256, 256, 0, stream>>>(dw_part, chunks, D, static_cast<TW*>(dw));
+    });
+  });
+}
+
+void swiglu_forward(const void* gate, long long ldg, const void* up, long long ldu, int dtype, void* out, long long ldo,
+                    bool out_fp32, long long rows, int F, cudaStream_t stream) {
+  if (rows <= 0 || F <= 0) return;
+  const int threads = 256;
+  const int grid = grid_for(rows * F, threads);
+  RLK_DISPATCH_T(dtype, {
+    if (out_fp32)
+      swiglu_fwd_kernel<T, float><<<grid, threads, 0, stream>>>(static_cast<const T*>(gate), ldg,
+                                                                static_cast<const T*>(up), ldu,
+                                                                static_cast<float*>(out), ldo, rows, F);
+    else
+      swiglu_fwd_kernel<T, T><<<grid, threads, 0, stream>>>(static_cast<const T*>(gate), ldg,
+                                                            static_cast<const T*>(up), ldu, static_cast<T*>(out), ldo,
+                                                            rows, F);
+  });
+}
+
+void swiglu_backward(const void* gate, long long ldg, const void* up, long long ldu, const void* dy, long long lddy,
+                     int dtype, void* dgate, long long lddg, void* dup, long long lddu, long long rows, int F,
+                     cudaStream_t stream) {
+  if (rows <= 0 || F <= 0) return;
+  const int threads = 256;
+  const int grid = grid_for(rows * F, threads);
+  RLK_DISPATCH_T(dtype, {
+    swiglu_bwd_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(gate), ldg, static_cast<const T*>(up), ldu,
+                                                       static_cast<const T*>(dy), lddy, static_cast<T*>(dgate), lddg,
+                                                       static_cast<T*>(dup), lddu, rows, F);
+  });
+}
+
+void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
+                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  const int threads = 256;
+  const int grid = grid_for(tokens * heads * (D / 2), threads);
+  RLK_DISPATCH_T(dtype, {
+    rope_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), ldt, pos, cos_t, sin_t,
+                                                 static_cast<T*>(out), ldo, tokens, heads, D, inverse ? -1.f : 1.f);
+  });
+}
+
+void embedding_forward(const long long* ids, const void* table, long long ldw, int dtype, void* out, long long rows,
+                       int D, long long vocab, cudaStream_t stream) {
+  if (rows <= 0) return;
+  RLK_DISPATCH_T(dtype, {
+    embedding_fwd_kernel<T><<<rows, 128, 0, stream>>>(ids, static_cast<const T*>(table), ldw, static_cast<T*>(out), D,
+                                                      vocab);
+  });
+}
+
+void embedding_backward(const long long* seg_ids, const long long* seg_start, long long segments,
+                        const long long* order, const void* dy, int dy_dtype, int D, void* dtable, bool table_fp32,
+                        long long ldw, cudaStream_t stream) {
+  if (segments <= 0) return;
+  RLK_DISPATCH_T(dy_dtype, {
+    if (table_fp32)
+      embedding_bwd_kernel<T, float><<<segments, 128, 0, stream>>>(seg_ids, seg_start, order,
+                                                                   static_cast<const T*>(dy), D,
+                                                                   static_cast<float*>(dtable), ldw);
+    else
+      embedding_bwd_kernel<T, T><<<segments, 128, 0, stream>>>(seg_ids, seg_start, order, static_cast<const T*>(dy), D,
+                                                               static_cast<T*>(dtable), ldw);
+  });
+}
+
+void adamw_step(void* p, int p_dtype, float* master, const void* g, int g_dtype, float* m, float* v, long long n,
+                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                cudaStream_t stream) {
+  if (n <= 0) return;
+  const int threads = 256;
+  const int grid = grid_for(n, threads);
+  RLK_DISPATCH_T(p_dtype, {
+    using TP = T;
+    RLK_DISPATCH_T(g_dtype, {
+      adamw_kernel<TP, T><<<grid, threads, 0, stream>>>(static_cast<TP*>(p), master, static_cast<const T*>(g), m, v, n,
+                                                        lr, b1, b2, eps, wd, bc1, bc2, grad_scale);
+    });
+  });
+}
+
+}  // namespace rlk

@@ -1,0 +1,619 @@
+// Python bindings (module rl_engine._C).  This is the only translation unit that sees torch; it
+// validates tensors, allocates outputs on the caller's device and launches on the current stream.
+// Reference counterpart: csrc/ops.cpp:1-99 (pybind of 11-13 functions, launches on the default stream).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <atomic>
+#include <optional>
+#include <vector>
+
+#include "kernels/kernels.h"
+#include "runtime/runtime.h"
+
+namespace {
+
+using torch::Tensor;
+std::atomic<long long> g_launches{0};
+
+int dtype_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case torch::kFloat32: return 0;
+    case torch::kBFloat16: return 1;
+    case torch::kFloat16: return 2;
+    default: TORCH_CHECK(false, "rl_engine: unsupported dtype ", t.scalar_type(), " (float32, bfloat16, float16 only)");
+  }
+}
+
+void check_cuda(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), "rl_engine: ", name, " must be a CUDA tensor");
+}
+void check_rowmajor(const Tensor& t, const char* name) {
+  check_cuda(t, name);
+  TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, "rl_engine: ", name, " must be 2-D with unit inner stride");
+}
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+// One 4-word error record per device, allocated on first use.
+Tensor& error_word(int device) {
+  static std::vector<Tensor> words(64);
+  if (!words[device].defined()) {
+    words[device] = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+  }
+  return words[device];
+}
+uint32_t* err_ptr(const Tensor& like) { return reinterpret_cast<uint32_t*>(error_word(like.get_device()).data_ptr<int>()); }
+
+int sm_count_of(int device) {
+  static std::vector<int> cache(64, 0);
+  if (cache[device] == 0) cache[device] = at::cuda::getDeviceProperties(device)->multiProcessorCount;
+  return cache[device];
+}
+
+void after_launch(int n = 1) {
+  g_launches += n;
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------ GEMM
+Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optional<Tensor> out, bool out_fp32,
+            bool accumulate, double alpha) {
+  check_rowmajor(a, "a");
+  check_rowmajor(b, "b");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "rl_engine.gemm: bf16 operands only");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_mn ? a.size(1) : a.size(0);
+  const int64_t K = a_mn ? a.size(0) : a.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "rl_engine.gemm: contraction sizes differ (", K, " vs ", Kb, ")");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "rl_engine.gemm: operand row pitch must be a multiple of 8 elements");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
+              "rl_engine.gemm: operands must be 16-byte aligned");
+  Tensor d;
+  if (out.has_value()) {
+    d = *out;
+    check_rowmajor(d, "out");
+    TORCH_CHECK(d.size(0) == M && d.size(1) == N, "rl_engine.gemm: out has the wrong shape");
+    TORCH_CHECK(d.scalar_type() == (out_fp32 ? torch::kFloat32 : torch::kBFloat16), "rl_engine.gemm: out dtype mismatch");
+  } else {
+    TORCH_CHECK(!accumulate, "rl_engine.gemm: accumulate needs an explicit out tensor");
+    d = torch::empty({M, N}, a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16));
+  }
+  if (M == 0 || N == 0) return d;
+  if (K == 0) {
+    if (!accumulate) d.zero_();
+    return d;
+  }
+  rlk::GemmArgs g;
+  g.A = reinterpret_cast<const __nv_bfloat16*>(a.data_ptr());
+  g.B = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+  g.D = d.data_ptr();
+  g.M = static_cast<int>(M);
+  g.N = static_cast<int>(N);
+  g.K = static_cast<int>(K);
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  g.ldd = d.stride(0);
+  g.a_mn_major = a_mn;
+  g.b_mn_major = b_mn;
+  g.out_fp32 = out_fp32;
+  g.accumulate = accumulate;
+  g.alpha = static_cast<float>(alpha);
+  g.sm_count = sm_count_of(a.get_device());
+  g.err = err_ptr(a);
+  rlk::gemm_bf16(g, stream_of(a));
+  after_launch();
+  return d;
+}
+
+// ------------------------------------------------------------------------- linear -> logprob
+std::vector<int64_t> linear_logp_workspace_shape(int64_t n_tokens, int64_t v_local, int64_t world) {
+  int items = 0, n_pad = 0, tiles_m = 0;
+  rlk::linear_logp_workspace_shape(static_cast<int>(n_tokens), static_cast<int>(v_local), static_cast<int>(world), &items,
+                                   &n_pad, &tiles_m);
+  return {items, n_pad, tiles_m};
+}
+
+std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, const Tensor& target,
+                                    std::optional<Tensor> bias, int64_t vocab_start, int64_t rank, int64_t world,
+                                    std::vector<int64_t> peer_partials, std::vector<int64_t> peer_counters,
+                                    int64_t next_counters, bool want_lse, bool want_entropy, double wait_limit_ms) {
+  check_rowmajor(hidden, "hidden");
+  check_rowmajor(weight, "weight");
+  check_cuda(target, "target");
+  TORCH_CHECK(hidden.scalar_type() == torch::kBFloat16 && weight.scalar_type() == torch::kBFloat16,
+              "rl_engine.linear_logp: bf16 hidden and weight only");
+  TORCH_CHECK(target.scalar_type() == torch::kInt64 && target.is_contiguous() && target.numel() == hidden.size(0),
+              "rl_engine.linear_logp: target must be contiguous int64 [N]");
+  TORCH_CHECK(hidden.size(1) == weight.size(1), "rl_engine.linear_logp: hidden dim mismatch");
+  TORCH_CHECK(hidden.stride(0) % 8 == 0 && weight.stride(0) % 8 == 0, "rl_engine.linear_logp: row pitch must be a multiple of 8");
+  TORCH_CHECK(world >= 1 && world <= 8 && rank >= 0 && rank < world, "rl_engine.linear_logp: bad rank/world");
+  TORCH_CHECK(static_cast<int64_t>(peer_partials.size()) == world && static_cast<int64_t>(peer_counters.size()) == world,
+              "rl_engine.linear_logp: need one partial buffer and one counter array per rank");
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  const int64_t n = hidden.size(0);
+  auto fopt = hidden.options().dtype(torch::kFloat32);
+  Tensor logp = torch::empty({n}, fopt);
+  Tensor lse = want_lse ? torch::empty({n}, fopt) : Tensor();
+  Tensor ent = want_entropy ? torch::empty({n}, fopt) : Tensor();
+  Tensor bias_f;
+  if (bias.has_value() && bias->defined()) {
+    bias_f = bias->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(bias_f.numel() == weight.size(0), "rl_engine.linear_logp: bias must have V_local elements");
+  }
+  if (n == 0) return {logp, lse, ent};
+  rlk::LinearLogpFwdArgs a{};
+  a.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden.data_ptr());
+  a.weight = reinterpret_cast<const __nv_bfloat16*>(weight.data_ptr());
+  a.target = target.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(target.data_ptr<int64_t>()) : nullptr;
+  a.bias = bias_f.defined() ? bias_f.data_ptr<float>() : nullptr;
+  a.n_tokens = static_cast<int>(n);
+  a.hidden_dim = static_cast<int>(hidden.size(1));
+  a.v_local = static_cast<int>(weight.size(0));
+  a.ld_hidden = hidden.stride(0);
+  a.ld_weight = weight.stride(0);
+  a.vocab_start = vocab_start;
+  a.rank = static_cast<int>(rank);
+  a.world = static_cast<int>(world);
+  for (int r = 0; r < world; ++r) {
+    a.peer_partials[r] = reinterpret_cast<void*>(peer_partials[r]);
+    a.peer_counters[r] = reinterpret_cast<unsigned int*>(peer_counters[r]);
+  }
+  a.next_counters = reinterpret_cast<unsigned int*>(next_counters);
+  a.logp = logp.data_ptr<float>();
+  a.lse = want_lse ? lse.data_ptr<float>() : nullptr;
+  a.entropy = want_entropy ? ent.data_ptr<float>() : nullptr;
+  a.sm_count = sm_count_of(hidden.get_device());
+  a.err = err_ptr(hidden);
+  a.wait_limit_ns = static_cast<unsigned long long>(wait_limit_ms * 1e6);
+  rlk::linear_logp_forward(a, stream_of(hidden));
+  after_launch();
+  return {logp, lse, ent};
+}
+
+void linear_logp_dz(const Tensor& hidden, const Tensor& weight, const Tensor& target, std::optional<Tensor> bias,
+                    const Tensor& lse, const Tensor& grad, int64_t vocab_start, Tensor dz) {
+  check_rowmajor(hidden, "hidden");
+  check_rowmajor(weight, "weight");
+  check_rowmajor(dz, "dz");
+  TORCH_CHECK(dz.scalar_type() == torch::kBFloat16 && dz.size(0) >= hidden.size(0) && dz.size(1) == weight.size(0),
+              "rl_engine.linear_logp_dz: dz must be bf16 [>=N, V_local]");
+  TORCH_CHECK(dz.stride(0) % 8 == 0, "rl_engine.linear_logp_dz: dz row pitch must be a multiple of 8");
+  TORCH_CHECK(lse.scalar_type() == torch::kFloat32 && grad.scalar_type() == torch::kFloat32 && lse.is_contiguous() &&
+                  grad.is_contiguous(),
+              "rl_engine.linear_logp_dz: lse and grad must be contiguous float32");
+  TORCH_CHECK(target.scalar_type() == torch::kInt64 && target.is_contiguous(), "target must be contiguous int64");
+  const c10::cuda::CUDAGuard guard(hidden.device());
+  if (hidden.size(0) == 0) return;
+  Tensor bias_f;
+  if (bias.has_value() && bias->defined()) bias_f = bias->to(torch::kFloat32).contiguous();
+  rlk::LinearLogpDzArgs a{};
+  a.hidden = reinterpret_cast<const __nv_bfloat16*>(hidden.data_ptr());
+  a.weight = reinterpret_cast<const __nv_bfloat16*>(weight.data_ptr());
+  a.target = reinterpret_cast<const long long*>(target.data_ptr<int64_t>());
+  a.bias = bias_f.defined() ? bias_f.data_ptr<float>() : nullptr;
+  a.lse = lse.data_ptr<float>();
+  a.grad = grad.data_ptr<float>();
+  a.n_tokens = static_cast<int>(hidden.size(0));
+  a.hidden_dim = static_cast<int>(hidden.size(1));
+  a.v_local = static_cast<int>(weight.size(0));
+  a.ld_hidden = hidden.stride(0);
+  a.ld_weight = weight.stride(0);
+  a.vocab_start = vocab_start;
+  a.dz = reinterpret_cast<__nv_bfloat16*>(dz.data_ptr());
+  a.ld_dz = dz.stride(0);
+  a.sm_count = sm_count_of(hidden.get_device());
+  a.err = err_ptr(hidden);
+  rlk::linear_logp_dz(a, stream_of(hidden));
+  after_launch();
+}
+
+// --------------------------------------------------------------------------- logp over logits
+void logp_rows(const Tensor& logits, const Tensor& ids, std::optional<Tensor> row_indices, Tensor out) {
+  check_rowmajor(logits, "logits");
+  check_cuda(out, "out");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.numel() == logits.size(0),
+              "rl_engine.logp_rows: ids must be contiguous int64 [rows]");
+  TORCH_CHECK(out.is_contiguous() && out.numel() == logits.size(0), "rl_engine.logp_rows: out must be contiguous [rows]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  rlk::LogpRowsArgs a{};
+  a.logits = logits.data_ptr();
+  a.ld = logits.stride(0);
+  a.in_dtype = dtype_code(logits);
+  a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
+  a.row_indices = nullptr;
+  a.launch_rows = static_cast<int>(logits.size(0));
+  if (row_indices.has_value() && row_indices->defined()) {
+    TORCH_CHECK(row_indices->is_cuda() && row_indices->scalar_type() == torch::kInt64 && row_indices->is_contiguous(),
+                "rl_engine.logp_rows: row_indices must be contiguous int64 on the GPU");
+    a.row_indices = reinterpret_cast<const long long*>(row_indices->data_ptr<int64_t>());
+    a.launch_rows = static_cast<int>(row_indices->numel());
+  }
+  a.V = static_cast<int>(logits.size(1));
+  a.out = out.data_ptr();
+  a.out_dtype = dtype_code(out);
+  if (a.launch_rows == 0) return;
+  rlk::logp_rows(a, stream_of(logits));
+  after_launch();
+}
+
+std::vector<Tensor> ratio_kl_fwd(const Tensor& policy, const Tensor& ref, const Tensor& ids, const Tensor& mask,
+                                 const Tensor& old_logp) {
+  check_rowmajor(policy, "policy_logits");
+  check_rowmajor(ref, "ref_logits");
+  TORCH_CHECK(policy.scalar_type() == ref.scalar_type() && policy.sizes() == ref.sizes(), "policy/ref logits must match");
+  const int64_t rows = policy.size(0);
+  TORCH_CHECK(ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && ids.numel() == rows, "ids: int64 [rows]");
+  TORCH_CHECK(mask.scalar_type() == torch::kBool && mask.is_contiguous() && mask.numel() == rows, "mask: bool [rows]");
+  TORCH_CHECK(old_logp.scalar_type() == torch::kFloat32 && old_logp.is_contiguous() && old_logp.numel() == rows,
+              "old_logps: float32 [rows]");
+  const c10::cuda::CUDAGuard guard(policy.device());
+  auto fopt = policy.options().dtype(torch::kFloat32);
+  Tensor ratio = torch::empty({rows}, fopt), kl = torch::empty({rows}, fopt), d = torch::empty({rows}, fopt),
+         lse = torch::empty({rows}, fopt);
+  Tensor bad = torch::zeros({1}, policy.options().dtype(torch::kInt32));
+  rlk::RatioKlFwdArgs a{};
+  a.policy = policy.data_ptr();
+  a.ref = ref.data_ptr();
+  a.ld_policy = policy.stride(0);
+  a.ld_ref = ref.stride(0);
+  a.dtype = dtype_code(policy);
+  a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
+  a.mask = reinterpret_cast<const unsigned char*>(mask.data_ptr<bool>());
+  a.old_logp = old_logp.data_ptr<float>();
+  a.rows = static_cast<int>(rows);
+  a.V = static_cast<int>(policy.size(1));
+  a.ratio = ratio.data_ptr<float>();
+  a.kl = kl.data_ptr<float>();
+  a.save_d = d.data_ptr<float>();
+  a.save_lse = lse.data_ptr<float>();
+  a.bad_id_flag = reinterpret_cast<unsigned int*>(bad.data_ptr<int>());
+  if (rows) {
+    rlk::ratio_kl_forward(a, stream_of(policy));
+    after_launch();
+  }
+  return {ratio, kl, d, lse, bad};
+}
+
+Tensor ratio_kl_bwd(const Tensor& policy, const Tensor& ids, const Tensor& mask, const Tensor& g_ratio,
+                    const Tensor& g_kl, const Tensor& ratio, const Tensor& d, const Tensor& lse) {
+  check_rowmajor(policy, "policy_logits");
+  const c10::cuda::CUDAGuard guard(policy.device());
+  Tensor grad = torch::empty({policy.size(0), policy.size(1)}, policy.options());
+  rlk::RatioKlBwdArgs a{};
+  a.policy = policy.data_ptr();
+  a.ld_policy = policy.stride(0);
+  a.dtype = dtype_code(policy);
+  a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
+  a.mask = reinterpret_cast<const unsigned char*>(mask.data_ptr<bool>());
+  Tensor gr = g_ratio.to(torch::kFloat32).contiguous(), gk = g_kl.to(torch::kFloat32).contiguous();
+  a.g_ratio = gr.data_ptr<float>();
+  a.g_kl = gk.data_ptr<float>();
+  a.ratio = ratio.data_ptr<float>();
+  a.save_d = d.data_ptr<float>();
+  a.save_lse = lse.data_ptr<float>();
+  a.rows = static_cast<int>(policy.size(0));
+  a.V = static_cast<int>(policy.size(1));
+  a.grad = grad.data_ptr();
+  a.ld_grad = grad.stride(0);
+  if (a.rows) {
+    rlk::ratio_kl_backward(a, stream_of(policy));
+    after_launch();
+  }
+  return grad;
+}
+
+// ------------------------------------------------------------------------------- RL losses
+Tensor group_advantages(const Tensor& rewards, std::optional<Tensor> bounds, int64_t uniform, double eps) {
+  check_cuda(rewards, "rewards");
+  TORCH_CHECK(rewards.scalar_type() == torch::kFloat32 && rewards.is_contiguous(), "rewards: contiguous float32");
+  const c10::cuda::CUDAGuard guard(rewards.device());
+  Tensor adv = torch::empty_like(rewards);
+  const long long* bptr = nullptr;
+  int64_t groups = 0;
+  if (bounds.has_value() && bounds->defined()) {
+    TORCH_CHECK(bounds->is_cuda() && bounds->scalar_type() == torch::kInt64 && bounds->is_contiguous(), "bounds: int64 GPU");
+    bptr = reinterpret_cast<const long long*>(bounds->data_ptr<int64_t>());
+    groups = bounds->numel() - 1;
+  } else {
+    TORCH_CHECK(uniform > 0 && rewards.numel() % uniform == 0, "uniform group size must divide the number of rewards");
+    groups = rewards.numel() / uniform;
+  }
+  if (groups > 0) {
+    rlk::group_advantages(rewards.data_ptr<float>(), bptr, static_cast<int>(groups), uniform, static_cast<float>(eps),
+                          adv.data_ptr<float>(), stream_of(rewards));
+    after_launch();
+  }
+  return adv;
+}
+
+std::vector<Tensor> surrogate_fwd(const Tensor& logp, std::optional<Tensor> ref_logp, const Tensor& old_logp,
+                                  std::optional<Tensor> adv_seq, std::optional<Tensor> adv_tok, const Tensor& mask,
+                                  int64_t T, double clip_eps, double beta, bool want_terms) {
+  check_cuda(logp, "logp");
+  auto f32c = [](const Tensor& t, const char* n) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(), n, ": contiguous float32 on GPU");
+  };
+  f32c(logp, "logp");
+  f32c(old_logp, "old_logps");
+  TORCH_CHECK(mask.is_cuda() && mask.scalar_type() == torch::kBool && mask.is_contiguous() && mask.numel() == logp.numel(),
+              "mask: contiguous bool, same size as logp");
+  const c10::cuda::CUDAGuard guard(logp.device());
+  const int64_t n = logp.numel();
+  auto fopt = logp.options();
+  Tensor d_pl = torch::empty({n}, fopt), d_kl = torch::empty({n}, fopt);
+  Tensor ratio = want_terms ? torch::empty({n}, fopt) : Tensor();
+  Tensor kl = want_terms ? torch::empty({n}, fopt) : Tensor();
+  Tensor partials = torch::empty({rlk::surrogate_partial_floats()}, fopt);
+  Tensor out4 = torch::empty({4}, fopt);
+  rlk::SurrogateFwdArgs a{};
+  a.logp = logp.data_ptr<float>();
+  a.ref_logp = nullptr;
+  if (ref_logp.has_value() && ref_logp->defined()) {
+    f32c(*ref_logp, "ref_logps");
+    a.ref_logp = ref_logp->data_ptr<float>();
+  }
+  a.old_logp = old_logp.data_ptr<float>();
+  a.adv_seq = nullptr;
+  a.adv_tok = nullptr;
+  if (adv_tok.has_value() && adv_tok->defined()) {
+    f32c(*adv_tok, "advantages");
+    TORCH_CHECK(adv_tok->numel() == n, "per-token advantages must match logp");
+    a.adv_tok = adv_tok->data_ptr<float>();
+  } else {
+    TORCH_CHECK(adv_seq.has_value() && adv_seq->defined(), "need per-sequence or per-token advantages");
+    f32c(*adv_seq, "sample_advantages");
+    TORCH_CHECK(T > 0 && adv_seq->numel() * T == n, "per-sequence advantages must have n / T entries");
+    a.adv_seq = adv_seq->data_ptr<float>();
+  }
+  a.mask = reinterpret_cast<const unsigned char*>(mask.data_ptr<bool>());
+  a.n = n;
+  a.T = T > 0 ? T : 1;
+  a.clip_eps = static_cast<float>(clip_eps);
+  a.beta = static_cast<float>(beta);
+  a.d_pl = d_pl.data_ptr<float>();
+  a.d_kl = d_kl.data_ptr<float>();
+  a.ratio_out = want_terms ? ratio.data_ptr<float>() : nullptr;
+  a.kl_out = want_terms ? kl.data_ptr<float>() : nullptr;
+  a.partials = partials.data_ptr<float>();
+  a.out4 = out4.data_ptr<float>();
+  rlk::surrogate_forward(a, stream_of(logp));
+  after_launch(2);
+  return {out4, d_pl, d_kl, ratio, kl};
+}
+
+Tensor surrogate_bwd(const Tensor& d_pl, const Tensor& d_kl, const Tensor& out4, const Tensor& g3, double beta) {
+  const c10::cuda::CUDAGuard guard(d_pl.device());
+  Tensor grad = torch::empty_like(d_pl);
+  Tensor g = g3.to(torch::kFloat32).contiguous();
+  rlk::surrogate_backward(d_pl.data_ptr<float>(), d_kl.data_ptr<float>(), out4.data_ptr<float>(), g.data_ptr<float>(),
+                          static_cast<float>(beta), d_pl.numel(), grad.data_ptr<float>(), stream_of(d_pl));
+  after_launch();
+  return grad;
+}
+
+std::vector<Tensor> dpo_fwd(const Tensor& pc, const Tensor& pr, const Tensor& rc, const Tensor& rr, double beta,
+                            double label_smoothing) {
+  const c10::cuda::CUDAGuard guard(pc.device());
+  auto prep = [](const Tensor& t) { return t.to(torch::kFloat32).contiguous().view({-1}); };
+  Tensor a = prep(pc), b = prep(pr), c = prep(rc), d = prep(rr);
+  const int64_t n = a.numel();
+  TORCH_CHECK(b.numel() == n && c.numel() == n && d.numel() == n, "dpo: all four log-prob vectors must match");
+  Tensor loss = torch::zeros({1}, a.options()), cr = torch::empty({n}, a.options()), rj = torch::empty({n}, a.options()),
+         dh = torch::empty({n}, a.options());
+  rlk::dpo_forward(a.data_ptr<float>(), b.data_ptr<float>(), c.data_ptr<float>(), d.data_ptr<float>(),
+                   static_cast<int>(n), static_cast<float>(beta), static_cast<float>(label_smoothing),
+                   loss.data_ptr<float>(), cr.data_ptr<float>(), rj.data_ptr<float>(), dh.data_ptr<float>(), stream_of(a));
+  after_launch();
+  return {loss, cr, rj, dh};
+}
+
+// ------------------------------------------------------------------------------ model ops
+std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps, bool out_fp32, bool save_rstd) {
+  check_rowmajor(x, "x");
+  TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.numel() == x.size(1), "weight must be contiguous [D]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty({x.size(0), x.size(1)}, x.options().dtype(out_fp32 ? torch::kFloat32 : x.scalar_type()));
+  Tensor rstd = save_rstd ? torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32)) : Tensor();
+  if (x.size(0)) {
+    rlk::rmsnorm_forward(x.data_ptr(), x.stride(0), dtype_code(x), w.data_ptr(), dtype_code(w), y.data_ptr(), y.stride(0),
+                         out_fp32, x.size(0), static_cast<int>(x.size(1)), static_cast<float>(eps),
+                         save_rstd ? rstd.data_ptr<float>() : nullptr, stream_of(x));
+    after_launch();
+  }
+  return {y, rstd};
+}
+
+std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd) {
+  check_rowmajor(x, "x");
+  check_rowmajor(dy, "dy");
+  TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "dy dtype must match x");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), D = x.size(1);
+  Tensor dx = torch::empty({rows, D}, x.options());
+  Tensor dw = torch::zeros({D}, w.options());
+  if (rows) {
+    Tensor part = torch::empty({rlk::rmsnorm_bwd_chunks(rows), D}, x.options().dtype(torch::kFloat32));
+    rlk::rmsnorm_backward(x.data_ptr(), x.stride(0), dtype_code(x), w.data_ptr(), dtype_code(w), dy.data_ptr(),
+                          dy.stride(0), rstd.data_ptr<float>(), dx.data_ptr(), dx.stride(0), rows, static_cast<int>(D),
+                          part.data_ptr<float>(), dw.data_ptr(), stream_of(x));
+    after_launch(2);
+  }
+  return {dx, dw};
+}
+
+Tensor swiglu_fwd(const Tensor& gate, std::optional<Tensor> up, bool out_fp32) {
+  check_rowmajor(gate, "gate");
+  const c10::cuda::CUDAGuard guard(gate.device());
+  const bool has_up = up.has_value() && up->defined();
+  if (has_up) {
+    check_rowmajor(*up, "up");
+    TORCH_CHECK(up->sizes() == gate.sizes() && up->scalar_type() == gate.scalar_type(), "gate/up must match");
+  }
+  Tensor out = torch::empty({gate.size(0), gate.size(1)}, gate.options().dtype(out_fp32 ? torch::kFloat32 : gate.scalar_type()));
+  if (gate.numel()) {
+    rlk::swiglu_forward(gate.data_ptr(), gate.stride(0), has_up ? up->data_ptr() : nullptr, has_up ? up->stride(0) : 0,
+                        dtype_code(gate), out.data_ptr(), out.stride(0), out_fp32, gate.size(0),
+                        static_cast<int>(gate.size(1)), stream_of(gate));
+    after_launch();
+  }
+  return out;
+}
+
+std::vector<Tensor> swiglu_bwd(const Tensor& gate, std::optional<Tensor> up, const Tensor& dy) {
+  check_rowmajor(gate, "gate");
+  check_rowmajor(dy, "dy");
+  TORCH_CHECK(dy.scalar_type() == gate.scalar_type(), "dy dtype must match gate");
+  const c10::cuda::CUDAGuard guard(gate.device());
+  const bool has_up = up.has_value() && up->defined();
+  Tensor dg = torch::empty({gate.size(0), gate.size(1)}, gate.options());
+  Tensor du = has_up ? torch::empty({gate.size(0), gate.size(1)}, gate.options()) : Tensor();
+  if (gate.numel()) {
+    rlk::swiglu_backward(gate.data_ptr(), gate.stride(0), has_up ? up->data_ptr() : nullptr, has_up ? up->stride(0) : 0,
+                         dy.data_ptr(), dy.stride(0), dtype_code(gate), dg.data_ptr(), dg.stride(0),
+                         has_up ? du.data_ptr() : nullptr, has_up ? du.stride(0) : 0, gate.size(0),
+                         static_cast<int>(gate.size(1)), stream_of(gate));
+    after_launch();
+  }
+  return {dg, du};
+}
+
+// x: [tokens, heads, D] with unit stride on D and stride D on heads
+Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const Tensor& sin_t, bool inverse) {
+  check_cuda(x, "x");
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [tokens, heads, D] with packed heads");
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == torch::kInt64 && positions.is_contiguous() &&
+                  positions.numel() == x.size(0),
+              "rope: positions must be contiguous int64 [tokens]");
+  TORCH_CHECK(cos_t.scalar_type() == torch::kFloat32 && sin_t.scalar_type() == torch::kFloat32 && cos_t.is_contiguous() &&
+                  sin_t.is_contiguous() && cos_t.size(-1) == x.size(2) / 2,
+              "rope: cos/sin tables must be contiguous float32 [max_pos, D/2]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  if (x.numel()) {
+    rlk::rope_apply(x.data_ptr(), x.stride(0), dtype_code(x), reinterpret_cast<const long long*>(positions.data_ptr<int64_t>()),
+                    cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), out.data_ptr(), out.stride(0), x.size(0),
+                    static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), inverse, stream_of(x));
+    after_launch();
+  }
+  return out;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
+  check_rowmajor(table, "weight");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 GPU");
+  const c10::cuda::CUDAGuard guard(table.device());
+  Tensor out = torch::empty({ids.numel(), table.size(1)}, table.options());
+  if (ids.numel()) {
+    rlk::embedding_forward(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), table.data_ptr(), table.stride(0),
+                           dtype_code(table), out.data_ptr(), ids.numel(), static_cast<int>(table.size(1)), table.size(0),
+                           stream_of(table));
+    after_launch();
+  }
+  return out;
+}
+
+// seg_ids [S], seg_start [S+1], order [tokens]: tokens stably sorted by id and run-length encoded.
+void embedding_bwd(const Tensor& seg_ids, const Tensor& seg_start, const Tensor& order, const Tensor& dy, Tensor dtable) {
+  check_rowmajor(dy, "dy");
+  check_rowmajor(dtable, "dtable");
+  TORCH_CHECK(dy.is_contiguous(), "dy must be contiguous");
+  const c10::cuda::CUDAGuard guard(dy.device());
+  const int64_t segs = seg_ids.numel();
+  if (segs == 0) return;
+  const bool tfp32 = dtable.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(tfp32 || dtable.scalar_type() == dy.scalar_type(), "dtable must be float32 or match dy");
+  rlk::embedding_backward(reinterpret_cast<const long long*>(seg_ids.data_ptr<int64_t>()),
+                          reinterpret_cast<const long long*>(seg_start.data_ptr<int64_t>()), segs,
+                          reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), dy.data_ptr(), dtype_code(dy),
+                          static_cast<int>(dy.size(1)), dtable.data_ptr(), tfp32, dtable.stride(0), stream_of(dy));
+  after_launch();
+}
+
+void adamw(Tensor p, std::optional<Tensor> master, const Tensor& g, Tensor m, Tensor v, double lr, double b1, double b2,
+           double eps, double wd, int64_t step, double grad_scale) {
+  check_cuda(p, "param");
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous tensors");
+  TORCH_CHECK(m.scalar_type() == torch::kFloat32 && v.scalar_type() == torch::kFloat32, "adamw: fp32 moments");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw: size mismatch");
+  const c10::cuda::CUDAGuard guard(p.device());
+  float* mp = nullptr;
+  if (master.has_value() && master->defined()) {
+    TORCH_CHECK(master->scalar_type() == torch::kFloat32 && master->is_contiguous() && master->numel() == p.numel(),
+                "adamw: master must be contiguous float32");
+    mp = master->data_ptr<float>();
+  }
+  const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
+  if (p.numel()) {
+    rlk::adamw_step(p.data_ptr(), dtype_code(p), mp, g.data_ptr(), dtype_code(g), m.data_ptr<float>(), v.data_ptr<float>(),
+                    p.numel(), static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2),
+                    static_cast<float>(eps), static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), stream_of(p));
+    after_launch();
+  }
+}
+
+// ---------------------------------------------------------------------------------- sampler
+std::vector<Tensor> sample(const Tensor& logits, int64_t top_k, double top_p, double temperature, int64_t seed,
+                           int64_t offset, bool want_logprob) {
+  check_rowmajor(logits, "logits");
+  TORCH_CHECK(top_k >= 1 && top_k <= rlk::sample_topk_limit(), "rl_engine.sample: top_k must be in [1, ",
+              rlk::sample_topk_limit(), "]");
+  TORCH_CHECK(top_p > 0.0 && top_p <= 1.0, "rl_engine.sample: top_p must be in (0, 1]");
+  TORCH_CHECK(temperature > 0.0, "rl_engine.sample: temperature must be positive");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  Tensor ids = torch::empty({logits.size(0)}, logits.options().dtype(torch::kInt64));
+  Tensor lp = want_logprob ? torch::empty({logits.size(0)}, logits.options().dtype(torch::kFloat32)) : Tensor();
+  if (logits.size(0)) {
+    rlk::sample_topk_topp(logits.data_ptr(), logits.stride(0), dtype_code(logits), static_cast<int>(logits.size(0)),
+                          static_cast<int>(logits.size(1)), static_cast<int>(top_k), static_cast<float>(top_p),
+                          static_cast<float>(temperature), static_cast<unsigned long long>(seed),
+                          static_cast<unsigned long long>(offset), reinterpret_cast<long long*>(ids.data_ptr<int64_t>()),
+                          want_logprob ? lp.data_ptr<float>() : nullptr, stream_of(logits));
+    after_launch();
+  }
+  return {ids, lp};
+}
+
+// ------------------------------------------------------------------------------ diagnostics
+std::vector<int64_t> error_state(int64_t device) {
+  Tensor w = error_word(static_cast<int>(device)).cpu();
+  auto a = w.accessor<int, 1>();
+  return {a[0], a[1], a[2], a[3]};
+}
+void reset_error(int64_t device) { error_word(static_cast<int>(device)).zero_(); }
+long long launch_count() { return g_launches.load(); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "rl_engine native sm_100a kernels";
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0);
+  m.def("linear_logp_workspace_shape", &linear_logp_workspace_shape);
+  m.def("linear_logp_fwd", &linear_logp_fwd);
+  m.def("linear_logp_dz", &linear_logp_dz);
+  m.def("logp_rows", &logp_rows);
+  m.def("ratio_kl_fwd", &ratio_kl_fwd);
+  m.def("ratio_kl_bwd", &ratio_kl_bwd);
+  m.def("group_advantages", &group_advantages);
+  m.def("surrogate_fwd", &surrogate_fwd);
+  m.def("surrogate_bwd", &surrogate_bwd);
+  m.def("dpo_fwd", &dpo_fwd);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope", &rope);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
+  m.def("adamw", &adamw);
+  m.def("sample", &sample);
+  m.def("error_state", &error_state);
+  m.def("reset_error", &reset_error);
+  m.def("launch_count", &launch_count);
+  rlk::bind_runtime(m);
+}

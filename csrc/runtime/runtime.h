@@ -1,0 +1,8 @@
+// C++ runtime pieces exposed to Python next to the kernels (symmetric heap, peer signals).
+#pragma once
+
+#include <pybind11/pybind11.h>
+
+namespace rlk {
+void bind_runtime(pybind11::module_& m);
+}
