@@ -16,7 +16,18 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Driver-API calls need the primary context bound to the calling thread.  Threads that have only been
+// handed a device index (e.g. autograd worker threads) may not have it yet; a runtime call binds it.
+inline void bind_primary_context() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 inline EncodeTiledFn encode_tiled_fn() {
+  bind_primary_context();
   static EncodeTiledFn fn = [] {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;

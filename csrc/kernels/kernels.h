@@ -41,6 +41,7 @@ struct LinearLogpFwdArgs {
   void* peer_partials[8];          // per rank: float4 [world * items_per_m, n_pad]
   unsigned int* peer_counters[8];  // per rank: [tiles_m] counters of the set used by this launch
   unsigned int* next_counters;     // local: the set the next launch will use (zeroed here)
+  int counter_capacity;            // entries per counter set
   float* logp;
   float* lse;
   float* entropy;
@@ -90,7 +91,7 @@ void logp_rows(const LogpRowsArgs& args, cudaStream_t stream);
 
 struct RatioKlFwdArgs {
   const void* policy;
-  const void* ref;
+  const void* ref;  // null: reference == policy
   long long ld_policy, ld_ref;
   int dtype;
   const long long* ids;
@@ -101,6 +102,7 @@ struct RatioKlFwdArgs {
   float* kl;
   float* save_d;
   float* save_lse;
+  float* save_lp;  // policy log-prob of the selected token
   unsigned int* bad_id_flag;
 };
 void ratio_kl_forward(const RatioKlFwdArgs& args, cudaStream_t stream);

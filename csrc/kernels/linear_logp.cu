@@ -33,6 +33,7 @@ struct LogpFwdParams {
   float4* peer_partials[kMaxWorld];   // each: [world * items_per_m, n_pad] records (m2, s, t, zt)
   unsigned int* peer_counters[kMaxWorld];  // each: [tiles_m] arrival counters of the current set
   unsigned int* next_counters;        // local counters of the other set, zeroed by this launch
+  int counter_capacity;
   float* logp;     // [N]
   float* lse;      // [N] or null
   float* entropy;  // [N] or null
@@ -130,7 +131,7 @@ __device__ void logp_merge_phase(const LogpFwdParams& ep, const GemmProblem& p, 
   const unsigned int* counters = ep.peer_counters[ep.rank];
   const float4* parts = ep.peer_partials[ep.rank];
   // zero the other counter set for the next launch (see host side for why this is race free)
-  for (int t = blockIdx.x * 128 + tid; t < p.tiles_m; t += gridDim.x * 128) ep.next_counters[t] = 0u;
+  for (int t = blockIdx.x * 128 + tid; t < ep.counter_capacity; t += gridDim.x * 128) ep.next_counters[t] = 0u;
   for (int t = blockIdx.x; t < p.tiles_m; t += gridDim.x) {
     // bounded wait for all records of row tile t
     unsigned int seen = 0;
@@ -294,6 +295,7 @@ void linear_logp_forward(const LinearLogpFwdArgs& a, cudaStream_t stream) {
     ep.peer_counters[r] = r < a.world ? a.peer_counters[r] : nullptr;
   }
   ep.next_counters = a.next_counters;
+  ep.counter_capacity = a.counter_capacity;
   ep.logp = a.logp;
   ep.lse = a.lse;
   ep.entropy = a.entropy;

@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kThreads) ratio_kl_fwd_kernel(const T* __restr
                                                                 const float* __restrict__ old_logp, int V,
                                                                 float* __restrict__ ratio, float* __restrict__ kl,
                                                                 float* __restrict__ save_d, float* __restrict__ save_lse,
+                                                                float* __restrict__ save_lp,
                                                                 unsigned int* __restrict__ bad_id_flag) {
   __shared__ MS red[kThreads / 32];
   const long long row = blockIdx.x;
@@ -169,13 +170,15 @@ __global__ void __launch_bounds__(kThreads) ratio_kl_fwd_kernel(const T* __restr
       kl[row] = 0.f;
       save_d[row] = 0.f;
       save_lse[row] = 0.f;
+      save_lp[row] = 0.f;
     }
     return;
   }
   const T* prow = pol + row * ld_p;
-  const T* rrow = ref + row * ld_r;
+  const T* rrow = ref ? ref + row * ld_r : nullptr;  // null: reference == policy (d = 0, kl = 0)
   MS a = block_merge(stream_row(prow, V), red);
-  MS b = block_merge(stream_row(rrow, V), red);
+  MS b = a;
+  if (rrow) b = block_merge(stream_row(rrow, V), red);
   if (threadIdx.x == 0) {
     long long t = ids[row];
     if (t < 0 || t >= V) {
@@ -185,12 +188,13 @@ __global__ void __launch_bounds__(kThreads) ratio_kl_fwd_kernel(const T* __restr
     const float lse_p = (a.m2 + log2f(a.s)) * kLn2;
     const float lse_r = (b.m2 + log2f(b.s)) * kLn2;
     const float lp = to_f(prow[t]) - lse_p;
-    const float lr = to_f(rrow[t]) - lse_r;
+    const float lr = rrow ? to_f(rrow[t]) - lse_r : lp;
     const float d = lr - lp;
     ratio[row] = expf(lp - old_logp[row]);
     kl[row] = expf(d) - d - 1.f;
     save_d[row] = d;
     save_lse[row] = lse_p;
+    save_lp[row] = lp;
   }
 }
 
@@ -231,7 +235,7 @@ void ratio_kl_forward(const RatioKlFwdArgs& a, cudaStream_t stream) {
 #define RLK_LAUNCH(T)                                                                                          \
   ratio_kl_fwd_kernel<T><<<a.rows, kThreads, 0, stream>>>(static_cast<const T*>(a.policy), static_cast<const T*>(a.ref), \
                                                           a.ld_policy, a.ld_ref, a.ids, a.mask, a.old_logp, a.V,      \
-                                                          a.ratio, a.kl, a.save_d, a.save_lse, a.bad_id_flag)
+                                                          a.ratio, a.kl, a.save_d, a.save_lse, a.save_lp, a.bad_id_flag)
   if (a.dtype == 0) RLK_LAUNCH(float);
   else if (a.dtype == 1) RLK_LAUNCH(__nv_bfloat16);
   else RLK_LAUNCH(__half);

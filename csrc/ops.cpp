@@ -120,7 +120,8 @@ std::vector<int64_t> linear_logp_workspace_shape(int64_t n_tokens, int64_t v_loc
 std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, const Tensor& target,
                                     std::optional<Tensor> bias, int64_t vocab_start, int64_t rank, int64_t world,
                                     std::vector<int64_t> peer_partials, std::vector<int64_t> peer_counters,
-                                    int64_t next_counters, bool want_lse, bool want_entropy, double wait_limit_ms) {
+                                    int64_t next_counters, int64_t counter_capacity, bool want_lse,
+                                    bool want_entropy, double wait_limit_ms) {
   check_rowmajor(hidden, "hidden");
   check_rowmajor(weight, "weight");
   check_cuda(target, "target");
@@ -163,6 +164,7 @@ std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, 
     a.peer_counters[r] = reinterpret_cast<unsigned int*>(peer_counters[r]);
   }
   a.next_counters = reinterpret_cast<unsigned int*>(next_counters);
+  a.counter_capacity = static_cast<int>(counter_capacity);
   a.logp = logp.data_ptr<float>();
   a.lse = want_lse ? lse.data_ptr<float>() : nullptr;
   a.entropy = want_entropy ? ent.data_ptr<float>() : nullptr;
@@ -240,9 +242,11 @@ void logp_rows(const Tensor& logits, const Tensor& ids, std::optional<Tensor> ro
   after_launch();
 }
 
-std::vector<Tensor> ratio_kl_fwd(const Tensor& policy, const Tensor& ref, const Tensor& ids, const Tensor& mask,
-                                 const Tensor& old_logp) {
+std::vector<Tensor> ratio_kl_fwd(const Tensor& policy, std::optional<Tensor> ref_opt, const Tensor& ids,
+                                 const Tensor& mask, const Tensor& old_logp) {
   check_rowmajor(policy, "policy_logits");
+  const bool has_ref = ref_opt.has_value() && ref_opt->defined();
+  Tensor ref = has_ref ? *ref_opt : policy;
   check_rowmajor(ref, "ref_logits");
   TORCH_CHECK(policy.scalar_type() == ref.scalar_type() && policy.sizes() == ref.sizes(), "policy/ref logits must match");
   const int64_t rows = policy.size(0);
@@ -253,11 +257,11 @@ std::vector<Tensor> ratio_kl_fwd(const Tensor& policy, const Tensor& ref, const 
   const c10::cuda::CUDAGuard guard(policy.device());
   auto fopt = policy.options().dtype(torch::kFloat32);
   Tensor ratio = torch::empty({rows}, fopt), kl = torch::empty({rows}, fopt), d = torch::empty({rows}, fopt),
-         lse = torch::empty({rows}, fopt);
+         lse = torch::empty({rows}, fopt), lp = torch::empty({rows}, fopt);
   Tensor bad = torch::zeros({1}, policy.options().dtype(torch::kInt32));
   rlk::RatioKlFwdArgs a{};
   a.policy = policy.data_ptr();
-  a.ref = ref.data_ptr();
+  a.ref = has_ref ? ref.data_ptr() : nullptr;
   a.ld_policy = policy.stride(0);
   a.ld_ref = ref.stride(0);
   a.dtype = dtype_code(policy);
@@ -270,12 +274,13 @@ std::vector<Tensor> ratio_kl_fwd(const Tensor& policy, const Tensor& ref, const 
   a.kl = kl.data_ptr<float>();
   a.save_d = d.data_ptr<float>();
   a.save_lse = lse.data_ptr<float>();
+  a.save_lp = lp.data_ptr<float>();
   a.bad_id_flag = reinterpret_cast<unsigned int*>(bad.data_ptr<int>());
   if (rows) {
     rlk::ratio_kl_forward(a, stream_of(policy));
     after_launch();
   }
-  return {ratio, kl, d, lse, bad};
+  return {ratio, kl, d, lse, bad, lp};
 }
 
 Tensor ratio_kl_bwd(const Tensor& policy, const Tensor& ids, const Tensor& mask, const Tensor& g_ratio,

@@ -1,0 +1,349 @@
+"""sm_100a kernels vs plain PyTorch fp32 references (numerics, masks, determinism)."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _gen(seed):
+    return torch.Generator(device=DEV).manual_seed(seed)
+
+
+# ------------------------------------------------------------------------------ logp rows
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("V", [300, 32000, 128256])
+def test_logp_rows_all_methods(dtype, V):
+    from rl_engine.kernels.ops.pytorch.loss.logp import NativeLogpOp
+    from rl_engine.kernels.ops.sm100.logp import FusedLogpSM100Op
+
+    g = _gen(V)
+    logits = (torch.randn(3, 5, V, device=DEV, generator=g) * 3).to(dtype)
+    ids = torch.randint(0, V, (3, 5), device=DEV, generator=g)
+    fused, native = FusedLogpSM100Op(), NativeLogpOp()
+    want32 = native.apply_fp32(logits, ids)
+    tol = 2e-5 if dtype == torch.float32 else 2e-5  # fp32 math on the same quantised inputs
+    assert torch.allclose(fused.apply_fp32(logits, ids), want32, atol=tol, rtol=1e-5)
+    assert fused.apply(logits, ids).dtype == dtype
+    out = torch.full((3, 5), 7.0, device=DEV)
+    rows = torch.tensor([1, 4, 9, 14], device=DEV)
+    fused.indexed_out(logits, ids, rows, out)
+    flat = out.view(-1)
+    assert torch.allclose(flat[rows], want32.view(-1)[rows], atol=tol, rtol=1e-5)
+    untouched = torch.ones(15, dtype=torch.bool, device=DEV)
+    untouched[rows] = False
+    assert bool((flat[untouched] == 7.0).all())
+    idx32 = fused.online_indexed_fp32(logits, ids, rows)
+    assert bool((idx32.view(-1)[untouched] == 0).all())
+    assert torch.equal(fused.apply_fp32(logits, ids), fused.online_fp32(logits, ids))  # bitwise repeatable
+    with pytest.raises(ValueError):
+        fused.indexed_fp32(logits, ids, torch.tensor([15], device=DEV))
+
+
+def test_logp_rows_out_of_range_id_gives_zero():
+    from rl_engine.kernels.ops.sm100.logp import FusedLogpSM100Op
+
+    logits = torch.randn(4, 50, device=DEV)
+    ids = torch.tensor([0, -1, 50, 3], device=DEV)
+    out = FusedLogpSM100Op().apply_fp32(logits, ids)
+    assert out[1] == 0 and out[2] == 0 and out[0] < 0
+
+
+# -------------------------------------------------------------------------- linear_logp
+def _ll_ref(h, w, t, b=None):
+    z = h.float() @ w.float().t()
+    if b is not None:
+        z = z + b.float()
+    lp = torch.log_softmax(z, -1)
+    return lp.gather(-1, t[..., None]).squeeze(-1), -(lp.exp() * lp).sum(-1)
+
+
+@pytest.mark.parametrize("N,D,V", [(96, 128, 500), (40, 80, 300), (300, 256, 9000), (1024, 512, 33000)])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_linear_logp_forward_backward(N, D, V, use_bias):
+    from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
+
+    g = _gen(N + V)
+    h = (torch.randn(N, D, device=DEV, generator=g)).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(V, D, device=DEV, generator=g) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn(V, device=DEV, generator=g) * 0.1).to(torch.bfloat16).requires_grad_(True) if use_bias else None
+    t = torch.randint(0, V, (N,), device=DEV, generator=g)
+    op = FusedLinearLogpSM100Op()
+    lp, ent = op.with_entropy(h, w, t, b)
+    want_lp, want_ent = _ll_ref(h.detach(), w.detach(), t, None if b is None else b.detach())
+    assert torch.allclose(lp, want_lp, atol=2e-3, rtol=1e-3)
+    assert torch.allclose(ent, want_ent, atol=2e-3, rtol=1e-3)
+    gl = torch.randn(N, device=DEV, generator=g)
+    lp.backward(gl)
+    hf = h.detach().float().requires_grad_(True)
+    wf = w.detach().float().requires_grad_(True)
+    bf = None if b is None else b.detach().float().requires_grad_(True)
+    ref_lp, _ = _ll_ref(hf, wf, t, bf)
+    ref_lp.backward(gl)
+    for got, want in ((h.grad, hf.grad), (w.grad, wf.grad)) + (((b.grad, bf.grad),) if use_bias else ()):
+        scale = want.abs().max().item() + 1e-8
+        assert (got.float() - want).abs().max().item() / scale < 2e-2
+
+
+def test_linear_logp_bitwise_deterministic_and_batch_invariant():
+    from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
+
+    g = _gen(7)
+    N, D, V = 700, 256, 20000
+    h = torch.randn(N, D, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(V, D, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    t = torch.randint(0, V, (N,), device=DEV, generator=g)
+    op = FusedLinearLogpSM100Op()
+    a = op(h, w, t)
+    b = op(h, w, t)
+    assert torch.equal(a, b)
+    # a row's value must not depend on which other rows are in the batch (train == rollout layouts)
+    part = op(h[100:357], w, t[100:357])
+    assert torch.equal(part, a[100:357])
+    shaped = op(h.view(7, 100, D), w, t.view(7, 100))
+    assert torch.equal(shaped.view(-1), a)
+    # backward determinism
+    hg = h.clone().requires_grad_(True)
+    wg = w.clone().requires_grad_(True)
+    op(hg, wg, t).sum().backward()
+    h2 = h.clone().requires_grad_(True)
+    w2 = w.clone().requires_grad_(True)
+    op(h2, w2, t).sum().backward()
+    assert torch.equal(hg.grad, h2.grad) and torch.equal(wg.grad, w2.grad)
+
+
+def test_linear_logp_rejects_out_of_range_targets():
+    from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
+
+    h = torch.randn(8, 64, device=DEV).to(torch.bfloat16)
+    w = torch.randn(100, 64, device=DEV).to(torch.bfloat16)
+    with pytest.raises(ValueError):
+        FusedLinearLogpSM100Op()(h, w, torch.full((8,), -100, device=DEV))
+
+
+# ------------------------------------------------------------------------ ratio_kl / grpo
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ratio_kl_and_grpo_loss_match_native(dtype):
+    from rl_engine.kernels.ops.pytorch.loss.grpo_loss import NativeGRPOLossOp
+    from rl_engine.kernels.ops.pytorch.loss.ratio_kl import NativeRatioKLOp
+    from rl_engine.kernels.ops.sm100.grpo_loss import FusedGRPOLossSM100Op
+    from rl_engine.kernels.ops.sm100.ratio_kl import FusedRatioKLSM100Op
+
+    g = _gen(11)
+    B, T, V = 8, 16, 777
+    pol = torch.randn(B, T, V, device=DEV, generator=g).to(dtype)
+    ref = (pol.float() + 0.1 * torch.randn(B, T, V, device=DEV, generator=g)).to(dtype)
+    ids = torch.randint(0, V, (B, T), device=DEV, generator=g)
+    mask = torch.rand(B, T, device=DEV, generator=g) > 0.3
+    ids = torch.where(mask, ids, torch.full_like(ids, -100))  # garbage at masked positions
+    old = torch.log_softmax(pol.float(), -1).gather(-1, ids.clamp(min=0)[..., None]).squeeze(-1)
+    old = old + 0.05 * torch.randn(B, T, device=DEV, generator=g)
+    rewards = torch.randn(B, device=DEV, generator=g)
+
+    p1 = pol.clone().requires_grad_(True)
+    p2 = pol.clone().float().requires_grad_(True)
+    r1, k1 = FusedRatioKLSM100Op()(p1, ref, ids, mask, old)
+    r2, k2 = NativeRatioKLOp()(p2, ref.float(), ids, mask, old)
+    assert torch.allclose(r1, r2, atol=1e-4, rtol=1e-4) and torch.allclose(k1, k2, atol=1e-4, rtol=1e-3)
+    assert bool((r1[~mask] == 1).all()) and bool((k1[~mask] == 0).all())
+    gr = torch.randn(B, T, device=DEV, generator=g)
+    gk = torch.randn(B, T, device=DEV, generator=g)
+    (r1 * gr + k1 * gk).sum().backward()
+    (r2 * gr + k2 * gk).sum().backward()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert (p1.grad.float() - p2.grad).abs().max().item() < tol
+    assert bool((p1.grad[~mask] == 0).all())
+
+    fused, native = FusedGRPOLossSM100Op(), NativeGRPOLossOp()
+    p1 = pol.clone().requires_grad_(True)
+    p2 = pol.clone().float().requires_grad_(True)
+    got = fused(p1, ref, ids, old, rewards, mask, clip_eps=0.2, beta=0.04, samples_per_prompt=4)
+    want = native(p2, ref.float(), ids, old, rewards, mask, clip_eps=0.2, beta=0.04, samples_per_prompt=4)
+    for a, b in zip(got, want):
+        assert torch.allclose(a, b, atol=2e-4, rtol=1e-3)
+    got[0].backward()
+    want[0].backward()
+    assert (p1.grad.float() - p2.grad).abs().max().item() < (1e-5 if dtype == torch.float32 else 2e-3)
+    with pytest.raises(ValueError):
+        bad = ids.clone()
+        bad[mask] = V
+        FusedRatioKLSM100Op()(pol, ref, bad, mask, old)
+
+
+def test_group_advantages_uniform_and_csr():
+    from rl_engine.kernels.ops.pytorch.loss.grpo_loss import NativeGRPOLossOp
+    from rl_engine.kernels.ops.sm100.grpo_loss import FusedGRPOLossSM100Op
+
+    r = torch.randn(48, device=DEV)
+    f, n = FusedGRPOLossSM100Op(), NativeGRPOLossOp()
+    assert torch.allclose(f.group_advantages(r, samples_per_prompt=8), n.group_advantages(r, samples_per_prompt=8), atol=1e-5)
+    bounds = [0, 3, 7, 12, 48]
+    assert torch.allclose(f.group_advantages(r, group_boundaries=bounds), n.group_advantages(r, group_boundaries=bounds), atol=1e-5)
+    const = torch.ones(8, device=DEV)
+    assert torch.isfinite(f.group_advantages(const, samples_per_prompt=4)).all()
+    with pytest.raises(ValueError):
+        f.group_advantages(r, samples_per_prompt=1)
+
+
+def test_logp_space_losses_match_native():
+    from rl_engine.kernels.ops.pytorch.loss.grpo_loss import NativeGRPOLossOp
+    from rl_engine.kernels.ops.pytorch.loss.policy_losses import NativeDPOLossOp, NativePPOLossOp
+    from rl_engine.kernels.ops.sm100.grpo_loss import FusedGRPOLossSM100Op
+    from rl_engine.kernels.ops.sm100.policy_losses import FusedDPOLossSM100Op, FusedPPOLossSM100Op
+
+    g = _gen(5)
+    B, T = 16, 33
+    lp = (-torch.rand(B, T, device=DEV, generator=g) * 3)
+    ref = lp + 0.1 * torch.randn(B, T, device=DEV, generator=g)
+    old = lp + 0.3 * torch.randn(B, T, device=DEV, generator=g)
+    mask = torch.rand(B, T, device=DEV, generator=g) > 0.2
+    adv_s = torch.randn(B, device=DEV, generator=g)
+    adv_t = torch.randn(B, T, device=DEV, generator=g)
+    a = lp.clone().requires_grad_(True)
+    b = lp.clone().requires_grad_(True)
+    got = FusedGRPOLossSM100Op().apply_from_logps(a, ref, old, adv_s, mask, clip_eps=0.2, beta=0.04)
+    want = NativeGRPOLossOp().apply_from_logps(b, ref, old, adv_s, mask, clip_eps=0.2, beta=0.04)
+    for x, y in zip(got, want):
+        assert torch.allclose(x, y, atol=1e-5, rtol=1e-4)
+    (got[0] + 2 * got[1] - got[2]).backward()
+    (want[0] + 2 * want[1] - want[2]).backward()
+    assert torch.allclose(a.grad, b.grad, atol=1e-6, rtol=1e-4)
+    again = FusedGRPOLossSM100Op().apply_from_logps(lp, ref, old, adv_s, mask, clip_eps=0.2, beta=0.04)
+    assert all(torch.equal(x.detach(), y) for x, y in zip(got, again))
+    a = lp.clone().requires_grad_(True)
+    b = lp.clone().requires_grad_(True)
+    got = FusedPPOLossSM100Op()(a, old, adv_t, mask, ref_logps=ref, clip_eps=0.1, beta=0.01)
+    want = NativePPOLossOp()(b, old, adv_t, mask, ref_logps=ref, clip_eps=0.1, beta=0.01)
+    for x, y in zip(got, want):
+        assert torch.allclose(x, y, atol=1e-5, rtol=1e-4)
+    got[0].backward()
+    want[0].backward()
+    assert torch.allclose(a.grad, b.grad, atol=1e-6, rtol=1e-4)
+    pc, pr, rc, rr = (torch.randn(12, device=DEV, generator=g) for _ in range(4))
+    x = pc.clone().requires_grad_(True)
+    y = pc.clone().requires_grad_(True)
+    xr = pr.clone().requires_grad_(True)
+    yr = pr.clone().requires_grad_(True)
+    got = FusedDPOLossSM100Op()(x, xr, rc, rr, beta=0.3, label_smoothing=0.1)
+    want = NativeDPOLossOp()(y, yr, rc, rr, beta=0.3, label_smoothing=0.1)
+    for u, v in zip(got, want):
+        assert torch.allclose(u, v, atol=1e-5, rtol=1e-4)
+    got[0].backward()
+    want[0].backward()
+    assert torch.allclose(x.grad, y.grad, atol=1e-6, rtol=1e-4) and torch.allclose(xr.grad, yr.grad, atol=1e-6, rtol=1e-4)
+
+
+# ----------------------------------------------------------------------------- model ops
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_swiglu_rope_embedding(dtype):
+    from rl_engine.kernels.ops.pytorch.activation.swiglu import NativeSiLUOp, NativeSwiGLUOp
+    from rl_engine.kernels.ops.pytorch.linear.rope import NativeRoPEOp
+    from rl_engine.kernels.ops.pytorch.norm.rms_norm import NativeRMSNormOp
+    from rl_engine.kernels.ops.sm100.model_ops import (
+        FusedEmbeddingSM100Op, FusedRMSNormSM100Op, FusedRoPESM100Op, FusedSiLUSM100Op, FusedSwiGLUSM100Op,
+    )
+
+    g = _gen(3)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    x = torch.randn(5, 37, 200, device=DEV, generator=g).to(dtype)
+    w = torch.randn(200, device=DEV, generator=g).to(dtype)
+    f, n = FusedRMSNormSM100Op(), NativeRMSNormOp()
+    assert torch.allclose(f.forward_fp32(x, w), n.forward_fp32(x, w), atol=1e-5, rtol=1e-5)
+    assert torch.equal(f(x, w)[2:4], f(x[2:4], w))  # batch invariance, bitwise
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.clone().float().requires_grad_(True), w.clone().float().requires_grad_(True)
+    dy = torch.randn_like(x)
+    f(xa, wa).backward(dy)
+    n.forward_fp32(xb, wb).backward(dy.float())
+    assert (xa.grad.float() - xb.grad).abs().max().item() < tol * 5
+    assert (wa.grad.float() - wb.grad).abs().max().item() / wb.grad.abs().max().item() < tol
+    with pytest.raises(ValueError):
+        f(x, w[:-1])
+
+    gate = torch.randn(7, 19, 96, device=DEV, generator=g).to(dtype)
+    up = torch.randn(7, 19, 96, device=DEV, generator=g).to(dtype)
+    fs, ns = FusedSwiGLUSM100Op(), NativeSwiGLUOp()
+    assert torch.allclose(fs.forward_fp32(gate, up), ns.forward_fp32(gate, up), atol=1e-5, rtol=1e-5)
+    ga, ua = gate.clone().requires_grad_(True), up.clone().requires_grad_(True)
+    gb, ub = gate.clone().float().requires_grad_(True), up.clone().float().requires_grad_(True)
+    dy = torch.randn_like(gate)
+    fs(ga, ua).backward(dy)
+    ns.forward_fp32(gb, ub).backward(dy.float())
+    assert (ga.grad.float() - gb.grad).abs().max().item() < tol * 5 and (ua.grad.float() - ub.grad).abs().max().item() < tol * 5
+    assert torch.allclose(FusedSiLUSM100Op().forward_fp32(gate), NativeSiLUOp().forward_fp32(gate), atol=1e-5)
+    with pytest.raises(ValueError):
+        fs(gate, up[:, :, :-1])
+
+    q = torch.randn(2, 50, 4, 64, device=DEV, generator=g).to(dtype)
+    pos = torch.arange(50, device=DEV).expand(2, 50) + 3
+    fr, nr = FusedRoPESM100Op(), NativeRoPEOp()
+    assert (fr(q, pos).float() - nr.forward_fp32(q, pos)).abs().max().item() < tol
+    qa = q.clone().requires_grad_(True)
+    qb = q.clone().float().requires_grad_(True)
+    dy = torch.randn_like(q)
+    fr(qa, pos).backward(dy)
+    nr.forward_fp32(qb, pos).backward(dy.float())
+    assert (qa.grad.float() - qb.grad).abs().max().item() < tol * 2
+
+    table = torch.randn(300, 72, device=DEV, generator=g).to(dtype)
+    ids = torch.randint(0, 300, (4, 25), device=DEV, generator=g)
+    ids[0, :5] = 17  # repeated id exercises the ordered segment sum
+    fe = FusedEmbeddingSM100Op()
+    ta = table.clone().requires_grad_(True)
+    tb = table.clone().float().requires_grad_(True)
+    out = fe(ids, ta)
+    assert torch.equal(out, table[ids])
+    dy = torch.randn(4, 25, 72, device=DEV, generator=g).to(dtype)
+    out.backward(dy)
+    torch.nn.functional.embedding(ids, tb).backward(dy.float())
+    assert (ta.grad.float() - tb.grad).abs().max().item() < tol * 4
+
+
+def test_adamw_matches_torch():
+    from rl_engine.kernels.ops.base import require_ext
+
+    g = _gen(9)
+    p = torch.randn(10000, device=DEV, generator=g)
+    grad = torch.randn(10000, device=DEV, generator=g)
+    ref = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    pb = p.to(torch.bfloat16)
+    master = p.clone()
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    for step in range(1, 4):
+        ref.grad = grad.clone()
+        opt.step()
+        require_ext().adamw(pb, master, grad.to(torch.bfloat16).float(), m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+    assert torch.allclose(master, ref.detach(), atol=2e-4, rtol=1e-3)
+    assert torch.allclose(pb.float(), master, atol=1e-2, rtol=1e-2)
+
+
+# -------------------------------------------------------------------------------- sampler
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sampler_matches_host_restatement(dtype):
+    from rl_engine.kernels.ops.sm100.sampler import sample_reference, sample_topk_topp
+
+    g = _gen(21)
+    logits = (torch.randn(16, 5000, device=DEV, generator=g) * 2).to(dtype)
+    for (k, p, temp) in [(50, 0.9, 0.7), (1, 1.0, 1.0), (8, 0.5, 1.3), (1024, 0.95, 1.0)]:
+        got, lp = sample_topk_topp(logits, top_k=k, top_p=p, temperature=temp, seed=123, offset=4, return_logprob=True)
+        want = sample_reference(logits, k, p, temp, 123, 4)
+        agree = (got.cpu() == want).float().mean().item()
+        assert agree >= 0.9, (k, p, temp, agree)  # float rounding at cut boundaries may flip a rare row
+        again, _ = sample_topk_topp(logits, top_k=k, top_p=p, temperature=temp, seed=123, offset=4)
+        assert torch.equal(got, again)
+        assert bool((lp <= 1e-6).all())
+    greedy, _ = sample_topk_topp(logits, top_k=1, top_p=1.0, temperature=1.0, seed=0, offset=0)
+    assert torch.equal(greedy, logits.float().argmax(-1))
+
+
+def test_sampler_distribution():
+    from rl_engine.kernels.ops.sm100.sampler import sample_topk_topp
+
+    z = torch.tensor([2.0, 1.0, 0.5, 0.0, -1.0, -3.0], device=DEV).repeat(20000, 1)
+    ids, _ = sample_topk_topp(z, top_k=4, top_p=1.0, temperature=1.0, seed=99, offset=0)
+    freq = torch.bincount(ids, minlength=6).float() / ids.numel()
+    want = torch.softmax(z[0, :4], 0)
+    assert freq[4:].sum() == 0 and torch.allclose(freq[:4], want, atol=0.015)
