@@ -196,3 +196,31 @@ void sample_topk_topp(const void* logits, long long ld, int dtype, int rows, int
 int sample_topk_limit();
 
 }  // namespace rlk
+
+namespace rlk {
+
+// -------------------------------------------------------------------------------- attention
+// Packed-token attention with head_dim 128.  `seqs` holds 8 int32 per sequence:
+//   {q_start, q_len, prefix_k_start, prefix_k_len, self_k_start, self_k_len, 0, 0}
+// `tiles` holds (sequence, first query row in that sequence) per 128-row query tile.
+struct AttnFwdArgs {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  long long ld_q, ld_k, ld_v;  // token pitches (elements)
+  long long total_q, total_kv;
+  int heads_q, heads_kv;
+  const int* seqs;
+  const int* tiles;
+  int num_tiles;
+  bool causal;
+  float softmax_scale;
+  __nv_bfloat16* out;
+  long long ld_out;
+  float* lse;  // [heads_q, total_q] or null
+  long long lse_head_stride;
+  uint32_t* err;
+};
+void attention_forward(const AttnFwdArgs& args, cudaStream_t stream);
+
+}  // namespace rlk

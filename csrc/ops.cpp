@@ -583,6 +583,57 @@ std::vector<Tensor> sample(const Tensor& logits, int64_t top_k, double top_p, do
   return {ids, lp};
 }
 
+// -------------------------------------------------------------------------------- attention
+std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& seqs,
+                                  const Tensor& tiles, bool causal, double softmax_scale, bool want_lse) {
+  auto check3 = [](const Tensor& t, const char* n) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 3 && t.size(2) == 128 &&
+                    t.stride(2) == 1 && t.stride(1) == 128,
+                "rl_engine.attention: ", n, " must be bf16 [tokens, heads, 128] with packed heads");
+    TORCH_CHECK(t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+                "rl_engine.attention: ", n, " must be 16-byte aligned with a 16-byte token pitch");
+  };
+  check3(q, "q");
+  check3(k, "k");
+  check3(v, "v");
+  TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1), "rl_engine.attention: k and v must match");
+  TORCH_CHECK(q.size(1) % k.size(1) == 0, "rl_engine.attention: q heads must be a multiple of kv heads");
+  TORCH_CHECK(seqs.is_cuda() && seqs.scalar_type() == torch::kInt32 && seqs.is_contiguous() && seqs.dim() == 2 &&
+                  seqs.size(1) == 8,
+              "rl_engine.attention: seqs must be int32 [S, 8]");
+  TORCH_CHECK(tiles.is_cuda() && tiles.scalar_type() == torch::kInt32 && tiles.is_contiguous() && tiles.dim() == 2 &&
+                  tiles.size(1) == 2,
+              "rl_engine.attention: tiles must be int32 [n, 2]");
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({q.size(0), q.size(1), 128}, q.options());
+  Tensor lse = want_lse ? torch::empty({q.size(1), q.size(0)}, q.options().dtype(torch::kFloat32)) : Tensor();
+  if (tiles.size(0) == 0) return {out, lse};
+  rlk::AttnFwdArgs a{};
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  a.k = reinterpret_cast<const __nv_bfloat16*>(k.data_ptr());
+  a.v = reinterpret_cast<const __nv_bfloat16*>(v.data_ptr());
+  a.ld_q = q.stride(0);
+  a.ld_k = k.stride(0);
+  a.ld_v = v.stride(0);
+  a.total_q = q.size(0);
+  a.total_kv = k.size(0);
+  a.heads_q = static_cast<int>(q.size(1));
+  a.heads_kv = static_cast<int>(k.size(1));
+  a.seqs = seqs.data_ptr<int>();
+  a.tiles = tiles.data_ptr<int>();
+  a.num_tiles = static_cast<int>(tiles.size(0));
+  a.causal = causal;
+  a.softmax_scale = static_cast<float>(softmax_scale);
+  a.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  a.ld_out = out.stride(0);
+  a.lse = want_lse ? lse.data_ptr<float>() : nullptr;
+  a.lse_head_stride = q.size(0);
+  a.err = err_ptr(q);
+  rlk::attention_forward(a, stream_of(q));
+  after_launch();
+  return {out, lse};
+}
+
 // ------------------------------------------------------------------------------ diagnostics
 std::vector<int64_t> error_state(int64_t device) {
   Tensor w = error_word(static_cast<int>(device)).cpu();
@@ -617,6 +668,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw", &adamw);
   m.def("sample", &sample);
+  m.def("attention_fwd", &attention_fwd);
   m.def("error_state", &error_state);
   m.def("reset_error", &reset_error);
   m.def("launch_count", &launch_count);

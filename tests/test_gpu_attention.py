@@ -1,0 +1,79 @@
+"""tcgen05 attention vs fp32 PyTorch: causal / non-causal, GQA, ragged lengths, GRPO prefix sharing."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    return (torch.randn(shape, device=DEV, generator=g) * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,s,hq,hkv", [(2, 128, 4, 4), (1, 384, 8, 2), (3, 200, 4, 1), (2, 77, 2, 2)])
+def test_attn_op_matches_sdpa(causal, b, s, hq, hkv):
+    from rl_engine.kernels.ops.pytorch.attention import NativeAttentionOp
+    from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
+
+    q, k, v = _rand((b, s, hq, 128), 1), _rand((b, s, hkv, 128), 2), _rand((b, s, hkv, 128), 3)
+    got = FlashAttentionSM100Op()(q, k, v, causal=causal)
+    want = NativeAttentionOp()(q.float(), k.float(), v.float(), causal=causal)
+    assert (got.float() - want).abs().max().item() < 2e-2
+    assert torch.equal(got, FlashAttentionSM100Op()(q, k, v, causal=causal))
+
+
+@pytest.mark.parametrize("bs,G,lq,lkv", [(1, 4, 128, 256), (2, 3, 192, 1000), (1, 8, 64, 130)])
+def test_prefix_shared_noncausal(bs, G, lq, lkv):
+    from rl_engine.kernels.ops.pytorch.attention import NativePrefixSharedAttentionOp
+    from rl_engine.kernels.ops.sm100.attention import PrefixSharedAttentionSM100Op
+
+    q, k, v = _rand((bs, G, lq, 128), 4), _rand((bs, lkv, 128), 5), _rand((bs, lkv, 128), 6)
+    got = PrefixSharedAttentionSM100Op()(q, k, v)
+    want = NativePrefixSharedAttentionOp()(q.float(), k.float(), v.float())
+    assert (got.float() - want).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("P,G,L,hq,hkv", [(256, 4, 128, 4, 2), (100, 3, 70, 8, 2), (1024, 2, 512, 4, 1)])
+def test_grpo_group_attention_forward_and_backward(P, G, L, hq, hkv):
+    from rl_engine.kernels.ops.pytorch.attention import grouped_prefix_causal_attention_reference
+    from rl_engine.kernels.ops.sm100.attention import grouped_prefix_attention, grpo_group_layout, packed_attention_forward
+
+    T = P + G * L
+    q, k, v = _rand((T, hq, 128), 7), _rand((T, hkv, 128), 8), _rand((T, hkv, 128), 9)
+    layout = grpo_group_layout(P, G, L, DEV)
+    out, lse = packed_attention_forward(q, k, v, layout)
+    # completions: oracle with explicit prefix + causal suffix
+    want, want_lse = grouped_prefix_causal_attention_reference(
+        q[P:].reshape(G, L, hq, 128), k[:P], v[:P], k[P:].reshape(G, L, hkv, 128), v[P:].reshape(G, L, hkv, 128)
+    )
+    assert (out[P:].reshape(G, L, hq, 128).float() - want).abs().max().item() < 2e-2
+    got_lse = lse[:, P:].reshape(hq, G, L).permute(1, 0, 2)
+    assert (got_lse - want_lse).abs().max().item() < 2e-2
+    # prompt rows: plain causal attention
+    qp = q[:P].float().transpose(0, 1)
+    kp = k[:P].float().transpose(0, 1).repeat_interleave(hq // hkv, 0)
+    vp = v[:P].float().transpose(0, 1).repeat_interleave(hq // hkv, 0)
+    ref_p = torch.nn.functional.scaled_dot_product_attention(qp, kp, vp, is_causal=True).transpose(0, 1)
+    assert (out[:P].float() - ref_p).abs().max().item() < 2e-2
+
+    # gradients vs autograd through the fp32 oracle
+    qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
+    dout = _rand((T, hq, 128), 10)
+    grouped_prefix_attention(qa, ka, va, P, G, L).backward(dout)
+    qb, kb, vb = (t.clone().float().requires_grad_(True) for t in (q, k, v))
+    oc, _ = grouped_prefix_causal_attention_reference(
+        qb[P:].reshape(G, L, hq, 128), kb[:P], vb[:P], kb[P:].reshape(G, L, hkv, 128), vb[P:].reshape(G, L, hkv, 128)
+    )
+    op = torch.nn.functional.scaled_dot_product_attention(
+        qb[:P].transpose(0, 1), kb[:P].transpose(0, 1).repeat_interleave(hq // hkv, 0),
+        vb[:P].transpose(0, 1).repeat_interleave(hq // hkv, 0), is_causal=True,
+    ).transpose(0, 1)
+    torch.cat([op, oc.reshape(G * L, hq, 128)]).backward(dout.float())
+    for got, want in ((qa.grad, qb.grad), (ka.grad, kb.grad), (va.grad, vb.grad)):
+        scale = want.abs().max().item()
+        assert (got.float() - want).abs().max().item() / scale < 3e-2
