@@ -487,7 +487,8 @@ std::vector<Tensor> swiglu_bwd(const Tensor& gate, std::optional<Tensor> up, con
 }
 
 // x: [tokens, heads, D] with unit stride on D and stride D on heads
-Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const Tensor& sin_t, bool inverse) {
+Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const Tensor& sin_t, bool inverse,
+            std::optional<Tensor> out_opt) {
   check_cuda(x, "x");
   TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [tokens, heads, D] with packed heads");
   TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == torch::kInt64 && positions.is_contiguous() &&
@@ -497,7 +498,16 @@ Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const
                   sin_t.is_contiguous() && cos_t.size(-1) == x.size(2) / 2,
               "rope: cos/sin tables must be contiguous float32 [max_pos, D/2]");
   const c10::cuda::CUDAGuard guard(x.device());
-  Tensor out = torch::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  Tensor out;
+  if (out_opt.has_value() && out_opt->defined()) {
+    out = *out_opt;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == x.scalar_type() && out.dim() == 3 && out.size(0) == x.size(0) &&
+                    out.size(1) == x.size(1) && out.size(2) == x.size(2) && out.stride(2) == 1 &&
+                    out.stride(1) == out.size(2),
+                "rope: out must match x with packed heads");
+  } else {
+    out = torch::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  }
   if (x.numel()) {
     rlk::rope_apply(x.data_ptr(), x.stride(0), dtype_code(x), reinterpret_cast<const long long*>(positions.data_ptr<int64_t>()),
                     cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), out.data_ptr(), out.stride(0), x.size(0),
@@ -663,7 +673,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
-  m.def("rope", &rope);
+  m.def("rope", &rope, py::arg("x"), py::arg("positions"), py::arg("cos"), py::arg("sin"), py::arg("inverse") = false,
+        py::arg("out") = py::none());
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("adamw", &adamw);

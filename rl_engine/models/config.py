@@ -1,0 +1,62 @@
+"""Architecture presets used by the benchmarks and tests."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    name: str
+    vocab_size: int
+    hidden_size: int
+    num_layers: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    ffn_size: int
+    rms_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    # mixture of experts (0 experts = dense SwiGLU FFN)
+    num_experts: int = 0
+    experts_per_token: int = 0
+    moe_ffn_size: int = 0
+    qk_norm: bool = False
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    def with_layers(self, n: int) -> "ModelConfig":
+        return replace(self, num_layers=n)
+
+    def param_count(self) -> int:
+        attn = self.hidden_size * (self.q_dim + 2 * self.kv_dim) + self.q_dim * self.hidden_size
+        if self.num_experts:
+            ffn = self.num_experts * 3 * self.hidden_size * self.moe_ffn_size + self.hidden_size * self.num_experts
+        else:
+            ffn = 3 * self.hidden_size * self.ffn_size
+        per_layer = attn + ffn + 2 * self.hidden_size
+        return self.num_layers * per_layer + 2 * self.vocab_size * self.hidden_size + self.hidden_size
+
+
+def llama3_8b() -> ModelConfig:
+    """Llama-3-8B: 32 layers, hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab 128256."""
+    return ModelConfig("llama3-8b", 128256, 4096, 32, 32, 8, 128, 14336, rms_eps=1e-5, rope_theta=500000.0)
+
+
+def qwen3_30b_a3b() -> ModelConfig:
+    """Qwen3-30B-A3B: 48 layers, hidden 2048, 32 q / 4 kv heads of 128, 128 experts top-8, expert FFN 768."""
+    return ModelConfig(
+        "qwen3-30b-a3b", 151936, 2048, 48, 32, 4, 128, 6144, rms_eps=1e-6, rope_theta=1000000.0,
+        num_experts=128, experts_per_token=8, moe_ffn_size=768, qk_norm=True,
+    )
+
+
+def tiny_llama(head_dim: int = 64) -> ModelConfig:
+    """2 layers, hidden 256, 4 heads, SwiGLU 688, vocab 32000 (the CPU fp32 GRPO configuration)."""
+    return ModelConfig("tiny-llama", 32000, 4 * head_dim, 2, 4, 4, head_dim, 688, rms_eps=1e-5, rope_theta=10000.0)

@@ -1,0 +1,218 @@
+"""Llama-style decoder over packed tokens, assembled from registry operators.
+
+Token layout: one flat axis ``[T]`` with a ``PackedLayout`` describing which key ranges every
+sequence attends (``rl_engine.kernels.ops.sm100.attention``), so a GRPO group is stored as
+``[prompt | completion_0 | ... ]`` and the prompt is embedded, projected and attended exactly once.
+
+On a Blackwell GPU with bf16 weights every matmul is the tcgen05 GEMM, attention is the tcgen05
+flash kernel and the elementwise ops are the sm_100a kernels; on CPU (or fp32) the PyTorch oracles
+run, which is the fp32 reference configuration.  All parameters are views into ONE flat buffer so
+the optimizer and any gradient collective work on a single contiguous range.
+
+The reference ships no model (only ``Embedding -> Linear`` toys:
+``rl_engine/executors/deepspeed_trainer.py:54-70``, ``examples/grpo_single_gpu.py:47-56``).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+from rl_engine.kernels.ops.pytorch.attention import NativeAttentionOp  # noqa: F401  (CPU oracle family)
+from rl_engine.kernels.ops.pytorch.linear.rope import rope_cos_sin
+from rl_engine.models.config import ModelConfig
+
+
+def _fused_path(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if _fused_path(x) and x.shape[-1] % 8 == 0:
+        from rl_engine.kernels.ops.sm100.gemm import matmul_nt
+
+        return matmul_nt(x, w)
+    return x @ w.t()
+
+
+def rms_norm(x, w, eps):
+    from rl_engine.kernels.registry import kernel_registry
+
+    return kernel_registry.get_op("rms_norm")(x, w, eps=eps)
+
+
+def swiglu(gate, up):
+    from rl_engine.kernels.registry import kernel_registry
+
+    return kernel_registry.get_op("swiglu")(gate, up)
+
+
+def reference_packed_attention(q, k, v, host_seqs, causal: bool, scale: float) -> torch.Tensor:
+    """Differentiable PyTorch restatement of packed attention (CPU path / oracle)."""
+    hq, hkv = q.shape[1], k.shape[1]
+    rep = hq // hkv
+    outs: List[Tuple[int, torch.Tensor]] = []
+    for (q_start, q_len, pk_start, pk_len, sk_start, sk_len) in host_seqs:
+        qs = q[q_start : q_start + q_len].transpose(0, 1)  # Hq, L, D
+        keys, vals, masks = [], [], []
+        for (k0, klen, masked) in ((pk_start, pk_len, False), (sk_start, sk_len, causal)):
+            if klen == 0:
+                continue
+            keys.append(k[k0 : k0 + klen].transpose(0, 1).repeat_interleave(rep, 0))
+            vals.append(v[k0 : k0 + klen].transpose(0, 1).repeat_interleave(rep, 0))
+            allow = torch.ones(q_len, klen, dtype=torch.bool, device=q.device)
+            masks.append(allow.tril() if masked else allow)
+        kk, vv, mm = torch.cat(keys, 1), torch.cat(vals, 1), torch.cat(masks, 1)
+        s = torch.einsum("hqd,hkd->hqk", qs.float(), kk.float()) * scale
+        p = torch.softmax(s.masked_fill(~mm, float("-inf")), dim=-1)
+        outs.append((q_start, torch.einsum("hqk,hkd->hqd", p, vv.float()).transpose(0, 1).to(q.dtype)))
+    outs.sort(key=lambda t: t[0])
+    return torch.cat([o for _, o in outs], 0)
+
+
+class _FusedAttentionBlock(torch.autograd.Function):
+    """qkv [T, Hq+2Hkv, 128] -> RoPE(q), RoPE(k) -> packed flash attention -> [T, Hq, 128]."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_t, sin_t, layout, hq, hkv, scale):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+
+        ext = require_ext()
+        q = ext.rope(qkv[:, :hq], positions, cos_t, sin_t, False)
+        k = ext.rope(qkv[:, hq : hq + hkv], positions, cos_t, sin_t, False)
+        v = qkv[:, hq + hkv :]
+        out, lse = packed_attention_forward(q, k, v, layout, scale, True)
+        ctx.save_for_backward(q, k, qkv, out, lse, positions, cos_t, sin_t)
+        ctx.meta = (layout, hq, hkv, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention_bwd import packed_attention_backward
+
+        q, k, qkv, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
+        layout, hq, hkv, scale = ctx.meta
+        v = qkv[:, hq + hkv :]
+        dq, dk, dv = packed_attention_backward(q, k, v, out, lse, dout.contiguous(), layout, scale)
+        dqkv = torch.empty_like(qkv)
+        ext = require_ext()
+        ext.rope(dq, positions, cos_t, sin_t, True, dqkv[:, :hq])
+        ext.rope(dk, positions, cos_t, sin_t, True, dqkv[:, hq : hq + hkv])
+        dqkv[:, hq + hkv :].copy_(dv)
+        return dqkv, None, None, None, None, None, None, None
+
+
+class LlamaModel(nn.Module):
+    def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
+                 activation_checkpointing: bool = True, max_positions: int = 8192) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.activation_checkpointing = activation_checkpointing
+        h, f = cfg.hidden_size, cfg.ffn_size
+        qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
+        shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab_size, h))]
+        for i in range(cfg.num_layers):
+            shapes += [
+                (f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h)), (f"l{i}.wo", (h, cfg.q_dim)),
+                (f"l{i}.mlp_norm", (h,)), (f"l{i}.w_gate_up", (2 * f, h)), (f"l{i}.w_down", (h, f)),
+            ]
+        shapes += [("final_norm", (h,)), ("lm_head", (cfg.vocab_size, h))]
+        # every parameter starts on a 16-byte boundary of ONE flat buffer
+        offsets, total = {}, 0
+        for name, shape in shapes:
+            offsets[name] = total
+            total += (math.prod(shape) + 127) // 128 * 128
+        self.flat = nn.Parameter(torch.empty(total, dtype=dtype, device=device))
+        self._shapes = dict(shapes)
+        self._offsets = offsets
+        self.reset_parameters(seed)
+        cos, sin = rope_cos_sin(torch.arange(max_positions, device=device), cfg.head_dim, cfg.rope_theta)
+        self.register_buffer("rope_cos", cos.contiguous(), persistent=False)
+        self.register_buffer("rope_sin", sin.contiguous(), persistent=False)
+
+    # -- parameters -------------------------------------------------------------------------
+    def view(self, name: str, flat: Optional[torch.Tensor] = None) -> torch.Tensor:
+        flat = self.flat if flat is None else flat
+        shape = self._shapes[name]
+        off = self._offsets[name]
+        return flat[off : off + math.prod(shape)].view(shape)
+
+    def named_views(self, flat: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
+        return {name: self.view(name, flat) for name in self._shapes}
+
+    @torch.no_grad()
+    def reset_parameters(self, seed: int = 0) -> None:
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.flat.zero_()
+        for name, shape in self._shapes.items():
+            dst = self.view(name)
+            if name.endswith("norm"):
+                dst.fill_(1.0)
+                continue
+            # chunked host-side init keeps peak host memory small for the 8B configuration
+            flat_dst = dst.view(-1)
+            step = 1 << 24
+            for i in range(0, flat_dst.numel(), step):
+                n = min(step, flat_dst.numel() - i)
+                flat_dst[i : i + n].copy_((torch.randn(n, generator=gen) * 0.02).to(dst.dtype))
+
+    def state_dict_views(self) -> Dict[str, torch.Tensor]:
+        """Checkpoint-format names -> tensors (views of the flat buffer), for the weight bridge."""
+        return {k: v.detach() for k, v in self.named_views().items()}
+
+    # -- forward ----------------------------------------------------------------------------
+    def _attention(self, qkv: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
+        cfg = self.cfg
+        t = qkv.shape[0]
+        qkv3 = qkv.view(t, cfg.num_heads + 2 * cfg.num_kv_heads, cfg.head_dim)
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        if _fused_path(qkv) and cfg.head_dim == 128:
+            out = _FusedAttentionBlock.apply(
+                qkv3, positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale
+            )
+            return out.reshape(t, cfg.q_dim)
+        from rl_engine.kernels.registry import kernel_registry
+
+        rope = kernel_registry.get_op("rope")
+        q = rope(qkv3[:, : cfg.num_heads], positions, theta=cfg.rope_theta)
+        k = rope(qkv3[:, cfg.num_heads : cfg.num_heads + cfg.num_kv_heads], positions, theta=cfg.rope_theta)
+        v = qkv3[:, cfg.num_heads + cfg.num_kv_heads :]
+        out = reference_packed_attention(q, k, v, layout.host_seqs, layout.causal, scale)
+        return out.reshape(t, cfg.q_dim)
+
+    def _layer(self, x: torch.Tensor, flat: torch.Tensor, index: int, positions: torch.Tensor, layout) -> torch.Tensor:
+        cfg = self.cfg
+        p = lambda n: self.view(f"l{index}.{n}", flat)
+        h = rms_norm(x, p("attn_norm"), cfg.rms_eps)
+        attn = self._attention(linear(h, p("wqkv")), positions, layout)
+        x = x + linear(attn, p("wo"))
+        h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
+        gu = linear(h, p("w_gate_up"))
+        act = swiglu(gu[:, : cfg.ffn_size], gu[:, cfg.ffn_size :])
+        return x + linear(act, p("w_down"))
+
+    def hidden_states(self, token_ids: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
+        """Packed ``token_ids [T]`` -> final-norm hidden states ``[T, H]``."""
+        from rl_engine.kernels.registry import kernel_registry
+
+        flat = self.flat
+        x = kernel_registry.get_op("embedding")(token_ids, self.view("embed", flat))
+        for i in range(self.cfg.num_layers):
+            if self.activation_checkpointing and torch.is_grad_enabled():
+                x = checkpoint(self._layer, x, flat, i, positions, layout, use_reentrant=False)
+            else:
+                x = self._layer(x, flat, i, positions, layout)
+        return rms_norm(x, self.view("final_norm", flat), self.cfg.rms_eps)
+
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.view("lm_head")
+
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
+        """Logits ``[T, V]`` (materialised; use ``hidden_states`` + ``linear_logp`` for training)."""
+        return linear(self.hidden_states(token_ids, positions, layout), self.lm_head_weight())
