@@ -224,3 +224,43 @@ struct AttnFwdArgs {
 void attention_forward(const AttnFwdArgs& args, cudaStream_t stream);
 
 }  // namespace rlk
+
+namespace rlk {
+
+// ----------------------------------------------------------------------- attention backward
+// kv_items: 8 int32 each {k_row, k_len, k_pos, qb_begin, qb_end, out_slot, 0, 0}
+// q_blocks: 4 int32 each {q_row, n_rows, q_pos, causal};  reduce_jobs: 4 int32 {k_row, k_len, slot_begin, slot_end}
+struct AttnBwdArgs {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* dout;
+  long long ld_q, ld_k, ld_v, ld_do;
+  long long total_q, total_kv;
+  int heads_q, heads_kv;
+  const int* seqs;
+  const int* q_tiles;
+  int num_q_tiles;
+  const int* kv_items;
+  int num_kv_items;
+  const int* q_blocks;
+  const int* reduce_jobs;
+  int num_reduce_jobs;
+  bool causal;
+  float softmax_scale;
+  const float* lse;    // [heads_q, total_q]
+  const float* delta;  // [heads_q, total_q]
+  __nv_bfloat16* dq;
+  long long ld_dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  long long ld_dkv;
+  float* partials;  // [slots, heads_kv, 2, 128, 128]
+  uint32_t* err;
+};
+void attention_delta(const __nv_bfloat16* out, const __nv_bfloat16* dout, long long ld, int heads, long long tokens,
+                     float* delta, cudaStream_t stream);
+void attention_backward_dq(const AttnBwdArgs& args, cudaStream_t stream);
+void attention_backward_dkv(const AttnBwdArgs& args, cudaStream_t stream);
+
+}  // namespace rlk

@@ -644,6 +644,83 @@ std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor
   return {out, lse};
 }
 
+std::vector<Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                                  const Tensor& dout, const Tensor& lse, const Tensor& seqs, const Tensor& q_tiles,
+                                  const Tensor& kv_items, const Tensor& q_blocks, const Tensor& reduce_jobs,
+                                  int64_t num_slots, bool causal, double softmax_scale) {
+  auto check3 = [](const Tensor& t, const char* n) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 3 && t.size(2) == 128 &&
+                    t.stride(2) == 1 && t.stride(1) == 128 && t.stride(0) % 8 == 0 &&
+                    reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+                "rl_engine.attention_bwd: ", n, " must be aligned bf16 [tokens, heads, 128] with packed heads");
+  };
+  check3(q, "q");
+  check3(k, "k");
+  check3(v, "v");
+  check3(out, "out");
+  check3(dout, "dout");
+  TORCH_CHECK(out.stride(0) == dout.stride(0), "rl_engine.attention_bwd: out and dout must share their token pitch");
+  TORCH_CHECK(lse.is_cuda() && lse.scalar_type() == torch::kFloat32 && lse.is_contiguous() && lse.size(0) == q.size(1) &&
+                  lse.size(1) == q.size(0),
+              "rl_engine.attention_bwd: lse must be float32 [heads, tokens]");
+  auto checki = [](const Tensor& t, int64_t w, const char* n) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous() && t.dim() == 2 && t.size(1) == w,
+                "rl_engine.attention_bwd: ", n, " must be int32 [n, ", w, "]");
+  };
+  checki(seqs, 8, "seqs");
+  checki(q_tiles, 2, "q_tiles");
+  checki(kv_items, 8, "kv_items");
+  checki(q_blocks, 4, "q_blocks");
+  checki(reduce_jobs, 4, "reduce_jobs");
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int64_t hq = q.size(1), hkv = k.size(1);
+  Tensor dq = torch::zeros({q.size(0), hq, 128}, q.options());
+  Tensor dk = torch::zeros({k.size(0), hkv, 128}, k.options());
+  Tensor dv = torch::zeros({k.size(0), hkv, 128}, k.options());
+  Tensor delta = torch::empty({hq, q.size(0)}, lse.options());
+  Tensor partials = torch::empty({std::max<int64_t>(num_slots, 1) * hkv * 2 * 128 * 128}, lse.options());
+  cudaStream_t stream = stream_of(q);
+  rlk::attention_delta(reinterpret_cast<const __nv_bfloat16*>(out.data_ptr()),
+                       reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), out.stride(0), static_cast<int>(hq),
+                       q.size(0), delta.data_ptr<float>(), stream);
+  rlk::AttnBwdArgs a{};
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q.data_ptr());
+  a.k = reinterpret_cast<const __nv_bfloat16*>(k.data_ptr());
+  a.v = reinterpret_cast<const __nv_bfloat16*>(v.data_ptr());
+  a.dout = reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr());
+  a.ld_q = q.stride(0);
+  a.ld_k = k.stride(0);
+  a.ld_v = v.stride(0);
+  a.ld_do = dout.stride(0);
+  a.total_q = q.size(0);
+  a.total_kv = k.size(0);
+  a.heads_q = static_cast<int>(hq);
+  a.heads_kv = static_cast<int>(hkv);
+  a.seqs = seqs.data_ptr<int>();
+  a.q_tiles = q_tiles.data_ptr<int>();
+  a.num_q_tiles = static_cast<int>(q_tiles.size(0));
+  a.kv_items = kv_items.data_ptr<int>();
+  a.num_kv_items = static_cast<int>(kv_items.size(0));
+  a.q_blocks = q_blocks.data_ptr<int>();
+  a.reduce_jobs = reduce_jobs.data_ptr<int>();
+  a.num_reduce_jobs = static_cast<int>(reduce_jobs.size(0));
+  a.causal = causal;
+  a.softmax_scale = static_cast<float>(softmax_scale);
+  a.lse = lse.data_ptr<float>();
+  a.delta = delta.data_ptr<float>();
+  a.dq = reinterpret_cast<__nv_bfloat16*>(dq.data_ptr());
+  a.ld_dq = dq.stride(0);
+  a.dk = reinterpret_cast<__nv_bfloat16*>(dk.data_ptr());
+  a.dv = reinterpret_cast<__nv_bfloat16*>(dv.data_ptr());
+  a.ld_dkv = dk.stride(0);
+  a.partials = partials.data_ptr<float>();
+  a.err = err_ptr(q);
+  rlk::attention_backward_dq(a, stream);
+  rlk::attention_backward_dkv(a, stream);
+  after_launch(a.num_reduce_jobs > 0 ? 4 : 3);
+  return {dq, dk, dv};
+}
+
 // ------------------------------------------------------------------------------ diagnostics
 std::vector<int64_t> error_state(int64_t device) {
   Tensor w = error_word(static_cast<int>(device)).cpu();
@@ -680,6 +757,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw", &adamw);
   m.def("sample", &sample);
   m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
   m.def("error_state", &error_state);
   m.def("reset_error", &reset_error);
   m.def("launch_count", &launch_count);

@@ -60,9 +60,12 @@ def synthetic_batch(vocab: int, prompt_len: int, group: int, completion_len: int
 class FlatAdamW:
     """AdamW over one flat parameter buffer; one fused kernel launch per step on the GPU."""
 
-    def __init__(self, param: torch.nn.Parameter, lr=1e-6, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
+    def __init__(self, model, lr=1e-6, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
                  master_weights: bool = False) -> None:
-        self.param = param
+        self.model = model
+        self.param = model.flat
+        self.grad = model.ensure_flat_grad()
+        param = self.param
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.m = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
         self.v = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
@@ -70,31 +73,28 @@ class FlatAdamW:
         self.steps = 0
 
     def zero_grad(self) -> None:
-        if self.param.grad is None:
-            self.param.grad = torch.zeros_like(self.param)
-        else:
-            self.param.grad.zero_()
+        self.grad.zero_()
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0) -> None:
         self.steps += 1
-        p, g = self.param, self.param.grad
+        p, g = self.param, self.grad
         if p.is_cuda:
             from rl_engine.kernels.ops.base import require_ext
 
-            require_ext().adamw(p.data, self.master, g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
+            require_ext().adamw(p, self.master, g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
                                 self.weight_decay, self.steps, grad_scale)
             return
         b1, b2 = self.betas
         gf = g.float() * grad_scale
         self.m.mul_(b1).add_(gf, alpha=1 - b1)
         self.v.mul_(b2).addcmul_(gf, gf, value=1 - b2)
-        w = p.data.float() if self.master is None else self.master
+        w = p.float() if self.master is None else self.master
         denom = (self.v / (1 - b2**self.steps)).sqrt_().add_(self.eps)
         w = w * (1 - self.lr * self.weight_decay) - self.lr * (self.m / (1 - b1**self.steps)) / denom
         if self.master is not None:
             self.master.copy_(w)
-        p.data.copy_(w.to(p.dtype))
+        p.copy_(w.to(p.dtype))
 
     def state_dict(self) -> Dict[str, object]:
         return {"m": self.m, "v": self.v, "master": self.master, "steps": self.steps}
@@ -112,7 +112,7 @@ class GRPOTrainer:
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False) -> None:
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
-        self.opt = FlatAdamW(model.flat, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
+        self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
         self._index_cache: Dict[tuple, tuple] = {}
 
     # -- batch geometry -----------------------------------------------------------------------

@@ -128,39 +128,60 @@ class LlamaModel(nn.Module):
         for name, shape in shapes:
             offsets[name] = total
             total += (math.prod(shape) + 127) // 128 * 128
-        self.flat = nn.Parameter(torch.empty(total, dtype=dtype, device=device))
+        # ``flat`` owns the storage; every nn.Parameter is a view into it, and ``flat_grad`` (allocated by
+        # ``ensure_flat_grad``) plays the same role for the gradients, so autograd accumulates straight
+        # into one contiguous buffer.
+        self.register_buffer("flat", torch.empty(total, dtype=dtype, device=device), persistent=False)
+        self.flat_grad: Optional[torch.Tensor] = None
         self._shapes = dict(shapes)
         self._offsets = offsets
+        self._names = [name for name, _ in shapes]
+        self.params = nn.ParameterList(
+            [nn.Parameter(self._slice(self.flat, name), requires_grad=True) for name in self._names]
+        )
+        self._index = {name: i for i, name in enumerate(self._names)}
         self.reset_parameters(seed)
         cos, sin = rope_cos_sin(torch.arange(max_positions, device=device), cfg.head_dim, cfg.rope_theta)
         self.register_buffer("rope_cos", cos.contiguous(), persistent=False)
         self.register_buffer("rope_sin", sin.contiguous(), persistent=False)
 
     # -- parameters -------------------------------------------------------------------------
-    def view(self, name: str, flat: Optional[torch.Tensor] = None) -> torch.Tensor:
-        flat = self.flat if flat is None else flat
+    def _slice(self, flat: torch.Tensor, name: str) -> torch.Tensor:
         shape = self._shapes[name]
         off = self._offsets[name]
         return flat[off : off + math.prod(shape)].view(shape)
 
-    def named_views(self, flat: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
-        return {name: self.view(name, flat) for name in self._shapes}
+    def view(self, name: str) -> torch.Tensor:
+        """The trainable parameter ``name`` (a view of the flat buffer)."""
+        return self.params[self._index[name]]
+
+    def named_views(self) -> Dict[str, torch.Tensor]:
+        return {name: self.view(name) for name in self._names}
+
+    def ensure_flat_grad(self) -> torch.Tensor:
+        """Allocate the flat gradient buffer once and point every ``param.grad`` into it."""
+        if self.flat_grad is None:
+            self.flat_grad = torch.zeros_like(self.flat)
+            for name in self._names:
+                self.view(name).grad = self._slice(self.flat_grad, name)
+        return self.flat_grad
 
     @torch.no_grad()
     def reset_parameters(self, seed: int = 0) -> None:
-        gen = torch.Generator(device="cpu").manual_seed(seed)
+        dev = self.flat.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
         self.flat.zero_()
         for name, shape in self._shapes.items():
-            dst = self.view(name)
+            dst = self._slice(self.flat, name)
             if name.endswith("norm"):
                 dst.fill_(1.0)
                 continue
-            # chunked host-side init keeps peak host memory small for the 8B configuration
+            # chunked init (on the parameter's own device) keeps the fp32 temporary small
             flat_dst = dst.view(-1)
-            step = 1 << 24
+            step = 1 << 26
             for i in range(0, flat_dst.numel(), step):
                 n = min(step, flat_dst.numel() - i)
-                flat_dst[i : i + n].copy_((torch.randn(n, generator=gen) * 0.02).to(dst.dtype))
+                flat_dst[i : i + n].copy_((torch.randn(n, generator=gen, device=dev) * 0.02).to(dst.dtype))
 
     def state_dict_views(self) -> Dict[str, torch.Tensor]:
         """Checkpoint-format names -> tensors (views of the flat buffer), for the weight bridge."""
@@ -186,9 +207,9 @@ class LlamaModel(nn.Module):
         out = reference_packed_attention(q, k, v, layout.host_seqs, layout.causal, scale)
         return out.reshape(t, cfg.q_dim)
 
-    def _layer(self, x: torch.Tensor, flat: torch.Tensor, index: int, positions: torch.Tensor, layout) -> torch.Tensor:
+    def _layer(self, x: torch.Tensor, index: int, positions: torch.Tensor, layout) -> torch.Tensor:
         cfg = self.cfg
-        p = lambda n: self.view(f"l{index}.{n}", flat)
+        p = lambda n: self.view(f"l{index}.{n}")
         h = rms_norm(x, p("attn_norm"), cfg.rms_eps)
         attn = self._attention(linear(h, p("wqkv")), positions, layout)
         x = x + linear(attn, p("wo"))
@@ -201,14 +222,13 @@ class LlamaModel(nn.Module):
         """Packed ``token_ids [T]`` -> final-norm hidden states ``[T, H]``."""
         from rl_engine.kernels.registry import kernel_registry
 
-        flat = self.flat
-        x = kernel_registry.get_op("embedding")(token_ids, self.view("embed", flat))
+        x = kernel_registry.get_op("embedding")(token_ids, self.view("embed"))
         for i in range(self.cfg.num_layers):
             if self.activation_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(self._layer, x, flat, i, positions, layout, use_reentrant=False)
+                x = checkpoint(self._layer, x, i, positions, layout, use_reentrant=False)
             else:
-                x = self._layer(x, flat, i, positions, layout)
-        return rms_norm(x, self.view("final_norm", flat), self.cfg.rms_eps)
+                x = self._layer(x, i, positions, layout)
+        return rms_norm(x, self.view("final_norm"), self.cfg.rms_eps)
 
     def lm_head_weight(self) -> torch.Tensor:
         return self.view("lm_head")

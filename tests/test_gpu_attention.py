@@ -77,3 +77,49 @@ def test_grpo_group_attention_forward_and_backward(P, G, L, hq, hkv):
     for got, want in ((qa.grad, qb.grad), (ka.grad, kb.grad), (va.grad, vb.grad)):
         scale = want.abs().max().item()
         assert (got.float() - want).abs().max().item() / scale < 3e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("b,s,hq,hkv", [(2, 128, 4, 4), (1, 320, 8, 2), (2, 77, 4, 1)])
+def test_attn_op_backward_matches_sdpa(causal, b, s, hq, hkv):
+    from rl_engine.kernels.ops.pytorch.attention import NativeAttentionOp
+    from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
+
+    q, k, v = _rand((b, s, hq, 128), 11), _rand((b, s, hkv, 128), 12), _rand((b, s, hkv, 128), 13)
+    dout = _rand((b, s, hq, 128), 14)
+    qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
+    FlashAttentionSM100Op()(qa, ka, va, causal=causal).backward(dout)
+    qb, kb, vb = (t.clone().float().requires_grad_(True) for t in (q, k, v))
+    NativeAttentionOp()(qb, kb, vb, causal=causal).backward(dout.float())
+    for got, want in ((qa.grad, qb.grad), (ka.grad, kb.grad), (va.grad, vb.grad)):
+        scale = want.abs().max().item()
+        assert (got.float() - want).abs().max().item() / scale < 3e-2
+    # bitwise reproducible
+    q2, k2, v2 = (t.clone().requires_grad_(True) for t in (q, k, v))
+    FlashAttentionSM100Op()(q2, k2, v2, causal=causal).backward(dout)
+    assert torch.equal(qa.grad, q2.grad) and torch.equal(ka.grad, k2.grad) and torch.equal(va.grad, v2.grad)
+
+
+def test_split_key_tiles_reduce_in_order():
+    """A prompt shared by many completions forces split dK/dV items plus the ordered reduction."""
+    from rl_engine.kernels.ops.pytorch.attention import grouped_prefix_causal_attention_reference
+    from rl_engine.kernels.ops.sm100.attention import grouped_prefix_attention
+
+    P, G, L, hq, hkv = 128, 40, 128, 2, 1   # 80 query blocks per prefix tile > 64 per item
+    T = P + G * L
+    q, k, v = _rand((T, hq, 128), 21), _rand((T, hkv, 128), 22), _rand((T, hkv, 128), 23)
+    dout = _rand((T, hq, 128), 24)
+    qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
+    grouped_prefix_attention(qa, ka, va, P, G, L).backward(dout)
+    qb, kb, vb = (t.clone().float().requires_grad_(True) for t in (q, k, v))
+    oc, _ = grouped_prefix_causal_attention_reference(
+        qb[P:].reshape(G, L, hq, 128), kb[:P], vb[:P], kb[P:].reshape(G, L, hkv, 128), vb[P:].reshape(G, L, hkv, 128)
+    )
+    op = torch.nn.functional.scaled_dot_product_attention(
+        qb[:P].transpose(0, 1), kb[:P].transpose(0, 1).repeat_interleave(hq // hkv, 0),
+        vb[:P].transpose(0, 1).repeat_interleave(hq // hkv, 0), is_causal=True,
+    ).transpose(0, 1)
+    torch.cat([op, oc.reshape(G * L, hq, 128)]).backward(dout.float())
+    for got, want in ((qa.grad, qb.grad), (ka.grad, kb.grad), (va.grad, vb.grad)):
+        scale = want.abs().max().item()
+        assert (got.float() - want).abs().max().item() / scale < 3e-2
