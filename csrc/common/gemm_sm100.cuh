@@ -223,6 +223,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int buf = 0;
     uint32_t buf_phase = 0;
     typename Epi::State st;
+    Epi::start(ep, p);
     for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
       const WorkItem w = decode_item(p, id);
       const int row = w.m_tile * kBM + t.row_in_tile;
@@ -273,6 +274,7 @@ struct EpiStore {
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void finish(const Params&, const GemmProblem&, uint32_t) {}
+  __device__ static void start(const Params&, const GemmProblem&) {}
 
   template <int BN>
   __device__ static void tile(State&, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {

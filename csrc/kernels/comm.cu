@@ -1,0 +1,226 @@
+// Communication kernels over the symmetric heap (plain NVLink peer loads / stores, no NCCL):
+//
+//   peer_barrier       : all ranks of a node meet; every wait is bounded and reports a timeout in the
+//                        error word instead of hanging.
+//   zero1_fused_step   : gradient reduce-scatter + scale + AdamW + parameter all-gather in ONE kernel.
+//                        Rank r owns elements [lo, hi) of the flat parameter vector: it loads that range
+//                        of every peer's bf16 gradient buffer, sums in fixed rank order in fp32, applies
+//                        AdamW on its fp32 moments (and optional fp32 master copy) and stores the new
+//                        bf16 values into every peer's parameter buffer.
+//   peer_sum           : out[i] = sum_r peer_r[i] in fixed rank order (used for the tensor-parallel
+//                        grad_hidden reduction of the vocab-parallel LM head).
+//   cast_broadcast     : weight sync: read a local buffer, cast dtype, store into every peer's buffer.
+//
+// In the reference these are, respectively: nothing; DeepSpeed ZeRO (external, deepspeed_trainer.py:
+// 115-169); an NCCL all-reduce (ops/pytorch/loss/linear_logp.py:331); and per-tensor cuMemcpyDtoD
+// into a VMM allocation (executors/bridge.py:2023-2123).
+#include "../common/ptx.cuh"
+#include "kernels.h"
+
+#include <cuda_fp16.h>
+
+namespace rlk {
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct PeerPtrs {
+  void* p[8];
+};
+
+// pads[r] points at rank r's signal pad (>= world u32 slots).  Thread r publishes `epoch` into slot
+// [my rank] of peer r's pad, then waits until slot [r] of the local pad reaches `epoch`.
+__global__ void peer_barrier_kernel(PeerPtrs pads, int rank, int world, unsigned int epoch,
+                                    unsigned long long limit_ns, uint32_t* err) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  st_release_sys(static_cast<unsigned int*>(pads.p[r]) + rank, epoch);
+  const unsigned int* mine = static_cast<const unsigned int*>(pads.p[rank]) + r;
+  const uint64_t t0 = global_timer_ns();
+  while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
+    if (global_timer_ns() - t0 > limit_ns) {
+      report_error(err, kErrPeerTimeout, 300, static_cast<uint32_t>(r));
+      return;
+    }
+    __nanosleep(100);
+  }
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+
+// [lo, hi) are element indices, multiples of 8.  m / v / master are indexed from 0 at element lo.
+__global__ void __launch_bounds__(256)
+zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int world, long long lo, long long hi, float* __restrict__ m,
+                        float* __restrict__ v, float* __restrict__ master, float lr, float b1, float b2, float eps,
+                        float wd, float bc1, float bc2, float grad_scale) {
+  const long long n8 = (hi - lo) / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = lo + i * 8;
+    float g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = 0.f;
+    for (int r = 0; r < world; ++r) {  // fixed rank order: bitwise identical on every run
+      const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[r]) + e);
+      float f[8];
+      unpack8(q, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] += f[j];
+    }
+    float w[8];
+    if (master != nullptr) {
+      const float4 a = reinterpret_cast<const float4*>(master + i * 8)[0];
+      const float4 b = reinterpret_cast<const float4*>(master + i * 8)[1];
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else {
+      // every rank holds identical parameters; read the local copy
+      unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(params.p[0]) + e), w);
+    }
+    float mm[8], vv[8];
+    {
+      const float4 a = reinterpret_cast<const float4*>(m + i * 8)[0], b = reinterpret_cast<const float4*>(m + i * 8)[1];
+      mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w; mm[4] = b.x; mm[5] = b.y; mm[6] = b.z; mm[7] = b.w;
+      const float4 c = reinterpret_cast<const float4*>(v + i * 8)[0], d = reinterpret_cast<const float4*>(v + i * 8)[1];
+      vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * grad_scale;
+      mm[j] = b1 * mm[j] + (1.f - b1) * gj;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+      const float denom = sqrtf(vv[j] / bc2) + eps;
+      w[j] = w[j] * (1.f - lr * wd) - lr * (mm[j] / bc1) / denom;
+    }
+    reinterpret_cast<float4*>(m + i * 8)[0] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(m + i * 8)[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    reinterpret_cast<float4*>(v + i * 8)[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(v + i * 8)[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    if (master != nullptr) {
+      reinterpret_cast<float4*>(master + i * 8)[0] = make_float4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<float4*>(master + i * 8)[1] = make_float4(w[4], w[5], w[6], w[7]);
+    }
+    const uint4 packed = pack8(w);
+    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = packed;
+  }
+}
+
+// out[i] = sum_r src_r[i]; SRC bf16 or float, OUT bf16 or float; n multiple of 8 for the vector path.
+template <typename TS, typename TO>
+__global__ void peer_sum_kernel(PeerPtrs srcs, int world, long long n, TO* __restrict__ out) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) {
+      if constexpr (sizeof(TS) == 2) acc += __bfloat162float(static_cast<const __nv_bfloat16*>(srcs.p[r])[i]);
+      else acc += static_cast<const float*>(srcs.p[r])[i];
+    }
+    if constexpr (sizeof(TO) == 2) out[i] = __float2bfloat16_rn(acc);
+    else out[i] = acc;
+  }
+}
+
+// dst_r[i] = cast(src[i]) for every peer r.  src dtype code / dst dtype code: 0 f32, 1 bf16, 2 f16.
+template <typename TS, typename TD>
+__global__ void cast_broadcast_kernel(const TS* __restrict__ src, PeerPtrs dsts, int world, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x;
+    if constexpr (sizeof(TS) == 4) x = src[i];
+    else if constexpr (std::is_same<TS, __nv_bfloat16>::value) x = __bfloat162float(src[i]);
+    else x = __half2float(src[i]);
+    TD y;
+    if constexpr (sizeof(TD) == 4) y = x;
+    else if constexpr (std::is_same<TD, __nv_bfloat16>::value) y = __float2bfloat16_rn(x);
+    else y = __float2half_rn(x);
+    for (int r = 0; r < world; ++r) static_cast<TD*>(dsts.p[r])[i] = y;
+  }
+}
+
+PeerPtrs make_ptrs(void* const* p, int world) {
+  PeerPtrs out;
+  for (int r = 0; r < 8; ++r) out.p[r] = r < world ? p[r] : nullptr;
+  return out;
+}
+
+int capped_grid(long long work_items, int threads) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = 148LL * 8;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace
+
+void peer_barrier(void* const* pads, int rank, int world, unsigned int epoch, unsigned long long limit_ns, uint32_t* err,
+                  cudaStream_t stream) {
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(make_ptrs(pads, world), rank, world, epoch, limit_ns, err);
+}
+
+void zero1_fused_step(void* const* grads, void* const* params, int world, long long lo, long long hi, float* m, float* v,
+                      float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                      float grad_scale, cudaStream_t stream) {
+  if (hi <= lo) return;
+  zero1_fused_step_kernel<<<capped_grid((hi - lo) / 8, 256), 256, 0, stream>>>(
+      make_ptrs(grads, world), make_ptrs(params, world), world, lo, hi, m, v, master, lr, b1, b2, eps, wd, bc1, bc2,
+      grad_scale);
+}
+
+void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream) {
+  if (n <= 0) return;
+  const int grid = capped_grid(n, 256);
+  const PeerPtrs p = make_ptrs(srcs, world);
+  if (src_fp32) {
+    if (out_fp32) peer_sum_kernel<float, float><<<grid, 256, 0, stream>>>(p, world, n, static_cast<float*>(out));
+    else peer_sum_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, static_cast<__nv_bfloat16*>(out));
+  } else {
+    if (out_fp32) peer_sum_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(p, world, n, static_cast<float*>(out));
+    else peer_sum_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, static_cast<__nv_bfloat16*>(out));
+  }
+}
+
+void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
+                    cudaStream_t stream) {
+  if (n <= 0) return;
+  const int grid = capped_grid(n, 256);
+  const PeerPtrs p = make_ptrs(dsts, world);
+#define RLK_CB(TS, TD) cast_broadcast_kernel<TS, TD><<<grid, 256, 0, stream>>>(static_cast<const TS*>(src), p, world, n)
+  if (src_dtype == 0) {
+    if (dst_dtype == 0) RLK_CB(float, float);
+    else if (dst_dtype == 1) RLK_CB(float, __nv_bfloat16);
+    else RLK_CB(float, __half);
+  } else if (src_dtype == 1) {
+    if (dst_dtype == 0) RLK_CB(__nv_bfloat16, float);
+    else if (dst_dtype == 1) RLK_CB(__nv_bfloat16, __nv_bfloat16);
+    else RLK_CB(__nv_bfloat16, __half);
+  } else {
+    if (dst_dtype == 0) RLK_CB(__half, float);
+    else if (dst_dtype == 1) RLK_CB(__half, __nv_bfloat16);
+    else RLK_CB(__half, __half);
+  }
+#undef RLK_CB
+}
+
+}  // namespace rlk

@@ -38,7 +38,9 @@ struct LinearLogpFwdArgs {
   long long ld_hidden, ld_weight;
   long long vocab_start;
   int rank, world;
-  void* peer_partials[8];          // per rank: float4 [world * items_per_m, n_pad]
+  int slot_base;      // first record slot of this rank in the partial buffers
+  int total_records;  // records per row over all ranks (0: world * items_per_m)
+  void* peer_partials[8];          // per rank: float4 [total_records, n_pad]
   unsigned int* peer_counters[8];  // per rank: [tiles_m] counters of the set used by this launch
   unsigned int* next_counters;     // local: the set the next launch will use (zeroed here)
   int counter_capacity;            // entries per counter set
@@ -262,5 +264,19 @@ void attention_delta(const __nv_bfloat16* out, const __nv_bfloat16* dout, long l
                      float* delta, cudaStream_t stream);
 void attention_backward_dq(const AttnBwdArgs& args, cudaStream_t stream);
 void attention_backward_dkv(const AttnBwdArgs& args, cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// ------------------------------------------------------------ peer-memory communication kernels
+void peer_barrier(void* const* pads, int rank, int world, unsigned int epoch, unsigned long long limit_ns, uint32_t* err,
+                  cudaStream_t stream);
+void zero1_fused_step(void* const* grads, void* const* params, int world, long long lo, long long hi, float* m, float* v,
+                      float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                      float grad_scale, cudaStream_t stream);
+void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream);
+void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
+                    cudaStream_t stream);
 
 }  // namespace rlk

@@ -29,6 +29,8 @@ struct LogpFwdParams {
   const float* bias;        // [V_local] or null
   long long vocab_start;    // global id of local column 0
   int rank, world;
+  int slot_base;            // first record slot of this rank (sum of the lower ranks' items_per_m)
+  int total_records;        // records per row over all ranks
   int n_pad;                // row pitch of the partial buffers (>= tiles_m * 128)
   float4* peer_partials[kMaxWorld];   // each: [world * items_per_m, n_pad] records (m2, s, t, zt)
   unsigned int* peer_counters[kMaxWorld];  // each: [tiles_m] arrival counters of the current set
@@ -110,7 +112,7 @@ struct EpiLogpStats {
 
   __device__ static void end_item(State& st, const Params& ep, const GemmProblem& p, const WorkItem& w, int row) {
     const float4 rec = make_float4(st.m2, st.s, st.t, st.zt);
-    const size_t slot = static_cast<size_t>(ep.rank * p.items_per_m + w.split) * ep.n_pad + row;
+    const size_t slot = static_cast<size_t>(ep.slot_base + w.split) * ep.n_pad + row;
     for (int r = 0; r < ep.world; ++r) ep.peer_partials[r][slot] = rec;
     __threadfence_system();
     epi_bar_sync();
@@ -127,11 +129,9 @@ struct EpiLogpStats {
 // Merge phase, run by the 128 epilogue threads of each CTA after its GEMM items.
 __device__ void logp_merge_phase(const LogpFwdParams& ep, const GemmProblem& p, uint32_t kernel_id) {
   const int tid = threadIdx.x - 64;  // 0..127
-  const unsigned int expect = static_cast<unsigned int>(ep.world * p.items_per_m);
+  const unsigned int expect = static_cast<unsigned int>(ep.total_records);
   const unsigned int* counters = ep.peer_counters[ep.rank];
   const float4* parts = ep.peer_partials[ep.rank];
-  // zero the other counter set for the next launch (see host side for why this is race free)
-  for (int t = blockIdx.x * 128 + tid; t < ep.counter_capacity; t += gridDim.x * 128) ep.next_counters[t] = 0u;
   for (int t = blockIdx.x; t < p.tiles_m; t += gridDim.x) {
     // bounded wait for all records of row tile t
     unsigned int seen = 0;
@@ -154,7 +154,7 @@ __device__ void logp_merge_phase(const LogpFwdParams& ep, const GemmProblem& p, 
     }
     const int row = t * kBM + tid;
     if (row >= p.M) continue;
-    const int records = ep.world * p.items_per_m;
+    const int records = ep.total_records;
     float M2 = -INFINITY;
     for (int i = 0; i < records; ++i) M2 = fmaxf(M2, parts[static_cast<size_t>(i) * ep.n_pad + row].x);
     float S = 0.f, T = 0.f, ZT = 0.f;
@@ -173,6 +173,15 @@ __device__ void logp_merge_phase(const LogpFwdParams& ep, const GemmProblem& p, 
 }
 
 struct EpiLogpStatsWithMerge : EpiLogpStats {
+  // Zero the counter set of the NEXT launch before this CTA publishes its first arrival.  A peer can
+  // only begin its next launch after it has seen every arrival of this one, so the zeroing is ordered
+  // before any arrival that will ever be counted in that set (every CTA of the grid owns >= 1 item).
+  __device__ static void start(const Params& ep, const GemmProblem&) {
+    const int tid = threadIdx.x - 64;
+    for (int t = blockIdx.x * 128 + tid; t < ep.counter_capacity; t += gridDim.x * 128) ep.next_counters[t] = 0u;
+    __threadfence();
+    epi_bar_sync();
+  }
   __device__ static void finish(const Params& ep, const GemmProblem& p, uint32_t kernel_id) {
     logp_merge_phase(ep, p, kernel_id);
   }
@@ -251,6 +260,7 @@ struct EpiLogpDz {
   }
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void finish(const Params&, const GemmProblem&, uint32_t) {}
+  __device__ static void start(const Params&, const GemmProblem&) {}
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -289,6 +299,8 @@ void linear_logp_forward(const LinearLogpFwdArgs& a, cudaStream_t stream) {
   ep.vocab_start = a.vocab_start;
   ep.rank = a.rank;
   ep.world = a.world;
+  ep.slot_base = a.slot_base;
+  ep.total_records = a.total_records > 0 ? a.total_records : p.items_per_m * a.world;
   ep.n_pad = p.tiles_m * kBM;
   for (int r = 0; r < kMaxWorld; ++r) {
     ep.peer_partials[r] = r < a.world ? reinterpret_cast<float4*>(a.peer_partials[r]) : nullptr;

@@ -119,7 +119,7 @@ std::vector<int64_t> linear_logp_workspace_shape(int64_t n_tokens, int64_t v_loc
 
 std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, const Tensor& target,
                                     std::optional<Tensor> bias, int64_t vocab_start, int64_t rank, int64_t world,
-                                    std::vector<int64_t> peer_partials, std::vector<int64_t> peer_counters,
+                                    int64_t slot_base, int64_t total_records, std::vector<int64_t> peer_partials, std::vector<int64_t> peer_counters,
                                     int64_t next_counters, int64_t counter_capacity, bool want_lse,
                                     bool want_entropy, double wait_limit_ms) {
   check_rowmajor(hidden, "hidden");
@@ -159,6 +159,8 @@ std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, 
   a.vocab_start = vocab_start;
   a.rank = static_cast<int>(rank);
   a.world = static_cast<int>(world);
+  a.slot_base = static_cast<int>(slot_base);
+  a.total_records = static_cast<int>(total_records);
   for (int r = 0; r < world; ++r) {
     a.peer_partials[r] = reinterpret_cast<void*>(peer_partials[r]);
     a.peer_counters[r] = reinterpret_cast<unsigned int*>(peer_counters[r]);

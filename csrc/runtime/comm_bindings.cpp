@@ -1,0 +1,95 @@
+// Python bindings of the peer-memory communication kernels.  Peer buffers are passed as raw device
+// addresses (ints) obtained from SymmetricHeap.ptrs(); local tensors as torch tensors.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cmath>
+#include <vector>
+
+#include "../kernels/kernels.h"
+#include "runtime.h"
+
+namespace rlk {
+
+namespace {
+
+using torch::Tensor;
+
+std::vector<void*> to_ptrs(const std::vector<uint64_t>& addrs) {
+  TORCH_CHECK(!addrs.empty() && addrs.size() <= 8, "rl_engine: need 1..8 peer addresses");
+  std::vector<void*> out;
+  for (auto a : addrs) {
+    TORCH_CHECK(a != 0, "rl_engine: null peer address");
+    out.push_back(reinterpret_cast<void*>(a));
+  }
+  return out;
+}
+
+int dtype_code(torch::ScalarType t) {
+  if (t == torch::kFloat32) return 0;
+  if (t == torch::kBFloat16) return 1;
+  if (t == torch::kFloat16) return 2;
+  TORCH_CHECK(false, "rl_engine: unsupported dtype");
+}
+
+cudaStream_t cur_stream(int device) { return at::cuda::getCurrentCUDAStream(device).stream(); }
+
+void py_peer_barrier(std::vector<uint64_t> pads, int64_t rank, int64_t epoch, double limit_ms, Tensor err_word) {
+  const c10::cuda::CUDAGuard guard(err_word.device());
+  auto p = to_ptrs(pads);
+  peer_barrier(p.data(), static_cast<int>(rank), static_cast<int>(p.size()), static_cast<unsigned int>(epoch),
+               static_cast<unsigned long long>(limit_ms * 1e6), reinterpret_cast<uint32_t*>(err_word.data_ptr<int>()),
+               cur_stream(err_word.get_device()));
+}
+
+void py_zero1_fused_step(std::vector<uint64_t> grads, std::vector<uint64_t> params, int64_t lo, int64_t hi, Tensor m,
+                         Tensor v, std::optional<Tensor> master, double lr, double b1, double b2, double eps, double wd,
+                         int64_t step, double grad_scale) {
+  TORCH_CHECK(lo % 8 == 0 && hi % 8 == 0 && hi >= lo, "rl_engine.zero1: shard bounds must be multiples of 8");
+  TORCH_CHECK(m.is_cuda() && m.scalar_type() == torch::kFloat32 && m.is_contiguous() && m.numel() >= hi - lo &&
+                  v.scalar_type() == torch::kFloat32 && v.is_contiguous() && v.numel() >= hi - lo,
+              "rl_engine.zero1: moments must be contiguous float32 of the shard size");
+  TORCH_CHECK(grads.size() == params.size(), "rl_engine.zero1: need one gradient and one parameter buffer per rank");
+  const c10::cuda::CUDAGuard guard(m.device());
+  float* mp = nullptr;
+  if (master.has_value() && master->defined()) {
+    TORCH_CHECK(master->scalar_type() == torch::kFloat32 && master->is_contiguous() && master->numel() >= hi - lo,
+                "rl_engine.zero1: master shard must be contiguous float32");
+    mp = master->data_ptr<float>();
+  }
+  auto g = to_ptrs(grads);
+  auto p = to_ptrs(params);
+  const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
+  const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
+  zero1_fused_step(g.data(), p.data(), static_cast<int>(g.size()), lo, hi, m.data_ptr<float>(), v.data_ptr<float>(), mp,
+                   static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2), static_cast<float>(eps),
+                   static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), cur_stream(m.get_device()));
+}
+
+void py_peer_sum(std::vector<uint64_t> srcs, int64_t n, bool src_fp32, Tensor out) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() >= n, "rl_engine.peer_sum: out too small");
+  const c10::cuda::CUDAGuard guard(out.device());
+  auto s = to_ptrs(srcs);
+  peer_sum(s.data(), static_cast<int>(s.size()), n, src_fp32, out.data_ptr(), out.scalar_type() == torch::kFloat32,
+           cur_stream(out.get_device()));
+}
+
+void py_cast_broadcast(const Tensor& src, std::vector<uint64_t> dsts, int64_t dst_dtype_code) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "rl_engine.cast_broadcast: src must be a contiguous CUDA tensor");
+  const c10::cuda::CUDAGuard guard(src.device());
+  auto d = to_ptrs(dsts);
+  cast_broadcast(src.data_ptr(), dtype_code(src.scalar_type()), d.data(), static_cast<int>(dst_dtype_code),
+                 static_cast<int>(d.size()), src.numel(), cur_stream(src.get_device()));
+}
+
+}  // namespace
+
+void bind_comm(pybind11::module_& m) {
+  m.def("peer_barrier", &py_peer_barrier);
+  m.def("zero1_fused_step", &py_zero1_fused_step);
+  m.def("peer_sum", &py_peer_sum);
+  m.def("cast_broadcast", &py_cast_broadcast);
+}
+
+}  // namespace rlk

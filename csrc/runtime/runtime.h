@@ -5,4 +5,6 @@
 
 namespace rlk {
 void bind_runtime(pybind11::module_& m);
-}
+void bind_symmetric_heap(pybind11::module_& m);
+void bind_comm(pybind11::module_& m);
+}  // namespace rlk

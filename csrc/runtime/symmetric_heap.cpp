@@ -1,0 +1,190 @@
+// Symmetric heap: one CUDA virtual-memory allocation per rank, exported as a POSIX file descriptor
+// and mapped by every peer of the node, so kernels can load/store any rank's segment over
+// NVLink / NVSwitch with ordinary pointers (no NCCL, no NVSHMEM).
+//
+// The driver API is resolved at run time through the CUDA runtime, so the extension has no link-time
+// dependency on libcuda.  File descriptors travel between processes over a unix socket (SCM_RIGHTS);
+// that part lives in Python (rl_engine/parallel/symmetric.py).
+//
+// The reference reaches the same driver calls through ctypes for its weight bridge
+// (rl_engine/executors/bridge.py:985-1332); this is the native equivalent and also serves the
+// fused compute+communication kernels.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "runtime.h"
+
+namespace rlk {
+
+namespace {
+
+template <class Fn>
+Fn driver_fn(const char* name) {
+  cudaFree(nullptr);  // make sure the primary context exists and is current
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p)
+    throw std::runtime_error(std::string("rl_engine: CUDA driver entry point not found: ") + name);
+  return reinterpret_cast<Fn>(p);
+}
+
+void check(CUresult r, const char* what) {
+  if (r != CUDA_SUCCESS) throw std::runtime_error(std::string("rl_engine: ") + what + " failed with CUresult " + std::to_string(int(r)));
+}
+
+struct Driver {
+  CUresult (*memCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long);
+  CUresult (*memRelease)(CUmemGenericAllocationHandle);
+  CUresult (*memGetGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags);
+  CUresult (*memAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long);
+  CUresult (*memAddressFree)(CUdeviceptr, size_t);
+  CUresult (*memMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+  CUresult (*memUnmap)(CUdeviceptr, size_t);
+  CUresult (*memSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t);
+  CUresult (*memExport)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long);
+  CUresult (*memImport)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType);
+
+  static const Driver& get() {
+    static Driver d = [] {
+      Driver x;
+      x.memCreate = driver_fn<decltype(x.memCreate)>("cuMemCreate");
+      x.memRelease = driver_fn<decltype(x.memRelease)>("cuMemRelease");
+      x.memGetGranularity = driver_fn<decltype(x.memGetGranularity)>("cuMemGetAllocationGranularity");
+      x.memAddressReserve = driver_fn<decltype(x.memAddressReserve)>("cuMemAddressReserve");
+      x.memAddressFree = driver_fn<decltype(x.memAddressFree)>("cuMemAddressFree");
+      x.memMap = driver_fn<decltype(x.memMap)>("cuMemMap");
+      x.memUnmap = driver_fn<decltype(x.memUnmap)>("cuMemUnmap");
+      x.memSetAccess = driver_fn<decltype(x.memSetAccess)>("cuMemSetAccess");
+      x.memExport = driver_fn<decltype(x.memExport)>("cuMemExportToShareableHandle");
+      x.memImport = driver_fn<decltype(x.memImport)>("cuMemImportFromShareableHandle");
+      return x;
+    }();
+    return d;
+  }
+};
+
+class SymmetricHeap {
+ public:
+  SymmetricHeap(int device, size_t bytes, int rank, int world)
+      : device_(device), rank_(rank), world_(world), handles_(world, 0), bases_(world, 0), mapped_(world, false) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) throw std::invalid_argument("SymmetricHeap: bad rank/world");
+    cudaSetDevice(device);
+    const Driver& d = Driver::get();
+    CUmemAllocationProp prop = {};
+    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    prop.location.id = device;
+    prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    size_t gran = 0;
+    check(d.memGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
+    size_ = (bytes + gran - 1) / gran * gran;
+    check(d.memCreate(&handles_[rank], size_, &prop, 0), "cuMemCreate");
+    map(rank);
+    cudaMemset(reinterpret_cast<void*>(bases_[rank]), 0, size_);
+    cudaDeviceSynchronize();
+  }
+
+  ~SymmetricHeap() { close(); }
+
+  int export_fd() {
+    int fd = -1;
+    check(Driver::get().memExport(&fd, handles_[rank_], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+          "cuMemExportToShareableHandle");
+    return fd;
+  }
+
+  void import_peer(int peer, int fd) {
+    if (peer < 0 || peer >= world_ || peer == rank_) throw std::invalid_argument("SymmetricHeap: bad peer rank");
+    if (mapped_[peer]) throw std::runtime_error("SymmetricHeap: peer already imported");
+    cudaSetDevice(device_);
+    check(Driver::get().memImport(&handles_[peer], reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                  CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+          "cuMemImportFromShareableHandle");
+    map(peer);
+  }
+
+  uint64_t ptr(int r) const {
+    if (r < 0 || r >= world_ || !mapped_[r]) throw std::invalid_argument("SymmetricHeap: rank not mapped");
+    return static_cast<uint64_t>(bases_[r]);
+  }
+  std::vector<uint64_t> ptrs() const {
+    std::vector<uint64_t> out;
+    for (int r = 0; r < world_; ++r) out.push_back(mapped_[r] ? static_cast<uint64_t>(bases_[r]) : 0);
+    return out;
+  }
+  size_t size() const { return size_; }
+  int rank() const { return rank_; }
+  int world() const { return world_; }
+
+  // A tensor aliasing [offset, offset + numel * itemsize) of rank r's segment.  The heap must outlive it.
+  torch::Tensor tensor(int r, size_t offset, std::vector<int64_t> shape, torch::ScalarType dtype) const {
+    int64_t numel = 1;
+    for (auto s : shape) numel *= s;
+    const size_t bytes = static_cast<size_t>(numel) * c10::elementSize(dtype);
+    if (offset + bytes > size_) throw std::out_of_range("SymmetricHeap: tensor exceeds the segment");
+    void* p = reinterpret_cast<void*>(ptr(r) + offset);
+    return torch::from_blob(p, shape, torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device_));
+  }
+
+  void close() {
+    const Driver& d = Driver::get();
+    cudaSetDevice(device_);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < world_; ++r) {
+      if (mapped_[r]) {
+        d.memUnmap(bases_[r], size_);
+        d.memAddressFree(bases_[r], size_);
+        mapped_[r] = false;
+      }
+      if (handles_[r]) {
+        d.memRelease(handles_[r]);
+        handles_[r] = 0;
+      }
+    }
+  }
+
+ private:
+  void map(int r) {
+    const Driver& d = Driver::get();
+    check(d.memAddressReserve(&bases_[r], size_, 0, 0, 0), "cuMemAddressReserve");
+    check(d.memMap(bases_[r], size_, 0, handles_[r], 0), "cuMemMap");
+    CUmemAccessDesc access = {};
+    access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    access.location.id = device_;
+    access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    check(d.memSetAccess(bases_[r], size_, &access, 1), "cuMemSetAccess");
+    mapped_[r] = true;
+  }
+
+  int device_, rank_, world_;
+  size_t size_ = 0;
+  std::vector<CUmemGenericAllocationHandle> handles_;
+  std::vector<CUdeviceptr> bases_;
+  std::vector<bool> mapped_;
+};
+
+}  // namespace
+
+void bind_symmetric_heap(pybind11::module_& m) {
+  namespace py = pybind11;
+  py::class_<SymmetricHeap>(m, "SymmetricHeap")
+      .def(py::init<int, size_t, int, int>(), py::arg("device"), py::arg("bytes"), py::arg("rank"), py::arg("world"))
+      .def("export_fd", &SymmetricHeap::export_fd)
+      .def("import_peer", &SymmetricHeap::import_peer)
+      .def("ptr", &SymmetricHeap::ptr)
+      .def("ptrs", &SymmetricHeap::ptrs)
+      .def("size", &SymmetricHeap::size)
+      .def("rank", &SymmetricHeap::rank)
+      .def("world", &SymmetricHeap::world)
+      .def("tensor", &SymmetricHeap::tensor)
+      .def("close", &SymmetricHeap::close);
+}
+
+}  // namespace rlk

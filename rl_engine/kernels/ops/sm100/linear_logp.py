@@ -82,7 +82,7 @@ def _forward_local(hidden2d, weight, target, bias, want_lse: bool, want_entropy:
     ws.ensure(items, n_pad, tiles_m)
     cur, nxt, cap = ws.next_sets()
     return ext.linear_logp_fwd(
-        hidden2d, weight, target, bias, 0, 0, 1, [ws.partials.data_ptr()], [cur], nxt, cap, want_lse, want_entropy, 0.0
+        hidden2d, weight, target, bias, 0, 0, 1, 0, items, [ws.partials.data_ptr()], [cur], nxt, cap, want_lse, want_entropy, 0.0
     )
 
 

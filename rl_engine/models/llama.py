@@ -158,6 +158,22 @@ class LlamaModel(nn.Module):
     def named_views(self) -> Dict[str, torch.Tensor]:
         return {name: self.view(name) for name in self._names}
 
+    @torch.no_grad()
+    def rebind_storage(self, flat: torch.Tensor, flat_grad: Optional[torch.Tensor] = None) -> None:
+        """Move parameters (and gradients) onto caller-provided flat buffers, e.g. symmetric memory.
+
+        ``flat`` must already hold the parameter values."""
+        if flat.numel() != self.flat.numel() or flat.dtype != self.flat.dtype:
+            raise ValueError("replacement storage must match the flat parameter buffer")
+        self.flat = flat
+        for name in self._names:
+            self.view(name).data = self._slice(flat, name)
+        if flat_grad is not None:
+            flat_grad.zero_()
+            self.flat_grad = flat_grad
+            for name in self._names:
+                self.view(name).grad = self._slice(flat_grad, name)
+
     def ensure_flat_grad(self) -> torch.Tensor:
         """Allocate the flat gradient buffer once and point every ``param.grad`` into it."""
         if self.flat_grad is None:

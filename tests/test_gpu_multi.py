@@ -1,0 +1,58 @@
+"""Multi-GPU checks (skipped with fewer than two GPUs) and the single-GPU bounded-wait test."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_peer_wait_is_bounded_and_reports():
+    """A barrier whose peer never arrives must return within its limit and leave the context usable."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    ext = require_ext()
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    absent_peer = torch.zeros(64, dtype=torch.int32, device="cuda")  # nothing ever raises its flag for us
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    ext.peer_barrier([mine.data_ptr(), absent_peer.data_ptr()], 0, 1, 30.0, err)
+    stop.record()
+    torch.cuda.synchronize()
+    assert 20.0 < start.elapsed_time(stop) < 2000.0
+    code, kernel, _block, site = err.tolist()
+    assert code == 2 and kernel == 300 and site == 1
+    # the context is still healthy
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0
+
+
+def test_symmetric_memory_single_rank_and_timeout_error():
+    from rl_engine.parallel.symmetric import SymmetricMemory
+
+    mem = SymmetricMemory(1 << 20)
+    a = mem.alloc((256,), torch.float32)
+    b = mem.alloc((3, 5), torch.bfloat16)
+    assert a.local.data_ptr() % 256 == 0 and b.local.data_ptr() % 256 == 0 and b.local.shape == (3, 5)
+    a.local.fill_(3.0)
+    mem.barrier()
+    mem.check()
+    assert float(a.peer(0).sum()) == 768.0
+    with pytest.raises(MemoryError):
+        mem.alloc((1 << 30,), torch.float32)
+    mem.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_parallel_checks_two_ranks():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [
+        sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+        "--master-port", "29731", os.path.join(ROOT, "tests", "multigpu", "run_parallel_checks.py"),
+    ]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "ALL OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
