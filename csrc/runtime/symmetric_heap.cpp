@@ -125,12 +125,24 @@ class SymmetricHeap {
 
   // A tensor aliasing [offset, offset + numel * itemsize) of rank r's segment.  The heap must outlive it.
   torch::Tensor tensor(int r, size_t offset, std::vector<int64_t> shape, torch::ScalarType dtype) const {
+    if (r != rank_) throw std::invalid_argument("SymmetricHeap.tensor: only the local segment can be viewed; use read_peer");
     int64_t numel = 1;
     for (auto s : shape) numel *= s;
     const size_t bytes = static_cast<size_t>(numel) * c10::elementSize(dtype);
     if (offset + bytes > size_) throw std::out_of_range("SymmetricHeap: tensor exceeds the segment");
     void* p = reinterpret_cast<void*>(ptr(r) + offset);
     return torch::from_blob(p, shape, torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device_));
+  }
+
+  // A local copy of a window of rank r's segment (debugging / tests; kernels use the raw pointers).
+  torch::Tensor read_peer(int r, size_t offset, std::vector<int64_t> shape, torch::ScalarType dtype) const {
+    torch::Tensor out = torch::empty(shape, torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device_));
+    const size_t bytes = static_cast<size_t>(out.numel()) * c10::elementSize(dtype);
+    if (offset + bytes > size_) throw std::out_of_range("SymmetricHeap: window exceeds the segment");
+    cudaSetDevice(device_);
+    cudaError_t e = cudaMemcpy(out.data_ptr(), reinterpret_cast<const void*>(ptr(r) + offset), bytes, cudaMemcpyDefault);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("SymmetricHeap: peer copy failed: ") + cudaGetErrorString(e));
+    return out;
   }
 
   void close() {
@@ -184,6 +196,7 @@ void bind_symmetric_heap(pybind11::module_& m) {
       .def("rank", &SymmetricHeap::rank)
       .def("world", &SymmetricHeap::world)
       .def("tensor", &SymmetricHeap::tensor)
+      .def("read_peer", &SymmetricHeap::read_peer)
       .def("close", &SymmetricHeap::close);
 }
 

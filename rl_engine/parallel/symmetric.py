@@ -143,7 +143,10 @@ class SymmetricTensor:
         self.local = mem.heap.tensor(mem.rank, offset, list(shape), dtype)
 
     def peer(self, rank: int) -> torch.Tensor:
-        return self.mem.heap.tensor(rank, self.offset, list(self.shape), self.dtype)
+        """A local COPY of rank ``rank``'s window (for tests and debugging; kernels use ``ptrs``)."""
+        if rank == self.mem.rank:
+            return self.local.clone()
+        return self.mem.heap.read_peer(rank, self.offset, list(self.shape), self.dtype)
 
     @property
     def ptrs(self) -> List[int]:
