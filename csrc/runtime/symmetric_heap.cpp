@@ -182,10 +182,87 @@ class SymmetricHeap {
   std::vector<bool> mapped_;
 };
 
+// One CUDA VMM allocation that can be handed to another process on the same node as a POSIX file
+// descriptor: the publisher side of the weight bridge creates it, a consumer opens the descriptor and
+// maps the same physical memory (zero copy).  Reference analogue: rl_engine/executors/bridge.py:
+// 1207-1332 (ctypes calls into libcuda).
+class VmmSegment {
+ public:
+  // fd < 0: create a fresh allocation of >= bytes; fd >= 0: map the allocation behind the descriptor.
+  VmmSegment(int device, size_t bytes, int fd) : device_(device) {
+    cudaSetDevice(device);
+    const Driver& d = Driver::get();
+    CUmemAllocationProp prop = {};
+    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    prop.location.id = device;
+    prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    size_t gran = 0;
+    check(d.memGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED), "cuMemGetAllocationGranularity");
+    size_ = (bytes + gran - 1) / gran * gran;
+    if (size_ == 0) size_ = gran;
+    if (fd < 0) {
+      check(d.memCreate(&handle_, size_, &prop, 0), "cuMemCreate");
+    } else {
+      check(d.memImport(&handle_, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                        CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
+            "cuMemImportFromShareableHandle");
+    }
+    check(d.memAddressReserve(&base_, size_, 0, 0, 0), "cuMemAddressReserve");
+    check(d.memMap(base_, size_, 0, handle_, 0), "cuMemMap");
+    CUmemAccessDesc access = {};
+    access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    access.location.id = device;
+    access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    check(d.memSetAccess(base_, size_, &access, 1), "cuMemSetAccess");
+    open_ = true;
+  }
+  ~VmmSegment() { close(); }
+
+  int export_fd() {
+    int fd = -1;
+    check(Driver::get().memExport(&fd, handle_, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0), "cuMemExportToShareableHandle");
+    return fd;
+  }
+  uint64_t ptr() const { return static_cast<uint64_t>(base_); }
+  size_t size() const { return size_; }
+  torch::Tensor tensor(size_t offset, std::vector<int64_t> shape, std::vector<int64_t> strides, torch::ScalarType dtype) const {
+    if (!open_) throw std::runtime_error("VmmSegment: closed");
+    void* p = reinterpret_cast<void*>(base_ + offset);
+    auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device_);
+    return strides.empty() ? torch::from_blob(p, shape, opts) : torch::from_blob(p, shape, strides, opts);
+  }
+  void close() {
+    if (!open_) return;
+    const Driver& d = Driver::get();
+    cudaSetDevice(device_);
+    cudaDeviceSynchronize();
+    d.memUnmap(base_, size_);
+    d.memAddressFree(base_, size_);
+    d.memRelease(handle_);
+    open_ = false;
+  }
+
+ private:
+  int device_;
+  size_t size_ = 0;
+  CUmemGenericAllocationHandle handle_ = 0;
+  CUdeviceptr base_ = 0;
+  bool open_ = false;
+};
+
 }  // namespace
 
 void bind_symmetric_heap(pybind11::module_& m) {
   namespace py = pybind11;
+  py::class_<VmmSegment>(m, "VmmSegment")
+      .def(py::init<int, size_t, int>(), py::arg("device"), py::arg("bytes"), py::arg("fd") = -1)
+      .def("export_fd", &VmmSegment::export_fd)
+      .def("ptr", &VmmSegment::ptr)
+      .def("size", &VmmSegment::size)
+      .def("tensor", &VmmSegment::tensor, py::arg("offset"), py::arg("shape"), py::arg("strides") = std::vector<int64_t>{},
+           py::arg("dtype"))
+      .def("close", &VmmSegment::close);
   py::class_<SymmetricHeap>(m, "SymmetricHeap")
       .def(py::init<int, size_t, int, int>(), py::arg("device"), py::arg("bytes"), py::arg("rank"), py::arg("world"))
       .def("export_fd", &SymmetricHeap::export_fd)

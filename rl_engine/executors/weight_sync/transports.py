@@ -1,0 +1,528 @@
+"""Weight transports on top of the common life cycle.
+
+* ``LocalTensorCopyBridge``   ``local-clone``     clones on publish and on import (safe default);
+* ``SharedMemoryTensorBridge`` ``shared-memory``  one POSIX shared-memory segment per CPU tensor,
+  zero-copy views on import, attachable from another process by manifest alone;
+* ``CUDAVMMTensorBridge``     ``cuda-vmm``        the whole state packed into ONE CUDA VMM allocation
+  (256-byte aligned), handed to consumers as a POSIX fd over a unix socket, cross-process ordering via
+  an interprocess CUDA event; consumers alias the memory (zero copy);
+* ``IPCWeightBridge``         ``cuda-ipc``        legacy CUDA-IPC handles from ``reduce_tensor``;
+* ``NVLinkBroadcastBridge``   ``nvlink-broadcast`` NEW: the trainer's packed state is cast and stored into
+  every rank's symmetric-memory window by one kernel (``cast_broadcast``) -- multi-GPU, no NCCL;
+* ``FileBlobBridge``          ``file``            NEW: the same packed blob + a JSON manifest on disk
+  (this is also the checkpoint format).
+
+Reference: ``rl_engine/executors/bridge.py:1508-2659``.  Metadata blocks under
+``metadata["weight_bridge"]`` keep the reference's keys and format tags for the transports it has.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import socket
+import tempfile
+import threading
+from multiprocessing import shared_memory
+from typing import Any, Dict, Mapping, Optional, Tuple
+
+import torch
+
+from rl_engine.executors.weight_sync.protocol import (
+    BRIDGE_METADATA_KEY, CUDA_IPC_FORMAT, CUDA_VMM_FORMAT, FILE_BLOB_FORMAT, NVLINK_BROADCAST_FORMAT,
+    SHARED_MEMORY_FORMAT, TENSOR_ALIGNMENT, BridgeStateMachine, TensorDescriptor, UpdateRecord,
+    WeightBridgeUnavailableError, WeightManifestValidationError, WeightUpdateManifest, WeightUpdateRejectedError,
+)
+
+_DTYPES = {str(d): d for d in (
+    torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8, torch.uint8, torch.int16, torch.int32,
+    torch.int64, torch.bool,
+)}
+
+
+def _clone(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().clone(memory_format=torch.preserve_format)
+
+
+def pack_layout(tensors: Mapping[str, torch.Tensor], alignment: int = TENSOR_ALIGNMENT) -> Tuple[Dict[str, Dict], int]:
+    """Offsets of every tensor inside one blob, each aligned to ``alignment`` bytes."""
+    entries: Dict[str, Dict[str, Any]] = {}
+    cursor = 0
+    for name, t in tensors.items():
+        cursor = (cursor + alignment - 1) // alignment * alignment
+        nbytes = t.numel() * t.element_size()
+        entries[name] = {"offset": cursor, "nbytes": nbytes, "shape": [int(d) for d in t.shape], "dtype": str(t.dtype)}
+        cursor += nbytes
+    return entries, cursor
+
+
+# ---------------------------------------------------------------------------------- local clone
+class LocalTensorCopyBridge(BridgeStateMachine):
+    transport = "local-clone"
+
+    def _capture(self, tensors, update_id):
+        return {n: _clone(t) for n, t in tensors.items()}, None, {}
+
+    def _hand_out(self, record: UpdateRecord):
+        return {n: _clone(t) for n, t in record.tensors.items()}
+
+
+# -------------------------------------------------------------------------------- shared memory
+def _open_segment(name: Optional[str], size: int = 0, create: bool = False) -> shared_memory.SharedMemory:
+    kwargs: Dict[str, Any] = {}
+    try:  # python >= 3.13: do not let the resource tracker unlink a segment we only attach to
+        import inspect
+
+        if "track" in inspect.signature(shared_memory.SharedMemory).parameters and not create:
+            kwargs["track"] = False
+    except (TypeError, ValueError):
+        pass
+    if create:
+        return shared_memory.SharedMemory(create=True, size=max(size, 1))
+    seg = shared_memory.SharedMemory(name=name, **kwargs)
+    if "track" not in kwargs:
+        try:  # older pythons register attachments too; undo that so only the creator unlinks
+            from multiprocessing import resource_tracker
+
+            resource_tracker.unregister(seg._name, "shared_memory")  # type: ignore[attr-defined]
+        except Exception:
+            pass
+    return seg
+
+
+class SharedMemoryTensorBridge(BridgeStateMachine):
+    transport = "shared-memory"
+
+    def _capture(self, tensors, update_id):
+        views: Dict[str, torch.Tensor] = {}
+        segments: Dict[str, shared_memory.SharedMemory] = {}
+        meta: Dict[str, Dict[str, Any]] = {}
+        try:
+            for name, t in tensors.items():
+                if t.device.type != "cpu":
+                    raise WeightBridgeUnavailableError(
+                        f"SharedMemoryTensorBridge currently supports CPU tensors only. Tensor {name} is on {t.device}."
+                    )
+                snap = t.detach().contiguous()
+                nbytes = snap.numel() * snap.element_size()
+                if snap.numel() == 0:
+                    views[name] = torch.empty_like(snap)
+                    meta[name] = {"name": None, "size": 0, "storage_numel": 0, "storage_nbytes": 0, "storage_offset": 0}
+                    continue
+                seg = _open_segment(None, nbytes, create=True)
+                segments[name] = seg
+                view = torch.frombuffer(seg.buf, dtype=snap.dtype, count=snap.numel()).view(snap.shape)
+                view.copy_(snap)
+                views[name] = view
+                meta[name] = {"name": seg.name, "size": int(seg.size), "storage_numel": snap.numel(),
+                              "storage_nbytes": nbytes, "storage_offset": 0}
+        except Exception:
+            for seg in segments.values():
+                seg.close()
+                seg.unlink()
+            raise
+        return views, {"format": SHARED_MEMORY_FORMAT, "tensors": meta}, {"segments": segments, "owner": True}
+
+    def _hand_out(self, record: UpdateRecord):
+        return dict(record.tensors)  # zero copy: the same shared pages
+
+    def _attach(self, manifest: WeightUpdateManifest) -> UpdateRecord:
+        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
+        if not isinstance(block, Mapping) or block.get("format") != SHARED_MEMORY_FORMAT:
+            raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        views, segments = {}, {}
+        try:
+            for name, desc in manifest.tensors.items():
+                info = block["tensors"][name]
+                dtype = _DTYPES[desc.dtype]
+                if not info["name"]:
+                    views[name] = torch.empty(desc.shape, dtype=dtype)
+                    continue
+                seg = _open_segment(info["name"])
+                segments[name] = seg
+                views[name] = torch.frombuffer(seg.buf, dtype=dtype, count=desc.numel).view(desc.shape)
+        except FileNotFoundError:
+            for seg in segments.values():
+                seg.close()
+            raise
+        return UpdateRecord(manifest=manifest, tensors=views, resources={"segments": segments, "owner": False})
+
+    def _dispose(self, record: UpdateRecord) -> None:
+        record.tensors.clear()
+        for seg in record.resources.get("segments", {}).values():
+            try:
+                seg.close()
+            except BufferError:
+                pass  # a consumer still holds a view; the mapping goes away with it
+            if record.resources.get("owner"):
+                try:
+                    seg.unlink()
+                except FileNotFoundError:
+                    pass
+
+
+# ------------------------------------------------------------------------------------- CUDA VMM
+def _serve_fd_forever(server: socket.socket, fd: int, stop: threading.Event) -> None:
+    server.settimeout(0.2)
+    while not stop.is_set():
+        try:
+            conn, _ = server.accept()
+        except socket.timeout:
+            continue
+        except OSError:
+            return
+        with conn:
+            try:
+                socket.send_fds(conn, [b"fd"], [fd])
+            except OSError:
+                pass
+
+
+class CUDAVMMTensorBridge(BridgeStateMachine):
+    """One VMM allocation per update, shared by POSIX fd.  ``backend_factory`` is injectable for tests."""
+
+    transport = "cuda-vmm"
+
+    def __init__(self, *, source_worker="local-training", source_rank=0, device_index: Optional[int] = None,
+                 backend_factory=None) -> None:
+        super().__init__(source_worker=source_worker, source_rank=source_rank)
+        self.device_index = device_index
+        self._backend_factory = backend_factory
+
+    def _segment(self, device: int, nbytes: int, fd: int = -1):
+        if self._backend_factory is not None:
+            return self._backend_factory(device, nbytes, fd)
+        from rl_engine.kernels.ops.base import require_ext
+
+        return require_ext().VmmSegment(device, nbytes, fd)
+
+    def _capture(self, tensors, update_id):
+        if not torch.cuda.is_available() and self._backend_factory is None:
+            raise WeightBridgeUnavailableError("CUDAVMMTensorBridge requires a CUDA device")
+        for name, t in tensors.items():
+            if t.device.type != "cuda" and self._backend_factory is None:
+                raise WeightBridgeUnavailableError(f"CUDAVMMTensorBridge needs CUDA tensors; {name} is on {t.device}")
+        device = self.device_index if self.device_index is not None else (
+            next(iter(tensors.values())).device.index or 0)
+        entries, total = pack_layout(tensors)
+        seg = self._segment(device, max(total, 1))
+        stored: Dict[str, torch.Tensor] = {}
+        for name, t in tensors.items():
+            e = entries[name]
+            dst = seg.tensor(e["offset"], e["shape"], [], t.dtype)
+            dst.copy_(t.detach())
+            stored[name] = dst
+        event_handle = None
+        if torch.cuda.is_available() and self._backend_factory is None:
+            ev = torch.cuda.Event(interprocess=True)
+            ev.record(torch.cuda.current_stream(device))
+            event_handle = ev.ipc_handle()
+        fd = seg.export_fd()
+        path = os.path.join(tempfile.gettempdir(), f"kernel-align-cuda-vmm-{os.getpid()}-{update_id}.sock")
+        server = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        server.bind(path)
+        server.listen(16)
+        stop = threading.Event()
+        thread = threading.Thread(target=_serve_fd_forever, args=(server, fd, stop), daemon=True)
+        thread.start()
+        block = {"format": CUDA_VMM_FORMAT, "socket_path": path, "mapped_nbytes": int(seg.size()),
+                 "requested_nbytes": int(total), "device_index": int(device), "ipc_event_handle": event_handle,
+                 "tensors": entries}
+        return stored, block, {"segment": seg, "fd": fd, "server": server, "stop": stop, "thread": thread, "path": path}
+
+    def _hand_out(self, record: UpdateRecord):
+        return dict(record.tensors)
+
+    def _attach(self, manifest: WeightUpdateManifest) -> UpdateRecord:
+        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
+        if not isinstance(block, Mapping) or block.get("format") != CUDA_VMM_FORMAT:
+            raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        try:
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as client:
+                client.settimeout(30.0)
+                client.connect(block["socket_path"])
+                _msg, fds, _f, _a = socket.recv_fds(client, 16, 1)
+        except OSError as exc:
+            raise WeightUpdateRejectedError(
+                f"cannot reach the publisher of update {manifest.update_id}: {exc}"
+            ) from exc
+        if not fds:
+            raise WeightUpdateRejectedError(f"publisher sent no file descriptor for update {manifest.update_id}")
+        device = int(block["device_index"])
+        try:
+            seg = self._segment(device, int(block["mapped_nbytes"]), fds[0])
+        finally:
+            os.close(fds[0])
+        if block.get("ipc_event_handle") is not None and torch.cuda.is_available():
+            ev = torch.cuda.Event.from_ipc_handle(torch.device("cuda", device), block["ipc_event_handle"])
+            ev.wait(torch.cuda.current_stream(device))
+        views = {}
+        for name, desc in manifest.tensors.items():
+            e = block["tensors"][name]
+            views[name] = seg.tensor(int(e["offset"]), list(desc.shape), [], _DTYPES[desc.dtype])
+        return UpdateRecord(manifest=manifest, tensors=views, resources={"segment": seg})
+
+    def _dispose(self, record: UpdateRecord) -> None:
+        record.tensors.clear()
+        res = record.resources
+        if "stop" in res:
+            res["stop"].set()
+            try:
+                res["server"].close()
+            except OSError:
+                pass
+            res["thread"].join(timeout=2.0)
+            for cleanup in (lambda: os.close(res["fd"]), lambda: os.unlink(res["path"])):
+                try:
+                    cleanup()
+                except OSError:
+                    pass
+        seg = res.get("segment")
+        if seg is not None:
+            seg.close()
+
+
+# ------------------------------------------------------------------------------------- CUDA IPC
+class IPCWeightBridge(BridgeStateMachine):
+    """Legacy transport: per-tensor CUDA IPC handles from ``torch.multiprocessing.reductions``."""
+
+    transport = "cuda-ipc"
+
+    def __init__(self, *, source_worker="local-training", source_rank=0, reduce_tensor=None) -> None:
+        super().__init__(source_worker=source_worker, source_rank=source_rank)
+        self._reduce_tensor = reduce_tensor
+
+    def _reduce(self):
+        if self._reduce_tensor is not None:
+            return self._reduce_tensor
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        return reduce_tensor
+
+    @staticmethod
+    def _gpu_uuid() -> str:
+        if not torch.cuda.is_available():
+            return "cpu"
+        return str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+
+    def _capture(self, tensors, update_id):
+        stored = {n: t.detach().contiguous() for n, t in tensors.items()}
+        reduce = self._reduce()
+        handles = {n: {"handle": reduce(t)} for n, t in stored.items()}
+        block = {"format": CUDA_IPC_FORMAT, "device_index": int(torch.cuda.current_device()) if torch.cuda.is_available() else 0,
+                 "gpu_uuid": self._gpu_uuid(), "tensors": handles}
+        return stored, block, {"keepalive": list(stored.values())}
+
+    def _hand_out(self, record: UpdateRecord):
+        return dict(record.tensors)
+
+    def _attach(self, manifest: WeightUpdateManifest) -> UpdateRecord:
+        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
+        if not isinstance(block, Mapping) or block.get("format") != CUDA_IPC_FORMAT:
+            raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        views = {}
+        for name in manifest.tensors:
+            rebuild, args = block["tensors"][name]["handle"]
+            args = list(args)
+            if len(args) > 6 and isinstance(args[6], int):
+                args[6] = device  # the device index travels in slot 6 of rebuild_cuda_tensor's arguments
+            views[name] = rebuild(*args)
+        return UpdateRecord(manifest=manifest, tensors=views)
+
+    # legacy entry points used by the reference's perf script (scripts/run_perf.py:65-69)
+    def export_model_handles(self, model) -> Mapping[str, Any]:
+        reduce = self._reduce()
+        self._legacy_keepalive = {n: t.detach().contiguous() for n, t in model.state_dict().items()}
+        return {n: reduce(t) for n, t in self._legacy_keepalive.items()}
+
+    def import_model_weights(self, handles: Mapping[str, Any]) -> Dict[str, torch.Tensor]:
+        return {n: rebuild(*args) for n, (rebuild, args) in handles.items()}
+
+
+# ----------------------------------------------------------------------------- NVLink broadcast
+class NVLinkBroadcastBridge(BridgeStateMachine):
+    """Trainer -> all rollout ranks of the node through symmetric memory, with the dtype cast fused in.
+
+    Every rank constructs the bridge with the same ``SymmetricMemory`` and the same ``capacity_bytes``.
+    ``publish`` is called on the source rank: one ``cast_broadcast`` kernel per tensor reads the
+    trainer's tensor once and stores the (optionally cast) values into every rank's window.
+    ``import_update`` on any rank returns views of the local window (zero copy).  The manifest is
+    shipped by the control plane (e.g. ``broadcast_object_list``).
+    """
+
+    transport = "nvlink-broadcast"
+    allow_multi_rank = True
+
+    def __init__(self, memory, capacity_bytes: int, *, target_dtype: Optional[torch.dtype] = None,
+                 source_worker="trainer", source_rank=0) -> None:
+        super().__init__(source_worker=source_worker, source_rank=source_rank)
+        self.memory = memory
+        self.target_dtype = target_dtype
+        self.window = memory.alloc((int(capacity_bytes),), torch.uint8)
+
+    def _capture(self, tensors, update_id):
+        from rl_engine.kernels.ops.base import require_ext
+
+        ext = require_ext()
+        out_dtype = lambda t: self.target_dtype if (self.target_dtype is not None and t.is_floating_point()) else t.dtype
+        shadows = {n: torch.empty(0, dtype=out_dtype(t)).new_empty(t.shape, device="meta") for n, t in tensors.items()}
+        entries, total = pack_layout(shadows)
+        if total > self.window.local.numel():
+            raise WeightBridgeUnavailableError(
+                f"update needs {total} bytes but the broadcast window holds {self.window.local.numel()}"
+            )
+        code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+        self.memory.barrier()  # consumers are done with the previous contents of the window
+        stored = {}
+        for name, t in tensors.items():
+            e = entries[name]
+            dst_dtype = out_dtype(t)
+            src = t.detach().contiguous()
+            if src.dtype in code and dst_dtype in code:
+                ext.cast_broadcast(src, [p + e["offset"] for p in self.window.ptrs], code[dst_dtype])
+            else:  # integer / bool tensors: move the raw bytes (bit-exact fp32 load/store, no arithmetic)
+                raw = src.view(-1).view(torch.uint8) if src.dtype != torch.bool else src.view(-1).to(torch.uint8)
+                pad = (-raw.numel()) % 4
+                if pad:
+                    raw = torch.cat([raw, raw.new_zeros(pad)])
+                ext.cast_broadcast(raw.view(torch.float32), [p + e["offset"] for p in self.window.ptrs], 0)
+            stored[name] = self._view(e, dst_dtype)
+        self.memory.barrier()  # every rank's window is complete
+        block = {"format": NVLINK_BROADCAST_FORMAT, "world_size": self.memory.world, "tensors": entries,
+                 "requested_nbytes": total}
+        return stored, block, {}
+
+    def _view(self, entry, dtype) -> torch.Tensor:
+        n = entry["nbytes"]
+        return self.window.local[entry["offset"] : entry["offset"] + n].view(dtype).view(entry["shape"])
+
+    def _hand_out(self, record: UpdateRecord):
+        return dict(record.tensors)
+
+    def _attach(self, manifest: WeightUpdateManifest) -> UpdateRecord:
+        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
+        if not isinstance(block, Mapping) or block.get("format") != NVLINK_BROADCAST_FORMAT:
+            raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        views = {n: self._view(block["tensors"][n], _DTYPES[d.dtype]) for n, d in manifest.tensors.items()}
+        return UpdateRecord(manifest=manifest, tensors=views)
+
+    def _validate(self, record, manifest) -> None:
+        # descriptors carry the publisher's device string; on a consumer rank only structure is compared
+        if record.manifest is manifest or manifest.source_rank == self.memory.rank:
+            return super()._validate(record, manifest)
+        for name, want in manifest.tensors.items():
+            got = record.tensors[name]
+            if tuple(got.shape) != tuple(want.shape) or str(got.dtype) != want.dtype:
+                raise WeightManifestValidationError(f"tensor descriptor mismatch for {name}")
+
+
+# ------------------------------------------------------------------------------------ file blob
+class FileBlobBridge(BridgeStateMachine):
+    """Packed 256-byte-aligned blob + JSON manifest on disk; also the checkpoint format."""
+
+    transport = "file"
+
+    def __init__(self, directory: str, *, source_worker="local-training", source_rank=0) -> None:
+        super().__init__(source_worker=source_worker, source_rank=source_rank)
+        self.directory = directory
+        os.makedirs(directory, exist_ok=True)
+
+    def _paths(self, update_id: str) -> Tuple[str, str]:
+        return (os.path.join(self.directory, f"{update_id}.blob"), os.path.join(self.directory, f"{update_id}.json"))
+
+    def _capture(self, tensors, update_id):
+        host = {n: t.detach().to("cpu").contiguous() for n, t in tensors.items()}
+        entries, total = pack_layout(host)
+        blob_path, _ = self._paths(update_id)
+        with open(blob_path, "wb") as f:
+            f.truncate(total)
+            for name, t in host.items():
+                f.seek(entries[name]["offset"])
+                raw = t.view(torch.uint8) if t.dtype != torch.bool else t.to(torch.uint8)
+                f.write(raw.numpy().tobytes())
+        block = {"format": FILE_BLOB_FORMAT, "blob_path": blob_path, "requested_nbytes": total, "tensors": entries}
+        return host, block, {"blob_path": blob_path}
+
+    def publish(self, model, *, weight_version: int, metadata=None):
+        manifest = super().publish(model, weight_version=weight_version, metadata=metadata)
+        _, json_path = self._paths(manifest.update_id)
+        with open(json_path, "w") as f:
+            json.dump(manifest_to_json(manifest), f)
+        return manifest
+
+    def _hand_out(self, record: UpdateRecord):
+        return {n: _clone(t) for n, t in record.tensors.items()}
+
+    def _attach(self, manifest: WeightUpdateManifest) -> UpdateRecord:
+        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
+        if not isinstance(block, Mapping) or block.get("format") != FILE_BLOB_FORMAT:
+            raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        return UpdateRecord(manifest=manifest, tensors=read_blob(block, manifest))
+
+    def load_manifest(self, update_id: str) -> WeightUpdateManifest:
+        with open(self._paths(update_id)[1]) as f:
+            return manifest_from_json(json.load(f))
+
+    def _dispose(self, record: UpdateRecord) -> None:
+        record.tensors.clear()
+
+
+def read_blob(block: Mapping[str, Any], manifest: WeightUpdateManifest) -> Dict[str, torch.Tensor]:
+    out = {}
+    with open(block["blob_path"], "rb") as f:
+        for name, desc in manifest.tensors.items():
+            e = block["tensors"][name]
+            f.seek(e["offset"])
+            raw = bytearray(f.read(e["nbytes"]))
+            dtype = _DTYPES[desc.dtype]
+            if desc.numel == 0:
+                out[name] = torch.empty(desc.shape, dtype=dtype)
+            elif dtype == torch.bool:
+                out[name] = torch.frombuffer(raw, dtype=torch.uint8).view(desc.shape).to(torch.bool)
+            else:
+                out[name] = torch.frombuffer(raw, dtype=dtype).view(desc.shape).clone()
+    return out
+
+
+def manifest_to_json(m: WeightUpdateManifest) -> Dict[str, Any]:
+    meta = {k: v for k, v in m.metadata.items()}
+    return {"update_id": m.update_id, "source_worker": m.source_worker, "source_rank": m.source_rank,
+            "weight_version": m.weight_version, "transport": m.transport, "created_at": m.created_at,
+            "tensors": {n: d.to_json() for n, d in m.tensors.items()}, "metadata": meta}
+
+
+def manifest_from_json(raw: Mapping[str, Any]) -> WeightUpdateManifest:
+    return WeightUpdateManifest(
+        update_id=str(raw["update_id"]), source_worker=str(raw["source_worker"]), source_rank=int(raw["source_rank"]),
+        weight_version=int(raw["weight_version"]), transport=str(raw["transport"]),
+        tensors={n: TensorDescriptor.from_json(d) for n, d in raw["tensors"].items()},
+        created_at=float(raw["created_at"]), metadata=dict(raw["metadata"]),
+    )
+
+
+def make_weight_bridge(transport: str = "local-clone", *, source_worker: str = "local-training", source_rank: int = 0,
+                       **kwargs: Any):
+    kw = dict(source_worker=source_worker, source_rank=source_rank)
+    if transport in {"local", "local-clone"}:
+        return LocalTensorCopyBridge(**kw)
+    if transport in {"shared-memory", "shm"}:
+        return SharedMemoryTensorBridge(**kw)
+    if transport in {"cuda-vmm", "cuda-vmm-fd"}:
+        return CUDAVMMTensorBridge(**kw, **kwargs)
+    if transport in {"cuda-ipc", "ipc"}:
+        return IPCWeightBridge(**kw)
+    if transport in {"nvlink-broadcast", "nvlink"}:
+        if "memory" not in kwargs or "capacity_bytes" not in kwargs:
+            raise WeightBridgeUnavailableError("nvlink-broadcast needs memory=SymmetricMemory and capacity_bytes=")
+        return NVLinkBroadcastBridge(kwargs.pop("memory"), kwargs.pop("capacity_bytes"), **kw, **kwargs)
+    if transport in {"file", "checkpoint"}:
+        if "directory" not in kwargs:
+            raise WeightBridgeUnavailableError("file transport needs directory=")
+        return FileBlobBridge(kwargs.pop("directory"), **kw)
+    if transport in {"multi-node", "rdma", "nccl-rdma"}:
+        raise WeightBridgeUnavailableError(
+            "multi-node/RDMA weight transport is not implemented. Use a same-node transport "
+            "(local-clone, shared-memory, cuda-vmm, nvlink-broadcast)."
+        )
+    raise WeightBridgeUnavailableError(f"unknown weight bridge transport: {transport}")
