@@ -175,6 +175,11 @@ void swiglu_forward(const void* gate, long long ldg, const void* up, long long l
 void swiglu_backward(const void* gate, long long ldg, const void* up, long long ldu, const void* dy, long long lddy,
                      int dtype, void* dgate, long long lddg, void* dup, long long lddu, long long rows, int F,
                      cudaStream_t stream);
+// packed bf16 [gate | up] rows of width 2F; dgu receives [dgate | dup]
+void swiglu_packed_forward(const __nv_bfloat16* gu, long long ldgu, __nv_bfloat16* out, long long ldo, long long rows, int F,
+                           cudaStream_t stream);
+void swiglu_packed_backward(const __nv_bfloat16* gu, long long ldgu, const __nv_bfloat16* dy, long long lddy,
+                            __nv_bfloat16* dgu, long long lddgu, long long rows, int F, cudaStream_t stream);
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
                 void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream);
 void embedding_forward(const long long* ids, const void* table, long long ldw, int dtype, void* out, long long rows,

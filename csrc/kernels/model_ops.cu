@@ -94,6 +94,141 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict_
   for (int i = threadIdx.x; i < D; i += kNormThreads) out[i] = dw_acc[i];
 }
 
+// bf16 fast paths (x, w, y all bf16; D % 8 == 0; 16-byte aligned rows): 16-byte loads, row kept in
+// registers between the two sweeps.  Same reduction order as the generic kernels? No: the per-thread
+// partial sums cover different elements, so these are used consistently for every bf16 call instead.
+constexpr int kNormVecMax = 4;  // up to 4 x 8 elements per thread -> D <= 4096 in registers
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                        __nv_bfloat16* __restrict__ y, long long ldy, int D, float eps, float* __restrict__ rstd_out) {
+  __shared__ float red[4];
+  const long long row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * ldy);
+  const int n8 = D / 8;
+  uint4 buf[kNormVecMax];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < kNormVecMax; ++v) {
+    const int i = threadIdx.x + v * kNormThreads;
+    if (i < n8) {
+      buf[v] = xr[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&buf[v]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+  }
+  ss = block_sum_128(ss, red);
+  const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+  if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+#pragma unroll
+  for (int v = 0; v < kNormVecMax; ++v) {
+    const int i = threadIdx.x + v * kNormThreads;
+    if (i < n8) {
+      const uint4 wv = wr[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&buf[v]);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]), g = __bfloat1622float2(wh[j]);
+        oh[j] = __floats2bfloat162_rn(f.x * rstd * g.x, f.y * rstd * g.y);
+      }
+      yr[i] = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, long long lddy, const float* __restrict__ rstd,
+                        __nv_bfloat16* __restrict__ dx, long long lddx, int rows, int D, float* __restrict__ dw_part) {
+  __shared__ float red[4];
+  const int n8 = D / 8;
+  float dwacc[kNormVecMax][8];
+  float wreg[kNormVecMax][8];
+#pragma unroll
+  for (int v = 0; v < kNormVecMax; ++v) {
+    const int i = threadIdx.x + v * kNormThreads;
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (i < n8) wv = reinterpret_cast<const uint4*>(w)[i];
+    const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(wh[j]);
+      wreg[v][2 * j] = g.x;
+      wreg[v][2 * j + 1] = g.y;
+      dwacc[v][2 * j] = 0.f;
+      dwacc[v][2 * j + 1] = 0.f;
+    }
+  }
+  const long long r0 = static_cast<long long>(blockIdx.x) * kNormBwdRows;
+  const long long r1 = r0 + kNormBwdRows < rows ? r0 + kNormBwdRows : rows;
+  for (long long row = r0; row < r1; ++row) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * lddy);
+    uint4* dr = reinterpret_cast<uint4*>(dx + row * lddx);
+    const float rs = rstd[row];
+    float xf[kNormVecMax][8], gf[kNormVecMax][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < kNormVecMax; ++v) {
+      const int i = threadIdx.x + v * kNormThreads;
+      if (i < n8) {
+        const uint4 xv = xr[i], gv = gr[i];
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(xh[j]), b = __bfloat1622float2(gh[j]);
+          xf[v][2 * j] = a.x; xf[v][2 * j + 1] = a.y;
+          gf[v][2 * j] = b.x; gf[v][2 * j + 1] = b.y;
+          dot = fmaf(b.x * wreg[v][2 * j], a.x, dot);
+          dot = fmaf(b.y * wreg[v][2 * j + 1], a.y, dot);
+        }
+      }
+    }
+    dot = block_sum_128(dot, red);
+    const float c = dot * rs * rs / static_cast<float>(D);
+#pragma unroll
+    for (int v = 0; v < kNormVecMax; ++v) {
+      const int i = threadIdx.x + v * kNormThreads;
+      if (i < n8) {
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float d0 = rs * (gf[v][2 * j] * wreg[v][2 * j] - xf[v][2 * j] * c);
+          const float d1 = rs * (gf[v][2 * j + 1] * wreg[v][2 * j + 1] - xf[v][2 * j + 1] * c);
+          oh[j] = __floats2bfloat162_rn(d0, d1);
+          dwacc[v][2 * j] = fmaf(gf[v][2 * j], xf[v][2 * j] * rs, dwacc[v][2 * j]);
+          dwacc[v][2 * j + 1] = fmaf(gf[v][2 * j + 1], xf[v][2 * j + 1] * rs, dwacc[v][2 * j + 1]);
+        }
+        dr[i] = o;
+      }
+    }
+  }
+  float* out = dw_part + static_cast<long long>(blockIdx.x) * D;
+#pragma unroll
+  for (int v = 0; v < kNormVecMax; ++v) {
+    const int i = threadIdx.x + v * kNormThreads;
+    if (i < n8) {
+      reinterpret_cast<float4*>(out + i * 8)[0] = make_float4(dwacc[v][0], dwacc[v][1], dwacc[v][2], dwacc[v][3]);
+      reinterpret_cast<float4*>(out + i * 8)[1] = make_float4(dwacc[v][4], dwacc[v][5], dwacc[v][6], dwacc[v][7]);
+    }
+  }
+}
+
+inline bool bf16_vec_ok(const void* a, long long lda, int D) {
+  return D % 8 == 0 && D <= 8 * kNormVecMax * kNormThreads && lda % 8 == 0 && (reinterpret_cast<uintptr_t>(a) & 15u) == 0;
+}
+
 template <typename TW>
 __global__ void colsum_kernel(const float* __restrict__ part, int chunks, int D, TW* __restrict__ dw) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -135,6 +270,62 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gate, long long ldg, con
     const float u = up ? ldf(up, r * ldu + c) : 1.f;
     stf(dgate, r * lddg + c, d * u * sig * (1.f + g * (1.f - sig)));
     if (dup) stf(dup, r * lddu + c, d * silu);
+  }
+}
+
+// Packed bf16 SwiGLU: gu = [gate | up] of width 2F per row (the output of one fused gate/up GEMM).
+// 16-byte accesses; F % 8 == 0.  The backward writes d(gu) in place of two separate tensors, so no
+// strided scatter / zero-fill is needed to rebuild the packed gradient.
+__global__ void swiglu_packed_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ldgu,
+                                         __nv_bfloat16* __restrict__ out, long long ldo, long long rows, int F) {
+  const int f8 = F / 8;
+  const long long total = rows * f8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / f8;
+    const int c = static_cast<int>(idx - r * f8) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ldgu + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ldgu + F + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 gf = __bfloat1622float2(gp[i]), uf = __bfloat1622float2(up[i]);
+      op[i] = __floats2bfloat162_rn(gf.x / (1.f + __expf(-gf.x)) * uf.x, gf.y / (1.f + __expf(-gf.y)) * uf.y);
+    }
+    *reinterpret_cast<uint4*>(out + r * ldo + c) = o;
+  }
+}
+
+__global__ void swiglu_packed_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ldgu,
+                                         const __nv_bfloat16* __restrict__ dy, long long lddy,
+                                         __nv_bfloat16* __restrict__ dgu, long long lddgu, long long rows, int F) {
+  const int f8 = F / 8;
+  const long long total = rows * f8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / f8;
+    const int c = static_cast<int>(idx - r * f8) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ldgu + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ldgu + F + c);
+    const uint4 d = *reinterpret_cast<const uint4*>(dy + r * lddy + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d);
+    uint4 og, ou;
+    __nv_bfloat162* ogp = reinterpret_cast<__nv_bfloat162*>(&og);
+    __nv_bfloat162* oup = reinterpret_cast<__nv_bfloat162*>(&ou);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 gf = __bfloat1622float2(gp[i]), uf = __bfloat1622float2(up[i]), df = __bfloat1622float2(dp[i]);
+      const float s0 = 1.f / (1.f + __expf(-gf.x)), s1 = 1.f / (1.f + __expf(-gf.y));
+      ogp[i] = __floats2bfloat162_rn(df.x * uf.x * s0 * (1.f + gf.x * (1.f - s0)), df.y * uf.y * s1 * (1.f + gf.y * (1.f - s1)));
+      oup[i] = __floats2bfloat162_rn(df.x * gf.x * s0, df.y * gf.y * s1);
+    }
+    *reinterpret_cast<uint4*>(dgu + r * lddgu + c) = og;
+    *reinterpret_cast<uint4*>(dgu + r * lddgu + F + c) = ou;
   }
 }
 
@@ -238,6 +429,13 @@ inline int grid_for(long long total, int threads) {
 void rmsnorm_forward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, void* y, long long ldy,
                      bool out_fp32, long long rows, int D, float eps, float* rstd, cudaStream_t stream) {
   if (rows <= 0) return;
+  if (x_dtype == 1 && w_dtype == 1 && !out_fp32 && bf16_vec_ok(x, ldx, D) && bf16_vec_ok(y, ldy, D) &&
+      bf16_vec_ok(w, 8, D)) {
+    rmsnorm_fwd_bf16_kernel<<<rows, kNormThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), ldx,
+                                                               static_cast<const __nv_bfloat16*>(w),
+                                                               static_cast<__nv_bfloat16*>(y), ldy, D, eps, rstd);
+    return;
+  }
   RLK_DISPATCH_T(x_dtype, {
     using TX = T;
     RLK_DISPATCH_T(w_dtype, {
@@ -259,6 +457,15 @@ void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, 
                       float* dw_part, void* dw, cudaStream_t stream) {
   if (rows <= 0) return;
   const int chunks = rmsnorm_bwd_chunks(rows);
+  if (x_dtype == 1 && w_dtype == 1 && bf16_vec_ok(x, ldx, D) && bf16_vec_ok(dy, lddy, D) && bf16_vec_ok(dx, lddx, D) &&
+      bf16_vec_ok(w, 8, D)) {
+    rmsnorm_bwd_bf16_kernel<<<chunks, kNormThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+        static_cast<const __nv_bfloat16*>(dy), lddy, rstd, static_cast<__nv_bfloat16*>(dx), lddx,
+        static_cast<int>(rows), D, dw_part);
+    colsum_kernel<__nv_bfloat16><<<(D + 255) / 256, 256, 0, stream>>>(dw_part, chunks, D, static_cast<__nv_bfloat16*>(dw));
+    return;
+  }
   RLK_DISPATCH_T(x_dtype, {
     using TX = T;
     RLK_DISPATCH_T(w_dtype, {
@@ -302,6 +509,18 @@ void swiglu_backward(const void* gate, long long ldg, const void* up, long long 
                                                        static_cast<const T*>(dy), lddy, static_cast<T*>(dgate), lddg,
                                                        static_cast<T*>(dup), lddu, rows, F);
   });
+}
+
+void swiglu_packed_forward(const __nv_bfloat16* gu, long long ldgu, __nv_bfloat16* out, long long ldo, long long rows, int F,
+                           cudaStream_t stream) {
+  if (rows <= 0 || F <= 0) return;
+  swiglu_packed_fwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, stream>>>(gu, ldgu, out, ldo, rows, F);
+}
+
+void swiglu_packed_backward(const __nv_bfloat16* gu, long long ldgu, const __nv_bfloat16* dy, long long lddy,
+                            __nv_bfloat16* dgu, long long lddgu, long long rows, int F, cudaStream_t stream) {
+  if (rows <= 0 || F <= 0) return;
+  swiglu_packed_bwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, stream>>>(gu, ldgu, dy, lddy, dgu, lddgu, rows, F);
 }
 
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,

@@ -488,6 +488,41 @@ std::vector<Tensor> swiglu_bwd(const Tensor& gate, std::optional<Tensor> up, con
   return {dg, du};
 }
 
+Tensor swiglu_packed_fwd(const Tensor& gu) {
+  check_rowmajor(gu, "gate_up");
+  TORCH_CHECK(gu.scalar_type() == torch::kBFloat16 && gu.size(1) % 16 == 0 && gu.stride(0) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(gu.data_ptr()) % 16 == 0,
+              "swiglu_packed: bf16 [rows, 2F] with F % 8 == 0 and 16-byte aligned rows");
+  const c10::cuda::CUDAGuard guard(gu.device());
+  const int64_t F = gu.size(1) / 2;
+  Tensor out = torch::empty({gu.size(0), F}, gu.options());
+  if (gu.numel()) {
+    rlk::swiglu_packed_forward(reinterpret_cast<const __nv_bfloat16*>(gu.data_ptr()), gu.stride(0),
+                               reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0), gu.size(0),
+                               static_cast<int>(F), stream_of(gu));
+    after_launch();
+  }
+  return out;
+}
+
+Tensor swiglu_packed_bwd(const Tensor& gu, const Tensor& dy) {
+  check_rowmajor(gu, "gate_up");
+  check_rowmajor(dy, "dy");
+  TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.size(0) == gu.size(0) && dy.size(1) * 2 == gu.size(1) &&
+                  dy.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(dy.data_ptr()) % 16 == 0,
+              "swiglu_packed_bwd: dy must be aligned bf16 [rows, F]");
+  const c10::cuda::CUDAGuard guard(gu.device());
+  Tensor dgu = torch::empty({gu.size(0), gu.size(1)}, gu.options());
+  if (gu.numel()) {
+    rlk::swiglu_packed_backward(reinterpret_cast<const __nv_bfloat16*>(gu.data_ptr()), gu.stride(0),
+                                reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()), dy.stride(0),
+                                reinterpret_cast<__nv_bfloat16*>(dgu.data_ptr()), dgu.stride(0), gu.size(0),
+                                static_cast<int>(gu.size(1) / 2), stream_of(gu));
+    after_launch();
+  }
+  return dgu;
+}
+
 // x: [tokens, heads, D] with unit stride on D and stride D on heads
 Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const Tensor& sin_t, bool inverse,
             std::optional<Tensor> out_opt) {
@@ -752,6 +787,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("swiglu_packed_fwd", &swiglu_packed_fwd);
+  m.def("swiglu_packed_bwd", &swiglu_packed_bwd);
   m.def("rope", &rope, py::arg("x"), py::arg("positions"), py::arg("cos"), py::arg("sin"), py::arg("inverse") = false,
         py::arg("out") = py::none());
   m.def("embedding_fwd", &embedding_fwd);

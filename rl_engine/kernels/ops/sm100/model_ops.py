@@ -95,6 +95,35 @@ class _SwiGLU(torch.autograd.Function):
         return dg.reshape(ctx.shape), (du.reshape(ctx.shape) if ctx.has_up else None)
 
 
+class _SwiGLUPacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return require_ext().swiglu_packed_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        dy2 = dy if (dy.stride(1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0) else dy.contiguous()
+        return require_ext().swiglu_packed_bwd(gu, dy2)
+
+
+def swiglu_packed(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for a packed ``[rows, 2F]`` tensor ``[gate | up]`` (the fused gate/up GEMM output).
+
+    The backward produces the packed gradient in one kernel, so autograd never has to scatter two
+    half-width gradients back into a zero-filled ``[rows, 2F]`` buffer."""
+    f = gate_up.shape[-1] // 2
+    gu2 = gate_up.reshape(-1, gate_up.shape[-1])
+    ok = (gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and f % 8 == 0 and gu2.stride(1) == 1
+          and gu2.stride(0) % 8 == 0 and gu2.data_ptr() % 16 == 0 and gu2.numel() > 0)
+    if not ok:
+        from rl_engine.kernels.registry import kernel_registry
+
+        return kernel_registry.get_op("swiglu")(gate_up[..., :f], gate_up[..., f:])
+    return _SwiGLUPacked.apply(gu2).reshape(*gate_up.shape[:-1], f)
+
+
 class FusedSiLUSM100Op(torch.nn.Module):
     def __init__(self) -> None:
         super().__init__()

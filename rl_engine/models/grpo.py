@@ -107,41 +107,52 @@ class FlatAdamW:
         self.steps = int(state["steps"])
 
 
+_GEOMETRY: Dict[tuple, tuple] = {}
+
+
+def group_geometry(p: int, g: int, l: int, device):
+    """(packed layout, positions [P + G*L], hidden row predicting each completion token [G*L])."""
+    key = (p, g, l, str(device))
+    hit = _GEOMETRY.get(key)
+    if hit is None:
+        from rl_engine.kernels.ops.sm100.attention import grpo_group_layout
+
+        layout = grpo_group_layout(p, g, l, device)
+        positions = torch.cat([torch.arange(p), (p + torch.arange(l)).repeat(g)]).to(device)
+        rows = p + torch.arange(g)[:, None] * l + torch.arange(l)[None, :] - 1  # the token before (g, i)
+        rows[:, 0] = p - 1
+        if len(_GEOMETRY) > 32:
+            _GEOMETRY.clear()
+        hit = _GEOMETRY[key] = (layout, positions, rows.reshape(-1).to(device))
+    return hit
+
+
+def policy_logps(model: LlamaModel, batch: "GRPOBatch") -> torch.Tensor:
+    """Selected-token log-probs ``[G, L]`` of the completions under ``model`` (differentiable).
+
+    Used by the trainer and by the native rollout engine, so both paths run the same kernels in the
+    same order: their log-probs for the same tokens and weights agree bitwise."""
+    from rl_engine.kernels.registry import kernel_registry
+
+    p, (g, l) = batch.prompt_ids.numel(), batch.completion_ids.shape
+    layout, positions, rows = group_geometry(p, g, l, batch.prompt_ids.device)
+    tokens = torch.cat([batch.prompt_ids, batch.completion_ids.reshape(-1)])
+    hidden = model.hidden_states(tokens, positions, layout)
+    # deterministic differentiable row gather (ordered segment sums in backward, no atomics)
+    picked = kernel_registry.get_op("embedding")(rows, hidden)
+    logp = kernel_registry.get_op("linear_logp")(picked, model.lm_head_weight(), batch.completion_ids.reshape(-1))
+    return logp.reshape(g, l)
+
+
 class GRPOTrainer:
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False) -> None:
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
         self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
-        self._index_cache: Dict[tuple, tuple] = {}
 
-    # -- batch geometry -----------------------------------------------------------------------
-    def _geometry(self, p: int, g: int, l: int, device):
-        key = (p, g, l, str(device))
-        hit = self._index_cache.get(key)
-        if hit is None:
-            from rl_engine.kernels.ops.sm100.attention import grpo_group_layout
-
-            layout = grpo_group_layout(p, g, l, device)
-            positions = torch.cat([torch.arange(p), (p + torch.arange(l)).repeat(g)]).to(device)
-            # hidden row that predicts completion token (g, i): the token before it
-            rows = (p + torch.arange(g)[:, None] * l + torch.arange(l)[None, :] - 1)
-            rows[:, 0] = p - 1
-            hit = self._index_cache[key] = (layout, positions, rows.reshape(-1).to(device))
-        return hit
-
-    # -- the step -------------------------------------------------------------------------------
     def policy_logps(self, batch: GRPOBatch) -> torch.Tensor:
-        from rl_engine.kernels.registry import kernel_registry
-
-        p, (g, l) = batch.prompt_ids.numel(), batch.completion_ids.shape
-        layout, positions, rows = self._geometry(p, g, l, batch.prompt_ids.device)
-        tokens = torch.cat([batch.prompt_ids, batch.completion_ids.reshape(-1)])
-        hidden = self.model.hidden_states(tokens, positions, layout)
-        # deterministic differentiable row gather (ordered segment sums in backward, no atomics)
-        picked = kernel_registry.get_op("embedding")(rows, hidden)
-        logp = kernel_registry.get_op("linear_logp")(picked, self.model.lm_head_weight(), batch.completion_ids.reshape(-1))
-        return logp.reshape(g, l)
+        return policy_logps(self.model, batch)
 
     def loss(self, batch: GRPOBatch):
         from rl_engine.kernels.registry import kernel_registry

@@ -51,6 +51,12 @@ def swiglu(gate, up):
     return kernel_registry.get_op("swiglu")(gate, up)
 
 
+def swiglu_packed(gate_up):
+    from rl_engine.kernels.ops.sm100.model_ops import swiglu_packed as fused
+
+    return fused(gate_up)
+
+
 def reference_packed_attention(q, k, v, host_seqs, causal: bool, scale: float) -> torch.Tensor:
     """Differentiable PyTorch restatement of packed attention (CPU path / oracle)."""
     hq, hkv = q.shape[1], k.shape[1]
@@ -231,7 +237,7 @@ class LlamaModel(nn.Module):
         x = x + linear(attn, p("wo"))
         h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
         gu = linear(h, p("w_gate_up"))
-        act = swiglu(gu[:, : cfg.ffn_size], gu[:, cfg.ffn_size :])
+        act = swiglu_packed(gu)
         return x + linear(act, p("w_down"))
 
     def hidden_states(self, token_ids: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:

@@ -73,7 +73,6 @@ class ShardedGRPOTrainer(GRPOTrainer):
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
         self.opt = ShardedFusedAdamW(model, self.mem, params, grads, lr=lr, weight_decay=weight_decay,
                                      master_weights=master_weights)
-        self._index_cache = {}
         self._slice: Optional[slice] = None
         self.mem.barrier()
 

@@ -347,3 +347,34 @@ def test_sampler_distribution():
     freq = torch.bincount(ids, minlength=6).float() / ids.numel()
     want = torch.softmax(z[0, :4], 0)
     assert freq[4:].sum() == 0 and torch.allclose(freq[:4], want, atol=0.015)
+
+
+def test_swiglu_packed_and_rmsnorm_wide_rows():
+    from rl_engine.kernels.ops.sm100.model_ops import FusedRMSNormSM100Op, swiglu_packed
+
+    g = _gen(31)
+    gu = torch.randn(3, 50, 2 * 1408, device=DEV, generator=g).to(torch.bfloat16)
+    dy = torch.randn(3, 50, 1408, device=DEV, generator=g).to(torch.bfloat16)
+    a = gu.clone().requires_grad_(True)
+    b = gu.clone().float().requires_grad_(True)
+    out = swiglu_packed(a)
+    ref = torch.nn.functional.silu(b[..., :1408]) * b[..., 1408:]
+    assert (out.float() - ref).abs().max().item() < 3e-2
+    out.backward(dy)
+    ref.backward(dy.float())
+    assert (a.grad.float() - b.grad).abs().max().item() < 6e-2
+
+    x = torch.randn(300, 4096, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(4096, device=DEV, generator=g).to(torch.bfloat16)
+    f = FusedRMSNormSM100Op()
+    xa, wa = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    xb, wb = x.clone().float().requires_grad_(True), w.clone().float().requires_grad_(True)
+    y = f(xa, wa, eps=1e-5)
+    yr = xb * torch.rsqrt(xb.square().mean(-1, keepdim=True) + 1e-5) * wb
+    assert (y.float() - yr).abs().max().item() < 5e-2
+    assert torch.equal(f(x[17:33], w, eps=1e-5), y[17:33].detach())
+    d = torch.randn_like(x)
+    y.backward(d)
+    yr.backward(d.float())
+    assert (xa.grad.float() - xb.grad).abs().max().item() < 0.1
+    assert (wa.grad.float() - wb.grad).abs().max().item() / wb.grad.abs().max().item() < 2e-2
