@@ -1,0 +1,190 @@
+"""Small, self-terminating workloads for per-kernel profiling and CUDA-event timing.
+
+    python benchmarks/profile_kernels.py --kernel gemm            # one of the names below
+    ncu --set full --clock-control none -k regex:gemm_sm100 -s 2 -c 1 -o out python benchmarks/profile_kernels.py --kernel gemm
+
+Each case touches more than the 126 MB L2 but at most a few GB, launches the kernel under test a
+handful of times, prints one JSON line with the CUDA-event time of the last launch (L2 flushed before
+it) and the achieved fraction of the measured peaks in ``MEASURED_PEAKS.json`` when that file exists.
+"""
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def timed(fn, launches=3):
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ms = 0.0
+    for _ in range(launches):
+        flush.zero_()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop)
+    return ms
+
+
+def rand(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * scale).to(torch.bfloat16)
+
+
+def case_gemm():
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    m, n, k = 8192, 14336, 4096  # 67 + 117 + 235 MB
+    a, b = rand((m, k)), rand((n, k), 0.02, 1)
+    ms = timed(lambda: gemm(a, b))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [m, n, k]}
+
+
+def case_gemm_wgrad():
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    m, n, k = 8192, 14336, 4096
+    dy, x = rand((m, n)), rand((m, k), 1.0, 1)
+    ms = timed(lambda: gemm(dy, x, a_mn=True, b_mn=True))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [n, k, m]}
+
+
+def case_linear_logp():
+    from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
+
+    n, d, v = 8192, 4096, 128256  # weight 1.05 GB
+    h, w = rand((n, d)), rand((v, d), 0.02, 1)
+    t = torch.randint(0, v, (n,), device="cuda")
+    op = FusedLinearLogpSM100Op(check_targets=False)
+    ms = timed(lambda: op(h, w, t))
+    return {"flops": 2.0 * n * d * v, "bytes": 2.0 * (n * d + v * d), "ms": ms, "shape": [n, d, v]}
+
+
+def case_linear_logp_bwd():
+    from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
+
+    n, d, v = 4096, 4096, 128256
+    h, w = rand((n, d)).requires_grad_(True), rand((v, d), 0.02, 1).requires_grad_(True)
+    t = torch.randint(0, v, (n,), device="cuda")
+    op = FusedLinearLogpSM100Op(check_targets=False)
+
+    def run():
+        h.grad = w.grad = None
+        op(h, w, t).sum().backward()
+
+    ms = timed(run, launches=2)
+    return {"flops": 8.0 * n * d * v, "bytes": 0.0, "ms": ms, "shape": [n, d, v], "note": "forward + recompute backward"}
+
+
+def _attn_inputs(prompt=1024, group=16, length=512, hq=32, hkv=8):
+    t = prompt + group * length
+    return rand((t, hq, 128)), rand((t, hkv, 128), 1.0, 1), rand((t, hkv, 128), 1.0, 2), prompt, group, length
+
+
+def _attn_flops(prompt, group, length, hq):
+    keys = group * length * prompt + group * length * (length + 1) / 2 + prompt * (prompt + 1) / 2
+    return 4.0 * hq * 128 * keys
+
+
+def case_attention_fwd():
+    from rl_engine.kernels.ops.sm100.attention import grpo_group_layout, packed_attention_forward
+
+    q, k, v, p, g, l = _attn_inputs()
+    layout = grpo_group_layout(p, g, l, "cuda")
+    ms = timed(lambda: packed_attention_forward(q, k, v, layout))
+    return {"flops": _attn_flops(p, g, l, 32), "bytes": 2.0 * (2 * q.numel() + 2 * k.numel()), "ms": ms, "shape": [p, g, l]}
+
+
+def case_attention_bwd():
+    from rl_engine.kernels.ops.sm100.attention import grpo_group_layout, packed_attention_forward
+    from rl_engine.kernels.ops.sm100.attention_bwd_kernels import fused_backward
+
+    q, k, v, p, g, l = _attn_inputs()
+    layout = grpo_group_layout(p, g, l, "cuda")
+    out, lse = packed_attention_forward(q, k, v, layout)
+    dout = rand(tuple(q.shape), 1.0, 3)
+    ms = timed(lambda: fused_backward(q, k, v, out, lse, dout, layout, 128**-0.5))
+    return {"flops": 3.5 * _attn_flops(p, g, l, 32), "bytes": 0.0, "ms": ms, "shape": [p, g, l],
+            "note": "dQ kernel (3 GEMMs / tile) + dK,dV kernel (4 GEMMs / tile)"}
+
+
+def case_logp_rows():
+    from rl_engine.kernels.ops.sm100.logp import FusedLogpSM100Op
+
+    rows, v = 4096, 128256  # 1.05 GB of bf16 logits
+    logits = rand((rows, v))
+    ids = torch.randint(0, v, (rows,), device="cuda")
+    op = FusedLogpSM100Op()
+    ms = timed(lambda: op.apply_fp32(logits, ids))
+    return {"flops": 0.0, "bytes": 2.0 * rows * v, "ms": ms, "shape": [rows, v]}
+
+
+def case_swiglu():
+    from rl_engine.kernels.ops.sm100.model_ops import swiglu_packed
+
+    rows, f = 16384, 14336
+    gu = rand((rows, 2 * f))
+    ms = timed(lambda: swiglu_packed(gu))
+    return {"flops": 0.0, "bytes": 2.0 * rows * 3 * f, "ms": ms, "shape": [rows, f]}
+
+
+def case_rmsnorm():
+    from rl_engine.kernels.ops.sm100.model_ops import FusedRMSNormSM100Op
+
+    rows, d = 65536, 4096
+    x, w = rand((rows, d)), rand((d,), 1.0, 1)
+    op = FusedRMSNormSM100Op()
+    ms = timed(lambda: op(x, w))
+    return {"flops": 0.0, "bytes": 2.0 * rows * d * 2, "ms": ms, "shape": [rows, d]}
+
+
+def case_sampler():
+    from rl_engine.kernels.ops.sm100.sampler import sample_topk_topp
+
+    logits = rand((256, 151936)).float()
+    ms = timed(lambda: sample_topk_topp(logits, top_k=50, top_p=0.9, temperature=0.7, seed=1, offset=0))
+    return {"flops": 0.0, "bytes": 4.0 * 256 * 151936, "ms": ms, "shape": [256, 151936],
+            "note": "bytes = one pass; the kernel makes 5 passes over each row (L2 resident)"}
+
+
+CASES = {name[5:]: fn for name, fn in globals().items() if name.startswith("case_")}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", choices=sorted(CASES) + ["all"], default="all")
+    args = ap.parse_args()
+    pk = peaks()
+    for name in (sorted(CASES) if args.kernel == "all" else [args.kernel]):
+        r = CASES[name]()
+        line = {"kernel": name, "ms": round(r["ms"], 4), "shape": r["shape"], "peaks": pk["source"]}
+        if r["flops"]:
+            line["tflops"] = round(r["flops"] / r["ms"] / 1e9, 1)
+            line["frac_of_bf16_peak"] = round(line["tflops"] / pk["bf16_tflops"], 3)
+        if r["bytes"]:
+            line["gbs"] = round(r["bytes"] / r["ms"] / 1e6, 1)
+            line["frac_of_hbm_peak"] = round(line["gbs"] / pk["hbm_gbs"], 3)
+        if "note" in r:
+            line["note"] = r["note"]
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -35,6 +35,26 @@ struct GemmProblem {
   int num_items;         // tiles_m * items_per_m
   int group_m;           // M-tiles per rasterisation group
   int k_blocks;          // ceil(K / 64)
+  // Grouped (mixture-of-experts) modes.  Rows of A are laid out expert by expert, each expert's block
+  // padded to a multiple of 128 rows, so an M-tile never straddles two experts.
+  //   0: plain GEMM.
+  //   1: grouped-M.  D[rows, N] = A[rows, K] * B_g^T with g = tile_group[m_tile]; B holds all groups
+  //      stacked along its row axis, b_group_rows rows per group.
+  //   2: grouped-K.  D_g[Mg, N] = A[rows_g, Mg]^T * B[rows_g, N] (both operands MN-major), contraction
+  //      over the rows of group g = [group_offsets[g], group_offsets[g+1]); D stacks the groups
+  //      (tiles_m_per_group M-tiles each).
+  int group_mode;
+  const int* tile_group;
+  const int* group_offsets;
+  int b_group_rows;
+  int tiles_m_per_group;
+};
+
+struct ItemGeometry {
+  int a_m0;        // M coordinate of the A tile
+  int b_row_off;   // added to B's row coordinate
+  int k_row0;      // first contraction index
+  int k_blocks;    // 64-wide contraction blocks
 };
 
 __host__ __device__ inline GemmProblem make_gemm_problem(int M, int N, int K, int BN, int n_tiles_per_item,
@@ -50,6 +70,11 @@ __host__ __device__ inline GemmProblem make_gemm_problem(int M, int N, int K, in
   p.num_items = p.tiles_m * p.items_per_m;
   p.group_m = group_m < 1 ? 1 : group_m;
   p.k_blocks = (K + kBK - 1) / kBK;
+  p.group_mode = 0;
+  p.tile_group = nullptr;
+  p.group_offsets = nullptr;
+  p.b_group_rows = 0;
+  p.tiles_m_per_group = 1;
   return p;
 }
 
@@ -72,6 +97,23 @@ __device__ __forceinline__ WorkItem decode_item(const GemmProblem& p, int id) {
   w.n_begin = w.split * p.n_tiles_per_item;
   w.n_end = min(w.n_begin + p.n_tiles_per_item, p.tiles_n);
   return w;
+}
+
+__device__ __forceinline__ ItemGeometry item_geometry(const GemmProblem& p, int m_tile) {
+  ItemGeometry g;
+  g.a_m0 = m_tile * kBM;
+  g.b_row_off = 0;
+  g.k_row0 = 0;
+  g.k_blocks = p.k_blocks;
+  if (p.group_mode == 1) {
+    g.b_row_off = p.tile_group[m_tile] * p.b_group_rows;
+  } else if (p.group_mode == 2) {
+    const int grp = m_tile / p.tiles_m_per_group;
+    g.a_m0 = (m_tile - grp * p.tiles_m_per_group) * kBM;
+    g.k_row0 = p.group_offsets[grp];
+    g.k_blocks = (p.group_offsets[grp + 1] - g.k_row0 + kBK - 1) / kBK;
+  }
+  return g;
 }
 
 template <int BN, int STAGES>
@@ -144,15 +186,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t phase = 0;
       for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
-        const int m0 = w.m_tile * kBM;
+        const ItemGeometry geo = item_geometry(p, w.m_tile);
+        const int m0 = geo.a_m0;
         for (int nt = w.n_begin; nt < w.n_end; ++nt) {
           const int n0 = nt * BN;
-          for (int kb = 0; kb < p.k_blocks; ++kb) {
+          for (int kb = 0; kb < geo.k_blocks; ++kb) {
             mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, err, kernel_id, 1);
             uint8_t* sa = smem + stage * L::kStageBytes;
             uint8_t* sb = sa + L::kABytes;
             mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            const int k0 = kb * kBK;
+            const int k0 = geo.k_row0 + kb * kBK;
             if constexpr (!A_MN) {
               tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
             } else {
@@ -160,10 +203,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
             }
             if constexpr (!B_MN) {
-              tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+              tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0 + geo.b_row_off);
             } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0 + geo.b_row_off);
             }
             if (++stage == STAGES) {
               stage = 0;
@@ -183,11 +227,12 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t buf_phase = 0;
       for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
+        const int item_k_blocks = item_geometry(p, w.m_tile).k_blocks;
         for (int nt = w.n_begin; nt < w.n_end; ++nt) {
           mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag, err, kernel_id, 2);
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          for (int kb = 0; kb < p.k_blocks; ++kb) {
+          for (int kb = 0; kb < item_k_blocks; ++kb) {
             mbar_wait(&full_bar[stage], phase, abort_flag, err, kernel_id, 3);
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);

@@ -16,11 +16,20 @@ constexpr int kStages = 4;
 template <bool A_MN, bool B_MN, class Epi>
 void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
   // Rasterise in groups of 8 M-tiles so concurrently running CTAs share A and B tiles in L2.
-  const GemmProblem p = make_gemm_problem(a.M, a.N, a.K, kBN, 1, 8);
+  const int total_m = a.group_mode == 2 ? a.M * a.num_groups : a.M;
+  GemmProblem p = make_gemm_problem(total_m, a.N, a.K, kBN, 1, 8);
+  const int g = a.group_mode ? a.num_groups : 1;
+  p.group_mode = a.group_mode;
+  p.tile_group = a.tile_group;
+  p.group_offsets = a.group_offsets;
+  p.tiles_m_per_group = a.group_mode == 2 ? a.M / kBM : 1;
+  // B stacks the groups along its row axis: N rows per group when K-major, K rows per group when MN-major
+  p.b_group_rows = a.group_mode == 1 ? (B_MN ? a.K : a.N) : 0;
+  const int b_stack = a.group_mode == 1 ? g : 1;
   const CUtensorMap ta = A_MN ? make_tmap_2d_bf16(a.A, a.K, a.M, a.lda, kBK, 64)
                               : make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
-  const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, a.K, a.N, a.ldb, kBK, 64)
-                              : make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kBN, kBK);
+  const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, static_cast<uint64_t>(a.K) * b_stack, a.N, a.ldb, kBK, 64)
+                              : make_tmap_2d_bf16(a.B, static_cast<uint64_t>(a.N) * b_stack, a.K, a.ldb, kBN, kBK);
   auto kernel = gemm_sm100_kernel<kBN, A_MN, B_MN, kStages, Epi>;
   using L = GemmSmem<kBN, kStages>;
   static bool configured = false;

@@ -25,6 +25,15 @@ struct GemmArgs {
   float alpha;
   int sm_count;
   uint32_t* err;
+  // Grouped (mixture-of-experts) modes; rows of the token-side operand are grouped expert by expert and
+  // every group's block is padded to a multiple of 128 rows.
+  //   group_mode 1: D[M, N] = A[M, K] * B_g^T, g = tile_group[row / 128]; B stacks num_groups blocks.
+  //   group_mode 2: D_g[M, N] = A[rows_g, M]^T * B[rows_g, N] with rows_g = group_offsets[g..g+1);
+  //                 both operands MN-major, K = total rows, D stacks num_groups blocks of M rows, M % 128 == 0.
+  int group_mode = 0;
+  const int* tile_group = nullptr;
+  const int* group_offsets = nullptr;
+  int num_groups = 1;
 };
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 
@@ -283,5 +292,27 @@ void zero1_fused_step(void* const* grads, void* const* params, int world, long l
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream);
 void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
                     cudaStream_t stream);
+
+}  // namespace rlk
+
+namespace rlk {
+
+// ---------------------------------------------------------------------------- mixture of experts
+// experts <= 512, k <= 32; hidden % 8 == 0 and 16-byte aligned rows for the row kernels.
+void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, float* weight, cudaStream_t stream);
+void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,
+                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream);
+void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, const float* weight, int k,
+                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream);
+void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,
+                int tokens, int hidden, float* out, cudaStream_t stream);
+// expert parallelism over peer-mapped buffers (dst / src / b hold one base pointer per rank)
+void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int* token, const int* dest_rank,
+                           const int* dest_slot, const float* scale, void* const* dst, int world, long long ld_dst,
+                           int assignments, int hidden, cudaStream_t stream);
+void moe_combine_peer(void* const* src, int world, long long ld_src, const int* rank, const int* slot, const float* weight,
+                      int k, __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream);
+void moe_rowdot_peer(const __nv_bfloat16* a, long long ld_a, void* const* b, int world, long long ld_b, const int* rank,
+                     const int* slot, int k, int tokens, int hidden, float* out, cudaStream_t stream);
 
 }  // namespace rlk

@@ -1,0 +1,317 @@
+// Mixture-of-experts support kernels (Qwen3-MoE style: softmax over all experts, top-k, renormalise):
+//   moe_topk           : per token, the k largest router probabilities (ties -> lower expert id) and their
+//                        renormalised weights; one warp per token, fixed-order reductions.
+//   moe_gather_rows    : dst[slot] = scale[slot] * src[src_row[slot]]  (src_row < 0 -> zero row).  With peer
+//                        destination pointers this is the all-to-all DISPATCH: every rank stores the rows it
+//                        routes to expert e directly into the owning rank's expert-grouped buffer over NVLink.
+//   moe_combine        : out[t] = sum_j w[t, j] * src[slot[t, j]] in fixed j order (deterministic); `src` may
+//                        live on a peer (the all-to-all COMBINE is this kernel reading peer memory).
+//   moe_rowdot         : d w[t, j] = <dout[t], y[slot[t, j]]>.
+// The reference has no MoE code (its README only shows a log-prob benchmark on Qwen3-30B-A3B).
+#include "../common/ptx.cuh"
+#include "kernels.h"
+
+namespace rlk {
+
+namespace {
+
+__global__ void moe_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int k,
+                                int* __restrict__ idx, float* __restrict__ weight) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const float* row = logits + static_cast<long long>(t) * experts;
+  // softmax statistics over all experts (experts <= 32 * 16)
+  float v[16];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < experts ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = (lane + 32 * i) < experts ? expf(v[i] - mx) : -1.f;  // probabilities (unnormalised); -1 = absent
+    if (v[i] > 0.f) sum += v[i];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  float picked_sum = 0.f;
+  float my_w = 0.f;
+  int my_e = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -2.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > best || (v[i] == best && e < best_e)) {
+        best = v[i];
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if ((best_e & 31) == lane) v[best_e >> 5] = -1.f;  // remove the winner
+    picked_sum += best;
+    if (lane == j) {
+      my_w = best;
+      my_e = best_e;
+    }
+  }
+  if (lane < k) {
+    idx[static_cast<long long>(t) * k + lane] = my_e;
+    weight[static_cast<long long>(t) * k + lane] = my_w / picked_sum;
+  }
+  (void)sum;
+}
+
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src,
+                                       const int* __restrict__ src_row, const float* __restrict__ scale,
+                                       __nv_bfloat16* __restrict__ dst, long long ld_dst, int slots, int h8) {
+  const int slot = blockIdx.x;
+  if (slot >= slots) return;
+  const int r = src_row[slot];
+  uint4* out = reinterpret_cast<uint4*>(dst + static_cast<long long>(slot) * ld_dst);
+  if (r < 0) {
+    for (int i = threadIdx.x; i < h8; i += blockDim.x) out[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long long>(r) * ld_src);
+  const float s = scale ? scale[slot] : 1.f;
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) {
+    uint4 q = in[i];
+    if (scale) {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        h[j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      }
+    }
+    out[i] = q;
+  }
+}
+
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, const int* __restrict__ slot,
+                                   const float* __restrict__ weight, int k, __nv_bfloat16* __restrict__ out,
+                                   long long ld_out, int tokens, int h8) {
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * ld_out);
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int j = 0; j < k; ++j) {  // fixed order
+      const int s = slot[static_cast<long long>(t) * k + j];
+      if (s < 0) continue;
+      const float w = weight ? weight[static_cast<long long>(t) * k + j] : 1.f;
+      const uint4 q = reinterpret_cast<const uint4*>(src + static_cast<long long>(s) * ld_src)[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    dst[i] = o;
+  }
+}
+
+__global__ void moe_rowdot_kernel(const __nv_bfloat16* __restrict__ a, long long ld_a, const __nv_bfloat16* __restrict__ b,
+                                  long long ld_b, const int* __restrict__ slot, int k, int tokens, int h8,
+                                  float* __restrict__ out) {
+  const int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (pair >= tokens * k) return;
+  const int t = pair / k;
+  const int s = slot[pair];
+  float acc = 0.f;
+  if (s >= 0) {
+    const uint4* pa = reinterpret_cast<const uint4*>(a + static_cast<long long>(t) * ld_a);
+    const uint4* pb = reinterpret_cast<const uint4*>(b + static_cast<long long>(s) * ld_b);
+    for (int i = lane; i < h8; i += 32) {
+      const uint4 x = pa[i], y = pb[i];
+      const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(hx[e]), g = __bfloat1622float2(hy[e]);
+        acc = fmaf(f.x, g.x, acc);
+        acc = fmaf(f.y, g.y, acc);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) out[pair] = acc;
+}
+
+struct PeerBases {
+  void* p[8];
+};
+
+// Expert-parallel DISPATCH: assignment a (one CTA each) copies row src[token[a]] (times scale[a] if given)
+// into rank dest_rank[a]'s slot buffer at row dest_slot[a] with plain stores over NVLink.
+__global__ void moe_scatter_rows_peer_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src,
+                                             const int* __restrict__ token, const int* __restrict__ dest_rank,
+                                             const int* __restrict__ dest_slot, const float* __restrict__ scale,
+                                             PeerBases dst, long long ld_dst, int assignments, int h8) {
+  const int a = blockIdx.x;
+  if (a >= assignments) return;
+  const uint4* in = reinterpret_cast<const uint4*>(src + static_cast<long long>(token[a]) * ld_src);
+  uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(dst.p[dest_rank[a]]) +
+                                        static_cast<long long>(dest_slot[a]) * ld_dst);
+  const float s = scale ? scale[a] : 1.f;
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) {
+    uint4 q = in[i];
+    if (scale) {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        h[j] = __floats2bfloat162_rn(f.x * s, f.y * s);
+      }
+    }
+    out[i] = q;
+  }
+}
+
+// Expert-parallel COMBINE: out[t] = sum_j w[t, j] * buffer_{rank[t, j]}[slot[t, j]] read from the peers in
+// fixed j order.
+__global__ void moe_combine_peer_kernel(PeerBases src, long long ld_src, const int* __restrict__ rank,
+                                        const int* __restrict__ slot, const float* __restrict__ weight, int k,
+                                        __nv_bfloat16* __restrict__ out, long long ld_out, int tokens, int h8) {
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * ld_out);
+  for (int i = threadIdx.x; i < h8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const long long a = static_cast<long long>(t) * k + j;
+      const float w = weight ? weight[a] : 1.f;
+      const uint4 q = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src.p[rank[a]]) +
+                                                      static_cast<long long>(slot[a]) * ld_src)[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    dst[i] = o;
+  }
+}
+
+// d w[t, j] = <a[t], buffer_{rank[t, j]}[slot[t, j]]>
+__global__ void moe_rowdot_peer_kernel(const __nv_bfloat16* __restrict__ a, long long ld_a, PeerBases b, long long ld_b,
+                                       const int* __restrict__ rank, const int* __restrict__ slot, int k, int tokens,
+                                       int h8, float* __restrict__ out) {
+  const int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (pair >= tokens * k) return;
+  const int t = pair / k;
+  const uint4* pa = reinterpret_cast<const uint4*>(a + static_cast<long long>(t) * ld_a);
+  const uint4* pb = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(b.p[rank[pair]]) +
+                                                   static_cast<long long>(slot[pair]) * ld_b);
+  float acc = 0.f;
+  for (int i = lane; i < h8; i += 32) {
+    const uint4 x = pa[i], y = pb[i];
+    const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&x);
+    const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(hx[e]), g = __bfloat1622float2(hy[e]);
+      acc = fmaf(f.x, g.x, acc);
+      acc = fmaf(f.y, g.y, acc);
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) out[pair] = acc;
+}
+
+PeerBases make_bases(void* const* p, int world) {
+  PeerBases b;
+  for (int r = 0; r < 8; ++r) b.p[r] = r < world ? p[r] : nullptr;
+  return b;
+}
+
+}  // namespace
+
+void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int* token, const int* dest_rank,
+                           const int* dest_slot, const float* scale, void* const* dst, int world, long long ld_dst,
+                           int assignments, int hidden, cudaStream_t stream) {
+  if (assignments <= 0) return;
+  moe_scatter_rows_peer_kernel<<<assignments, 128, 0, stream>>>(src, ld_src, token, dest_rank, dest_slot, scale,
+                                                                make_bases(dst, world), ld_dst, assignments, hidden / 8);
+}
+
+void moe_combine_peer(void* const* src, int world, long long ld_src, const int* rank, const int* slot, const float* weight,
+                      int k, __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  moe_combine_peer_kernel<<<tokens, 128, 0, stream>>>(make_bases(src, world), ld_src, rank, slot, weight, k, out, ld_out,
+                                                      tokens, hidden / 8);
+}
+
+void moe_rowdot_peer(const __nv_bfloat16* a, long long ld_a, void* const* b, int world, long long ld_b, const int* rank,
+                     const int* slot, int k, int tokens, int hidden, float* out, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  const int threads = 128;
+  const long long warps = static_cast<long long>(tokens) * k;
+  moe_rowdot_peer_kernel<<<static_cast<unsigned int>((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
+      a, ld_a, make_bases(b, world), ld_b, rank, slot, k, tokens, hidden / 8, out);
+}
+
+void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, float* weight, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  const int threads = 128;
+  moe_topk_kernel<<<(tokens * 32 + threads - 1) / threads, threads, 0, stream>>>(logits, tokens, experts, k, idx, weight);
+}
+
+void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,
+                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream) {
+  if (slots <= 0) return;
+  moe_gather_rows_kernel<<<slots, 128, 0, stream>>>(src, ld_src, src_row, scale, dst, ld_dst, slots, hidden / 8);
+}
+
+void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, const float* weight, int k,
+                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  moe_combine_kernel<<<tokens, 128, 0, stream>>>(src, ld_src, slot, weight, k, out, ld_out, tokens, hidden / 8);
+}
+
+void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,
+                int tokens, int hidden, float* out, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  const int threads = 128;
+  const long long warps = static_cast<long long>(tokens) * k;
+  moe_rowdot_kernel<<<static_cast<unsigned int>((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
+      a, ld_a, b, ld_b, slot, k, tokens, hidden / 8, out);
+}
+
+}  // namespace rlk

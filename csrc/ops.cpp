@@ -109,6 +109,173 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optiona
   return d;
 }
 
+// Grouped GEMM for mixture-of-experts layers (see GemmArgs::group_mode in kernels.h).
+//   mode 1: a [rows, K] (rows grouped by expert, 128-row padded blocks), b [G * N, K] (b_mn = false) or
+//           [G * K, N] (b_mn = true, used for dX = dY * W_g), tile_group int32 [rows / 128]  -> out [rows, N]
+//   mode 2: a [rows, M], b [rows, N], group_offsets int32 [G + 1]  -> out [G * M, N] = per-group a^T b
+Tensor grouped_gemm(const Tensor& a, const Tensor& b, int64_t mode, const Tensor& table, int64_t num_groups, bool b_mn,
+                    bool out_fp32) {
+  check_rowmajor(a, "a");
+  check_rowmajor(b, "b");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "grouped_gemm: bf16 operands only");
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == torch::kInt32 && table.is_contiguous(), "grouped_gemm: int32 table on GPU");
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
+              "grouped_gemm: operands must be 16-byte aligned with 16-byte row pitch");
+  const c10::cuda::CUDAGuard guard(a.device());
+  rlk::GemmArgs g;
+  g.A = reinterpret_cast<const __nv_bfloat16*>(a.data_ptr());
+  g.B = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  g.out_fp32 = out_fp32;
+  g.accumulate = false;
+  g.alpha = 1.f;
+  g.sm_count = sm_count_of(a.get_device());
+  g.err = err_ptr(a);
+  g.group_mode = static_cast<int>(mode);
+  g.num_groups = static_cast<int>(num_groups);
+  Tensor d;
+  auto odt = a.options().dtype(out_fp32 ? torch::kFloat32 : torch::kBFloat16);
+  if (mode == 1) {
+    TORCH_CHECK(a.size(0) % 128 == 0 && table.numel() == a.size(0) / 128, "grouped_gemm(1): rows must be 128-padded, one table entry per tile");
+    const int64_t K = a.size(1);
+    const int64_t N = b_mn ? b.size(1) : b.size(0) / num_groups;
+    TORCH_CHECK(b_mn ? (b.size(0) == num_groups * K) : (b.size(1) == K && b.size(0) == num_groups * N), "grouped_gemm(1): b has the wrong shape");
+    TORCH_CHECK(!b_mn || K % 64 == 0, "grouped_gemm(1): contraction size must be a multiple of 64 for stacked MN-major b");
+    d = torch::empty({a.size(0), N}, odt);
+    g.M = static_cast<int>(a.size(0));
+    g.N = static_cast<int>(N);
+    g.K = static_cast<int>(K);
+    g.a_mn_major = false;
+    g.b_mn_major = b_mn;
+    g.tile_group = table.data_ptr<int>();
+  } else {
+    TORCH_CHECK(mode == 2 && a.size(0) == b.size(0) && table.numel() == num_groups + 1, "grouped_gemm(2): bad operands");
+    TORCH_CHECK(a.size(1) % 128 == 0, "grouped_gemm(2): per-group output rows must be a multiple of 128");
+    d = torch::empty({num_groups * a.size(1), b.size(1)}, odt);
+    g.M = static_cast<int>(a.size(1));
+    g.N = static_cast<int>(b.size(1));
+    g.K = static_cast<int>(a.size(0));
+    g.a_mn_major = true;
+    g.b_mn_major = true;
+    g.group_offsets = table.data_ptr<int>();
+  }
+  g.D = d.data_ptr();
+  g.ldd = d.stride(0);
+  if (d.numel() == 0) return d;
+  rlk::gemm_bf16(g, stream_of(a));
+  after_launch();
+  return d;
+}
+
+std::vector<Tensor> moe_topk(const Tensor& logits, int64_t k) {
+  check_rowmajor(logits, "router_logits");
+  TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.is_contiguous(), "moe_topk: contiguous float32 logits");
+  TORCH_CHECK(logits.size(1) <= 512 && k >= 1 && k <= 32 && k <= logits.size(1), "moe_topk: experts <= 512, 1 <= k <= min(32, experts)");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  Tensor idx = torch::empty({logits.size(0), k}, logits.options().dtype(torch::kInt32));
+  Tensor w = torch::empty({logits.size(0), k}, logits.options());
+  if (logits.size(0)) {
+    rlk::moe_topk(logits.data_ptr<float>(), static_cast<int>(logits.size(0)), static_cast<int>(logits.size(1)),
+                  static_cast<int>(k), idx.data_ptr<int>(), w.data_ptr<float>(), stream_of(logits));
+    after_launch();
+  }
+  return {idx, w};
+}
+
+void check_bf16_rows(const Tensor& t, const char* n) {
+  check_rowmajor(t, n);
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16 && t.size(1) % 8 == 0 && t.stride(0) % 8 == 0 &&
+                  reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              "rl_engine.moe: ", n, " must be bf16 rows of a multiple of 8 elements, 16-byte aligned");
+}
+
+// dst_ptr == 0: allocate [slots, H] locally; else write to that device address (e.g. a peer's buffer).
+Tensor moe_gather_rows(const Tensor& src, const Tensor& src_row, std::optional<Tensor> scale, int64_t dst_ptr,
+                       int64_t dst_ld) {
+  check_bf16_rows(src, "src");
+  TORCH_CHECK(src_row.is_cuda() && src_row.scalar_type() == torch::kInt32 && src_row.is_contiguous(), "src_row: int32 GPU");
+  const c10::cuda::CUDAGuard guard(src.device());
+  const int64_t slots = src_row.numel(), h = src.size(1);
+  Tensor out;
+  __nv_bfloat16* dst;
+  long long ld;
+  if (dst_ptr == 0) {
+    out = torch::empty({slots, h}, src.options());
+    dst = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    ld = h;
+  } else {
+    dst = reinterpret_cast<__nv_bfloat16*>(dst_ptr);
+    ld = dst_ld;
+  }
+  const float* sp = nullptr;
+  Tensor sc;
+  if (scale.has_value() && scale->defined()) {
+    sc = scale->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(sc.numel() == slots, "scale must have one entry per slot");
+    sp = sc.data_ptr<float>();
+  }
+  if (slots) {
+    rlk::moe_gather_rows(reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), src.stride(0), src_row.data_ptr<int>(), sp,
+                         dst, ld, static_cast<int>(slots), static_cast<int>(h), stream_of(src));
+    after_launch();
+  }
+  return out;
+}
+
+// src_ptr != 0 reads rows from that device address (e.g. a peer's expert output buffer) with pitch src_ld.
+Tensor moe_combine(std::optional<Tensor> src, int64_t src_ptr, int64_t src_ld, int64_t hidden, const Tensor& slot,
+                   std::optional<Tensor> weight) {
+  TORCH_CHECK(slot.is_cuda() && slot.scalar_type() == torch::kInt32 && slot.is_contiguous() && slot.dim() == 2, "slot: int32 [T, k]");
+  const c10::cuda::CUDAGuard guard(slot.device());
+  const __nv_bfloat16* sp;
+  long long ld;
+  if (src.has_value() && src->defined()) {
+    check_bf16_rows(*src, "src");
+    sp = reinterpret_cast<const __nv_bfloat16*>(src->data_ptr());
+    ld = src->stride(0);
+    hidden = src->size(1);
+  } else {
+    TORCH_CHECK(src_ptr != 0 && hidden % 8 == 0, "moe_combine: need src tensor or src_ptr");
+    sp = reinterpret_cast<const __nv_bfloat16*>(src_ptr);
+    ld = src_ld;
+  }
+  const float* wp = nullptr;
+  Tensor w;
+  if (weight.has_value() && weight->defined()) {
+    w = weight->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(w.numel() == slot.numel(), "weight must match slot");
+    wp = w.data_ptr<float>();
+  }
+  Tensor out = torch::empty({slot.size(0), hidden}, slot.options().dtype(torch::kBFloat16));
+  if (slot.size(0)) {
+    rlk::moe_combine(sp, ld, slot.data_ptr<int>(), wp, static_cast<int>(slot.size(1)),
+                     reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0), static_cast<int>(slot.size(0)),
+                     static_cast<int>(hidden), stream_of(slot));
+    after_launch();
+  }
+  return out;
+}
+
+Tensor moe_rowdot(const Tensor& a, const Tensor& b, const Tensor& slot) {
+  check_bf16_rows(a, "a");
+  check_bf16_rows(b, "b");
+  TORCH_CHECK(slot.is_cuda() && slot.scalar_type() == torch::kInt32 && slot.is_contiguous() && slot.dim() == 2 &&
+                  slot.size(0) == a.size(0) && a.size(1) == b.size(1),
+              "moe_rowdot: slot int32 [T, k], a [T, H], b [slots, H]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = torch::empty({slot.size(0), slot.size(1)}, a.options().dtype(torch::kFloat32));
+  if (slot.numel()) {
+    rlk::moe_rowdot(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), a.stride(0),
+                    reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), b.stride(0), slot.data_ptr<int>(),
+                    static_cast<int>(slot.size(1)), static_cast<int>(slot.size(0)), static_cast<int>(a.size(1)),
+                    out.data_ptr<float>(), stream_of(a));
+    after_launch();
+  }
+  return out;
+}
+
 // ------------------------------------------------------------------------- linear -> logprob
 std::vector<int64_t> linear_logp_workspace_shape(int64_t n_tokens, int64_t v_local, int64_t world) {
   int items = 0, n_pad = 0, tiles_m = 0;
@@ -773,6 +940,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "rl_engine native sm_100a kernels";
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("moe_topk", &moe_topk);
+  m.def("moe_gather_rows", &moe_gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
+        py::arg("dst_ptr") = 0, py::arg("dst_ld") = 0);
+  m.def("moe_combine", &moe_combine, py::arg("src"), py::arg("src_ptr"), py::arg("src_ld"), py::arg("hidden"), py::arg("slot"),
+        py::arg("weight") = py::none());
+  m.def("moe_rowdot", &moe_rowdot);
   m.def("linear_logp_workspace_shape", &linear_logp_workspace_shape);
   m.def("linear_logp_fwd", &linear_logp_fwd);
   m.def("linear_logp_dz", &linear_logp_dz);

@@ -83,9 +83,78 @@ void py_cast_broadcast(const Tensor& src, std::vector<uint64_t> dsts, int64_t ds
                  static_cast<int>(d.size()), src.numel(), cur_stream(src.get_device()));
 }
 
+void check_rows(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && t.size(1) % 8 == 0 &&
+                  t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
+              "rl_engine.moe: ", n, " must be aligned bf16 rows");
+}
+void check_i32(const Tensor& t, int64_t n, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous() && t.numel() == n, "rl_engine.moe: ", name,
+              " must be contiguous int32 with ", n, " entries");
+}
+
+void py_moe_scatter_rows_peer(const Tensor& src, const Tensor& token, const Tensor& dest_rank, const Tensor& dest_slot,
+                              std::optional<Tensor> scale, std::vector<uint64_t> dst, int64_t ld_dst) {
+  check_rows(src, "src");
+  const int64_t n = token.numel();
+  check_i32(token, n, "token");
+  check_i32(dest_rank, n, "dest_rank");
+  check_i32(dest_slot, n, "dest_slot");
+  const c10::cuda::CUDAGuard guard(src.device());
+  auto d = to_ptrs(dst);
+  Tensor sc;
+  const float* sp = nullptr;
+  if (scale.has_value() && scale->defined()) {
+    sc = scale->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(sc.numel() == n, "scale must have one entry per assignment");
+    sp = sc.data_ptr<float>();
+  }
+  moe_scatter_rows_peer(reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), src.stride(0), token.data_ptr<int>(),
+                        dest_rank.data_ptr<int>(), dest_slot.data_ptr<int>(), sp, d.data(), static_cast<int>(d.size()), ld_dst,
+                        static_cast<int>(n), static_cast<int>(src.size(1)), cur_stream(src.get_device()));
+}
+
+Tensor py_moe_combine_peer(std::vector<uint64_t> src, int64_t ld_src, int64_t hidden, const Tensor& rank, const Tensor& slot,
+                           std::optional<Tensor> weight) {
+  TORCH_CHECK(slot.dim() == 2 && hidden % 8 == 0, "moe_combine_peer: slot [T, k], hidden % 8 == 0");
+  check_i32(slot, slot.numel(), "slot");
+  check_i32(rank, slot.numel(), "rank");
+  const c10::cuda::CUDAGuard guard(slot.device());
+  auto s = to_ptrs(src);
+  Tensor w;
+  const float* wp = nullptr;
+  if (weight.has_value() && weight->defined()) {
+    w = weight->to(torch::kFloat32).contiguous();
+    TORCH_CHECK(w.numel() == slot.numel(), "weight must match slot");
+    wp = w.data_ptr<float>();
+  }
+  Tensor out = torch::empty({slot.size(0), hidden}, slot.options().dtype(torch::kBFloat16));
+  moe_combine_peer(s.data(), static_cast<int>(s.size()), ld_src, rank.data_ptr<int>(), slot.data_ptr<int>(), wp,
+                   static_cast<int>(slot.size(1)), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0),
+                   static_cast<int>(slot.size(0)), static_cast<int>(hidden), cur_stream(slot.get_device()));
+  return out;
+}
+
+Tensor py_moe_rowdot_peer(const Tensor& a, std::vector<uint64_t> b, int64_t ld_b, const Tensor& rank, const Tensor& slot) {
+  check_rows(a, "a");
+  TORCH_CHECK(slot.dim() == 2 && slot.size(0) == a.size(0), "moe_rowdot_peer: slot [T, k]");
+  check_i32(slot, slot.numel(), "slot");
+  check_i32(rank, slot.numel(), "rank");
+  const c10::cuda::CUDAGuard guard(a.device());
+  auto p = to_ptrs(b);
+  Tensor out = torch::empty({slot.size(0), slot.size(1)}, a.options().dtype(torch::kFloat32));
+  moe_rowdot_peer(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), a.stride(0), p.data(), static_cast<int>(p.size()), ld_b,
+                  rank.data_ptr<int>(), slot.data_ptr<int>(), static_cast<int>(slot.size(1)), static_cast<int>(slot.size(0)),
+                  static_cast<int>(a.size(1)), out.data_ptr<float>(), cur_stream(a.get_device()));
+  return out;
+}
+
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
+  m.def("moe_scatter_rows_peer", &py_moe_scatter_rows_peer);
+  m.def("moe_combine_peer", &py_moe_combine_peer);
+  m.def("moe_rowdot_peer", &py_moe_rowdot_peer);
   m.def("peer_barrier", &py_peer_barrier);
   m.def("zero1_fused_step", &py_zero1_fused_step);
   m.def("peer_sum", &py_peer_sum);

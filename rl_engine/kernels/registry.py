@@ -51,6 +51,7 @@ class OpBackend(Enum, metaclass=_BackendEnumMeta):
     SM100_ROPE = f"{_SM}.model_ops.FusedRoPESM100Op"
     SM100_EMBEDDING = f"{_SM}.model_ops.FusedEmbeddingSM100Op"
     SM100_LM_HEAD = f"{_SM}.model_ops.FusedLMHeadSM100Op"
+    SM100_MOE = f"{_SM}.moe.FusedMoESM100Op"
 
     # PyTorch oracles (CPU path and ground truth)
     PYTORCH_NATIVE = f"{_PT}.loss.logp.NativeLogpOp"
@@ -67,6 +68,7 @@ class OpBackend(Enum, metaclass=_BackendEnumMeta):
     PYTORCH_NATIVE_ROPE = f"{_PT}.linear.rope.NativeRoPEOp"
     PYTORCH_NATIVE_EMBEDDING = f"{_PT}.linear.embedding.NativeEmbeddingOp"
     PYTORCH_NATIVE_LM_HEAD = f"{_PT}.linear.lm_head.NativeLMHeadOp"
+    PYTORCH_MOE = f"{_SM}.moe.NativeMoEOp"
 
 
 _B = OpBackend
@@ -88,6 +90,7 @@ _PAIRS: Dict[str, tuple] = {
     "silu": (_B.SM100_SILU, _B.PYTORCH_NATIVE_SILU),
     "swiglu": (_B.SM100_SWIGLU, _B.PYTORCH_NATIVE_SWIGLU),
     "rope": (_B.SM100_ROPE, _B.PYTORCH_NATIVE_ROPE),
+    "moe": (_B.SM100_MOE, _B.PYTORCH_MOE),
 }
 
 

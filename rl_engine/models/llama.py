@@ -123,11 +123,16 @@ class LlamaModel(nn.Module):
         h, f = cfg.hidden_size, cfg.ffn_size
         qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab_size, h))]
+        e, fe = cfg.num_experts, cfg.moe_ffn_size
         for i in range(cfg.num_layers):
-            shapes += [
-                (f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h)), (f"l{i}.wo", (h, cfg.q_dim)),
-                (f"l{i}.mlp_norm", (h,)), (f"l{i}.w_gate_up", (2 * f, h)), (f"l{i}.w_down", (h, f)),
-            ]
+            shapes += [(f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h)), (f"l{i}.wo", (h, cfg.q_dim))]
+            if cfg.qk_norm:
+                shapes += [(f"l{i}.q_norm", (cfg.head_dim,)), (f"l{i}.k_norm", (cfg.head_dim,))]
+            shapes += [(f"l{i}.mlp_norm", (h,))]
+            if e:  # mixture of experts: router + per-expert [gate | up] and down projections, stacked by expert
+                shapes += [(f"l{i}.router", (e, h)), (f"l{i}.w_gate_up", (e * 2 * fe, h)), (f"l{i}.w_down", (e * h, fe))]
+            else:
+                shapes += [(f"l{i}.w_gate_up", (2 * f, h)), (f"l{i}.w_down", (h, f))]
         shapes += [("final_norm", (h,)), ("lm_head", (cfg.vocab_size, h))]
         # every parameter starts on a 16-byte boundary of ONE flat buffer
         offsets, total = {}, 0
@@ -210,11 +215,16 @@ class LlamaModel(nn.Module):
         return {k: v.detach() for k, v in self.named_views().items()}
 
     # -- forward ----------------------------------------------------------------------------
-    def _attention(self, qkv: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
+    def _attention(self, qkv: torch.Tensor, positions: torch.Tensor, layout, index: int = 0) -> torch.Tensor:
         cfg = self.cfg
         t = qkv.shape[0]
         qkv3 = qkv.view(t, cfg.num_heads + 2 * cfg.num_kv_heads, cfg.head_dim)
         scale = 1.0 / math.sqrt(cfg.head_dim)
+        if cfg.qk_norm:  # Qwen3: per-head RMSNorm on q and k before the rotary embedding
+            hq, hkv = cfg.num_heads, cfg.num_kv_heads
+            qn = rms_norm(qkv3[:, :hq].reshape(-1, cfg.head_dim), self.view(f"l{index}.q_norm"), cfg.rms_eps)
+            kn = rms_norm(qkv3[:, hq : hq + hkv].reshape(-1, cfg.head_dim), self.view(f"l{index}.k_norm"), cfg.rms_eps)
+            qkv3 = torch.cat([qn.view(t, hq, -1), kn.view(t, hkv, -1), qkv3[:, hq + hkv :]], dim=1)
         if _fused_path(qkv) and cfg.head_dim == 128:
             out = _FusedAttentionBlock.apply(
                 qkv3, positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale
@@ -233,9 +243,13 @@ class LlamaModel(nn.Module):
         cfg = self.cfg
         p = lambda n: self.view(f"l{index}.{n}")
         h = rms_norm(x, p("attn_norm"), cfg.rms_eps)
-        attn = self._attention(linear(h, p("wqkv")), positions, layout)
+        attn = self._attention(linear(h, p("wqkv")), positions, layout, index)
         x = x + linear(attn, p("wo"))
         h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
+        if cfg.num_experts:
+            from rl_engine.kernels.registry import kernel_registry
+
+            return x + kernel_registry.get_op("moe")(h, p("router"), p("w_gate_up"), p("w_down"), cfg.experts_per_token)
         gu = linear(h, p("w_gate_up"))
         act = swiglu_packed(gu)
         return x + linear(act, p("w_down"))

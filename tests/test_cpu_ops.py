@@ -17,7 +17,7 @@ def test_registry_routes_cpu_to_pytorch_ops_and_caches():
         "linear_logp": "NativeLinearLogpOp", "ratio_kl": "NativeRatioKLOp", "rms_norm": "NativeRMSNormOp",
         "lm_head": "NativeLMHeadOp", "embedding": "NativeEmbeddingOp", "silu": "NativeSiLUOp",
         "swiglu": "NativeSwiGLUOp", "rope": "NativeRoPEOp", "ppo_loss": "NativePPOLossOp", "dpo_loss": "NativeDPOLossOp",
-        "prefix_shared_attn": "NativePrefixSharedAttentionOp",
+        "prefix_shared_attn": "NativePrefixSharedAttentionOp", "moe": "NativeMoEOp",
     }
     for op_type, cls in expected.items():
         op = reg.get_op(op_type)
