@@ -116,6 +116,12 @@ __device__ __forceinline__ ItemGeometry item_geometry(const GemmProblem& p, int 
   return g;
 }
 
+// Grouped-M mode: a 128-row tile whose group id is negative holds no rows (the unused tail of a
+// statically sized slot buffer); the three warp roles skip it alike and its output stays unwritten.
+__device__ __forceinline__ bool item_skipped(const GemmProblem& p, int m_tile) {
+  return p.group_mode == 1 && p.tile_group[m_tile] < 0;
+}
+
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
@@ -186,6 +192,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t phase = 0;
       for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
+        if (item_skipped(p, w.m_tile)) continue;
         const ItemGeometry geo = item_geometry(p, w.m_tile);
         const int m0 = geo.a_m0;
         for (int nt = w.n_begin; nt < w.n_end; ++nt) {
@@ -227,6 +234,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t buf_phase = 0;
       for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
+        if (item_skipped(p, w.m_tile)) continue;
         const int item_k_blocks = item_geometry(p, w.m_tile).k_blocks;
         for (int nt = w.n_begin; nt < w.n_end; ++nt) {
           mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag, err, kernel_id, 2);
@@ -271,6 +279,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     Epi::start(ep, p);
     for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
       const WorkItem w = decode_item(p, id);
+      if (item_skipped(p, w.m_tile)) continue;
       const int row = w.m_tile * kBM + t.row_in_tile;
       Epi::begin_item(st, ep, p, w, row);
       for (int nt = w.n_begin; nt < w.n_end; ++nt) {

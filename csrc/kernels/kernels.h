@@ -312,7 +312,5 @@ void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int
                            int assignments, int hidden, cudaStream_t stream);
 void moe_combine_peer(void* const* src, int world, long long ld_src, const int* rank, const int* slot, const float* weight,
                       int k, __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream);
-void moe_rowdot_peer(const __nv_bfloat16* a, long long ld_a, void* const* b, int world, long long ld_b, const int* rank,
-                     const int* slot, int k, int tokens, int hidden, float* out, cudaStream_t stream);
 
 }  // namespace rlk

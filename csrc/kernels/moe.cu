@@ -227,34 +227,6 @@ __global__ void moe_combine_peer_kernel(PeerBases src, long long ld_src, const i
   }
 }
 
-// d w[t, j] = <a[t], buffer_{rank[t, j]}[slot[t, j]]>
-__global__ void moe_rowdot_peer_kernel(const __nv_bfloat16* __restrict__ a, long long ld_a, PeerBases b, long long ld_b,
-                                       const int* __restrict__ rank, const int* __restrict__ slot, int k, int tokens,
-                                       int h8, float* __restrict__ out) {
-  const int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (pair >= tokens * k) return;
-  const int t = pair / k;
-  const uint4* pa = reinterpret_cast<const uint4*>(a + static_cast<long long>(t) * ld_a);
-  const uint4* pb = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(b.p[rank[pair]]) +
-                                                   static_cast<long long>(slot[pair]) * ld_b);
-  float acc = 0.f;
-  for (int i = lane; i < h8; i += 32) {
-    const uint4 x = pa[i], y = pb[i];
-    const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&x);
-    const __nv_bfloat162* hy = reinterpret_cast<const __nv_bfloat162*>(&y);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __bfloat1622float2(hx[e]), g = __bfloat1622float2(hy[e]);
-      acc = fmaf(f.x, g.x, acc);
-      acc = fmaf(f.y, g.y, acc);
-    }
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) out[pair] = acc;
-}
-
 PeerBases make_bases(void* const* p, int world) {
   PeerBases b;
   for (int r = 0; r < 8; ++r) b.p[r] = r < world ? p[r] : nullptr;
@@ -276,15 +248,6 @@ void moe_combine_peer(void* const* src, int world, long long ld_src, const int* 
   if (tokens <= 0) return;
   moe_combine_peer_kernel<<<tokens, 128, 0, stream>>>(make_bases(src, world), ld_src, rank, slot, weight, k, out, ld_out,
                                                       tokens, hidden / 8);
-}
-
-void moe_rowdot_peer(const __nv_bfloat16* a, long long ld_a, void* const* b, int world, long long ld_b, const int* rank,
-                     const int* slot, int k, int tokens, int hidden, float* out, cudaStream_t stream) {
-  if (tokens <= 0) return;
-  const int threads = 128;
-  const long long warps = static_cast<long long>(tokens) * k;
-  moe_rowdot_peer_kernel<<<static_cast<unsigned int>((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
-      a, ld_a, make_bases(b, world), ld_b, rank, slot, k, tokens, hidden / 8, out);
 }
 
 void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, float* weight, cudaStream_t stream) {

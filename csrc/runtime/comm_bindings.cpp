@@ -135,26 +135,11 @@ Tensor py_moe_combine_peer(std::vector<uint64_t> src, int64_t ld_src, int64_t hi
   return out;
 }
 
-Tensor py_moe_rowdot_peer(const Tensor& a, std::vector<uint64_t> b, int64_t ld_b, const Tensor& rank, const Tensor& slot) {
-  check_rows(a, "a");
-  TORCH_CHECK(slot.dim() == 2 && slot.size(0) == a.size(0), "moe_rowdot_peer: slot [T, k]");
-  check_i32(slot, slot.numel(), "slot");
-  check_i32(rank, slot.numel(), "rank");
-  const c10::cuda::CUDAGuard guard(a.device());
-  auto p = to_ptrs(b);
-  Tensor out = torch::empty({slot.size(0), slot.size(1)}, a.options().dtype(torch::kFloat32));
-  moe_rowdot_peer(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), a.stride(0), p.data(), static_cast<int>(p.size()), ld_b,
-                  rank.data_ptr<int>(), slot.data_ptr<int>(), static_cast<int>(slot.size(1)), static_cast<int>(slot.size(0)),
-                  static_cast<int>(a.size(1)), out.data_ptr<float>(), cur_stream(a.get_device()));
-  return out;
-}
-
 }  // namespace
 
 void bind_comm(pybind11::module_& m) {
   m.def("moe_scatter_rows_peer", &py_moe_scatter_rows_peer);
   m.def("moe_combine_peer", &py_moe_combine_peer);
-  m.def("moe_rowdot_peer", &py_moe_rowdot_peer);
   m.def("peer_barrier", &py_peer_barrier);
   m.def("zero1_fused_step", &py_zero1_fused_step);
   m.def("peer_sum", &py_peer_sum);

@@ -1,7 +1,7 @@
 """Host-side work lists for the fused attention backward kernels.
 
 The dQ kernel reuses the forward's query-tile table.  The dK/dV kernel needs, for every 128-key
-tile of every distinct key range, the list of 64-query blocks that can see it; long lists (a shared
+tile of the key axis, the list of 64-query blocks that can see it; long lists (a shared
 prompt is seen by every completion) are split into items whose partial sums are reduced in slot
 order, which keeps the result bitwise reproducible.  Lists depend only on the packed layout and are
 cached with it.
@@ -26,37 +26,46 @@ def build_plan(layout) -> tuple:
     hit = _PLAN_CACHE.get(id(layout))
     if hit is not None and hit[0] is layout:
         return hit[1]
-    # key range -> [(q_start, q_len, causal)]
-    ranges: Dict[Tuple[int, int], List[Tuple[int, int, int]]] = {}
+    # readers: (k_start, k_len, q_start, q_len, causal).  Key ranges of different sequences may be equal
+    # (a prompt shared by a group), disjoint, or overlap partly (context-parallel shards whose "prefix"
+    # covers another shard's "self" keys), so the key axis is cut at every range boundary and each
+    # elementary interval is tiled on its own: one key tile is then written by exactly one job.
+    readers: List[Tuple[int, int, int, int, int]] = []
     for (q_start, q_len, pk_start, pk_len, sk_start, sk_len) in layout.host_seqs:
         if pk_len:
-            ranges.setdefault((pk_start, pk_len), []).append((q_start, q_len, 0))
+            readers.append((pk_start, pk_len, q_start, q_len, 0))
         if sk_len:
-            ranges.setdefault((sk_start, sk_len), []).append((q_start, q_len, 1 if layout.causal else 0))
+            readers.append((sk_start, sk_len, q_start, q_len, 1 if layout.causal else 0))
+    cuts = sorted({r[0] for r in readers} | {r[0] + r[1] for r in readers})
     q_blocks: List[List[int]] = []
     items: List[List[int]] = []
     jobs: List[List[int]] = []
     slots = 0
-    for (k_start, k_len), readers in sorted(ranges.items()):
-        for k_pos in range(0, k_len, KEY_TILE):
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        covering = [r for r in readers if r[0] <= lo and hi <= r[0] + r[1]]
+        if not covering:
+            continue
+        for k_abs in range(lo, hi, KEY_TILE):
             begin = len(q_blocks)
-            for (q_start, q_len, causal) in readers:
+            for (k_start, _k_len, q_start, q_len, causal) in covering:
+                k_pos = k_abs - k_start  # index of the tile's first key inside this reader's range
                 for q_pos in range(0, q_len, Q_BLOCK):
                     n_rows = min(Q_BLOCK, q_len - q_pos)
                     if causal and q_pos + n_rows - 1 < k_pos:
                         continue  # every query of the block precedes the tile's first key
-                    q_blocks.append([q_start + q_pos, n_rows, q_pos, causal])
+                    # the kernel's causal test only uses (item k_pos - block q_pos): fold k_pos in here
+                    q_blocks.append([q_start + q_pos, n_rows, q_pos - k_pos, causal])
             end = len(q_blocks)
             if end == begin:
                 continue
-            tile_len = min(KEY_TILE, k_len - k_pos)
+            tile_len = min(KEY_TILE, hi - k_abs)
             pieces = [(b, min(b + MAX_BLOCKS_PER_ITEM, end)) for b in range(begin, end, MAX_BLOCKS_PER_ITEM)]
             if len(pieces) == 1:
-                items.append([k_start + k_pos, tile_len, k_pos, begin, end, -1, 0, 0])
+                items.append([k_abs, tile_len, 0, begin, end, -1, 0, 0])
             else:
-                jobs.append([k_start + k_pos, tile_len, slots, slots + len(pieces)])
+                jobs.append([k_abs, tile_len, slots, slots + len(pieces)])
                 for (b, e) in pieces:
-                    items.append([k_start + k_pos, tile_len, k_pos, b, e, slots, 0, 0])
+                    items.append([k_abs, tile_len, 0, b, e, slots, 0, 0])
                     slots += 1
     items.sort(key=lambda it: it[3] - it[4])  # longest lists first
     dev = layout.seqs.device

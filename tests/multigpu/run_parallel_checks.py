@@ -2,7 +2,9 @@
 
 Covers: symmetric heap mapping + device barrier, vocab-parallel fused linear_logp (forward bitwise
 equal on all ranks and close to the single-GPU op, backward vs autograd), the fused
-reduce-scatter + AdamW + all-gather step vs a single-process AdamW, and the weight broadcast+cast.
+reduce-scatter + AdamW + all-gather step vs a single-process AdamW, the weight broadcast+cast, the
+context-parallel causal attention (zig-zag shards) against full-sequence attention, and the
+expert-parallel MoE (peer-store dispatch / peer-load combine) against the single-GPU fused MoE.
 Every rank prints ``OK <name>`` lines; rank 0 prints ``ALL OK`` at the end.
 """
 
@@ -113,6 +115,82 @@ def main() -> None:
     assert all(torch.equal(both[0], x) for x in both), "parameters diverged between ranks"
     mem.check()
     print(f"[{rank}] OK zero1 fused step", flush=True)
+
+    # ---- expert-parallel MoE over peer stores / loads ----------------------------------------------
+    from rl_engine.kernels.ops.sm100.moe import FusedMoESM100Op
+    from rl_engine.parallel.expert_parallel import ExpertParallelContext, ExpertParallelMoE
+
+    E, K, H, F, T = 4 * world, 2, 256, 128, 300 + 17 * rank
+    gw = torch.Generator(device=dev).manual_seed(21)  # same weights on all ranks
+    router = (torch.randn(E, H, device=dev, generator=gw) * 0.3).to(torch.bfloat16)
+    w1 = (torch.randn(E * 2 * F, H, device=dev, generator=gw) * 0.06).to(torch.bfloat16)
+    w2 = (torch.randn(E * H, F, device=dev, generator=gw) * 0.09).to(torch.bfloat16)
+    gx = torch.Generator(device=dev).manual_seed(300 + rank)  # own tokens
+    x = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
+    dout = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
+    el = E // world
+    ctx = ExpertParallelContext(H, E, K, max_tokens=400, group=dist.group.WORLD, device=dev)
+    ep_op = ExpertParallelMoE(ctx)
+    xe = x.clone().requires_grad_(True)
+    re_ = router.clone().requires_grad_(True)
+    w1l = w1.view(E, 2 * F, H)[rank * el:(rank + 1) * el].reshape(-1, H).clone().requires_grad_(True)
+    w2l = w2.view(E, H, F)[rank * el:(rank + 1) * el].reshape(-1, F).clone().requires_grad_(True)
+    out_ep = ep_op(xe, re_, w1l, w2l)
+    out_ep.backward(dout)
+    xf = x.clone().requires_grad_(True)
+    rf = router.clone().requires_grad_(True)
+    w1f = w1.clone().requires_grad_(True)
+    w2f = w2.clone().requires_grad_(True)
+    out_full = FusedMoESM100Op()(xf, rf, w1f, w2f, K)
+    out_full.backward(dout)
+
+    def close(a, b, tol, what):
+        scale = b.float().abs().max().clamp_min(1e-6)
+        err_ = ((a.float() - b.float()).abs().max() / scale).item()
+        assert err_ < tol, f"expert parallel {what}: relative error {err_:.3e}"
+
+    close(out_ep, out_full, 2e-2, "output")
+    close(xe.grad, xf.grad, 2e-2, "dx")
+    close(re_.grad, rf.grad, 3e-2, "router grad")
+    g1 = w1f.grad.float().clone()
+    g2 = w2f.grad.float().clone()
+    dist.all_reduce(g1)
+    dist.all_reduce(g2)
+    close(w1l.grad, g1.view(E, 2 * F, H)[rank * el:(rank + 1) * el].reshape(-1, H), 2e-2, "dW1")
+    close(w2l.grad, g2.view(E, H, F)[rank * el:(rank + 1) * el].reshape(-1, F), 2e-2, "dW2")
+    out_again = ep_op(x, router, w1l.detach(), w2l.detach())
+    assert torch.equal(out_again, out_ep.detach()), "expert-parallel forward is not run-to-run deterministic"
+    ctx.mem.check()
+    check_device_errors(local)
+    print(f"[{rank}] OK expert-parallel MoE", flush=True)
+
+    # ---- context-parallel causal attention (zig-zag shards, peer-store K/V gather, peer_sum dK/dV) ----
+    from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
+    from rl_engine.parallel.context_parallel import ContextParallelAttention, shard_sequence
+
+    HQ, HKV, C = 4, 2, 192
+    S = 2 * world * C
+    ga = torch.Generator(device=dev).manual_seed(77)  # same full sequence on all ranks
+    qa = torch.randn(S, HQ, 128, device=dev, generator=ga).to(torch.bfloat16)
+    ka = torch.randn(S, HKV, 128, device=dev, generator=ga).to(torch.bfloat16)
+    va = torch.randn(S, HKV, 128, device=dev, generator=ga).to(torch.bfloat16)
+    da = torch.randn(S, HQ, 128, device=dev, generator=ga).to(torch.bfloat16)
+    cp = ContextParallelAttention(S, HKV, group=dist.group.WORLD, device=dev)
+    ql, kl, vl = (shard_sequence(t, rank, world).clone().requires_grad_(True) for t in (qa, ka, va))
+    out_cp = cp(ql, kl, vl)
+    out_cp.backward(shard_sequence(da, rank, world))
+    qf_, kf_, vf_ = (t.clone().requires_grad_(True) for t in (qa, ka, va))
+    full_out = FlashAttentionSM100Op()(qf_[None], kf_[None], vf_[None], causal=True)[0]
+    full_out.backward(da)
+    close(out_cp, shard_sequence(full_out.detach(), rank, world), 2e-2, "cp output")
+    close(ql.grad, shard_sequence(qf_.grad, rank, world), 2e-2, "cp dq")
+    close(kl.grad, shard_sequence(kf_.grad, rank, world), 2e-2, "cp dk")
+    close(vl.grad, shard_sequence(vf_.grad, rank, world), 2e-2, "cp dv")
+    out_cp2 = cp(ql.detach(), kl.detach(), vl.detach())
+    assert torch.equal(out_cp2, out_cp.detach()), "context-parallel forward is not run-to-run deterministic"
+    cp.mem.check()
+    check_device_errors(local)
+    print(f"[{rank}] OK context-parallel attention", flush=True)
 
     dist.barrier()
     if rank == 0:

@@ -238,3 +238,55 @@ def test_ppo_and_dpo_oracles():
     tok = torch.randn(2, 4)
     m = torch.tensor([[1, 1, 0, 0], [1, 1, 1, 1]], dtype=torch.bool)
     assert torch.allclose(NativeDPOLossOp.sequence_logps(tok, m), (tok * m).sum(-1))
+
+
+def test_expert_parallel_plan_is_a_consistent_partition():
+    """Every rank derives its send slots from the same count matrix: together the assignments of all
+    ranks fill each owner's expert blocks exactly once, in (source rank, assignment) order."""
+    from rl_engine.parallel.expert_parallel import build_ep_plan
+
+    world, experts, k = 4, 8, 2
+    g = torch.Generator().manual_seed(0)
+    idxs = [torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(40 + 7 * r)]).int() for r in range(world)]
+    counts = torch.stack([torch.bincount(i.reshape(-1).long(), minlength=experts) for i in idxs])
+    plans = [build_ep_plan(idxs[r], counts, r, world, 4096) for r in range(world)]
+    el = experts // world
+    for owner in range(world):
+        taken = []
+        for r in range(world):
+            sel = plans[r].dest_rank == owner
+            slots = plans[r].dest_slot[sel].long()
+            exp = idxs[r].reshape(-1)[sel].long() - owner * el
+            off = plans[owner].offsets.long()
+            assert bool(((slots >= off[exp]) & (slots < off[exp + 1])).all())
+            taken.append(slots)
+        taken = torch.cat(taken)
+        assert taken.unique().numel() == taken.numel()
+        total = counts[:, owner * el:(owner + 1) * el].sum(0)
+        off = plans[owner].offsets.long()
+        for e in range(el):
+            want = torch.arange(off[e], off[e] + total[e])
+            got = taken[(taken >= off[e]) & (taken < off[e + 1])].sort().values
+            assert torch.equal(got, want)
+        tg = plans[owner].tile_group
+        used_tiles = int(off[-1]) // 128
+        assert bool((tg[:used_tiles] >= 0).all()) and bool((tg[used_tiles:] == -1).all())
+
+
+def test_context_parallel_zigzag_shards_round_trip_and_balance():
+    from rl_engine.parallel.context_parallel import local_layout_rows, shard_sequence, unshard_sequence, zigzag_chunks
+
+    world, chunk = 4, 6
+    x = torch.arange(2 * world * chunk * 3).view(2 * world * chunk, 3)
+    parts = [shard_sequence(x, r, world) for r in range(world)]
+    assert torch.equal(unshard_sequence(parts), x)
+    assert sorted(c for r in range(world) for c in zigzag_chunks(r, world)) == list(range(2 * world))
+    work = []
+    for r in range(world):
+        rows = local_layout_rows(r, world, chunk)
+        assert [row[0] for row in rows] == [0, chunk] and all(row[1] == chunk and row[5] == chunk for row in rows)
+        assert all(row[2] == 0 and row[3] == row[4] for row in rows)  # prefix = every key before the chunk
+        work.append(sum(row[3] + row[5] / 2 for row in rows))
+    assert max(work) == min(work)  # zig-zag gives every rank the same number of visible keys
+    with pytest.raises(ValueError):
+        shard_sequence(x[:-1], 0, world)

@@ -123,3 +123,38 @@ def test_split_key_tiles_reduce_in_order():
     for got, want in ((qa.grad, qb.grad), (ka.grad, kb.grad), (va.grad, vb.grad)):
         scale = want.abs().max().item()
         assert (got.float() - want).abs().max().item() / scale < 3e-2
+
+
+@pytest.mark.parametrize("chunk", [192, 256])
+def test_overlapping_key_ranges_match_full_causal_attention(chunk):
+    """Context-parallel style layout on one GPU: four query chunks in zig-zag order, each seeing the keys
+    before it without a mask and its own keys causally.  The prefix of one chunk overlaps other chunks'
+    self ranges, which the dK/dV work lists must cut into key tiles written exactly once."""
+    from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op, make_layout, packed_attention
+
+    hq, hkv, s = 4, 2, 4 * chunk
+    order = [0, 3, 1, 2]  # query chunks as two zig-zag shards laid end to end
+    q, k, v, do = _rand((s, hq, 128), 1), _rand((s, hkv, 128), 2), _rand((s, hkv, 128), 3), _rand((s, hq, 128), 4)
+    rows = [(i * chunk, chunk, 0, cid * chunk, cid * chunk, chunk) for i, cid in enumerate(order)]
+    layout = make_layout(rows, True, DEV)
+    perm = torch.cat([torch.arange(c * chunk, (c + 1) * chunk, device=DEV) for c in order])
+    qs = q[perm].clone().requires_grad_(True)
+    ks, vs = k.clone().requires_grad_(True), v.clone().requires_grad_(True)
+    out = packed_attention(qs, ks, vs, layout)
+    out.backward(do[perm])
+    qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
+    ref = FlashAttentionSM100Op()(qf[None], kf[None], vf[None], causal=True)[0]
+    ref.backward(do)
+    assert torch.allclose(out.float(), ref[perm].float(), atol=2e-2, rtol=2e-2)
+    for got, want in ((qs.grad, qf.grad[perm]), (ks.grad, kf.grad), (vs.grad, vf.grad)):
+        scale = want.float().abs().max()
+        assert (got.float() - want.float()).abs().max() / scale < 2e-2
+    # and against fp32 PyTorch for the key gradients
+    qd, kd, vd = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    rep = hq // hkv
+    sc = torch.einsum("qhd,khd->hqk", qd, kd.repeat_interleave(rep, 1)) / math.sqrt(128)
+    sc = sc.masked_fill(~torch.ones(s, s, dtype=torch.bool, device=DEV).tril(), float("-inf"))
+    o = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), vd.repeat_interleave(rep, 1))
+    o.backward(do.float())
+    for got, want in ((ks.grad, kd.grad), (vs.grad, vd.grad)):
+        assert (got.float() - want).abs().max() / want.abs().max() < 3e-2
