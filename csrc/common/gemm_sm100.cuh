@@ -6,6 +6,7 @@
 //   warp 1      : TMEM allocator + single-thread tcgen05.mma issuer (128 x BN x 16 per instruction)
 //   warps 2..5  : epilogue; warp w reads TMEM lanes 32*(w%4).. with tcgen05.ld, one accumulator
 //                 row per thread, so row-wise reductions need no shuffles
+//   warps 6..   : optional communication warps of a fused compute+collective functor (Epi::kCommWarps)
 //
 // Two accumulators (2 x BN columns) live in TMEM so the epilogue of tile i overlaps the MMAs of
 // tile i+1.  Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the
@@ -48,6 +49,13 @@ struct GemmProblem {
   const int* group_offsets;
   int b_group_rows;
   int tiles_m_per_group;
+  // Tensor-parallel fusions.  m_rot rotates the M-tile order (each rank starts on a different slab).
+  // When a_ready is set, the rows of M-tile t of A are produced by another agent (a peer GPU's copy
+  // warps) and may be loaded only once a_ready[t] >= a_ready_target.
+  int m_rot;
+  const unsigned int* a_ready;
+  unsigned int a_ready_target;
+  unsigned long long a_wait_ns;
 };
 
 struct ItemGeometry {
@@ -75,6 +83,10 @@ __host__ __device__ inline GemmProblem make_gemm_problem(int M, int N, int K, in
   p.group_offsets = nullptr;
   p.b_group_rows = 0;
   p.tiles_m_per_group = 1;
+  p.m_rot = 0;
+  p.a_ready = nullptr;
+  p.a_ready_target = 0;
+  p.a_wait_ns = 0;
   return p;
 }
 
@@ -93,6 +105,7 @@ __device__ __forceinline__ WorkItem decode_item(const GemmProblem& p, int id) {
   const int within = id - group * per_group;
   WorkItem w;
   w.m_tile = first_m + within % gm;
+  if (p.m_rot) w.m_tile = (w.m_tile + p.m_rot) % p.tiles_m;
   w.split = within / gm;
   w.n_begin = w.split * p.n_tiles_per_item;
   w.n_end = min(w.n_begin + p.n_tiles_per_item, p.tiles_n);
@@ -139,8 +152,38 @@ struct EpiThread {
   uint32_t lane_addr;  // (32 * quadrant) << 16, to be OR-ed into TMEM addresses
 };
 
+// Bounded wait until the rows of M-tile `m_tile` of A have landed in this GPU's memory (written by a
+// peer with generic stores + release); the fence orders the following TMA (async proxy) reads after it.
+__device__ __forceinline__ void wait_a_ready(const GemmProblem& p, int m_tile, volatile uint32_t* abort_flag,
+                                             uint32_t* err, uint32_t kernel_id) {
+  const unsigned int* flag = p.a_ready + m_tile;
+  unsigned int seen = 0;
+  uint64_t deadline = 0;
+  for (;;) {
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (static_cast<int>(seen - p.a_ready_target) >= 0) break;
+    if (*abort_flag) return;
+    const uint64_t now = global_timer_ns();
+    if (deadline == 0) {
+      deadline = now + p.a_wait_ns;
+    } else if (now > deadline) {
+      *abort_flag = 1;
+      report_error(err, kErrPeerTimeout, kernel_id, 20);
+      return;
+    }
+    __nanosleep(100);
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
+// Number of threads of a kernel instance: the six mainloop warps plus the functor's communication warps.
+template <class Epi>
+constexpr int gemm_threads() {
+  return kGemmThreads + 32 * Epi::kCommWarps;
+}
+
 template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<Epi>(), 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmProblem p, const typename Epi::Params ep, uint32_t* __restrict__ err,
                   const uint32_t kernel_id) {
@@ -195,6 +238,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (item_skipped(p, w.m_tile)) continue;
         const ItemGeometry geo = item_geometry(p, w.m_tile);
         const int m0 = geo.a_m0;
+        if (p.a_ready != nullptr) wait_a_ready(p, w.m_tile, abort_flag, err, kernel_id);
         for (int nt = w.n_begin; nt < w.n_end; ++nt) {
           const int n0 = nt * BN;
           for (int kb = 0; kb < geo.k_blocks; ++kb) {
@@ -267,6 +311,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------ communication warps (optional) ------------------------------
+    if constexpr (Epi::kCommWarps > 0) Epi::comm(ep, p, err, kernel_id);
   } else {
     // ------------------------------ epilogue ------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
@@ -324,6 +371,7 @@ struct EpiStore {
     float alpha;
   };
   struct State {};
+  static constexpr int kCommWarps = 0;
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}

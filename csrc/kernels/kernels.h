@@ -306,6 +306,48 @@ void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, co
                  __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream);
 void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,
                 int tokens, int hidden, float* out, cudaStream_t stream);
+// ---- tensor-parallel linears fused with their collectives (tp_linear.cu) -------------------------
+struct TpAgGemmArgs {
+  const __nv_bfloat16* x_local;  // [rows_local, K] this rank's rows
+  long long ldx;
+  int rows_local;                // multiple of 128
+  int K, N;
+  const __nv_bfloat16* B;        // [N, K] (K-major) or [K, N] (b_mn)
+  long long ldb;
+  bool b_mn;
+  __nv_bfloat16* C;              // [rows_local * world, N]
+  long long ldc;
+  int rank, world;
+  unsigned int epoch;            // 1, 2, ... per use of this buffer set
+  int chunks;                    // column chunks per tile (arrivals per tile and call)
+  void* gathered[8];             // bf16 [M, K] on every rank
+  void* ready[8];                // unsigned int [M / 128] on every rank
+  unsigned long long wait_ns;
+  int sm_count;
+  uint32_t* err;
+};
+void tp_ag_gemm(const TpAgGemmArgs& a, cudaStream_t stream);
+
+struct TpGemmRsArgs {
+  const __nv_bfloat16* A;        // [rows_local * world, K]
+  long long lda;
+  int rows_local;                // multiple of 128
+  int K, N;
+  const __nv_bfloat16* B;
+  long long ldb;
+  bool b_mn;
+  __nv_bfloat16* out;            // [rows_local, N]
+  long long ldo;
+  int rank, world;
+  unsigned int target;           // world * (uses of this buffer set so far, this one included)
+  void* partial[8];              // bf16 [world, rows_local, N] on every rank
+  void* counters[8];             // unsigned int [rows_local / 128 * ceil(N / 256)] on every rank
+  unsigned long long wait_ns;
+  int sm_count;
+  uint32_t* err;
+};
+void tp_gemm_rs(const TpGemmRsArgs& a, cudaStream_t stream);
+
 // expert parallelism over peer-mapped buffers (dst / src / b hold one base pointer per rank)
 void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int* token, const int* dest_rank,
                            const int* dest_slot, const float* scale, void* const* dst, int world, long long ld_dst,

@@ -109,6 +109,98 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optiona
   return d;
 }
 
+// --------------------------------------------------------------- tensor-parallel fused linears
+void fill_peers(void** dst, const std::vector<uint64_t>& src, const char* what) {
+  TORCH_CHECK(!src.empty() && src.size() <= 8, "rl_engine.tp: need 1..8 addresses for ", what);
+  for (size_t i = 0; i < 8; ++i) dst[i] = i < src.size() ? reinterpret_cast<void*>(src[i]) : nullptr;
+  for (auto a : src) TORCH_CHECK(a != 0 && a % 16 == 0, "rl_engine.tp: bad peer address for ", what);
+}
+
+// out[M, N] = allgather_rows(x_local) * B^T, the gather fused into the GEMM kernel.
+Tensor tp_ag_gemm(const Tensor& x_local, const Tensor& b, bool b_mn, int64_t rank, std::vector<uint64_t> gathered,
+                  std::vector<uint64_t> ready, int64_t epoch, int64_t chunks, double wait_ms) {
+  check_rowmajor(x_local, "x_local");
+  check_rowmajor(b, "b");
+  TORCH_CHECK(x_local.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "rl_engine.tp_ag_gemm: bf16 only");
+  const c10::cuda::CUDAGuard guard(x_local.device());
+  const int64_t world = static_cast<int64_t>(gathered.size());
+  const int64_t rows = x_local.size(0), K = x_local.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "rl_engine.tp_ag_gemm: contraction sizes differ");
+  TORCH_CHECK(rows > 0 && rows % 128 == 0, "rl_engine.tp_ag_gemm: local rows must be a positive multiple of 128");
+  TORCH_CHECK(chunks >= 1 && K % (8 * chunks) == 0, "rl_engine.tp_ag_gemm: K must be a multiple of 8 * chunks");
+  TORCH_CHECK(x_local.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(x_local.data_ptr()) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
+              "rl_engine.tp_ag_gemm: operands must be 16-byte aligned with row pitch % 8 == 0");
+  TORCH_CHECK(ready.size() == gathered.size() && rank >= 0 && rank < world, "rl_engine.tp_ag_gemm: bad rank / peer lists");
+  Tensor out = torch::empty({rows * world, N}, x_local.options());
+  rlk::TpAgGemmArgs a;
+  a.x_local = reinterpret_cast<const __nv_bfloat16*>(x_local.data_ptr());
+  a.ldx = x_local.stride(0);
+  a.rows_local = static_cast<int>(rows);
+  a.K = static_cast<int>(K);
+  a.N = static_cast<int>(N);
+  a.B = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+  a.ldb = b.stride(0);
+  a.b_mn = b_mn;
+  a.C = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  a.ldc = out.stride(0);
+  a.rank = static_cast<int>(rank);
+  a.world = static_cast<int>(world);
+  a.epoch = static_cast<unsigned int>(epoch);
+  a.chunks = static_cast<int>(chunks);
+  fill_peers(a.gathered, gathered, "gathered");
+  fill_peers(a.ready, ready, "ready");
+  a.wait_ns = static_cast<unsigned long long>(wait_ms * 1e6);
+  a.sm_count = sm_count_of(x_local.get_device());
+  a.err = err_ptr(x_local);
+  rlk::tp_ag_gemm(a, stream_of(x_local));
+  after_launch();
+  return out;
+}
+
+// out[M / W, N] = reduce_scatter_rows(a * B^T), the reduction fused into the GEMM kernel.
+Tensor tp_gemm_rs(const Tensor& a_in, const Tensor& b, bool b_mn, int64_t rank, std::vector<uint64_t> partial,
+                  std::vector<uint64_t> counters, int64_t target, double wait_ms) {
+  check_rowmajor(a_in, "a");
+  check_rowmajor(b, "b");
+  TORCH_CHECK(a_in.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "rl_engine.tp_gemm_rs: bf16 only");
+  const c10::cuda::CUDAGuard guard(a_in.device());
+  const int64_t world = static_cast<int64_t>(partial.size());
+  const int64_t M = a_in.size(0), K = a_in.size(1);
+  const int64_t N = b_mn ? b.size(1) : b.size(0);
+  TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "rl_engine.tp_gemm_rs: contraction sizes differ");
+  TORCH_CHECK(M % (128 * world) == 0 && M > 0, "rl_engine.tp_gemm_rs: rows must be a positive multiple of 128 * world");
+  TORCH_CHECK(N % 8 == 0, "rl_engine.tp_gemm_rs: N must be a multiple of 8");
+  TORCH_CHECK(a_in.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(a_in.data_ptr()) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
+              "rl_engine.tp_gemm_rs: operands must be 16-byte aligned with row pitch % 8 == 0");
+  TORCH_CHECK(counters.size() == partial.size() && rank >= 0 && rank < world, "rl_engine.tp_gemm_rs: bad rank / peer lists");
+  Tensor out = torch::empty({M / world, N}, a_in.options());
+  rlk::TpGemmRsArgs g;
+  g.A = reinterpret_cast<const __nv_bfloat16*>(a_in.data_ptr());
+  g.lda = a_in.stride(0);
+  g.rows_local = static_cast<int>(M / world);
+  g.K = static_cast<int>(K);
+  g.N = static_cast<int>(N);
+  g.B = reinterpret_cast<const __nv_bfloat16*>(b.data_ptr());
+  g.ldb = b.stride(0);
+  g.b_mn = b_mn;
+  g.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  g.ldo = out.stride(0);
+  g.rank = static_cast<int>(rank);
+  g.world = static_cast<int>(world);
+  g.target = static_cast<unsigned int>(target);
+  fill_peers(g.partial, partial, "partial");
+  fill_peers(g.counters, counters, "counters");
+  g.wait_ns = static_cast<unsigned long long>(wait_ms * 1e6);
+  g.sm_count = sm_count_of(a_in.get_device());
+  g.err = err_ptr(a_in);
+  rlk::tp_gemm_rs(g, stream_of(a_in));
+  after_launch();
+  return out;
+}
+
 // Grouped GEMM for mixture-of-experts layers (see GemmArgs::group_mode in kernels.h).
 //   mode 1: a [rows, K] (rows grouped by expert, 128-row padded blocks), b [G * N, K] (b_mn = false) or
 //           [G * K, N] (b_mn = true, used for dX = dY * W_g), tile_group int32 [rows / 128]  -> out [rows, N]
@@ -941,6 +1033,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0);
   m.def("grouped_gemm", &grouped_gemm);
+  m.def("tp_ag_gemm", &tp_ag_gemm);
+  m.def("tp_gemm_rs", &tp_gemm_rs);
   m.def("moe_topk", &moe_topk);
   m.def("moe_gather_rows", &moe_gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
         py::arg("dst_ptr") = 0, py::arg("dst_ld") = 0);

@@ -3,7 +3,7 @@
 Covers: symmetric heap mapping + device barrier, vocab-parallel fused linear_logp (forward bitwise
 equal on all ranks and close to the single-GPU op, backward vs autograd), the fused
 reduce-scatter + AdamW + all-gather step vs a single-process AdamW, the weight broadcast+cast, the
-context-parallel causal attention (zig-zag shards) against full-sequence attention, and the
+tensor-parallel linears fused with their all-gather / reduce-scatter, the context-parallel causal attention (zig-zag shards) against full-sequence attention, and the
 expert-parallel MoE (peer-store dispatch / peer-load combine) against the single-GPU fused MoE.
 Every rank prints ``OK <name>`` lines; rank 0 prints ``ALL OK`` at the end.
 """
@@ -191,6 +191,43 @@ def main() -> None:
     cp.mem.check()
     check_device_errors(local)
     print(f"[{rank}] OK context-parallel attention", flush=True)
+
+    # ---- tensor-parallel linears: all-gather -> GEMM and GEMM -> reduce-scatter in one kernel ---------
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+
+    tp = TensorParallelLinears(group=dist.group.WORLD, device=dev)
+    RL, KK, NC, NR = 256, 512, 384 * world, 640
+    MM = RL * world
+    rows = slice(rank * RL, (rank + 1) * RL)
+    for it in range(3):  # three rounds: both buffer parities and the monotonic counters get reused
+        gt = torch.Generator(device=dev).manual_seed(500 + it)  # same full problem on all ranks
+        X = torch.randn(MM, KK, device=dev, generator=gt).to(torch.bfloat16)
+        WC = (torch.randn(NC, KK, device=dev, generator=gt) * 0.05).to(torch.bfloat16)
+        DY = torch.randn(MM, NC, device=dev, generator=gt).to(torch.bfloat16)
+        ncol = slice(rank * NC // world, (rank + 1) * NC // world)
+        xl = X[rows].clone().requires_grad_(True)
+        wl = WC[ncol].clone().requires_grad_(True)
+        y = tp.column_parallel(xl, wl)
+        y.backward(DY[:, ncol].contiguous())
+        close(y, X.float() @ WC[ncol].float().t(), 1e-2, f"column-parallel output (round {it})")
+        close(xl.grad, (DY.float() @ WC.float())[rows], 2e-2, f"column-parallel dx (round {it})")
+        close(wl.grad, DY[:, ncol].float().t() @ X.float(), 1e-2, f"column-parallel dw (round {it})")
+
+        KL = KK // world
+        kcol = slice(rank * KL, (rank + 1) * KL)
+        WR = (torch.randn(NR, KK, device=dev, generator=gt) * 0.05).to(torch.bfloat16)
+        DY2 = torch.randn(MM, NR, device=dev, generator=gt).to(torch.bfloat16)
+        x2 = X[:, kcol].clone().requires_grad_(True)
+        w2l = WR[:, kcol].clone().requires_grad_(True)
+        y2 = tp.row_parallel(x2, w2l)
+        y2.backward(DY2[rows].contiguous())
+        close(y2, (X.float() @ WR.float().t())[rows], 2e-2, f"row-parallel output (round {it})")
+        close(x2.grad, DY2.float() @ WR[:, kcol].float(), 1e-2, f"row-parallel dx (round {it})")
+        close(w2l.grad, DY2.float().t() @ X[:, kcol].float(), 1e-2, f"row-parallel dw (round {it})")
+        y2b = tp.row_parallel(x2.detach(), w2l.detach())
+        assert torch.equal(y2b, y2.detach()), "GEMM -> reduce-scatter is not run-to-run deterministic"
+    tp.check()
+    print(f"[{rank}] OK tensor-parallel fused linears", flush=True)
 
     dist.barrier()
     if rank == 0:

@@ -47,6 +47,32 @@ def test_symmetric_memory_single_rank_and_timeout_error():
     mem.close()
 
 
+def test_fused_tp_linears_single_rank_match_plain_gemm():
+    """World size 1: the copy warps feed this GPU's own gathered buffer and the reduce phase sums a single
+    slab, so both fused kernels must reproduce the plain GEMM (three rounds reuse both buffer parities)."""
+    from rl_engine.kernels.ops.base import check_device_errors
+    from rl_engine.parallel.tp_linear import TensorParallelLinears, pick_chunks
+
+    assert pick_chunks(1024, 4096) == 8 and pick_chunks(128, 512) == 1 and pick_chunks(16384, 4096) == 2
+    tp = TensorParallelLinears()
+    for it in range(3):
+        g = torch.Generator(device="cuda").manual_seed(40 + it)
+        x = torch.randn(640, 1024, device="cuda", generator=g).to(torch.bfloat16).requires_grad_(True)
+        w = (torch.randn(712, 1024, device="cuda", generator=g) * 0.05).to(torch.bfloat16).requires_grad_(True)
+        dy = torch.randn(640, 712, device="cuda", generator=g).to(torch.bfloat16)
+        for layer in (tp.column_parallel, tp.row_parallel):
+            x.grad = w.grad = None
+            y = layer(x, w)
+            y.backward(dy)
+            ref = x.detach().float() @ w.detach().float().t()
+            assert (y.float() - ref).abs().max() / ref.abs().max() < 1e-2
+            dx = dy.float() @ w.detach().float()
+            dw = dy.float().t() @ x.detach().float()
+            assert (x.grad.float() - dx).abs().max() / dx.abs().max() < 1e-2
+            assert (w.grad.float() - dw).abs().max() / dw.abs().max() < 1e-2
+    check_device_errors(0)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
 def test_parallel_checks_two_ranks():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
