@@ -93,7 +93,7 @@ def case_linear_logp_bwd():
     return {"flops": 8.0 * n * d * v, "bytes": 0.0, "ms": ms, "shape": [n, d, v], "note": "forward + recompute backward"}
 
 
-def _attn_inputs(prompt=1024, group=16, length=512, hq=32, hkv=8):
+def _attn_inputs(prompt=1024, group=32, length=512, hq=32, hkv=8):  # Q + O = 285 MB > L2
     t = prompt + group * length
     return rand((t, hq, 128)), rand((t, hkv, 128), 1.0, 1), rand((t, hkv, 128), 1.0, 2), prompt, group, length
 
