@@ -66,6 +66,37 @@ def case_gemm_wgrad():
     return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [n, k, m]}
 
 
+def case_gemm_pair():
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    m, n, k = 8192, 14336, 4096
+    a, b = rand((m, k)), rand((n, k), 0.02, 1)
+    ms = timed(lambda: gemm(a, b, pair=True))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [m, n, k],
+            "note": "256 x 256 tiles on SM pairs (cta_group::2)"}
+
+
+def case_gemm_wgrad_pair():
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    m, n, k = 8192, 14336, 4096
+    dy, x = rand((m, n)), rand((m, k), 1.0, 1)
+    ms = timed(lambda: gemm(dy, x, a_mn=True, b_mn=True, pair=True))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [n, k, m],
+            "note": "256 x 256 tiles on SM pairs (cta_group::2)"}
+
+
+def case_gemm_dgrad_pair():
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    m, n, k = 8192, 4096, 14336
+    dy, w = rand((m, k)), rand((k, n), 0.02, 1)
+    ms_pair = timed(lambda: gemm(dy, w, b_mn=True, pair=True))
+    ms_single = timed(lambda: gemm(dy, w, b_mn=True, pair=False))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms_pair, "shape": [m, n, k],
+            "note": f"B as [K, N]; single-CTA kernel on the same problem: {ms_single:.4f} ms"}
+
+
 def case_linear_logp():
     from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
 

@@ -90,6 +90,17 @@ __host__ __device__ inline GemmProblem make_gemm_problem(int M, int N, int K, in
   return p;
 }
 
+// M-tiles per rasterisation group.  The A rows of a group are re-read for every N-tile, B is streamed once
+// per group: take as many M-tiles as keep the group's A rows within `budget_bytes` of L2 (never fewer than
+// `min_group`), so that B comes from DRAM as few times as possible.
+inline int raster_group_m(int tiles_m, int K, int min_group, long long budget_bytes = 48ll << 20) {
+  const long long per_tile = static_cast<long long>(kBM) * K * 2;
+  long long g = budget_bytes / (per_tile > 0 ? per_tile : 1);
+  if (g < min_group) g = min_group;
+  if (g > tiles_m) g = tiles_m;
+  return g < 1 ? 1 : static_cast<int>(g);
+}
+
 struct WorkItem {
   int m_tile;
   int split;    // index of the item within its M-tile

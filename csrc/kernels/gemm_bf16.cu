@@ -2,6 +2,7 @@
 // bf16 or fp32 output, optionally accumulating into the destination.  The reference has no GEMM of
 // its own (it calls cuBLAS through torch.matmul, e.g. rl_engine/kernels/ops/pytorch/loss/
 // linear_logp.py:17-38); this kernel exists so that no hot path needs a library GEMM.
+#include "../common/gemm2_sm100.cuh"
 #include "../common/gemm_sm100.cuh"
 #include "../common/tensormap.h"
 #include "kernels.h"
@@ -15,9 +16,11 @@ constexpr int kStages = 4;
 
 template <bool A_MN, bool B_MN, class Epi>
 void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
-  // Rasterise in groups of 8 M-tiles so concurrently running CTAs share A and B tiles in L2.
+  // Rasterise in groups of M-tiles so concurrently running CTAs share A and B tiles in L2 (at least 8; for
+  // a plain GEMM as many as keep the group's A rows L2-resident, so that B streams from DRAM once per group).
   const int total_m = a.group_mode == 2 ? a.M * a.num_groups : a.M;
-  GemmProblem p = make_gemm_problem(total_m, a.N, a.K, kBN, 1, 8);
+  const int group_m = a.group_mode == 0 ? raster_group_m((total_m + kBM - 1) / kBM, a.K, 8) : 8;
+  GemmProblem p = make_gemm_problem(total_m, a.N, a.K, kBN, 1, group_m);
   const int g = a.group_mode ? a.num_groups : 1;
   p.group_mode = a.group_mode;
   p.tile_group = a.tile_group;
@@ -42,8 +45,54 @@ void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stre
   kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, a.err, 100u);
 }
 
+// CTA-pair kernel: 256 x 256 tiles, one work item per pair of SMs.
+constexpr int kPairStages = 6;
+
+template <bool A_MN, bool B_MN, class Epi>
+void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
+  GemmProblem p = make_gemm_problem(a.M, a.N, a.K, kBN, 1, 1);
+  p.tiles_m = (a.M + kPairBM - 1) / kPairBM;
+  p.num_items = p.tiles_m * p.items_per_m;
+  p.group_m = raster_group_m(p.tiles_m, 2 * a.K, 4);
+  const CUtensorMap ta = A_MN ? make_tmap_2d_bf16(a.A, a.K, a.M, a.lda, kBK, 64)
+                              : make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
+  const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, a.K, a.N, a.ldb, kBK, 64)
+                              : make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kBN / 2, kBK);
+  auto kernel = gemm_pair_sm100_kernel<kBN, A_MN, B_MN, kPairStages, Epi>;
+  using L = PairSmem<kBN, kPairStages>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    configured = true;
+  }
+  int pairs = a.sm_count / 2;
+  if (p.num_items < pairs) pairs = p.num_items;
+  if (pairs < 1) return;
+  kernel<<<2 * pairs, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, a.err, 110u);
+}
+
 template <bool A_MN, bool B_MN>
 void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
+  if (a.cta_pair && a.group_mode == 0) {
+    if (a.out_fp32) {
+      if (a.accumulate) {
+        using E = EpiStore<float, true>;
+        launch_pair<A_MN, B_MN, E>(a, typename E::Params{static_cast<float*>(a.D), a.ldd, a.alpha}, stream);
+      } else {
+        using E = EpiStore<float, false>;
+        launch_pair<A_MN, B_MN, E>(a, typename E::Params{static_cast<float*>(a.D), a.ldd, a.alpha}, stream);
+      }
+    } else {
+      if (a.accumulate) {
+        using E = EpiStore<__nv_bfloat16, true>;
+        launch_pair<A_MN, B_MN, E>(a, typename E::Params{static_cast<__nv_bfloat16*>(a.D), a.ldd, a.alpha}, stream);
+      } else {
+        using E = EpiStore<__nv_bfloat16, false>;
+        launch_pair<A_MN, B_MN, E>(a, typename E::Params{static_cast<__nv_bfloat16*>(a.D), a.ldd, a.alpha}, stream);
+      }
+    }
+    return;
+  }
   if (a.out_fp32) {
     if (a.accumulate) {
       using E = EpiStore<float, true>;

@@ -34,6 +34,8 @@ struct GemmArgs {
   const int* tile_group = nullptr;
   const int* group_offsets = nullptr;
   int num_groups = 1;
+  // Plain GEMM only: compute 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2, cluster of two CTAs).
+  bool cta_pair = false;
 };
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 

@@ -292,6 +292,8 @@ void linear_logp_forward(const LinearLogpFwdArgs& a, cudaStream_t stream) {
   int items_per_m_probe = (((a.v_local + kLogpBN - 1) / kLogpBN) + splits_tiles - 1) / splits_tiles;
   int group_m = a.sm_count / (items_per_m_probe > 0 ? items_per_m_probe : 1);
   if (group_m < 1) group_m = 1;
+  // keep as many token tiles per group as stay L2-resident, so the weight streams from DRAM once per group
+  group_m = raster_group_m((a.n_tokens + kBM - 1) / kBM, a.hidden_dim, group_m, 64ll << 20);
   const GemmProblem p = make_gemm_problem(a.n_tokens, a.v_local, a.hidden_dim, kLogpBN, splits_tiles, group_m);
   const CUtensorMap ta = make_tmap_2d_bf16(a.hidden, a.n_tokens, a.hidden_dim, a.ld_hidden, kBM, kBK);
   const CUtensorMap tb = make_tmap_2d_bf16(a.weight, a.v_local, a.hidden_dim, a.ld_weight, kLogpBN, kBK);
@@ -326,7 +328,8 @@ void linear_logp_forward(const LinearLogpFwdArgs& a, cudaStream_t stream) {
 void linear_logp_dz(const LinearLogpDzArgs& a, cudaStream_t stream) {
   const int tiles_n = (a.v_local + kLogpBN - 1) / kLogpBN;
   (void)tiles_n;
-  const GemmProblem p = make_gemm_problem(a.n_tokens, a.v_local, a.hidden_dim, kLogpBN, 1, 16);
+  const GemmProblem p = make_gemm_problem(a.n_tokens, a.v_local, a.hidden_dim, kLogpBN, 1,
+                                          raster_group_m((a.n_tokens + kBM - 1) / kBM, a.hidden_dim, 16, 64ll << 20));
   const CUtensorMap ta = make_tmap_2d_bf16(a.hidden, a.n_tokens, a.hidden_dim, a.ld_hidden, kBM, kBK);
   const CUtensorMap tb = make_tmap_2d_bf16(a.weight, a.v_local, a.hidden_dim, a.ld_weight, kLogpBN, kBK);
   LogpDzParams ep;

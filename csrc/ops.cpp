@@ -5,6 +5,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+
 #include <atomic>
 #include <optional>
 #include <vector>
@@ -58,8 +60,19 @@ void after_launch(int n = 1) {
 }
 
 // ------------------------------------------------------------------------------------ GEMM
+// Default tile engine of the plain GEMM: CTA pairs (256 x 256 tiles, cta_group::2) or single CTAs.
+// RLK_GEMM_PAIR=0/1 overrides the built-in default; gemm(..., pair=0/1) overrides both for one call.
+bool gemm_pair_default() {
+  static const int value = [] {
+    const char* env = std::getenv("RLK_GEMM_PAIR");
+    if (env != nullptr && env[0] != '\0') return env[0] != '0' ? 1 : 0;
+    return 1;
+  }();
+  return value != 0;
+}
+
 Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optional<Tensor> out, bool out_fp32,
-            bool accumulate, double alpha) {
+            bool accumulate, double alpha, int64_t pair) {
   check_rowmajor(a, "a");
   check_rowmajor(b, "b");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "rl_engine.gemm: bf16 operands only");
@@ -104,6 +117,7 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optiona
   g.alpha = static_cast<float>(alpha);
   g.sm_count = sm_count_of(a.get_device());
   g.err = err_ptr(a);
+  g.cta_pair = pair < 0 ? (gemm_pair_default() && M > 128) : pair != 0;  // one 128-row tile gains nothing from a pair
   rlk::gemm_bf16(g, stream_of(a));
   after_launch();
   return d;
@@ -1031,7 +1045,8 @@ long long launch_count() { return g_launches.load(); }
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "rl_engine native sm_100a kernels";
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
-        py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0);
+        py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0,
+        py::arg("pair") = -1);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("tp_ag_gemm", &tp_ag_gemm);
   m.def("tp_gemm_rs", &tp_gemm_rs);

@@ -32,9 +32,14 @@ def gemm(
     out_dtype: torch.dtype = torch.bfloat16,
     accumulate: bool = False,
     alpha: float = 1.0,
+    pair: Optional[bool] = None,
 ) -> torch.Tensor:
-    """``D[M,N] = alpha * op(A) @ op(B).T (+ D)``; see ``csrc/kernels/kernels.h`` for layouts."""
-    return require_ext().gemm(a, b, a_mn, b_mn, out, out_dtype == torch.float32, accumulate, alpha)
+    """``D[M,N] = alpha * op(A) @ op(B).T (+ D)``; see ``csrc/kernels/kernels.h`` for layouts.
+
+    ``pair`` selects the tile engine: ``True`` = 256 x 256 tiles on pairs of SMs (``tcgen05`` ``cta_group::2``),
+    ``False`` = 128 x 256 tiles on single SMs, ``None`` = the library default (``RLK_GEMM_PAIR`` overrides it)."""
+    flag = -1 if pair is None else int(bool(pair))
+    return require_ext().gemm(a, b, a_mn, b_mn, out, out_dtype == torch.float32, accumulate, alpha, flag)
 
 
 class _LinearNT(torch.autograd.Function):

@@ -20,10 +20,15 @@ def _rand(shape, seed):
 SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 512), (200, 328, 136), (1, 8, 8), (129, 257, 72), (1000, 1000, 1000)]
 
 
+@pytest.mark.parametrize("pair", [False, True], ids=["single_cta", "cta_pair"])
 @pytest.mark.parametrize("M,N,K", SHAPES)
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
-def test_gemm_layouts(M, N, K, a_mn, b_mn):
-    from rl_engine.kernels.ops.sm100.gemm import gemm
+def test_gemm_layouts(M, N, K, a_mn, b_mn, pair):
+    from functools import partial
+
+    from rl_engine.kernels.ops.sm100 import gemm as gemm_module
+
+    gemm = partial(gemm_module.gemm, pair=pair)
 
     if (a_mn and M % 8) or (b_mn and N % 8):
         pytest.skip("MN-major operands need a 16-byte row pitch")
@@ -43,13 +48,14 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert torch.equal(got32, again)
 
 
-def test_gemm_accumulate_and_alpha():
+@pytest.mark.parametrize("pair", [False, True], ids=["single_cta", "cta_pair"])
+def test_gemm_accumulate_and_alpha(pair):
     from rl_engine.kernels.ops.sm100.gemm import gemm
 
     a, b = _rand((300, 192), 3), _rand((520, 192), 4)
     base = torch.randn(300, 520, device="cuda")
     out = base.clone()
-    gemm(a, b, out=out, out_dtype=torch.float32, accumulate=True, alpha=0.5)
+    gemm(a, b, out=out, out_dtype=torch.float32, accumulate=True, alpha=0.5, pair=pair)
     want = base + 0.5 * (a.float() @ b.float().t())
     assert torch.allclose(out, want, atol=2e-2, rtol=2e-3)
 
@@ -68,3 +74,17 @@ def test_linear_autograd_matches_torch():
     for got, want in ((y, yf), (x.grad, xf.grad), (w.grad, wf.grad)):
         scale = want.abs().max().item()
         assert (got.float() - want).abs().max().item() / scale < 1e-2
+
+
+def test_cta_pair_gemm_matches_single_cta_bitwise_on_a_large_problem():
+    """Both tile engines accumulate every output element over k in the same order, so they must agree bitwise."""
+    from rl_engine.kernels.ops.base import check_device_errors
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    a, b = _rand((4096 + 128, 2048), 7), _rand((3000, 2048), 8)
+    one = gemm(a, b, pair=False)
+    two = gemm(a, b, pair=True)
+    assert torch.equal(one, two)
+    w = _rand((2048, 1536), 9)
+    assert torch.equal(gemm(a, w, b_mn=True, pair=False), gemm(a, w, b_mn=True, pair=True))
+    check_device_errors(0)
