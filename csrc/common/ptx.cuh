@@ -23,6 +23,7 @@ enum ErrorCode : uint32_t {
   kErrMbarTimeout = 1,
   kErrPeerTimeout = 2,
   kErrBadArgument = 3,
+  kErrBadIndex = 4,
 };
 
 // Layout of the 4-word error record: [0]=code, [1]=kernel id, [2]=block, [3]=site.
@@ -41,6 +42,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+// Checked indexing for debug builds (-DRLK_DEBUG_BOUNDS=1, see setup.py): an index outside [0, limit)
+// records (kErrBadIndex, kernel id, block, site) in the error word and the macro evaluates to false so the
+// caller can skip the access.  Release builds compile the test away.
+#if defined(RLK_DEBUG_BOUNDS)
+#define RLK_INDEX_OK(idx, limit, err, kernel_id, site) \
+  (((idx) >= 0 && (idx) < (limit)) ? true : (::rlk::report_error((err), ::rlk::kErrBadIndex, (kernel_id), (site)), false))
+#else
+#define RLK_INDEX_OK(idx, limit, err, kernel_id, site) (true)
+#endif
 
 constexpr uint64_t kWaitLimitNs = 4ull * 1000ull * 1000ull * 1000ull;  // 4 s
 

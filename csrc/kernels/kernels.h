@@ -303,11 +303,16 @@ namespace rlk {
 // experts <= 512, k <= 32; hidden % 8 == 0 and 16-byte aligned rows for the row kernels.
 void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, float* weight, cudaStream_t stream);
 void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,
-                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream);
+                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream,
+                     long long src_rows = 0, uint32_t* err = nullptr);  // last two: checked indexing in debug builds
 void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, const float* weight, int k,
-                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream);
+                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream,
+                 long long src_rows = 0, uint32_t* err = nullptr);
 void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,
                 int tokens, int hidden, float* out, cudaStream_t stream);
+// ---- tracing (trace.cu): out[slot] = %globaltimer in stream order
+void device_stamp(unsigned long long* out, int slot, cudaStream_t stream);
+
 // ---- tensor-parallel linears fused with their collectives (tp_linear.cu) -------------------------
 struct TpAgGemmArgs {
   const __nv_bfloat16* x_local;  // [rows_local, K] this rank's rows

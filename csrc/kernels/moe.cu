@@ -79,10 +79,12 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int tokens, in
 
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src,
                                        const int* __restrict__ src_row, const float* __restrict__ scale,
-                                       __nv_bfloat16* __restrict__ dst, long long ld_dst, int slots, int h8) {
+                                       __nv_bfloat16* __restrict__ dst, long long ld_dst, int slots, int h8,
+                                       long long src_rows, uint32_t* err) {
   const int slot = blockIdx.x;
   if (slot >= slots) return;
   const int r = src_row[slot];
+  if (r >= 0 && !RLK_INDEX_OK(r, src_rows, err, 500u, 1)) return;
   uint4* out = reinterpret_cast<uint4*>(dst + static_cast<long long>(slot) * ld_dst);
   if (r < 0) {
     for (int i = threadIdx.x; i < h8; i += blockDim.x) out[i] = make_uint4(0, 0, 0, 0);
@@ -106,7 +108,7 @@ __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, lo
 
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, const int* __restrict__ slot,
                                    const float* __restrict__ weight, int k, __nv_bfloat16* __restrict__ out,
-                                   long long ld_out, int tokens, int h8) {
+                                   long long ld_out, int tokens, int h8, long long src_rows, uint32_t* err) {
   const int t = blockIdx.x;
   if (t >= tokens) return;
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * ld_out);
@@ -117,6 +119,7 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ src, long l
     for (int j = 0; j < k; ++j) {  // fixed order
       const int s = slot[static_cast<long long>(t) * k + j];
       if (s < 0) continue;
+      if (src_rows > 0 && !RLK_INDEX_OK(s, src_rows, err, 501u, 1)) continue;
       const float w = weight ? weight[static_cast<long long>(t) * k + j] : 1.f;
       const uint4 q = reinterpret_cast<const uint4*>(src + static_cast<long long>(s) * ld_src)[i];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
@@ -257,15 +260,19 @@ void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, flo
 }
 
 void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,
-                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream) {
+                     __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream, long long src_rows,
+                     uint32_t* err) {
   if (slots <= 0) return;
-  moe_gather_rows_kernel<<<slots, 128, 0, stream>>>(src, ld_src, src_row, scale, dst, ld_dst, slots, hidden / 8);
+  moe_gather_rows_kernel<<<slots, 128, 0, stream>>>(src, ld_src, src_row, scale, dst, ld_dst, slots, hidden / 8, src_rows,
+                                                    err);
 }
 
 void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, const float* weight, int k,
-                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream) {
+                 __nv_bfloat16* out, long long ld_out, int tokens, int hidden, cudaStream_t stream, long long src_rows,
+                 uint32_t* err) {
   if (tokens <= 0) return;
-  moe_combine_kernel<<<tokens, 128, 0, stream>>>(src, ld_src, slot, weight, k, out, ld_out, tokens, hidden / 8);
+  moe_combine_kernel<<<tokens, 128, 0, stream>>>(src, ld_src, slot, weight, k, out, ld_out, tokens, hidden / 8, src_rows,
+                                                 err);
 }
 
 void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,

@@ -11,6 +11,7 @@
 #include <optional>
 #include <vector>
 
+#include "common/trace.h"
 #include "kernels/kernels.h"
 #include "runtime/runtime.h"
 
@@ -324,7 +325,7 @@ Tensor moe_gather_rows(const Tensor& src, const Tensor& src_row, std::optional<T
   }
   if (slots) {
     rlk::moe_gather_rows(reinterpret_cast<const __nv_bfloat16*>(src.data_ptr()), src.stride(0), src_row.data_ptr<int>(), sp,
-                         dst, ld, static_cast<int>(slots), static_cast<int>(h), stream_of(src));
+                         dst, ld, static_cast<int>(slots), static_cast<int>(h), stream_of(src), src.size(0), err_ptr(src));
     after_launch();
   }
   return out;
@@ -358,7 +359,8 @@ Tensor moe_combine(std::optional<Tensor> src, int64_t src_ptr, int64_t src_ld, i
   if (slot.size(0)) {
     rlk::moe_combine(sp, ld, slot.data_ptr<int>(), wp, static_cast<int>(slot.size(1)),
                      reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0), static_cast<int>(slot.size(0)),
-                     static_cast<int>(hidden), stream_of(slot));
+                     static_cast<int>(hidden), stream_of(slot), (src.has_value() && src->defined()) ? src->size(0) : 0,
+                     err_ptr(slot));
     after_launch();
   }
   return out;
@@ -1037,51 +1039,67 @@ std::vector<int64_t> error_state(int64_t device) {
   auto a = w.accessor<int, 1>();
   return {a[0], a[1], a[2], a[3]};
 }
+void device_stamp(Tensor stamps, int64_t slot) {
+  TORCH_CHECK(stamps.is_cuda() && stamps.scalar_type() == torch::kInt64 && stamps.is_contiguous() && slot >= 0 &&
+                  slot < stamps.numel(),
+              "rl_engine.device_stamp: stamps must be a contiguous int64 CUDA tensor and slot in range");
+  const c10::cuda::CUDAGuard guard(stamps.device());
+  rlk::device_stamp(reinterpret_cast<unsigned long long*>(stamps.data_ptr<int64_t>()), static_cast<int>(slot), stream_of(stamps));
+  after_launch();
+}
+
 void reset_error(int64_t device) { error_word(static_cast<int>(device)).zero_(); }
 long long launch_count() { return g_launches.load(); }
+}  // namespace
+namespace rlk {
+void count_launch(int n) { g_launches += n; }
+}  // namespace rlk
+namespace {
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "rl_engine native sm_100a kernels";
-  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+  m.def("device_stamp", &device_stamp);
+  m.def("trace_enabled", [] { return rlk::trace_enabled(); });
+  m.def("gemm", rlk::traced("rlk::gemm", &gemm), py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0,
         py::arg("pair") = -1);
-  m.def("grouped_gemm", &grouped_gemm);
-  m.def("tp_ag_gemm", &tp_ag_gemm);
-  m.def("tp_gemm_rs", &tp_gemm_rs);
-  m.def("moe_topk", &moe_topk);
-  m.def("moe_gather_rows", &moe_gather_rows, py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
+  m.def("grouped_gemm", rlk::traced("rlk::grouped_gemm", &grouped_gemm));
+  m.def("tp_ag_gemm", rlk::traced("rlk::tp_ag_gemm", &tp_ag_gemm));
+  m.def("tp_gemm_rs", rlk::traced("rlk::tp_gemm_rs", &tp_gemm_rs));
+  m.def("moe_topk", rlk::traced("rlk::moe_topk", &moe_topk));
+  m.def("moe_gather_rows", rlk::traced("rlk::moe_gather_rows", &moe_gather_rows), py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
         py::arg("dst_ptr") = 0, py::arg("dst_ld") = 0);
-  m.def("moe_combine", &moe_combine, py::arg("src"), py::arg("src_ptr"), py::arg("src_ld"), py::arg("hidden"), py::arg("slot"),
+  m.def("moe_combine", rlk::traced("rlk::moe_combine", &moe_combine), py::arg("src"), py::arg("src_ptr"), py::arg("src_ld"), py::arg("hidden"), py::arg("slot"),
         py::arg("weight") = py::none());
-  m.def("moe_rowdot", &moe_rowdot);
-  m.def("linear_logp_workspace_shape", &linear_logp_workspace_shape);
-  m.def("linear_logp_fwd", &linear_logp_fwd);
-  m.def("linear_logp_dz", &linear_logp_dz);
-  m.def("logp_rows", &logp_rows);
-  m.def("ratio_kl_fwd", &ratio_kl_fwd);
-  m.def("ratio_kl_bwd", &ratio_kl_bwd);
-  m.def("group_advantages", &group_advantages);
-  m.def("surrogate_fwd", &surrogate_fwd);
-  m.def("surrogate_bwd", &surrogate_bwd);
-  m.def("dpo_fwd", &dpo_fwd);
-  m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
-  m.def("swiglu_packed_fwd", &swiglu_packed_fwd);
-  m.def("swiglu_packed_bwd", &swiglu_packed_bwd);
-  m.def("rope", &rope, py::arg("x"), py::arg("positions"), py::arg("cos"), py::arg("sin"), py::arg("inverse") = false,
+  m.def("moe_rowdot", rlk::traced("rlk::moe_rowdot", &moe_rowdot));
+  m.def("linear_logp_workspace_shape", rlk::traced("rlk::linear_logp_workspace_shape", &linear_logp_workspace_shape));
+  m.def("linear_logp_fwd", rlk::traced("rlk::linear_logp_fwd", &linear_logp_fwd));
+  m.def("linear_logp_dz", rlk::traced("rlk::linear_logp_dz", &linear_logp_dz));
+  m.def("logp_rows", rlk::traced("rlk::logp_rows", &logp_rows));
+  m.def("ratio_kl_fwd", rlk::traced("rlk::ratio_kl_fwd", &ratio_kl_fwd));
+  m.def("ratio_kl_bwd", rlk::traced("rlk::ratio_kl_bwd", &ratio_kl_bwd));
+  m.def("group_advantages", rlk::traced("rlk::group_advantages", &group_advantages));
+  m.def("surrogate_fwd", rlk::traced("rlk::surrogate_fwd", &surrogate_fwd));
+  m.def("surrogate_bwd", rlk::traced("rlk::surrogate_bwd", &surrogate_bwd));
+  m.def("dpo_fwd", rlk::traced("rlk::dpo_fwd", &dpo_fwd));
+  m.def("rmsnorm_fwd", rlk::traced("rlk::rmsnorm_fwd", &rmsnorm_fwd));
+  m.def("rmsnorm_bwd", rlk::traced("rlk::rmsnorm_bwd", &rmsnorm_bwd));
+  m.def("swiglu_fwd", rlk::traced("rlk::swiglu_fwd", &swiglu_fwd));
+  m.def("swiglu_bwd", rlk::traced("rlk::swiglu_bwd", &swiglu_bwd));
+  m.def("swiglu_packed_fwd", rlk::traced("rlk::swiglu_packed_fwd", &swiglu_packed_fwd));
+  m.def("swiglu_packed_bwd", rlk::traced("rlk::swiglu_packed_bwd", &swiglu_packed_bwd));
+  m.def("rope", rlk::traced("rlk::rope", &rope), py::arg("x"), py::arg("positions"), py::arg("cos"), py::arg("sin"), py::arg("inverse") = false,
         py::arg("out") = py::none());
-  m.def("embedding_fwd", &embedding_fwd);
-  m.def("embedding_bwd", &embedding_bwd);
-  m.def("adamw", &adamw);
-  m.def("sample", &sample);
-  m.def("attention_fwd", &attention_fwd);
-  m.def("attention_bwd", &attention_bwd);
-  m.def("error_state", &error_state);
-  m.def("reset_error", &reset_error);
-  m.def("launch_count", &launch_count);
+  m.def("embedding_fwd", rlk::traced("rlk::embedding_fwd", &embedding_fwd));
+  m.def("embedding_bwd", rlk::traced("rlk::embedding_bwd", &embedding_bwd));
+  m.def("adamw", rlk::traced("rlk::adamw", &adamw));
+  m.def("sample", rlk::traced("rlk::sample", &sample));
+  m.def("attention_fwd", rlk::traced("rlk::attention_fwd", &attention_fwd));
+  m.def("attention_bwd", rlk::traced("rlk::attention_bwd", &attention_bwd));
+  m.def("error_state", rlk::traced("rlk::error_state", &error_state));
+  m.def("reset_error", rlk::traced("rlk::reset_error", &reset_error));
+  m.def("launch_count", rlk::traced("rlk::launch_count", &launch_count));
   rlk::bind_runtime(m);
 }

@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "../kernels/kernels.h"
+#include "../common/trace.h"
 #include "runtime.h"
 
 namespace rlk {
@@ -137,13 +138,23 @@ Tensor py_moe_combine_peer(std::vector<uint64_t> src, int64_t ld_src, int64_t hi
 
 }  // namespace
 
+// Every binding below launches exactly one kernel: count it and (with RLK_NVTX=1) put it in a range.
+template <typename R, typename... Args>
+auto counted(const char* name, R (*fn)(Args...)) {
+  return [name, fn](Args... args) -> R {
+    TraceRange range(name);
+    count_launch(1);
+    return fn(std::forward<Args>(args)...);
+  };
+}
+
 void bind_comm(pybind11::module_& m) {
-  m.def("moe_scatter_rows_peer", &py_moe_scatter_rows_peer);
-  m.def("moe_combine_peer", &py_moe_combine_peer);
-  m.def("peer_barrier", &py_peer_barrier);
-  m.def("zero1_fused_step", &py_zero1_fused_step);
-  m.def("peer_sum", &py_peer_sum);
-  m.def("cast_broadcast", &py_cast_broadcast);
+  m.def("moe_scatter_rows_peer", counted("rlk::moe_scatter_rows_peer", &py_moe_scatter_rows_peer));
+  m.def("moe_combine_peer", counted("rlk::moe_combine_peer", &py_moe_combine_peer));
+  m.def("peer_barrier", counted("rlk::peer_barrier", &py_peer_barrier));
+  m.def("zero1_fused_step", counted("rlk::zero1_fused_step", &py_zero1_fused_step));
+  m.def("peer_sum", counted("rlk::peer_sum", &py_peer_sum));
+  m.def("cast_broadcast", counted("rlk::cast_broadcast", &py_cast_broadcast));
 }
 
 }  // namespace rlk

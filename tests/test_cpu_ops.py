@@ -290,3 +290,60 @@ def test_context_parallel_zigzag_shards_round_trip_and_balance():
     assert max(work) == min(work)  # zig-zag gives every rank the same number of visible keys
     with pytest.raises(ValueError):
         shard_sequence(x[:-1], 0, world)
+
+
+def test_phase_timer_and_trace_range_on_cpu():
+    from rl_engine.utils.tracing import PhaseTimer, trace_range, traced
+
+    timer = PhaseTimer(device="cpu")
+    with trace_range("outer"):
+        for _ in range(3):
+            with timer.phase("matmul"):
+                torch.randn(64, 64) @ torch.randn(64, 64)
+        with timer.phase("other"):
+            pass
+    s = timer.summary()
+    assert list(s) == ["matmul", "other"] and s["matmul"]["calls"] == 3 and s["matmul"]["total_ms"] > 0
+    assert list(timer.max_over_ranks()) == ["matmul", "other"]
+
+    @traced("labelled")
+    def f(x):
+        return x + 1
+
+    assert f(1) == 2
+    timer.reset()
+    assert not timer.summary()
+
+
+def test_alias_package_exposes_the_same_modules():
+    import rl_kernel_b200
+
+    assert rl_kernel_b200.ops.registry.kernel_registry is not None
+    assert rl_kernel_b200.parallel.__name__ == "rl_engine.parallel"
+    from rl_kernel_b200 import models, utils  # noqa: F401
+
+    assert sorted(dir(rl_kernel_b200))[:2] == ["executors", "models"]
+    with pytest.raises(AttributeError):
+        rl_kernel_b200.nothing_here
+
+
+def test_debug_bounds_build_compiles(tmp_path):
+    """``RLK_DEBUG_BOUNDS=1`` turns ``RLK_INDEX_OK`` into a checked access that reports to the error word; the
+    kernels that take user indices must still compile for sm_100a with it switched on."""
+    import os
+    import shutil
+    import subprocess
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "csrc", "kernels", "moe.cu")
+    text = open(os.path.join(root, "csrc", "common", "ptx.cuh")).read()
+    assert "RLK_DEBUG_BOUNDS" in text and "kErrBadIndex" in text
+    out = subprocess.run(
+        [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O1", "-DRLK_DEBUG_BOUNDS=1", "-c", src,
+         "-o", str(tmp_path / "moe_debug.o")],
+        capture_output=True, text=True, timeout=600,
+    )
+    assert out.returncode == 0, out.stderr[-2000:]

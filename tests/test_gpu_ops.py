@@ -378,3 +378,46 @@ def test_swiglu_packed_and_rmsnorm_wide_rows():
     yr.backward(d.float())
     assert (xa.grad.float() - xb.grad).abs().max().item() < 0.1
     assert (wa.grad.float() - wb.grad).abs().max().item() / wb.grad.abs().max().item() < 2e-2
+
+
+def test_device_stamps_and_phase_timer():
+    from rl_engine.utils.tracing import DeviceStamps, PhaseTimer
+
+    stamps = DeviceStamps(4)
+    timer = PhaseTimer()
+    a = torch.randn(4096, 4096, device="cuda")
+    stamps.stamp(0)
+    with timer.phase("matmul"):
+        for _ in range(10):
+            a @ a
+    stamps.stamp(1)
+    ms = stamps.elapsed_ms(0, 1)
+    s = timer.summary()
+    assert ms > 0 and s["matmul"]["total_ms"] > 0
+    assert abs(ms - s["matmul"]["total_ms"]) < 0.5 * ms + 1.0  # two clocks, same interval
+
+
+def test_outputs_do_not_overrun_canary_padded_buffers():
+    """Kernels that write into caller-provided outputs must stay inside them: the outputs are carved out of
+    a larger buffer filled with a sentinel, which must be intact afterwards."""
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+    from rl_engine.kernels.ops.sm100.logp import FusedLogpSM100Op
+
+    pad = 4096
+    m, n, k = 200, 328, 136
+    a = (torch.randn(m, k, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda") * 0.5).to(torch.bfloat16)
+    for pair in (False, True):
+        buf = torch.full((pad + m * n + pad,), 12345.0, device="cuda")
+        out = buf[pad:pad + m * n].view(m, n)
+        gemm(a, b, out=out, out_dtype=torch.float32, pair=pair)
+        assert bool((buf[:pad] == 12345.0).all()) and bool((buf[-pad:] == 12345.0).all())
+        assert torch.allclose(out, a.float() @ b.float().t(), atol=2e-2, rtol=2e-3)
+    rows, v = 333, 1000
+    logits = torch.randn(rows, v, device="cuda").to(torch.bfloat16)
+    ids = torch.randint(0, v, (rows,), device="cuda")
+    buf = torch.full((pad + rows + pad,), 777.0, device="cuda")
+    FusedLogpSM100Op().out(logits, ids, buf[pad:pad + rows])
+    assert bool((buf[:pad] == 777.0).all()) and bool((buf[-pad:] == 777.0).all())
+    want = torch.log_softmax(logits.float(), -1).gather(1, ids[:, None]).squeeze(1)
+    assert torch.allclose(buf[pad:pad + rows], want, atol=1e-3, rtol=1e-3)
