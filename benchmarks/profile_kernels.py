@@ -97,6 +97,20 @@ def case_gemm_dgrad_pair():
             "note": f"B as [K, N]; single-CTA kernel on the same problem: {ms_single:.4f} ms"}
 
 
+def case_gemm_shape():
+    """Any GEMM: PROFILE_GEMM="M,N,K,layout,pair" with layout in nt|nn|tn|tt (A then B; t = MN-major) and pair 0|1."""
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    spec = os.environ.get("PROFILE_GEMM", "8192,4096,28672,nn,1").split(",")
+    m, n, k = int(spec[0]), int(spec[1]), int(spec[2])
+    a_mn, b_mn, pair = spec[3][0] == "t", spec[3][1] == "n", spec[4] == "1"
+    a = rand((k, m) if a_mn else (m, k))
+    b = rand((k, n) if b_mn else (n, k), 0.02, 1)
+    ms = timed(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=pair))
+    return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [m, n, k],
+            "note": f"layout {spec[3]} (A {'MN' if a_mn else 'K'}-major, B {'MN' if b_mn else 'K'}-major), pair={int(pair)}"}
+
+
 def case_linear_logp():
     from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
 

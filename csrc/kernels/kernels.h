@@ -212,6 +212,10 @@ void sample_topk_topp(const void* logits, long long ld, int dtype, int rows, int
                       float temperature, unsigned long long seed, unsigned long long offset, long long* out_ids,
                       float* out_logprob, cudaStream_t stream);
 int sample_topk_limit();
+// Full-vocabulary nucleus (top-p only) / plain temperature sampling (top_p = 1).
+void sample_nucleus(const void* logits, long long ld, int dtype, int rows, int V, float top_p, float temperature,
+                    unsigned long long seed, unsigned long long offset, long long* out_ids, float* out_logprob,
+                    cudaStream_t stream);
 
 }  // namespace rlk
 

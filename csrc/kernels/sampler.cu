@@ -200,7 +200,183 @@ sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int t
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Full-vocabulary nucleus sampling (no top-k): temperature softmax over the whole row, keep the
+// smallest set of highest-probability tokens whose mass reaches top_p (all tokens tied with the
+// cut value are kept), draw by inverse CDF in INDEX order inside the kept set.
+//
+// The cut is found by a 4-pass radix search over the order-preserving keys, with the bins holding
+// probability MASS instead of counts.  Masses are 40-bit fixed point in 64-bit integers, so the
+// shared-memory atomics that build the histograms are order-independent and the result is
+// deterministic: a pure function of (row, top_p, T, seed, offset, row index).
+// ---------------------------------------------------------------------------------------------
+constexpr int kNucleusThreads = 1024;
+
+__device__ __forceinline__ unsigned long long fixed_mass(float x, float row_max, float inv_temp) {
+  // exp((x - max) / T) in [0, 1], scaled by 2^40 and rounded down; every token gets at least 0
+  const float e = __expf((x - row_max) * inv_temp);
+  return static_cast<unsigned long long>(e * 1099511627776.0f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNucleusThreads)
+sample_nucleus_kernel(const T* __restrict__ logits, long long ld, int V, float top_p, float inv_temp,
+                      unsigned long long seed, unsigned long long offset, long long* __restrict__ out_ids,
+                      float* __restrict__ out_logprob) {
+  __shared__ unsigned long long hist[256];
+  __shared__ unsigned long long warp_part[kNucleusThreads / 32];
+  __shared__ float warp_max[kNucleusThreads / 32];
+  __shared__ unsigned long long s_total, s_above, s_target, s_base;
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_pick;
+  __shared__ float s_max;
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* z = logits + static_cast<long long>(row) * ld;
+
+  // ---- row maximum
+  float m = -INFINITY;
+  for (int i = tid; i < V; i += kNucleusThreads) m = fmaxf(m, ldv(z, i));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) warp_max[warp] = m;
+  __syncthreads();
+  if (tid == 0) {
+    float r = warp_max[0];
+    for (int w = 1; w < kNucleusThreads / 32; ++w) r = fmaxf(r, warp_max[w]);
+    s_max = r;
+    s_prefix = 0u;
+    s_above = 0ull;
+  }
+  __syncthreads();
+  const float row_max = s_max;
+
+  // ---- radix search for the cut key: after pass r the top 8*(r+1) bits of the cut are known
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int b = tid; b < 256; b += kNucleusThreads) hist[b] = 0ull;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = tid; i < V; i += kNucleusThreads) {
+      const float x = ldv(z, i);
+      const uint32_t key = f2key(x);
+      if ((key & mask) == (prefix & mask)) atomicAdd(&hist[(key >> shift) & 0xffu], fixed_mass(x, row_max, inv_temp));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      if (pass == 0) {
+        unsigned long long total = 0ull;
+        for (int b = 0; b < 256; ++b) total += hist[b];
+        s_total = total;
+        // mass that the kept set must reach (at least one unit so that the best token is always kept)
+        const double want = static_cast<double>(top_p) * static_cast<double>(total);
+        s_target = want < 1.0 ? 1ull : static_cast<unsigned long long>(want);
+      }
+      unsigned long long above = s_above;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (above + hist[b] >= s_target) break;
+        above += hist[b];
+      }
+      s_above = above;  // mass of the tokens strictly above the chosen bin
+      s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+    }
+    __syncthreads();
+  }
+  const uint32_t cut = s_prefix;  // keep every token with key >= cut
+
+  // ---- mass of the kept set, then the draw
+  unsigned long long part = 0ull;
+  for (int i = tid; i < V; i += kNucleusThreads) {
+    const float x = ldv(z, i);
+    if (f2key(x) >= cut) part += fixed_mass(x, row_max, inv_temp);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) warp_part[warp] = part;
+  __syncthreads();
+  if (tid == 0) {
+    unsigned long long kept = 0ull;
+    for (int w = 0; w < kNucleusThreads / 32; ++w) kept += warp_part[w];
+    const uint4 rnd = philox4x32_10(
+        make_uint4(static_cast<uint32_t>(offset), static_cast<uint32_t>(offset >> 32), static_cast<uint32_t>(row), 0u),
+        make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32)));
+    const double u = (static_cast<double>(rnd.x >> 8) + 0.5) * (1.0 / 16777216.0);
+    unsigned long long t = static_cast<unsigned long long>(u * static_cast<double>(kept));
+    if (t >= kept) t = kept ? kept - 1 : 0ull;
+    s_total = kept;
+    s_target = t;  // pick the first kept token (index order) whose inclusive cumulative mass exceeds t
+    s_base = 0ull;
+    s_pick = -1;
+  }
+  __syncthreads();
+
+  // ---- index-order scan in tiles of kNucleusThreads tokens
+  for (int base = 0; base < V && s_pick < 0; base += kNucleusThreads) {
+    const int i = base + tid;
+    unsigned long long mine = 0ull;
+    float x = 0.f;
+    if (i < V) {
+      x = ldv(z, i);
+      if (f2key(x) >= cut) mine = fixed_mass(x, row_max, inv_temp);
+    }
+    unsigned long long incl = mine;  // inclusive scan inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_part[warp] = incl;
+    __syncthreads();
+    unsigned long long before = s_base;
+    for (int w = 0; w < warp; ++w) before += warp_part[w];
+    const unsigned long long lo = before + incl - mine, hi = before + incl;
+    if (mine != 0ull && lo <= s_target && s_target < hi) {
+      s_pick = i;  // exactly one thread satisfies this
+      out_ids[row] = i;
+      if (out_logprob) out_logprob[row] = logf(static_cast<float>(static_cast<double>(mine) / static_cast<double>(s_total)));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned long long tile = 0ull;
+      for (int w = 0; w < kNucleusThreads / 32; ++w) tile += warp_part[w];
+      s_base += tile;
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && s_pick < 0) {  // all masses rounded to zero except none kept: fall back to the arg-max
+    int best = 0;
+    float bv = ldv(z, 0);
+    for (int i = 1; i < V; ++i) {
+      const float x = ldv(z, i);
+      if (x > bv) {
+        bv = x;
+        best = i;
+      }
+    }
+    out_ids[row] = best;
+    if (out_logprob) out_logprob[row] = 0.f;
+  }
+}
+
 }  // namespace
+
+void sample_nucleus(const void* logits, long long ld, int dtype, int rows, int V, float top_p, float temperature,
+                    unsigned long long seed, unsigned long long offset, long long* out_ids, float* out_logprob,
+                    cudaStream_t stream) {
+  if (rows <= 0) return;
+  const float inv_temp = 1.f / temperature;
+  if (dtype == 0)
+    sample_nucleus_kernel<float><<<rows, kNucleusThreads, 0, stream>>>(static_cast<const float*>(logits), ld, V, top_p,
+                                                                       inv_temp, seed, offset, out_ids, out_logprob);
+  else if (dtype == 1)
+    sample_nucleus_kernel<__nv_bfloat16><<<rows, kNucleusThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(logits), ld, V, top_p, inv_temp, seed, offset, out_ids, out_logprob);
+  else
+    sample_nucleus_kernel<__half><<<rows, kNucleusThreads, 0, stream>>>(static_cast<const __half*>(logits), ld, V, top_p,
+                                                                        inv_temp, seed, offset, out_ids, out_logprob);
+}
 
 void sample_topk_topp(const void* logits, long long ld, int dtype, int rows, int V, int top_k, float top_p,
                       float temperature, unsigned long long seed, unsigned long long offset, long long* out_ids,

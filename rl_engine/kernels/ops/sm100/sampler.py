@@ -56,6 +56,35 @@ def sample_reference(logits: torch.Tensor, top_k: int, top_p: float, temperature
     return torch.tensor(out, dtype=torch.long)
 
 
+def nucleus_reference(logits: torch.Tensor, top_p: float, temperature: float, seed: int, offset: int):
+    """CPU oracle of the full-vocabulary nucleus kernel: 40-bit fixed-point masses, cut = smallest value v such
+    that the mass of tokens >= v reaches ``top_p`` of the total (ties kept), inverse CDF in index order."""
+    import math
+
+    out = []
+    z = logits.float().cpu()
+    for row in range(z.shape[0]):
+        m = float(z[row].max())
+        # float32 arithmetic as in the kernel; __expf differs from exp by a few ulp, so tests compare the kept
+        # set and the drawn token's cumulative interval with a tolerance instead of bit-exact masses
+        e = torch.exp((z[row] - m) / temperature).double()
+        mass = torch.floor(e * float(1 << 40)).to(torch.int64)
+        total = int(mass.sum())
+        want = max(1, int(top_p * total))
+        order = torch.argsort(z[row], descending=True, stable=True)
+        cum = torch.cumsum(mass[order], 0)
+        first = int(torch.searchsorted(cum, torch.tensor(want), right=False))
+        first = min(first, z.shape[1] - 1)
+        cut = float(z[row, order[first]])
+        keep = z[row] >= cut
+        kept_mass = torch.where(keep, mass, torch.zeros_like(mass))
+        kept = int(kept_mass.sum())
+        t = min(int(philox_uniform(seed, offset, row) * kept), max(kept - 1, 0))
+        c = torch.cumsum(kept_mass, 0)
+        out.append(int(torch.searchsorted(c, torch.tensor(t), right=True)))
+    return torch.tensor(out, dtype=torch.long)
+
+
 def sample_topk_topp(
     logits: torch.Tensor, *, top_k: Optional[int], top_p: Optional[float], temperature: float = 1.0,
     seed: int = 0, offset: int = 0, return_logprob: bool = False,
@@ -64,9 +93,11 @@ def sample_topk_topp(
     rows = logits.reshape(-1, v)
     if rows.stride(1) != 1:
         rows = rows.contiguous()
-    k = min(v, TOPK_LIMIT) if top_k is None else int(top_k)
+    # top_k None (or >= vocab): the full-vocabulary nucleus kernel (k = 0 in the native call); its kept set is the
+    # smallest set of most probable tokens reaching top_p, drawn in index order -- see ``nucleus_reference``.
+    k = 0 if (top_k is None or int(top_k) >= v) else int(top_k)
     if k > TOPK_LIMIT:
-        raise ValueError(f"top_k must be <= {TOPK_LIMIT} for the fused sampler, got {k}")
+        raise ValueError(f"top_k must be <= {TOPK_LIMIT} (or None / >= vocab) for the fused sampler, got {k}")
     p = 1.0 if top_p is None else float(top_p)
     ids, lp = require_ext().sample(rows, k, p, float(temperature), int(seed), int(offset), bool(return_logprob))
     return ids.reshape(logits.shape[:-1]), (lp.reshape(logits.shape[:-1]) if return_logprob else None)

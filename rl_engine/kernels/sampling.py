@@ -48,7 +48,7 @@ class SamplerBackend(nn.Module):
         if self.backend == constants.BackendLib.SM100.value and logits.is_cuda:
             from rl_engine.kernels.ops.sm100 import sampler as fused
 
-            if top_k is None or top_k <= fused.TOPK_LIMIT:
+            if top_k is None or top_k <= fused.TOPK_LIMIT or top_k >= logits.shape[-1]:
                 offset = self._offset
                 self._offset += 1
                 ids, _ = fused.sample_topk_topp(

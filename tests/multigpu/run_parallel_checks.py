@@ -164,6 +164,43 @@ def main() -> None:
     check_device_errors(local)
     print(f"[{rank}] OK expert-parallel MoE", flush=True)
 
+    # ---- a whole Llama layer under tensor + sequence parallelism vs the single-GPU layer ---------------
+    from rl_engine.kernels.ops.sm100.attention import make_layout
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.llama import LlamaModel
+    from rl_engine.parallel.tp_transformer import TensorParallelLlamaLayer, shard_layer_weights
+
+    cfg = ModelConfig("tp-check", 1024, 512, 1, 4 * world, 2 * world, 128, 512 * world)
+    full = LlamaModel(cfg, dtype=torch.bfloat16, device=dev, seed=9, activation_checkpointing=False)
+    TT = 256 * world
+    gl_ = torch.Generator(device=dev).manual_seed(901)
+    xin = torch.randn(TT, cfg.hidden_size, device=dev, generator=gl_).to(torch.bfloat16)
+    dout_l = torch.randn(TT, cfg.hidden_size, device=dev, generator=gl_).to(torch.bfloat16)
+    pos = torch.arange(TT, device=dev)
+    lay = make_layout([(0, TT, 0, 0, 0, TT)], True, dev)
+    xf = xin.clone().requires_grad_(True)
+    yf = full._layer(xf, 0, pos, lay)
+    yf.backward(dout_l)
+    shard = {k: v.requires_grad_(True) for k, v in shard_layer_weights(full, 0, rank, world).items()}
+    layer = TensorParallelLlamaLayer(cfg, shard, tp, full.rope_cos, full.rope_sin)
+    tok = slice(rank * 256, (rank + 1) * 256)
+    xl_ = xin[tok].clone().requires_grad_(True)
+    yl = layer(xl_, pos, lay)
+    yl.backward(dout_l[tok].contiguous())
+    close(yl, yf.detach()[tok], 3e-2, "tp layer output")
+    close(xl_.grad, xf.grad[tok], 3e-2, "tp layer dx")
+    hq_l, d_ = cfg.num_heads // world, cfg.head_dim
+    close(shard["wo"].grad, full.params[full._index["l0.wo"]].grad[:, rank * hq_l * d_:(rank + 1) * hq_l * d_], 3e-2, "tp layer dWo")
+    f_l = cfg.ffn_size // world
+    close(shard["w_down"].grad, full.params[full._index["l0.w_down"]].grad[:, rank * f_l:(rank + 1) * f_l], 3e-2, "tp layer dWdown")
+    gq = full.params[full._index["l0.wqkv"]].grad[: cfg.q_dim].view(cfg.num_heads, d_, -1)[rank * hq_l:(rank + 1) * hq_l]
+    close(shard["wqkv"].grad[: hq_l * d_], gq.reshape(hq_l * d_, -1), 3e-2, "tp layer dWq")
+    norm_g = shard["mlp_norm"].grad.float().clone()
+    dist.all_reduce(norm_g)
+    close(norm_g, full.params[full._index["l0.mlp_norm"]].grad, 3e-2, "tp layer d(mlp_norm), summed over ranks")
+    tp.check()
+    print(f"[{rank}] OK tensor-parallel Llama layer", flush=True)
+
     # ---- context-parallel causal attention (zig-zag shards, peer-store K/V gather, peer_sum dK/dV) ----
     from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
     from rl_engine.parallel.context_parallel import ContextParallelAttention, shard_sequence

@@ -73,6 +73,35 @@ def test_fused_tp_linears_single_rank_match_plain_gemm():
     check_device_errors(0)
 
 
+def test_tensor_parallel_layer_single_rank_matches_model_layer():
+    from rl_engine.kernels.ops.sm100.attention import make_layout
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.llama import LlamaModel
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+    from rl_engine.parallel.tp_transformer import TensorParallelLlamaLayer, shard_layer_weights
+
+    cfg = ModelConfig("tp-check", 1024, 512, 1, 4, 2, 128, 768)
+    model = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=4, activation_checkpointing=False)
+    t = 384
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(t, 512, device="cuda", generator=g).to(torch.bfloat16)
+    dout = torch.randn(t, 512, device="cuda", generator=g).to(torch.bfloat16)
+    pos = torch.arange(t, device="cuda")
+    layout = make_layout([(0, 128, 0, 0, 0, 128), (128, 256, 0, 0, 128, 256)], True, "cuda")
+    xf = x.clone().requires_grad_(True)
+    yf = model._layer(xf, 0, pos, layout)
+    yf.backward(dout)
+    w = {k: v.requires_grad_(True) for k, v in shard_layer_weights(model, 0, 0, 1).items()}
+    layer = TensorParallelLlamaLayer(cfg, w, TensorParallelLinears(), model.rope_cos, model.rope_sin)
+    xl = x.clone().requires_grad_(True)
+    yl = layer(xl, pos, layout)
+    yl.backward(dout)
+    assert torch.allclose(yl.float(), yf.float(), atol=3e-2, rtol=3e-2)
+    assert (xl.grad.float() - xf.grad.float()).abs().max() / xf.grad.float().abs().max() < 3e-2
+    gw = model.params[model._index["l0.w_down"]].grad
+    assert (w["w_down"].grad.float() - gw.float()).abs().max() / gw.float().abs().max() < 3e-2
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
 def test_parallel_checks_two_ranks():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")

@@ -421,3 +421,63 @@ def test_outputs_do_not_overrun_canary_padded_buffers():
     assert bool((buf[:pad] == 777.0).all()) and bool((buf[-pad:] == 777.0).all())
     want = torch.log_softmax(logits.float(), -1).gather(1, ids[:, None]).squeeze(1)
     assert torch.allclose(buf[pad:pad + rows], want, atol=1e-3, rtol=1e-3)
+
+
+def test_full_vocab_nucleus_sampler_matches_oracle_and_distribution():
+    """top_k=None goes to the full-vocabulary nucleus kernel: cut by probability mass, draw in index order."""
+    from rl_engine.kernels.ops.sm100.sampler import nucleus_reference, sample_topk_topp
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows, v = 96, 5000
+    logits = torch.randn(rows, v, device="cuda", generator=g) * 2.5
+    for top_p, temp in ((0.9, 0.8), (0.5, 1.0), (1.0, 1.3)):
+        ids, lp = sample_topk_topp(logits, top_k=None, top_p=top_p, temperature=temp, seed=11, offset=5, return_logprob=True)
+        again, _ = sample_topk_topp(logits, top_k=None, top_p=top_p, temperature=temp, seed=11, offset=5)
+        assert torch.equal(ids, again)
+        want = nucleus_reference(logits, top_p, temp, 11, 5)
+        # __expf vs exp: a draw that lands within a few ulp of a boundary may move to the neighbouring token
+        assert (ids.cpu() == want).float().mean() > 0.97
+        # every draw lies inside the nucleus: its probability is at least the smallest kept probability
+        probs = torch.softmax(logits / temp, -1)
+        sorted_p, _ = probs.sort(dim=-1, descending=True)
+        cum = sorted_p.cumsum(-1)
+        n_keep = (cum < top_p - 1e-6).sum(-1).clamp(max=v - 1)
+        floor = sorted_p.gather(1, n_keep[:, None]).squeeze(1)
+        picked = probs.gather(1, ids[:, None]).squeeze(1)
+        assert bool((picked >= floor * (1 - 1e-3)).all())
+        kept_mass = torch.where(probs >= floor[:, None] * (1 - 1e-6), probs, torch.zeros_like(probs)).sum(-1)
+        assert torch.allclose(lp.exp(), picked / kept_mass, rtol=2e-2, atol=1e-6)
+    # a tiny nucleus is the arg-max
+    ids, _ = sample_topk_topp(logits, top_k=None, top_p=1e-6, temperature=1.0, seed=1, offset=0)
+    assert torch.equal(ids, logits.argmax(-1))
+    # distribution: the same row 4096 times (different row index -> different uniform)
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, 1.5, -3.0, 0.2], device="cuda")
+    many = row.expand(4096, 8).contiguous()
+    ids, _ = sample_topk_topp(many, top_k=None, top_p=0.8, temperature=1.0, seed=5, offset=0)
+    p = torch.softmax(row, -1)
+    keep = torch.zeros(8, dtype=torch.bool, device="cuda")
+    order = p.argsort(descending=True)
+    mass = 0.0
+    for i in order.tolist():
+        keep[i] = True
+        mass += float(p[i])
+        if mass >= 0.8:
+            break
+    target = torch.where(keep, p, torch.zeros_like(p))
+    target = target / target.sum()
+    freq = torch.bincount(ids, minlength=8).float() / 4096
+    assert bool((freq[~keep] == 0).all()) and (freq - target).abs().max() < 0.03
+
+
+def test_sampler_backend_uses_the_fused_kernels_without_top_k():
+    from rl_engine.kernels.ops.base import require_ext
+    from rl_engine.kernels.sampling import SamplerBackend
+
+    ext = require_ext()
+    sampler = SamplerBackend(seed=3)
+    logits = torch.randn(32, 3000, device="cuda")
+    before = ext.launch_count()
+    a = sampler.sample(logits, top_k=None, top_p=0.9, temperature=0.7)
+    b = sampler.sample(logits, top_k=None, top_p=None, temperature=1.0)
+    assert ext.launch_count() - before == 2, "both calls must run one native kernel each"
+    assert a.shape == (32,) and b.shape == (32,) and int(a.min()) >= 0 and int(b.max()) < 3000
