@@ -12,9 +12,13 @@
 //
 // One CTA = one 128-query tile of one head.  Warp 0 loads Q once and K/V tiles through a 2-stage TMA
 // ring; warp 1 issues S = Q K^T and O_j = P_j V_j on tcgen05 with S, O_j double-buffered in TMEM
-// (4 x 128 columns); warps 2..5 own one query row per thread: tcgen05.ld the S row, online softmax
-// in registers, write P as bf16 into a 128B-swizzled smem tile (the A operand of the second MMA), and
-// accumulate O in registers as O = O * alpha + O_j.
+// (4 x 128 columns).  Two groups of four warps own one query row per thread each:
+//   softmax warps 2..5   : pull the whole S row into registers with four tcgen05.ld in flight (one wait), free
+//                          the S buffer at once, online softmax, P as bf16 into a 128B-swizzled smem tile (the
+//                          A operand of the second MMA), the row's rescale factor alpha into shared memory;
+//   output warps 6..9    : O = O * alpha + O_j in registers, final normalisation, output and log-sum-exp.
+// Splitting the two jobs keeps each thread under the register limit with all its TMEM loads in flight and
+// puts two warps on every scheduler, so TMEM-load latency of one group hides behind the other's arithmetic.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "kernels.h"
@@ -26,7 +30,7 @@ namespace {
 constexpr int kD = 128;        // head dim
 constexpr int kTileQ = 128;
 constexpr int kTileK = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int kTileBytes = kTileQ * kD * 2;  // 32 KB: two 128B-swizzle atoms of [128 x 64]
 constexpr int kAtomBytes = 128 * 64 * 2;     // 16 KB
 
@@ -35,9 +39,10 @@ struct Smem {
   static constexpr int kK = kQ + kTileBytes;       // 2 stages
   static constexpr int kV = kK + 2 * kTileBytes;   // 2 stages
   static constexpr int kP = kV + 2 * kTileBytes;   // 2 buffers
-  static constexpr int kBars = kP + 2 * kTileBytes;
-  // q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2]
-  static constexpr int kNumBars = 15;
+  static constexpr int kAlpha = kP + 2 * kTileBytes;  // float [2][128] rescale factors
+  static constexpr int kBars = kAlpha + 2 * 128 * 4;
+  // q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2], a_full[2], a_empty[2], fin
+  static constexpr int kNumBars = 20;
   static constexpr int kBytes = kBars + kNumBars * 8 + 16;
   static constexpr int kDynamic = kBytes + 1024;
 };
@@ -64,6 +69,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* p_full = bars + 9;
   uint64_t* o_full = bars + 11;
   uint64_t* o_empty = bars + 13;
+  uint64_t* a_full = bars + 15;
+  uint64_t* a_empty = bars + 17;
+  uint64_t* fin = bars + 19;
+  float* alpha_s = reinterpret_cast<float*>(smem + Smem::kAlpha);
+  // final (m2, l) per row: overlays the Q tile, which is dead once the last S = Q K^T has completed
+  float2* final_s = reinterpret_cast<float2*>(smem + Smem::kQ);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -91,7 +102,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&p_full[b], 128);
       mbar_init(&o_full[b], 1);
       mbar_init(&o_empty[b], 128);
+      mbar_init(&a_full[b], 128);
+      mbar_init(&a_empty[b], 128);
     }
+    mbar_init(fin, 128);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -168,34 +182,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       if (n_tiles >= 1) issue_pv(n_tiles - 1);
     }
-  } else {
-    // ------------------------------ softmax / output warps ------------------------------
+  } else if (warp < 6) {
+    // ------------------------------ softmax warps ------------------------------
     const int quad = warp & 3;
     const int r = quad * 32 + lane;  // query row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int qi = q0 + r;           // query index within the sequence
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
-    float m2 = -INFINITY, l = 0.f, alpha_prev = 1.f;
-
-    auto accumulate = [&](int j, float alpha) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      mbar_wait(&o_full[b], ph, abort_flag, err, 200, 7);
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < kD; c += 32) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem + 256 + b * 128 + c + lane_addr, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(t[i]));
-      }
-      tc_fence_before();
-      mbar_arrive(&o_empty[b]);
-    };
-
+    float m2 = -INFINITY, l = 0.f;
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
@@ -206,59 +199,86 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (is_self && causal) limit = min(limit, qi - key0 + 1);
       mbar_wait(&s_full[b], ph, abort_flag, err, 200, 8);
       tc_fence_after();
-      // pass 1: row maximum (the S row is re-read from TMEM in pass 2 instead of living in registers)
+      // the whole S row: four loads in flight, one wait, then the TMEM buffer is free for S(j + 2)
+      uint32_t t[kTileK];
+      tmem_ld_32x32b_x32(tmem + b * 128 + 0 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+      tmem_ld_32x32b_x32(tmem + b * 128 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
+      tmem_ld_32x32b_x32(tmem + b * 128 + 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[64]));
+      tmem_ld_32x32b_x32(tmem + b * 128 + 96 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[96]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[b]);
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < kTileK; c += 32) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem + b * 128 + c + lane_addr, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c + i < limit) mx = fmaxf(mx, __uint_as_float(t[i]));
-      }
+      for (int i = 0; i < kTileK; ++i)
+        if (i < limit) mx = fmaxf(mx, __uint_as_float(t[i]));
       const float new_m2 = fmaxf(m2, mx * scale_log2e);
       const float m_safe = new_m2 == -INFINITY ? 0.f : new_m2;
       const float alpha = fast_exp2(m2 - m_safe);  // m2 = -inf -> 0
+      mbar_wait(&a_empty[b], ph ^ 1, abort_flag, err, 200, 9);
+      alpha_s[b * 128 + r] = alpha;
+      mbar_arrive(&a_full[b]);
       float sum = 0.f;
       uint8_t* prow = smem + Smem::kP + b * kTileBytes + r * 128;
-      // pass 2: p = 2^(s * scale - m), packed to bf16 into the swizzled P tile
+      // p = 2^(s * scale - m), packed to bf16 into the swizzled P tile
 #pragma unroll
-      for (int c = 0; c < kTileK; c += 32) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem + b * 128 + c + lane_addr, t);
-        tmem_ld_wait();
+      for (int c8 = 0; c8 < kTileK / 8; ++c8) {
+        uint32_t w[4];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = c + c8 * 8 + 2 * i;
-            const float p0 = col < limit ? fast_exp2(fmaf(__uint_as_float(t[c8 * 8 + 2 * i]), scale_log2e, -m_safe)) : 0.f;
-            const float p1 =
-                col + 1 < limit ? fast_exp2(fmaf(__uint_as_float(t[c8 * 8 + 2 * i + 1]), scale_log2e, -m_safe)) : 0.f;
-            sum += p0 + p1;
-            __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            w[i] = *reinterpret_cast<uint32_t*>(&pk);
-          }
-          // 128B swizzle: 16-byte chunk index XOR (row mod 8); one atom = 64 keys
-          const int chunk16 = (c >> 3) + c8;  // 16-byte chunk index within the 128-key row
-          const int atom = chunk16 >> 3, chunk = chunk16 & 7;
-          *reinterpret_cast<uint4*>(prow + atom * kAtomBytes + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
+        for (int i = 0; i < 4; ++i) {
+          const int col = c8 * 8 + 2 * i;
+          const float p0 = col < limit ? fast_exp2(fmaf(__uint_as_float(t[col]), scale_log2e, -m_safe)) : 0.f;
+          const float p1 = col + 1 < limit ? fast_exp2(fmaf(__uint_as_float(t[col + 1]), scale_log2e, -m_safe)) : 0.f;
+          sum += p0 + p1;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          w[i] = *reinterpret_cast<uint32_t*>(&pk);
         }
+        // 128B swizzle: 16-byte chunk index XOR (row mod 8); one atom = 64 keys
+        const int atom = c8 >> 3, chunk = c8 & 7;
+        *reinterpret_cast<uint4*>(prow + atom * kAtomBytes + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      tc_fence_before();
-      mbar_arrive(&s_empty[b]);
       l = fmaf(l, alpha, sum);
       m2 = new_m2;
       fence_proxy_async_smem();
       mbar_arrive(&p_full[b]);
-      if (j >= 1) accumulate(j - 1, alpha_prev);
-      alpha_prev = alpha;
     }
-    if (n_tiles >= 1) accumulate(n_tiles - 1, alpha_prev);
-
+    if (n_tiles == 0) mbar_wait(q_full, 0, abort_flag, err, 200, 12);  // Q's TMA write must have landed before the overlay
+    final_s[r] = make_float2(m2, l);
+    mbar_arrive(fin);
+  } else {
+    // ------------------------------ output warps ------------------------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int qi = q0 + r;
+    float o[kD];
+#pragma unroll
+    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      mbar_wait(&a_full[b], ph, abort_flag, err, 200, 10);
+      const float alpha = alpha_s[b * 128 + r];
+      mbar_arrive(&a_empty[b]);
+      mbar_wait(&o_full[b], ph, abort_flag, err, 200, 7);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kD; c += 64) {
+        uint32_t t0[32], t1[32];
+        tmem_ld_32x32b_x32(tmem + 256 + b * 128 + c + lane_addr, t0);
+        tmem_ld_32x32b_x32(tmem + 256 + b * 128 + c + 32 + lane_addr, t1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(t0[i]));
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c + 32 + i] = fmaf(o[c + 32 + i], alpha, __uint_as_float(t1[i]));
+      }
+      tc_fence_before();
+      mbar_arrive(&o_empty[b]);
+    }
+    mbar_wait(fin, 0, abort_flag, err, 200, 11);
+    const float2 ml = final_s[r];
+    const float m2 = ml.x, l = ml.y;
     if (qi < sd.q_len) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = out + static_cast<long long>(sd.q_start + qi) * ld_out + head * kD;

@@ -168,7 +168,10 @@ def main() -> None:
     from rl_engine.kernels.ops.sm100.attention import make_layout
     from rl_engine.models.config import ModelConfig
     from rl_engine.models.llama import LlamaModel
+    from rl_engine.parallel.tp_linear import TensorParallelLinears as _TPL
     from rl_engine.parallel.tp_transformer import TensorParallelLlamaLayer, shard_layer_weights
+
+    tp_layer = _TPL(group=dist.group.WORLD, device=dev)
 
     cfg = ModelConfig("tp-check", 1024, 512, 1, 4 * world, 2 * world, 128, 512 * world)
     full = LlamaModel(cfg, dtype=torch.bfloat16, device=dev, seed=9, activation_checkpointing=False)
@@ -182,7 +185,7 @@ def main() -> None:
     yf = full._layer(xf, 0, pos, lay)
     yf.backward(dout_l)
     shard = {k: v.requires_grad_(True) for k, v in shard_layer_weights(full, 0, rank, world).items()}
-    layer = TensorParallelLlamaLayer(cfg, shard, tp, full.rope_cos, full.rope_sin)
+    layer = TensorParallelLlamaLayer(cfg, shard, tp_layer, full.rope_cos, full.rope_sin)
     tok = slice(rank * 256, (rank + 1) * 256)
     xl_ = xin[tok].clone().requires_grad_(True)
     yl = layer(xl_, pos, lay)
@@ -198,7 +201,7 @@ def main() -> None:
     norm_g = shard["mlp_norm"].grad.float().clone()
     dist.all_reduce(norm_g)
     close(norm_g, full.params[full._index["l0.mlp_norm"]].grad, 3e-2, "tp layer d(mlp_norm), summed over ranks")
-    tp.check()
+    tp_layer.check()
     print(f"[{rank}] OK tensor-parallel Llama layer", flush=True)
 
     # ---- context-parallel causal attention (zig-zag shards, peer-store K/V gather, peer_sum dK/dV) ----
