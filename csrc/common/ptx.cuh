@@ -89,6 +89,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One arrival per WARP: every lane has finished the work that the barrier publishes, lane 0 arrives for all of
+// them.  Barriers used this way are initialised with the number of arriving warps; it keeps hundreds of
+// same-address shared-memory atomics per tile out of the softmax loops.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -332,6 +340,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x for x <= 0 on the FMA and integer pipes (no MUFU): round-to-nearest split x = n + f with f in [-0.5, 0.5],
+// a cubic for 2^f (maximum relative error 7.7e-5, far below bf16 resolution) and n added to the exponent field.
+// Softmax kernels route a fixed share of their exponentials here because the MUFU unit (16 ex2 per clock per SM)
+// is as busy as the tensor cores in attention.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;  // 1.5 * 2^23: the integer part lands in the low mantissa bits
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.05508868f, 0.24260405f);
+  p = fmaf(p, f, 0.69327624f);
+  p = fmaf(p, f, 0.99992894f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 __device__ __forceinline__ float fast_log2(float x) {
   float y;

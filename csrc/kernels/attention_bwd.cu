@@ -24,7 +24,7 @@ namespace rlk {
 namespace {
 
 constexpr int kD = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, two compute groups of four warps (ping-pong over tiles)
 constexpr int kAtom128 = 128 * 128;  // bytes of a [128 rows x 64 cols] bf16 swizzle atom
 constexpr int kAtom64 = 64 * 128;    // bytes of a [64 rows x 64 cols] atom
 
@@ -56,17 +56,43 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const _
   if (lane == 0) delta[static_cast<long long>(h) * tokens + t] = s;
 }
 
+// One query row against a 64-key tile: dS = P * (dP - delta) with P = 2^(S * scale - lse), packed to bf16 into the
+// row's 128-byte swizzle line.  MASKED = false: the whole tile is visible to the row.
+template <bool MASKED>
+__device__ __forceinline__ void dq_row(const uint32_t (&ts)[64], const uint32_t (&tp)[64], int limit, float scale_log2e,
+                                       float lse2, float dlt, uint8_t* dsrow, int r) {
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int col = c8 * 8 + 2 * i;
+      const float x0 = fmaf(__uint_as_float(ts[col]), scale_log2e, -lse2);
+      const float x1 = fmaf(__uint_as_float(ts[col + 1]), scale_log2e, -lse2);
+      float p0 = fast_exp2(x0);
+      float p1 = (i & 1) ? poly_exp2(x1) : fast_exp2(x1);
+      if (MASKED) {
+        p0 = col < limit ? p0 : 0.f;
+        p1 = col + 1 < limit ? p1 : 0.f;
+      }
+      __nv_bfloat162 pk = __floats2bfloat162_rn(p0 * (__uint_as_float(tp[col]) - dlt), p1 * (__uint_as_float(tp[col + 1]) - dlt));
+      w[i] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    *reinterpret_cast<uint4*>(dsrow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // ---------------------------------------------------------------------------------------- dQ
 struct DqSmem {
   static constexpr int kQ = 0;                       // [128 x 128] 32 KB
   static constexpr int kDO = 32768;                  // 32 KB
-  static constexpr int kStages = 3;
+  static constexpr int kStages = 4;  // a stage is held until the dQ MMA of its tile: depth hides the TMA latency
   static constexpr int kStageBytes = 2 * 2 * kAtom64;  // K tile + V tile, each [64 keys x 128 d] = 16 KB
   static constexpr int kKV = 65536;
   static constexpr int kDS = kKV + kStages * kStageBytes;  // 2 buffers of [128 x 64] bf16 = 16 KB each
   static constexpr int kBars = kDS + 2 * kAtom128;
-  // qdo_full, kv_full[3], kv_empty[3], s_full[2], s_empty[2], ds_full[2], ds_empty[2]
-  static constexpr int kNumBars = 15;
+  // qdo_full, kv_full[4], kv_empty[4], s_full[2], s_empty[2], ds_full[2], ds_empty[2]
+  static constexpr int kNumBars = 17;
   static constexpr int kDynamic = kBars + kNumBars * 8 + 16 + 1024;
 };
 static_assert(DqSmem::kDynamic <= 232448 && DqSmem::kDynamic > 116 * 1024, "dQ kernel shared memory out of range");
@@ -82,11 +108,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DqSmem::kBars);
   uint64_t* qdo_full = bars;
   uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 4;
-  uint64_t* s_full = bars + 7;
-  uint64_t* s_empty = bars + 9;
-  uint64_t* ds_full = bars + 11;
-  uint64_t* ds_empty = bars + 13;
+  uint64_t* kv_empty = kv_full + DqSmem::kStages;
+  uint64_t* s_full = kv_empty + DqSmem::kStages;
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* ds_full = s_empty + 2;
+  uint64_t* ds_empty = ds_full + 2;
+  static_assert(1 + 2 * DqSmem::kStages + 8 == DqSmem::kNumBars, "dQ barrier layout");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DqSmem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -112,8 +139,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 128);
-      mbar_init(&ds_full[b], 128);
+      mbar_init(&s_empty[b], 4);  // one arrival per warp of the group that owns buffer b
+      mbar_init(&ds_full[b], 4);
       mbar_init(&ds_empty[b], 1);
     }
     *abort_flag = 0;
@@ -218,7 +245,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const float lse2 = row_ok ? lse[stat_idx] * kLog2e : 0.f;
     const float dlt = row_ok ? delta[stat_idx] : 0.f;
     const float scale_log2e = scale * kLog2e;
-    for (int j = 0; j < n_tiles; ++j) {
+    // Two groups of four warps: group g handles the tiles j = g, g + 2, ... (TMEM / smem buffer g), so that the
+    // exponentials of one tile overlap the TMEM loads and the MMAs of the next.
+    const int group = (warp - 2) >> 2;
+    for (int j = group; j < n_tiles; j += 2) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       const bool is_self = j >= n_prefix;
@@ -228,37 +258,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (!row_ok) limit = 0;
       mbar_wait(&s_full[b], ph, abort_flag, err, 210, 6);
       tc_fence_after();
-      mbar_wait(&ds_empty[b], ph ^ 1, abort_flag, err, 210, 7);  // dS buffer b free (dQ MMA of tile j-2 done)
       uint8_t* dsrow = smem + DqSmem::kDS + b * kAtom128 + r * 128;
-#pragma unroll
-      for (int c = 0; c < TK; c += 32) {
-        uint32_t ts[32], tp[32];
-        tmem_ld_32x32b_x32(tmem + b * 64 + c + lane_addr, ts);
-        tmem_ld_32x32b_x32(tmem + 128 + b * 64 + c + lane_addr, tp);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float d2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int idx = c8 * 8 + 2 * i + e;
-              const float p = (c + idx < limit) ? fast_exp2(fmaf(__uint_as_float(ts[idx]), scale_log2e, -lse2)) : 0.f;
-              d2[e] = p * (__uint_as_float(tp[idx]) - dlt);
-            }
-            __nv_bfloat162 pk = __floats2bfloat162_rn(d2[0], d2[1]);
-            w[i] = *reinterpret_cast<uint32_t*>(&pk);
-          }
-          const int chunk = (c >> 3) + c8;  // 16-byte chunk within the 64-key (128-byte) row
-          *reinterpret_cast<uint4*>(dsrow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
+      uint32_t ts[64], tp[64];
+      tmem_ld_32x32b_x32(tmem + b * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&ts[0]));
+      tmem_ld_32x32b_x32(tmem + b * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&ts[32]));
+      tmem_ld_32x32b_x32(tmem + 128 + b * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&tp[0]));
+      tmem_ld_32x32b_x32(tmem + 128 + b * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&tp[32]));
+      tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[b]);
+      mbar_arrive_warp(&s_empty[b]);  // S / dP are in registers: the TMEM buffers are free for tile j + 2
+      mbar_wait(&ds_empty[b], ph ^ 1, abort_flag, err, 210, 7);  // dS buffer b free (dQ MMA of tile j-2 done)
+      if (__any_sync(0xffffffffu, limit < TK)) {
+        dq_row<true>(ts, tp, limit, scale_log2e, lse2, dlt, dsrow, r);
+      } else {
+        dq_row<false>(ts, tp, limit, scale_log2e, lse2, dlt, dsrow, r);
+      }
       fence_proxy_async_smem();
-      mbar_arrive(&ds_full[b]);
+      mbar_arrive_warp(&ds_full[b]);
     }
     // wait for the last dQ MMA, then write dQ * scale
     if (n_tiles >= 1) {
@@ -267,8 +283,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tc_fence_after();
     }
     __nv_bfloat16* dst = dq + static_cast<long long>(sd.q_start + qi) * ld_dq + head * kD;
+    // each group writes its half of the dQ columns
 #pragma unroll
-    for (int c = 0; c < kD; c += 32) {
+    for (int c = group * 64; c < group * 64 + 64; c += 32) {
       uint32_t t[32];
       if (n_tiles >= 1) {
         tmem_ld_32x32b_x32(tmem + 256 + c + lane_addr, t);
@@ -325,17 +342,53 @@ struct QBlock {  // up to 64 consecutive queries of one sequence
 struct DkvSmem {
   static constexpr int kK = 0;        // [128 keys x 128 d] 32 KB
   static constexpr int kV = 32768;    // 32 KB
-  static constexpr int kStages = 2;
+  static constexpr int kStages = 3;  // a stage is held until the dV / dK MMAs of its block: depth hides the TMA latency
   static constexpr int kStageBytes = 2 * 2 * kAtom64;  // Q block + dO block, each [64 q x 128 d] = 16 KB
   static constexpr int kQdO = 65536;
   static constexpr int kPT = kQdO + kStages * kStageBytes;  // P^T: 2 buffers of [128 keys x 64 q] = 16 KB
   static constexpr int kDST = kPT + 2 * kAtom128;           // dS^T: 2 buffers
-  static constexpr int kBars = kDST + 2 * kAtom128;
-  // kv_full, q_full[2], q_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], acc_full
+  static constexpr int kStat = kDST + 2 * kAtom128;         // float [2 groups][64 lse * log2e | 64 delta]
+  static constexpr int kBars = kStat + 2 * 128 * 4;
+  // kv_full, q_full[3], q_empty[3], s_full[2], s_empty[2], p_full[2], p_empty[2], acc_full
   static constexpr int kNumBars = 16;
   static constexpr int kDynamic = kBars + kNumBars * 8 + 16 + 1024;
 };
 static_assert(DkvSmem::kDynamic <= 232448 && DkvSmem::kDynamic > 116 * 1024, "dK/dV kernel shared memory out of range");
+
+// One key row against a 64-query block: P^T = 2^(S^T * scale - lse) and dS^T = P^T * (dP^T - delta), both packed to
+// bf16 into the row's 128-byte swizzle lines.  `stat` holds lse * log2(e) for the 64 queries followed by their delta.
+// MASKED = false: every query of the block is visible to the row.  One exponential in four runs on the FMA pipe.
+template <bool MASKED>
+__device__ __forceinline__ void dkv_row(const uint32_t (&ts)[64], const uint32_t (&tp)[64], const float* stat, int c_lo,
+                                        int c_hi, float scale_log2e, uint8_t* prow, uint8_t* dsrow, int r) {
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) {
+    uint32_t wp[4], wd[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int col = c8 * 8 + 2 * i;
+      const float2 l2 = *reinterpret_cast<const float2*>(stat + col);
+      const float2 dl = *reinterpret_cast<const float2*>(stat + 64 + col);
+      const float x0 = fmaf(__uint_as_float(ts[col]), scale_log2e, -l2.x);
+      const float x1 = fmaf(__uint_as_float(ts[col + 1]), scale_log2e, -l2.y);
+      float p0 = fast_exp2(x0);
+      float p1 = (i & 1) ? poly_exp2(x1) : fast_exp2(x1);
+      if (MASKED) {
+        p0 = (col >= c_lo && col < c_hi) ? p0 : 0.f;
+        p1 = (col + 1 >= c_lo && col + 1 < c_hi) ? p1 : 0.f;
+      }
+      const float d0 = p0 * (__uint_as_float(tp[col]) - dl.x);
+      const float d1 = p1 * (__uint_as_float(tp[col + 1]) - dl.y);
+      __nv_bfloat162 a = __floats2bfloat162_rn(p0, p1);
+      __nv_bfloat162 d = __floats2bfloat162_rn(d0, d1);
+      wp[i] = *reinterpret_cast<uint32_t*>(&a);
+      wd[i] = *reinterpret_cast<uint32_t*>(&d);
+    }
+    const int sw = (c8 ^ (r & 7)) << 4;
+    *reinterpret_cast<uint4*>(prow + sw) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+    *reinterpret_cast<uint4*>(dsrow + sw) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+  }
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
@@ -349,12 +402,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkvSmem::kBars);
   uint64_t* kv_full = bars;
   uint64_t* q_full = bars + 1;
-  uint64_t* q_empty = bars + 3;
-  uint64_t* s_full = bars + 5;
-  uint64_t* s_empty = bars + 7;
-  uint64_t* p_full = bars + 9;
-  uint64_t* p_empty = bars + 11;
-  uint64_t* acc_full = bars + 13;
+  uint64_t* q_empty = q_full + DkvSmem::kStages;
+  uint64_t* s_full = q_empty + DkvSmem::kStages;
+  uint64_t* s_empty = s_full + 2;
+  uint64_t* p_full = s_empty + 2;
+  uint64_t* p_empty = p_full + 2;
+  uint64_t* acc_full = p_empty + 2;
+  static_assert(1 + 2 * DkvSmem::kStages + 8 + 1 == DkvSmem::kNumBars, "dK/dV barrier layout");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DkvSmem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -368,12 +422,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     mbar_init(acc_full, 1);
+    for (int s = 0; s < DkvSmem::kStages; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&q_full[b], 1);
-      mbar_init(&q_empty[b], 1);
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 128);
-      mbar_init(&p_full[b], 128);
+      mbar_init(&s_empty[b], 4);  // one arrival per warp of the group that owns buffer b
+      mbar_init(&p_full[b], 4);
       mbar_init(&p_empty[b], 1);
     }
     *abort_flag = 0;
@@ -397,17 +453,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tma_load_2d(smem + DkvSmem::kV + c * kAtom128, &tmap_v, kv_full, kv_head * kD + c * 64, it.k_row);
       }
       for (int t = 0; t < n_iter; ++t) {
-        const int b = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
+        const int st = t % DkvSmem::kStages;
+        const uint32_t ph = (t / DkvSmem::kStages) & 1;
         const int hq = kv_head * q_per_kv + t / n_qb;
         const QBlock qb = qblocks[it.qb_begin + t % n_qb];
-        mbar_wait(&q_empty[b], ph ^ 1, abort_flag, err, 220, 1);
-        uint8_t* sq = smem + DkvSmem::kQdO + b * DkvSmem::kStageBytes;
+        mbar_wait(&q_empty[st], ph ^ 1, abort_flag, err, 220, 1);
+        uint8_t* sq = smem + DkvSmem::kQdO + st * DkvSmem::kStageBytes;
         uint8_t* sdo = sq + 2 * kAtom64;
-        mbar_arrive_expect_tx(&q_full[b], DkvSmem::kStageBytes);
+        mbar_arrive_expect_tx(&q_full[st], DkvSmem::kStageBytes);
         for (int c = 0; c < 2; ++c) {
-          tma_load_2d(sq + c * kAtom64, &tmap_q, &q_full[b], hq * kD + c * 64, qb.q_row);
-          tma_load_2d(sdo + c * kAtom64, &tmap_do, &q_full[b], hq * kD + c * 64, qb.q_row);
+          tma_load_2d(sq + c * kAtom64, &tmap_q, &q_full[st], hq * kD + c * 64, qb.q_row);
+          tma_load_2d(sdo + c * kAtom64, &tmap_do, &q_full[st], hq * kD + c * 64, qb.q_row);
         }
       }
     }
@@ -425,7 +481,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_fence_after();
         const uint32_t spt = smem_u32(smem + DkvSmem::kPT + b * kAtom128);
         const uint32_t sdst = smem_u32(smem + DkvSmem::kDST + b * kAtom128);
-        const uint32_t sq = smem_u32(smem + DkvSmem::kQdO + b * DkvSmem::kStageBytes);
+        const int st = t % DkvSmem::kStages;
+        const uint32_t sq = smem_u32(smem + DkvSmem::kQdO + st * DkvSmem::kStageBytes);
         const uint32_t sdo = sq + 2 * kAtom64;
 #pragma unroll
         for (int k = 0; k < 64 / 16; ++k) {
@@ -438,15 +495,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     umma_smem_desc_sw128(sq + k * 2048, kAtom64, 1024), idesc_acc, (t | k) != 0 ? 1u : 0u);
         }
         umma_commit(&p_empty[b]);
-        umma_commit(&q_empty[b]);
+        umma_commit(&q_empty[st]);
       };
       for (int t = 0; t < n_iter; ++t) {
         const int b = t & 1;
         const uint32_t ph = (t >> 1) & 1;
-        mbar_wait(&q_full[b], ph, abort_flag, err, 220, 4);
+        const int st = t % DkvSmem::kStages;
+        mbar_wait(&q_full[st], (t / DkvSmem::kStages) & 1, abort_flag, err, 220, 4);
         mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 220, 5);
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + DkvSmem::kQdO + b * DkvSmem::kStageBytes);
+        const uint32_t sq = smem_u32(smem + DkvSmem::kQdO + st * DkvSmem::kStageBytes);
         const uint32_t sdo = sq + 2 * kAtom64;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
@@ -474,67 +532,56 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const bool key_ok = r < it.k_len;
     const float scale_log2e = scale * kLog2e;
-    for (int t = 0; t < n_iter; ++t) {
+    const int group = (warp - 2) >> 2;  // group g handles the iterations t = g, g + 2, ... (buffer g)
+    for (int t = group; t < n_iter; t += 2) {
       const int b = t & 1;
       const uint32_t ph = (t >> 1) & 1;
       const int hq = kv_head * q_per_kv + t / n_qb;
       const QBlock qb = qblocks[it.qb_begin + t % n_qb];
-      const float* lse_h = lse + static_cast<long long>(hq) * head_stride + qb.q_row;
-      const float* dl_h = delta + static_cast<long long>(hq) * head_stride + qb.q_row;
       // columns c (queries) visible to this key row: c < n_rows and (not causal or k_pos + r <= q_pos + c)
       int c_lo = 0;
       if (qb.causal) c_lo = max(0, it.k_pos + r - qb.q_pos);
       const int c_hi = key_ok ? qb.n_rows : 0;
+      // stage the block's 64 (lse * log2e, delta) pairs in shared memory: every key row needs all of them
+      float* stat = reinterpret_cast<float*>(smem + DkvSmem::kStat) + group * 128;
+      const int gt = threadIdx.x - 64 - group * 128;  // 0..127 inside the group
+      asm volatile("bar.sync %0, 128;" ::"r"(3 + group) : "memory");  // the previous block's readers are done
+      {
+        const int c = gt & 63;
+        const long long idx = static_cast<long long>(hq) * head_stride + qb.q_row + c;
+        float val = 0.f;
+        if (c < qb.n_rows) val = gt < 64 ? lse[idx] * kLog2e : delta[idx];
+        stat[gt] = val;
+      }
+      asm volatile("bar.sync %0, 128;" ::"r"(3 + group) : "memory");
       mbar_wait(&s_full[b], ph, abort_flag, err, 220, 6);
       tc_fence_after();
       mbar_wait(&p_empty[b], ph ^ 1, abort_flag, err, 220, 7);
       uint8_t* prow = smem + DkvSmem::kPT + b * kAtom128 + r * 128;
       uint8_t* dsrow = smem + DkvSmem::kDST + b * kAtom128 + r * 128;
-#pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t ts[32], tp[32];
-        tmem_ld_32x32b_x32(tmem + b * 64 + c + lane_addr, ts);
-        tmem_ld_32x32b_x32(tmem + 128 + b * 64 + c + lane_addr, tp);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t wp[4], wd[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float p2[2], d2[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int idx = c8 * 8 + 2 * i + e;
-              const int col = c + idx;
-              const bool ok = col >= c_lo && col < c_hi;
-              const float l2 = ok ? __ldg(lse_h + col) * kLog2e : 0.f;
-              const float dl = ok ? __ldg(dl_h + col) : 0.f;
-              const float p = ok ? fast_exp2(fmaf(__uint_as_float(ts[idx]), scale_log2e, -l2)) : 0.f;
-              p2[e] = p;
-              d2[e] = p * (__uint_as_float(tp[idx]) - dl);
-            }
-            __nv_bfloat162 a = __floats2bfloat162_rn(p2[0], p2[1]);
-            __nv_bfloat162 d = __floats2bfloat162_rn(d2[0], d2[1]);
-            wp[i] = *reinterpret_cast<uint32_t*>(&a);
-            wd[i] = *reinterpret_cast<uint32_t*>(&d);
-          }
-          const int chunk = (c >> 3) + c8;
-          const int sw = (chunk ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + sw) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-          *reinterpret_cast<uint4*>(dsrow + sw) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
-        }
-      }
+      uint32_t ts[64], tp[64];
+      tmem_ld_32x32b_x32(tmem + b * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&ts[0]));
+      tmem_ld_32x32b_x32(tmem + b * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&ts[32]));
+      tmem_ld_32x32b_x32(tmem + 128 + b * 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&tp[0]));
+      tmem_ld_32x32b_x32(tmem + 128 + b * 64 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&tp[32]));
+      tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[b]);
+      mbar_arrive_warp(&s_empty[b]);  // S^T / dP^T are in registers: the TMEM buffers are free for block t + 2
+      if (__any_sync(0xffffffffu, c_lo > 0 || c_hi < 64)) {
+        dkv_row<true>(ts, tp, stat, c_lo, c_hi, scale_log2e, prow, dsrow, r);
+      } else {
+        dkv_row<false>(ts, tp, stat, c_lo, c_hi, scale_log2e, prow, dsrow, r);
+      }
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[b]);
+      mbar_arrive_warp(&p_full[b]);
     }
     // epilogue: dV (TMEM 256..383) and dK * scale (384..511)
     mbar_wait(acc_full, 0, abort_flag, err, 220, 8);
     tc_fence_after();
     const long long krow = static_cast<long long>(it.k_row) + r;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
+    // group 0 writes dV, group 1 writes dK
+    {
+      const int which = group;
       const float mul = which == 0 ? 1.f : scale;
 #pragma unroll
       for (int c = 0; c < kD; c += 32) {

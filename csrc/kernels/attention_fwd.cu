@@ -12,18 +12,35 @@
 //
 // One CTA = one 128-query tile of one head.  Warp 0 loads Q once and K/V tiles through a 2-stage TMA
 // ring; warp 1 issues S = Q K^T and O_j = P_j V_j on tcgen05 with S, O_j double-buffered in TMEM
-// (4 x 128 columns).  Two groups of four warps own one query row per thread each:
-//   softmax warps 2..5   : pull the whole S row into registers with four tcgen05.ld in flight (one wait), free
-//                          the S buffer at once, online softmax, P as bf16 into a 128B-swizzled smem tile (the
-//                          A operand of the second MMA), the row's rescale factor alpha into shared memory;
-//   output warps 6..9    : O = O * alpha + O_j in registers, final normalisation, output and log-sum-exp.
-// Splitting the two jobs keeps each thread under the register limit with all its TMEM loads in flight and
-// puts two warps on every scheduler, so TMEM-load latency of one group hides behind the other's arithmetic.
+// (4 x 128 columns).  Eight softmax warps share the 128 query rows TWO threads per row: warps 2..5 own keys
+// 0..63 of every tile and output columns 0..63, warps 6..9 own keys 64..127 and output columns 64..127.
+// Each thread pulls its half of the S row with two tcgen05.ld in flight, the two halves exchange their row
+// maximum through shared memory (one named barrier per tile), then each runs its half of the online softmax,
+// writes its 64-key atom of P as bf16 into the 128B-swizzled smem tile (the A operand of the second MMA) and
+// accumulates its half of O in registers as O = O * alpha + O_j.  Two warps per scheduler hide the
+// fixed-latency and TMEM-load stalls that one warp per scheduler exposes.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "kernels.h"
 
 namespace rlk {
+
+#ifdef RLK_ATTN_PROFILE
+// Phase timing of one softmax thread (debug builds only): cycles accumulated per phase over the tiles of one CTA.
+__device__ unsigned long long g_attn_prof[16];
+#define PROF_DECL unsigned long long prof_t = clock64(); const bool prof_on = (blockIdx.x == gridDim.x / 2) && threadIdx.x == 64
+#define PROF(slot)                                   \
+  if (prof_on) {                                     \
+    const unsigned long long now = clock64();        \
+    atomicAdd(&g_attn_prof[slot], now - prof_t);     \
+    prof_t = now;                                    \
+  }
+void attention_profile_read(unsigned long long* out) { cudaMemcpyFromSymbol(out, g_attn_prof, sizeof(unsigned long long) * 16); }
+void attention_profile_reset() { unsigned long long z[16] = {0}; cudaMemcpyToSymbol(g_attn_prof, z, sizeof(z)); }
+#else
+#define PROF_DECL
+#define PROF(slot)
+#endif
 
 namespace {
 
@@ -31,6 +48,7 @@ constexpr int kD = 128;        // head dim
 constexpr int kTileQ = 128;
 constexpr int kTileK = 128;
 constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
 constexpr int kTileBytes = kTileQ * kD * 2;  // 32 KB: two 128B-swizzle atoms of [128 x 64]
 constexpr int kAtomBytes = 128 * 64 * 2;     // 16 KB
 
@@ -39,10 +57,10 @@ struct Smem {
   static constexpr int kK = kQ + kTileBytes;       // 2 stages
   static constexpr int kV = kK + 2 * kTileBytes;   // 2 stages
   static constexpr int kP = kV + 2 * kTileBytes;   // 2 buffers
-  static constexpr int kAlpha = kP + 2 * kTileBytes;  // float [2][128] rescale factors
-  static constexpr int kBars = kAlpha + 2 * 128 * 4;
-  // q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2], a_full[2], a_empty[2], fin
-  static constexpr int kNumBars = 20;
+  static constexpr int kXmax = kP + 2 * kTileBytes;  // float [2 halves][128 rows]: row-maximum exchange
+  static constexpr int kBars = kXmax + 2 * 128 * 4;
+  // q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2], v_full[2], v_empty[2]
+  static constexpr int kNumBars = 19;
   static constexpr int kBytes = kBars + kNumBars * 8 + 16;
   static constexpr int kDynamic = kBytes + 1024;
 };
@@ -51,6 +69,50 @@ static_assert(Smem::kDynamic <= 232448, "attention forward exceeds the 227 KB sh
 struct SeqDesc {  // one per sequence, int32 x 8
   int q_start, q_len, pk_start, pk_len, sk_start, sk_len, pad0, pad1;
 };
+
+// Half a score row (64 keys) of one query: p = 2^(s * scale - m) packed to bf16 into the row's 128-byte swizzle
+// line; returns the fp32 sum.  One exponential in four runs on the FMA pipe (poly_exp2), the rest on MUFU.
+// MASKED = false is the common case of a tile that is entirely visible to the row.
+template <bool MASKED>
+__device__ __forceinline__ float softmax_half_row(const uint32_t (&t)[64], int limit, float scale_log2e, float m_safe,
+                                                  uint8_t* prow, int r) {
+  float sum = 0.f;
+#pragma unroll
+  for (int c8 = 0; c8 < 8; ++c8) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int col = c8 * 8 + 2 * i;
+      const float x0 = fmaf(__uint_as_float(t[col]), scale_log2e, -m_safe);
+      const float x1 = fmaf(__uint_as_float(t[col + 1]), scale_log2e, -m_safe);
+      float p0 = fast_exp2(x0);
+      float p1 = (i & 1) ? poly_exp2(x1) : fast_exp2(x1);
+      if (MASKED) {
+        p0 = col < limit ? p0 : 0.f;
+        p1 = col + 1 < limit ? p1 : 0.f;
+      }
+      sum += p0 + p1;
+      __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+      w[i] = *reinterpret_cast<uint32_t*>(&pk);
+    }
+    // 128B swizzle: 16-byte chunk index XOR (row mod 8)
+    *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return sum;
+}
+
+template <bool MASKED>
+__device__ __forceinline__ float max_half_row(const uint32_t (&t)[64], int limit) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 64; i += 4) {
+    if (!MASKED || i < limit) m0 = fmaxf(m0, __uint_as_float(t[i]));
+    if (!MASKED || i + 1 < limit) m1 = fmaxf(m1, __uint_as_float(t[i + 1]));
+    if (!MASKED || i + 2 < limit) m2 = fmaxf(m2, __uint_as_float(t[i + 2]));
+    if (!MASKED || i + 3 < limit) m3 = fmaxf(m3, __uint_as_float(t[i + 3]));
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -62,19 +124,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
+  // K and V have separate rings: a K stage is free as soon as S = Q K^T of its tile has completed, long before
+  // the P V product releases the V stage, so the K tile two steps ahead is in flight while the softmax runs.
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 15;
+  uint64_t* v_empty = bars + 17;
   uint64_t* s_full = bars + 5;
   uint64_t* s_empty = bars + 7;
   uint64_t* p_full = bars + 9;
   uint64_t* o_full = bars + 11;
   uint64_t* o_empty = bars + 13;
-  uint64_t* a_full = bars + 15;
-  uint64_t* a_empty = bars + 17;
-  uint64_t* fin = bars + 19;
-  float* alpha_s = reinterpret_cast<float*>(smem + Smem::kAlpha);
-  // final (m2, l) per row: overlays the Q tile, which is dead once the last S = Q K^T has completed
-  float2* final_s = reinterpret_cast<float2*>(smem + Smem::kQ);
+  float* xmax_s = reinterpret_cast<float*>(smem + Smem::kXmax);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -95,17 +156,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&kv_full[b], 1);
-      mbar_init(&kv_empty[b], 1);
+      mbar_init(&k_full[b], 1);
+      mbar_init(&k_empty[b], 1);
+      mbar_init(&v_full[b], 1);
+      mbar_init(&v_empty[b], 1);
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 128);
-      mbar_init(&p_full[b], 128);
+      mbar_init(&s_empty[b], kSoftmaxThreads / 32);  // one arrival per softmax warp
+      mbar_init(&p_full[b], kSoftmaxThreads / 32);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], 128);
-      mbar_init(&a_full[b], 128);
-      mbar_init(&a_empty[b], 128);
+      mbar_init(&o_empty[b], kSoftmaxThreads / 32);
     }
-    mbar_init(fin, 128);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -126,18 +186,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_arrive_expect_tx(q_full, kTileBytes);
       tma_load_2d(smem + Smem::kQ, &tmap_q, q_full, head * kD, sd.q_start + q0);
       tma_load_2d(smem + Smem::kQ + kAtomBytes, &tmap_q, q_full, head * kD + 64, sd.q_start + q0);
-      for (int j = 0; j < n_tiles; ++j) {
+      auto key_row = [&](int j) { return j < n_prefix ? sd.pk_start + j * kTileK : sd.sk_start + (j - n_prefix) * kTileK; };
+      auto load_k = [&](int j) {
         const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        mbar_wait(&kv_empty[b], ph ^ 1, abort_flag, err, 200, 1);
-        const int row = j < n_prefix ? sd.pk_start + j * kTileK : sd.sk_start + (j - n_prefix) * kTileK;
-        mbar_arrive_expect_tx(&kv_full[b], 2 * kTileBytes);
+        mbar_wait(&k_empty[b], ((j >> 1) & 1) ^ 1, abort_flag, err, 200, 1);
+        mbar_arrive_expect_tx(&k_full[b], kTileBytes);
         uint8_t* sk = smem + Smem::kK + b * kTileBytes;
+        tma_load_2d(sk, &tmap_k, &k_full[b], kv_head * kD, key_row(j));
+        tma_load_2d(sk + kAtomBytes, &tmap_k, &k_full[b], kv_head * kD + 64, key_row(j));
+      };
+      auto load_v = [&](int j) {
+        const int b = j & 1;
+        mbar_wait(&v_empty[b], ((j >> 1) & 1) ^ 1, abort_flag, err, 200, 13);
+        mbar_arrive_expect_tx(&v_full[b], kTileBytes);
         uint8_t* sv = smem + Smem::kV + b * kTileBytes;
-        tma_load_2d(sk, &tmap_k, &kv_full[b], kv_head * kD, row);
-        tma_load_2d(sk + kAtomBytes, &tmap_k, &kv_full[b], kv_head * kD + 64, row);
-        tma_load_2d(sv, &tmap_v, &kv_full[b], kv_head * kD, row);
-        tma_load_2d(sv + kAtomBytes, &tmap_v, &kv_full[b], kv_head * kD + 64, row);
+        tma_load_2d(sv, &tmap_v, &v_full[b], kv_head * kD, key_row(j));
+        tma_load_2d(sv + kAtomBytes, &tmap_v, &v_full[b], kv_head * kD + 64, key_row(j));
+      };
+      // K runs one tile ahead of V in issue order: K(j + 1) only waits for S(j - 1), V(j) for P V of tile j - 2
+      if (n_tiles >= 1) load_k(0);
+      for (int j = 0; j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) load_k(j + 1);
+        load_v(j);
       }
     }
   } else if (warp == 1) {
@@ -151,6 +221,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint32_t ph = (j >> 1) & 1;
         mbar_wait(&p_full[b], ph, abort_flag, err, 200, 3);
         mbar_wait(&o_empty[b], ph ^ 1, abort_flag, err, 200, 4);
+        mbar_wait(&v_full[b], ph, abort_flag, err, 200, 14);
         tc_fence_after();
         const uint32_t sp = smem_u32(smem + Smem::kP + b * kTileBytes);
         const uint32_t sv = smem_u32(smem + Smem::kV + b * kTileBytes);
@@ -162,12 +233,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_bf16(tmem + 256 + b * 128, da, db, idesc_o, k != 0 ? 1u : 0u);
         }
         umma_commit(&o_full[b]);
-        umma_commit(&kv_empty[b]);
+        umma_commit(&v_empty[b]);
       };
       for (int j = 0; j < n_tiles; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        mbar_wait(&kv_full[b], ph, abort_flag, err, 200, 5);
+        mbar_wait(&k_full[b], ph, abort_flag, err, 200, 5);
         mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 200, 6);
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + Smem::kK + b * kTileBytes);
@@ -178,17 +249,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[b]);
+        umma_commit(&k_empty[b]);
         if (j >= 1) issue_pv(j - 1);
       }
       if (n_tiles >= 1) issue_pv(n_tiles - 1);
     }
-  } else if (warp < 6) {
-    // ------------------------------ softmax warps ------------------------------
+  } else {
+    // ------------------------------ softmax / output warps ------------------------------
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;  // query row within the tile
+    const int half = (warp - 2) >> 2;  // 0: keys / output columns 0..63, 1: 64..127
+    const int r = quad * 32 + lane;    // query row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int qi = q0 + r;           // query index within the sequence
-    float m2 = -INFINITY, l = 0.f;
+    const int qi = q0 + r;             // query index within the sequence
+    constexpr int kHalf = 64;
+    float o[kHalf];
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) o[i] = 0.f;
+    float m2 = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    PROF_DECL;
+
+    auto accumulate = [&](int j, float alpha) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      PROF(0);
+      mbar_wait(&o_full[b], ph, abort_flag, err, 200, 7);
+      PROF(6);
+      tc_fence_after();
+      uint32_t t0[32], t1[32];
+      tmem_ld_32x32b_x32(tmem + 256 + b * 128 + half * kHalf + lane_addr, t0);
+      tmem_ld_32x32b_x32(tmem + 256 + b * 128 + half * kHalf + 32 + lane_addr, t1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(t0[i]));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(t1[i]));
+      tc_fence_before();
+      mbar_arrive_warp(&o_empty[b]);
+      PROF(7);
+    };
+
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
@@ -197,93 +296,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int range_len = is_self ? sd.sk_len : sd.pk_len;
       int limit = range_len - key0;  // keys [0, limit) of this tile are in range
       if (is_self && causal) limit = min(limit, qi - key0 + 1);
+      limit -= half * kHalf;         // in this thread's 64 columns
+      PROF(0);
       mbar_wait(&s_full[b], ph, abort_flag, err, 200, 8);
+      PROF(1);
       tc_fence_after();
-      // the whole S row: four loads in flight, one wait, then the TMEM buffer is free for S(j + 2)
-      uint32_t t[kTileK];
-      tmem_ld_32x32b_x32(tmem + b * 128 + 0 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
-      tmem_ld_32x32b_x32(tmem + b * 128 + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
-      tmem_ld_32x32b_x32(tmem + b * 128 + 64 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[64]));
-      tmem_ld_32x32b_x32(tmem + b * 128 + 96 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[96]));
+      // this thread's half of the S row: both loads in flight, one wait, then the TMEM buffer is released
+      uint32_t t[kHalf];
+      tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+      tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[b]);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < kTileK; ++i)
-        if (i < limit) mx = fmaxf(mx, __uint_as_float(t[i]));
+      mbar_arrive_warp(&s_empty[b]);
+      PROF(2);
+      // a tile is mask-free for the whole warp in all but the diagonal and the last tile of a range
+      const bool masked = __any_sync(0xffffffffu, limit < kHalf);
+      float mx = masked ? max_half_row<true>(t, limit) : max_half_row<false>(t, limit);
+      // exchange the half-row maxima through shared memory; the second barrier keeps the next tile's writes
+      // behind this tile's reads
+      xmax_s[half * 128 + r] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");  // only the two warps that share these 32 rows
+      mx = fmaxf(mx, xmax_s[(half ^ 1) * 128 + r]);
+      asm volatile("bar.sync %0, 64;" ::"r"(5 + quad) : "memory");
+      PROF(3);
       const float new_m2 = fmaxf(m2, mx * scale_log2e);
       const float m_safe = new_m2 == -INFINITY ? 0.f : new_m2;
       const float alpha = fast_exp2(m2 - m_safe);  // m2 = -inf -> 0
-      mbar_wait(&a_empty[b], ph ^ 1, abort_flag, err, 200, 9);
-      alpha_s[b * 128 + r] = alpha;
-      mbar_arrive(&a_full[b]);
-      float sum = 0.f;
-      uint8_t* prow = smem + Smem::kP + b * kTileBytes + r * 128;
-      // p = 2^(s * scale - m), packed to bf16 into the swizzled P tile
-#pragma unroll
-      for (int c8 = 0; c8 < kTileK / 8; ++c8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c8 * 8 + 2 * i;
-          const float p0 = col < limit ? fast_exp2(fmaf(__uint_as_float(t[col]), scale_log2e, -m_safe)) : 0.f;
-          const float p1 = col + 1 < limit ? fast_exp2(fmaf(__uint_as_float(t[col + 1]), scale_log2e, -m_safe)) : 0.f;
-          sum += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          w[i] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        // 128B swizzle: 16-byte chunk index XOR (row mod 8); one atom = 64 keys
-        const int atom = c8 >> 3, chunk = c8 & 7;
-        *reinterpret_cast<uint4*>(prow + atom * kAtomBytes + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      l = fmaf(l, alpha, sum);
+      // 64 keys of a row = one 128-byte swizzle row of atom `half`
+      uint8_t* prow = smem + Smem::kP + b * kTileBytes + half * kAtomBytes + r * 128;
+      const float sum = masked ? softmax_half_row<true>(t, limit, scale_log2e, m_safe, prow, r)
+                               : softmax_half_row<false>(t, limit, scale_log2e, m_safe, prow, r);
+      l = fmaf(l, alpha, sum);  // this thread's share of the row sum; both halves use the same maximum
       m2 = new_m2;
       fence_proxy_async_smem();
-      mbar_arrive(&p_full[b]);
+      mbar_arrive_warp(&p_full[b]);
+      PROF(4);
+      if (j >= 1) accumulate(j - 1, alpha_prev);
+      alpha_prev = alpha;
     }
-    if (n_tiles == 0) mbar_wait(q_full, 0, abort_flag, err, 200, 12);  // Q's TMA write must have landed before the overlay
-    final_s[r] = make_float2(m2, l);
-    mbar_arrive(fin);
-  } else {
-    // ------------------------------ output warps ------------------------------
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int qi = q0 + r;
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      mbar_wait(&a_full[b], ph, abort_flag, err, 200, 10);
-      const float alpha = alpha_s[b * 128 + r];
-      mbar_arrive(&a_empty[b]);
-      mbar_wait(&o_full[b], ph, abort_flag, err, 200, 7);
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < kD; c += 64) {
-        uint32_t t0[32], t1[32];
-        tmem_ld_32x32b_x32(tmem + 256 + b * 128 + c + lane_addr, t0);
-        tmem_ld_32x32b_x32(tmem + 256 + b * 128 + c + 32 + lane_addr, t1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, __uint_as_float(t0[i]));
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + 32 + i] = fmaf(o[c + 32 + i], alpha, __uint_as_float(t1[i]));
-      }
-      tc_fence_before();
-      mbar_arrive(&o_empty[b]);
-    }
-    mbar_wait(fin, 0, abort_flag, err, 200, 11);
-    const float2 ml = final_s[r];
-    const float m2 = ml.x, l = ml.y;
+    if (n_tiles >= 1) accumulate(n_tiles - 1, alpha_prev);
+
+    // total row sum = the two halves' shares (the exchange buffer is free: every reader passed barrier 2)
+    xmax_s[half * 128 + r] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+    l += xmax_s[(half ^ 1) * 128 + r];
+
     if (qi < sd.q_len) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + static_cast<long long>(sd.q_start + qi) * ld_out + head * kD;
+      __nv_bfloat16* dst = out + static_cast<long long>(sd.q_start + qi) * ld_out + head * kD + half * kHalf;
 #pragma unroll
-      for (int c8 = 0; c8 < kD / 8; ++c8) {
+      for (int c8 = 0; c8 < kHalf / 8; ++c8) {
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -292,7 +354,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         reinterpret_cast<uint4*>(dst)[c8] = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      if (lse != nullptr) {
+      if (lse != nullptr && half == 0) {
         lse[static_cast<long long>(head) * lse_head_stride + sd.q_start + qi] =
             l > 0.f ? (m2 + log2f(l)) * kLn2 : -INFINITY;
       }

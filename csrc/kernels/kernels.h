@@ -314,6 +314,11 @@ void moe_combine(const __nv_bfloat16* src, long long ld_src, const int* slot, co
                  long long src_rows = 0, uint32_t* err = nullptr);
 void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, long long ld_b, const int* slot, int k,
                 int tokens, int hidden, float* out, cudaStream_t stream);
+#ifdef RLK_ATTN_PROFILE
+void attention_profile_read(unsigned long long* out);
+void attention_profile_reset();
+#endif
+
 // ---- tracing (trace.cu): out[slot] = %globaltimer in stream order
 void device_stamp(unsigned long long* out, int slot, cudaStream_t stream);
 

@@ -1073,6 +1073,14 @@ namespace {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "rl_engine native sm_100a kernels";
+#ifdef RLK_ATTN_PROFILE
+  m.def("attention_profile", [] {
+    std::vector<unsigned long long> v(16);
+    rlk::attention_profile_read(v.data());
+    rlk::attention_profile_reset();
+    return v;
+  });
+#endif
   m.def("device_stamp", &device_stamp);
   m.def("trace_enabled", [] { return rlk::trace_enabled(); });
   m.def("gemm", rlk::traced("rlk::gemm", &gemm), py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,

@@ -15,6 +15,7 @@ from torch.utils.cpp_extension import BuildExtension, CUDAExtension
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
+CXX_FLAGS = ["-O3", "-std=c++17"]
 NVCC_FLAGS = [
     "-O3",
     "-std=c++17",
@@ -27,6 +28,9 @@ NVCC_FLAGS = [
 ]
 if os.environ.get("RLK_DEBUG_BOUNDS") == "1":
     NVCC_FLAGS.append("-DRLK_DEBUG_BOUNDS=1")
+if os.environ.get("RLK_ATTN_PROFILE") == "1":  # per-phase cycle counters in the attention forward kernel
+    NVCC_FLAGS.append("-DRLK_ATTN_PROFILE=1")
+    CXX_FLAGS.append("-DRLK_ATTN_PROFILE=1")
 if os.environ.get("RLK_PTXAS_VERBOSE") == "1":
     NVCC_FLAGS += ["-Xptxas", "-v"]
 
@@ -49,7 +53,7 @@ setup(
             name="rl_engine._C",
             sources=sources(),
             include_dirs=[os.path.join(ROOT, "csrc")],
-            extra_compile_args={"cxx": ["-O3", "-std=c++17"], "nvcc": NVCC_FLAGS},
+            extra_compile_args={"cxx": CXX_FLAGS, "nvcc": NVCC_FLAGS},
         )
     ],
     cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
