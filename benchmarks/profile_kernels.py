@@ -111,6 +111,30 @@ def case_gemm_shape():
             "note": f"layout {spec[3]} (A {'MN' if a_mn else 'K'}-major, B {'MN' if b_mn else 'K'}-major), pair={int(pair)}"}
 
 
+def case_tp_ag_gemm():
+    """The fused all-gather -> GEMM kernel on ONE rank: the copy warps feed this GPU's own gathered buffer, so the
+    kernel (copy warps + arrival counters + waiting TMA producer) can be captured without a multi-rank launch."""
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+
+    tp = TensorParallelLinears()
+    t, h, n = 16384, 4096, 7168
+    x, w = rand((t, h)), rand((n, h), 0.02, 1)
+    ms = timed(lambda: tp.ag_gemm(x, w))
+    return {"flops": 2.0 * t * h * n, "bytes": 2.0 * (2 * t * h + n * h + t * n), "ms": ms, "shape": [t, n, h],
+            "note": "world = 1: gathered rows are written and read locally"}
+
+
+def case_tp_gemm_rs():
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+
+    tp = TensorParallelLinears()
+    t, h, k = 16384, 4096, 7168
+    a, w = rand((t, k)), rand((h, k), 0.02, 1)
+    ms = timed(lambda: tp.gemm_rs(a, w))
+    return {"flops": 2.0 * t * h * k, "bytes": 2.0 * (t * k + h * k + 3 * t * h), "ms": ms, "shape": [t, h, k],
+            "note": "world = 1: one partial slab, written by the epilogue and summed by the in-kernel reduce phase"}
+
+
 def case_linear_logp():
     from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
 
@@ -206,7 +230,7 @@ def case_sampler():
     logits = rand((256, 151936)).float()
     ms = timed(lambda: sample_topk_topp(logits, top_k=50, top_p=0.9, temperature=0.7, seed=1, offset=0))
     return {"flops": 0.0, "bytes": 4.0 * 256 * 151936, "ms": ms, "shape": [256, 151936],
-            "note": "bytes = one pass; the kernel makes 5 passes over each row (L2 resident)"}
+            "note": "bytes = one pass over the logits; the kernel reads each row twice (histogram, gather)"}
 
 
 CASES = {name[5:]: fn for name, fn in globals().items() if name.startswith("case_")}

@@ -383,6 +383,7 @@ struct EpiStore {
   };
   struct State {};
   static constexpr int kCommWarps = 0;
+  static constexpr int kStagingBytes = 0;
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}

@@ -2,6 +2,8 @@
 // bf16 or fp32 output, optionally accumulating into the destination.  The reference has no GEMM of
 // its own (it calls cuBLAS through torch.matmul, e.g. rl_engine/kernels/ops/pytorch/loss/
 // linear_logp.py:17-38); this kernel exists so that no hot path needs a library GEMM.
+#include <cstdlib>
+
 #include "../common/gemm2_sm100.cuh"
 #include "../common/gemm_sm100.cuh"
 #include "../common/tensormap.h"
@@ -45,10 +47,20 @@ void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stre
   kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, a.err, 100u);
 }
 
+// RLK_GEMM_TMA_STORE=0 keeps the pair kernel on the direct-store epilogue (for A/B comparisons).
+bool pair_tma_store_disabled() {
+  static const bool off = [] {
+    const char* env = std::getenv("RLK_GEMM_TMA_STORE");
+    return env != nullptr && env[0] == '0';
+  }();
+  return off;
+}
+
 // CTA-pair kernel: 256 x 256 tiles, one work item per pair of SMs.
 constexpr int kPairStages = 6;
+constexpr int kPairStagesTma = 5;  // one ring stage makes room for the 64 KB output staging tile
 
-template <bool A_MN, bool B_MN, class Epi>
+template <bool A_MN, bool B_MN, class Epi, int STAGES = kPairStages>
 void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
   GemmProblem p = make_gemm_problem(a.M, a.N, a.K, kBN, 1, 1);
   p.tiles_m = (a.M + kPairBM - 1) / kPairBM;
@@ -58,8 +70,8 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
                               : make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
   const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, a.K, a.N, a.ldb, kBK, 64)
                               : make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kBN / 2, kBK);
-  auto kernel = gemm_pair_sm100_kernel<kBN, A_MN, B_MN, kPairStages, Epi>;
-  using L = PairSmem<kBN, kPairStages>;
+  auto kernel = gemm_pair_sm100_kernel<kBN, A_MN, B_MN, STAGES, Epi>;
+  using L = PairSmem<kBN, STAGES, Epi::kStagingBytes>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -74,6 +86,16 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
 template <bool A_MN, bool B_MN>
 void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
   if (a.cta_pair && a.group_mode == 0) {
+    // bf16 output that TMA can address: stage the tile in shared memory and store full lines
+    const bool tma_out = !a.out_fp32 && !a.accumulate && a.ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 &&
+                         !pair_tma_store_disabled();
+    if (tma_out) {
+      EpiStoreTma::Params ep;
+      ep.tmap_c = make_tmap_2d_bf16(a.D, a.M, a.N, a.ldd, kBM, 64);
+      ep.alpha = a.alpha;
+      launch_pair<A_MN, B_MN, EpiStoreTma, kPairStagesTma>(a, ep, stream);
+      return;
+    }
     if (a.out_fp32) {
       if (a.accumulate) {
         using E = EpiStore<float, true>;

@@ -1,9 +1,10 @@
 // Temperature / top-k / top-p sampling, one CTA per row of logits.
 //
-//   1. exact k-th largest logit by 4-pass radix select on order-preserving 32-bit keys
-//      (integer histograms in shared memory: counts are exact, so the threshold is deterministic);
-//   2. candidates (> threshold, plus ties) gathered into shared memory and bitonic-sorted by
-//      (logit descending, index ascending) -- a total order, so the gather order does not matter;
+//   1. radix select on order-preserving 32-bit keys (integer histograms in shared memory: counts are exact, so
+//      the threshold is deterministic) with a 12-bit first digit; the search stops as soon as the elements at or
+//      above the threshold bin fit into the candidate buffer, normally after ONE pass over the row;
+//   2. those candidates are gathered into shared memory and bitonic-sorted by (logit descending, index
+//      ascending) -- a total order, so the gather order does not matter -- and cut to the first k plus ties;
 //   3. softmax with temperature over the candidates, inclusive scan in a fixed tree, top-p cut
 //      "keep token i iff the mass strictly before it is <= p" (first token always kept);
 //   4. inverse-CDF draw with a Philox4x32-10 uniform keyed by (seed, row, offset).
@@ -55,60 +56,105 @@ __global__ void __launch_bounds__(kThreads)
 sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int top_k, float top_p, float inv_temp,
                         unsigned long long seed, unsigned long long offset, long long* __restrict__ out_ids,
                         float* __restrict__ out_logprob) {
-  __shared__ unsigned int hist[256];
+  __shared__ unsigned int hist[4096];
   __shared__ unsigned long long cand[kCap];
   __shared__ float prob[kCap];
   __shared__ float warp_tot[kThreads / 32];
-  __shared__ unsigned int s_prefix, s_remaining, s_count, s_nkeep;
+  __shared__ unsigned int warp_cnt[kThreads / 32];
+  __shared__ unsigned int s_prefix, s_remaining, s_above, s_pop, s_count, s_nkeep;
   __shared__ float s_mass;
 
   const int row = blockIdx.x;
   const T* z = logits + static_cast<long long>(row) * ld;
   const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
   const int k = top_k < 1 ? 1 : (top_k > V ? V : top_k);
 
-  // ---- 1. radix select: key of the k-th largest element
+  // ---- 1. radix select on order-preserving keys, digits of 12, 8, 8 and 4 bits from the top.  After each digit
+  //         the threshold bin is located by a parallel suffix scan; as soon as the elements above the bin plus the
+  //         bin itself fit into the candidate buffer the search stops and they are all gathered (the sort below
+  //         finds the exact k-th among them).  With k <= 1024 that is the case after the first digit for any
+  //         reasonable logit distribution, so a row is read twice (histogram, gather) instead of five times.
   if (tid == 0) {
     s_prefix = 0;
     s_remaining = static_cast<unsigned int>(k);
+    s_above = 0;
+    s_pop = static_cast<unsigned int>(V);
   }
+  __syncthreads();
+  int shift = 32;
+#pragma unroll 1
   for (int pass = 0; pass < 4; ++pass) {
-    const int shift = 24 - 8 * pass;
-    if (tid < 256) hist[tid] = 0;
+    const int bits = pass == 0 ? 12 : (pass == 3 ? 4 : 8);
+    if (s_above + s_pop <= static_cast<unsigned int>(kCap)) break;  // uniform: shared values behind a barrier
+    const uint32_t himask = pass == 0 ? 0u : (0xffffffffu << shift);
+    shift -= bits;
+    const int nb = 1 << bits;
+    for (int i = tid; i < nb; i += kThreads) hist[i] = 0;
     __syncthreads();
     const uint32_t prefix = s_prefix;
-    const uint32_t himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
     for (int i = tid; i < V; i += kThreads) {
       const uint32_t key = f2key(ldv(z, i));
-      if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+      if ((key & himask) == prefix) atomicAdd(&hist[(key >> shift) & static_cast<uint32_t>(nb - 1)], 1u);
     }
     __syncthreads();
-    if (tid == 0) {
-      unsigned int need = s_remaining;
-      int b = 255;
-      for (; b > 0; --b) {
-        if (hist[b] >= need) break;
-        need -= hist[b];
+    // thread t owns `per` consecutive bins, highest bins first; block-wide exclusive scan of the per-thread sums
+    const int per = (nb + kThreads - 1) / kThreads;
+    const int top = nb - 1 - tid * per;  // highest bin of this thread
+    unsigned int mine = 0;
+    for (int j = 0; j < per; ++j)
+      if (top - j >= 0) mine += hist[top - j];
+    unsigned int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    if (lane == 31) warp_cnt[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned int w = warp_cnt[lane];
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned int o = __shfl_up_sync(0xffffffffu, w, off);
+        if (lane >= off) w += o;
       }
-      s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
-      s_remaining = need;
+      warp_cnt[lane] = w;
+    }
+    __syncthreads();
+    const unsigned int before = (warp == 0 ? 0u : warp_cnt[warp - 1]) + (incl - mine);  // count in higher bins
+    const unsigned int need = s_remaining;
+    __syncthreads();
+    if (before < need && need <= before + mine) {  // exactly one thread: the threshold bin is one of its bins
+      unsigned int acc = before;
+      int bsel = top;
+      for (int j = 0; j < per; ++j) {
+        bsel = top - j;
+        if (acc + hist[bsel] >= need) break;
+        acc += hist[bsel];
+      }
+      s_prefix = prefix | (static_cast<uint32_t>(bsel) << shift);
+      s_remaining = need - acc;
+      s_above += acc;
+      s_pop = hist[bsel];
     }
     __syncthreads();
   }
-  const uint32_t kth = s_prefix;
+  // keys >= gather_from are candidates: everything above the threshold bin plus the bin itself
+  const uint32_t gather_from = s_prefix;
 
-  // ---- 2. gather candidates with key >= kth, then sort (key desc, index asc)
+  // ---- 2. gather the candidates, then sort (key desc, index asc)
   if (tid == 0) s_count = 0;
   __syncthreads();
   for (int i = tid; i < V; i += kThreads) {
     const uint32_t key = f2key(ldv(z, i));
-    if (key >= kth) {
+    if (key >= gather_from) {
       const unsigned int slot = atomicAdd(&s_count, 1u);
       if (slot < kCap) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(i));
     }
   }
   __syncthreads();
-  const int n = static_cast<int>(s_count < static_cast<unsigned int>(kCap) ? s_count : kCap);
+  int n = static_cast<int>(s_count < static_cast<unsigned int>(kCap) ? s_count : kCap);
   for (int i = n + tid; i < kCap; i += kThreads) cand[i] = 0ull;
   __syncthreads();
   // bitonic sort, descending, kCap elements (2 per thread)
@@ -128,6 +174,19 @@ sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int t
     }
   }
 
+  // the gathered set may extend below the k-th largest value: keep the first k and everything tied with the k-th
+  {
+    const uint32_t kth_key = static_cast<uint32_t>(cand[(k < n ? k : n) - 1] >> 32);
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    unsigned int local = 0;
+    for (int i = tid; i < n; i += kThreads)
+      if (static_cast<uint32_t>(cand[i] >> 32) >= kth_key) ++local;
+    if (local) atomicAdd(&s_count, local);
+    __syncthreads();
+    n = static_cast<int>(s_count);
+  }
+
   // ---- 3. softmax over candidates + inclusive scan (fixed tree) + top-p cut
   const float zmax = key2f(static_cast<uint32_t>(cand[0] >> 32));
   float e0 = 0.f, e1 = 0.f;
@@ -137,7 +196,6 @@ sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int t
     if (i1 < n) e1 = expf((key2f(static_cast<uint32_t>(cand[i1] >> 32)) - zmax) * inv_temp);
   }
   float incl = e0 + e1;  // thread total, then warp inclusive scan
-  const int lane = tid & 31, warp = tid >> 5;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
     const float o = __shfl_up_sync(0xffffffffu, incl, off);
