@@ -210,72 +210,3 @@ gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 }
 
 }  // namespace rlk
-
-namespace rlk {
-
-// ---------------------------------------------------------------------------------------------
-// Epilogue with coalesced output: the accumulator tile is converted to bf16 into a 128B-swizzled staging
-// tile in shared memory and written by four TMA bulk-tensor stores (64 columns x 128 rows each) instead of
-// 4096 scattered 16-byte stores.  Full 128-byte lines reach L2, and the M / N tails are clipped by the
-// tensor map.  Needs a 16-byte aligned C with a 16-byte row pitch; the launcher falls back to EpiStore otherwise.
-// ---------------------------------------------------------------------------------------------
-struct EpiStoreTma {
-  struct Params {
-    CUtensorMap tmap_c;  // bf16 [M, N], box 64 x 128, 128B swizzle
-    float alpha;
-  };
-  struct State {
-    uint8_t* staging;
-  };
-  static constexpr int kCommWarps = 0;
-  static constexpr int kStagingBytes = kBM * 256 * 2;  // one 128 x 256 bf16 tile
-
-  __device__ static void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-  __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
-  __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
-  __device__ static void start(const Params&, const GemmProblem&) {}
-  __device__ static void finish(const Params&, const GemmProblem&, uint32_t) {
-    if (threadIdx.x == 64) tma_store_wait<0>();  // the stores must have drained before the CTA's smem goes away
-  }
-
-  template <int BN>
-  __device__ static void tile(State& st, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
-    static_assert(BN == 256, "staging tile is 256 columns wide");
-    const int r = ((threadIdx.x >> 5) & 3) * 32 + (threadIdx.x & 31);  // row inside the tile = TMEM lane of this thread
-    // the previous tile's stores have finished READING the staging tile
-    if (threadIdx.x == 64) tma_store_wait_read<0>();
-    epi_bar();
-#pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
-      uint32_t t[32];
-      tmem_ld_32x32b_x32(acc + c, t);
-      tmem_ld_wait();
-      uint8_t* box = st.staging + (c >> 6) * (kBM * 128) + r * 128;  // 64-column box, 128 bytes per row
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(t[v * 8 + 2 * j]) * ep.alpha,
-                                                   __uint_as_float(t[v * 8 + 2 * j + 1]) * ep.alpha);
-          w[j] = *reinterpret_cast<uint32_t*>(&b);
-        }
-        const int chunk = ((c & 63) >> 3) + v;  // 16-byte chunk inside the 128-byte row
-        *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-    fence_proxy_async_smem();
-    epi_bar();
-    if (threadIdx.x == 64) {
-      const int m0 = row - r;  // first row of this CTA's tile
-#pragma unroll
-      for (int b = 0; b < BN / 64; ++b) {
-        if (n0 + b * 64 < p.N) tma_store_2d(&ep.tmap_c, st.staging + b * (kBM * 128), n0 + b * 64, m0);
-      }
-      tma_store_commit();
-    }
-  }
-};
-
-}  // namespace rlk

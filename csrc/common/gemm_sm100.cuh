@@ -146,12 +146,13 @@ __device__ __forceinline__ bool item_skipped(const GemmProblem& p, int m_tile) {
   return p.group_mode == 1 && p.tile_group[m_tile] < 0;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int STAGING = 0>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarrierOffset = STAGES * kStageBytes;
+  static constexpr int kStagingOffset = STAGES * kStageBytes;  // output staging for TMA-store epilogues
+  static constexpr int kBarrierOffset = kStagingOffset + STAGING;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base (u32), abort flag (u32)
   static constexpr int kBytes = kBarrierOffset + (2 * STAGES + 4) * 8 + 16;
   static constexpr int kDynamicBytes = kBytes + 1024;  // slack for manual 1024-byte alignment
@@ -196,9 +197,9 @@ constexpr int gemm_threads() {
 template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi>
 __global__ void __launch_bounds__(gemm_threads<Epi>(), 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const GemmProblem p, const typename Epi::Params ep, uint32_t* __restrict__ err,
+                  const GemmProblem p, const __grid_constant__ typename Epi::Params ep, uint32_t* __restrict__ err,
                   const uint32_t kernel_id) {
-  using L = GemmSmem<BN, STAGES>;
+  using L = GemmSmem<BN, STAGES, Epi::kStagingBytes>;
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
   constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
   static_assert(kTmemCols <= 256 || L::kDynamicBytes > 116 * 1024,
@@ -334,6 +335,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int buf = 0;
     uint32_t buf_phase = 0;
     typename Epi::State st;
+    if constexpr (Epi::kStagingBytes > 0) st.staging = smem + L::kStagingOffset;
     Epi::start(ep, p);
     for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
       const WorkItem w = decode_item(p, id);
@@ -454,6 +456,76 @@ struct EpiStore {
             crow[col0 + j] = x;
           }
         }
+      }
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// Epilogue with coalesced output: the accumulator tile is converted to bf16 into a 128B-swizzled staging
+// tile in shared memory, COLS columns at a time, and written by TMA bulk-tensor stores (64 columns x 128 rows
+// each) instead of thousands of scattered 16-byte stores.  Full 128-byte lines reach L2, and the M / N tails
+// are clipped by the tensor map.  Needs a 16-byte aligned C with a 16-byte row pitch; the launchers fall back to
+// EpiStore otherwise.  COLS = 256 stages a whole tile (64 KB), COLS = 128 half a tile (32 KB).
+// ---------------------------------------------------------------------------------------------
+template <int COLS>
+struct EpiStoreTma {
+  struct Params {
+    CUtensorMap tmap_c;  // bf16 [M, N], box 64 x 128, 128B swizzle
+    float alpha;
+  };
+  struct State {
+    uint8_t* staging;
+  };
+  static constexpr int kCommWarps = 0;
+  static constexpr int kStagingBytes = kBM * COLS * 2;
+
+  __device__ static void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+  __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
+  __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
+  __device__ static void start(const Params&, const GemmProblem&) {}
+  __device__ static void finish(const Params&, const GemmProblem&, uint32_t) {
+    if (threadIdx.x == 64) tma_store_wait<0>();  // the stores must have drained before the CTA's smem goes away
+  }
+
+  template <int BN>
+  __device__ static void tile(State& st, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
+    static_assert(BN % COLS == 0 && COLS % 64 == 0, "staging width must divide the tile width");
+    const int r = ((threadIdx.x >> 5) & 3) * 32 + (threadIdx.x & 31);  // row inside the tile = TMEM lane of this thread
+    const int m0 = row - r;                                             // first row of this CTA's tile
+#pragma unroll 1
+    for (int seg = 0; seg < BN; seg += COLS) {
+      // the previous stores have finished READING the staging tile
+      if (threadIdx.x == 64) tma_store_wait_read<0>();
+      epi_bar();
+#pragma unroll 1
+      for (int c = 0; c < COLS; c += 32) {
+        uint32_t t[32];
+        tmem_ld_32x32b_x32(acc + seg + c, t);
+        tmem_ld_wait();
+        uint8_t* box = st.staging + (c >> 6) * (kBM * 128) + r * 128;  // 64-column box, 128 bytes per row
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(t[v * 8 + 2 * j]) * ep.alpha,
+                                                     __uint_as_float(t[v * 8 + 2 * j + 1]) * ep.alpha);
+            w[j] = *reinterpret_cast<uint32_t*>(&b);
+          }
+          const int chunk = ((c & 63) >> 3) + v;  // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(box + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      epi_bar();
+      if (threadIdx.x == 64) {
+#pragma unroll
+        for (int b = 0; b < COLS / 64; ++b) {
+          if (n0 + seg + b * 64 < p.N) tma_store_2d(&ep.tmap_c, st.staging + b * (kBM * 128), n0 + seg + b * 64, m0);
+        }
+        tma_store_commit();
       }
     }
   }

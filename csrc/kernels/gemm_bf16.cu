@@ -36,7 +36,7 @@ void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stre
   const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, static_cast<uint64_t>(a.K) * b_stack, a.N, a.ldb, kBK, 64)
                               : make_tmap_2d_bf16(a.B, static_cast<uint64_t>(a.N) * b_stack, a.K, a.ldb, kBN, kBK);
   auto kernel = gemm_sm100_kernel<kBN, A_MN, B_MN, kStages, Epi>;
-  using L = GemmSmem<kBN, kStages>;
+  using L = GemmSmem<kBN, kStages, Epi::kStagingBytes>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -85,15 +85,27 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
 
 template <bool A_MN, bool B_MN>
 void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
+  if (!(a.cta_pair && a.group_mode == 0) && a.group_mode != 2) {
+    // single-CTA engine, bf16 output that TMA can address: half-tile staging (32 KB next to the 4-stage ring)
+    const bool tma_out = !a.out_fp32 && !a.accumulate && a.ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 &&
+                         !pair_tma_store_disabled();
+    if (tma_out) {
+      EpiStoreTma<128>::Params ep;
+      ep.tmap_c = make_tmap_2d_bf16(a.D, a.M, a.N, a.ldd, kBM, 64);
+      ep.alpha = a.alpha;
+      launch<A_MN, B_MN, EpiStoreTma<128>>(a, ep, stream);
+      return;
+    }
+  }
   if (a.cta_pair && a.group_mode == 0) {
     // bf16 output that TMA can address: stage the tile in shared memory and store full lines
     const bool tma_out = !a.out_fp32 && !a.accumulate && a.ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 &&
                          !pair_tma_store_disabled();
     if (tma_out) {
-      EpiStoreTma::Params ep;
+      EpiStoreTma<256>::Params ep;
       ep.tmap_c = make_tmap_2d_bf16(a.D, a.M, a.N, a.ldd, kBM, 64);
       ep.alpha = a.alpha;
-      launch_pair<A_MN, B_MN, EpiStoreTma, kPairStagesTma>(a, ep, stream);
+      launch_pair<A_MN, B_MN, EpiStoreTma<256>, kPairStagesTma>(a, ep, stream);
       return;
     }
     if (a.out_fp32) {

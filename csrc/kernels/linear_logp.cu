@@ -48,6 +48,7 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 struct EpiLogpStats {
   using Params = LogpFwdParams;
   static constexpr int kCommWarps = 0;
+  static constexpr int kStagingBytes = 0;
   struct State {
     float m2, s, t, zt;
     int tgt;  // local target column or -1
@@ -203,6 +204,7 @@ struct LogpDzParams {
 
 struct EpiLogpDz {
   static constexpr int kCommWarps = 0;
+  static constexpr int kStagingBytes = 0;
   using Params = LogpDzParams;
   struct State {
     float g, lse2;

@@ -57,6 +57,7 @@ struct EpiAgStore {
   using Store = EpiStore<__nv_bfloat16, false>;
   struct State {};
   static constexpr int kCommWarps = kCommThreads / 32;
+  static constexpr int kStagingBytes = 0;
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
@@ -121,6 +122,7 @@ struct EpiRsStore {
   using Params = RsParams;
   struct State {};
   static constexpr int kCommWarps = 0;
+  static constexpr int kStagingBytes = 0;
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
