@@ -347,3 +347,37 @@ def test_debug_bounds_build_compiles(tmp_path):
         capture_output=True, text=True, timeout=600,
     )
     assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_poly_exp2_coefficients_are_accurate_enough_for_bf16_probabilities():
+    """Host restatement of ``poly_exp2`` (csrc/common/ptx.cuh): round-to-nearest split through the 1.5 * 2^23 magic
+    constant, cubic on [-0.5, 0.5], exponent add.  Relative error must stay far below bf16 resolution (3.9e-3)."""
+    import re
+    import struct
+
+    root = __import__("os").path.dirname(__import__("os").path.dirname(__import__("os").path.abspath(__file__)))
+    src = open(__import__("os").path.join(root, "csrc", "common", "ptx.cuh")).read()
+    body = src[src.index("float poly_exp2(float x)"):]
+    coeffs = [float(c) for c in re.findall(r"(0\.\d+)f", body[: body.index("return")])]
+    assert len(coeffs) == 4, coeffs
+    c3, c2, c1, c0 = coeffs
+
+    def f32(v):
+        return struct.unpack("f", struct.pack("f", v))[0]
+
+    def poly_exp2(x):
+        x = max(x, -126.0)
+        t = f32(x + 12582912.0)
+        f = f32(x - f32(t - 12582912.0))
+        p = f32(f32(f * c3) + c2)
+        p = f32(f32(p * f) + c1)
+        p = f32(f32(p * f) + c0)
+        bits = struct.unpack("I", struct.pack("f", p))[0] + ((struct.unpack("I", struct.pack("f", t))[0] << 23) & 0xFFFFFFFF)
+        return struct.unpack("f", struct.pack("I", bits & 0xFFFFFFFF))[0]
+
+    worst = 0.0
+    for i in range(4001):
+        x = -40.0 * i / 4000.0
+        worst = max(worst, abs(poly_exp2(x) / 2.0 ** x - 1.0))
+    assert worst < 2e-4, worst
+    assert abs(poly_exp2(0.0) - 1.0) < 1e-4 and abs(poly_exp2(-1.0) - 0.5) < 1e-4
