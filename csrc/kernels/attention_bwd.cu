@@ -21,6 +21,26 @@
 
 namespace rlk {
 
+#ifdef RLK_ATTN_PROFILE
+// Phase timing of one compute thread of the dQ kernel (debug builds only), cycles per phase summed over its tiles.
+__device__ unsigned long long g_attn_bwd_prof[16];
+#define BPROF_DECL unsigned long long prof_t = clock64(); const bool prof_on = (blockIdx.x == gridDim.x / 2) && threadIdx.x == 64
+#define BPROF(slot)                                     \
+  if (prof_on) {                                        \
+    const unsigned long long now = clock64();           \
+    atomicAdd(&g_attn_bwd_prof[slot], now - prof_t);    \
+    prof_t = now;                                       \
+  }
+void attention_bwd_profile_read(unsigned long long* out) {
+  cudaMemcpyFromSymbol(out, g_attn_bwd_prof, sizeof(unsigned long long) * 16);
+  unsigned long long z[16] = {0};
+  cudaMemcpyToSymbol(g_attn_bwd_prof, z, sizeof(z));
+}
+#else
+#define BPROF_DECL
+#define BPROF(slot)
+#endif
+
 namespace {
 
 constexpr int kD = 128;
@@ -248,6 +268,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // Two groups of four warps: group g handles the tiles j = g, g + 2, ... (TMEM / smem buffer g), so that the
     // exponentials of one tile overlap the TMEM loads and the MMAs of the next.
     const int group = (warp - 2) >> 2;
+    BPROF_DECL;
     for (int j = group; j < n_tiles; j += 2) {
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
@@ -256,7 +277,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       int limit = (is_self ? sd.sk_len : sd.pk_len) - key0;
       if (is_self && causal) limit = min(limit, qi - key0 + 1);
       if (!row_ok) limit = 0;
+      BPROF(0);
       mbar_wait(&s_full[b], ph, abort_flag, err, 210, 6);
+      BPROF(1);
       tc_fence_after();
       uint8_t* dsrow = smem + DqSmem::kDS + b * kAtom128 + r * 128;
       uint32_t ts[64], tp[64];
@@ -267,7 +290,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(&s_empty[b]);  // S / dP are in registers: the TMEM buffers are free for tile j + 2
+      BPROF(2);
       mbar_wait(&ds_empty[b], ph ^ 1, abort_flag, err, 210, 7);  // dS buffer b free (dQ MMA of tile j-2 done)
+      BPROF(3);
       if (__any_sync(0xffffffffu, limit < TK)) {
         dq_row<true>(ts, tp, limit, scale_log2e, lse2, dlt, dsrow, r);
       } else {
@@ -275,6 +300,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(&ds_full[b]);
+      BPROF(4);
     }
     // wait for the last dQ MMA, then write dQ * scale
     if (n_tiles >= 1) {

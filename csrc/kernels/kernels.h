@@ -317,6 +317,7 @@ void moe_rowdot(const __nv_bfloat16* a, long long ld_a, const __nv_bfloat16* b, 
 #ifdef RLK_ATTN_PROFILE
 void attention_profile_read(unsigned long long* out);
 void attention_profile_reset();
+void attention_bwd_profile_read(unsigned long long* out);
 #endif
 
 // ---- tracing (trace.cu): out[slot] = %globaltimer in stream order

@@ -40,9 +40,8 @@ __device__ __forceinline__ void comm_bar_sync() { asm volatile("bar.sync 2, 64;"
 // all-gather -> GEMM
 // ---------------------------------------------------------------------------------------------
 struct AgParams {
-  __nv_bfloat16* C;
-  long long ldc;
-  const __nv_bfloat16* x_local;  // [rows_local, K]
+  EpiStoreTma<128>::Params store;  // output tensor map (bf16 [M, N]) + alpha, used by the staged TMA-store epilogue
+  const __nv_bfloat16* x_local;    // [rows_local, K]
   long long ldx;
   int rows_local;
   int k;        // elements per row (multiple of 8 * chunks)
@@ -54,20 +53,19 @@ struct AgParams {
 
 struct EpiAgStore {
   using Params = AgParams;
-  using Store = EpiStore<__nv_bfloat16, false>;
-  struct State {};
+  using Store = EpiStoreTma<128>;  // half-tile staging + TMA bulk stores: full lines to L2
+  using State = Store::State;
   static constexpr int kCommWarps = kCommThreads / 32;
-  static constexpr int kStagingBytes = 0;
+  static constexpr int kStagingBytes = Store::kStagingBytes;
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
-  __device__ static void finish(const Params&, const GemmProblem&, uint32_t) {}
+  __device__ static void finish(const Params& ep, const GemmProblem& p, uint32_t id) { Store::finish(ep.store, p, id); }
   __device__ static void start(const Params&, const GemmProblem&) {}
 
   template <int BN>
-  __device__ static void tile(State&, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
-    Store::State st;
-    Store::template tile<BN>(st, Store::Params{ep.C, ep.ldc, 1.f}, p, acc, row, n0);
+  __device__ static void tile(State& st, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
+    Store::template tile<BN>(st, ep.store, p, acc, row, n0);
   }
 
   // Copy units (tile, chunk) are striped over the CTAs; each unit goes to every rank, own rank first.
@@ -120,49 +118,72 @@ struct RsParams {
 
 struct EpiRsStore {
   using Params = RsParams;
-  struct State {};
+  struct State {
+    uint8_t* staging;
+  };
   static constexpr int kCommWarps = 0;
-  static constexpr int kStagingBytes = 0;
+  static constexpr int kSegCols = 128;                      // columns staged at a time
+  static constexpr int kStagingBytes = kBM * kSegCols * 2;  // 32 KB next to the 4-stage ring
 
   __device__ static void begin_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void end_item(State&, const Params&, const GemmProblem&, const WorkItem&, int) {}
   __device__ static void start(const Params&, const GemmProblem&) {}
 
+  // The partial tile goes to the rank that owns its rows.  Accumulator rows live one per thread, so writing them
+  // out directly would send 16-byte pieces of 128 different rows over NVLink per instruction; instead the tile is
+  // converted to bf16 into a swizzled shared-memory buffer, 128 columns at a time, and every warp then stores whole
+  // 256-byte row segments (two rows per instruction), which reach the link as full lines.
   template <int BN>
-  __device__ static void tile(State&, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
-    const int owner = row / ep.rows_local;
-    const int lrow = row - owner * ep.rows_local;
-    __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(ep.partial.p[owner]) +
-                          (static_cast<long long>(ep.rank) * ep.rows_local + lrow) * p.N;
+  __device__ static void tile(State& st, const Params& ep, const GemmProblem& p, uint32_t acc, int row, int n0) {
+    const int warp = (threadIdx.x >> 5) - 2, lane = threadIdx.x & 31;
+    const int r = ((threadIdx.x >> 5) & 3) * 32 + lane;  // accumulator row of this thread
+    const int m0 = row - r;
+    const int owner = m0 / ep.rows_local;
+    __nv_bfloat16* dbase = static_cast<__nv_bfloat16*>(ep.partial.p[owner]) +
+                           (static_cast<long long>(ep.rank) * ep.rows_local + (m0 - owner * ep.rows_local)) * p.N;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(acc + c, r);
-      tmem_ld_wait();
-      const int col0 = n0 + c;
-      if (col0 >= p.N) continue;
-      if (col0 + 32 <= p.N) {
-        uint4* dst = reinterpret_cast<uint4*>(drow + col0);
+    for (int seg = 0; seg < BN; seg += kSegCols) {
+      epi_bar_sync();  // the previous segment has been copied out of the staging buffer
+#pragma unroll 1
+      for (int c = 0; c < kSegCols; c += 32) {
+        uint32_t t[32];
+        tmem_ld_32x32b_x32(acc + seg + c, t);
+        tmem_ld_wait();
+        uint8_t* srow = st.staging + r * (kSegCols * 2);  // 256 bytes per row, 16 chunks of 16 bytes
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(t[v * 8 + 2 * j]), __uint_as_float(t[v * 8 + 2 * j + 1]));
             w[j] = *reinterpret_cast<uint32_t*>(&b);
           }
-          dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          const int chunk = (c >> 3) + v;
+          *reinterpret_cast<uint4*>(srow + ((chunk ^ (r & 15)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-      } else {
-        for (int j = 0; j < 32 && col0 + j < p.N; ++j) drow[col0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+      }
+      epi_bar_sync();
+      // warp w copies rows w*32 .. w*32+31, two rows per instruction (16 lanes x 16 bytes each)
+      const int sub = lane >> 4, chunk = lane & 15;
+      const int col = n0 + seg + chunk * 8;
+#pragma unroll 4
+      for (int i = 0; i < 32; i += 2) {
+        const int rr = warp * 32 + i + sub;
+        const uint4 q = *reinterpret_cast<const uint4*>(st.staging + rr * (kSegCols * 2) + ((chunk ^ (rr & 15)) << 4));
+        __nv_bfloat16* dst = dbase + static_cast<long long>(rr) * p.N + col;
+        if (col + 8 <= p.N) {
+          *reinterpret_cast<uint4*>(dst) = q;
+        } else {
+          const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&q);
+          for (int e = 0; e < 8 && col + e < p.N; ++e) dst[e] = h[e];
+        }
       }
     }
     __threadfence_system();
     epi_bar_sync();
     if (threadIdx.x == 64) {
       const int tiles_local = ep.rows_local / kBM;
-      const int m_tile = row / kBM;
-      const int lt = m_tile - owner * tiles_local;
+      const int lt = m0 / kBM - owner * tiles_local;
       unsigned int* ctr = static_cast<unsigned int*>(ep.counters.p[owner]) + lt * p.tiles_n + n0 / BN;
       asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
     }
@@ -247,7 +268,7 @@ void launch(const void* a_base, int M, int K, long long lda, const void* b_base,
   const CUtensorMap ta = make_tmap_2d_bf16(a_base, M, K, lda, kBM, kBK);
   const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(b_base, K, N, ldb, kBK, 64) : make_tmap_2d_bf16(b_base, N, K, ldb, kBN, kBK);
   auto kernel = gemm_sm100_kernel<kBN, false, B_MN, kStages, Epi>;
-  using L = GemmSmem<kBN, kStages>;
+  using L = GemmSmem<kBN, kStages, Epi::kStagingBytes>;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
@@ -269,8 +290,8 @@ void tp_ag_gemm(const TpAgGemmArgs& a, cudaStream_t stream) {
   p.a_ready_target = a.epoch * static_cast<unsigned int>(a.chunks);
   p.a_wait_ns = a.wait_ns;
   AgParams ep;
-  ep.C = a.C;
-  ep.ldc = a.ldc;
+  ep.store.tmap_c = make_tmap_2d_bf16(a.C, M, a.N, a.ldc, kBM, 64);
+  ep.store.alpha = 1.f;
   ep.x_local = a.x_local;
   ep.ldx = a.ldx;
   ep.rows_local = a.rows_local;

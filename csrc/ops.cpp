@@ -149,6 +149,7 @@ Tensor tp_ag_gemm(const Tensor& x_local, const Tensor& b, bool b_mn, int64_t ran
   TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "rl_engine.tp_ag_gemm: contraction sizes differ");
   TORCH_CHECK(rows > 0 && rows % 128 == 0, "rl_engine.tp_ag_gemm: local rows must be a positive multiple of 128");
   TORCH_CHECK(chunks >= 1 && K % (8 * chunks) == 0, "rl_engine.tp_ag_gemm: K must be a multiple of 8 * chunks");
+  TORCH_CHECK(N % 8 == 0, "rl_engine.tp_ag_gemm: N must be a multiple of 8 (the output is written by TMA)");
   TORCH_CHECK(x_local.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(x_local.data_ptr()) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
               "rl_engine.tp_ag_gemm: operands must be 16-byte aligned with row pitch % 8 == 0");
@@ -1078,6 +1079,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     std::vector<unsigned long long> v(16);
     rlk::attention_profile_read(v.data());
     rlk::attention_profile_reset();
+    return v;
+  });
+  m.def("attention_bwd_profile", [] {
+    std::vector<unsigned long long> v(16);
+    rlk::attention_bwd_profile_read(v.data());
     return v;
   });
 #endif
