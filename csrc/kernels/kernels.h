@@ -365,6 +365,10 @@ struct TpGemmRsArgs {
 };
 void tp_gemm_rs(const TpGemmRsArgs& a, cudaStream_t stream);
 
+// Dispatch plan on the device: slot of every assignment, token of every slot (src_row must be pre-filled with -1),
+// expert of every 128-row tile, padded expert offsets [E + 1] and counts [E].  chunk_hist: scratch [ceil(A / 256), E].
+void moe_build_plan(const int* idx, int assignments, int k, int experts, int num_slots, int unused_group, int* chunk_hist,
+                    int* offsets, int* counts, int* tile_group, int* slot, int* src_row, cudaStream_t stream);
 // expert parallelism over peer-mapped buffers (dst / src / b hold one base pointer per rank)
 void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int* token, const int* dest_rank,
                            const int* dest_slot, const float* scale, void* const* dst, int world, long long ld_dst,

@@ -230,6 +230,77 @@ __global__ void moe_combine_peer_kernel(PeerBases src, long long ld_src, const i
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Dispatch plan in three small kernels (instead of a dozen framework index ops): assignments are
+// grouped expert by expert, every expert block padded to 128 rows, order inside an expert = assignment
+// order (so every later summation order is fixed).
+//   count : per 256-assignment chunk, histogram over experts                     -> chunk_hist [chunks, E]
+//   scan  : per expert, exclusive prefix over the chunks (in place) and totals; padded expert offsets;
+//           expert id of every 128-row tile (unused tail tiles get `unused_group`)
+//   place : slot of every assignment = offsets[e] + prefix[chunk, e] + rank inside the chunk;
+//           src_row[slot] = token
+// ---------------------------------------------------------------------------------------------
+constexpr int kPlanChunk = 256;
+
+__global__ void moe_plan_count_kernel(const int* __restrict__ idx, int assignments, int experts, int* __restrict__ chunk_hist) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int a = blockIdx.x * kPlanChunk + threadIdx.x;
+  if (a < assignments) atomicAdd(&hist[idx[a]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) chunk_hist[blockIdx.x * experts + e] = hist[e];
+}
+
+__global__ void moe_plan_scan_kernel(int* __restrict__ chunk_hist, int chunks, int experts, int num_tiles, int unused_group,
+                                     int* __restrict__ offsets, int* __restrict__ counts, int* __restrict__ tile_group) {
+  extern __shared__ int off_s[];  // experts + 1
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const int v = chunk_hist[c * experts + e];
+      chunk_hist[c * experts + e] = run;  // assignments of this expert in earlier chunks
+      run += v;
+    }
+    counts[e] = run;
+    const int blocks = run > 0 ? (run + 127) / 128 : 1;
+    off_s[e + 1] = blocks * 128;  // padded size, turned into offsets below
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    off_s[0] = 0;
+    for (int e = 0; e < experts; ++e) off_s[e + 1] += off_s[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = off_s[e];
+  for (int t = threadIdx.x; t < num_tiles; t += blockDim.x) {
+    const int row = t * 128;
+    int lo = 0, hi = experts;  // first expert whose end is beyond `row`
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (off_s[mid + 1] > row) hi = mid;
+      else lo = mid + 1;
+    }
+    tile_group[t] = lo < experts ? lo : unused_group;
+  }
+}
+
+__global__ void moe_plan_place_kernel(const int* __restrict__ idx, int assignments, int k, int experts,
+                                      const int* __restrict__ chunk_prefix, const int* __restrict__ offsets,
+                                      int* __restrict__ slot, int* __restrict__ src_row) {
+  __shared__ int e_s[kPlanChunk];
+  const int a = blockIdx.x * kPlanChunk + threadIdx.x;
+  const int e = a < assignments ? idx[a] : -1;
+  e_s[threadIdx.x] = e;
+  __syncthreads();
+  if (a >= assignments) return;
+  int rank = 0;
+  for (int j = 0; j < threadIdx.x; ++j) rank += (e_s[j] == e) ? 1 : 0;
+  const int s = offsets[e] + chunk_prefix[blockIdx.x * experts + e] + rank;
+  slot[a] = s;
+  src_row[s] = a / k;
+}
+
 PeerBases make_bases(void* const* p, int world) {
   PeerBases b;
   for (int r = 0; r < 8; ++r) b.p[r] = r < world ? p[r] : nullptr;
@@ -237,6 +308,16 @@ PeerBases make_bases(void* const* p, int world) {
 }
 
 }  // namespace
+
+void moe_build_plan(const int* idx, int assignments, int k, int experts, int num_slots, int unused_group, int* chunk_hist,
+                    int* offsets, int* counts, int* tile_group, int* slot, int* src_row, cudaStream_t stream) {
+  if (assignments <= 0) return;
+  const int chunks = (assignments + kPlanChunk - 1) / kPlanChunk;
+  moe_plan_count_kernel<<<chunks, kPlanChunk, experts * sizeof(int), stream>>>(idx, assignments, experts, chunk_hist);
+  moe_plan_scan_kernel<<<1, 512, (experts + 1) * sizeof(int), stream>>>(chunk_hist, chunks, experts, num_slots / 128,
+                                                                       unused_group, offsets, counts, tile_group);
+  moe_plan_place_kernel<<<chunks, kPlanChunk, 0, stream>>>(idx, assignments, k, experts, chunk_hist, offsets, slot, src_row);
+}
 
 void moe_scatter_rows_peer(const __nv_bfloat16* src, long long ld_src, const int* token, const int* dest_rank,
                            const int* dest_slot, const float* scale, void* const* dst, int world, long long ld_dst,

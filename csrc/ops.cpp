@@ -297,6 +297,32 @@ std::vector<Tensor> moe_topk(const Tensor& logits, int64_t k) {
   return {idx, w};
 }
 
+// (slot [T, k], src_row [S], tile_group [S / 128], offsets [E + 1], counts [E]) for expert ids `idx` int32 [T, k].
+std::vector<Tensor> moe_build_plan(const Tensor& idx, int64_t experts, int64_t num_slots, int64_t unused_group) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == torch::kInt32 && idx.is_contiguous() && idx.dim() == 2, "moe_build_plan: idx int32 [T, k]");
+  TORCH_CHECK(experts >= 1 && experts <= 4096 && num_slots % 128 == 0, "moe_build_plan: 1 <= experts <= 4096, num_slots % 128 == 0");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  const int64_t a = idx.numel(), k = idx.size(1);
+  // every expert block is padded to a multiple of 128 rows (empty experts keep one block): at most a + 128 * experts rows
+  TORCH_CHECK(num_slots >= (a + 128 * experts) / 128 * 128, "moe_build_plan: num_slots is below the worst-case padded size");
+  auto opt = idx.options();
+  Tensor slot = torch::empty({idx.size(0), k}, opt);
+  Tensor src_row = torch::full({num_slots}, -1, opt);
+  Tensor tile_group = torch::empty({num_slots / 128}, opt);
+  Tensor offsets = torch::empty({experts + 1}, opt);
+  Tensor counts = torch::empty({experts}, opt);
+  const int64_t chunks = (a + 255) / 256;
+  Tensor scratch = torch::empty({std::max<int64_t>(chunks, 1) * experts}, opt);
+  if (a > 0) {
+    rlk::moe_build_plan(idx.data_ptr<int>(), static_cast<int>(a), static_cast<int>(k), static_cast<int>(experts),
+                        static_cast<int>(num_slots), static_cast<int>(unused_group), scratch.data_ptr<int>(),
+                        offsets.data_ptr<int>(), counts.data_ptr<int>(), tile_group.data_ptr<int>(), slot.data_ptr<int>(),
+                        src_row.data_ptr<int>(), stream_of(idx));
+    after_launch(3);
+  }
+  return {slot, src_row, tile_group, offsets, counts};
+}
+
 void check_bf16_rows(const Tensor& t, const char* n) {
   check_rowmajor(t, n);
   TORCH_CHECK(t.scalar_type() == torch::kBFloat16 && t.size(1) % 8 == 0 && t.stride(0) % 8 == 0 &&
@@ -1096,6 +1122,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_ag_gemm", rlk::traced("rlk::tp_ag_gemm", &tp_ag_gemm));
   m.def("tp_gemm_rs", rlk::traced("rlk::tp_gemm_rs", &tp_gemm_rs));
   m.def("moe_topk", rlk::traced("rlk::moe_topk", &moe_topk));
+  m.def("moe_build_plan", rlk::traced("rlk::moe_build_plan", &moe_build_plan));
   m.def("moe_gather_rows", rlk::traced("rlk::moe_gather_rows", &moe_gather_rows), py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
         py::arg("dst_ptr") = 0, py::arg("dst_ld") = 0);
   m.def("moe_combine", rlk::traced("rlk::moe_combine", &moe_combine), py::arg("src"), py::arg("src_ptr"), py::arg("src_ld"), py::arg("hidden"), py::arg("slot"),

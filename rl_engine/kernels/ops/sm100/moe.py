@@ -58,9 +58,17 @@ class DispatchPlan:
 
 
 def build_dispatch_plan(expert_idx: torch.Tensor, num_experts: int) -> DispatchPlan:
-    """Index plumbing (no host synchronisation): slot tables for ``expert_idx`` int32 ``[T, k]``."""
+    """Index plumbing (no host synchronisation): slot tables for ``expert_idx`` int32 ``[T, k]``.
+
+    On the GPU three small kernels (``moe_build_plan``: chunk histograms, per-expert prefix + padded offsets, placement)
+    replace the dozen framework index ops of the portable path below; both produce identical tables."""
     t, k = expert_idx.shape
     dev = expert_idx.device
+    if expert_idx.is_cuda and expert_idx.dtype == torch.int32 and t * k > 0:
+        num_slots = (t * k + num_experts * BLOCK + BLOCK - 1) // BLOCK * BLOCK
+        slot, src_row, tile_group, offsets, counts = require_ext().moe_build_plan(
+            expert_idx.contiguous(), int(num_experts), int(num_slots), int(num_experts - 1))
+        return DispatchPlan(slot, src_row, tile_group, offsets, counts.long(), num_slots)
     flat = expert_idx.reshape(-1).long()
     order = torch.argsort(flat, stable=True)                 # assignments by (expert, assignment id)
     counts = torch.bincount(flat, minlength=num_experts)

@@ -145,3 +145,19 @@ def test_qwen3_style_moe_model_grpo_steps():
         assert float(flat_grad[off:off + n].float().abs().sum()) > 0, f"no gradient reached {name}"
     assert type(kernel_registry.get_op("moe")).__name__ == "FusedMoESM100Op"
     check_device_errors(0)
+
+
+def test_device_dispatch_plan_matches_portable_plan():
+    """The three-kernel plan builder must reproduce the framework-op plan exactly (same slots, same padding)."""
+    from rl_engine.kernels.ops.sm100 import moe
+
+    g = torch.Generator(device=DEV).manual_seed(9)
+    for t, k, e in ((700, 2, 6), (4096, 8, 128), (33, 1, 4), (1000, 4, 64)):
+        idx = torch.stack([torch.randperm(e, device=DEV, generator=g)[:k] for _ in range(t)]).to(torch.int32)
+        if e > 3:
+            idx[idx == 3] = 0  # an expert that receives nothing keeps one padded block
+        fast = moe.build_dispatch_plan(idx, e)
+        slow = moe.build_dispatch_plan(idx.cpu(), e)
+        assert torch.equal(fast.slot.cpu(), slow.slot) and torch.equal(fast.src_row.cpu(), slow.src_row)
+        assert torch.equal(fast.offsets.cpu(), slow.offsets) and torch.equal(fast.counts.cpu(), slow.counts)
+        assert torch.equal(fast.tile_group.cpu(), slow.tile_group) and fast.num_slots == slow.num_slots
