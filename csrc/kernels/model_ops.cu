@@ -355,6 +355,46 @@ __global__ void rope_kernel(const T* __restrict__ x, long long ldt, const long l
   }
 }
 
+// bf16 fast path: one thread rotates 8 element pairs (16-byte loads and stores, float4 cos / sin).
+__global__ void rope_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, long long ldt, const long long* __restrict__ pos,
+                                     const float* __restrict__ cs, const float* __restrict__ sn,
+                                     __nv_bfloat16* __restrict__ out, long long ldo, long long tokens, int heads, int D,
+                                     float sign) {
+  const int half = D / 2;
+  const int vec_per_head = half / 8;  // threads per (token, head)
+  const long long total = tokens * heads * vec_per_head;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(idx % vec_per_head);
+    const long long th = idx / vec_per_head;
+    const int h = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    const long long p = pos[t];
+    const float4* c4 = reinterpret_cast<const float4*>(cs + p * half + v * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sn + p * half + v * 8);
+    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float s[8] = {s0.x * sign, s0.y * sign, s0.z * sign, s0.w * sign, s1.x * sign, s1.y * sign, s1.z * sign, s1.w * sign};
+    const __nv_bfloat16* src = x + t * ldt + static_cast<long long>(h) * D + v * 8;
+    __nv_bfloat16* dst = out + t * ldo + static_cast<long long>(h) * D + v * 8;
+    const uint4 qa = *reinterpret_cast<const uint4*>(src);
+    const uint4 qb = *reinterpret_cast<const uint4*>(src + half);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&qa);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&qb);
+    uint4 oa, ob;
+    __nv_bfloat162* ra = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* rb = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = __bfloat1622float2(pa[i]), b = __bfloat1622float2(pb[i]);
+      ra[i] = __floats2bfloat162_rn(a.x * c[2 * i] - b.x * s[2 * i], a.y * c[2 * i + 1] - b.y * s[2 * i + 1]);
+      rb[i] = __floats2bfloat162_rn(b.x * c[2 * i] + a.x * s[2 * i], b.y * c[2 * i + 1] + a.y * s[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(dst) = oa;
+    *reinterpret_cast<uint4*>(dst + half) = ob;
+  }
+}
+
 // -------------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ table, long long ldw,
@@ -527,6 +567,15 @@ void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, c
                 void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream) {
   if (tokens <= 0) return;
   const int threads = 256;
+  const bool vec_ok = dtype == 1 && D % 16 == 0 && ldt % 8 == 0 && ldo % 8 == 0 &&
+                      (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(cos_t) & 15u) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15u) == 0;
+  if (vec_ok) {
+    rope_bf16_vec_kernel<<<grid_for(tokens * heads * (D / 16), threads), threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ldt, pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(out), ldo, tokens, heads, D,
+        inverse ? -1.f : 1.f);
+    return;
+  }
   const int grid = grid_for(tokens * heads * (D / 2), threads);
   RLK_DISPATCH_T(dtype, {
     rope_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), ldt, pos, cos_t, sin_t,

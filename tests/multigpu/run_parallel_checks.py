@@ -129,7 +129,7 @@ def main() -> None:
     x = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
     dout = torch.randn(T, H, device=dev, generator=gx).to(torch.bfloat16)
     el = E // world
-    ctx = ExpertParallelContext(H, E, K, max_tokens=400, group=dist.group.WORLD, device=dev)
+    ctx = ExpertParallelContext(H, E, K, max_tokens=300 + 17 * world, group=dist.group.WORLD, device=dev)
     ep_op = ExpertParallelMoE(ctx)
     xe = x.clone().requires_grad_(True)
     re_ = router.clone().requires_grad_(True)
