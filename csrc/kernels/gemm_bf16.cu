@@ -85,13 +85,14 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
 
 template <bool A_MN, bool B_MN>
 void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
-  if (!(a.cta_pair && a.group_mode == 0) && a.group_mode != 2) {
+  if (!(a.cta_pair && a.group_mode == 0)) {
     // single-CTA engine, bf16 output that TMA can address: half-tile staging (32 KB next to the 4-stage ring)
     const bool tma_out = !a.out_fp32 && !a.accumulate && a.ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 &&
                          !pair_tma_store_disabled();
     if (tma_out) {
       EpiStoreTma<128>::Params ep;
-      ep.tmap_c = make_tmap_2d_bf16(a.D, a.M, a.N, a.ldd, kBM, 64);
+      // grouped-K stacks one [M, N] block per group along the rows of D
+      ep.tmap_c = make_tmap_2d_bf16(a.D, a.group_mode == 2 ? static_cast<uint64_t>(a.M) * a.num_groups : a.M, a.N, a.ldd, kBM, 64);
       ep.alpha = a.alpha;
       launch<A_MN, B_MN, EpiStoreTma<128>>(a, ep, stream);
       return;
