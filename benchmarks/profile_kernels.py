@@ -135,6 +135,63 @@ def case_tp_gemm_rs():
             "note": "world = 1: one partial slab, written by the epilogue and summed by the in-kernel reduce phase"}
 
 
+def case_zero1_step():
+    """Fused reduce-scatter + AdamW + all-gather kernel on ONE rank (the peer lists hold this GPU's own buffers)."""
+    from rl_engine.kernels.ops.base import require_ext
+    from rl_engine.parallel.symmetric import SymmetricMemory
+
+    ext = require_ext()
+    n = 1 << 28  # 268 M parameters: 0.5 GB of bf16 params + grads, 3 GB of fp32 state
+    mem = SymmetricMemory(4 * n + (1 << 20))
+    params, grads = mem.alloc((n,), torch.bfloat16), mem.alloc((n,), torch.bfloat16)
+    params.local.normal_()
+    grads.local.normal_()
+    m, v, master = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), params.local.float()
+    step = [0]
+
+    def run():
+        step[0] += 1
+        ext.zero1_fused_step(grads.ptrs, params.ptrs, 0, n, m, v, master, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0)
+
+    ms = timed(run)
+    return {"flops": 0.0, "bytes": n * (2.0 + 2.0 + 3 * 4 * 2), "ms": ms, "shape": [n],
+            "note": "world = 1; bytes = grad read + param write + fp32 master/m/v read and write"}
+
+
+def case_cast_broadcast():
+    from rl_engine.kernels.ops.base import require_ext
+    from rl_engine.parallel.symmetric import SymmetricMemory
+
+    ext = require_ext()
+    n = 1 << 28
+    mem = SymmetricMemory(2 * n + (1 << 20))
+    window = mem.alloc((n,), torch.bfloat16)
+    src = torch.randn(n, device="cuda")
+    ms = timed(lambda: ext.cast_broadcast(src, window.ptrs, 1))
+    return {"flops": 0.0, "bytes": n * 6.0, "ms": ms, "shape": [n], "note": "world = 1: fp32 read, bf16 write into the local window"}
+
+
+def case_moe_layer():
+    """One Qwen3-30B-A3B-shaped MoE layer, forward + backward, single GPU (all 128 experts local)."""
+    from rl_engine.kernels.ops.sm100.moe import FusedMoESM100Op
+
+    e, k, h, f, t = 128, 8, 2048, 768, 8192
+    x = rand((t, h)).requires_grad_(True)
+    router = rand((e, h), 1 / 45, 1).requires_grad_(True)
+    w1 = rand((e * 2 * f, h), 0.02, 2).requires_grad_(True)
+    w2 = rand((e * h, f), 0.02, 3).requires_grad_(True)
+    do = rand((t, h), 1.0, 4)
+    op = FusedMoESM100Op()
+
+    def run():
+        x.grad = router.grad = w1.grad = w2.grad = None
+        op(x, router, w1, w2, k).backward(do)
+
+    ms = timed(run)
+    return {"flops": 3.0 * 2.0 * t * k * (h * 2 * f + f * h), "bytes": 0.0, "ms": ms, "shape": [t, h, e, k, f],
+            "note": "router + top-8 + plan kernels + gather + grouped GEMMs + SwiGLU + combine, forward and backward"}
+
+
 def case_linear_logp():
     from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
 

@@ -128,35 +128,112 @@ zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int world, long long lo
   }
 }
 
-// out[i] = sum_r src_r[i]; SRC bf16 or float, OUT bf16 or float; n multiple of 8 for the vector path.
-template <typename TS, typename TO>
-__global__ void peer_sum_kernel(PeerPtrs srcs, int world, long long n, TO* __restrict__ out) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float acc = 0.f;
-    for (int r = 0; r < world; ++r) {
-      if constexpr (sizeof(TS) == 2) acc += __bfloat162float(static_cast<const __nv_bfloat16*>(srcs.p[r])[i]);
-      else acc += static_cast<const float*>(srcs.p[r])[i];
+// Eight consecutive elements of T (float, bf16 or half) <-> eight floats, by 16- or 32-byte vector accesses.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    unpack8(*reinterpret_cast<const uint4*>(p), f);
+  } else {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __half22float2(h[j]);
+      f[2 * j] = x.x;
+      f[2 * j + 1] = x.y;
     }
-    if constexpr (sizeof(TO) == 2) out[i] = __float2bfloat16_rn(acc);
-    else out[i] = acc;
   }
 }
 
-// dst_r[i] = cast(src[i]) for every peer r.  src dtype code / dst dtype code: 0 f32, 1 bf16, 2 f16.
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    *reinterpret_cast<uint4*>(p) = pack8(f);
+  } else {
+    uint4 q;
+    __half2* h = reinterpret_cast<__half2*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float load1(const T* p) {
+  if constexpr (sizeof(T) == 4) return *p;
+  else if constexpr (std::is_same<T, __nv_bfloat16>::value) return __bfloat162float(*p);
+  else return __half2float(*p);
+}
+
+template <typename T>
+__device__ __forceinline__ void store1(T* p, float x) {
+  if constexpr (sizeof(T) == 4) *p = x;
+  else if constexpr (std::is_same<T, __nv_bfloat16>::value) *p = __float2bfloat16_rn(x);
+  else *p = __float2half_rn(x);
+}
+
+// out[i] = sum_r src_r[i]; SRC bf16 or float, OUT bf16 or float.  ``n8`` groups of eight elements go through the
+// vector path, two groups per thread and iteration so that 2 * world independent 16-byte loads are in flight per
+// thread; the last n - 8 * n8 elements are scalar.  The host passes n8 = 0 unless every pointer is 16-byte aligned.
+template <typename TS, typename TO>
+__global__ void peer_sum_kernel(PeerPtrs srcs, int world, long long n, long long n8, TO* __restrict__ out) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (long long i = tid; i < n8; i += 2 * stride) {
+    const long long i2 = i + stride;
+    const bool two = i2 < n8;
+    float acc0[8] = {}, acc1[8] = {};
+    for (int r = 0; r < world; ++r) {
+      float f0[8], f1[8] = {};
+      load8(static_cast<const TS*>(srcs.p[r]) + i * 8, f0);
+      if (two) load8(static_cast<const TS*>(srcs.p[r]) + i2 * 8, f1);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc0[j] += f0[j];
+        acc1[j] += f1[j];
+      }
+    }
+    store8(out + i * 8, acc0);
+    if (two) store8(out + i2 * 8, acc1);
+  }
+  for (long long i = n8 * 8 + tid; i < n; i += stride) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) acc += load1(static_cast<const TS*>(srcs.p[r]) + i);
+    store1(out + i, acc);
+  }
+}
+
+// dst_r[i] = cast(src[i]) for every peer r.  Four groups of eight elements per thread and iteration: the loads are
+// issued before the first store, so four 16/32-byte loads are in flight per thread.
 template <typename TS, typename TD>
-__global__ void cast_broadcast_kernel(const TS* __restrict__ src, PeerPtrs dsts, int world, long long n) {
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float x;
-    if constexpr (sizeof(TS) == 4) x = src[i];
-    else if constexpr (std::is_same<TS, __nv_bfloat16>::value) x = __bfloat162float(src[i]);
-    else x = __half2float(src[i]);
-    TD y;
-    if constexpr (sizeof(TD) == 4) y = x;
-    else if constexpr (std::is_same<TD, __nv_bfloat16>::value) y = __float2bfloat16_rn(x);
-    else y = __float2half_rn(x);
-    for (int r = 0; r < world; ++r) static_cast<TD*>(dsts.p[r])[i] = y;
+__global__ void cast_broadcast_kernel(const TS* __restrict__ src, PeerPtrs dsts, int world, long long n, long long n8) {
+  constexpr int kUnroll = 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  for (long long i = tid; i < n8; i += kUnroll * stride) {
+    float f[kUnroll][8];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long iu = i + u * stride;
+      if (iu < n8) load8(src + iu * 8, f[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long iu = i + u * stride;
+      if (iu < n8) {
+        for (int r = 0; r < world; ++r) store8(static_cast<TD*>(dsts.p[r]) + iu * 8, f[u]);
+      }
+    }
+  }
+  for (long long i = n8 * 8 + tid; i < n; i += stride) {
+    const float x = load1(src + i);
+    for (int r = 0; r < world; ++r) store1(static_cast<TD*>(dsts.p[r]) + i, x);
   }
 }
 
@@ -164,6 +241,13 @@ PeerPtrs make_ptrs(void* const* p, int world) {
   PeerPtrs out;
   for (int r = 0; r < 8; ++r) out.p[r] = r < world ? p[r] : nullptr;
   return out;
+}
+
+// Number of 8-element groups that may use vector accesses: all of them if every pointer is 16-byte aligned, else none.
+long long vector_groups(void* const* ptrs, int world, const void* other, long long n) {
+  uintptr_t bits = reinterpret_cast<uintptr_t>(other);
+  for (int r = 0; r < world; ++r) bits |= reinterpret_cast<uintptr_t>(ptrs[r]);
+  return (bits & 15) == 0 ? n / 8 : 0;
 }
 
 int capped_grid(long long work_items, int threads) {
@@ -190,23 +274,26 @@ void zero1_fused_step(void* const* grads, void* const* params, int world, long l
 
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream) {
   if (n <= 0) return;
-  const int grid = capped_grid(n, 256);
   const PeerPtrs p = make_ptrs(srcs, world);
+  const long long n8 = vector_groups(srcs, world, out, n);
+  const int grid = capped_grid(n8 > 0 ? (n8 + 1) / 2 : n, 256);
   if (src_fp32) {
-    if (out_fp32) peer_sum_kernel<float, float><<<grid, 256, 0, stream>>>(p, world, n, static_cast<float*>(out));
-    else peer_sum_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, static_cast<__nv_bfloat16*>(out));
+    if (out_fp32) peer_sum_kernel<float, float><<<grid, 256, 0, stream>>>(p, world, n, n8, static_cast<float*>(out));
+    else peer_sum_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, n8, static_cast<__nv_bfloat16*>(out));
   } else {
-    if (out_fp32) peer_sum_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(p, world, n, static_cast<float*>(out));
-    else peer_sum_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, static_cast<__nv_bfloat16*>(out));
+    if (out_fp32) peer_sum_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(p, world, n, n8, static_cast<float*>(out));
+    else peer_sum_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(p, world, n, n8, static_cast<__nv_bfloat16*>(out));
   }
 }
 
 void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
                     cudaStream_t stream) {
   if (n <= 0) return;
-  const int grid = capped_grid(n, 256);
   const PeerPtrs p = make_ptrs(dsts, world);
-#define RLK_CB(TS, TD) cast_broadcast_kernel<TS, TD><<<grid, 256, 0, stream>>>(static_cast<const TS*>(src), p, world, n)
+  const long long n8 = vector_groups(dsts, world, src, n);
+  const int grid = capped_grid(n8 > 0 ? (n8 + 3) / 4 : n, 256);
+#define RLK_CB(TS, TD) \
+  cast_broadcast_kernel<TS, TD><<<grid, 256, 0, stream>>>(static_cast<const TS*>(src), p, world, n, n8)
   if (src_dtype == 0) {
     if (dst_dtype == 0) RLK_CB(float, float);
     else if (dst_dtype == 1) RLK_CB(float, __nv_bfloat16);

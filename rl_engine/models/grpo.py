@@ -165,9 +165,22 @@ class GRPOTrainer:
         )
 
     def step_device(self, batch: GRPOBatch) -> torch.Tensor:
-        self.opt.zero_grad()
-        loss, _pl, _kl = self.loss(batch)
-        loss.backward()
+        """Forward, backward and optimiser step.  If the kept activations do not fit after all (the plan of
+        ``LlamaModel.plan_checkpointing`` is an estimate), the forward/backward is repeated with four more layers
+        recomputed; nothing has been applied to the parameters at that point."""
+        while True:
+            self.opt.zero_grad()
+            loss = None
+            try:
+                loss, _pl, _kl = self.loss(batch)
+                loss.backward()
+                break
+            except torch.cuda.OutOfMemoryError:
+                if not hasattr(self.model, "kept_layers") or self.model.kept_layers() == 0:
+                    raise
+            loss = None
+            torch.cuda.empty_cache()
+            self.model.reduce_kept_layers(4)
         self.opt.step()
         return loss.detach()
 

@@ -16,7 +16,7 @@ The reference ships no model (only ``Embedding -> Linear`` toys:
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple, Union
 
 import torch
 from torch import nn
@@ -24,6 +24,7 @@ from torch.utils.checkpoint import checkpoint
 
 from rl_engine.kernels.ops.pytorch.attention import NativeAttentionOp  # noqa: F401  (CPU oracle family)
 from rl_engine.kernels.ops.pytorch.linear.rope import rope_cos_sin
+from rl_engine.models.activation_plan import ActivationPlanner
 from rl_engine.models.config import ModelConfig
 
 
@@ -116,10 +117,13 @@ class _FusedAttentionBlock(torch.autograd.Function):
 
 class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
-                 activation_checkpointing: bool = True, max_positions: int = 8192) -> None:
+                 activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192) -> None:
+        """``activation_checkpointing``: ``True`` recomputes every layer in the backward pass, ``False`` keeps every
+        layer's activations, ``"auto"`` (default) keeps as many trailing layers as the free device memory allows at the
+        first training forward and recomputes the rest (``plan_checkpointing``)."""
         super().__init__()
         self.cfg = cfg
-        self.activation_checkpointing = activation_checkpointing
+        self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)
         h, f = cfg.hidden_size, cfg.ffn_size
         qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab_size, h))]
@@ -254,13 +258,39 @@ class LlamaModel(nn.Module):
         act = swiglu_packed(gu)
         return x + linear(act, p("w_down"))
 
+    # -- activation memory ------------------------------------------------------------------
+    def activation_bytes_per_layer(self, tokens: int) -> int:
+        """Bytes autograd keeps alive for one dense layer that is not recomputed: the layer input, the two normed
+        inputs, the mid-layer residual, qkv, rotated q and k, the attention output, gate/up and the SwiGLU output."""
+        cfg = self.cfg
+        per_token = (4 * cfg.hidden_size + (cfg.q_dim + 2 * cfg.kv_dim) + 2 * cfg.q_dim + cfg.kv_dim + 3 * cfg.ffn_size)
+        return tokens * (per_token * self.flat.element_size() + 4 * cfg.num_heads + 8)
+
+    def plan_checkpointing(self, tokens: int) -> int:
+        """Number of trailing layers whose activations are kept for the backward pass (the others are recomputed);
+        see ``ActivationPlanner``.  Mixture-of-experts layers are always recomputed (their activation size depends on
+        the routing)."""
+        if self.cfg.num_experts and self._planner.mode == "auto":
+            return 0
+        layer_input = tokens * self.cfg.hidden_size * self.flat.element_size()
+        return self._planner.kept(tokens, self.activation_bytes_per_layer(tokens), layer_input, self.flat.device)
+
+    def kept_layers(self) -> int:
+        return self._planner.current()
+
+    def reduce_kept_layers(self, by: int = 4) -> int:
+        """After an out-of-memory error: recompute ``by`` more layers from now on.  Returns the new number kept."""
+        return self._planner.reduce(by)
+
     def hidden_states(self, token_ids: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
         """Packed ``token_ids [T]`` -> final-norm hidden states ``[T, H]``."""
         from rl_engine.kernels.registry import kernel_registry
 
         x = kernel_registry.get_op("embedding")(token_ids, self.view("embed"))
+        training = torch.is_grad_enabled()
+        first_kept = self.cfg.num_layers - (self.plan_checkpointing(token_ids.numel()) if training else 0)
         for i in range(self.cfg.num_layers):
-            if self.activation_checkpointing and torch.is_grad_enabled():
+            if training and i < first_kept:
                 x = checkpoint(self._layer, x, i, positions, layout, use_reentrant=False)
             else:
                 x = self._layer(x, i, positions, layout)

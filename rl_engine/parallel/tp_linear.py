@@ -125,6 +125,14 @@ class TensorParallelLinears:
         bufs.mem.barrier()
         return buf.local
 
+    def process_group(self):
+        """The ``torch.distributed`` group of this instance (``None`` on a single rank), for ops that take ``tp_group``."""
+        if self.world == 1:
+            return None
+        import torch.distributed as dist
+
+        return self.group if self.group is not None else dist.group.WORLD
+
     def supports(self, rows_local: int, k: int, n: int) -> bool:
         return rows_local > 0 and rows_local % TILE_M == 0 and k % 8 == 0 and n % 8 == 0
 

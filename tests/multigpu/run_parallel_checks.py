@@ -204,6 +204,34 @@ def main() -> None:
     tp_layer.check()
     print(f"[{rank}] OK tensor-parallel Llama layer", flush=True)
 
+    # ---- a whole GRPO step under tensor parallelism vs the single-GPU trainer ---------------------------
+    from rl_engine.models.grpo import GRPOTrainer, synthetic_batch
+    from rl_engine.parallel.tp_model import TensorParallelGRPOTrainer, TensorParallelLlama
+
+    mcfg = ModelConfig("tp-model", 2048, 512, 2, max(8, 2 * world), max(4, world), 128, 1024)
+    ref_model = LlamaModel(mcfg, dtype=torch.bfloat16, device=dev, seed=21)
+    tp_model = TensorParallelLlama(ref_model, _TPL(group=dist.group.WORLD, device=dev))
+    hb = synthetic_batch(mcfg.vocab_size, prompt_len=256, group=4, completion_len=192, seed=3)
+    ref_tr = GRPOTrainer(ref_model, lr=1e-3)
+    tp_tr = TensorParallelGRPOTrainer(tp_model, lr=1e-3)
+    db = hb.to(dev)
+    with torch.no_grad():
+        lp_ref = ref_tr.policy_logps(db)
+        lp_tp = tp_model.policy_logps(db)
+    assert torch.allclose(lp_tp, lp_ref, atol=5e-2, rtol=5e-2), (lp_tp - lp_ref).abs().max()
+    allg = [torch.empty_like(lp_tp) for _ in range(world)]
+    dist.all_gather(allg, lp_tp)
+    assert all(torch.equal(allg[0], t_) for t_ in allg), "TP log-probs differ between ranks"
+    loss_ref = [ref_tr.step(hb) for _ in range(3)]
+    loss_tp = [tp_tr.step(hb) for _ in range(3)]
+    assert abs(loss_tp[0] - loss_ref[0]) < 2e-2 * max(1.0, abs(loss_ref[0])), (loss_tp, loss_ref)
+    assert loss_tp[-1] < loss_tp[0], f"TP training does not reduce the loss: {loss_tp}"
+    close(tp_model.params["final_norm"], ref_model.view("final_norm"), 2e-2, "tp model final_norm after 3 steps")
+    hq_m = mcfg.num_heads // world * mcfg.head_dim
+    close(tp_model.params["l1.wo"], ref_model.view("l1.wo")[:, rank * hq_m:(rank + 1) * hq_m], 5e-2, "tp model wo shard after 3 steps")
+    check_device_errors(local)
+    print(f"[{rank}] OK tensor-parallel GRPO step (loss {loss_tp[0]:.4f} -> {loss_tp[-1]:.4f}, single GPU {loss_ref[0]:.4f} -> {loss_ref[-1]:.4f})", flush=True)
+
     # ---- context-parallel causal attention (zig-zag shards, peer-store K/V gather, peer_sum dK/dV) ----
     from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
     from rl_engine.parallel.context_parallel import ContextParallelAttention, shard_sequence

@@ -283,3 +283,21 @@ def test_vocab_parallel_linear_logp_four_gloo_ranks_uneven_shards():
     for rank, err, bad_partition in results:
         assert isinstance(err, float), (rank, err)
         assert err < 1e-5 and bad_partition, (rank, err, bad_partition)
+
+
+def test_activation_checkpoint_plan_modes_and_fallback():
+    """``True`` recomputes every layer, ``False`` keeps every layer, ``"auto"`` on a CPU model recomputes (there is
+    no device memory to plan against); an out-of-memory fallback lowers the number of kept layers by four."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("plan", 256, 64, 6, 4, 2, 16, 128)
+    assert LlamaModel(cfg, dtype=torch.float32, activation_checkpointing=True).plan_checkpointing(100) == 0
+    keep_all = LlamaModel(cfg, dtype=torch.float32, activation_checkpointing=False)
+    assert keep_all.plan_checkpointing(100) == 6
+    assert LlamaModel(cfg, dtype=torch.float32).plan_checkpointing(100) == 0
+    # per token: 4 H + qkv rows + 2 q_dim + kv_dim + 3 F elements, plus the fp32 softmax statistics and two rstd
+    per_token = 4 * 64 + (64 + 2 * 32) + 2 * 64 + 32 + 3 * 128
+    assert keep_all.activation_bytes_per_layer(10) == 10 * (per_token * 4 + 4 * 4 + 8)
+    assert keep_all.reduce_kept_layers(4) == 2 and keep_all.plan_checkpointing(100) == 2 and keep_all.kept_layers() == 2
+    assert keep_all.reduce_kept_layers(4) == 0

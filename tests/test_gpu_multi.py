@@ -47,6 +47,31 @@ def test_symmetric_memory_single_rank_and_timeout_error():
     mem.close()
 
 
+@pytest.mark.parametrize("n,offset", [(8 * 4096, 0), (8 * 4096 + 5, 0), (3, 0), (8 * 1000 + 3, 1), (8 * 5000, 8)])
+def test_cast_broadcast_and_peer_sum_vector_and_scalar_paths(n, offset):
+    """Sizes that are not multiples of 8 take a scalar tail; an element offset that leaves the pointer off a 16-byte boundary takes the
+    scalar path for everything.  Both must agree with a plain cast / sum."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    ext = require_ext()
+    torch.manual_seed(n)
+    src = torch.randn(n, device="cuda")
+    for code, dtype in ((0, torch.float32), (1, torch.bfloat16), (2, torch.float16)):
+        dst = torch.zeros(n + 64, dtype=dtype, device="cuda")
+        view = dst[offset:]
+        ext.cast_broadcast(src, [view.data_ptr()], code)
+        torch.testing.assert_close(view[:n], src.to(dtype), rtol=0, atol=0)
+        assert float(view[n:].abs().sum()) == 0.0
+    a, b = src.to(torch.bfloat16), torch.randn(n, device="cuda").to(torch.bfloat16)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.zeros(n, dtype=out_dtype, device="cuda")
+        ext.peer_sum([a.data_ptr(), b.data_ptr()], n, False, out)
+        torch.testing.assert_close(out, (a.float() + b.float()).to(out_dtype), rtol=0, atol=0)
+    out = torch.zeros(n, device="cuda")
+    ext.peer_sum([src.data_ptr(), src.data_ptr(), src.data_ptr()], n, True, out)
+    torch.testing.assert_close(out, src + src + src, rtol=0, atol=1e-6)
+
+
 def test_fused_tp_linears_single_rank_match_plain_gemm():
     """World size 1: the copy warps feed this GPU's own gathered buffer and the reduce phase sums a single
     slab, so both fused kernels must reproduce the plain GEMM (three rounds reuse both buffer parities)."""
@@ -100,6 +125,28 @@ def test_tensor_parallel_layer_single_rank_matches_model_layer():
     assert (xl.grad.float() - xf.grad.float()).abs().max() / xf.grad.float().abs().max() < 3e-2
     gw = model.params[model._index["l0.w_down"]].grad
     assert (w["w_down"].grad.float() - gw.float()).abs().max() / gw.float().abs().max() < 3e-2
+
+
+def test_tensor_parallel_model_single_rank_trains_like_the_plain_model():
+    """World size 1: the tensor-parallel model / trainer (fused TP kernels, flat local optimiser) must follow the plain
+    single-GPU trainer on the same weights and batch."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.grpo import GRPOTrainer, synthetic_batch
+    from rl_engine.models.llama import LlamaModel
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+    from rl_engine.parallel.tp_model import TensorParallelGRPOTrainer, TensorParallelLlama
+
+    cfg = ModelConfig("tp-model", 2048, 512, 2, 4, 2, 128, 1024)
+    plain = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=21)
+    tp_model = TensorParallelLlama(plain, TensorParallelLinears())
+    batch = synthetic_batch(cfg.vocab_size, prompt_len=128, group=4, completion_len=96, seed=3)
+    a, b = GRPOTrainer(plain, lr=1e-3), TensorParallelGRPOTrainer(tp_model, lr=1e-3)
+    la = [a.step(batch) for _ in range(3)]
+    lb = [b.step(batch) for _ in range(3)]
+    assert abs(la[0] - lb[0]) < 2e-2 * max(1.0, abs(la[0])), (la, lb)
+    assert lb[-1] < lb[0], lb
+    diff = (tp_model.params["final_norm"].float() - plain.view("final_norm").float()).abs().max()
+    assert float(diff) < 5e-2
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")

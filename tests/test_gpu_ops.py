@@ -481,3 +481,41 @@ def test_sampler_backend_uses_the_fused_kernels_without_top_k():
     b = sampler.sample(logits, top_k=None, top_p=None, temperature=1.0)
     assert ext.launch_count() - before == 2, "both calls must run one native kernel each"
     assert a.shape == (32,) and b.shape == (32,) and int(a.min()) >= 0 and int(b.max()) < 3000
+
+
+def test_kept_and_recomputed_activations_give_identical_gradients_and_oom_falls_back(monkeypatch):
+    """Recomputation replays the same deterministic kernels, so keeping a layer's activations or recomputing them
+    must not change one bit of the gradient.  An out-of-memory error in the forward/backward (raised here by a fake,
+    not by exhausting the device) makes the trainer recompute four more layers and repeat the step."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.grpo import GRPOTrainer, synthetic_batch
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("ckpt", 1024, 256, 6, 2, 1, 128, 512)
+    batch = synthetic_batch(cfg.vocab_size, prompt_len=64, group=4, completion_len=64, seed=5).to("cuda")
+    grads = {}
+    for mode in (True, False, "auto"):
+        model = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=8, activation_checkpointing=mode)
+        trainer = GRPOTrainer(model, lr=1e-3)
+        trainer.opt.zero_grad()
+        loss, _, _ = trainer.loss(batch)
+        loss.backward()
+        grads[mode] = model.flat_grad.clone()
+        if mode == "auto":
+            assert model.plan_checkpointing(batch.prompt_ids.numel() + batch.completion_ids.numel()) == 6
+    assert torch.equal(grads[True], grads[False]) and torch.equal(grads[True], grads["auto"])
+
+    model = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=8)
+    trainer = GRPOTrainer(model, lr=1e-3)
+    trainer.step_device(batch)  # makes the plan: all six layers fit
+    real_loss, calls = trainer.loss, []
+
+    def flaky_loss(b):
+        calls.append(model.kept_layers())
+        if len(calls) == 1:
+            raise torch.cuda.OutOfMemoryError("injected")
+        return real_loss(b)
+
+    monkeypatch.setattr(trainer, "loss", flaky_loss)
+    out = trainer.step_device(batch)
+    assert torch.isfinite(out) and calls == [6, 2] and model.kept_layers() == 2
