@@ -179,7 +179,6 @@ def main() -> None:
         del model  # only this rank's shards stay resident
         torch.cuda.empty_cache()
         trainer = TensorParallelGRPOTrainer(tp_model, lr=1e-6, clip_eps=0.2, beta=0.04)
-        trainer.policy_logps = tp_model.policy_logps
         parallelism = f"tp{world}-sequence-parallel-fused"
     elif world > 1:
         from rl_engine.parallel.data_parallel import ShardedGRPOTrainer

@@ -27,10 +27,22 @@ class ActivationPlanner:
         self.layers, self.mode, self.headroom = layers, mode, headroom_bytes
         self._plan: Optional[Tuple[int, int]] = None  # (packed tokens the plan was made for, layers kept)
 
+    def estimate(self, per_layer_bytes: int, layer_input_bytes: int, device: torch.device) -> int:
+        """Layers that would fit right now (no caching).  The reserve is the inputs of all layers, the transients of
+        three layers (one being recomputed plus its backward temporaries) and the head room."""
+        if self.mode is True or device.type != "cuda":
+            return 0
+        if self.mode is False:
+            return self.layers
+        free, _total = torch.cuda.mem_get_info(device)
+        cached = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+        per_layer = max(1, per_layer_bytes)
+        reserve = self.layers * layer_input_bytes + 3 * per_layer + self.headroom
+        return int(max(0, min(self.layers, (free + cached - reserve) // per_layer)))
+
     def kept(self, tokens: int, per_layer_bytes: int, layer_input_bytes: int, device: torch.device) -> int:
         """Trailing layers that keep their activations.  ``per_layer_bytes``: what autograd holds for one kept layer;
-        ``layer_input_bytes``: the input every recomputed layer holds.  The reserve is the inputs of all layers, the
-        transients of three layers (one being recomputed plus its backward temporaries) and the head room."""
+        ``layer_input_bytes``: the input every recomputed layer holds.  Planned once per packed length."""
         if self.mode is True:
             return 0
         if self.mode is False:
@@ -39,13 +51,8 @@ class ActivationPlanner:
             return self._plan[1]
         if device.type != "cuda":
             return 0
-        free, _total = torch.cuda.mem_get_info(device)
-        cached = torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
-        per_layer = max(1, per_layer_bytes)
-        reserve = self.layers * layer_input_bytes + 3 * per_layer + self.headroom
-        keep = int(max(0, min(self.layers, (free + cached - reserve) // per_layer)))
-        self._plan = (tokens, keep)
-        return keep
+        self._plan = (tokens, self.estimate(per_layer_bytes, layer_input_bytes, device))
+        return self._plan[1]
 
     def current(self) -> int:
         """The number of layers kept by the plan in force (all layers before any plan under ``False``)."""

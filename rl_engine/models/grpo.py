@@ -43,6 +43,12 @@ class GRPOBatch:
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors())
 
+    def completions(self, begin: int, end: int) -> "GRPOBatch":
+        """The same prompt with completions ``[begin, end)`` (``rewards`` stay those of the whole group)."""
+        return GRPOBatch(self.prompt_ids, self.completion_ids[begin:end].contiguous(), self.rewards,
+                         self.old_logps[begin:end].contiguous(), self.ref_logps[begin:end].contiguous(),
+                         self.completion_mask[begin:end].contiguous())
+
 
 def synthetic_batch(vocab: int, prompt_len: int, group: int, completion_len: int, seed: int = 0) -> GRPOBatch:
     """Seeded host batch: uniform token ids, N(0,1) rewards, old/ref = N(-2, 0.1) placeholders."""
@@ -144,25 +150,102 @@ def policy_logps(model: LlamaModel, batch: "GRPOBatch") -> torch.Tensor:
     return logp.reshape(g, l)
 
 
+def choose_micro_group(group: int, prompt_len: int, completion_len: int, layers: int, kept_for_tokens) -> int:
+    """Completions per forward/backward pass that minimise the step's compute.
+
+    Splitting the group into micro-batches re-processes the shared prompt once per micro-batch, but the smaller
+    packed length lets more layers keep their activations, which saves their recomputation (a third of a layer's
+    forward + backward work).  Cost model per candidate ``m`` (``group``, ``group / 2``, ... while even and the packed
+    length stays above 4096 tokens): ``(group / m) * (prompt + m * completion) * (3 + recomputed / layers)``.
+    ``kept_for_tokens(tokens)`` answers how many layers could keep their activations at that packed length."""
+    best, best_cost = group, None
+    m = group
+    while m >= 1:
+        tokens = prompt_len + m * completion_len
+        if m != group and tokens < 4096:
+            break
+        kept = min(layers, max(0, int(kept_for_tokens(tokens))))
+        cost = (group // m) * tokens * (3.0 + (layers - kept) / max(1, layers))
+        if best_cost is None or cost < best_cost * 0.98:  # a smaller micro-batch has to pay for its extra launches
+            best, best_cost = m, cost
+        if m % 2:
+            break
+        m //= 2
+    return best
+
+
 class GRPOTrainer:
+    """``micro_group``: completions per forward/backward pass.  ``None`` runs the whole group in one pass, an integer
+    fixes it, ``"auto"`` (default) picks it at the first step with ``choose_micro_group``.  Gradients of the
+    micro-batches accumulate in the flat gradient buffer; each micro-batch's loss is weighted by its share of the
+    unmasked tokens, so the step optimises the same token-mean loss as a single pass."""
+
+    retry_on_out_of_memory = True
+
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
-                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False) -> None:
+                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False,
+                 micro_group="auto") -> None:
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
+        self.micro_group = micro_group
+        self._micro_choice: Dict[tuple, int] = {}
         self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
 
     def policy_logps(self, batch: GRPOBatch) -> torch.Tensor:
         return policy_logps(self.model, batch)
 
-    def loss(self, batch: GRPOBatch):
+    def advantages(self, batch: GRPOBatch) -> torch.Tensor:
+        """Group-normalised advantage of each completion of ``batch`` (``[G]``)."""
         from rl_engine.kernels.registry import kernel_registry
 
         op = kernel_registry.get_op("grpo_loss")
-        adv = op.group_advantages(batch.rewards.float(), samples_per_prompt=batch.rewards.numel(), eps=self.adv_eps)
+        return op.group_advantages(batch.rewards.float(), samples_per_prompt=batch.rewards.numel(), eps=self.adv_eps)
+
+    def loss_with_advantages(self, batch: GRPOBatch, adv: torch.Tensor):
+        from rl_engine.kernels.registry import kernel_registry
+
         logp = self.policy_logps(batch)
-        return op.apply_from_logps(
+        return kernel_registry.get_op("grpo_loss").apply_from_logps(
             logp, batch.ref_logps, batch.old_logps, adv, batch.completion_mask, clip_eps=self.clip_eps, beta=self.beta
         )
+
+    def loss(self, batch: GRPOBatch):
+        return self.loss_with_advantages(batch, self.advantages(batch))
+
+    def completions_per_pass(self, batch: GRPOBatch) -> int:
+        g, l = batch.completion_ids.shape
+        if self.micro_group is None:
+            return g
+        if isinstance(self.micro_group, int):
+            return max(1, min(g, self.micro_group))
+        key = (g, l, batch.prompt_ids.numel())
+        if key not in self._micro_choice:
+            estimate = getattr(self.model, "estimate_kept_layers", None)
+            layers = self.model.cfg.num_layers
+            self._micro_choice[key] = g if estimate is None else choose_micro_group(g, key[2], l, layers, estimate)
+        return self._micro_choice[key]
+
+    def forward_backward(self, batch: GRPOBatch) -> torch.Tensor:
+        """Accumulates the gradient of the group's token-mean loss into the flat gradient buffer; returns the loss."""
+        g = batch.completion_ids.shape[0]
+        m = self.completions_per_pass(batch)
+        if m >= g:
+            loss, _pl, _kl = self.loss(batch)
+            loss.backward()
+            return loss.detach()
+        adv = self.advantages(batch)
+        unmasked = batch.completion_mask.sum().clamp_min(1).float()
+        total = torch.zeros((), dtype=torch.float32, device=batch.completion_ids.device)
+        for i0 in range(0, g, m):
+            part = batch.completions(i0, min(g, i0 + m))
+            loss, _pl, _kl = self.loss_with_advantages(part, adv[i0:i0 + m].contiguous())
+            weighted = loss * (part.completion_mask.sum().float() / unmasked)
+            weighted.backward()
+            total += weighted.detach()
+        return total
+
+    def before_optimizer_step(self) -> None:
+        """Hook for trainers whose gradients need a reduction that the optimiser kernel does not do."""
 
     def step_device(self, batch: GRPOBatch) -> torch.Tensor:
         """Forward, backward and optimiser step.  If the kept activations do not fit after all (the plan of
@@ -170,19 +253,18 @@ class GRPOTrainer:
         recomputed; nothing has been applied to the parameters at that point."""
         while True:
             self.opt.zero_grad()
-            loss = None
             try:
-                loss, _pl, _kl = self.loss(batch)
-                loss.backward()
+                loss = self.forward_backward(batch)
                 break
             except torch.cuda.OutOfMemoryError:
-                if not hasattr(self.model, "kept_layers") or self.model.kept_layers() == 0:
+                if (not self.retry_on_out_of_memory or not hasattr(self.model, "kept_layers")
+                        or self.model.kept_layers() == 0):
                     raise
-            loss = None
             torch.cuda.empty_cache()
             self.model.reduce_kept_layers(4)
+        self.before_optimizer_step()
         self.opt.step()
-        return loss.detach()
+        return loss
 
     def step(self, host_batch: GRPOBatch) -> float:
         """Public end-to-end step: host (pinned) batch in, loss value out."""

@@ -90,11 +90,14 @@ class _FusedAttentionBlock(torch.autograd.Function):
         from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
 
         ext = require_ext()
-        q = ext.rope(qkv[:, :hq], positions, cos_t, sin_t, False)
-        k = ext.rope(qkv[:, hq : hq + hkv], positions, cos_t, sin_t, False)
-        v = qkv[:, hq + hkv :]
+        # q and k are rotated in place: the projection that produced ``qkv`` does not need its output for its own
+        # backward pass, and this block's backward un-rotates the gradients, so the unrotated values are never read
+        # again.  One [T, Hq + 2 Hkv, 128] tensor is kept instead of that plus rotated copies of q and k.
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        ext.rope(q, positions, cos_t, sin_t, False, q)
+        ext.rope(k, positions, cos_t, sin_t, False, k)
         out, lse = packed_attention_forward(q, k, v, layout, scale, True)
-        ctx.save_for_backward(q, k, qkv, out, lse, positions, cos_t, sin_t)
+        ctx.save_for_backward(qkv, out, lse, positions, cos_t, sin_t)
         ctx.meta = (layout, hq, hkv, scale)
         return out
 
@@ -103,9 +106,9 @@ class _FusedAttentionBlock(torch.autograd.Function):
         from rl_engine.kernels.ops.base import require_ext
         from rl_engine.kernels.ops.sm100.attention_bwd import packed_attention_backward
 
-        q, k, qkv, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
+        qkv, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
         layout, hq, hkv, scale = ctx.meta
-        v = qkv[:, hq + hkv :]
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
         dq, dk, dv = packed_attention_backward(q, k, v, out, lse, dout.contiguous(), layout, scale)
         dqkv = torch.empty_like(qkv)
         ext = require_ext()
@@ -246,24 +249,31 @@ class LlamaModel(nn.Module):
     def _layer(self, x: torch.Tensor, index: int, positions: torch.Tensor, layout) -> torch.Tensor:
         cfg = self.cfg
         p = lambda n: self.view(f"l{index}.{n}")
-        h = rms_norm(x, p("attn_norm"), cfg.rms_eps)
-        attn = self._attention(linear(h, p("wqkv")), positions, layout, index)
-        x = x + linear(attn, p("wo"))
-        h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
+        lean = _fused_path(x)  # recompute normalised inputs and the SwiGLU output in backward instead of keeping them
+        if lean:
+            from rl_engine.kernels.ops.sm100.lean_blocks import norm_linear, swiglu_linear
+
+            qkv = norm_linear(x, p("attn_norm"), p("wqkv"), cfg.rms_eps)
+        else:
+            qkv = linear(rms_norm(x, p("attn_norm"), cfg.rms_eps), p("wqkv"))
+        x = x + linear(self._attention(qkv, positions, layout, index), p("wo"))
         if cfg.num_experts:
             from rl_engine.kernels.registry import kernel_registry
 
+            h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
             return x + kernel_registry.get_op("moe")(h, p("router"), p("w_gate_up"), p("w_down"), cfg.experts_per_token)
-        gu = linear(h, p("w_gate_up"))
-        act = swiglu_packed(gu)
-        return x + linear(act, p("w_down"))
+        if lean:
+            return x + swiglu_linear(norm_linear(x, p("mlp_norm"), p("w_gate_up"), cfg.rms_eps), p("w_down"))
+        gu = linear(rms_norm(x, p("mlp_norm"), cfg.rms_eps), p("w_gate_up"))
+        return x + linear(swiglu_packed(gu), p("w_down"))
 
     # -- activation memory ------------------------------------------------------------------
     def activation_bytes_per_layer(self, tokens: int) -> int:
-        """Bytes autograd keeps alive for one dense layer that is not recomputed: the layer input, the two normed
-        inputs, the mid-layer residual, qkv, rotated q and k, the attention output, gate/up and the SwiGLU output."""
+        """Bytes autograd keeps alive for one dense layer that is not recomputed: the layer input, the mid-layer
+        residual, qkv (q and k rotated in place), the attention output and the packed gate/up projection; plus the
+        fp32 softmax statistics per head and the two RMSNorm ``rstd`` values."""
         cfg = self.cfg
-        per_token = (4 * cfg.hidden_size + (cfg.q_dim + 2 * cfg.kv_dim) + 2 * cfg.q_dim + cfg.kv_dim + 3 * cfg.ffn_size)
+        per_token = 2 * cfg.hidden_size + (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim + 2 * cfg.ffn_size
         return tokens * (per_token * self.flat.element_size() + 4 * cfg.num_heads + 8)
 
     def plan_checkpointing(self, tokens: int) -> int:
@@ -274,6 +284,13 @@ class LlamaModel(nn.Module):
             return 0
         layer_input = tokens * self.cfg.hidden_size * self.flat.element_size()
         return self._planner.kept(tokens, self.activation_bytes_per_layer(tokens), layer_input, self.flat.device)
+
+    def estimate_kept_layers(self, tokens: int) -> int:
+        """What ``plan_checkpointing`` would answer for a packed length of ``tokens`` right now, without fixing it."""
+        if self.cfg.num_experts and self._planner.mode == "auto":
+            return 0
+        layer_input = tokens * self.cfg.hidden_size * self.flat.element_size()
+        return self._planner.estimate(self.activation_bytes_per_layer(tokens), layer_input, self.flat.device)
 
     def kept_layers(self) -> int:
         return self._planner.current()

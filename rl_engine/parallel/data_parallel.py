@@ -61,7 +61,8 @@ class ShardedGRPOTrainer(GRPOTrainer):
     """``GRPOTrainer`` whose parameters/gradients live in symmetric memory and whose optimizer is fused."""
 
     def __init__(self, model: LlamaModel, *, group=None, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
-                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True) -> None:
+                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
+                 micro_group="auto") -> None:
         n = model.flat.numel()
         itemsize = model.flat.element_size()
         self.mem = SymmetricMemory(2 * n * itemsize + (1 << 20), group=group, device=model.flat.device)
@@ -71,6 +72,8 @@ class ShardedGRPOTrainer(GRPOTrainer):
         model.rebind_storage(params.local, grads.local)
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
+        self.micro_group = micro_group
+        self._micro_choice = {}
         self.opt = ShardedFusedAdamW(model, self.mem, params, grads, lr=lr, weight_decay=weight_decay,
                                      master_weights=master_weights)
         self._slice: Optional[slice] = None
@@ -80,21 +83,9 @@ class ShardedGRPOTrainer(GRPOTrainer):
         """This rank trains on completions ``sl`` of the group; advantages use the whole group's rewards."""
         self._slice = sl
 
-    def loss(self, batch: GRPOBatch):
-        from rl_engine.kernels.registry import kernel_registry
-
-        op = kernel_registry.get_op("grpo_loss")
-        adv = op.group_advantages(batch.rewards.float(), samples_per_prompt=batch.rewards.numel(), eps=self.adv_eps)
-        if self._slice is not None:
-            adv = adv[self._slice].contiguous()
-        logp = self.policy_logps(batch)
-        return op.apply_from_logps(
-            logp, batch.ref_logps, batch.old_logps, adv, batch.completion_mask, clip_eps=self.clip_eps, beta=self.beta
-        )
-
-    def step_device(self, batch: GRPOBatch) -> torch.Tensor:
-        out = super().step_device(batch)
-        return out
+    def advantages(self, batch: GRPOBatch) -> torch.Tensor:
+        adv = super().advantages(batch)
+        return adv if self._slice is None else adv[self._slice].contiguous()
 
     def check(self) -> None:
         self.mem.check()

@@ -24,7 +24,7 @@ import torch
 from torch.utils.checkpoint import checkpoint
 
 from rl_engine.models.activation_plan import ActivationPlanner
-from rl_engine.models.grpo import FlatAdamW, GRPOBatch, group_geometry
+from rl_engine.models.grpo import GRPOBatch, GRPOTrainer, group_geometry
 from rl_engine.models.llama import LlamaModel, rms_norm
 from rl_engine.parallel.tp_linear import TensorParallelLinears
 from rl_engine.parallel.tp_transformer import TensorParallelLlamaLayer, shard_layer_weights
@@ -53,7 +53,10 @@ class TensorParallelLlama:
         self.cfg, self.tp = cfg, tp
         self.rank, self.world = tp.rank, tp.world
         self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)
-        self._per_token_bytes = full.activation_bytes_per_layer(1)  # of the whole layer; a rank holds 1/W of it
+        # kept per token by a tensor-parallel layer, summed over the ranks: the layer input, both normalised inputs and
+        # the mid-layer residual (row shards), qkv, the attention output, gate/up and the SwiGLU output (column shards)
+        self._per_token_bytes = full.flat.element_size() * (
+            4 * cfg.hidden_size + (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim + 3 * cfg.ffn_size) + 4 * cfg.num_heads + 8
         if cfg.vocab_size % (8 * self.world):
             raise ValueError("vocabulary must divide by 8 * TP size")
         v_local = cfg.vocab_size // self.world
@@ -113,6 +116,18 @@ class TensorParallelLlama:
             self._planner._plan = (tokens, keep)
         return keep
 
+    def estimate_kept_layers(self, tokens: int) -> int:
+        """The ranks' minimum of what would fit for ``tokens`` packed tokens (collective: call on every rank)."""
+        import torch.distributed as dist
+
+        layer_input = tokens // self.world * self.cfg.hidden_size * self.flat.element_size()
+        keep = self._planner.estimate(tokens * self._per_token_bytes // self.world, layer_input, self.flat.device)
+        if self.world > 1:
+            agreed = torch.tensor([keep], device=self.flat.device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.tp.group)
+            keep = int(agreed.item())
+        return keep
+
     def kept_layers(self) -> int:
         return self._planner.current()
 
@@ -162,31 +177,21 @@ class TensorParallelLlama:
             dist.all_reduce(self.flat_grad[: self._replicated_numel], group=self.tp.group)
 
 
-class TensorParallelGRPOTrainer:
-    """``step(host_batch) -> loss`` with the same contract as ``GRPOTrainer`` (same batch on every rank)."""
+class TensorParallelGRPOTrainer(GRPOTrainer):
+    """``step(host_batch) -> loss`` with the same contract as ``GRPOTrainer`` (the same batch on every rank).
+
+    Every rank runs the same passes (micro-batch size and kept layers are agreed by the ranks, because a recomputed
+    layer re-runs its fused collectives), so an out-of-memory error is not retried here: it is raised."""
+
+    retry_on_out_of_memory = False
 
     def __init__(self, model: TensorParallelLlama, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
-                 adv_eps: float = 1e-6, weight_decay: float = 0.0) -> None:
-        self.model = model
-        self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
-        self.opt = FlatAdamW(model, lr=lr, weight_decay=weight_decay)
+                 adv_eps: float = 1e-6, weight_decay: float = 0.0, micro_group="auto") -> None:
+        super().__init__(model, lr=lr, clip_eps=clip_eps, beta=beta, adv_eps=adv_eps, weight_decay=weight_decay,
+                         micro_group=micro_group)
 
-    def loss(self, batch: GRPOBatch):
-        from rl_engine.kernels.registry import kernel_registry
+    def policy_logps(self, batch: GRPOBatch) -> torch.Tensor:
+        return self.model.policy_logps(batch)
 
-        op = kernel_registry.get_op("grpo_loss")
-        adv = op.group_advantages(batch.rewards.float(), samples_per_prompt=batch.rewards.numel(), eps=self.adv_eps)
-        logp = self.model.policy_logps(batch)
-        return op.apply_from_logps(logp, batch.ref_logps, batch.old_logps, adv, batch.completion_mask,
-                                   clip_eps=self.clip_eps, beta=self.beta)
-
-    def step_device(self, batch: GRPOBatch) -> torch.Tensor:
-        self.opt.zero_grad()
-        loss, _pl, _kl = self.loss(batch)
-        loss.backward()
+    def before_optimizer_step(self) -> None:
         self.model.sync_replicated_grads()
-        self.opt.step()
-        return loss.detach()
-
-    def step(self, host_batch: GRPOBatch) -> float:
-        return float(self.step_device(host_batch.to(self.model.flat.device)).item())

@@ -296,8 +296,48 @@ def test_activation_checkpoint_plan_modes_and_fallback():
     keep_all = LlamaModel(cfg, dtype=torch.float32, activation_checkpointing=False)
     assert keep_all.plan_checkpointing(100) == 6
     assert LlamaModel(cfg, dtype=torch.float32).plan_checkpointing(100) == 0
-    # per token: 4 H + qkv rows + 2 q_dim + kv_dim + 3 F elements, plus the fp32 softmax statistics and two rstd
-    per_token = 4 * 64 + (64 + 2 * 32) + 2 * 64 + 32 + 3 * 128
+    # per token: 2 H + qkv rows + q_dim + 2 F elements, plus the fp32 softmax statistics and two rstd
+    per_token = 2 * 64 + (64 + 2 * 32) + 64 + 2 * 128
     assert keep_all.activation_bytes_per_layer(10) == 10 * (per_token * 4 + 4 * 4 + 8)
     assert keep_all.reduce_kept_layers(4) == 2 and keep_all.plan_checkpointing(100) == 2 and keep_all.kept_layers() == 2
     assert keep_all.reduce_kept_layers(4) == 0
+
+
+def test_micro_batched_step_matches_the_single_pass_step():
+    """Gradient accumulation over micro-batches of completions, each weighted by its share of the unmasked tokens,
+    optimises the same token-mean loss as one pass over the whole group."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.grpo import GRPOTrainer, choose_micro_group, policy_logps, synthetic_batch
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("micro", 512, 64, 2, 4, 2, 16, 128)
+    batch = synthetic_batch(cfg.vocab_size, prompt_len=16, group=6, completion_len=12, seed=4)
+    batch.completion_mask[1, 7:] = False  # uneven token counts between the micro-batches
+    batch.completion_mask[4, 3:] = False
+    results = []
+    for micro in (None, 2, 4):  # 4: micro-batches of 4 and 2 completions
+        model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=2)
+        with torch.no_grad():
+            cur = policy_logps(model, batch)
+        gen = torch.Generator().manual_seed(7)
+        batch.old_logps = cur + 0.05 * torch.randn(cur.shape, generator=gen)
+        batch.ref_logps = cur + 0.05 * torch.randn(cur.shape, generator=gen)
+        trainer = GRPOTrainer(model, lr=1e-3, micro_group=micro)
+        assert trainer.completions_per_pass(batch) == (6 if micro is None else micro)
+        loss = trainer.step(batch)
+        results.append((loss, model.flat_grad.clone()))
+    for loss, grad in results[1:]:
+        assert abs(loss - results[0][0]) < 1e-6
+        assert (grad - results[0][1]).abs().max() < 1e-6 * max(1.0, float(results[0][1].abs().max()))
+
+    # the chooser: everything fits -> one pass; all 32 layers fit at 17408 tokens but only 20 at 33792 -> 32 completions
+    assert choose_micro_group(256, 1024, 512, 32, lambda tokens: 32) == 256
+    gib = float(2**30)
+
+    def kept(tokens, free=88.7):
+        per, inp = tokens * 94344 / gib, tokens * 8192 / gib
+        return (free - (32 * inp + 3 * per + 12)) // per
+
+    assert choose_micro_group(256, 1024, 512, 32, kept) == 32
+    assert choose_micro_group(32, 1024, 512, 32, kept) == 32
+    assert choose_micro_group(6, 16, 12, 2, lambda tokens: 0) == 6  # short packed lengths are never split

@@ -519,3 +519,55 @@ def test_kept_and_recomputed_activations_give_identical_gradients_and_oom_falls_
     monkeypatch.setattr(trainer, "loss", flaky_loss)
     out = trainer.step_device(batch)
     assert torch.isfinite(out) and calls == [6, 2] and model.kept_layers() == 2
+
+
+def test_lean_blocks_match_the_unfused_composition_bitwise_and_the_fp32_reference():
+    """``norm_linear`` / ``swiglu_linear`` recompute the cheap op's output in backward; forward values and all gradients
+    must be the bits of rms_norm -> matmul / swiglu -> matmul, and close to a plain fp32 PyTorch restatement."""
+    from rl_engine.kernels.ops.sm100.gemm import matmul_nt
+    from rl_engine.kernels.ops.sm100.lean_blocks import norm_linear, swiglu_linear
+    from rl_engine.kernels.ops.sm100.model_ops import swiglu_packed
+    from rl_engine.kernels.registry import kernel_registry
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    rows, h, n, f = 384, 512, 640, 768
+    x = torch.randn(rows, h, device="cuda", generator=g).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(h, device="cuda", generator=g)).to(torch.bfloat16)
+    w = (0.05 * torch.randn(n, h, device="cuda", generator=g)).to(torch.bfloat16)
+    dy = torch.randn(rows, n, device="cuda", generator=g).to(torch.bfloat16)
+
+    def run(fn):
+        leaves = [t.clone().requires_grad_(True) for t in (x, nw, w)]
+        y = fn(*leaves)
+        y.backward(dy)
+        return [y.detach()] + [t.grad for t in leaves]
+
+    lean = run(lambda a, b, c: norm_linear(a, b, c, 1e-5))
+    plain = run(lambda a, b, c: matmul_nt(kernel_registry.get_op("rms_norm")(a, b, eps=1e-5), c))
+    for a, b in zip(lean, plain):
+        assert torch.equal(a, b)
+    xf, nwf, wf = (t.float().requires_grad_(True) for t in (x, nw, w))
+    ref = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * nwf) @ wf.t()
+    ref.backward(dy.float())
+    for got, want in zip(lean, (ref.detach(), xf.grad, nwf.grad, wf.grad)):
+        assert (got.float() - want).abs().max() / want.abs().max() < 2e-2
+
+    gu = torch.randn(rows, 2 * f, device="cuda", generator=g).to(torch.bfloat16)
+    w2 = (0.05 * torch.randn(h, f, device="cuda", generator=g)).to(torch.bfloat16)
+    dy2 = torch.randn(rows, h, device="cuda", generator=g).to(torch.bfloat16)
+
+    def run2(fn):
+        leaves = [t.clone().requires_grad_(True) for t in (gu, w2)]
+        y = fn(*leaves)
+        y.backward(dy2)
+        return [y.detach()] + [t.grad for t in leaves]
+
+    lean2 = run2(swiglu_linear)
+    plain2 = run2(lambda a, b: matmul_nt(swiglu_packed(a), b))
+    for a, b in zip(lean2, plain2):
+        assert torch.equal(a, b)
+    guf, w2f = gu.float().requires_grad_(True), w2.float().requires_grad_(True)
+    ref2 = (torch.nn.functional.silu(guf[:, :f]) * guf[:, f:]) @ w2f.t()
+    ref2.backward(dy2.float())
+    for got, want in zip(lean2, (ref2.detach(), guf.grad, w2f.grad)):
+        assert (got.float() - want).abs().max() / want.abs().max() < 2e-2
