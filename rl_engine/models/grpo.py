@@ -133,6 +133,38 @@ def group_geometry(p: int, g: int, l: int, device):
     return hit
 
 
+def suffix_geometry(p: int, m: int, l: int, device):
+    """Geometry of a pass that holds ``m`` completions of ``l`` tokens after a cached prompt of ``p`` tokens:
+    (layout with queries in the pass's rows and keys in ``[prompt | pass]``, positions ``[m * l]``, for every
+    completion token the row of ``[last prompt state | pass states]`` that predicts it ``[m * l]``)."""
+    key = ("suffix", p, m, l, str(device))
+    hit = _GEOMETRY.get(key)
+    if hit is None:
+        from rl_engine.kernels.ops.sm100.attention import make_layout
+
+        layout = make_layout([(i * l, l, 0, p, p + i * l, l) for i in range(m)], True, device)
+        positions = (p + torch.arange(l)).repeat(m).to(device)
+        rows = torch.arange(m)[:, None] * l + torch.arange(l)[None, :]  # 1 + (i * l + j - 1)
+        rows[:, 0] = 0                                                   # the prompt's last state
+        if len(_GEOMETRY) > 32:
+            _GEOMETRY.clear()
+        hit = _GEOMETRY[key] = (layout, positions, rows.reshape(-1).to(device))
+    return hit
+
+
+def policy_logps_after_prefix(model: LlamaModel, batch: "GRPOBatch", last_state: torch.Tensor, kv) -> torch.Tensor:
+    """``policy_logps`` for completions whose prompt was processed by ``model.prefix_states`` (``last_state``, ``kv``):
+    same kernels and per-row arithmetic as the single pass, without re-processing the prompt."""
+    from rl_engine.kernels.registry import kernel_registry
+
+    p, (m, l) = batch.prompt_ids.numel(), batch.completion_ids.shape
+    layout, positions, rows = suffix_geometry(p, m, l, batch.prompt_ids.device)
+    hidden = model.hidden_states_after_prefix(batch.completion_ids.reshape(-1), positions, layout, kv)
+    picked = kernel_registry.get_op("embedding")(rows, torch.cat([last_state, hidden]))
+    logp = kernel_registry.get_op("linear_logp")(picked, model.lm_head_weight(), batch.completion_ids.reshape(-1))
+    return logp.reshape(m, l)
+
+
 def policy_logps(model: LlamaModel, batch: "GRPOBatch") -> torch.Tensor:
     """Selected-token log-probs ``[G, L]`` of the completions under ``model`` (differentiable).
 
@@ -150,28 +182,56 @@ def policy_logps(model: LlamaModel, batch: "GRPOBatch") -> torch.Tensor:
     return logp.reshape(g, l)
 
 
-def choose_micro_group(group: int, prompt_len: int, completion_len: int, layers: int, kept_for_tokens) -> int:
+def choose_micro_group(group: int, prompt_len: int, completion_len: int, layers: int, kept_for_tokens,
+                       prompt_once: bool = False) -> int:
     """Completions per forward/backward pass that minimise the step's compute.
 
     Splitting the group into micro-batches re-processes the shared prompt once per micro-batch, but the smaller
     packed length lets more layers keep their activations, which saves their recomputation (a third of a layer's
     forward + backward work).  Cost model per candidate ``m`` (``group``, ``group / 2``, ... while even and the packed
     length stays above 4096 tokens): ``(group / m) * (prompt + m * completion) * (3 + recomputed / layers)``.
-    ``kept_for_tokens(tokens)`` answers how many layers could keep their activations at that packed length."""
+    ``kept_for_tokens(tokens)`` answers how many layers could keep their activations at that packed length.  With
+    ``prompt_once`` the micro-batches attend to cached prompt keys / values: the prompt costs one extra pass of its own
+    instead of one per micro-batch."""
     best, best_cost = group, None
     m = group
     while m >= 1:
-        tokens = prompt_len + m * completion_len
+        split_prompt = prompt_once and m != group  # the prompt is its own pass; micro-batches hold completions only
+        tokens = m * completion_len + (0 if split_prompt else prompt_len)
         if m != group and tokens < 4096:
             break
         kept = min(layers, max(0, int(kept_for_tokens(tokens))))
-        cost = (group // m) * tokens * (3.0 + (layers - kept) / max(1, layers))
+        cost = (group // m) * tokens * (3.0 + (layers - kept) / max(1, layers)) + (3.0 * prompt_len if split_prompt else 0)
         if best_cost is None or cost < best_cost * 0.98:  # a smaller micro-batch has to pay for its extra launches
             best, best_cost = m, cost
         if m % 2:
             break
         m //= 2
     return best
+
+
+class _PromptPass:
+    """The shared prompt, processed once per step.  Micro-batches read its last hidden state and per-layer keys /
+    values through fp32 leaves, which collect their gradients; ``backward`` then back-propagates the sums through the
+    prompt pass once."""
+
+    def __init__(self, model: LlamaModel, prompt_ids: torch.Tensor) -> None:
+        self.last_state, self.kv = model.prefix_states(prompt_ids)
+        leaf = lambda t: t.detach().float().requires_grad_(True)
+        self.last_leaf = leaf(self.last_state)
+        self.kv_leaves = [(leaf(k), leaf(v)) for k, v in self.kv]
+
+    def inputs(self):
+        dtype = self.last_state.dtype
+        return self.last_leaf.to(dtype), [(k.to(dtype), v.to(dtype)) for k, v in self.kv_leaves]
+
+    def backward(self) -> None:
+        outputs, grads = [self.last_state], [self.last_leaf.grad]
+        for (k, v), (k_leaf, v_leaf) in zip(self.kv, self.kv_leaves):
+            outputs += [k, v]
+            grads += [k_leaf.grad, v_leaf.grad]
+        keep = [(o, g.to(o.dtype)) for o, g in zip(outputs, grads) if g is not None]
+        torch.autograd.backward([o for o, _ in keep], [g for _, g in keep])
 
 
 class GRPOTrainer:
@@ -181,6 +241,7 @@ class GRPOTrainer:
     unmasked tokens, so the step optimises the same token-mean loss as a single pass."""
 
     retry_on_out_of_memory = True
+    cache_prompt = True  # micro-batches attend to the prompt's cached keys / values instead of re-processing it
 
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False,
@@ -201,10 +262,13 @@ class GRPOTrainer:
         op = kernel_registry.get_op("grpo_loss")
         return op.group_advantages(batch.rewards.float(), samples_per_prompt=batch.rewards.numel(), eps=self.adv_eps)
 
-    def loss_with_advantages(self, batch: GRPOBatch, adv: torch.Tensor):
+    def loss_with_advantages(self, batch: GRPOBatch, adv: torch.Tensor, prefix: Optional["_PromptPass"] = None):
         from rl_engine.kernels.registry import kernel_registry
 
-        logp = self.policy_logps(batch)
+        if prefix is None:
+            logp = self.policy_logps(batch)
+        else:
+            logp = policy_logps_after_prefix(self.model, batch, *prefix.inputs())
         return kernel_registry.get_op("grpo_loss").apply_from_logps(
             logp, batch.ref_logps, batch.old_logps, adv, batch.completion_mask, clip_eps=self.clip_eps, beta=self.beta
         )
@@ -222,7 +286,10 @@ class GRPOTrainer:
         if key not in self._micro_choice:
             estimate = getattr(self.model, "estimate_kept_layers", None)
             layers = self.model.cfg.num_layers
-            self._micro_choice[key] = g if estimate is None else choose_micro_group(g, key[2], l, layers, estimate)
+            supported = getattr(self.model, "supports_prefix_cache", None)
+            once = bool(self.cache_prompt and supported is not None and supported())
+            self._micro_choice[key] = (g if estimate is None
+                                       else choose_micro_group(g, key[2], l, layers, estimate, prompt_once=once))
         return self._micro_choice[key]
 
     def forward_backward(self, batch: GRPOBatch) -> torch.Tensor:
@@ -236,13 +303,23 @@ class GRPOTrainer:
         adv = self.advantages(batch)
         unmasked = batch.completion_mask.sum().clamp_min(1).float()
         total = torch.zeros((), dtype=torch.float32, device=batch.completion_ids.device)
+        prefix = self.prompt_pass(batch)
         for i0 in range(0, g, m):
             part = batch.completions(i0, min(g, i0 + m))
-            loss, _pl, _kl = self.loss_with_advantages(part, adv[i0:i0 + m].contiguous())
+            loss, _pl, _kl = self.loss_with_advantages(part, adv[i0:i0 + m].contiguous(), prefix)
             weighted = loss * (part.completion_mask.sum().float() / unmasked)
             weighted.backward()
             total += weighted.detach()
+        if prefix is not None:
+            prefix.backward()
         return total
+
+    def prompt_pass(self, batch: GRPOBatch) -> Optional["_PromptPass"]:
+        """Runs the shared prompt once for all micro-batches if the model supports prefix-cached passes."""
+        supported = getattr(self.model, "supports_prefix_cache", None)
+        if not self.cache_prompt or supported is None or not supported():
+            return None
+        return _PromptPass(self.model, batch.prompt_ids)
 
     def before_optimizer_step(self) -> None:
         """Hook for trainers whose gradients need a reduction that the optimiser kernel does not do."""

@@ -118,6 +118,84 @@ class _FusedAttentionBlock(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None
 
 
+def _unrotate_into(dqkv, dq, dk, dv, positions, cos_t, sin_t, hq, hkv):
+    """Gradients w.r.t. rotated q / k (and v) -> gradient of the packed, unrotated qkv projection output."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    ext = require_ext()
+    ext.rope(dq, positions, cos_t, sin_t, True, dqkv[:, :hq])
+    ext.rope(dk, positions, cos_t, sin_t, True, dqkv[:, hq : hq + hkv])
+    dqkv[:, hq + hkv :].copy_(dv)
+    return dqkv
+
+
+class _FusedAttentionBlockKV(torch.autograd.Function):
+    """``_FusedAttentionBlock`` that also returns copies of the rotated k and v, for a prefix (prompt) whose keys and
+    values later passes attend to.  Their gradients come back as extra inputs of the backward pass."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_t, sin_t, layout, hq, hkv, scale):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+
+        ext = require_ext()
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        ext.rope(q, positions, cos_t, sin_t, False, q)
+        ext.rope(k, positions, cos_t, sin_t, False, k)
+        out, lse = packed_attention_forward(q, k, v, layout, scale, True)
+        ctx.save_for_backward(qkv, out, lse, positions, cos_t, sin_t)
+        ctx.meta = (layout, hq, hkv, scale)
+        return out, k.contiguous(), v.contiguous()
+
+    @staticmethod
+    def backward(ctx, dout, dk_later, dv_later):
+        from rl_engine.kernels.ops.sm100.attention_bwd import packed_attention_backward
+
+        qkv, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
+        layout, hq, hkv, scale = ctx.meta
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        dq, dk, dv = packed_attention_backward(q, k, v, out, lse, dout.contiguous(), layout, scale)
+        if dk_later is not None:
+            dk = (dk.float() + dk_later.float()).to(dk.dtype)
+        if dv_later is not None:
+            dv = (dv.float() + dv_later.float()).to(dv.dtype)
+        dqkv = _unrotate_into(torch.empty_like(qkv), dq, dk, dv, positions, cos_t, sin_t, hq, hkv)
+        return dqkv, None, None, None, None, None, None, None
+
+
+class _FusedAttentionBlockPrefix(torch.autograd.Function):
+    """Attention of a pass that holds only suffix tokens: keys / values are ``[prefix | this pass]``, the prefix part
+    (already rotated) coming from ``_FusedAttentionBlockKV`` of an earlier pass.  ``layout`` indexes queries in this
+    pass's rows and keys in the concatenation."""
+
+    @staticmethod
+    def forward(ctx, qkv, k_prefix, v_prefix, positions, cos_t, sin_t, layout, hq, hkv, scale):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+
+        ext = require_ext()
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        ext.rope(q, positions, cos_t, sin_t, False, q)
+        ext.rope(k, positions, cos_t, sin_t, False, k)
+        out, lse = packed_attention_forward(q, torch.cat([k_prefix, k]), torch.cat([v_prefix, v]), layout, scale, True)
+        ctx.save_for_backward(qkv, k_prefix, v_prefix, out, lse, positions, cos_t, sin_t)
+        ctx.meta = (layout, hq, hkv, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from rl_engine.kernels.ops.sm100.attention_bwd import packed_attention_backward
+
+        qkv, k_prefix, v_prefix, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
+        layout, hq, hkv, scale = ctx.meta
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        n = k_prefix.shape[0]
+        dq, dk, dv = packed_attention_backward(q, torch.cat([k_prefix, k]), torch.cat([v_prefix, v]), out, lse,
+                                               dout.contiguous(), layout, scale)
+        dqkv = _unrotate_into(torch.empty_like(qkv), dq, dk[n:], dv[n:], positions, cos_t, sin_t, hq, hkv)
+        return dqkv, dk[:n], dv[:n], None, None, None, None, None, None, None
+
+
 class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
                  activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192) -> None:
@@ -222,7 +300,8 @@ class LlamaModel(nn.Module):
         return {k: v.detach() for k, v in self.named_views().items()}
 
     # -- forward ----------------------------------------------------------------------------
-    def _attention(self, qkv: torch.Tensor, positions: torch.Tensor, layout, index: int = 0) -> torch.Tensor:
+    def _attention(self, qkv: torch.Tensor, positions: torch.Tensor, layout, index: int = 0, k_prefix=None,
+                   v_prefix=None, return_kv: bool = False):
         cfg = self.cfg
         t = qkv.shape[0]
         qkv3 = qkv.view(t, cfg.num_heads + 2 * cfg.num_kv_heads, cfg.head_dim)
@@ -233,10 +312,15 @@ class LlamaModel(nn.Module):
             kn = rms_norm(qkv3[:, hq : hq + hkv].reshape(-1, cfg.head_dim), self.view(f"l{index}.k_norm"), cfg.rms_eps)
             qkv3 = torch.cat([qn.view(t, hq, -1), kn.view(t, hkv, -1), qkv3[:, hq + hkv :]], dim=1)
         if _fused_path(qkv) and cfg.head_dim == 128:
-            out = _FusedAttentionBlock.apply(
-                qkv3, positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale
-            )
-            return out.reshape(t, cfg.q_dim)
+            tail = (positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale)
+            if return_kv:
+                out, k_rot, v_rot = _FusedAttentionBlockKV.apply(qkv3, *tail)
+                return out.reshape(t, cfg.q_dim), k_rot, v_rot
+            if k_prefix is not None:
+                return _FusedAttentionBlockPrefix.apply(qkv3, k_prefix, v_prefix, *tail).reshape(t, cfg.q_dim)
+            return _FusedAttentionBlock.apply(qkv3, *tail).reshape(t, cfg.q_dim)
+        if return_kv or k_prefix is not None:
+            raise RuntimeError("prefix-cached passes need the fused attention path (CUDA, bf16, head_dim 128)")
         from rl_engine.kernels.registry import kernel_registry
 
         rope = kernel_registry.get_op("rope")
@@ -246,17 +330,31 @@ class LlamaModel(nn.Module):
         out = reference_packed_attention(q, k, v, layout.host_seqs, layout.causal, scale)
         return out.reshape(t, cfg.q_dim)
 
-    def _layer(self, x: torch.Tensor, index: int, positions: torch.Tensor, layout) -> torch.Tensor:
+    def _layer(self, x: torch.Tensor, index: int, positions: torch.Tensor, layout, k_prefix=None, v_prefix=None,
+               return_kv: bool = False):
+        """One decoder layer.  ``k_prefix`` / ``v_prefix``: rotated keys / values of a prefix that is not part of ``x``;
+        ``return_kv``: also return this pass's rotated keys and values (``(x, k, v)``)."""
         cfg = self.cfg
         p = lambda n: self.view(f"l{index}.{n}")
         lean = _fused_path(x)  # recompute normalised inputs and the SwiGLU output in backward instead of keeping them
         if lean:
-            from rl_engine.kernels.ops.sm100.lean_blocks import norm_linear, swiglu_linear
+            from rl_engine.kernels.ops.sm100.lean_blocks import norm_linear
 
             qkv = norm_linear(x, p("attn_norm"), p("wqkv"), cfg.rms_eps)
         else:
             qkv = linear(rms_norm(x, p("attn_norm"), cfg.rms_eps), p("wqkv"))
-        x = x + linear(self._attention(qkv, positions, layout, index), p("wo"))
+        attn = self._attention(qkv, positions, layout, index, k_prefix, v_prefix, return_kv)
+        if return_kv:
+            attn, k_rot, v_rot = attn
+        x = x + linear(attn, p("wo"))
+        x = self._ffn(x, index, lean)
+        return (x, k_rot, v_rot) if return_kv else x
+
+    def _ffn(self, x: torch.Tensor, index: int, lean: bool) -> torch.Tensor:
+        cfg = self.cfg
+        p = lambda n: self.view(f"l{index}.{n}")
+        if lean:
+            from rl_engine.kernels.ops.sm100.lean_blocks import norm_linear, swiglu_linear
         if cfg.num_experts:
             from rl_engine.kernels.registry import kernel_registry
 
@@ -311,6 +409,43 @@ class LlamaModel(nn.Module):
                 x = checkpoint(self._layer, x, i, positions, layout, use_reentrant=False)
             else:
                 x = self._layer(x, i, positions, layout)
+        return rms_norm(x, self.view("final_norm"), self.cfg.rms_eps)
+
+    # -- prefix-cached passes: the shared prompt runs once, later passes hold only completion tokens ------------
+    def supports_prefix_cache(self) -> bool:
+        cfg = self.cfg
+        return (self.flat.is_cuda and self.flat.dtype == torch.bfloat16 and cfg.head_dim == 128 and not cfg.num_experts)
+
+    def prefix_states(self, prompt_ids: torch.Tensor):
+        """One pass over the prompt alone: ``(final-norm hidden state of its last token [1, H], [(k, v)] per layer)``
+        with the rotated keys / values ``[P, Hkv, 128]`` every later pass attends to.  All outputs carry the
+        autograd graph of the prompt pass."""
+        from rl_engine.kernels.ops.sm100.attention import make_layout
+        from rl_engine.kernels.registry import kernel_registry
+
+        n = prompt_ids.numel()
+        positions = torch.arange(n, device=prompt_ids.device)
+        layout = make_layout([(0, n, 0, 0, 0, n)], True, prompt_ids.device)
+        x = kernel_registry.get_op("embedding")(prompt_ids, self.view("embed"))
+        kv = []
+        for i in range(self.cfg.num_layers):
+            x, k_rot, v_rot = self._layer(x, i, positions, layout, return_kv=True)
+            kv.append((k_rot, v_rot))
+        return rms_norm(x[-1:], self.view("final_norm"), self.cfg.rms_eps), kv
+
+    def hidden_states_after_prefix(self, token_ids: torch.Tensor, positions: torch.Tensor, layout, kv) -> torch.Tensor:
+        """Final-norm hidden states ``[T, H]`` of tokens that follow a prefix given by its per-layer ``kv``.
+        ``layout`` indexes queries in ``token_ids`` and keys in ``[prefix | token_ids]``."""
+        from rl_engine.kernels.registry import kernel_registry
+
+        x = kernel_registry.get_op("embedding")(token_ids, self.view("embed"))
+        training = torch.is_grad_enabled()
+        first_kept = self.cfg.num_layers - (self.plan_checkpointing(token_ids.numel()) if training else 0)
+        for i, (k_prefix, v_prefix) in enumerate(kv):
+            if training and i < first_kept:
+                x = checkpoint(self._layer, x, i, positions, layout, k_prefix, v_prefix, use_reentrant=False)
+            else:
+                x = self._layer(x, i, positions, layout, k_prefix, v_prefix)
         return rms_norm(x, self.view("final_norm"), self.cfg.rms_eps)
 
     def lm_head_weight(self) -> torch.Tensor:

@@ -571,3 +571,52 @@ def test_lean_blocks_match_the_unfused_composition_bitwise_and_the_fp32_referenc
     ref2.backward(dy2.float())
     for got, want in zip(lean2, (ref2.detach(), guf.grad, w2f.grad)):
         assert (got.float() - want).abs().max() / want.abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("prompt_len,completion_len", [(128, 128), (100, 72)])
+def test_prompt_cached_micro_batches_match_the_single_pass(prompt_len, completion_len):
+    """The shared prompt runs once; micro-batches of completions attend to its cached keys / values and send their
+    gradients back through fp32 leaves.  Log-probs must equal the single pass (bitwise when the prompt and completion
+    lengths are multiples of the 128-row tile, so that every row sees the same tiles in the same order), and the
+    accumulated gradients must agree with the single pass to bf16 rounding."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.grpo import (GRPOTrainer, _PromptPass, policy_logps, policy_logps_after_prefix,
+                                       synthetic_batch)
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("prefix", 1024, 256, 3, 4, 2, 128, 512)
+    host = synthetic_batch(cfg.vocab_size, prompt_len=prompt_len, group=6, completion_len=completion_len, seed=9)
+    host.completion_mask[2, completion_len // 2:] = False
+    batch = host.to("cuda")
+    model = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=12)
+    assert model.supports_prefix_cache()
+    with torch.no_grad():
+        full = policy_logps(model, batch)
+        prefix = _PromptPass(model, batch.prompt_ids)
+        parts = [policy_logps_after_prefix(model, batch.completions(i, i + 2), *prefix.inputs()) for i in (0, 2, 4)]
+    cached = torch.cat(parts)
+    if prompt_len % 128 == 0 and completion_len % 128 == 0:
+        assert torch.equal(cached, full)
+    else:
+        assert torch.allclose(cached, full, atol=2e-2, rtol=2e-2)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    batch.old_logps = full + 0.05 * torch.randn(full.shape, device="cuda", generator=gen)
+    batch.ref_logps = full + 0.05 * torch.randn(full.shape, device="cuda", generator=gen)
+
+    results = {}
+    for name, micro, cache in (("single", None, False), ("micro", 2, False), ("cached", 2, True)):
+        m = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=12)
+        trainer = GRPOTrainer(m, lr=1e-3, micro_group=micro)
+        trainer.cache_prompt = cache
+        trainer.opt.zero_grad()
+        loss = trainer.forward_backward(batch)
+        results[name] = (float(loss), m.flat_grad.float().clone())
+    ref_loss, ref_grad = results["single"]
+    for name in ("micro", "cached"):
+        loss, grad = results[name]
+        assert abs(loss - ref_loss) < 2e-3 * max(1.0, abs(ref_loss)), (name, loss, ref_loss)
+        rel = (grad - ref_grad).norm() / ref_grad.norm()
+        assert float(rel) < 2e-2, (name, float(rel))
+    # the embedding rows of prompt tokens receive gradient only through the prompt pass
+    emb = results["cached"][1][: cfg.vocab_size * cfg.hidden_size].view(cfg.vocab_size, cfg.hidden_size)
+    assert float(emb[host.prompt_ids.unique().cuda()].abs().sum()) > 0
