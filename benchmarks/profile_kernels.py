@@ -57,6 +57,26 @@ def case_gemm():
     return {"flops": 2.0 * m * n * k, "bytes": 2.0 * (m * k + n * k + m * n), "ms": ms, "shape": [m, n, k]}
 
 
+def case_gemm_fp8():
+    from rl_engine.kernels.ops.sm100.gemm_fp8 import gemm_fp8, quantize_rows
+
+    m, n, k = 8192, 14336, 4096
+    (aq, sa), (bq, sb) = quantize_rows(rand((m, k))), quantize_rows(rand((n, k), 0.02, 1))
+    pair = os.environ.get("PROFILE_FP8_PAIR", "1") != "0"
+    ms = timed(lambda: gemm_fp8(aq, sa, bq, sb, pair=pair))
+    return {"flops": 2.0 * m * n * k, "bytes": 1.0 * (m * k + n * k) + 2.0 * m * n, "ms": ms, "shape": [m, n, k],
+            "note": f"e4m3 x e4m3 with row-wise scales, bf16 out, pair={pair}; the fraction is against the bf16 cuBLAS peak"}
+
+
+def case_quantize_fp8():
+    from rl_engine.kernels.ops.sm100.gemm_fp8 import quantize_rows
+
+    m, k = 65536, 4096  # 537 MB in, 268 MB out
+    x = rand((m, k))
+    ms = timed(lambda: quantize_rows(x))
+    return {"flops": 0.0, "bytes": 3.0 * m * k, "ms": ms, "shape": [m, k], "note": "bf16 read twice (amax, convert) is counted once"}
+
+
 def case_gemm_wgrad():
     from rl_engine.kernels.ops.sm100.gemm import gemm
 

@@ -34,7 +34,8 @@ struct PairSmem {
   static constexpr int kDynamicBytes = kBytes + 1024;
 };
 
-template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi>
+// ELT: bytes per operand element (2 = bf16, 1 = e4m3 with K-major operands), as in the single-CTA kernel.
+template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi, int ELT = 2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        const GemmProblem p, const __grid_constant__ typename Epi::Params ep, uint32_t* __restrict__ err,
@@ -42,6 +43,8 @@ gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   using L = PairSmem<BN, STAGES, Epi::kStagingBytes>;
   static_assert(BN == 256, "the pair kernel uses 256-wide N tiles (128 columns of B per CTA)");
   static_assert(Epi::kCommWarps == 0, "communication warps are not supported by the pair kernel");
+  static_assert(ELT == 2 || (ELT == 1 && !A_MN && !B_MN), "8-bit operands must be K-major");
+  constexpr int kBKElems = kBK * 2 / ELT;  // elements of one 128-byte k-block
   constexpr uint32_t kTmemCols = 512;
   constexpr int kHalfN = BN / 2;
 
@@ -100,7 +103,7 @@ gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             uint8_t* sb = sa + L::kABytes;
             if (cta == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
             const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
-            const int k0 = kb * kBK;
+            const int k0 = kb * kBKElems;
             if constexpr (!A_MN) {
               tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);
             } else {
@@ -124,7 +127,7 @@ gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (even CTA only) ------------------------------
     if (lane == 0 && cta == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kPairBM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = ELT == 1 ? umma_idesc_e4m3(kPairBM, BN) : umma_idesc_bf16(kPairBM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -146,7 +149,8 @@ gemm_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                                        : umma_smem_desc_sw128(sa + k * 32, 16, 1024);
               const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * 2048, 8192, 1024)
                                        : umma_smem_desc_sw128(sb + k * 32, 16, 1024);
-              umma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              if constexpr (ELT == 1) umma_f8_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              else umma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit_pair(&empty_bar[stage]);  // frees this stage in both CTAs
             if (++stage == STAGES) {

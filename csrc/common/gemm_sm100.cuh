@@ -194,13 +194,17 @@ constexpr int gemm_threads() {
   return kGemmThreads + 32 * Epi::kCommWarps;
 }
 
-template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi>
+// ELT: bytes per operand element.  2 = bf16 (kind::f16, 64 elements per 128-byte k-block); 1 = e4m3 (kind::f8f6f4,
+// 128 elements per k-block, K-major operands only).  Tile bytes, swizzle and descriptors are the same for both.
+template <int BN, bool A_MN, bool B_MN, int STAGES, class Epi, int ELT = 2>
 __global__ void __launch_bounds__(gemm_threads<Epi>(), 1)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmProblem p, const __grid_constant__ typename Epi::Params ep, uint32_t* __restrict__ err,
                   const uint32_t kernel_id) {
   using L = GemmSmem<BN, STAGES, Epi::kStagingBytes>;
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
+  static_assert(ELT == 2 || (ELT == 1 && !A_MN && !B_MN), "8-bit operands must be K-major");
+  constexpr int kBKElems = kBK * 2 / ELT;  // elements of one 128-byte k-block
   constexpr uint32_t kTmemCols = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
   static_assert(kTmemCols <= 256 || L::kDynamicBytes > 116 * 1024,
                 "a kernel that takes all of TMEM must not share its SM with another CTA");
@@ -258,7 +262,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             uint8_t* sa = smem + stage * L::kStageBytes;
             uint8_t* sb = sa + L::kABytes;
             mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
-            const int k0 = geo.k_row0 + kb * kBK;
+            const int k0 = geo.k_row0 + kb * kBKElems;
             if constexpr (!A_MN) {
               tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
             } else {
@@ -283,7 +287,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = ELT == 1 ? umma_idesc_e4m3(kBM, BN) : umma_idesc_bf16(kBM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -307,7 +311,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                        : umma_smem_desc_sw128(sa + k * 32, 16, 1024);
               const uint64_t db = B_MN ? umma_smem_desc_sw128(sb + k * 2048, 8192, 1024)
                                        : umma_smem_desc_sw128(sb + k * 32, 16, 1024);
-              umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              if constexpr (ELT == 1) umma_f8(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              else umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             }
             umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
             if (++stage == STAGES) {

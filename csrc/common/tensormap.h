@@ -61,6 +61,25 @@ inline CUtensorMap make_tmap_2d_bf16(const void* base, uint64_t rows, uint64_t c
   return m;
 }
 
+// 2-D row-major tensor of 8-bit elements [rows, cols] (pitch `ld` bytes); box_cols <= 128 with the 128-byte swizzle.
+inline CUtensorMap make_tmap_2d_u8(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                                   uint32_t box_cols) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) throw std::invalid_argument("TMA base must be 16-byte aligned");
+  if (ld % 16 != 0) throw std::invalid_argument("TMA row pitch must be a multiple of 16 bytes");
+  CUtensorMap m;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_tiled_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    throw std::runtime_error("rl_engine: cuTensorMapEncodeTiled(u8) failed with code " + std::to_string(int(r)));
+  }
+  return m;
+}
+
 // 3-D variant: [batch, rows, cols] with explicit row and batch pitches (elements).
 inline CUtensorMap make_tmap_3d_bf16(const void* base, uint64_t batch, uint64_t rows, uint64_t cols, uint64_t row_ld,
                                      uint64_t batch_ld, uint32_t box_rows, uint32_t box_cols) {

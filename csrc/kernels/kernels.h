@@ -39,6 +39,15 @@ struct GemmArgs {
 };
 void gemm_bf16(const GemmArgs& args, cudaStream_t stream);
 
+// fp8 (e4m3) GEMM with one fp32 scale per row of A and per row of B: D[M, N] (bf16) = (A_q B_q^T) * sa[m] * sb[n].
+// Operands are K-major codes with row pitches (bytes) that are multiples of 16.
+void gemm_fp8_rowscaled(const void* a_q, long long lda, const float* scale_a, const void* b_q, long long ldb,
+                        const float* scale_b, void* d, long long ldd, int M, int N, int K, bool cta_pair, int sm_count,
+                        uint32_t* err, cudaStream_t stream);
+// bf16 rows -> e4m3 codes and per-row scale (amax / 448); columns [cols, ldq) of the code rows are zero-filled.
+void quantize_rows_e4m3(const void* x, long long ldx, long long rows, int cols, void* q, long long ldq, float* scale,
+                        cudaStream_t stream);
+
 // ----------------------------------------------------------------- fused linear -> log-prob
 struct LinearLogpFwdArgs {
   const __nv_bfloat16* hidden;  // [n_tokens, hidden_dim]

@@ -129,6 +129,51 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optiona
   return d;
 }
 
+// x [rows, cols] bf16 -> (e4m3 codes [rows, cols] as uint8, fp32 scale per row) with x ~= code * scale.
+std::vector<Tensor> quantize_fp8_rows(const Tensor& x) {
+  check_rowmajor(x, "x");
+  TORCH_CHECK(x.scalar_type() == torch::kBFloat16, "rl_engine.quantize_fp8_rows: bf16 input only");
+  TORCH_CHECK(x.size(1) % 16 == 0, "rl_engine.quantize_fp8_rows: the row length must be a multiple of 16");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kUInt8));
+  Tensor scale = torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32));
+  if (x.numel()) {
+    rlk::quantize_rows_e4m3(x.data_ptr(), x.stride(0), x.size(0), static_cast<int>(x.size(1)), q.data_ptr(), q.stride(0),
+                            scale.data_ptr<float>(), stream_of(x));
+    after_launch();
+  }
+  return {q, scale};
+}
+
+// D[M, N] bf16 = (A_q[M, K] @ B_q[N, K]^T) * scale_a[:, None] * scale_b[None, :]; e4m3 codes as uint8.
+Tensor gemm_fp8(const Tensor& a_q, const Tensor& scale_a, const Tensor& b_q, const Tensor& scale_b, int64_t pair) {
+  check_rowmajor(a_q, "a_q");
+  check_rowmajor(b_q, "b_q");
+  TORCH_CHECK(a_q.scalar_type() == torch::kUInt8 && b_q.scalar_type() == torch::kUInt8,
+              "rl_engine.gemm_fp8: operands are e4m3 codes stored as uint8");
+  TORCH_CHECK(a_q.size(1) == b_q.size(1), "rl_engine.gemm_fp8: contraction sizes differ");
+  TORCH_CHECK(a_q.stride(0) % 16 == 0 && b_q.stride(0) % 16 == 0, "rl_engine.gemm_fp8: row pitch must be a multiple of 16 bytes");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(a_q.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b_q.data_ptr()) % 16 == 0,
+              "rl_engine.gemm_fp8: operands must be 16-byte aligned");
+  auto check_scale = [](const Tensor& s, int64_t n, const char* name) {
+    TORCH_CHECK(s.is_cuda() && s.scalar_type() == torch::kFloat32 && s.is_contiguous() && s.numel() == n,
+                "rl_engine.gemm_fp8: ", name, " must be a contiguous float32 vector with one entry per row");
+  };
+  check_scale(scale_a, a_q.size(0), "scale_a");
+  check_scale(scale_b, b_q.size(0), "scale_b");
+  const c10::cuda::CUDAGuard guard(a_q.device());
+  const int64_t M = a_q.size(0), N = b_q.size(0), K = a_q.size(1);
+  Tensor d = torch::empty({M, N}, a_q.options().dtype(torch::kBFloat16));
+  if (M == 0 || N == 0) return d;
+  if (K == 0) return d.zero_();
+  rlk::gemm_fp8_rowscaled(a_q.data_ptr(), a_q.stride(0), scale_a.data_ptr<float>(), b_q.data_ptr(), b_q.stride(0),
+                          scale_b.data_ptr<float>(), d.data_ptr(), d.stride(0), static_cast<int>(M), static_cast<int>(N),
+                          static_cast<int>(K), pair < 0 ? (gemm_pair_default() && M > 128) : pair != 0,
+                          sm_count_of(a_q.get_device()), err_ptr(a_q), stream_of(a_q));
+  after_launch();
+  return d;
+}
+
 // --------------------------------------------------------------- tensor-parallel fused linears
 void fill_peers(void** dst, const std::vector<uint64_t>& src, const char* what) {
   TORCH_CHECK(!src.empty() && src.size() <= 8, "rl_engine.tp: need 1..8 addresses for ", what);
@@ -1138,6 +1183,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("surrogate_fwd", rlk::traced("rlk::surrogate_fwd", &surrogate_fwd));
   m.def("surrogate_bwd", rlk::traced("rlk::surrogate_bwd", &surrogate_bwd));
   m.def("dpo_fwd", rlk::traced("rlk::dpo_fwd", &dpo_fwd));
+  m.def("quantize_fp8_rows", rlk::traced("rlk::quantize_fp8_rows", &quantize_fp8_rows));
+  m.def("gemm_fp8", rlk::traced("rlk::gemm_fp8", &gemm_fp8), py::arg("a_q"), py::arg("scale_a"), py::arg("b_q"),
+        py::arg("scale_b"), py::arg("pair") = -1);
   m.def("rmsnorm_fwd", rlk::traced("rlk::rmsnorm_fwd", &rmsnorm_fwd));
   m.def("rmsnorm_bwd", rlk::traced("rlk::rmsnorm_bwd", &rmsnorm_bwd));
   m.def("swiglu_fwd", rlk::traced("rlk::swiglu_fwd", &swiglu_fwd));

@@ -88,3 +88,36 @@ def test_cta_pair_gemm_matches_single_cta_bitwise_on_a_large_problem():
     w = _rand((2048, 1536), 9)
     assert torch.equal(gemm(a, w, b_mn=True, pair=False), gemm(a, w, b_mn=True, pair=True))
     check_device_errors(0)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (300, 1000, 1168), (1024, 4096, 4096), (77, 264, 144)])
+def test_fp8_gemm_matches_the_dequantised_fp32_product(m, n, k):
+    """The kernel multiplies e4m3 codes exactly (fp32 accumulation) and applies the row / channel scales in the
+    epilogue, so it must agree with the fp32 product of the dequantised operands to bf16 output rounding; the
+    quantiser must agree with a PyTorch restatement code for code."""
+    from rl_engine.kernels.ops.base import check_device_errors
+    from rl_engine.kernels.ops.sm100.gemm_fp8 import (Fp8Linear, gemm_fp8, matmul_nt_fp8, quantize_rows,
+                                                      quantize_rows_reference)
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(n, k, device="cuda", generator=g)).to(torch.bfloat16)
+    x[3] = 0  # an all-zero row gets scale 1 and zero codes
+    xq, xs = quantize_rows(x)
+    wq, ws = quantize_rows(w)
+    xq_ref, xs_ref = quantize_rows_reference(x)
+    assert torch.allclose(xs, xs_ref, rtol=2e-7, atol=0)
+    same = xq.view(torch.float8_e4m3fn).float() == xq_ref.float()
+    assert float(same.float().mean()) > 0.999  # a scale that differs in its last bit may move a code at a rounding tie
+    ref = (xq.view(torch.float8_e4m3fn).float() * xs[:, None]) @ (wq.view(torch.float8_e4m3fn).float() * ws[:, None]).t()
+    out = gemm_fp8(xq, xs, wq, ws)
+    assert out.dtype == torch.bfloat16 and out.shape == (m, n)
+    assert (out.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    assert torch.equal(out, gemm_fp8(xq, xs, wq, ws))  # run to run
+    assert torch.equal(gemm_fp8(xq, xs, wq, ws, pair=True), gemm_fp8(xq, xs, wq, ws, pair=False))  # both tile engines
+    # against the unquantised product: e4m3 has a 3-bit mantissa, errors average out over K
+    full = x.float() @ w.float().t()
+    rel = (out.float() - full).norm() / full.norm()
+    assert float(rel) < 6e-2
+    assert torch.equal(matmul_nt_fp8(x, wq, ws), out) and torch.equal(Fp8Linear(w)(x), out)
+    check_device_errors(0)
