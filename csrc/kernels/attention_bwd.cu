@@ -31,6 +31,14 @@ __device__ unsigned long long g_attn_bwd_prof[16];
     atomicAdd(&g_attn_bwd_prof[slot], now - prof_t);    \
     prof_t = now;                                       \
   }
+// The same for the MMA-issuing thread of the profiled CTA (slots 8..15): waits and issue sections.
+#define MPROF_DECL unsigned long long mprof_t = clock64(); const bool mprof_on = (blockIdx.x == gridDim.x / 2)
+#define MPROF(slot)                                          \
+  if (mprof_on) {                                            \
+    const unsigned long long now = clock64();                \
+    atomicAdd(&g_attn_bwd_prof[8 + slot], now - mprof_t);    \
+    mprof_t = now;                                           \
+  }
 void attention_bwd_profile_read(unsigned long long* out) {
   cudaMemcpyFromSymbol(out, g_attn_bwd_prof, sizeof(unsigned long long) * 16);
   unsigned long long z[16] = {0};
@@ -39,6 +47,8 @@ void attention_bwd_profile_read(unsigned long long* out) {
 #else
 #define BPROF_DECL
 #define BPROF(slot)
+#define MPROF_DECL
+#define MPROF(slot)
 #endif
 
 namespace {
@@ -111,8 +121,8 @@ struct DqSmem {
   static constexpr int kKV = 65536;
   static constexpr int kDS = kKV + kStages * kStageBytes;  // 2 buffers of [128 x 64] bf16 = 16 KB each
   static constexpr int kBars = kDS + 2 * kAtom128;
-  // qdo_full, kv_full[4], kv_empty[4], s_full[2], s_empty[2], ds_full[2], ds_empty[2]
-  static constexpr int kNumBars = 17;
+  // qdo_full, kv_full[4], kv_empty[4], s_full[2], s_empty[2], ds_full[2], ds_empty[2], dq_done
+  static constexpr int kNumBars = 18;
   static constexpr int kDynamic = kBars + kNumBars * 8 + 16 + 1024;
 };
 static_assert(DqSmem::kDynamic <= 232448 && DqSmem::kDynamic > 116 * 1024, "dQ kernel shared memory out of range");
@@ -133,7 +143,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* s_empty = s_full + 2;
   uint64_t* ds_full = s_empty + 2;
   uint64_t* ds_empty = ds_full + 2;
-  static_assert(1 + 2 * DqSmem::kStages + 8 == DqSmem::kNumBars, "dQ barrier layout");
+  uint64_t* dq_done = ds_empty + 2;  // all dQ MMAs of this CTA have completed
+  static_assert(1 + 2 * DqSmem::kStages + 9 == DqSmem::kNumBars, "dQ barrier layout");
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + DqSmem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -163,6 +174,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&ds_full[b], 4);
       mbar_init(&ds_empty[b], 1);
     }
+    mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -207,11 +219,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t sq = smem_u32(smem + DqSmem::kQ);
       const uint32_t sdo = smem_u32(smem + DqSmem::kDO);
       mbar_wait(qdo_full, 0, abort_flag, err, 210, 2);
+      MPROF_DECL;
       auto issue_dq = [&](int j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int stage = j % DqSmem::kStages;
+        MPROF(0);
         mbar_wait(&ds_full[b], ph, abort_flag, err, 210, 3);
+        MPROF(3);
         tc_fence_after();
         const uint32_t sds = smem_u32(smem + DqSmem::kDS + b * kAtom128);
         const uint32_t sk = smem_u32(smem + DqSmem::kKV + stage * DqSmem::kStageBytes);
@@ -223,14 +238,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
         umma_commit(&ds_empty[b]);
         umma_commit(&kv_empty[stage]);
+        MPROF(4);
       };
       for (int j = 0; j < n_tiles; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int stage = j % DqSmem::kStages;
         const uint32_t kv_phase = (j / DqSmem::kStages) & 1;
+        MPROF(0);
         mbar_wait(&kv_full[stage], kv_phase, abort_flag, err, 210, 4);
+        MPROF(5);
         mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 210, 5);
+        MPROF(1);
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + DqSmem::kKV + stage * DqSmem::kStageBytes);
         const uint32_t sv = sk + 2 * kAtom64;
@@ -249,11 +268,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                     umma_smem_desc_sw128(sv + offb, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[b]);
-        if (j >= 1) issue_dq(j - 1);
+        MPROF(2);
+        // dQ trails S / dP by TWO tiles: a compute group releases its S / dP buffer as soon as the values are in
+        // registers, so S, dP of tile j + 1 are issued before this thread blocks on the dS of tile j - 1, and each
+        // group finds its next S / dP ready when it finishes a tile.  (A K/V stage is held for three tiles; the ring
+        // has four.)
+        if (j >= 2) issue_dq(j - 2);
       }
+      if (n_tiles >= 2) issue_dq(n_tiles - 2);
       if (n_tiles >= 1) issue_dq(n_tiles - 1);
-      // dQ complete: reuse s_full[0] is not possible (phases); signal through ds_empty of the last tile,
-      // which the epilogue waits on below.
+      // A barrier of its own for "dQ complete": the groups must not take this from ds_empty of the last tile, because
+      // a group that does not own that buffer has not followed its phases and could see an older phase of the same
+      // parity as complete.
+      umma_commit(dq_done);
     }
   } else {
     const int quad = warp & 3;
@@ -304,8 +331,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
     // wait for the last dQ MMA, then write dQ * scale
     if (n_tiles >= 1) {
-      const int jl = n_tiles - 1;
-      mbar_wait(&ds_empty[jl & 1], (jl >> 1) & 1, abort_flag, err, 210, 8);
+      mbar_wait(dq_done, 0, abort_flag, err, 210, 8);
       tc_fence_after();
     }
     __nv_bfloat16* dst = dq + static_cast<long long>(sd.q_start + qi) * ld_dq + head * kD;
