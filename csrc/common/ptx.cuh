@@ -351,6 +351,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// The descriptor of the same matrix `byte_offset` further on in shared memory (a multiple of 16 bytes; the sum must
+// stay inside the 256 KB window, so the 14-bit address field cannot carry): one 32-bit add instead of rebuilding it.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t byte_offset) {
+  uint32_t lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(desc));
+  lo += byte_offset >> 4;
+  uint64_t out;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(out) : "r"(lo), "r"(hi));
+  return out;
+}
+
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 accumulate.
 //   [4,6) c fmt (1=f32)  [7,10) a fmt (1=bf16)  [10,13) b fmt  [15] a major (1=MN)  [16] b major
 //   [17,23) N>>3   [24,29) M>>4

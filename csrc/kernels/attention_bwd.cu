@@ -219,6 +219,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t sq = smem_u32(smem + DqSmem::kQ);
       const uint32_t sdo = smem_u32(smem + DqSmem::kDO);
       mbar_wait(qdo_full, 0, abort_flag, err, 210, 2);
+      // This thread's instruction stream is the kernel's critical path (20 MMAs per 64 keys), so every descriptor is
+      // built once: Q / dO operands are fixed, K / V / dS operands are stage 0 (buffer 0) plus one add per use.
+      const uint32_t skv0 = smem_u32(smem + DqSmem::kKV);
+      uint64_t desc_q[kD / 16], desc_do[kD / 16], desc_k0[kD / 16], desc_v0[kD / 16];
+#pragma unroll
+      for (int k = 0; k < kD / 16; ++k) {
+        const uint32_t offa = (k >> 2) * kAtom128 + (k & 3) * 32;
+        const uint32_t offb = (k >> 2) * kAtom64 + (k & 3) * 32;
+        desc_q[k] = umma_smem_desc_sw128(sq + offa, 16, 1024);
+        desc_do[k] = umma_smem_desc_sw128(sdo + offa, 16, 1024);
+        desc_k0[k] = umma_smem_desc_sw128(skv0 + offb, 16, 1024);
+        desc_v0[k] = umma_smem_desc_sw128(skv0 + 2 * kAtom64 + offb, 16, 1024);
+      }
+      uint64_t desc_ds0[TK / 16], desc_kt0[TK / 16];  // dS buffer 0 (K-major) and the K tile of stage 0 read MN-major
+#pragma unroll
+      for (int k = 0; k < TK / 16; ++k) {
+        desc_ds0[k] = umma_smem_desc_sw128(smem_u32(smem + DqSmem::kDS) + k * 32, 16, 1024);
+        desc_kt0[k] = umma_smem_desc_sw128(skv0 + k * 2048, kAtom64, 1024);
+      }
       MPROF_DECL;
       auto issue_dq = [&](int j) {
         const int b = j & 1;
@@ -228,13 +247,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_wait(&ds_full[b], ph, abort_flag, err, 210, 3);
         MPROF(3);
         tc_fence_after();
-        const uint32_t sds = smem_u32(smem + DqSmem::kDS + b * kAtom128);
-        const uint32_t sk = smem_u32(smem + DqSmem::kKV + stage * DqSmem::kStageBytes);
+        const uint32_t ds_off = b * kAtom128, kv_off = stage * DqSmem::kStageBytes;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {
-          const uint64_t da = umma_smem_desc_sw128(sds + k * 32, 16, 1024);
-          const uint64_t db = umma_smem_desc_sw128(sk + k * 2048, kAtom64, 1024);
-          umma_bf16(tmem + 256, da, db, idesc_dq, (j | k) != 0 ? 1u : 0u);
+          umma_bf16(tmem + 256, umma_desc_advance(desc_ds0[k], ds_off), umma_desc_advance(desc_kt0[k], kv_off), idesc_dq,
+                    (j | k) != 0 ? 1u : 0u);
         }
         umma_commit(&ds_empty[b]);
         umma_commit(&kv_empty[stage]);
@@ -251,22 +268,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 210, 5);
         MPROF(1);
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + DqSmem::kKV + stage * DqSmem::kStageBytes);
-        const uint32_t sv = sk + 2 * kAtom64;
+        const uint32_t kv_off = stage * DqSmem::kStageBytes;
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
-          const uint32_t offa = (k >> 2) * kAtom128 + (k & 3) * 32;
-          const uint32_t offb = (k >> 2) * kAtom64 + (k & 3) * 32;
-          umma_bf16(tmem + b * 64, umma_smem_desc_sw128(sq + offa, 16, 1024), umma_smem_desc_sw128(sk + offb, 16, 1024),
-                    idesc_s, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < kD / 16; ++k)
+          umma_bf16(tmem + b * 64, desc_q[k], umma_desc_advance(desc_k0[k], kv_off), idesc_s, k != 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
-          const uint32_t offa = (k >> 2) * kAtom128 + (k & 3) * 32;
-          const uint32_t offb = (k >> 2) * kAtom64 + (k & 3) * 32;
-          umma_bf16(tmem + 128 + b * 64, umma_smem_desc_sw128(sdo + offa, 16, 1024),
-                    umma_smem_desc_sw128(sv + offb, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
-        }
+        for (int k = 0; k < kD / 16; ++k)
+          umma_bf16(tmem + 128 + b * 64, desc_do[k], umma_desc_advance(desc_v0[k], kv_off), idesc_s, k != 0 ? 1u : 0u);
         umma_commit(&s_full[b]);
         MPROF(2);
         // dQ trails S / dP by TWO tiles: a compute group releases its S / dP buffer as soon as the values are in

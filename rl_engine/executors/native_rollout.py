@@ -1,8 +1,9 @@
 """Native rollout engine: G completions of one prompt with prefix-shared attention and the fused sampler.
 
-The prompt is stored once in the packed batch ``[prompt | completion_0 | ...]``; every decoding step
-re-runs the stateless forward over the packed tokens (no KV cache is kept between steps -- the same
-"stateless" trade the scoring executor makes) and draws the next token of every completion with the
+On the fused path the prompt is processed once and every decoding step runs the model on the G new tokens against a
+per-layer key / value cache (``LlamaModel.decode_step``, optionally with fp8 copies of the layer projections); the
+fallback keeps no state and re-runs the packed forward ``[prompt | completion_0 | ...]`` every step (the same
+"stateless" trade the scoring executor makes).  Both draw the next token of every completion with the
 ``sample_topk_topp`` kernel.  Rollout log-probs come from ``linear_logp``, the kernel the trainer
 differentiates, so training-time and rollout-time log-probs of the same tokens agree bitwise.
 The reference has no rollout engine of its own (it delegates to vLLM).
@@ -16,14 +17,72 @@ import torch
 
 
 class NativeRolloutEngine:
-    def __init__(self, model: torch.nn.Module, seed: int = 0) -> None:
+    """``use_kv_cache`` (default: whenever the model supports it): the prompt is processed once, every decoding step
+    runs the model on the G new tokens only and attends to per-layer key / value buffers ``[prompt | G x max_new]``.
+    ``fp8_linears``: the cached path multiplies with e4m3 copies of the layer projections (refresh them with
+    ``model.enable_fp8_inference()`` after weight updates).  Without the cache every step re-runs the packed forward."""
+
+    def __init__(self, model: torch.nn.Module, seed: int = 0, use_kv_cache: Optional[bool] = None,
+                 fp8_linears: bool = False) -> None:
         self.model = model
         self.seed = seed
         self._offset = 0
+        supported = getattr(model, "supports_prefix_cache", None)
+        can_cache = bool(supported is not None and supported())
+        self.use_kv_cache = can_cache if use_kv_cache is None else bool(use_kv_cache)
+        if self.use_kv_cache and not can_cache:
+            raise ValueError("this model does not support key / value cached decoding")
+        if fp8_linears:
+            if not self.use_kv_cache:
+                raise ValueError("fp8_linears needs the key / value cached path")
+            model.enable_fp8_inference()
 
     @torch.no_grad()
     def generate(self, prompt_ids: torch.Tensor, *, num_generations: int, max_new_tokens: int, temperature: float = 1.0,
                  top_k: Optional[int] = 50, top_p: Optional[float] = 1.0) -> Dict[str, Any]:
+        if self.use_kv_cache:
+            return self._generate_cached(prompt_ids, num_generations, max_new_tokens, temperature, top_k, top_p)
+        return self._generate_stateless(prompt_ids, num_generations, max_new_tokens, temperature, top_k, top_p)
+
+    def _generate_cached(self, prompt_ids, g: int, max_new_tokens: int, temperature, top_k, top_p) -> Dict[str, Any]:
+        from rl_engine.kernels.ops.sm100.attention import make_layout
+        from rl_engine.kernels.registry import kernel_registry
+        from rl_engine.kernels.sampling import SamplerBackend
+
+        model = self.model
+        dev = model.flat.device
+        prompt = prompt_ids.to(dev).long().reshape(-1)
+        p = prompt.numel()
+        sampler = SamplerBackend(seed=self.seed)
+        sampler._offset = self._offset
+        head = model.lm_head_weight()
+        lm_head = kernel_registry.get_op("lm_head")
+        draw = lambda hidden: sampler.sample(lm_head(hidden, head), top_k=top_k, top_p=top_p, temperature=temperature)
+        # prompt pass: last hidden state (predicts the first token of every completion) and per-layer keys / values
+        last_state, prompt_kv = model.prefix_states(prompt)
+        cache = model.new_kv_cache(p + g * max_new_tokens)
+        for (ck, cv), (pk, pv) in zip(cache, prompt_kv):
+            ck[:p].copy_(pk)
+            cv[:p].copy_(pv)
+        del prompt_kv
+        completions = torch.empty(g, max_new_tokens, dtype=torch.long, device=dev)
+        tokens = draw(last_state.expand(g, -1).contiguous()).reshape(g)
+        base = p + torch.arange(g, device=dev) * max_new_tokens  # first cache row of every completion
+        for step in range(max_new_tokens):
+            completions[:, step] = tokens
+            if step + 1 == max_new_tokens:
+                break
+            # the token drawn at `step` sits at position p + step; its query sees the prompt and its own rows so far
+            positions = torch.full((g,), p + step, dtype=torch.long, device=dev)
+            layout = make_layout([(i, 1, 0, p, p + i * max_new_tokens, step + 1) for i in range(g)], False, dev)
+            hidden = model.decode_step(tokens, positions, cache, base + step, layout)
+            tokens = draw(hidden).reshape(g)
+        self._offset = sampler._offset
+        logps = self.score(prompt, completions)
+        return {"prompt_ids": prompt, "completion_ids": completions, "rollout_logps": logps}
+
+    def _generate_stateless(self, prompt_ids, num_generations: int, max_new_tokens: int, temperature, top_k,
+                            top_p) -> Dict[str, Any]:
         from rl_engine.kernels.ops.sm100.attention import grpo_group_layout
         from rl_engine.kernels.registry import kernel_registry
         from rl_engine.kernels.sampling import SamplerBackend

@@ -205,6 +205,7 @@ class LlamaModel(nn.Module):
         super().__init__()
         self.cfg = cfg
         self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)
+        self._fp8_linears: Dict[str, object] = {}
         h, f = cfg.hidden_size, cfg.ffn_size
         qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab_size, h))]
@@ -447,6 +448,65 @@ class LlamaModel(nn.Module):
             else:
                 x = self._layer(x, i, positions, layout, k_prefix, v_prefix)
         return rms_norm(x, self.view("final_norm"), self.cfg.rms_eps)
+
+    # -- incremental decoding with a key / value cache (rollout side, no autograd) -------------------------
+    @torch.no_grad()
+    def new_kv_cache(self, rows: int):
+        """Per-layer ``(k, v)`` buffers ``[rows, Hkv, 128]`` for ``decode_step``."""
+        cfg = self.cfg
+        make = lambda: torch.empty(rows, cfg.num_kv_heads, cfg.head_dim, dtype=self.flat.dtype, device=self.flat.device)
+        return [(make(), make()) for _ in range(cfg.num_layers)]
+
+    @torch.no_grad()
+    def decode_step(self, token_ids: torch.Tensor, positions: torch.Tensor, cache, slots: torch.Tensor, layout) -> torch.Tensor:
+        """One new token for each of ``n`` sequences: final-norm hidden states ``[n, H]``.
+
+        The rotated key and value of token ``i`` are written to row ``slots[i]`` of every layer's cache before the
+        attention of that layer runs; ``layout`` (non-causal) gives each one-token query its key ranges in the cache
+        (shared prefix rows + its own rows up to and including ``slots[i]``)."""
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+        from rl_engine.kernels.registry import kernel_registry
+
+        if not self.supports_prefix_cache():
+            raise RuntimeError("decode_step needs the fused path (CUDA, bf16, head_dim 128, dense FFN)")
+        cfg, ext = self.cfg, require_ext()
+        hq, hkv = cfg.num_heads, cfg.num_kv_heads
+        scale = 1.0 / math.sqrt(cfg.head_dim)
+        n = token_ids.numel()
+        x = kernel_registry.get_op("embedding")(token_ids, self.view("embed"))
+        for i in range(cfg.num_layers):
+            p = lambda name: self.view(f"l{i}.{name}")
+            qkv = self._project(rms_norm(x, p("attn_norm"), cfg.rms_eps), f"l{i}.wqkv").view(n, hq + 2 * hkv, cfg.head_dim)
+            q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+            ext.rope(q, positions, self.rope_cos, self.rope_sin, False, q)
+            ext.rope(k, positions, self.rope_cos, self.rope_sin, False, k)
+            cache[i][0].index_copy_(0, slots, k)
+            cache[i][1].index_copy_(0, slots, v)
+            out, _ = packed_attention_forward(q, cache[i][0], cache[i][1], layout, scale, False)
+            x = x + self._project(out.reshape(n, cfg.q_dim), f"l{i}.wo")
+            gu = self._project(rms_norm(x, p("mlp_norm"), cfg.rms_eps), f"l{i}.w_gate_up")
+            x = x + self._project(swiglu_packed(gu), f"l{i}.w_down")
+        return rms_norm(x, self.view("final_norm"), cfg.rms_eps)
+
+    def _project(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        """``x @ W[name].T`` for inference-only passes: the fp8 copy of the weight if ``enable_fp8_inference`` made one."""
+        fp8 = self._fp8_linears.get(name) if self._fp8_linears else None
+        return fp8(x) if fp8 is not None else linear(x, self.view(name))
+
+    @torch.no_grad()
+    def enable_fp8_inference(self, enabled: bool = True) -> None:
+        """Quantise the layer projections to e4m3 codes with one scale per output channel (8 bits per weight more
+        memory) for ``decode_step``; training and scoring passes keep using the bf16 weights.  Call again after an
+        optimiser step to refresh the copies."""
+        self._fp8_linears = {}
+        if not enabled:
+            return
+        from rl_engine.kernels.ops.sm100.gemm_fp8 import Fp8Linear
+
+        for i in range(self.cfg.num_layers):
+            for n in ("wqkv", "wo", "w_gate_up", "w_down"):
+                self._fp8_linears[f"l{i}.{n}"] = Fp8Linear(self.view(f"l{i}.{n}"))
 
     def lm_head_weight(self) -> torch.Tensor:
         return self.view("lm_head")
