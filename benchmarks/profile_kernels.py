@@ -77,6 +77,39 @@ def case_quantize_fp8():
     return {"flops": 0.0, "bytes": 3.0 * m * k, "ms": ms, "shape": [m, k], "note": "bf16 read twice (amax, convert) is counted once"}
 
 
+def _decode_case(fp8: bool):
+    """One key / value cached decoding step of 4 Llama-3-8B layers: 32 completions at token 256 after a 1024-token
+    prompt.  Bytes = the layers' projection weights, which every step streams once."""
+    from rl_engine.models.config import llama3_8b
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = llama3_8b().with_layers(4)
+    model = LlamaModel(cfg, dtype=torch.bfloat16, device="cuda", seed=0, max_positions=2048)
+    if fp8:
+        model.enable_fp8_inference()
+    p, g, lmax, t = 1024, 32, 512, 256
+    cache = model.new_kv_cache(p + g * lmax)
+    for ck, cv in cache:
+        ck.normal_()
+        cv.normal_()
+    tokens = torch.randint(0, cfg.vocab_size, (g,), device="cuda")
+    pos = torch.full((g,), p + t, dtype=torch.long, device="cuda")
+    slots = p + torch.arange(g, device="cuda") * lmax + t
+    prefix_layout, own_layout = model.decode_layouts(g, p, lmax, t + 1)
+    ms = timed(lambda: model.decode_step(tokens, pos, cache, slots, prefix_layout, own_layout))
+    per_layer = cfg.hidden_size * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.hidden_size + 3 * cfg.hidden_size * cfg.ffn_size
+    return {"flops": 0.0, "bytes": (1.0 if fp8 else 2.0) * per_layer * cfg.num_layers, "ms": ms, "shape": [g, p, t, cfg.num_layers],
+            "note": ("fp8" if fp8 else "bf16") + " projections; 4 layers, embedding and final norm included, LM head not"}
+
+
+def case_decode_step():
+    return _decode_case(False)
+
+
+def case_decode_step_fp8():
+    return _decode_case(True)
+
+
 def case_gemm_wgrad():
     from rl_engine.kernels.ops.sm100.gemm import gemm
 

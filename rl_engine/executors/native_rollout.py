@@ -23,10 +23,11 @@ class NativeRolloutEngine:
     ``model.enable_fp8_inference()`` after weight updates).  Without the cache every step re-runs the packed forward."""
 
     def __init__(self, model: torch.nn.Module, seed: int = 0, use_kv_cache: Optional[bool] = None,
-                 fp8_linears: bool = False) -> None:
+                 fp8_linears: bool = False, use_cuda_graph: bool = True) -> None:
         self.model = model
         self.seed = seed
         self._offset = 0
+        self.use_cuda_graph = use_cuda_graph
         supported = getattr(model, "supports_prefix_cache", None)
         can_cache = bool(supported is not None and supported())
         self.use_kv_cache = can_cache if use_kv_cache is None else bool(use_kv_cache)
@@ -45,7 +46,6 @@ class NativeRolloutEngine:
         return self._generate_stateless(prompt_ids, num_generations, max_new_tokens, temperature, top_k, top_p)
 
     def _generate_cached(self, prompt_ids, g: int, max_new_tokens: int, temperature, top_k, top_p) -> Dict[str, Any]:
-        from rl_engine.kernels.ops.sm100.attention import make_layout
         from rl_engine.kernels.registry import kernel_registry
         from rl_engine.kernels.sampling import SamplerBackend
 
@@ -67,19 +67,47 @@ class NativeRolloutEngine:
         del prompt_kv
         completions = torch.empty(g, max_new_tokens, dtype=torch.long, device=dev)
         tokens = draw(last_state.expand(g, -1).contiguous()).reshape(g)
-        base = p + torch.arange(g, device=dev) * max_new_tokens  # first cache row of every completion
+        # Step state lives in fixed device tensors that are advanced in place, so that one decoding step (some 14
+        # launches per layer, launch-bound at G tokens) can be captured once as a CUDA graph and replayed per token:
+        # the token drawn at `step` sits at position p + step and in cache row base + step; its one-token query sees
+        # the prompt rows and its own rows so far (sk_len = step + 1, column 5 of the layout table).
+        step_tokens = tokens.clone()
+        positions = torch.full((g,), p, dtype=torch.long, device=dev)
+        slots = p + torch.arange(g, device=dev) * max_new_tokens
+        prefix_layout, layout = model.decode_layouts(g, p, max_new_tokens)
+        run_step = lambda: model.decode_step(step_tokens, positions, cache, slots, prefix_layout, layout)
+        graph, hidden = None, None
         for step in range(max_new_tokens):
             completions[:, step] = tokens
             if step + 1 == max_new_tokens:
                 break
-            # the token drawn at `step` sits at position p + step; its query sees the prompt and its own rows so far
-            positions = torch.full((g,), p + step, dtype=torch.long, device=dev)
-            layout = make_layout([(i, 1, 0, p, p + i * max_new_tokens, step + 1) for i in range(g)], False, dev)
-            hidden = model.decode_step(tokens, positions, cache, base + step, layout)
+            step_tokens.copy_(tokens)
+            if graph is None and self.use_cuda_graph and step == 1:
+                # step 0 ran eagerly (it also warmed up every kernel); capture from step 1 on
+                graph, hidden = self._capture(run_step)
+            if graph is not None:
+                graph.replay()
+            else:
+                hidden = run_step()
             tokens = draw(hidden).reshape(g)
+            positions += 1
+            slots += 1
+            layout.seqs[:, 5] += 1
         self._offset = sampler._offset
         logps = self.score(prompt, completions)
         return {"prompt_ids": prompt, "completion_ids": completions, "rollout_logps": logps}
+
+    @staticmethod
+    def _capture(run_step):
+        """Capture one decoding step; ``(None, None)`` if capture is not possible here (the caller then runs eagerly)."""
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                hidden = run_step()
+            return graph, hidden
+        except RuntimeError:
+            torch.cuda.synchronize()
+            return None, None
 
     def _generate_stateless(self, prompt_ids, num_generations: int, max_new_tokens: int, temperature, top_k,
                             top_p) -> Dict[str, Any]:

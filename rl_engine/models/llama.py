@@ -458,12 +458,18 @@ class LlamaModel(nn.Module):
         return [(make(), make()) for _ in range(cfg.num_layers)]
 
     @torch.no_grad()
-    def decode_step(self, token_ids: torch.Tensor, positions: torch.Tensor, cache, slots: torch.Tensor, layout) -> torch.Tensor:
+    def decode_step(self, token_ids: torch.Tensor, positions: torch.Tensor, cache, slots: torch.Tensor, prefix_layout,
+                    self_layout) -> torch.Tensor:
         """One new token for each of ``n`` sequences: final-norm hidden states ``[n, H]``.
 
         The rotated key and value of token ``i`` are written to row ``slots[i]`` of every layer's cache before the
-        attention of that layer runs; ``layout`` (non-causal) gives each one-token query its key ranges in the cache
-        (shared prefix rows + its own rows up to and including ``slots[i]``)."""
+        attention of that layer runs.  Attention packs the queries so that rows which read the same keys share a tile:
+        the ``Hq / Hkv`` query heads of a key / value head become rows (``n * Hq / Hkv`` rows, ``Hkv`` heads).
+        ``prefix_layout`` is ONE sequence of all those rows against the shared prefix rows of the cache (for 32
+        completions of a 4:1 grouped-query model exactly one 128-row tile per key / value head, instead of 1024
+        one-row tiles); ``self_layout`` has one sequence per completion: its ``Hq / Hkv`` rows against its own cache rows
+        up to and including ``slots[i]``.  Both are non-causal; the two partial results are merged by their
+        log-sum-exp (``decode_layouts`` builds the pair)."""
         from rl_engine.kernels.ops.base import require_ext
         from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
         from rl_engine.kernels.registry import kernel_registry
@@ -483,11 +489,32 @@ class LlamaModel(nn.Module):
             ext.rope(k, positions, self.rope_cos, self.rope_sin, False, k)
             cache[i][0].index_copy_(0, slots, k)
             cache[i][1].index_copy_(0, slots, v)
-            out, _ = packed_attention_forward(q, cache[i][0], cache[i][1], layout, scale, False)
-            x = x + self._project(out.reshape(n, cfg.q_dim), f"l{i}.wo")
+            rep = hq // hkv
+            rows = q.reshape(n, hkv, rep, cfg.head_dim).permute(0, 2, 1, 3).reshape(n * rep, hkv, cfg.head_dim)
+            o1, l1 = packed_attention_forward(rows, cache[i][0], cache[i][1], prefix_layout, scale, True)
+            o2, l2 = packed_attention_forward(rows, cache[i][0], cache[i][1], self_layout, scale, True)
+            top = torch.maximum(l1, l2)
+            w1, w2 = torch.exp(l1 - top).t().unsqueeze(-1), torch.exp(l2 - top).t().unsqueeze(-1)  # [n * rep, Hkv, 1]
+            merged = ((o1.float() * w1 + o2.float() * w2) / (w1 + w2)).to(o1.dtype)
+            out = merged.reshape(n, rep, hkv, cfg.head_dim).permute(0, 2, 1, 3).reshape(n, cfg.q_dim)
+            x = x + self._project(out, f"l{i}.wo")
             gu = self._project(rms_norm(x, p("mlp_norm"), cfg.rms_eps), f"l{i}.w_gate_up")
             x = x + self._project(swiglu_packed(gu), f"l{i}.w_down")
         return rms_norm(x, self.view("final_norm"), cfg.rms_eps)
+
+    def decode_layouts(self, n: int, prefix_len: int, rows_per_sequence: int, own_len: int = 1):
+        """The two layouts of ``decode_step`` for ``n`` sequences whose cache rows are ``[prefix | n x rows_per_sequence]``
+        when every sequence holds ``own_len`` tokens including the new one.  Column 5 of ``self_layout.seqs`` is that
+        length: a caller that decodes step by step adds one to it in place (the tables are private copies)."""
+        from dataclasses import replace
+
+        from rl_engine.kernels.ops.sm100.attention import make_layout
+
+        dev = self.flat.device
+        rep = self.cfg.num_heads // self.cfg.num_kv_heads
+        prefix = make_layout([(0, n * rep, 0, prefix_len, 0, 0)], False, dev)
+        own = make_layout([(i * rep, rep, 0, 0, prefix_len + i * rows_per_sequence, own_len) for i in range(n)], False, dev)
+        return prefix, replace(own, seqs=own.seqs.clone())
 
     def _project(self, x: torch.Tensor, name: str) -> torch.Tensor:
         """``x @ W[name].T`` for inference-only passes: the fp8 copy of the weight if ``enable_fp8_inference`` made one."""
