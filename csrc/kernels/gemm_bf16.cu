@@ -83,8 +83,38 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
   kernel<<<2 * pairs, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, a.err, 110u);
 }
 
+// Skinny problems (one 128-row tile of A, e.g. the G tokens of a decoding step): the GEMM is a stream over the
+// weight matrix, so parallelism has to come from N.  64-column tiles give four times as many CTAs as the 256-column
+// engine (N = 4096: 64 instead of 16) and an 8-stage ring of 24 KB keeps enough loads in flight per SM.
+constexpr int kSkinnyBN = 64;
+constexpr int kSkinnyStages = 8;
+
+void launch_skinny(const GemmArgs& a, cudaStream_t stream) {
+  using Epi = EpiStore<__nv_bfloat16, false>;
+  GemmProblem p = make_gemm_problem(a.M, a.N, a.K, kSkinnyBN, 1, 1);
+  const CUtensorMap ta = make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
+  const CUtensorMap tb = make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kSkinnyBN, kBK);
+  auto kernel = gemm_sm100_kernel<kSkinnyBN, false, false, kSkinnyStages, Epi>;
+  using L = GemmSmem<kSkinnyBN, kSkinnyStages, 0>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+    configured = true;
+  }
+  const int grid = p.num_items < a.sm_count ? p.num_items : a.sm_count;
+  if (grid < 1) return;
+  kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(
+      ta, tb, p, typename Epi::Params{static_cast<__nv_bfloat16*>(a.D), a.ldd, a.alpha}, a.err, 101u);
+}
+
 template <bool A_MN, bool B_MN>
 void dispatch_out(const GemmArgs& a, cudaStream_t stream) {
+  if constexpr (!A_MN && !B_MN) {
+    if (a.group_mode == 0 && a.M <= kBM && !a.out_fp32 && !a.accumulate && a.N >= 4 * kSkinnyBN) {
+      launch_skinny(a, stream);
+      return;
+    }
+  }
   if (!(a.cta_pair && a.group_mode == 0)) {
     // single-CTA engine, bf16 output that TMA can address: half-tile staging (32 KB next to the 4-stage ring)
     const bool tma_out = !a.out_fp32 && !a.accumulate && a.ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(a.D) & 15u) == 0 &&

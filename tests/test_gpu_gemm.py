@@ -121,3 +121,20 @@ def test_fp8_gemm_matches_the_dequantised_fp32_product(m, n, k):
     assert float(rel) < 6e-2
     assert torch.equal(matmul_nt_fp8(x, wq, ws), out) and torch.equal(Fp8Linear(w)(x), out)
     check_device_errors(0)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (32, 4096, 14336), (128, 1000, 520), (77, 28672, 4096)])
+def test_skinny_gemm_rows_equal_the_same_rows_of_a_tall_gemm(m, n, k):
+    """At most 128 rows of A take the 64-column-tile engine (more CTAs to stream the weight matrix); every output
+    element accumulates over K in the same order as on the other engines, so the rows must be the bits that a taller
+    problem containing them produces."""
+    from rl_engine.kernels.ops.sm100.gemm import gemm
+
+    g = torch.Generator(device="cuda").manual_seed(m + n)
+    x = torch.randn(256, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(n, k, device="cuda", generator=g)).to(torch.bfloat16)
+    tall = gemm(x, w, pair=False)
+    skinny = gemm(x[:m], w)
+    assert torch.equal(skinny, tall[:m])
+    ref = x[:m].float() @ w.float().t()
+    assert (skinny.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
