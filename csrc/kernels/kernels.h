@@ -200,6 +200,10 @@ void swiglu_packed_forward(const __nv_bfloat16* gu, long long ldgu, __nv_bfloat1
                            cudaStream_t stream);
 void swiglu_packed_backward(const __nv_bfloat16* gu, long long ldgu, const __nv_bfloat16* dy, long long lddy,
                             __nv_bfloat16* dgu, long long lddgu, long long rows, int F, cudaStream_t stream);
+// out[n, Hkv * rep * 128] = merge by log-sum-exp of two partial attention results o1 / o2 [n * rep, Hkv, 128] (bf16)
+// with l1 / l2 [Hkv, n * rep]; rows = n * rep.
+void attn_merge2(const void* o1, const float* l1, const void* o2, const float* l2, void* out, long long rows, int hkv,
+                 int rep, cudaStream_t stream);
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
                 void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream);
 void embedding_forward(const long long* ids, const void* table, long long ldw, int dtype, void* out, long long rows,

@@ -451,6 +451,42 @@ __global__ void adamw_kernel(TP* __restrict__ p, float* __restrict__ master, con
   }
 }
 
+// Merge of two partial attention results over disjoint key sets by their log-sum-exp, for decoding with packed
+// queries: o1 / o2 are [n * rep rows, Hkv, 128] (row = sequence * rep + query head within its key / value group),
+// l1 / l2 are [Hkv, n * rep]; out is [n, Hkv * rep * 128] in the model's head order (head = kv head * rep + j).
+__global__ void attn_merge2_kernel(const __nv_bfloat16* __restrict__ o1, const float* __restrict__ l1,
+                                   const __nv_bfloat16* __restrict__ o2, const float* __restrict__ l2,
+                                   __nv_bfloat16* __restrict__ out, long long rows, int hkv, int rep) {
+  const long long total = rows * hkv * 16;  // 16 vectors of 8 elements per (row, head)
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(idx & 15);
+    const long long rh = idx >> 4;
+    const int h = static_cast<int>(rh % hkv);
+    const long long r = rh / hkv;
+    const float a = l1[h * rows + r], b = l2[h * rows + r];
+    const float top = fmaxf(a, b);
+    float w1 = top == -INFINITY ? 0.f : __expf(a - top), w2 = top == -INFINITY ? 0.f : __expf(b - top);
+    const float inv = (w1 + w2) > 0.f ? 1.f / (w1 + w2) : 0.f;
+    w1 *= inv;
+    w2 *= inv;
+    const uint4 q1 = reinterpret_cast<const uint4*>(o1 + (r * hkv + h) * 128)[v];
+    const uint4 q2 = reinterpret_cast<const uint4*>(o2 + (r * hkv + h) * 128)[v];
+    const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&q1);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&q2);
+    uint4 res;
+    __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(p1[i]), y = __bfloat1622float2(p2[i]);
+      pr[i] = __floats2bfloat162_rn(x.x * w1 + y.x * w2, x.y * w1 + y.y * w2);
+    }
+    const long long seq = r / rep;
+    const int j = static_cast<int>(r - seq * rep);
+    reinterpret_cast<uint4*>(out + (seq * hkv * rep + static_cast<long long>(h) * rep + j) * 128)[v] = res;
+  }
+}
+
 inline int grid_for(long long total, int threads) {
   long long b = (total + threads - 1) / threads;
   const long long cap = 148LL * 16;
@@ -561,6 +597,14 @@ void swiglu_packed_backward(const __nv_bfloat16* gu, long long ldgu, const __nv_
                             __nv_bfloat16* dgu, long long lddgu, long long rows, int F, cudaStream_t stream) {
   if (rows <= 0 || F <= 0) return;
   swiglu_packed_bwd_kernel<<<grid_for(rows * (F / 8), 256), 256, 0, stream>>>(gu, ldgu, dy, lddy, dgu, lddgu, rows, F);
+}
+
+void attn_merge2(const void* o1, const float* l1, const void* o2, const float* l2, void* out, long long rows, int hkv,
+                 int rep, cudaStream_t stream) {
+  if (rows <= 0) return;
+  attn_merge2_kernel<<<grid_for(rows * hkv * 16, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(o1), l1, static_cast<const __nv_bfloat16*>(o2), l2,
+      static_cast<__nv_bfloat16*>(out), rows, hkv, rep);
 }
 
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,

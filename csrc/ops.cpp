@@ -906,6 +906,29 @@ Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const
   return out;
 }
 
+// Decoding with packed queries: merge the prefix part and the own-keys part of the attention by log-sum-exp.
+Tensor attn_merge2(const Tensor& o1, const Tensor& l1, const Tensor& o2, const Tensor& l2, int64_t rep) {
+  check_cuda(o1, "o1");
+  TORCH_CHECK(o1.scalar_type() == torch::kBFloat16 && o2.scalar_type() == torch::kBFloat16 && o1.dim() == 3 &&
+                  o1.size(2) == 128 && o1.is_contiguous() && o2.is_contiguous() && o1.sizes() == o2.sizes(),
+              "rl_engine.attn_merge2: o1 / o2 must be contiguous bf16 [rows, heads, 128]");
+  const int64_t rows = o1.size(0), hkv = o1.size(1);
+  auto ok = [&](const Tensor& l) {
+    return l.is_cuda() && l.scalar_type() == torch::kFloat32 && l.is_contiguous() && l.dim() == 2 && l.size(0) == hkv &&
+           l.size(1) == rows;
+  };
+  TORCH_CHECK(ok(l1) && ok(l2), "rl_engine.attn_merge2: l1 / l2 must be contiguous float32 [heads, rows]");
+  TORCH_CHECK(rep >= 1 && rows % rep == 0, "rl_engine.attn_merge2: rows must be a multiple of rep");
+  const c10::cuda::CUDAGuard guard(o1.device());
+  Tensor out = torch::empty({rows / rep, hkv * rep * 128}, o1.options());
+  if (rows) {
+    rlk::attn_merge2(o1.data_ptr(), l1.data_ptr<float>(), o2.data_ptr(), l2.data_ptr<float>(), out.data_ptr(), rows,
+                     static_cast<int>(hkv), static_cast<int>(rep), stream_of(o1));
+    after_launch();
+  }
+  return out;
+}
+
 Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
   check_rowmajor(table, "weight");
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous(), "ids: contiguous int64 GPU");
@@ -1186,6 +1209,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quantize_fp8_rows", rlk::traced("rlk::quantize_fp8_rows", &quantize_fp8_rows));
   m.def("gemm_fp8", rlk::traced("rlk::gemm_fp8", &gemm_fp8), py::arg("a_q"), py::arg("scale_a"), py::arg("b_q"),
         py::arg("scale_b"), py::arg("pair") = -1);
+  m.def("attn_merge2", rlk::traced("rlk::attn_merge2", &attn_merge2));
   m.def("rmsnorm_fwd", rlk::traced("rlk::rmsnorm_fwd", &rmsnorm_fwd));
   m.def("rmsnorm_bwd", rlk::traced("rlk::rmsnorm_bwd", &rmsnorm_bwd));
   m.def("swiglu_fwd", rlk::traced("rlk::swiglu_fwd", &swiglu_fwd));

@@ -493,10 +493,7 @@ class LlamaModel(nn.Module):
             rows = q.reshape(n, hkv, rep, cfg.head_dim).permute(0, 2, 1, 3).reshape(n * rep, hkv, cfg.head_dim)
             o1, l1 = packed_attention_forward(rows, cache[i][0], cache[i][1], prefix_layout, scale, True)
             o2, l2 = packed_attention_forward(rows, cache[i][0], cache[i][1], self_layout, scale, True)
-            top = torch.maximum(l1, l2)
-            w1, w2 = torch.exp(l1 - top).t().unsqueeze(-1), torch.exp(l2 - top).t().unsqueeze(-1)  # [n * rep, Hkv, 1]
-            merged = ((o1.float() * w1 + o2.float() * w2) / (w1 + w2)).to(o1.dtype)
-            out = merged.reshape(n, rep, hkv, cfg.head_dim).permute(0, 2, 1, 3).reshape(n, cfg.q_dim)
+            out = ext.attn_merge2(o1, l1, o2, l2, rep)  # [n, Hq * 128] in the model's head order
             x = x + self._project(out, f"l{i}.wo")
             gu = self._project(rms_norm(x, p("mlp_norm"), cfg.rms_eps), f"l{i}.w_gate_up")
             x = x + self._project(swiglu_packed(gu), f"l{i}.w_down")
