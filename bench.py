@@ -49,6 +49,8 @@ def parse_args():
     # development switches; any use marks the run as not comparable
     ap.add_argument("--dev-layers", type=int, default=0)
     ap.add_argument("--dev-group", type=int, default=0)
+    ap.add_argument("--dev-micro-group", type=int, default=0,
+                    help="development only: fix the completions per forward/backward pass instead of planning them")
     return ap.parse_args()
 
 
@@ -170,6 +172,7 @@ def main() -> None:
     tensor_parallel = args.parallelism == "tp" and world > 1
     local_group = group if tensor_parallel else group // world
 
+    micro = args.dev_micro_group or "auto"
     model = LlamaModel(cfg, dtype=torch.bfloat16, device=device, seed=0, max_positions=PROMPT_LEN + COMPLETION_LEN)
     if tensor_parallel:
         from rl_engine.parallel.tp_linear import TensorParallelLinears
@@ -183,10 +186,10 @@ def main() -> None:
     elif world > 1:
         from rl_engine.parallel.data_parallel import ShardedGRPOTrainer
 
-        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04)
+        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro)
         parallelism = f"dp{world}-zero1-fused"
     else:
-        trainer = GRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04)
+        trainer = GRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro)
         parallelism = "single"
 
     # the same global batch on every run; each rank takes its slice of the G completions
@@ -264,7 +267,7 @@ def main() -> None:
                 "activation_memory": activation_note,
                 "peak_torch_allocated_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
                 "device_memory_in_use_gb": round((mem_total - mem_free) / 2**30, 1),
-                "dev_overrides": bool(args.dev_layers or args.dev_group),
+                "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group),
             },
             "clocks": sampler.summary(),
             "e2e": {
