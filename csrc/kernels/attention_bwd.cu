@@ -116,10 +116,12 @@ __device__ __forceinline__ void dq_row(const uint32_t (&ts)[64], const uint32_t 
 struct DqSmem {
   static constexpr int kQ = 0;                       // [128 x 128] 32 KB
   static constexpr int kDO = 32768;                  // 32 KB
-  static constexpr int kStages = 4;  // a stage is held until the dQ MMA of its tile: depth hides the TMA latency
-  static constexpr int kStageBytes = 2 * 2 * kAtom64;  // K tile + V tile, each [64 keys x 128 d] = 16 KB
-  static constexpr int kKV = 65536;
-  static constexpr int kDS = kKV + kStages * kStageBytes;  // 2 buffers of [128 x 64] bf16 = 16 KB each
+  static constexpr int kStages = 4;                    // barrier slots: K ring (3) + the V buffer (1)
+  static constexpr int kKRing = 3;                     // K pair stages; a stage is held until the dQ products of its pair
+  static constexpr int kPairBytes = 2 * kAtom128;      // [128 keys x 128 d] = two [128 x 64] atoms = 32 KB
+  static constexpr int kKV = 65536;                    // K ring
+  static constexpr int kV = kKV + kKRing * kPairBytes; // one V pair buffer
+  static constexpr int kDS = kV + kPairBytes;          // 2 buffers of [128 x 64] bf16 = 16 KB each
   static constexpr int kBars = kDS + 2 * kAtom128;
   // qdo_full, kv_full[4], kv_empty[4], s_full[2], s_empty[2], ds_full[2], ds_empty[2], dq_done
   static constexpr int kNumBars = 18;
@@ -139,6 +141,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* qdo_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + DqSmem::kStages;
+  uint64_t* k_full = kv_full;        // [kKRing]
+  uint64_t* k_empty = kv_empty;      // [kKRing]
+  uint64_t* v_full = kv_full + DqSmem::kKRing;
+  uint64_t* v_empty = kv_empty + DqSmem::kKRing;
   uint64_t* s_full = kv_empty + DqSmem::kStages;
   uint64_t* s_empty = s_full + 2;
   uint64_t* ds_full = s_empty + 2;
@@ -161,6 +167,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   if (causal) self_keys = min(self_keys, q0 + 128);
   const int n_self = (self_keys + TK - 1) / TK;
   const int n_tiles = n_prefix + n_self;
+  const int n_pairs = (n_tiles + 1) / 2;
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -194,97 +201,107 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tma_load_2d(smem + DqSmem::kQ + c * kAtom128, &tmap_q, qdo_full, head * kD + c * 64, sd.q_start + q0);
         tma_load_2d(smem + DqSmem::kDO + c * kAtom128, &tmap_do, qdo_full, head * kD + c * 64, sd.q_start + q0);
       }
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int j = 0; j < n_tiles; ++j) {
-        mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, err, 210, 1);
-        const int row = j < n_prefix ? sd.pk_start + j * TK : sd.sk_start + (j - n_prefix) * TK;
-        uint8_t* sk = smem + DqSmem::kKV + stage * DqSmem::kStageBytes;
-        uint8_t* sv = sk + 2 * kAtom64;
-        mbar_arrive_expect_tx(&kv_full[stage], DqSmem::kStageBytes);
-        for (int c = 0; c < 2; ++c) {
-          tma_load_2d(sk + c * kAtom64, &tmap_k, &kv_full[stage], kv_head * kD + c * 64, row);
-          tma_load_2d(sv + c * kAtom64, &tmap_v, &kv_full[stage], kv_head * kD + c * 64, row);
-        }
-        if (++stage == DqSmem::kStages) {
-          stage = 0;
-          phase ^= 1;
+      // Key tiles travel in PAIRS (128 keys): S and dP of a pair are one N = 128 product each, at the tensor cores' full
+      // rate and with half the instructions of two N = 64 products.  K has a ring of three pair stages (a stage is held
+      // until the dQ products of its pair), V one pair buffer (free again as soon as dP of the pair has completed).
+      // Inside a [128 keys x 64 d] swizzle atom the first tile of the pair is rows 0..63, the second rows 64..127; each
+      // tile is loaded by its own TMA copies, so a pair may straddle the prefix / self boundary.
+      auto key_row = [&](int j) { return j < n_prefix ? sd.pk_start + j * TK : sd.sk_start + (j - n_prefix) * TK; };
+      int ks = 0;
+      uint32_t kphase = 0;
+      for (int p = 0; p < n_pairs; ++p) {
+        const int halves = min(2, n_tiles - 2 * p);
+        uint8_t* sk = smem + DqSmem::kKV + ks * DqSmem::kPairBytes;
+        uint8_t* sv = smem + DqSmem::kV;
+        mbar_wait(&k_empty[ks], kphase ^ 1, abort_flag, err, 210, 1);
+        mbar_arrive_expect_tx(&k_full[ks], halves * 2 * kAtom64);
+        for (int h = 0; h < halves; ++h)
+          for (int c = 0; c < 2; ++c)
+            tma_load_2d(sk + c * kAtom128 + h * kAtom64, &tmap_k, &k_full[ks], kv_head * kD + c * 64, key_row(2 * p + h));
+        mbar_wait(v_empty, (p & 1) ^ 1, abort_flag, err, 210, 9);
+        mbar_arrive_expect_tx(v_full, halves * 2 * kAtom64);
+        for (int h = 0; h < halves; ++h)
+          for (int c = 0; c < 2; ++c)
+            tma_load_2d(sv + c * kAtom128 + h * kAtom64, &tmap_v, v_full, kv_head * kD + c * 64, key_row(2 * p + h));
+        if (++ks == DqSmem::kKRing) {
+          ks = 0;
+          kphase ^= 1;
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);   // [128 q] x [64 keys], K = d
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);  // [128 q] x [128 keys of a pair], K = d
       constexpr uint32_t idesc_dq = umma_idesc_bf16(128, 128, false, true);  // dS (K-major) x K tile (MN-major)
       const uint32_t sq = smem_u32(smem + DqSmem::kQ);
       const uint32_t sdo = smem_u32(smem + DqSmem::kDO);
       mbar_wait(qdo_full, 0, abort_flag, err, 210, 2);
-      // This thread's instruction stream is the kernel's critical path (20 MMAs per 64 keys), so every descriptor is
-      // built once: Q / dO operands are fixed, K / V / dS operands are stage 0 (buffer 0) plus one add per use.
-      const uint32_t skv0 = smem_u32(smem + DqSmem::kKV);
-      uint64_t desc_q[kD / 16], desc_do[kD / 16], desc_k0[kD / 16], desc_v0[kD / 16];
+      // This thread's instruction stream is the kernel's critical path, so every descriptor is built once: Q / dO / V
+      // operands are fixed, K and dS operands are stage 0 / buffer 0 plus one add per use.
+      const uint32_t sk0 = smem_u32(smem + DqSmem::kKV), sv0 = smem_u32(smem + DqSmem::kV);
+      uint64_t desc_q[kD / 16], desc_do[kD / 16], desc_k0[kD / 16], desc_v[kD / 16];
 #pragma unroll
       for (int k = 0; k < kD / 16; ++k) {
-        const uint32_t offa = (k >> 2) * kAtom128 + (k & 3) * 32;
-        const uint32_t offb = (k >> 2) * kAtom64 + (k & 3) * 32;
-        desc_q[k] = umma_smem_desc_sw128(sq + offa, 16, 1024);
-        desc_do[k] = umma_smem_desc_sw128(sdo + offa, 16, 1024);
-        desc_k0[k] = umma_smem_desc_sw128(skv0 + offb, 16, 1024);
-        desc_v0[k] = umma_smem_desc_sw128(skv0 + 2 * kAtom64 + offb, 16, 1024);
+        const uint32_t off = (k >> 2) * kAtom128 + (k & 3) * 32;  // all four are [128 rows x 64 cols] atoms
+        desc_q[k] = umma_smem_desc_sw128(sq + off, 16, 1024);
+        desc_do[k] = umma_smem_desc_sw128(sdo + off, 16, 1024);
+        desc_k0[k] = umma_smem_desc_sw128(sk0 + off, 16, 1024);
+        desc_v[k] = umma_smem_desc_sw128(sv0 + off, 16, 1024);
       }
-      uint64_t desc_ds0[TK / 16], desc_kt0[TK / 16];  // dS buffer 0 (K-major) and the K tile of stage 0 read MN-major
+      // dQ operands: dS buffer 0 (K-major) and the first tile of K stage 0 read MN-major (its two d atoms are kAtom128 apart)
+      uint64_t desc_ds0[TK / 16], desc_kt0[TK / 16];
 #pragma unroll
       for (int k = 0; k < TK / 16; ++k) {
         desc_ds0[k] = umma_smem_desc_sw128(smem_u32(smem + DqSmem::kDS) + k * 32, 16, 1024);
-        desc_kt0[k] = umma_smem_desc_sw128(skv0 + k * 2048, kAtom64, 1024);
+        desc_kt0[k] = umma_smem_desc_sw128(sk0 + k * 2048, kAtom128, 1024);
       }
       MPROF_DECL;
-      auto issue_dq = [&](int j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int stage = j % DqSmem::kStages;
-        MPROF(0);
-        mbar_wait(&ds_full[b], ph, abort_flag, err, 210, 3);
-        MPROF(3);
-        tc_fence_after();
-        const uint32_t ds_off = b * kAtom128, kv_off = stage * DqSmem::kStageBytes;
+      auto issue_dq_pair = [&](int p) {
+        const int ks = p % DqSmem::kKRing;
+        for (int h = 0; h < 2 && 2 * p + h < n_tiles; ++h) {
+          const int j = 2 * p + h;
+          MPROF(0);
+          mbar_wait(&ds_full[h], p & 1, abort_flag, err, 210, 3);
+          MPROF(3);
+          tc_fence_after();
+          const uint32_t ds_off = h * kAtom128, k_off = ks * DqSmem::kPairBytes + h * kAtom64;
 #pragma unroll
-        for (int k = 0; k < TK / 16; ++k) {
-          umma_bf16(tmem + 256, umma_desc_advance(desc_ds0[k], ds_off), umma_desc_advance(desc_kt0[k], kv_off), idesc_dq,
-                    (j | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < TK / 16; ++k) {
+            umma_bf16(tmem + 256, umma_desc_advance(desc_ds0[k], ds_off), umma_desc_advance(desc_kt0[k], k_off), idesc_dq,
+                      (j | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&ds_empty[h]);
+          MPROF(4);
         }
-        umma_commit(&ds_empty[b]);
-        umma_commit(&kv_empty[stage]);
-        MPROF(4);
+        umma_commit(&k_empty[ks]);
       };
-      for (int j = 0; j < n_tiles; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int stage = j % DqSmem::kStages;
-        const uint32_t kv_phase = (j / DqSmem::kStages) & 1;
+      for (int p = 0; p < n_pairs; ++p) {
+        const int ks = p % DqSmem::kKRing;
         MPROF(0);
-        mbar_wait(&kv_full[stage], kv_phase, abort_flag, err, 210, 4);
+        mbar_wait(&k_full[ks], (p / DqSmem::kKRing) & 1, abort_flag, err, 210, 4);
         MPROF(5);
-        mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 210, 5);
+        // both halves of the S / dP columns are rewritten, so both groups must have taken the previous pair's values
+        mbar_wait(&s_empty[0], (p & 1) ^ 1, abort_flag, err, 210, 5);
+        mbar_wait(&s_empty[1], (p & 1) ^ 1, abort_flag, err, 210, 5);
         MPROF(1);
         tc_fence_after();
-        const uint32_t kv_off = stage * DqSmem::kStageBytes;
+        const uint32_t k_off = ks * DqSmem::kPairBytes;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k)
-          umma_bf16(tmem + b * 64, desc_q[k], umma_desc_advance(desc_k0[k], kv_off), idesc_s, k != 0 ? 1u : 0u);
+          umma_bf16(tmem, desc_q[k], umma_desc_advance(desc_k0[k], k_off), idesc_s, k != 0 ? 1u : 0u);
+        mbar_wait(v_full, p & 1, abort_flag, err, 210, 10);
+        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k)
-          umma_bf16(tmem + 128 + b * 64, desc_do[k], umma_desc_advance(desc_v0[k], kv_off), idesc_s, k != 0 ? 1u : 0u);
-        umma_commit(&s_full[b]);
+        for (int k = 0; k < kD / 16; ++k) umma_bf16(tmem + 128, desc_do[k], desc_v[k], idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(&s_full[0]);
+        if (2 * p + 1 < n_tiles) umma_commit(&s_full[1]);
+        umma_commit(v_empty);
         MPROF(2);
-        // dQ trails S / dP by TWO tiles: a compute group releases its S / dP buffer as soon as the values are in
-        // registers, so S, dP of tile j + 1 are issued before this thread blocks on the dS of tile j - 1, and each
-        // group finds its next S / dP ready when it finishes a tile.  (A K/V stage is held for three tiles; the ring
-        // has four.)
-        if (j >= 2) issue_dq(j - 2);
+        // dQ trails S / dP by one PAIR: a compute group releases its S / dP columns as soon as the values are in
+        // registers, so S, dP of the next pair are issued before this thread blocks on the dS of the previous one.
+        if (p >= 1) issue_dq_pair(p - 1);
       }
-      if (n_tiles >= 2) issue_dq(n_tiles - 2);
-      if (n_tiles >= 1) issue_dq(n_tiles - 1);
+      if (n_pairs >= 1) issue_dq_pair(n_pairs - 1);
       // A barrier of its own for "dQ complete": the groups must not take this from ds_empty of the last tile, because
       // a group that does not own that buffer has not followed its phases and could see an older phase of the same
       // parity as complete.
