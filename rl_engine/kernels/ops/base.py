@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from typing import Any
 
+import torch  # noqa: F401  (must be loaded first: the extension links against libc10 / libtorch)
+
 from rl_engine.utils.logger import logger
 
 _C: Any = None

@@ -381,3 +381,17 @@ def test_poly_exp2_coefficients_are_accurate_enough_for_bf16_probabilities():
         worst = max(worst, abs(poly_exp2(x) / 2.0 ** x - 1.0))
     assert worst < 2e-4, worst
     assert abs(poly_exp2(0.0) - 1.0) < 1e-4 and abs(poly_exp2(-1.0) - 0.5) < 1e-4
+
+
+def test_extension_imports_in_a_fresh_interpreter_without_torch_preloaded():
+    """The extension links against libtorch; the package has to load torch itself before importing it."""
+    import glob
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not glob.glob(os.path.join(root, "rl_engine", "_C*.so")):
+        pytest.skip("extension not built")
+    code = "import rl_engine.kernels.ops.base as b; assert b._EXT_AVAILABLE, b._EXT_ERROR; print('ok')"
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
