@@ -386,6 +386,7 @@ def test_poly_exp2_coefficients_are_accurate_enough_for_bf16_probabilities():
 def test_extension_imports_in_a_fresh_interpreter_without_torch_preloaded():
     """The extension links against libtorch; the package has to load torch itself before importing it."""
     import glob
+    import os
     import subprocess
     import sys
 
