@@ -19,6 +19,12 @@ L2 flush is needed between steps.  SM clocks and throttle reasons are sampled th
 the timed region.  The ``e2e`` entry times the same K steps through the public
 ``GRPOTrainer.step(host_batch)`` call, which copies the step's inputs from pinned host memory and
 reads the loss back every step.
+
+The same line also carries the other two thirds of the headline metric, measured after the step timing
+with the trainer's memory released (``ops``): the fused linear -> log-prob op forward + backward at
+``[131072, 4096] x [128256, 4096]`` with 4096-token chunks (vocabulary-parallel over the N ranks when
+N > 1) as TFLOP/s, its extra device memory at G = 64 / 128 / 256 completions of 512 tokens, and the
+sampler's latency at ``[256, 151936]`` logits with temperature 0.7, top-k 50, top-p 0.9.
 """
 
 from __future__ import annotations
@@ -117,6 +123,138 @@ def physical_gpu_index(local_rank: int) -> int:
         except (ValueError, IndexError):
             return local_rank
     return local_rank
+
+
+OPS_DEADLINE_S = 300
+LOGP_HIDDEN, LOGP_VOCAB, LOGP_CHUNK = 4096, 128256, 4096
+SAMPLER_ROWS, SAMPLER_VOCAB = 256, 151936
+
+
+def _median_ms(fn, iters: int, warmup: int = 1):
+    """Median device time of ``fn`` in ms (one CUDA-event pair per call, on the launching stream)."""
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def measure_fused_logp(device, rank: int, world: int, iters: int = 20):
+    """Fused linear -> log-prob, forward + backward, at G x 512 tokens for G = 64 / 128 / 256; timing at G = 256.
+
+    With ``world`` > 1 every rank holds ``V / world`` rows of the LM head and the same tokens (vocabulary parallel);
+    times are the max over ranks.  ``extra_vram_mb`` = peak allocated during the call minus the inputs (hidden states,
+    weights, targets, upstream gradient) and minus what the call returns (log-probs; gradients), i.e. the op's
+    workspaces and temporaries."""
+    import torch
+    import torch.distributed as dist
+
+    from rl_engine.kernels.registry import kernel_registry
+
+    op = kernel_registry.get_op("linear_logp")
+    d, v = LOGP_HIDDEN, LOGP_VOCAB
+    v_local = v // world
+    v0 = rank * v_local
+    if rank == world - 1:
+        v_local = v - v0
+    torch.cuda.synchronize()
+    floor = torch.cuda.memory_allocated(device)  # nothing of this measurement exists yet
+    gen = torch.Generator(device=device).manual_seed(7)  # the same tokens on every rank
+    shard_gen = torch.Generator(device=device).manual_seed(11 + rank)
+    weight = (torch.randn(v_local, d, device=device, generator=shard_gen) * 0.02).to(torch.bfloat16).requires_grad_(True)
+    kw = {} if world == 1 else {"tp_group": dist.group.WORLD, "vocab_start_index": v0, "global_vocab_size": v}
+    nbytes = lambda *ts: sum(t.numel() * t.element_size() for t in ts)
+    extra, times = {}, {}
+    for group in (64, 128, 256):
+        n = group * 512
+        hidden = torch.randn(n, d, device=device, generator=gen).to(torch.bfloat16).requires_grad_(True)
+        targets = torch.randint(0, v, (n,), device=device, generator=gen)
+        grad_out = torch.randn(n, device=device, generator=gen)
+
+        def fwd():
+            with torch.no_grad():
+                return op(hidden, weight, targets, None, **kw)
+
+        def fwd_bwd():
+            hidden.grad = None
+            weight.grad = None
+            op(hidden, weight, targets, None, **kw).backward(grad_out)
+
+        # everything above ``floor`` that is not an input or a returned tensor counts as extra, including the
+        # workspaces that the op keeps between calls (created at the first call, they do not grow with G)
+        inputs = nbytes(hidden, weight, targets, grad_out)
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(device)
+        fwd()
+        torch.cuda.synchronize()
+        peak_fwd = torch.cuda.max_memory_allocated(device) - floor - inputs - n * 4
+        torch.cuda.reset_peak_memory_stats(device)
+        fwd_bwd()
+        torch.cuda.synchronize()
+        peak_bwd = torch.cuda.max_memory_allocated(device) - floor - inputs - nbytes(hidden.grad, weight.grad)
+        extra[f"G{group}"] = {"fwd": round(peak_fwd / 2**20, 1), "fwd_bwd": round(peak_bwd / 2**20, 1)}
+        if group == 256:
+            times = {"fwd_ms": _median_ms(fwd, iters), "fwd_bwd_ms": _median_ms(fwd_bwd, iters)}
+        del hidden, targets, grad_out
+    if world > 1:
+        t = torch.tensor([times["fwd_ms"], times["fwd_bwd_ms"]], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times = {"fwd_ms": float(t[0]), "fwd_bwd_ms": float(t[1])}
+    n = 256 * 512
+    return {
+        "shape": f"[{n},{d}]x[{v},{d}]", "tp": world, "chunk_tokens": LOGP_CHUNK, "iters": iters,
+        "backend": type(op).__name__,
+        "fwd_ms": round(times["fwd_ms"], 3), "fwd_bwd_ms": round(times["fwd_bwd_ms"], 3),
+        "tflops_fwd": round(2.0 * n * d * v / (times["fwd_ms"] * 1e-3) / 1e12, 1),
+        "tflops_fwd_bwd": round(6.0 * n * d * v / (times["fwd_bwd_ms"] * 1e-3) / 1e12, 1),
+        "flops_counted": "2*N*D*V forward, 6*N*D*V forward+backward (the recomputation in backward is not counted)",
+        "extra_vram_mb": extra,
+        "l2": "inputs larger than L2 (1 GB of hidden states and 1 GB of weights per call)",
+    }
+
+
+def measure_sampler(device, iters: int = 30):
+    """Temperature 0.7 / top-k 50 / top-p 0.9 sampling of one token per row of ``[256, 151936]`` fp32 logits; two
+    input buffers alternate so that no call finds its logits in L2."""
+    import torch
+
+    from rl_engine.kernels.sampling import SamplerBackend
+
+    sampler = SamplerBackend(seed=5)
+    gen = torch.Generator(device=device).manual_seed(3)
+    buffers = [torch.randn(SAMPLER_ROWS, SAMPLER_VOCAB, device=device, generator=gen) for _ in range(2)]
+    state = {"i": 0}
+
+    def call():
+        state["i"] += 1
+        return sampler.sample(buffers[state["i"] % 2], top_k=50, top_p=0.9, temperature=0.7)
+
+    ids = call()
+    assert ids.shape == (SAMPLER_ROWS,) and int(ids.min()) >= 0 and int(ids.max()) < SAMPLER_VOCAB
+    return {"shape": [SAMPLER_ROWS, SAMPLER_VOCAB], "dtype": "fp32", "temperature": 0.7, "top_k": 50, "top_p": 0.9,
+            "ms": round(_median_ms(call, iters, warmup=3), 4), "iters": iters, "backend": sampler.backend,
+            "l2": "two 155 MB logit buffers alternate (each larger than L2)"}
+
+
+def measure_ops(device, rank: int, world: int):
+    """The per-operator part of the headline metric; a failure is reported in place of the numbers."""
+    out = {}
+    for name, fn in (("fused_logp", lambda: measure_fused_logp(device, rank, world)),
+                     ("sampler", lambda: measure_sampler(device))):
+        try:
+            out[name] = fn()
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    return out
 
 
 def run_reference(args) -> None:
@@ -242,6 +380,8 @@ def main() -> None:
     barrier()
     e2e_s = time.perf_counter() - t0
     check_device_errors(local_rank)
+    if hasattr(trainer, "check"):
+        trainer.check()  # bounded peer waits of the symmetric-memory barriers report here, not in the global word
 
     if world > 1:
         t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
@@ -250,33 +390,69 @@ def main() -> None:
     tokens = group * COMPLETION_LEN
     value = tokens * args.steps / (ms / 1e3)
     mem_free, mem_total = torch.cuda.mem_get_info(device)
+    peak_allocated = torch.cuda.max_memory_allocated(device)
     kept = trainer.model.kept_layers()
+    master = ("fp32 master weights (bf16 parameter + 16-bit residual per element)" if getattr(trainer.opt, "residual", None)
+              is not None else "fp32 master weights" if getattr(trainer.opt, "master", None) is not None else "none")
+    line = {}
+    emitted = threading.Event()
+
+    def emit(ops):
+        if emitted.is_set():
+            return
+        emitted.set()
+        if rank == 0:
+            line["ops"] = ops
+            print(json.dumps(line), flush=True)
     activation_note = (f"{kept} of {cfg.num_layers} layers keep their activations, the others are recomputed in "
                        "the backward pass (planned from free device memory)")
-    if rank == 0:
-        line = {
-            "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-            "config": {
-                "model": cfg.name, "layers": cfg.num_layers, "global_batch": group, "seq_len": PROMPT_LEN + COMPLETION_LEN,
-                "prompt_len": PROMPT_LEN, "completion_len": COMPLETION_LEN, "parallelism": parallelism,
-                "tokens_counted": "completion tokens (G x 512) per step",
-                "optimizer": "AdamW (fp32 moments) over all parameters, inside the timed region",
-                "l2": "inputs larger than L2 (16 GB of weights streamed every step); no explicit flush",
-                "activation_memory": activation_note,
-                "peak_torch_allocated_gb": round(torch.cuda.max_memory_allocated(device) / 2**30, 1),
-                "device_memory_in_use_gb": round((mem_total - mem_free) / 2**30, 1),
-                "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group),
-            },
-            "clocks": sampler.summary(),
-            "e2e": {
-                "value": round(tokens * args.steps / e2e_s, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": host.nbytes(), "d2h_bytes_per_step": 4, "last_loss": loss_value,
-            },
-            "gpu_launches": int(launches),
-        }
-        print(json.dumps(line), flush=True)
+    line.update({
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": cfg.name, "layers": cfg.num_layers, "global_batch": group, "seq_len": PROMPT_LEN + COMPLETION_LEN,
+            "prompt_len": PROMPT_LEN, "completion_len": COMPLETION_LEN, "parallelism": parallelism,
+            "tokens_counted": "completion tokens (G x 512) per step",
+            "optimizer": "AdamW (fp32 moments) over all parameters, inside the timed region",
+            "master_weights": master,
+            "l2": "inputs larger than L2 (16 GB of weights streamed every step); no explicit flush",
+            "activation_memory": activation_note,
+            "peak_torch_allocated_gb": round(peak_allocated / 2**30, 1),
+            "device_memory_in_use_gb": round((mem_total - mem_free) / 2**30, 1),
+            "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group),
+        },
+        "clocks": sampler.summary(),
+        "e2e": {
+            "value": round(tokens * args.steps / e2e_s, 1), "unit": "tokens/s",
+            "h2d_bytes_per_step": host.nbytes(), "d2h_bytes_per_step": 4, "last_loss": loss_value,
+        },
+        "gpu_launches": int(launches),
+    })
+
+    # The per-operator numbers need a few GB: release the trainer first.  If that part does not finish in time the
+    # line is printed without it, so the step result is never lost.
+    def watchdog():
+        emit({"error": f"operator measurements did not finish within {OPS_DEADLINE_S} s"})
+        os._exit(0)
+
+    timer = threading.Timer(OPS_DEADLINE_S, watchdog)
+    timer.daemon = True
+    timer.start()
+    ops = {"skipped": "development overrides in use"}
+    if not (args.dev_layers or args.dev_group) or os.environ.get("RLK_BENCH_OPS") == "1":
+        if hasattr(trainer, "mem"):
+            torch.cuda.synchronize()
+            trainer.mem.close()
+        del trainer, dev_batch, host, full
+        model = tp_model = None  # noqa: F841 - drop the last references to the parameters
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        ops = measure_ops(device, rank, world)
+    timer.cancel()
+    emit(ops)
     if world > 1:
         dist.destroy_process_group()
 

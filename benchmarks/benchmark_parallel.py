@@ -196,7 +196,7 @@ def bench_zero1(args, rank, world):
     def run():
         step[0] += 1
         mem.barrier()
-        ext.zero1_fused_step(grads.ptrs, params.ptrs, lo, hi, m, v, master, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0 / world)
+        ext.zero1_fused_step(grads.ptrs, params.ptrs, lo, hi, m, v, master, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0 / world, rank, None, 0)
         mem.barrier()
 
     ms = timed(run, args.warmup, args.repeat)

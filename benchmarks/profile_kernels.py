@@ -204,7 +204,7 @@ def case_zero1_step():
 
     def run():
         step[0] += 1
-        ext.zero1_fused_step(grads.ptrs, params.ptrs, 0, n, m, v, master, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0)
+        ext.zero1_fused_step(grads.ptrs, params.ptrs, 0, n, m, v, master, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0, 0, None, 0)
 
     ms = timed(run)
     return {"flops": 0.0, "bytes": n * (2.0 + 2.0 + 3 * 4 * 2), "ms": ms, "shape": [n],

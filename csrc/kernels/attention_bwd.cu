@@ -735,10 +735,9 @@ __global__ void attn_bwd_reduce_kernel(const ReduceJob* __restrict__ jobs, const
 
 template <class K>
 void set_max_smem(K kernel, int bytes) {
-  static bool done = false;
-  if (!done) {
+  static PerDeviceOnce done;
+  if (done.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    done = true;
   }
 }
 

@@ -380,10 +380,9 @@ void attention_forward(const AttnFwdArgs& a, cudaStream_t stream) {
   const CUtensorMap tq = make_tmap_2d_bf16(a.q, a.total_q, static_cast<uint64_t>(a.heads_q) * kD, a.ld_q, kTileQ, 64);
   const CUtensorMap tk = make_tmap_2d_bf16(a.k, a.total_kv, static_cast<uint64_t>(a.heads_kv) * kD, a.ld_k, kTileK, 64);
   const CUtensorMap tv = make_tmap_2d_bf16(a.v, a.total_kv, static_cast<uint64_t>(a.heads_kv) * kD, a.ld_v, kTileK, 64);
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
-    configured = true;
   }
   const long long grid = static_cast<long long>(a.num_tiles) * a.heads_q;
   attn_fwd_kernel<<<static_cast<unsigned int>(grid), kThreads, Smem::kDynamic, stream>>>(

@@ -73,10 +73,15 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // [lo, hi) are element indices, multiples of 8.  m / v / master are indexed from 0 at element lo.
+// ``skip_if_set``: the error word of the device barrier that precedes this kernel (or nullptr).  If that barrier
+// gave up waiting for a peer, some gradients are not final, so the kernel applies nothing and returns.
 __global__ void __launch_bounds__(256)
-zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int world, long long lo, long long hi, float* __restrict__ m,
-                        float* __restrict__ v, float* __restrict__ master, float lr, float b1, float b2, float eps,
-                        float wd, float bc1, float bc2, float grad_scale) {
+zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world, long long lo, long long hi,
+                        float* __restrict__ m, float* __restrict__ v, float* __restrict__ master, float lr, float b1,
+                        float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                        const uint32_t* __restrict__ skip_if_set) {
+  if (skip_if_set != nullptr && *skip_if_set != 0u) return;
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
   const long long n8 = (hi - lo) / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -97,8 +102,8 @@ zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int world, long long lo
       const float4 b = reinterpret_cast<const float4*>(master + i * 8)[1];
       w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
     } else {
-      // every rank holds identical parameters; read the local copy
-      unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(params.p[0]) + e), w);
+      // every rank holds identical parameters; read this rank's own copy
+      unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(params.p[rank]) + e), w);
     }
     float mm[8], vv[8];
     {
@@ -112,8 +117,8 @@ zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int world, long long lo
       const float gj = g[j] * grad_scale;
       mm[j] = b1 * mm[j] + (1.f - b1) * gj;
       vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
-      const float denom = sqrtf(vv[j] / bc2) + eps;
-      w[j] = w[j] * (1.f - lr * wd) - lr * (mm[j] / bc1) / denom;
+      const float denom = sqrtf(vv[j] * inv_bc2) + eps;
+      w[j] = w[j] * decay - lr * (mm[j] * inv_bc1) / denom;
     }
     reinterpret_cast<float4*>(m + i * 8)[0] = make_float4(mm[0], mm[1], mm[2], mm[3]);
     reinterpret_cast<float4*>(m + i * 8)[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
@@ -263,13 +268,15 @@ void peer_barrier(void* const* pads, int rank, int world, unsigned int epoch, un
   peer_barrier_kernel<<<1, 32, 0, stream>>>(make_ptrs(pads, world), rank, world, epoch, limit_ns, err);
 }
 
-void zero1_fused_step(void* const* grads, void* const* params, int world, long long lo, long long hi, float* m, float* v,
-                      float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                      float grad_scale, cudaStream_t stream) {
+void zero1_fused_step(void* const* grads, void* const* params, int rank, int world, long long lo, long long hi, float* m,
+                      float* v, float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                      float grad_scale, const uint32_t* skip_if_set, int max_blocks, cudaStream_t stream) {
   if (hi <= lo) return;
-  zero1_fused_step_kernel<<<capped_grid((hi - lo) / 8, 256), 256, 0, stream>>>(
-      make_ptrs(grads, world), make_ptrs(params, world), world, lo, hi, m, v, master, lr, b1, b2, eps, wd, bc1, bc2,
-      grad_scale);
+  int grid = capped_grid((hi - lo) / 8, 256);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
+  zero1_fused_step_kernel<<<grid, 256, 0, stream>>>(make_ptrs(grads, world), make_ptrs(params, world), rank, world, lo,
+                                                    hi, m, v, master, lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
+                                                    skip_if_set);
 }
 
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream) {

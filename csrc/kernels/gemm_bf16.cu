@@ -37,10 +37,9 @@ void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stre
                               : make_tmap_2d_bf16(a.B, static_cast<uint64_t>(a.N) * b_stack, a.K, a.ldb, kBN, kBK);
   auto kernel = gemm_sm100_kernel<kBN, A_MN, B_MN, kStages, Epi>;
   using L = GemmSmem<kBN, kStages, Epi::kStagingBytes>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-    configured = true;
   }
   int grid = p.num_items < a.sm_count ? p.num_items : a.sm_count;
   if (grid < 1) return;
@@ -72,10 +71,9 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
                               : make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kBN / 2, kBK);
   auto kernel = gemm_pair_sm100_kernel<kBN, A_MN, B_MN, STAGES, Epi>;
   using L = PairSmem<kBN, STAGES, Epi::kStagingBytes>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-    configured = true;
   }
   int pairs = a.sm_count / 2;
   if (p.num_items < pairs) pairs = p.num_items;
@@ -96,10 +94,9 @@ void launch_skinny(const GemmArgs& a, cudaStream_t stream) {
   const CUtensorMap tb = make_tmap_2d_bf16(a.B, a.N, a.K, a.ldb, kSkinnyBN, kBK);
   auto kernel = gemm_sm100_kernel<kSkinnyBN, false, false, kSkinnyStages, Epi>;
   using L = GemmSmem<kSkinnyBN, kSkinnyStages, 0>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-    configured = true;
   }
   const int grid = p.num_items < a.sm_count ? p.num_items : a.sm_count;
   if (grid < 1) return;

@@ -165,10 +165,9 @@ void gemm_fp8_rowscaled(const void* a_q, long long lda, const float* scale_a, co
     const CUtensorMap tb = make_tmap_2d_u8(b_q, N, K, ldb, kBN / 2, 128);
     auto kernel = gemm_pair_sm100_kernel<kBN, false, false, kPairStages, EpiStoreRowScaled, 1>;
     using L = PairSmem<kBN, kPairStages, 0>;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    if (configured.first()) {
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-      configured = true;
     }
     int pairs = sm_count / 2;
     if (p.num_items < pairs) pairs = p.num_items;
@@ -181,10 +180,9 @@ void gemm_fp8_rowscaled(const void* a_q, long long lda, const float* scale_a, co
   const CUtensorMap tb = make_tmap_2d_u8(b_q, N, K, ldb, kBN, 128);
   auto kernel = gemm_sm100_kernel<kBN, false, false, kStages, EpiStoreRowScaled, 1>;
   using L = GemmSmem<kBN, kStages, 0>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-    configured = true;
   }
   const int grid = p.num_items < sm_count ? p.num_items : sm_count;
   kernel<<<grid, kGemmThreads, L::kDynamicBytes, stream>>>(ta, tb, p, ep, err, 111u);

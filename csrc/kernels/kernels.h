@@ -7,6 +7,22 @@
 #include <stdint.h>
 
 namespace rlk {
+// Kernel attributes such as the opt-in shared-memory size belong to one device's context.  A function-local
+// ``static PerDeviceOnce flag;`` with ``if (flag.first()) { cudaFuncSetAttribute(...); }`` configures the kernel once
+// on every device that launches it, not once per process.
+struct PerDeviceOnce {
+  bool done[64] = {};
+  bool first() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= 64) return true;
+    if (done[d]) return false;
+    done[d] = true;
+    return true;
+  }
+};
+}  // namespace rlk
+
+namespace rlk {
 
 // ----------------------------------------------------------------------------- GEMM (tcgen05)
 // D[M,N] = alpha * op(A) * op(B)^T (+ D if accumulate).
@@ -211,8 +227,10 @@ void embedding_forward(const long long* ids, const void* table, long long ldw, i
 void embedding_backward(const long long* seg_ids, const long long* seg_start, long long segments,
                         const long long* order, const void* dy, int dy_dtype, int D, void* dtable, bool table_fp32,
                         long long ldw, cudaStream_t stream);
-void adamw_step(void* p, int p_dtype, float* master, const void* g, int g_dtype, float* m, float* v, long long n,
-                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+// master: fp32 master weights or nullptr.  residual: 16-bit residuals of a bf16 parameter (fp32 master = parameter
+// bits << 16 plus the sign-extended residual) or nullptr; at most one of the two.
+void adamw_step(void* p, int p_dtype, float* master, short* residual, const void* g, int g_dtype, float* m, float* v,
+                long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
                 cudaStream_t stream);
 
 }  // namespace rlk
@@ -305,9 +323,11 @@ namespace rlk {
 // ------------------------------------------------------------ peer-memory communication kernels
 void peer_barrier(void* const* pads, int rank, int world, unsigned int epoch, unsigned long long limit_ns, uint32_t* err,
                   cudaStream_t stream);
-void zero1_fused_step(void* const* grads, void* const* params, int world, long long lo, long long hi, float* m, float* v,
-                      float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                      float grad_scale, cudaStream_t stream);
+// skip_if_set: error word of the preceding device barrier (the kernel applies nothing if it is non-zero) or nullptr;
+// max_blocks > 0 limits the grid, for launches that share the GPU with compute on another stream.
+void zero1_fused_step(void* const* grads, void* const* params, int rank, int world, long long lo, long long hi, float* m,
+                      float* v, float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                      float grad_scale, const uint32_t* skip_if_set, int max_blocks, cudaStream_t stream);
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream);
 void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
                     cudaStream_t stream);

@@ -272,10 +272,9 @@ struct EpiLogpDz {
 // ---------------------------------------------------------------------------------------------
 template <class Kernel>
 static void set_smem(Kernel k, int bytes) {
-  static bool done = false;  // one static per instantiation
-  if (!done) {
+  static PerDeviceOnce done;  // one static per instantiation
+  if (done.first()) {
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    done = true;
   }
 }
 

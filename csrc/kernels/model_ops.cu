@@ -444,10 +444,122 @@ __global__ void adamw_kernel(TP* __restrict__ p, float* __restrict__ master, con
     const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
     m[i] = mi;
     v[i] = vi;
-    const float denom = sqrtf(vi / bc2) + eps;
-    w = w * (1.f - lr * wd) - lr * (mi / bc1) / denom;
+    const float denom = sqrtf(vi * (1.f / bc2)) + eps;
+    w = w * (1.f - lr * wd) - lr * (mi * (1.f / bc1)) / denom;
     if (master) master[i] = w;
     stf(p, i, w);
+  }
+}
+
+// The fp32 master weight of a bf16 parameter, stored as the parameter itself plus a 16-bit residual:
+//   master_bits = (bf16_bits << 16) + sign_extend(residual).
+// The parameter is the master rounded to bf16 (ties away from zero in magnitude, one integer add), so the residual
+// always fits 16 bits and the pair reproduces every bit of the fp32 value: the optimiser has exact fp32-master
+// arithmetic at 2 extra bytes per parameter instead of 4.
+__device__ __forceinline__ float master_from_split(unsigned short hi, short residual) {
+  return __uint_as_float((static_cast<unsigned int>(hi) << 16) + static_cast<unsigned int>(static_cast<int>(residual)));
+}
+__device__ __forceinline__ void master_to_split(float w, unsigned short& hi, short& residual) {
+  const unsigned int bits = __float_as_uint(w);
+  const unsigned int up = (bits + 0x8000u) >> 16;  // round half away from zero (in magnitude)
+  hi = static_cast<unsigned short>(up);
+  residual = static_cast<short>(static_cast<int>(bits - (up << 16)));
+}
+
+// Eight elements per thread and iteration through 16-byte accesses.  kMaster: 0 none (bf16 parameter is the state),
+// 1 fp32 master, 2 bf16 parameter + 16-bit residual.  TG: gradient type (bf16 or fp32).
+template <typename TG, int kMaster>
+__global__ void __launch_bounds__(256)
+adamw_bf16_vec_kernel(__nv_bfloat16* __restrict__ p, float* __restrict__ master, short* __restrict__ residual,
+                      const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v, long long n8, float lr,
+                      float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale) {
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 8;
+    float gj[8], w[8], mm[8], vv[8];
+    if constexpr (sizeof(TG) == 4) {
+      const float4 a = reinterpret_cast<const float4*>(g + e)[0], b = reinterpret_cast<const float4*>(g + e)[1];
+      gj[0] = a.x; gj[1] = a.y; gj[2] = a.z; gj[3] = a.w; gj[4] = b.x; gj[5] = b.y; gj[6] = b.z; gj[7] = b.w;
+    } else {
+      const uint4 q = *reinterpret_cast<const uint4*>(g + e);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(h[j]);
+        gj[2 * j] = x.x;
+        gj[2 * j + 1] = x.y;
+      }
+    }
+    uint4 pq = *reinterpret_cast<const uint4*>(p + e);
+    unsigned short* ph = reinterpret_cast<unsigned short*>(&pq);
+    uint4 rq = make_uint4(0, 0, 0, 0);
+    short* rh = reinterpret_cast<short*>(&rq);
+    if constexpr (kMaster == 1) {
+      const float4 a = reinterpret_cast<const float4*>(master + e)[0], b = reinterpret_cast<const float4*>(master + e)[1];
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else if constexpr (kMaster == 2) {
+      rq = *reinterpret_cast<const uint4*>(residual + e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = master_from_split(ph[j], rh[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = __uint_as_float(static_cast<unsigned int>(ph[j]) << 16);
+    }
+    {
+      const float4 a = reinterpret_cast<const float4*>(m + e)[0], b = reinterpret_cast<const float4*>(m + e)[1];
+      mm[0] = a.x; mm[1] = a.y; mm[2] = a.z; mm[3] = a.w; mm[4] = b.x; mm[5] = b.y; mm[6] = b.z; mm[7] = b.w;
+      const float4 c = reinterpret_cast<const float4*>(v + e)[0], d = reinterpret_cast<const float4*>(v + e)[1];
+      vv[0] = c.x; vv[1] = c.y; vv[2] = c.z; vv[3] = c.w; vv[4] = d.x; vv[5] = d.y; vv[6] = d.z; vv[7] = d.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gi = gj[j] * grad_scale;
+      mm[j] = b1 * mm[j] + (1.f - b1) * gi;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gi * gi;
+      const float denom = sqrtf(vv[j] * inv_bc2) + eps;
+      w[j] = w[j] * decay - lr * (mm[j] * inv_bc1) / denom;
+    }
+    reinterpret_cast<float4*>(m + e)[0] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(m + e)[1] = make_float4(mm[4], mm[5], mm[6], mm[7]);
+    reinterpret_cast<float4*>(v + e)[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    reinterpret_cast<float4*>(v + e)[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    if constexpr (kMaster == 1) {
+      reinterpret_cast<float4*>(master + e)[0] = make_float4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<float4*>(master + e)[1] = make_float4(w[4], w[5], w[6], w[7]);
+    }
+    if constexpr (kMaster == 2) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) master_to_split(w[j], ph[j], rh[j]);
+      *reinterpret_cast<uint4*>(residual + e) = rq;
+      *reinterpret_cast<uint4*>(p + e) = pq;
+    } else {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pq);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(w[2 * j], w[2 * j + 1]);
+      *reinterpret_cast<uint4*>(p + e) = pq;
+    }
+  }
+}
+
+// Scalar form of the residual representation (tails and unaligned buffers).
+template <typename TG>
+__global__ void adamw_residual_kernel(__nv_bfloat16* __restrict__ p, short* __restrict__ residual,
+                                      const TG* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                                      long long n, float lr, float b1, float b2, float eps, float wd, float bc1,
+                                      float bc2, float grad_scale) {
+  unsigned short* pb = reinterpret_cast<unsigned short*>(p);
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float gi = ldf(g, i) * grad_scale;
+    float w = master_from_split(pb[i], residual[i]);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    w = w * decay - lr * (mi * inv_bc1) / (sqrtf(vi * inv_bc2) + eps);
+    master_to_split(w, pb[i], residual[i]);
   }
 }
 
@@ -651,17 +763,48 @@ void embedding_backward(const long long* seg_ids, const long long* seg_start, lo
   });
 }
 
-void adamw_step(void* p, int p_dtype, float* master, const void* g, int g_dtype, float* m, float* v, long long n,
-                float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
+void adamw_step(void* p, int p_dtype, float* master, short* residual, const void* g, int g_dtype, float* m, float* v,
+                long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
                 cudaStream_t stream) {
   if (n <= 0) return;
   const int threads = 256;
-  const int grid = grid_for(n, threads);
+  long long done = 0;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                         reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(master) |
+                         reinterpret_cast<uintptr_t>(residual);
+  if (p_dtype == 1 && g_dtype != 2 && (bits & 15) == 0 && n >= 8) {
+    const long long n8 = n / 8;
+    const int grid = grid_for(n8, threads);
+    __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p);
+#define RLK_ADAMW_VEC(TG, MODE)                                                                                    \
+  adamw_bf16_vec_kernel<TG, MODE><<<grid, threads, 0, stream>>>(pb, master, residual, static_cast<const TG*>(g), m, v, \
+                                                                 n8, lr, b1, b2, eps, wd, bc1, bc2, grad_scale)
+    const int mode = residual ? 2 : (master ? 1 : 0);
+    if (g_dtype == 0) {
+      if (mode == 2) RLK_ADAMW_VEC(float, 2); else if (mode == 1) RLK_ADAMW_VEC(float, 1); else RLK_ADAMW_VEC(float, 0);
+    } else {
+      if (mode == 2) RLK_ADAMW_VEC(__nv_bfloat16, 2); else if (mode == 1) RLK_ADAMW_VEC(__nv_bfloat16, 1); else RLK_ADAMW_VEC(__nv_bfloat16, 0);
+    }
+#undef RLK_ADAMW_VEC
+    done = n8 * 8;
+  }
+  const long long rest = n - done;
+  if (rest <= 0) return;
+  const int grid = grid_for(rest, threads);
+  if (residual) {  // bf16 parameters only (checked by the binding)
+    __nv_bfloat16* pb = static_cast<__nv_bfloat16*>(p) + done;
+    RLK_DISPATCH_T(g_dtype, {
+      adamw_residual_kernel<T><<<grid, threads, 0, stream>>>(pb, residual + done, static_cast<const T*>(g) + done, m + done,
+                                                             v + done, rest, lr, b1, b2, eps, wd, bc1, bc2, grad_scale);
+    });
+    return;
+  }
   RLK_DISPATCH_T(p_dtype, {
     using TP = T;
     RLK_DISPATCH_T(g_dtype, {
-      adamw_kernel<TP, T><<<grid, threads, 0, stream>>>(static_cast<TP*>(p), master, static_cast<const T*>(g), m, v, n,
-                                                        lr, b1, b2, eps, wd, bc1, bc2, grad_scale);
+      adamw_kernel<TP, T><<<grid, threads, 0, stream>>>(static_cast<TP*>(p) + done, master ? master + done : nullptr,
+                                                        static_cast<const T*>(g) + done, m + done, v + done, rest, lr,
+                                                        b1, b2, eps, wd, bc1, bc2, grad_scale);
     });
   });
 }

@@ -57,6 +57,11 @@ extern "C" int rlk_rmsnorm_backward_noalloc(const void* x, const void* weight, c
     g_last_error = "null pointer, non-positive size, ld < dim or unknown dtype code";
     return RLK_NOALLOC_BAD_ARGUMENT;
   }
+  if (static_cast<long long>(dim) * 4 > RLK_NOALLOC_MAX_ROW_BYTES) {
+    g_last_error = "dim * 4 bytes exceeds the " + std::to_string(RLK_NOALLOC_MAX_ROW_BYTES) +
+                   "-byte shared-memory row buffer of the kernel";
+    return RLK_NOALLOC_BAD_ARGUMENT;
+  }
   if (rlk_rmsnorm_backward_noalloc_scratch_floats(rows, dim) > RLK_NOALLOC_SCRATCH_FLOATS) {
     g_last_error = "problem needs " + std::to_string(rlk_rmsnorm_backward_noalloc_scratch_floats(rows, dim)) +
                    " scratch floats; the built-in scratch holds " + std::to_string(RLK_NOALLOC_SCRATCH_FLOATS);
@@ -65,8 +70,11 @@ extern "C" int rlk_rmsnorm_backward_noalloc(const void* x, const void* weight, c
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != RLK_NOALLOC_OK) return rc;
+  // Drop a launch error that an earlier, unrelated call left behind, so that what is read after the launches below
+  // belongs to them; then read AND clear the result, so that a failure here is not blamed on the host's next call.
+  (void)cudaGetLastError();
   rlk::rmsnorm_backward(x, ld, x_dtype, weight, w_dtype, dy, ld, rstd, dx, ld, rows, dim, scratch, dweight, stream);
-  const cudaError_t e = cudaPeekAtLastError();
+  const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     g_last_error = std::string("launch failed: ") + cudaGetErrorString(e);
     return RLK_NOALLOC_CUDA_ERROR;

@@ -14,8 +14,14 @@
 //     RLK_NOALLOC_TOO_LARGE and nothing is launched; use the regular entry point (caller-provided
 //     scratch) for those.
 //   * The first call on a device resolves the device address of the scratch array
-//     (cudaGetSymbolAddress) and raises the kernel's shared-memory limit if dim needs it.  Make that
-//     first call outside of any stream capture.
+//     (cudaGetSymbolAddress).  Make that first call outside of any stream capture.
+//   * Rows of more than 12288 elements (dim * 4 bytes above 48 KB) on the generic path -- anything but
+//     bfloat16 x with bfloat16 weight -- need the kernel's opt-in shared-memory size: EVERY such call
+//     sets that attribute (a host-side call on the kernel for that dtype pair, no allocation), not only
+//     the first.  dim * 4 bytes above RLK_NOALLOC_MAX_ROW_BYTES cannot run at all and is rejected with
+//     RLK_NOALLOC_BAD_ARGUMENT before anything is launched.
+//   * The function reads and clears the CUDA runtime's last-error state before and after its launches:
+//     a launch failure is returned here (RLK_NOALLOC_CUDA_ERROR) and not left for the host's next call.
 //   * The function never calls cudaMalloc / cudaFree or any allocating library routine.
 //   * All calls on a device share the one scratch array, and it keeps the previous call's contents.
 //     The kernels overwrite every scratch element they later read, so nothing needs clearing, but two
@@ -28,6 +34,7 @@
 #include <cuda_runtime.h>
 
 #define RLK_NOALLOC_SCRATCH_FLOATS (1 << 20)
+#define RLK_NOALLOC_MAX_ROW_BYTES (227 * 1024)
 
 #define RLK_NOALLOC_OK 0
 #define RLK_NOALLOC_TOO_LARGE 1

@@ -269,10 +269,9 @@ void launch(const void* a_base, int M, int K, long long lda, const void* b_base,
   const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(b_base, K, N, ldb, kBK, 64) : make_tmap_2d_bf16(b_base, N, K, ldb, kBN, kBK);
   auto kernel = gemm_sm100_kernel<kBN, false, B_MN, kStages, Epi>;
   using L = GemmSmem<kBN, kStages, Epi::kStagingBytes>;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  if (configured.first()) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
-    configured = true;
   }
   const int grid = p.num_items < sm_count ? p.num_items : sm_count;
   if (grid < 1) return;

@@ -968,15 +968,22 @@ void adamw(Tensor p, std::optional<Tensor> master, const Tensor& g, Tensor m, Te
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw: size mismatch");
   const c10::cuda::CUDAGuard guard(p.device());
   float* mp = nullptr;
+  short* rp = nullptr;
   if (master.has_value() && master->defined()) {
-    TORCH_CHECK(master->scalar_type() == torch::kFloat32 && master->is_contiguous() && master->numel() == p.numel(),
-                "adamw: master must be contiguous float32");
-    mp = master->data_ptr<float>();
+    TORCH_CHECK(master->is_cuda() && master->is_contiguous() && master->numel() == p.numel(),
+                "adamw: master must be a contiguous CUDA tensor of the parameter's size");
+    if (master->scalar_type() == torch::kInt16) {  // 16-bit residuals of a bf16 parameter
+      TORCH_CHECK(p.scalar_type() == torch::kBFloat16, "adamw: int16 residual masters need bfloat16 parameters");
+      rp = reinterpret_cast<short*>(master->data_ptr<int16_t>());
+    } else {
+      TORCH_CHECK(master->scalar_type() == torch::kFloat32, "adamw: master must be float32 or int16 residuals");
+      mp = master->data_ptr<float>();
+    }
   }
   const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
   const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
   if (p.numel()) {
-    rlk::adamw_step(p.data_ptr(), dtype_code(p), mp, g.data_ptr(), dtype_code(g), m.data_ptr<float>(), v.data_ptr<float>(),
+    rlk::adamw_step(p.data_ptr(), dtype_code(p), mp, rp, g.data_ptr(), dtype_code(g), m.data_ptr<float>(), v.data_ptr<float>(),
                     p.numel(), static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2),
                     static_cast<float>(eps), static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), stream_of(p));
     after_launch();

@@ -2,9 +2,11 @@
 // addresses (ints) obtained from SymmetricHeap.ptrs(); local tensors as torch tensors.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAException.h>
 #include <torch/extension.h>
 
 #include <cmath>
+#include <type_traits>
 #include <vector>
 
 #include "../kernels/kernels.h"
@@ -46,7 +48,9 @@ void py_peer_barrier(std::vector<uint64_t> pads, int64_t rank, int64_t epoch, do
 
 void py_zero1_fused_step(std::vector<uint64_t> grads, std::vector<uint64_t> params, int64_t lo, int64_t hi, Tensor m,
                          Tensor v, std::optional<Tensor> master, double lr, double b1, double b2, double eps, double wd,
-                         int64_t step, double grad_scale) {
+                         int64_t step, double grad_scale, int64_t rank, std::optional<Tensor> barrier_err,
+                         int64_t max_blocks) {
+  TORCH_CHECK(rank >= 0 && rank < static_cast<int64_t>(params.size()), "rl_engine.zero1: rank out of range");
   TORCH_CHECK(lo % 8 == 0 && hi % 8 == 0 && hi >= lo, "rl_engine.zero1: shard bounds must be multiples of 8");
   TORCH_CHECK(m.is_cuda() && m.scalar_type() == torch::kFloat32 && m.is_contiguous() && m.numel() >= hi - lo &&
                   v.scalar_type() == torch::kFloat32 && v.is_contiguous() && v.numel() >= hi - lo,
@@ -63,9 +67,16 @@ void py_zero1_fused_step(std::vector<uint64_t> grads, std::vector<uint64_t> para
   auto p = to_ptrs(params);
   const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
   const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
-  zero1_fused_step(g.data(), p.data(), static_cast<int>(g.size()), lo, hi, m.data_ptr<float>(), v.data_ptr<float>(), mp,
-                   static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2), static_cast<float>(eps),
-                   static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), cur_stream(m.get_device()));
+  const uint32_t* skip = nullptr;
+  if (barrier_err.has_value() && barrier_err->defined()) {
+    TORCH_CHECK(barrier_err->is_cuda() && barrier_err->scalar_type() == torch::kInt32 && barrier_err->numel() >= 1,
+                "rl_engine.zero1: barrier_err must be the int32 error word of the preceding barrier");
+    skip = reinterpret_cast<const uint32_t*>(barrier_err->data_ptr<int>());
+  }
+  zero1_fused_step(g.data(), p.data(), static_cast<int>(rank), static_cast<int>(g.size()), lo, hi, m.data_ptr<float>(),
+                   v.data_ptr<float>(), mp, static_cast<float>(lr), static_cast<float>(b1), static_cast<float>(b2),
+                   static_cast<float>(eps), static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), skip,
+                   static_cast<int>(max_blocks), cur_stream(m.get_device()));
 }
 
 void py_peer_sum(std::vector<uint64_t> srcs, int64_t n, bool src_fp32, Tensor out) {
@@ -138,13 +149,21 @@ Tensor py_moe_combine_peer(std::vector<uint64_t> src, int64_t ld_src, int64_t hi
 
 }  // namespace
 
-// Every binding below launches exactly one kernel: count it and (with RLK_NVTX=1) put it in a range.
+// Every binding below launches exactly one kernel: count it, (with RLK_NVTX=1) put it in a range, and raise if the
+// launch itself was refused (bad configuration, attribute not set on this device, ...).
 template <typename R, typename... Args>
 auto counted(const char* name, R (*fn)(Args...)) {
   return [name, fn](Args... args) -> R {
     TraceRange range(name);
     count_launch(1);
-    return fn(std::forward<Args>(args)...);
+    if constexpr (std::is_void_v<R>) {
+      fn(std::forward<Args>(args)...);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    } else {
+      R out = fn(std::forward<Args>(args)...);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+      return out;
+    }
   };
 }
 

@@ -11,6 +11,7 @@ The reference's counterpart is ``DeepSpeedTrainingWorker.train``
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 from typing import Dict, Optional
 
@@ -63,11 +64,34 @@ def synthetic_batch(vocab: int, prompt_len: int, group: int, completion_len: int
     )
 
 
+def split_master(master: torch.Tensor):
+    """fp32 ``master`` -> (bf16 parameter, int16 residual) with ``master_bits = (bf16_bits << 16) + residual``.
+    The parameter is the master rounded to bf16 (ties away from zero in magnitude), so the pair holds every bit of
+    the fp32 value at 2 extra bytes per parameter."""
+    bits = master.contiguous().view(torch.int32)
+    up = (bits + 0x8000) >> 16  # arithmetic shift keeps the sign bit in place for the narrowing below
+    residual = (bits - (up << 16)).to(torch.int16)
+    return up.to(torch.int16).view(torch.bfloat16), residual
+
+
+def join_master(param: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``split_master``: the fp32 master of a bf16 ``param`` and its int16 ``residual``."""
+    bits = (param.contiguous().view(torch.int16).to(torch.int32) << 16) + residual.to(torch.int32)
+    return bits.view(torch.float32)
+
+
 class FlatAdamW:
-    """AdamW over one flat parameter buffer; one fused kernel launch per step on the GPU."""
+    """AdamW over one flat parameter buffer; one fused kernel launch per step on the GPU.
+
+    ``master_weights`` (default on): the update is applied to an fp32 master copy and the low-precision parameter is
+    its rounding, as DeepSpeed's bf16 optimiser does for the reference (``rl_engine/executors/deepspeed_trainer.py:
+    101-126``).  At a learning rate of 1e-6 an update is far below the bf16 spacing of a weight, so without a master
+    nearly every update would round away.  For bf16 parameters on the GPU the master is kept as the parameter plus a
+    16-bit residual (``split_master``): exact fp32 arithmetic for 2 extra bytes per parameter instead of 4, which is
+    what lets an 8 B-parameter model keep all activations on one 180 GB device."""
 
     def __init__(self, model, lr=1e-6, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0,
-                 master_weights: bool = False) -> None:
+                 master_weights: bool = True) -> None:
         self.model = model
         self.param = model.flat
         self.grad = model.ensure_flat_grad()
@@ -75,8 +99,24 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.m = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
         self.v = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
-        self.master = param.detach().float().clone() if master_weights else None
+        self.master: Optional[torch.Tensor] = None     # fp32 master (CPU, or parameters that are not bf16)
+        self.residual: Optional[torch.Tensor] = None   # int16 residuals of a bf16 parameter (GPU)
+        if master_weights and param.dtype != torch.float32:
+            if param.is_cuda and param.dtype == torch.bfloat16:
+                self.residual = torch.zeros(param.numel(), dtype=torch.int16, device=param.device)
+            else:
+                self.master = param.detach().float().clone()
         self.steps = 0
+
+    @property
+    def has_master(self) -> bool:
+        return self.master is not None or self.residual is not None
+
+    def master_weights(self) -> torch.Tensor:
+        """The fp32 values the optimiser works on (a copy when they are stored in split form)."""
+        if self.residual is not None:
+            return join_master(self.param.detach(), self.residual)
+        return self.master if self.master is not None else self.param.detach().float()
 
     def zero_grad(self) -> None:
         self.grad.zero_()
@@ -88,7 +128,8 @@ class FlatAdamW:
         if p.is_cuda:
             from rl_engine.kernels.ops.base import require_ext
 
-            require_ext().adamw(p, self.master, g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
+            state = self.residual if self.residual is not None else self.master
+            require_ext().adamw(p, state, g, self.m, self.v, self.lr, self.betas[0], self.betas[1], self.eps,
                                 self.weight_decay, self.steps, grad_scale)
             return
         b1, b2 = self.betas
@@ -103,14 +144,37 @@ class FlatAdamW:
         p.copy_(w.to(p.dtype))
 
     def state_dict(self) -> Dict[str, object]:
-        return {"m": self.m, "v": self.v, "master": self.master, "steps": self.steps}
+        """Tensors and ints only.  The master is saved in the form it is held in: ``master`` (fp32) or
+        ``master_residual`` (int16, to be joined with the saved bf16 parameters), so saving allocates nothing large."""
+        return {"m": self.m, "v": self.v, "master": self.master, "master_residual": self.residual, "steps": self.steps}
 
     def load_state_dict(self, state: Dict[str, object]) -> None:
+        """Call after the parameters have been restored.  A checkpoint without a master re-seeds the master from
+        the loaded parameters instead of keeping the values it had before."""
         self.m.copy_(state["m"])
         self.v.copy_(state["v"])
-        if self.master is not None and state.get("master") is not None:
-            self.master.copy_(state["master"])
         self.steps = int(state["steps"])
+        if not self.has_master:
+            return
+        saved, saved_residual = state.get("master"), state.get("master_residual")
+        if self.residual is not None:
+            if saved_residual is not None:      # same form: the restored parameters already are the rounded master
+                self.residual.copy_(saved_residual)
+            elif saved is not None:
+                param, residual = split_master(saved.to(self.param.device, torch.float32))
+                self.param.copy_(param)
+                self.residual.copy_(residual)
+            else:
+                self.residual.zero_()           # master == loaded parameters
+            return
+        if saved is not None:
+            master = saved.to(self.param.device, torch.float32)
+        elif saved_residual is not None:
+            master = join_master(self.param.detach(), saved_residual.to(self.param.device))
+        else:
+            master = self.param.detach().float()
+        self.master.copy_(master)
+        self.param.copy_(master.to(self.param.dtype))
 
 
 _GEOMETRY: Dict[tuple, tuple] = {}
@@ -244,7 +308,7 @@ class GRPOTrainer:
     cache_prompt = True  # micro-batches attend to the prompt's cached keys / values instead of re-processing it
 
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
-                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = False,
+                 adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
                  micro_group="auto") -> None:
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
@@ -297,16 +361,20 @@ class GRPOTrainer:
         g = batch.completion_ids.shape[0]
         m = self.completions_per_pass(batch)
         if m >= g:
-            loss, _pl, _kl = self.loss(batch)
+            with self.final_pass():
+                loss, _pl, _kl = self.loss(batch)
             loss.backward()
             return loss.detach()
         adv = self.advantages(batch)
         unmasked = batch.completion_mask.sum().clamp_min(1).float()
         total = torch.zeros((), dtype=torch.float32, device=batch.completion_ids.device)
-        prefix = self.prompt_pass(batch)
+        with self.final_pass():  # the prompt's backward pass runs after those of all micro-batches
+            prefix = self.prompt_pass(batch)
         for i0 in range(0, g, m):
             part = batch.completions(i0, min(g, i0 + m))
-            loss, _pl, _kl = self.loss_with_advantages(part, adv[i0:i0 + m].contiguous(), prefix)
+            last_without_prefix = prefix is None and i0 + m >= g
+            with (self.final_pass() if last_without_prefix else contextlib.nullcontext()):
+                loss, _pl, _kl = self.loss_with_advantages(part, adv[i0:i0 + m].contiguous(), prefix)
             weighted = loss * (part.completion_mask.sum().float() / unmasked)
             weighted.backward()
             total += weighted.detach()
@@ -321,6 +389,11 @@ class GRPOTrainer:
             return None
         return _PromptPass(self.model, batch.prompt_ids)
 
+    def final_pass(self):
+        """Context manager around the FORWARD of the pass whose backward runs last in the step.  A trainer that
+        overlaps its gradient exchange with that backward pass hooks in here; the plain trainer does nothing."""
+        return contextlib.nullcontext()
+
     def before_optimizer_step(self) -> None:
         """Hook for trainers whose gradients need a reduction that the optimiser kernel does not do."""
 
@@ -334,8 +407,9 @@ class GRPOTrainer:
                 loss = self.forward_backward(batch)
                 break
             except torch.cuda.OutOfMemoryError:
+                applied = getattr(self.opt, "_launched", None)  # buckets an overlapped optimiser has already applied
                 if (not self.retry_on_out_of_memory or not hasattr(self.model, "kept_layers")
-                        or self.model.kept_layers() == 0):
+                        or self.model.kept_layers() == 0 or (applied and any(applied))):
                     raise
             torch.cuda.empty_cache()
             self.model.reduce_kept_layers(4)

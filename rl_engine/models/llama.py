@@ -205,6 +205,10 @@ class LlamaModel(nn.Module):
         super().__init__()
         self.cfg = cfg
         self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)
+        # Optional ``callable(layer_index)``: while it is set, every training forward registers gradient hooks that
+        # call it from inside backward when the backward pass has left layer ``layer_index`` (``num_layers`` = the
+        # final norm), i.e. when nothing of this pass touches the parameters of layers >= ``layer_index`` again.
+        self.layer_grad_hook = None
         self._fp8_linears: Dict[str, object] = {}
         h, f = cfg.hidden_size, cfg.ffn_size
         qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
@@ -398,6 +402,16 @@ class LlamaModel(nn.Module):
         """After an out-of-memory error: recompute ``by`` more layers from now on.  Returns the new number kept."""
         return self._planner.reduce(by)
 
+    def _watch(self, x: torch.Tensor, layer: int) -> torch.Tensor:
+        """Registers the ``layer_grad_hook`` notification on ``x``, the input of layer ``layer``."""
+        hook = self.layer_grad_hook
+        if hook is not None and x.requires_grad:
+            def fire(_grad, layer=layer, hook=hook):
+                hook(layer)
+
+            x.register_hook(fire)
+        return x
+
     def hidden_states(self, token_ids: torch.Tensor, positions: torch.Tensor, layout) -> torch.Tensor:
         """Packed ``token_ids [T]`` -> final-norm hidden states ``[T, H]``."""
         from rl_engine.kernels.registry import kernel_registry
@@ -406,10 +420,12 @@ class LlamaModel(nn.Module):
         training = torch.is_grad_enabled()
         first_kept = self.cfg.num_layers - (self.plan_checkpointing(token_ids.numel()) if training else 0)
         for i in range(self.cfg.num_layers):
+            self._watch(x, i)
             if training and i < first_kept:
                 x = checkpoint(self._layer, x, i, positions, layout, use_reentrant=False)
             else:
                 x = self._layer(x, i, positions, layout)
+        self._watch(x, self.cfg.num_layers)
         return rms_norm(x, self.view("final_norm"), self.cfg.rms_eps)
 
     # -- prefix-cached passes: the shared prompt runs once, later passes hold only completion tokens ------------
@@ -430,8 +446,10 @@ class LlamaModel(nn.Module):
         x = kernel_registry.get_op("embedding")(prompt_ids, self.view("embed"))
         kv = []
         for i in range(self.cfg.num_layers):
+            self._watch(x, i)
             x, k_rot, v_rot = self._layer(x, i, positions, layout, return_kv=True)
             kv.append((k_rot, v_rot))
+        self._watch(x, self.cfg.num_layers)
         return rms_norm(x[-1:], self.view("final_norm"), self.cfg.rms_eps), kv
 
     def hidden_states_after_prefix(self, token_ids: torch.Tensor, positions: torch.Tensor, layout, kv) -> torch.Tensor:

@@ -1,11 +1,19 @@
 """Data-parallel GRPO step with optimizer state sharded over the ranks (ZeRO-1 style) and ONE fused
-kernel for the whole gradient/parameter exchange.
+kernel for the whole gradient/parameter exchange of a bucket.
 
 Every rank keeps the full bf16 parameters and gradients as flat buffers inside the symmetric heap.
-After backward, ``zero1_fused_step`` on rank r reads slice r of every peer's gradient buffer over
-NVLink, sums in fixed rank order in fp32, scales by 1/world, applies AdamW on its fp32 moments (and
-fp32 master slice) and writes the updated bf16 slice into every peer's parameter buffer.  Two
-device-side barriers bracket the kernel.  There is no NCCL call in the step.
+The flat vector is cut into buckets at layer boundaries (``[embedding] [4 layers] ... [final norm +
+LM head]``); inside a bucket rank r owns the r-th slice.  ``zero1_fused_step`` on rank r reads its
+slice of every peer's gradient buffer over NVLink, sums in fixed rank order in fp32, scales by
+1/world, applies AdamW on its fp32 moments and fp32 master slice and writes the updated bf16 slice
+into every peer's parameter buffer.  There is no NCCL call in the step.
+
+Overlap: the last backward pass of a step (the shared prompt's, or the only pass) visits the layers
+from last to first, and once it has left a layer nothing of the step reads that layer's parameters or
+adds to its gradients again.  The model reports that through ``layer_grad_hook``; the optimiser then
+launches the bucket's barrier + fused kernel on a side stream (its own barrier channel) while the
+backward pass continues on the main stream.  Only the first bucket (embedding + first layers) and the
+closing barrier stay exposed.
 
 The reference delegates all of this to DeepSpeed (``rl_engine/executors/deepspeed_trainer.py:
 101-126,168-169``).
@@ -13,7 +21,8 @@ The reference delegates all of this to DeepSpeed (``rl_engine/executors/deepspee
 
 from __future__ import annotations
 
-from typing import Optional
+import contextlib
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -22,39 +31,149 @@ from rl_engine.models.grpo import GRPOBatch, GRPOTrainer
 from rl_engine.models.llama import LlamaModel
 from rl_engine.parallel.symmetric import SymmetricMemory
 
+_SIDE_CHANNEL = 1  # barrier channel of the side stream
+
+
+def layer_buckets(model: LlamaModel, layers_per_bucket: int = 4) -> Tuple[List[Tuple[int, int]], Dict[int, int]]:
+    """Cuts the flat parameter vector at layer boundaries.
+
+    Returns ``(ranges, ready_at)``: ``ranges[b] = (lo, hi)`` in elements of the flat vector, in flat order; bucket
+    ``b`` is final once the backward pass has left layer ``ready_at[b]`` (``num_layers`` stands for the final norm).
+    Bucket 0 (the embedding and the first layers) has no entry: it is final only when the whole backward has ended."""
+    offsets = model._offsets
+    n_layers = model.cfg.num_layers
+    total = model.flat.numel()
+    start = lambda i: offsets[f"l{i}.attn_norm"] if i < n_layers else offsets["final_norm"]
+    step = max(1, int(layers_per_bucket))
+    first = min(step, n_layers)
+    cuts = [0] + [start(i) for i in range(first, n_layers, step)] + [start(n_layers), total]
+    layer_of_cut = [0] + list(range(first, n_layers, step)) + [n_layers]
+    ranges, ready_at = [], {}
+    for b in range(len(cuts) - 1):
+        if cuts[b + 1] > cuts[b]:
+            ranges.append((cuts[b], cuts[b + 1]))
+            if b > 0:
+                ready_at[len(ranges) - 1] = layer_of_cut[b]
+    return ranges, ready_at
+
 
 class ShardedFusedAdamW:
+    """AdamW whose moments and fp32 master weights exist only for this rank's slices of the buckets."""
+
     def __init__(self, model: LlamaModel, mem: SymmetricMemory, params, grads, lr=1e-6, betas=(0.9, 0.95), eps=1e-8,
-                 weight_decay=0.0, master_weights: bool = True) -> None:
+                 weight_decay=0.0, master_weights: bool = True, layers_per_bucket: int = 4, overlap: bool = True,
+                 overlap_blocks: int = 148 * 2) -> None:
         self.model, self.mem, self.params, self.grads = model, mem, params, grads
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
-        n = params.local.numel()
-        per = (n + mem.world - 1) // mem.world
-        per = (per + 7) // 8 * 8
-        self.lo = min(mem.rank * per, n)
-        self.hi = min(self.lo + per, n)
-        shard = self.hi - self.lo
+        n = model.flat.numel()
+        ranges, self.ready_at = layer_buckets(model, layers_per_bucket)
+        # the symmetric buffers are padded to a multiple of 8 elements; the pad belongs to the last bucket
+        ranges[-1] = (ranges[-1][0], params.local.numel())
+        self.numel = n
+        self.slices: List[Tuple[int, int, int]] = []  # (lo, hi, offset into m / v / master) per bucket
+        off = 0
+        for lo_b, hi_b in ranges:
+            size = hi_b - lo_b
+            per = ((size + mem.world - 1) // mem.world + 7) // 8 * 8
+            lo = min(lo_b + mem.rank * per, hi_b)
+            hi = min(lo + per, hi_b)
+            self.slices.append((lo, hi, off))
+            off += hi - lo
         dev = params.local.device
-        self.m = torch.zeros(shard, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(shard, dtype=torch.float32, device=dev)
-        self.master = params.local[self.lo : self.hi].float() if master_weights else None
+        self.m = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.master = self._gather_local(params.local).float() if master_weights else None
         self.steps = 0
+        self.overlap = bool(overlap) and mem.world > 1
+        self.overlap_blocks = int(overlap_blocks)
+        self._side = torch.cuda.Stream(device=dev) if self.overlap else None
+        self._launched: List[bool] = [False] * len(self.slices)
+        self._side_used = False
+        self._armed = False
+
+    def _gather_local(self, flat: torch.Tensor) -> torch.Tensor:
+        return torch.cat([flat[lo:hi] for lo, hi, _ in self.slices]) if self.slices else flat[:0]
 
     def zero_grad(self) -> None:
         self.grads.local.zero_()
 
+    # -- one bucket ---------------------------------------------------------------------------------------
+    def _launch_bucket(self, b: int, channel: int, max_blocks: int) -> None:
+        lo, hi, off = self.slices[b]
+        self.mem.barrier(channel)  # every rank's gradients of this bucket are final
+        n = hi - lo
+        master = None if self.master is None else self.master[off : off + n]
+        require_ext().zero1_fused_step(
+            self.grads.ptrs, self.params.ptrs, lo, hi, self.m[off : off + n], self.v[off : off + n], master, self.lr,
+            self.betas[0], self.betas[1], self.eps, self.weight_decay, self.steps + 1, 1.0 / self.mem.world,
+            self.mem.rank, self.mem.error_word, max_blocks,
+        )
+        self._launched[b] = True
+
+    # -- overlap with the last backward pass --------------------------------------------------------------
+    def arm(self) -> None:
+        """The pass whose forward starts now is the last one that is back-propagated in this step."""
+        self._launched = [False] * len(self.slices)
+        self._side_used = False
+        self._armed = True
+
+    def on_layer_done(self, layer: int) -> None:
+        """Called from inside backward when it has left layer ``layer``: buckets holding only layers >= ``layer``
+        are final on this rank."""
+        if not (self.overlap and self._armed):
+            return
+        ready = [b for b, at in self.ready_at.items() if at >= layer and not self._launched[b]]
+        if not ready:
+            return
+        main = torch.cuda.current_stream(self.m.device)
+        self._side.wait_stream(main)
+        self._side_used = True
+        with torch.cuda.stream(self._side):
+            for b in sorted(ready, reverse=True):  # the same order on every rank
+                self._launch_bucket(b, _SIDE_CHANNEL, self.overlap_blocks)
+
     @torch.no_grad()
     def step(self) -> None:
+        """Launches what the backward pass has not launched yet and waits (on the device) for all of it."""
+        if not self._armed:
+            self._launched = [False] * len(self.slices)
+        main = torch.cuda.current_stream(self.m.device)
+        for b in range(len(self.slices) - 1, -1, -1):
+            if not self._launched[b]:
+                self._launch_bucket(b, 0, 0)
+        if self._side_used:
+            main.wait_stream(self._side)
         self.steps += 1
-        self.mem.barrier()  # every rank's gradients are final
-        require_ext().zero1_fused_step(
-            self.grads.ptrs, self.params.ptrs, self.lo, self.hi, self.m, self.v, self.master, self.lr, self.betas[0],
-            self.betas[1], self.eps, self.weight_decay, self.steps, 1.0 / self.mem.world,
-        )
-        self.mem.barrier()  # every rank's parameter slice has landed everywhere
+        self._armed = False
+        self._launched = [False] * len(self.slices)
+        self.mem.barrier()  # every rank's parameter slices have landed everywhere
 
+    # -- checkpoint ---------------------------------------------------------------------------------------
     def state_dict(self):
-        return {"m": self.m, "v": self.v, "master": self.master, "steps": self.steps, "lo": self.lo, "hi": self.hi}
+        """This rank's shard: tensors, ints and lists of ints only."""
+        return {"m": self.m, "v": self.v, "master": self.master, "steps": self.steps, "rank": self.mem.rank,
+                "world": self.mem.world, "slices": [[lo, hi] for lo, hi, _ in self.slices]}
+
+    @torch.no_grad()
+    def load_state_dict(self, state) -> None:
+        """Restores a shard saved by the same rank of the same world size and bucket layout.  Call after the
+        parameters were restored; a checkpoint without master weights re-seeds them from the parameters."""
+        mine = [[lo, hi] for lo, hi, _ in self.slices]
+        theirs = [list(map(int, s)) for s in state.get("slices", [])]
+        if theirs != mine or int(state.get("world", self.mem.world)) != self.mem.world \
+                or int(state.get("rank", self.mem.rank)) != self.mem.rank:
+            raise ValueError(f"optimizer shard does not match this rank: saved slices {theirs[:2]}... of rank "
+                             f"{state.get('rank')}/{state.get('world')}, expected {mine[:2]}... of rank "
+                             f"{self.mem.rank}/{self.mem.world}")
+        for lo, hi in mine:
+            if lo % 8 or hi % 8 or hi < lo:
+                raise ValueError("shard bounds must be ordered multiples of 8")
+        self.m.copy_(state["m"])
+        self.v.copy_(state["v"])
+        self.steps = int(state["steps"])
+        if self.master is not None:
+            saved = state.get("master")
+            self.master.copy_(self._gather_local(self.params.local).float() if saved is None else saved)
 
 
 class ShardedGRPOTrainer(GRPOTrainer):
@@ -62,20 +181,22 @@ class ShardedGRPOTrainer(GRPOTrainer):
 
     def __init__(self, model: LlamaModel, *, group=None, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
-                 micro_group="auto") -> None:
+                 micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4) -> None:
         n = model.flat.numel()
+        padded = (n + 7) // 8 * 8
         itemsize = model.flat.element_size()
-        self.mem = SymmetricMemory(2 * n * itemsize + (1 << 20), group=group, device=model.flat.device)
-        params = self.mem.alloc((n,), model.flat.dtype)
-        grads = self.mem.alloc((n,), model.flat.dtype)
-        params.local.copy_(model.flat)
-        model.rebind_storage(params.local, grads.local)
+        self.mem = SymmetricMemory(2 * padded * itemsize + (1 << 20), group=group, device=model.flat.device)
+        params = self.mem.alloc((padded,), model.flat.dtype)
+        grads = self.mem.alloc((padded,), model.flat.dtype)
+        params.local[:n].copy_(model.flat)
+        model.rebind_storage(params.local[:n], grads.local[:n])
         self.model = model
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
         self.micro_group = micro_group
         self._micro_choice = {}
         self.opt = ShardedFusedAdamW(model, self.mem, params, grads, lr=lr, weight_decay=weight_decay,
-                                     master_weights=master_weights)
+                                     master_weights=master_weights, layers_per_bucket=layers_per_bucket,
+                                     overlap=overlap)
         self._slice: Optional[slice] = None
         self.mem.barrier()
 
@@ -86,6 +207,16 @@ class ShardedGRPOTrainer(GRPOTrainer):
     def advantages(self, batch: GRPOBatch) -> torch.Tensor:
         adv = super().advantages(batch)
         return adv if self._slice is None else adv[self._slice].contiguous()
+
+    @contextlib.contextmanager
+    def final_pass(self):
+        """Wraps the forward of the pass that is back-propagated last: its layer hooks start the buckets."""
+        self.opt.arm()
+        self.model.layer_grad_hook = self.opt.on_layer_done
+        try:
+            yield
+        finally:
+            self.model.layer_grad_hook = None
 
     def check(self) -> None:
         self.mem.check()

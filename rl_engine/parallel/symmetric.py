@@ -32,6 +32,7 @@ from rl_engine.kernels.ops.base import require_ext
 
 _ALIGN = 256
 _PAD_BYTES = 4096  # signal pad at the start of every segment
+_BARRIER_CHANNELS = 8  # independent barrier sequences, 64 bytes of the pad each (one per stream that synchronises)
 
 
 class PeerTimeoutError(RuntimeError):
@@ -61,7 +62,7 @@ class SymmetricMemory:
         ext = require_ext()
         self.heap = ext.SymmetricHeap(self.device.index or 0, int(nbytes) + _PAD_BYTES, self.rank, self.world)
         self._cursor = _PAD_BYTES
-        self._epoch = 0
+        self._epochs = [0] * _BARRIER_CHANNELS
         self._err = torch.zeros(4, dtype=torch.int32, device=self.device)
         if self.world > 1:
             self._exchange(dist)
@@ -115,10 +116,22 @@ class SymmetricMemory:
         return SymmetricTensor(self, offset, tuple(int(s) for s in shape), dtype)
 
     # -- synchronisation ------------------------------------------------------------------------
-    def barrier(self) -> None:
-        """Device-side barrier on the current stream (bounded)."""
-        self._epoch += 1
-        require_ext().peer_barrier(self.ptrs, self.rank, self._epoch, self.wait_limit_ms, self._err)
+    def barrier(self, channel: int = 0) -> None:
+        """Device-side barrier on the current stream (bounded).
+
+        Barriers of one ``channel`` must be issued by all ranks in the same order and on one stream per rank: the
+        flags of a channel are epoch counters, so two barriers of a channel that ran concurrently on different
+        streams could overtake each other.  Work on a second stream uses its own channel (0..7)."""
+        if not 0 <= channel < _BARRIER_CHANNELS:
+            raise ValueError(f"barrier channel must be in [0, {_BARRIER_CHANNELS})")
+        self._epochs[channel] += 1
+        pads = self.ptrs if channel == 0 else [p + 64 * channel for p in self.ptrs]
+        require_ext().peer_barrier(pads, self.rank, self._epochs[channel], self.wait_limit_ms, self._err)
+
+    @property
+    def error_word(self) -> torch.Tensor:
+        """int32[4] on the device: non-zero first element once a bounded wait of ``barrier`` has expired."""
+        return self._err
 
     def check(self) -> None:
         """Synchronise and raise ``PeerTimeoutError`` if a bounded wait expired since the last check."""

@@ -100,7 +100,7 @@ def main() -> None:
     all_grads = [torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + r)).to(torch.bfloat16)
                  for r in range(world)]
     mem.barrier()
-    ext.zero1_fused_step(grads.ptrs, params.ptrs, lo, hi, m, v, master, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0 / world)
+    ext.zero1_fused_step(grads.ptrs, params.ptrs, lo, hi, m, v, master, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1, 1.0 / world, rank, None, 0)
     mem.barrier()
     ref = params.local.new_empty(n, dtype=torch.float32).copy_(p0.to(torch.bfloat16).float()).requires_grad_(True)
     opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)

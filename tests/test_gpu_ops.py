@@ -320,6 +320,40 @@ def test_adamw_matches_torch():
     assert torch.allclose(pb.float(), master, atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("lr", [1e-6, 1e-2])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_adamw_split_master_is_the_fp32_master_bit_for_bit(lr, offset):
+    """bf16 parameter + 16-bit residual carries the same fp32 master as a separate fp32 copy (vector path, scalar
+    tail, and the scalar path of an unaligned buffer)."""
+    from rl_engine.kernels.ops.base import require_ext
+    from rl_engine.models.grpo import join_master, split_master
+
+    ext = require_ext()
+    g = _gen(21)
+    n = 100003
+    base = (torch.randn(n + 8, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    pa, pb = base.clone()[offset : offset + n], base.clone()[offset : offset + n]
+    master = pa.float()
+    residual = torch.zeros(n + 8, dtype=torch.int16, device=DEV)[offset : offset + n]
+    ma, va = torch.zeros(n + 8, device=DEV)[offset : offset + n], torch.zeros(n + 8, device=DEV)[offset : offset + n]
+    mb, vb = torch.zeros(n + 8, device=DEV)[offset : offset + n], torch.zeros(n + 8, device=DEV)[offset : offset + n]
+    start = pa.clone()
+    for step in range(1, 6):
+        grad = torch.randn(n + 8, device=DEV, generator=g).to(torch.bfloat16)[offset : offset + n]
+        ext.adamw(pa, master, grad, ma, va, lr, 0.9, 0.95, 1e-8, 0.01, step, 0.5)
+        ext.adamw(pb, residual, grad, mb, vb, lr, 0.9, 0.95, 1e-8, 0.01, step, 0.5)
+        assert torch.equal(join_master(pb, residual).view(torch.int32), master.view(torch.int32))
+    assert torch.equal(ma, mb) and torch.equal(va, vb)
+    want_param, want_residual = split_master(master)
+    assert torch.equal(pb, want_param) and torch.equal(residual, want_residual)
+    # the two roundings of the same master differ only on exact ties, by one bf16 step
+    differ = pa != pb
+    assert differ.float().mean().item() < 1e-3
+    if lr == 1e-6:
+        assert (pb != start).float().mean().item() < 0.2  # bf16 weights barely move in five such steps ...
+        assert (master != start.float()).float().mean().item() > 0.99  # ... the master always does
+
+
 # -------------------------------------------------------------------------------- sampler
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_sampler_matches_host_restatement(dtype):

@@ -67,6 +67,36 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         assert torch.equal(dw, want_dw)
 
 
+@pytest.mark.parametrize("case", ["fp16", "fp32_wide_rows", "mixed_dtypes", "row_pitch"])
+def test_noalloc_other_paths_match_regular_entry_point(case):
+    """The generic kernel (fp16, mixed x / weight types), rows wider than 48 KB of shared memory, and a row pitch
+    larger than the row, each called twice in a row."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    ext = require_ext()
+    lib = _lib()
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    xdt, wdt, dim, pitch = {
+        "fp16": (torch.float16, torch.float16, 640, 640),
+        "fp32_wide_rows": (torch.float32, torch.float32, 16384, 16384),
+        "mixed_dtypes": (torch.bfloat16, torch.float32, 768, 768),
+        "row_pitch": (torch.bfloat16, torch.bfloat16, 512, 640),
+    }[case]
+    for rows in (130, 65):
+        x = torch.randn(rows, pitch, device="cuda", generator=gen).to(xdt)[:, :dim]
+        dy = torch.randn(rows, pitch, device="cuda", generator=gen).to(xdt)[:, :dim]
+        w = torch.randn(dim, device="cuda", generator=gen).to(wdt)
+        _, rstd = ext.rmsnorm_fwd(x.contiguous(), w, 1e-6, False, True)
+        want_dx, want_dw = ext.rmsnorm_bwd(x.contiguous(), w, dy.contiguous(), rstd)
+        dx = torch.full((rows, pitch), float("nan"), device="cuda", dtype=xdt)[:, :dim]
+        dw = torch.full_like(w, float("nan"))
+        rc = _call(lib, x, w, dy, rstd, dx, dw)
+        assert rc == 0, lib.rlk_noalloc_last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(dx, want_dx)
+        assert torch.equal(dw, want_dw)
+
+
 def test_noalloc_rejects_oversized_and_bad_arguments():
     lib = _lib()
     rows, dim = 64 * 300, 4096  # 300 chunks x 4096 floats > 2^20
@@ -78,3 +108,11 @@ def test_noalloc_rejects_oversized_and_bad_arguments():
     assert _call(lib, x, w, x, rstd, dx, dw) == 1
     assert b"scratch" in lib.rlk_noalloc_last_error()
     assert lib.rlk_rmsnorm_backward_noalloc(0, 0, 0, 0, 0, 0, 1, 1, 1, 0, 0, None) == 2
+    # a row that cannot fit the kernel's shared-memory buffer is refused before any launch
+    wide = 60000
+    xw = torch.zeros(1, wide, device="cuda")
+    ww = torch.ones(wide, device="cuda")
+    assert _call(lib, xw, ww, xw, torch.ones(1, device="cuda"), torch.zeros_like(xw), torch.zeros_like(ww)) == 2
+    assert b"shared-memory" in lib.rlk_noalloc_last_error()
+    torch.cuda.synchronize()
+    assert torch.zeros(1, device="cuda").item() == 0.0  # the context is intact and no error was left behind
