@@ -313,6 +313,8 @@ def measure_ops(torch, dist, kernel_registry, device, rank, world):
                 op(hidden, weight, targets, None, **kw).backward(grad_out)
 
             inputs = nbytes(hidden, weight, targets, grad_out)
+            hidden.grad = None
+            weight.grad = None  # left over from the previous G: not part of this call
             torch.cuda.synchronize()
             torch.cuda.reset_peak_memory_stats(device)
             fwd()

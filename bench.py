@@ -192,6 +192,8 @@ def measure_fused_logp(device, rank: int, world: int, iters: int = 20):
         # everything above ``floor`` that is not an input or a returned tensor counts as extra, including the
         # workspaces that the op keeps between calls (created at the first call, they do not grow with G)
         inputs = nbytes(hidden, weight, targets, grad_out)
+        hidden.grad = None
+        weight.grad = None  # left over from the previous G: not part of this call
         torch.cuda.synchronize()
         torch.cuda.reset_peak_memory_stats(device)
         fwd()

@@ -73,6 +73,7 @@ struct LinearLogpFwdArgs {
   int n_tokens, hidden_dim, v_local;
   long long ld_hidden, ld_weight;
   long long vocab_start;
+  long long global_vocab;  // > 0: target ids outside [0, global_vocab) set kErrBadArgument (site 11) and give NaN
   int rank, world;
   int slot_base;      // first record slot of this rank in the partial buffers
   int total_records;  // records per row over all ranks (0: world * items_per_m)

@@ -28,6 +28,7 @@ struct LogpFwdParams {
   const long long* target;  // [N] global vocab ids
   const float* bias;        // [V_local] or null
   long long vocab_start;    // global id of local column 0
+  long long global_vocab;   // > 0: a target id outside [0, global_vocab) is reported in the error word
   int rank, world;
   int slot_base;            // first record slot of this rank (sum of the lower ranks' items_per_m)
   int total_records;        // records per row over all ranks
@@ -168,6 +169,15 @@ __device__ void logp_merge_phase(const LogpFwdParams& ep, const GemmProblem& p, 
       ZT += rec.w;
     }
     const float lse = (M2 + log2f(S)) * kLn2;
+    if (ep.global_vocab > 0) {
+      // The range check of the target ids happens here, on the device, instead of a host read-back per call: the
+      // row's log-prob becomes NaN and the error word tells the host at its next check.
+      const long long id = ep.target[row];
+      if (id < 0 || id >= ep.global_vocab) {
+        report_error(ep.err, kErrBadArgument, kernel_id, 11);
+        ZT = __int_as_float(0x7fc00000);
+      }
+    }
     ep.logp[row] = ZT - lse;
     if (ep.lse != nullptr) ep.lse[row] = lse;
     if (ep.entropy != nullptr) ep.entropy[row] = lse - T / S;
@@ -302,6 +312,7 @@ void linear_logp_forward(const LinearLogpFwdArgs& a, cudaStream_t stream) {
   ep.target = a.target;
   ep.bias = a.bias;
   ep.vocab_start = a.vocab_start;
+  ep.global_vocab = a.global_vocab;
   ep.rank = a.rank;
   ep.world = a.world;
   ep.slot_base = a.slot_base;

@@ -473,7 +473,7 @@ std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, 
                                     std::optional<Tensor> bias, int64_t vocab_start, int64_t rank, int64_t world,
                                     int64_t slot_base, int64_t total_records, std::vector<int64_t> peer_partials, std::vector<int64_t> peer_counters,
                                     int64_t next_counters, int64_t counter_capacity, bool want_lse,
-                                    bool want_entropy, double wait_limit_ms) {
+                                    bool want_entropy, double wait_limit_ms, int64_t global_vocab) {
   check_rowmajor(hidden, "hidden");
   check_rowmajor(weight, "weight");
   check_cuda(target, "target");
@@ -509,6 +509,7 @@ std::vector<Tensor> linear_logp_fwd(const Tensor& hidden, const Tensor& weight, 
   a.ld_hidden = hidden.stride(0);
   a.ld_weight = weight.stride(0);
   a.vocab_start = vocab_start;
+  a.global_vocab = global_vocab;
   a.rank = static_cast<int>(rank);
   a.world = static_cast<int>(world);
   a.slot_base = static_cast<int>(slot_base);
@@ -1204,7 +1205,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("weight") = py::none());
   m.def("moe_rowdot", rlk::traced("rlk::moe_rowdot", &moe_rowdot));
   m.def("linear_logp_workspace_shape", rlk::traced("rlk::linear_logp_workspace_shape", &linear_logp_workspace_shape));
-  m.def("linear_logp_fwd", rlk::traced("rlk::linear_logp_fwd", &linear_logp_fwd));
+  m.def("linear_logp_fwd", rlk::traced("rlk::linear_logp_fwd", &linear_logp_fwd), py::arg("hidden"), py::arg("weight"),
+        py::arg("target"), py::arg("bias"), py::arg("vocab_start"), py::arg("rank"), py::arg("world"),
+        py::arg("slot_base"), py::arg("total_records"), py::arg("peer_partials"), py::arg("peer_counters"),
+        py::arg("next_counters"), py::arg("counter_capacity"), py::arg("want_lse"), py::arg("want_entropy"),
+        py::arg("wait_limit_ms"), py::arg("global_vocab") = 0);
   m.def("linear_logp_dz", rlk::traced("rlk::linear_logp_dz", &linear_logp_dz));
   m.def("logp_rows", rlk::traced("rlk::logp_rows", &logp_rows));
   m.def("ratio_kl_fwd", rlk::traced("rlk::ratio_kl_fwd", &ratio_kl_fwd));

@@ -19,19 +19,46 @@ import torch
 from rl_engine.executors.bridge import FileBlobBridge
 
 
+def _optimizer_file(directory: str, rank: int, world: int) -> str:
+    """One file per rank when the optimizer state is sharded (``optimizer.rank3of8.pt``), else ``optimizer.pt``."""
+    return os.path.join(directory, "optimizer.pt" if world <= 1 else f"optimizer.rank{rank}of{world}.pt")
+
+
+def _plain(value: Any) -> Any:
+    """Optimizer state as tensors (on the CPU), numbers, strings, ``None`` and lists / dicts of those: what
+    ``torch.load(..., weights_only=True)`` accepts, so that loading a checkpoint never unpickles code."""
+    if torch.is_tensor(value):
+        return value.detach().cpu()
+    if isinstance(value, dict):
+        return {str(k): _plain(v) for k, v in value.items()}
+    if isinstance(value, (list, tuple)):
+        return [_plain(v) for v in value]
+    if value is None or isinstance(value, (bool, int, float, str)):
+        return value
+    raise TypeError(f"optimizer state holds a {type(value).__name__}, which a checkpoint cannot carry")
+
+
 def save_checkpoint(directory: str, model: Any, optimizer: Any = None, *, weight_version: int = 0,
-                    sampler: Any = None, extra: Optional[Dict[str, Any]] = None) -> str:
-    """Write ``weights.{blob,json}``, ``optimizer.pt`` and ``state.json`` under ``directory``; returns the update id."""
+                    sampler: Any = None, extra: Optional[Dict[str, Any]] = None, rank: int = 0,
+                    world: int = 1) -> Optional[str]:
+    """Write ``weights.{blob,json}``, the optimizer state and ``state.json`` under ``directory``.
+
+    With data-parallel ranks (``world`` > 1) every rank calls this with its ``rank``: rank 0 writes the weights and
+    ``state.json`` (all ranks hold the same weights), every rank writes its own optimizer shard.  Returns the update
+    id on the rank that wrote the weights, ``None`` elsewhere."""
     os.makedirs(directory, exist_ok=True)
+    if optimizer is not None:
+        torch.save(_plain(optimizer.state_dict()), _optimizer_file(directory, rank, world))
+    if rank != 0:
+        return None
     bridge = FileBlobBridge(directory, source_worker="checkpoint")
     bridge._latest_published_weight_version = int(weight_version) - 1
     source = model.state_dict_views() if hasattr(model, "state_dict_views") else model
     manifest = bridge.publish(source, weight_version=int(weight_version), metadata={"checkpoint": True})
-    if optimizer is not None:
-        torch.save(optimizer.state_dict(), os.path.join(directory, "optimizer.pt"))
     state = {
         "update_id": manifest.update_id,
         "weight_version": int(weight_version),
+        "world": int(world),
         "sampler": None if sampler is None else {"seed": int(sampler.seed), "offset": int(sampler._offset)},
         "extra": dict(extra or {}),
     }
@@ -41,9 +68,15 @@ def save_checkpoint(directory: str, model: Any, optimizer: Any = None, *, weight
 
 
 @torch.no_grad()
-def load_checkpoint(directory: str, model: Any, optimizer: Any = None, *, sampler: Any = None) -> Dict[str, Any]:
+def load_checkpoint(directory: str, model: Any, optimizer: Any = None, *, sampler: Any = None, rank: int = 0,
+                    world: int = 1) -> Dict[str, Any]:
+    """Restores weights (validated against the manifest), then the optimizer state of this ``rank`` (the optimizer's
+    ``load_state_dict`` runs after the weights are in place, so it can re-derive master weights from them), then the
+    sampler's stream position.  Returns ``state.json``."""
     with open(os.path.join(directory, "state.json")) as f:
         state = json.load(f)
+    if int(state.get("world", 1)) != int(world):
+        raise ValueError(f"checkpoint was written by {state.get('world', 1)} rank(s), resuming with {world}")
     bridge = FileBlobBridge(directory, source_worker="checkpoint")
     manifest = bridge.load_manifest(state["update_id"])
     tensors = bridge.import_update(manifest)
@@ -54,9 +87,11 @@ def load_checkpoint(directory: str, model: Any, optimizer: Any = None, *, sample
     for name, dst in targets.items():
         dst.copy_(tensors[name].to(device=dst.device, dtype=dst.dtype))
     bridge.acknowledge(manifest.update_id)
-    opt_path = os.path.join(directory, "optimizer.pt")
-    if optimizer is not None and os.path.exists(opt_path):
-        optimizer.load_state_dict(torch.load(opt_path, map_location="cpu", weights_only=False))
+    opt_path = _optimizer_file(directory, rank, world)
+    if optimizer is not None:
+        if not os.path.exists(opt_path):
+            raise FileNotFoundError(f"checkpoint has no optimizer state for rank {rank} of {world}: {opt_path}")
+        optimizer.load_state_dict(torch.load(opt_path, map_location="cpu", weights_only=True))
     if sampler is not None and state.get("sampler"):
         sampler.seed, sampler._offset = state["sampler"]["seed"], state["sampler"]["offset"]
     return state

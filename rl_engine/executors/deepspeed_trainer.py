@@ -3,26 +3,32 @@
 Parity: ``rl_engine/executors/deepspeed_trainer.py:41-693`` of the reference:
 ``DeepSpeedTrainingConfig`` (ZeRO stage, config deep-merged over defaults), ``deepspeed.initialize``
 with an AdamW optimizer, ``engine.backward`` / ``engine.step``, ZeRO-3 ``GatheredParameters`` around
-the LM head for the fused log-prob, rank-0 gathered publish, ``DeepSpeedUnavailableError`` when the
-package is missing.  The step math is inherited from ``NativeTrainingWorker``; DeepSpeed is looked up
-in ``sys.modules`` / imported lazily so tests can install a fake module.  This build's own
-data-parallel path does not need DeepSpeed (see ``rl_engine.parallel.data_parallel``).
+the LM head for the fused log-prob, ZeRO-3 publication from rank 0 through a gathered clone of the full
+state (``:204-286,644-675``), ``CUDA_HOME`` discovery for CUDA toolkits that came as Python wheels
+(``:332-391``), ``DeepSpeedUnavailableError`` when the package is missing.  The objective is the one
+function shared with ``NativeTrainingWorker`` (``clipped_ratio_objective``); DeepSpeed is looked up in
+``sys.modules`` / imported lazily so tests can install a fake module.  This build's own data-parallel
+path does not need DeepSpeed (see ``rl_engine.parallel.data_parallel``).
 """
 
 from __future__ import annotations
 
 import contextlib
 import importlib
+import os
+import sysconfig
 import time
 from dataclasses import dataclass, field
-from typing import Any, Dict, Mapping, Optional
+from pathlib import Path
+from typing import Any, Dict, List, Mapping, Optional
 
 import torch
 
 from rl_engine.executors.bridge import WeightBridgeUnavailableError
-from rl_engine.executors.trainer import NativeTrainingConfig, NativeTrainingWorker, validate_model_input_token_ids
-from rl_engine.executors.training_contract import RolloutStageResult, TrainingStageResult, objective_reference_logps
-from rl_engine.testing import compute_policy_ratio, compute_reference_kl, masked_mean
+from rl_engine.executors.trainer import (
+    NativeTrainingConfig, NativeTrainingWorker, advantage_metrics, clipped_ratio_objective, validate_model_input_token_ids,
+)
+from rl_engine.executors.training_contract import RolloutStageResult, TrainingStageResult
 
 
 class DeepSpeedUnavailableError(RuntimeError):
@@ -56,15 +62,84 @@ class DeepSpeedTrainingConfig(NativeTrainingConfig):
         return _deep_merge(defaults, self.deepspeed_config)
 
 
+def cuda_home_candidates() -> List[Path]:
+    """Places a CUDA toolkit may live when it was installed as Python wheels (``site-packages/nvidia/cu*``, newest
+    first), followed by the toolkit torch's extension builder already knows."""
+    roots = {Path(p) for key in ("purelib", "platlib") if (p := sysconfig.get_paths().get(key))}
+    found: List[Path] = []
+    for root in sorted(roots):
+        if (root / "nvidia").is_dir():
+            found += sorted((root / "nvidia").glob("cu*"), reverse=True)
+    try:
+        from torch.utils.cpp_extension import CUDA_HOME
+    except Exception:  # noqa: BLE001 - torch without the extension builder
+        CUDA_HOME = None
+    if CUDA_HOME:
+        found.append(Path(str(CUDA_HOME)))
+    return found
+
+
+def configure_cuda_home(environ: Optional[Dict[str, str]] = None) -> Optional[str]:
+    """DeepSpeed compiles its ops at import and needs ``CUDA_HOME`` to hold ``bin/nvcc`` and ``include/cuda.h``.  An
+    explicit ``CUDA_HOME`` wins (torch's extension builder is pointed at it); otherwise the first candidate that
+    looks like a toolkit is exported, with its ``bin`` on ``PATH`` and ``lib64`` / ``lib`` on ``LD_LIBRARY_PATH``.
+    Returns the toolkit root that is in effect, or ``None``."""
+    env = os.environ if environ is None else environ
+
+    def tell_torch(path: str) -> None:
+        try:
+            import torch.utils.cpp_extension as ext
+
+            ext.CUDA_HOME = path
+        except Exception:  # noqa: BLE001
+            pass
+
+    def prepend(key: str, value: str) -> None:
+        parts = [p for p in env.get(key, "").split(os.pathsep) if p]
+        if value not in parts:
+            env[key] = os.pathsep.join([value] + parts)
+
+    if env.get("CUDA_HOME"):
+        tell_torch(env["CUDA_HOME"])
+        return env["CUDA_HOME"]
+    for root in cuda_home_candidates():
+        if (root / "bin" / "nvcc").is_file() and (root / "include" / "cuda.h").is_file():
+            env["CUDA_HOME"] = str(root)
+            tell_torch(str(root))
+            prepend("PATH", str(root / "bin"))
+            for lib in ("lib64", "lib"):
+                if (root / lib).is_dir():
+                    prepend("LD_LIBRARY_PATH", str(root / lib))
+            return str(root)
+    return None
+
+
 def _load_deepspeed(module: Any = None) -> Any:
     if module is not None:
         return module
+    configure_cuda_home()
     try:
         return importlib.import_module("deepspeed")
     except ImportError as exc:
         raise DeepSpeedUnavailableError(
-            "DeepSpeed is not installed; use NativeTrainingWorker or install deepspeed."
+            "DeepSpeed is not installed; use NativeTrainingWorker / GRPOTrainingWorker or install deepspeed."
         ) from exc
+    except Exception as exc:  # noqa: BLE001 - installed, but its import-time op build failed
+        raise DeepSpeedUnavailableError(
+            "DeepSpeed is installed but failed to import here. If CUDA came as Python wheels, point CUDA_HOME at the "
+            "toolkit root that holds bin/nvcc and include/cuda.h."
+        ) from exc
+
+
+class FullStateSnapshot(torch.nn.Module):
+    """A detached full copy of a state dict, presented as a module so that a weight bridge can publish it."""
+
+    def __init__(self, state: Mapping[str, torch.Tensor]) -> None:
+        super().__init__()
+        self._state = {name: t.detach().clone() for name, t in state.items()}
+
+    def state_dict(self, *args: Any, **kwargs: Any) -> Dict[str, torch.Tensor]:  # noqa: D401 - nn.Module signature
+        return dict(self._state)
 
 
 class DeepSpeedTrainingWorker(NativeTrainingWorker):
@@ -101,17 +176,9 @@ class DeepSpeedTrainingWorker(NativeTrainingWorker):
         if callable(zero):
             zero()
         with self._gathered():
-            cur = self._current_logps(batch)
-            old = cur.detach() - cfg.old_logp_offset
-            ref = objective_reference_logps(cur, batch)
-            adv = batch.advantages.float()
-            ratio = compute_policy_ratio(cur, old, batch.completion_mask)
-            policy = -torch.minimum(ratio * adv, torch.clamp(ratio, cfg.clip_low, cfg.clip_high) * adv)
-            kl = compute_reference_kl(cur, ref, batch.completion_mask)
-            loss = masked_mean(policy + cfg.kl_beta * kl, batch.completion_mask)
+            loss = clipped_ratio_objective(self._current_logps(batch), batch, cfg)
             self.engine.backward(loss)
         self.engine.step()
-        active = adv[batch.completion_mask]
         return TrainingStageResult(
             iteration=rollout.iteration, consumed_weight_version=rollout.weight_version,
             published_weight_version=self._next_published_weight_version(rollout.weight_version),
@@ -121,22 +188,54 @@ class DeepSpeedTrainingWorker(NativeTrainingWorker):
                 "training_device": str(self.device), "deepspeed_engine": type(self.engine).__name__,
                 "deepspeed_zero_stage": self._zero_stage, "current_logp_path": "linear_logp",
                 "current_logp_backend": type(self._linear_logp).__name__,
-                "active_advantage_mean_global": float(active.mean()) if active.numel() else 0.0,
-                "active_advantage_std_global": float(active.std(unbiased=False)) if active.numel() else 0.0,
+                **advantage_metrics(batch),
                 **payload_metrics,
             },
             started_at=t0, finished_at=time.perf_counter(),
         )
 
+    def _engine_attr(self, names, default: int) -> int:
+        for name in names:
+            value = getattr(self.engine, name, None)
+            if value is not None:
+                return int(value)
+        return default
+
     def publish_weights(self, weight_version=None, metadata=None):
+        """Publishes the COMPLETE model state.  Under ZeRO-3 every rank holds a slice of each parameter, so rank 0
+        clones the full state inside DeepSpeed's gather context and publishes that clone; a runtime that cannot
+        gather fails loudly rather than publishing a shard, and so does any rank but 0."""
+        rank = self._engine_attr(("global_rank", "rank", "local_rank"), 0)
+        world = self._engine_attr(("world_size", "dp_world_size"), 1)
         meta = dict(metadata or {})
-        layout = dict(meta.get("layout", {}))
-        layout.setdefault("zero_stage", self._zero_stage)
+        layout = {"kind": "full-state", "zero_stage": self._zero_stage, "world_size": world, "rank": rank}
+        layout.update(dict(meta.get("layout", {})))
         meta["layout"] = layout
-        if self._zero_stage >= 3:
-            gather = getattr(getattr(self._deepspeed, "zero", None), "GatheredParameters", None)
-            if not callable(gather):
-                raise WeightBridgeUnavailableError("ZeRO-3 publish needs deepspeed.zero.GatheredParameters")
-            with gather(list(self.model.parameters()), modifier_rank=None):
-                return super().publish_weights(weight_version, meta)
-        return super().publish_weights(weight_version, meta)
+        if self._zero_stage < 3:
+            return super().publish_weights(weight_version, meta)
+        if rank != 0:
+            raise WeightBridgeUnavailableError("DeepSpeed ZeRO-3 full-state publish is only supported from rank 0")
+        module = getattr(self.engine, "module", None)
+        module = module if isinstance(module, torch.nn.Module) else self.model
+        gather = getattr(getattr(self._deepspeed, "zero", None), "GatheredParameters", None)
+        if callable(gather):
+            with gather(list(module.parameters()), modifier_rank=0):
+                snapshot = FullStateSnapshot(module.state_dict())
+            how = "deepspeed.zero.GatheredParameters"
+        elif world == 1:
+            snapshot = FullStateSnapshot(module.state_dict())
+            how = "single-rank-state-dict"
+        else:
+            raise WeightBridgeUnavailableError(
+                "DeepSpeed ZeRO-3 publish requires deepspeed.zero.GatheredParameters or an equivalent full-state export"
+            )
+        state = snapshot.state_dict()
+        if not state:
+            raise WeightBridgeUnavailableError("DeepSpeed ZeRO-3 full-state export produced no tensors")
+        meta["deepspeed_zero3_full_state_export"] = {"method": how, "rank": rank, "world_size": world,
+                                                     "tensor_count": len(state)}
+        live, self.model = self.model, snapshot
+        try:
+            return super().publish_weights(weight_version, meta)
+        finally:
+            self.model = live

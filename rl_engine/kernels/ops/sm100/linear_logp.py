@@ -75,14 +75,16 @@ def _workspace(device: torch.device) -> _LocalWorkspace:
     return ws
 
 
-def _forward_local(hidden2d, weight, target, bias, want_lse: bool, want_entropy: bool):
+def _forward_local(hidden2d, weight, target, bias, want_lse: bool, want_entropy: bool, check_vocab: int = 0):
+    """``check_vocab`` > 0: the kernel flags target ids outside ``[0, check_vocab)`` in the device error word."""
     ext = require_ext()
     items, n_pad, tiles_m = ext.linear_logp_workspace_shape(hidden2d.shape[0], weight.shape[0], 1)
     ws = _workspace(hidden2d.device)
     ws.ensure(items, n_pad, tiles_m)
     cur, nxt, cap = ws.next_sets()
     return ext.linear_logp_fwd(
-        hidden2d, weight, target, bias, 0, 0, 1, 0, items, [ws.partials.data_ptr()], [cur], nxt, cap, want_lse, want_entropy, 0.0
+        hidden2d, weight, target, bias, 0, 0, 1, 0, items, [ws.partials.data_ptr()], [cur], nxt, cap, want_lse, want_entropy, 0.0,
+        int(check_vocab),
     )
 
 
@@ -129,13 +131,13 @@ def linear_logp_backward_local(
 
 class _LinearLogp(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, bias, target, want_entropy, chunk_tokens):
+    def forward(ctx, hidden, weight, bias, target, want_entropy, chunk_tokens, check_vocab=0):
         h2 = hidden.reshape(-1, hidden.shape[-1])
         if h2.stride(1) != 1 or h2.stride(0) % 8 or h2.data_ptr() % 16:
             h2 = h2.contiguous()
         w = weight if (weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0) else weight.contiguous()
         t = target.reshape(-1).to(device=h2.device, dtype=torch.long).contiguous()
-        logp, lse, ent = _forward_local(h2, w, t, bias, True, bool(want_entropy))
+        logp, lse, ent = _forward_local(h2, w, t, bias, True, bool(want_entropy), check_vocab)
         ctx.save_for_backward(h2, w, t, lse, *(() if bias is None else (bias,)))
         ctx.has_bias = bias is not None
         ctx.hidden_shape = hidden.shape
@@ -158,16 +160,34 @@ class _LinearLogp(torch.autograd.Function):
             None if gh is None else gh.reshape(ctx.hidden_shape),
             None if gw is None else gw.to(w.dtype),
             None if gb is None else gb.to(bias.dtype),
-            None, None, None,
+            None, None, None, None,
         )
 
 
+def target_check_mode(check_targets=None) -> str:
+    """``"device"`` (default), ``"sync"`` or ``"off"``, from the argument or ``RL_KERNEL_CHECK_TARGETS``
+    (``1`` / ``device``, ``sync``, ``0``)."""
+    if check_targets is None:
+        check_targets = os.environ.get("RL_KERNEL_CHECK_TARGETS", "device")
+    if check_targets in (True, "1", "device", "true", "True"):
+        return "device"
+    if check_targets in (False, "0", "off", "false", "False"):
+        return "off"
+    if check_targets == "sync":
+        return "sync"
+    raise ValueError(f"check_targets must be 'device', 'sync' or 'off', got {check_targets!r}")
+
+
 class FusedLinearLogpSM100Op:
-    def __init__(self, *, check_targets: Optional[bool] = None, bwd_chunk_tokens: int = DEFAULT_BWD_CHUNK_TOKENS) -> None:
+    """``check_targets``: how unmasked target ids outside ``[0, V)`` are caught.  ``"device"`` (default): the forward
+    kernel itself tests every id, makes that row's log-prob NaN and records a bad-argument error that the next
+    ``check_device_errors()`` raises -- no host round trip per call (the reference reads ``min`` / ``max`` back on every
+    call: ``rl_engine/kernels/ops/cuda/loss/linear_logp.py:353-358``).  ``"sync"``: that host check, raising
+    ``ValueError`` at once.  ``"off"``: no check."""
+
+    def __init__(self, *, check_targets=None, bwd_chunk_tokens: int = DEFAULT_BWD_CHUNK_TOKENS) -> None:
         self._native = NativeLinearLogpOp()
-        if check_targets is None:
-            check_targets = os.environ.get("RL_KERNEL_CHECK_TARGETS", "1") != "0"
-        self.check_targets = check_targets
+        self.check_targets = target_check_mode(check_targets)
         self.bwd_chunk_tokens = bwd_chunk_tokens
 
     def __call__(self, hidden, lm_head_weight, target_ids, bias=None, **kw):
@@ -181,7 +201,7 @@ class FusedLinearLogpSM100Op:
         )
 
     def _validate_targets(self, target_ids: torch.Tensor, vocab: int) -> None:
-        if self.check_targets and target_ids.numel():
+        if self.check_targets == "sync" and target_ids.numel():
             lo, hi = torch.aminmax(target_ids)
             lo, hi = int(lo), int(hi)  # one host sync, like the reference (ops/cuda/loss/linear_logp.py:353-358)
             if lo < 0 or hi >= vocab:
@@ -213,12 +233,17 @@ class FusedLinearLogpSM100Op:
         if not self._fusable(hidden, lm_head_weight):
             return self._native.apply(hidden, lm_head_weight, target_ids, bias)
         self._validate_targets(target_ids, lm_head_weight.shape[0])
-        logp, _ = _LinearLogp.apply(hidden, lm_head_weight, bias, target_ids, False, self.bwd_chunk_tokens)
+        logp, _ = _LinearLogp.apply(hidden, lm_head_weight, bias, target_ids, False, self.bwd_chunk_tokens,
+                                    self._device_check(lm_head_weight.shape[0]))
         return logp
+
+    def _device_check(self, vocab: int) -> int:
+        return int(vocab) if self.check_targets == "device" else 0
 
     def with_entropy(self, hidden, lm_head_weight, target_ids, bias=None) -> Tuple[torch.Tensor, torch.Tensor]:
         check_linear_logp_args(hidden, lm_head_weight, target_ids, bias)
         if not self._fusable(hidden, lm_head_weight):
             return self._native.with_entropy(hidden, lm_head_weight, target_ids, bias)
         self._validate_targets(target_ids, lm_head_weight.shape[0])
-        return _LinearLogp.apply(hidden, lm_head_weight, bias, target_ids, True, self.bwd_chunk_tokens)
+        return _LinearLogp.apply(hidden, lm_head_weight, bias, target_ids, True, self.bwd_chunk_tokens,
+                                 self._device_check(lm_head_weight.shape[0]))

@@ -99,6 +99,7 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.m = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
         self.v = torch.zeros(param.numel(), dtype=torch.float32, device=param.device)
+        self.grad_scale = 1.0  # multiplies the accumulated gradient in ``step`` (1 / number of accumulated groups)
         self.master: Optional[torch.Tensor] = None     # fp32 master (CPU, or parameters that are not bf16)
         self.residual: Optional[torch.Tensor] = None   # int16 residuals of a bf16 parameter (GPU)
         if master_weights and param.dtype != torch.float32:
@@ -122,7 +123,8 @@ class FlatAdamW:
         self.grad.zero_()
 
     @torch.no_grad()
-    def step(self, grad_scale: float = 1.0) -> None:
+    def step(self, grad_scale: Optional[float] = None) -> None:
+        grad_scale = self.grad_scale if grad_scale is None else float(grad_scale)
         self.steps += 1
         p, g = self.param, self.grad
         if p.is_cuda:
@@ -306,6 +308,7 @@ class GRPOTrainer:
 
     retry_on_out_of_memory = True
     cache_prompt = True  # micro-batches attend to the prompt's cached keys / values instead of re-processing it
+    _last_group = True   # False while ``step_groups`` is accumulating a group that is not the step's last one
 
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
@@ -416,6 +419,27 @@ class GRPOTrainer:
         self.before_optimizer_step()
         self.opt.step()
         return loss
+
+    def step_groups(self, batches) -> torch.Tensor:
+        """One optimiser step on several prompt groups (a sequence of device ``GRPOBatch``): the gradient is the mean
+        over the groups of each group's token-mean loss.  Returns that mean loss.  No out-of-memory retry here."""
+        batches = list(batches)
+        if not batches:
+            raise ValueError("step_groups needs at least one prompt group")
+        self.opt.zero_grad()
+        self.opt.grad_scale = 1.0 / len(batches)
+        total = None
+        try:
+            for i, batch in enumerate(batches):
+                self._last_group = i + 1 == len(batches)
+                loss = self.forward_backward(batch)
+                total = loss if total is None else total + loss
+            self.before_optimizer_step()
+            self.opt.step()
+        finally:
+            self._last_group = True
+            self.opt.grad_scale = 1.0
+        return total / len(batches)
 
     def step(self, host_batch: GRPOBatch) -> float:
         """Public end-to-end step: host (pinned) batch in, loss value out."""

@@ -84,6 +84,7 @@ class ShardedFusedAdamW:
         self.v = torch.zeros(off, dtype=torch.float32, device=dev)
         self.master = self._gather_local(params.local).float() if master_weights else None
         self.steps = 0
+        self.grad_scale = 1.0  # extra factor on the summed gradient (1 / number of accumulated prompt groups)
         self.overlap = bool(overlap) and mem.world > 1
         self.overlap_blocks = int(overlap_blocks)
         self._side = torch.cuda.Stream(device=dev) if self.overlap else None
@@ -105,7 +106,8 @@ class ShardedFusedAdamW:
         master = None if self.master is None else self.master[off : off + n]
         require_ext().zero1_fused_step(
             self.grads.ptrs, self.params.ptrs, lo, hi, self.m[off : off + n], self.v[off : off + n], master, self.lr,
-            self.betas[0], self.betas[1], self.eps, self.weight_decay, self.steps + 1, 1.0 / self.mem.world,
+            self.betas[0], self.betas[1], self.eps, self.weight_decay, self.steps + 1,
+            float(self.grad_scale) / self.mem.world,
             self.mem.rank, self.mem.error_word, max_blocks,
         )
         self._launched[b] = True
@@ -211,6 +213,9 @@ class ShardedGRPOTrainer(GRPOTrainer):
     @contextlib.contextmanager
     def final_pass(self):
         """Wraps the forward of the pass that is back-propagated last: its layer hooks start the buckets."""
+        if not self._last_group:  # more prompt groups will add to these gradients before the optimiser step
+            yield
+            return
         self.opt.arm()
         self.model.layer_grad_hook = self.opt.on_layer_done
         try:

@@ -86,7 +86,8 @@ def _workspace(tp_group, device, records, n_pad, tiles_m, chunk, hidden_dim) -> 
 
 class _TPLinearLogp(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, bias, target, v_start, tp_group, shards, chunk_tokens, want_entropy):
+    def forward(ctx, hidden, weight, bias, target, v_start, tp_group, shards, chunk_tokens, want_entropy,
+                check_vocab=0):
         import torch.distributed as dist
 
         ext = require_ext()
@@ -109,7 +110,7 @@ class _TPLinearLogp(torch.autograd.Function):
         logp, lse, ent = ext.linear_logp_fwd(
             h2, w, t, bias, v_start, rank, world, sum(per_rank_items[:rank]), sum(per_rank_items),
             ws.partials[parity].ptrs, ws.counters[parity].ptrs, ws.counters[1 - parity].local.data_ptr(), ws.cap,
-            True, bool(want_entropy), ws.mem.wait_limit_ms,
+            True, bool(want_entropy), ws.mem.wait_limit_ms, int(check_vocab),
         )
         ctx.save_for_backward(h2, w, t, lse, *(() if bias is None else (bias,)))
         ctx.meta = (bias is not None, hidden.shape, v_start, tp_group, chunk)
@@ -151,18 +152,23 @@ class _TPLinearLogp(torch.autograd.Function):
                 grad_b += dz.float().sum(0)
         return (
             grad_h.reshape(hidden_shape), None if grad_w is None else grad_w.to(w.dtype),
-            None if grad_b is None else grad_b.to(bias.dtype), None, None, None, None, None, None,
+            None if grad_b is None else grad_b.to(bias.dtype), None, None, None, None, None, None, None,
         )
 
 
 def tensor_parallel_linear_logp_fused(
     hidden, lm_head_weight, target_ids, bias=None, *, tp_group: Any, vocab_start_index: int = 0,
-    global_vocab_size: Optional[int] = None, check_targets: bool = True, chunk_tokens: int = 4096,
+    global_vocab_size: Optional[int] = None, check_targets="device", chunk_tokens: int = 4096,
     with_entropy: bool = False,
 ):
+    """``check_targets``: ``"device"`` (the kernel flags out-of-range ids in the error word), ``"sync"`` (host check,
+    raises at once) or ``"off"``; booleans mean ``"device"`` / ``"off"``."""
+    from rl_engine.kernels.ops.sm100.linear_logp import target_check_mode
+
+    mode = target_check_mode(check_targets)
     check_linear_logp_args(hidden, lm_head_weight, target_ids, bias)
     v_global, shards = _partition(tp_group, int(vocab_start_index), lm_head_weight.shape[0], global_vocab_size)
-    if check_targets and target_ids.numel():
+    if mode == "sync" and target_ids.numel():
         lo, hi = (int(x) for x in torch.aminmax(target_ids))
         if lo < 0 or hi >= v_global:
             raise ValueError(
@@ -171,6 +177,6 @@ def tensor_parallel_linear_logp_fused(
             )
     logp, ent = _TPLinearLogp.apply(
         hidden, lm_head_weight, bias, target_ids, int(vocab_start_index), tp_group, tuple(shards), int(chunk_tokens),
-        bool(with_entropy),
+        bool(with_entropy), int(v_global) if mode == "device" else 0,
     )
     return (logp, ent) if with_entropy else logp

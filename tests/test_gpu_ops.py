@@ -115,12 +115,29 @@ def test_linear_logp_bitwise_deterministic_and_batch_invariant():
 
 
 def test_linear_logp_rejects_out_of_range_targets():
+    """``sync`` mode raises at the call; the default mode checks on the device: no host read-back per call, the bad
+    rows come back NaN and the next ``check_device_errors`` raises."""
+    from rl_engine.kernels.ops.base import check_device_errors
     from rl_engine.kernels.ops.sm100.linear_logp import FusedLinearLogpSM100Op
 
     h = torch.randn(8, 64, device=DEV).to(torch.bfloat16)
     w = torch.randn(100, 64, device=DEV).to(torch.bfloat16)
     with pytest.raises(ValueError):
-        FusedLinearLogpSM100Op()(h, w, torch.full((8,), -100, device=DEV))
+        FusedLinearLogpSM100Op(check_targets="sync")(h, w, torch.full((8,), -100, device=DEV))
+    op = FusedLinearLogpSM100Op()
+    assert op.check_targets == "device"
+    good = torch.arange(8, device=DEV)
+    clean = op(h, w, good)
+    check_device_errors(torch.cuda.current_device())  # valid ids leave the error word alone
+    bad = good.clone()
+    bad[3], bad[5] = 100, -1
+    out = op(h, w, bad)
+    with pytest.raises(RuntimeError, match="bad argument"):
+        check_device_errors(torch.cuda.current_device())
+    assert torch.isnan(out[[3, 5]]).all() and torch.equal(out[[0, 1, 2, 4, 6, 7]], clean[[0, 1, 2, 4, 6, 7]])
+    check_device_errors(torch.cuda.current_device())  # the word was reset by the raise
+    assert torch.isfinite(FusedLinearLogpSM100Op(check_targets="off")(h, w, bad)[[0, 1]]).all()
+    check_device_errors(torch.cuda.current_device())
 
 
 # ------------------------------------------------------------------------ ratio_kl / grpo
