@@ -247,11 +247,69 @@ def measure_sampler(device, iters: int = 30):
             "l2": "two 155 MB logit buffers alternate (each larger than L2)"}
 
 
-def measure_ops(device, rank: int, world: int):
-    """The per-operator part of the headline metric; a failure is reported in place of the numbers."""
-    out = {}
-    for name, fn in (("fused_logp", lambda: measure_fused_logp(device, rank, world)),
-                     ("sampler", lambda: measure_sampler(device))):
+def measure_tp_step(device, rank: int, world: int, warmup: int = 1, steps: int = 2):
+    """The same GRPO step with the model tensor + sequence parallel over all ``world`` ranks (every rank sees the whole
+    group of 256 completions; layers on the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels, vocabulary-parallel
+    LM head): the configuration the benchmark's config names as TP=N.  Data parallel stays the headline because it is
+    faster for an 8 B model on 180 GB GPUs; this entry puts the TP number beside it."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    from rl_engine.models.config import llama3_8b
+    from rl_engine.models.grpo import synthetic_batch
+    from rl_engine.models.llama import LlamaModel
+    from rl_engine.parallel.tp_linear import TensorParallelLinears
+    from rl_engine.parallel.tp_model import TensorParallelGRPOTrainer, TensorParallelLlama
+
+    cfg = llama3_8b()
+    model = LlamaModel(cfg, dtype=torch.bfloat16, device=device, seed=0, max_positions=PROMPT_LEN + COMPLETION_LEN)
+    tp_model = TensorParallelLlama(model, TensorParallelLinears(group=dist.group.WORLD, device=device))
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    trainer = TensorParallelGRPOTrainer(tp_model, lr=1e-6, clip_eps=0.2, beta=0.04)
+    host = synthetic_batch(cfg.vocab_size, PROMPT_LEN, GROUP, COMPLETION_LEN, seed=1234)
+    batch = host.to(device)
+    with torch.no_grad():
+        cur = trainer.policy_logps(batch).float()
+    gen = torch.Generator(device=device).manual_seed(99)
+    batch.old_logps = cur + 0.01 * torch.randn(cur.shape, device=device, generator=gen)
+    batch.ref_logps = cur + 0.01 * torch.randn(cur.shape, device=device, generator=gen)
+    for _ in range(warmup):
+        trainer.step_device(batch)
+    torch.cuda.synchronize()
+    dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        loss = trainer.step_device(batch)
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0]) / steps
+    from rl_engine.kernels.ops.base import check_device_errors
+
+    check_device_errors(device.index or 0)
+    out = {"parallelism": f"tp{world}-sequence-parallel-fused", "ms_per_step": round(ms, 3),
+           "value": round(GROUP * COMPLETION_LEN / (ms * 1e-3), 1), "unit": "tokens/s", "steps": steps, "warmup": warmup,
+           "global_batch": GROUP, "kept_layers": tp_model.kept_layers(), "last_loss": float(loss)}
+    del trainer, tp_model, batch
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def measure_ops(device, rank: int, world: int, out=None):
+    """The per-operator part of the headline metric (and, on more than one GPU, the tensor-parallel form of the step);
+    a failure is reported in place of the numbers.  Results are added to ``out`` as they complete."""
+    out = {} if out is None else out
+    parts = [("fused_logp", lambda: measure_fused_logp(device, rank, world)), ("sampler", lambda: measure_sampler(device))]
+    if world > 1 and os.environ.get("RLK_BENCH_TP", "1") != "0":
+        parts.append(("tp_step", lambda: measure_tp_step(device, rank, world)))
+    for name, fn in parts:
         try:
             out[name] = fn()
         except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
@@ -389,6 +447,10 @@ def main() -> None:
         t = torch.tensor([ms, e2e_s], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0]), float(t[1])
+        if not tensor_parallel:  # every rank's loss is the mean over its own completions: report the group's mean
+            mean_loss = torch.tensor([loss_value], device=device, dtype=torch.float64)
+            dist.all_reduce(mean_loss, op=dist.ReduceOp.AVG)
+            loss_value = float(mean_loss[0])
     tokens = group * COMPLETION_LEN
     value = tokens * args.steps / (ms / 1e3)
     mem_free, mem_total = torch.cuda.mem_get_info(device)
@@ -434,15 +496,18 @@ def main() -> None:
 
     # The per-operator numbers need a few GB: release the trainer first.  If that part does not finish in time the
     # line is printed without it, so the step result is never lost.
+    ops = {}
+
     def watchdog():
-        emit({"error": f"operator measurements did not finish within {OPS_DEADLINE_S} s"})
+        emit({**ops, "error": f"operator measurements did not finish within {OPS_DEADLINE_S} s"})
         os._exit(0)
 
     timer = threading.Timer(OPS_DEADLINE_S, watchdog)
     timer.daemon = True
     timer.start()
-    ops = {"skipped": "development overrides in use"}
-    if not (args.dev_layers or args.dev_group) or os.environ.get("RLK_BENCH_OPS") == "1":
+    if (args.dev_layers or args.dev_group) and os.environ.get("RLK_BENCH_OPS") != "1":
+        ops["skipped"] = "development overrides in use"
+    else:
         if hasattr(trainer, "mem"):
             torch.cuda.synchronize()
             trainer.mem.close()
@@ -452,7 +517,9 @@ def main() -> None:
 
         gc.collect()
         torch.cuda.empty_cache()
-        ops = measure_ops(device, rank, world)
+        if tensor_parallel:
+            os.environ["RLK_BENCH_TP"] = "0"  # the step above already was the tensor-parallel one
+        measure_ops(device, rank, world, ops)
     timer.cancel()
     emit(ops)
     if world > 1:

@@ -230,6 +230,14 @@ def _logp_flops(batch, seq, vocab):
     return 5.0 * batch * seq * vocab  # max, subtract, exp, sum, gather-subtract per element (rough)
 
 
+def _fused(op):
+    """A ``*_fused`` workload measures the sm_100a kernels.  If the registry handed out a PyTorch fallback (no GPU, no
+    extension) the workload is reported as ``blocked`` instead of timing the wrong thing under the fused name."""
+    if type(op).__name__.startswith("Native"):
+        raise RuntimeError(f"fused backend unavailable: the registry dispatched {type(op).__name__}")
+    return op
+
+
 def _guard(name):
     def deco(fn):
         def run(profiler, args, device, dtype, batch, seq, vocab):
@@ -259,7 +267,7 @@ def _run_logp_fused(profiler, args, device, dtype, batch, seq, vocab):
     from rl_engine.kernels.registry import kernel_registry
     from rl_engine.testing import selected_logprobs_reference
 
-    op = kernel_registry.get_op("logp")
+    op = _fused(kernel_registry.get_op("logp"))
     logits, ids = _rand_logits(device, dtype, batch, seq, vocab, args.seed), _ids(device, batch, seq, vocab, args.seed + 1)
     fn = lambda: op.apply_fp32(logits, ids)
     out, ms, std = profiler.time_fn(fn)
@@ -275,7 +283,7 @@ def _run_logp_fused(profiler, args, device, dtype, batch, seq, vocab):
 def _run_linear_logp_fused(profiler, args, device, dtype, batch, seq, vocab):
     from rl_engine.kernels.registry import kernel_registry
 
-    op = kernel_registry.get_op("linear_logp")
+    op = _fused(kernel_registry.get_op("linear_logp"))
     hidden = args.hidden
     g = torch.Generator(device=device).manual_seed(args.seed)
     h = torch.randn(batch * seq, hidden, device=device, generator=g).to(dtype)
@@ -309,6 +317,8 @@ def _sampling(profiler, args, device, dtype, batch, seq, vocab, name, fused):
     from rl_engine.kernels.sampling import SamplerBackend
 
     sampler = SamplerBackend(seed=args.seed)
+    if fused and sampler.backend != "sm100":
+        raise RuntimeError(f"fused sampler unavailable: backend is {sampler.backend}")
     if not fused:
         sampler.backend = "torch"
     rows = batch * seq
@@ -334,7 +344,7 @@ def _run_sampling_fused(profiler, args, device, dtype, batch, seq, vocab):
 def _run_ratio_kl(profiler, args, device, dtype, batch, seq, vocab):
     from rl_engine.kernels.registry import kernel_registry
 
-    op = kernel_registry.get_op("ratio_kl")
+    op = _fused(kernel_registry.get_op("ratio_kl"))
     pol, ref = _rand_logits(device, dtype, batch, seq, vocab, args.seed), _rand_logits(device, dtype, batch, seq, vocab, args.seed + 2)
     ids = _ids(device, batch, seq, vocab, args.seed + 1)
     mask = torch.ones(batch, seq, device=device, dtype=torch.bool)
@@ -349,7 +359,7 @@ def _run_ratio_kl(profiler, args, device, dtype, batch, seq, vocab):
 def _run_grpo_loss(profiler, args, device, dtype, batch, seq, vocab):
     from rl_engine.kernels.registry import kernel_registry
 
-    op = kernel_registry.get_op("grpo_loss")
+    op = _fused(kernel_registry.get_op("grpo_loss"))
     pol = _rand_logits(device, dtype, batch, seq, vocab, args.seed).requires_grad_(True)
     ref = _rand_logits(device, dtype, batch, seq, vocab, args.seed + 2)
     ids = _ids(device, batch, seq, vocab, args.seed + 1)
@@ -372,7 +382,7 @@ def _run_grpo_loss(profiler, args, device, dtype, batch, seq, vocab):
 def _run_attention(profiler, args, device, dtype, batch, seq, vocab):
     from rl_engine.kernels.registry import kernel_registry
 
-    op = kernel_registry.get_op("attn")
+    op = _fused(kernel_registry.get_op("attn"))
     g = torch.Generator(device=device).manual_seed(args.seed)
     q = torch.randn(batch, seq, 32, 128, device=device, generator=g).to(dtype)
     k = torch.randn(batch, seq, 8, 128, device=device, generator=g).to(dtype)
@@ -413,11 +423,12 @@ def _parse_dtype(value: str) -> torch.dtype:
 
 
 def _parse_workloads(value: str) -> List[str]:
-    names = [x.strip() for x in value.split(",") if x.strip()]
-    unknown = sorted(set(names) - set(WORKLOAD_REGISTRY))
+    raw = [x.strip() for x in value.split(",") if x.strip()]
+    # the reference's CLI spells workloads with hyphens (``logp-native``); both spellings name the same workload
+    unknown = sorted(x for x in set(raw) if x.replace("-", "_") not in WORKLOAD_REGISTRY)
     if unknown:
         raise ValueError(f"unsupported workloads: {', '.join(unknown)}; supported: {', '.join(available_workloads())}")
-    return names
+    return [x.replace("-", "_") for x in raw]
 
 
 def run_automated_suite(args: argparse.Namespace) -> PerformanceProfiler:

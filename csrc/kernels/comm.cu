@@ -75,12 +75,18 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // [lo, hi) are element indices, multiples of 8.  m / v / master are indexed from 0 at element lo.
 // ``skip_if_set``: the error word of the device barrier that precedes this kernel (or nullptr).  If that barrier
 // gave up waiting for a peer, some gradients are not final, so the kernel applies nothing and returns.
+// kWorld > 0 fixes the number of ranks at compile time: the loads from all peers are then issued back to back, before
+// the first use, so a thread has kWorld remote loads in flight instead of one (a remote load takes microseconds; with
+// one in flight per thread the kernel ran at 0.42 of the link bandwidth per direction).  kWorld == 0 is the generic
+// form for other rank counts.
+template <int kWorld>
 __global__ void __launch_bounds__(256)
-zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world, long long lo, long long hi,
+zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world_rt, long long lo, long long hi,
                         float* __restrict__ m, float* __restrict__ v, float* __restrict__ master, float lr, float b1,
                         float b2, float eps, float wd, float bc1, float bc2, float grad_scale,
                         const uint32_t* __restrict__ skip_if_set) {
   if (skip_if_set != nullptr && *skip_if_set != 0u) return;
+  const int world = kWorld > 0 ? kWorld : world_rt;
   const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
   const long long n8 = (hi - lo) / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
@@ -89,12 +95,26 @@ zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world, lo
     float g[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) g[j] = 0.f;
-    for (int r = 0; r < world; ++r) {  // fixed rank order: bitwise identical on every run
-      const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[r]) + e);
-      float f[8];
-      unpack8(q, f);
+    if constexpr (kWorld > 0) {
+      uint4 q[kWorld];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] += f[j];
+      for (int r = 0; r < kWorld; ++r)
+        q[r] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[r]) + e);
+#pragma unroll
+      for (int r = 0; r < kWorld; ++r) {  // fixed rank order: bitwise identical on every run and every rank
+        float f[8];
+        unpack8(q[r], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += f[j];
+      }
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grads.p[r]) + e);
+        float f[8];
+        unpack8(q, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += f[j];
+      }
     }
     float w[8];
     if (master != nullptr) {
@@ -129,7 +149,12 @@ zero1_fused_step_kernel(PeerPtrs grads, PeerPtrs params, int rank, int world, lo
       reinterpret_cast<float4*>(master + i * 8)[1] = make_float4(w[4], w[5], w[6], w[7]);
     }
     const uint4 packed = pack8(w);
-    for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = packed;
+    if constexpr (kWorld > 0) {
+#pragma unroll
+      for (int r = 0; r < kWorld; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = packed;
+    } else {
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + e) = packed;
+    }
   }
 }
 
@@ -274,9 +299,18 @@ void zero1_fused_step(void* const* grads, void* const* params, int rank, int wor
   if (hi <= lo) return;
   int grid = capped_grid((hi - lo) / 8, 256);
   if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;
-  zero1_fused_step_kernel<<<grid, 256, 0, stream>>>(make_ptrs(grads, world), make_ptrs(params, world), rank, world, lo,
-                                                    hi, m, v, master, lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
-                                                    skip_if_set);
+#define RLK_ZERO1(W)                                                                                              \
+  zero1_fused_step_kernel<W><<<grid, 256, 0, stream>>>(make_ptrs(grads, world), make_ptrs(params, world), rank, world, \
+                                                       lo, hi, m, v, master, lr, b1, b2, eps, wd, bc1, bc2,          \
+                                                       grad_scale, skip_if_set)
+  switch (world) {
+    case 1: RLK_ZERO1(1); break;
+    case 2: RLK_ZERO1(2); break;
+    case 4: RLK_ZERO1(4); break;
+    case 8: RLK_ZERO1(8); break;
+    default: RLK_ZERO1(0); break;
+  }
+#undef RLK_ZERO1
 }
 
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream) {

@@ -192,13 +192,32 @@ def configure_stateless_model(model: torch.nn.Module, config: Optional[Stateless
     return policy
 
 
+def _raised_inside_flash_attention(exc: BaseException) -> bool:
+    """True if any frame of the exception's traceback belongs to a flash-attention code path (the ``flash_attn``
+    package or a library's ``flash_attention`` integration module)."""
+    tb = exc.__traceback__
+    while tb is not None:
+        name = tb.tb_frame.f_code.co_filename.replace("\\", "/").lower()
+        if "flash_att" in name or "flash-att" in name:
+            return True
+        tb = tb.tb_next
+    return False
+
+
 def _attention_import_like(exc: Exception, config: StatelessForwardConfig) -> bool:
+    """Should a failed forward be retried with eager attention?  Only when flash attention was requested, and the
+    failure says so: a missing / unusable kernel package (ImportError, NotImplementedError), an error message that
+    names flash attention or ``attn_implementation``, or ANY error raised from inside a flash-attention code path --
+    libraries fail there in untyped ways, e.g. a bare ``StopIteration`` while probing an fp32 model's dtype (the
+    reference special-cases that type: ``rl_engine/executors/stateless_executor.py:496-513``)."""
     if config.attention_backend != "flash_attention_2":
         return False
+    if isinstance(exc, (ImportError, NotImplementedError, StopIteration)):
+        return True
     text = f"{type(exc).__name__}: {exc}".lower()
-    return isinstance(exc, (ImportError, NotImplementedError)) or any(
-        key in text for key in ("flash_attn", "flash attention", "flashattention", "attn_implementation")
-    )
+    if any(key in text for key in ("flash_attn", "flash attention", "flashattention", "flash-attn", "attn_implementation")):
+        return True
+    return _raised_inside_flash_attention(exc)
 
 
 def _forward_no_cache(model: torch.nn.Module, inputs: StatelessForwardInputs):

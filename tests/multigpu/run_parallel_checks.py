@@ -2,7 +2,8 @@
 
 Covers: symmetric heap mapping + device barrier, vocab-parallel fused linear_logp (forward bitwise
 equal on all ranks and close to the single-GPU op, backward vs autograd), the fused
-reduce-scatter + AdamW + all-gather step vs a single-process AdamW, the weight broadcast+cast, the
+reduce-scatter + AdamW + all-gather step vs a single-process AdamW, one data-parallel GRPO step (bucketed and
+overlapped with backward) vs the single-GPU trainer on the same batch, the weight broadcast+cast, the
 tensor-parallel linears fused with their all-gather / reduce-scatter, the context-parallel causal attention (zig-zag shards) against full-sequence attention, and the
 expert-parallel MoE (peer-store dispatch / peer-load combine) against the single-GPU fused MoE.
 Every rank prints ``OK <name>`` lines; rank 0 prints ``ALL OK`` at the end.
@@ -231,6 +232,62 @@ def main() -> None:
     close(tp_model.params["l1.wo"], ref_model.view("l1.wo")[:, rank * hq_m:(rank + 1) * hq_m], 5e-2, "tp model wo shard after 3 steps")
     check_device_errors(local)
     print(f"[{rank}] OK tensor-parallel GRPO step (loss {loss_tp[0]:.4f} -> {loss_tp[-1]:.4f}, single GPU {loss_ref[0]:.4f} -> {loss_ref[-1]:.4f})", flush=True)
+
+    # ---- data-parallel GRPO step (bucketed fused reduce-scatter + AdamW + all-gather, overlapped with the last
+    # ---- backward pass) vs the single-GPU trainer on the same batch ------------------------------------------
+    from rl_engine.models.grpo import GRPOBatch
+    from rl_engine.parallel.data_parallel import ShardedGRPOTrainer
+
+    dcfg = ModelConfig("dp-check", 2048, 512, 3, 8, 4, 128, 1024)
+    per_rank = 2
+    G_dp = per_rank * world
+    hb_dp = synthetic_batch(dcfg.vocab_size, prompt_len=256, group=G_dp, completion_len=192, seed=5)
+    single = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=33, activation_checkpointing=False)
+    start = single.flat.clone()
+    single_tr = GRPOTrainer(single, lr=1e-3, micro_group=None)
+    with torch.no_grad():
+        cur = single_tr.policy_logps(hb_dp.to(dev)).float()
+    gn = torch.Generator(device=dev).manual_seed(71)  # the same noise on every rank
+    hb_dp.old_logps = (cur + 0.01 * torch.randn(cur.shape, device=dev, generator=gn)).cpu()
+    hb_dp.ref_logps = (cur + 0.01 * torch.randn(cur.shape, device=dev, generator=gn)).cpu()
+    full_dev = hb_dp.to(dev)
+    loss_single = [float(single_tr.step_device(full_dev)) for _ in range(2)]
+    sl = slice(rank * per_rank, (rank + 1) * per_rank)
+    local_dev = GRPOBatch(full_dev.prompt_ids, full_dev.completion_ids[sl].contiguous(), full_dev.rewards,
+                          full_dev.old_logps[sl].contiguous(), full_dev.ref_logps[sl].contiguous(),
+                          full_dev.completion_mask[sl].contiguous())
+    results = {}
+    for name, kw in (("one pass, overlapped", dict(micro_group=None, overlap=True)),
+                     ("one pass, not overlapped", dict(micro_group=None, overlap=False)),
+                     ("prompt pass + micro-batches, overlapped", dict(micro_group=1, overlap=True))):
+        model_dp = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=33, activation_checkpointing=False)
+        assert torch.equal(model_dp.flat, start)
+        dp_tr = ShardedGRPOTrainer(model_dp, lr=1e-3, layers_per_bucket=1, **kw)
+        dp_tr.set_group_slice(sl)
+        losses = []
+        for _ in range(2):
+            l_ = dp_tr.step_device(local_dev).float().reshape(1)
+            dist.all_reduce(l_, op=dist.ReduceOp.AVG)
+            losses.append(float(l_))
+        dp_tr.check()
+        check_device_errors(local)
+        every = [torch.empty_like(model_dp.flat) for _ in range(world)]
+        dist.all_gather(every, model_dp.flat.contiguous())
+        assert all(torch.equal(every[0], e_) for e_ in every), f"data parallel ({name}): parameters differ between ranks"
+        assert abs(losses[0] - loss_single[0]) < 2e-2 * max(1.0, abs(loss_single[0])), (name, losses, loss_single)
+        d_dp = model_dp.flat.float() - start.float()
+        d_one = single.flat.float() - start.float()
+        moved = d_one.abs() > 0
+        assert moved.float().mean() > 0.5, "the single-GPU reference step did not move the parameters"
+        # AdamW's first steps are close to lr * sign(gradient): compare the updates, not just the parameters
+        rel = ((d_dp - d_one).abs().mean() / d_one.abs().mean()).item()
+        agree = (torch.sign(d_dp[moved]) == torch.sign(d_one[moved])).float().mean().item()
+        assert rel < 0.25 and agree > 0.9, f"data parallel ({name}): update differs from the single-GPU step: {rel:.3f}, {agree:.3f}"
+        results[name] = model_dp.flat.clone()
+        dp_tr.mem.close()
+    assert torch.equal(results["one pass, overlapped"], results["one pass, not overlapped"]), \
+        "overlapping the gradient exchange with backward changed the result"
+    print(f"[{rank}] OK data-parallel GRPO step == single-GPU step (loss {losses[0]:.4f} vs {loss_single[0]:.4f})", flush=True)
 
     # ---- context-parallel causal attention (zig-zag shards, peer-store K/V gather, peer_sum dK/dV) ----
     from rl_engine.kernels.ops.sm100.attention import FlashAttentionSM100Op
