@@ -11,7 +11,8 @@ bandwidth per direction), and ``frac_of_roofline = roofline_ms / ms``.
 Paths: ``tp_ag_gemm`` (all-gather -> QKV/up GEMM), ``tp_gemm_rs`` (down/out GEMM -> reduce-scatter), ``linear_logp_tp``
 (vocabulary-parallel LM head with the in-kernel merge, forward and backward), ``cp_attention`` (context-parallel causal
 attention forward+backward), ``ep_moe`` (expert-parallel MoE layer forward+backward), ``zero1`` (fused reduce-scatter +
-AdamW + all-gather), ``weight_broadcast`` (trainer -> all ranks with fp32 -> bf16 cast).
+AdamW + all-gather), ``weight_broadcast`` (trainer -> all ranks with fp32 -> bf16 cast), ``weight_sync`` (the whole weight
+update protocol over ``NVLinkBroadcastBridge``, relay and direct).
 """
 
 from __future__ import annotations
@@ -241,8 +242,67 @@ def bench_broadcast(args, rank, world):
     mem.check()
 
 
+def bench_weight_sync(args, rank, world):
+    """The whole trainer -> rollout weight update through ``NVLinkBroadcastBridge.sync`` at the size of a model state
+    (``--sync-gb`` of bf16 in ``--sync-tensors`` tensors): cast + stores, relay hop, manifest shipped with
+    ``broadcast_object_list``, import, digest validation and acknowledge on every rank.  Times are host wall clock around
+    the collective call with a device synchronise on both sides, max over ranks (the call contains host work)."""
+    import time
+
+    from rl_engine.executors.bridge import NVLinkBroadcastBridge
+    from rl_engine.parallel.symmetric import SymmetricMemory
+
+    total = int(args.sync_gb * (1 << 30))
+    count = args.sync_tensors
+    per = total // count // 512 * 256  # bf16 elements per tensor
+    nbytes = per * 2 * count + 256 * count
+    mem = SymmetricMemory((2 if world > 2 else 1) * (nbytes + 4096) + (1 << 20))  # one window per measured mode
+    results = {}
+    for relay in ((True, False) if world > 2 else (False,)):
+        bridge = NVLinkBroadcastBridge(mem, nbytes, relay=relay)
+        state = None
+        if rank == 0:
+            flat = torch.empty(per * count, dtype=torch.bfloat16, device="cuda").normal_()
+            state = {f"t{i}": flat[i * per:(i + 1) * per] for i in range(count)}
+        samples = []
+        for it in range(args.warmup + args.repeat):
+            torch.cuda.synchronize()
+            dist.barrier()
+            t0 = time.perf_counter()
+            manifest, tensors = bridge.sync(state, weight_version=it + 1)
+            torch.cuda.synchronize()
+            t = torch.tensor([time.perf_counter() - t0], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if it >= args.warmup:
+                samples.append(float(t) * 1e3)
+            if it + 1 < args.warmup + args.repeat:
+                bridge.release(manifest.update_id)
+        ok = torch.tensor([1], device="cuda")
+        if rank == 0:
+            ok[0] = int(torch.equal(tensors["t0"], state["t0"]) and torch.equal(tensors[f"t{count - 1}"], state[f"t{count - 1}"]))
+        check = tensors[f"t{count // 2}"].float().sum().reshape(1).double()
+        lo, hi = check.clone(), check.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        results[relay] = (statistics.median(samples), bool(ok.item()) and float(lo) == float(hi))
+        mem.check()
+        del bridge, state
+        torch.cuda.empty_cache()
+    if rank == 0:
+        size = per * 2 * count
+        for relay, (ms, ok) in results.items():
+            # unique bytes must leave the source once (relay) or once per peer (direct); every peer must receive all
+            roof = (size if relay else size * (world - 1)) / (NVLINK_GBS * 1e6) if world > 1 else size * 2 / (peaks()["hbm_gbs"] * 1e6)
+            print(json.dumps({"path": "weight_sync_bridge", "mode": "relay" if relay else "direct", "world": world,
+                              "ms": round(ms, 3), "gbytes": round(size / 2**30, 2), "tensors": count,
+                              "delivered_gbs_per_rank": round(size / ms / 1e6, 1), "roofline_ms": round(roof, 3),
+                              "frac_of_roofline": round(roof / ms, 3), "verified_identical_on_all_ranks": ok,
+                              "note": "publish + manifest broadcast + import + device digest check + acknowledge"}), flush=True)
+    mem.close()
+
+
 PATHS = {"tp": bench_tp, "linear_logp": bench_linear_logp, "cp": bench_cp, "ep": bench_ep, "zero1": bench_zero1,
-         "broadcast": bench_broadcast}
+         "broadcast": bench_broadcast, "weight_sync": bench_weight_sync}
 
 
 def main() -> None:
@@ -254,6 +314,8 @@ def main() -> None:
     ap.add_argument("--moe-tokens", type=int, default=8192, help="tokens per rank for the MoE layer")
     ap.add_argument("--zero1-params", type=int, default=1 << 29)
     ap.add_argument("--broadcast-params", type=int, default=1 << 29)
+    ap.add_argument("--sync-gb", type=float, default=1.0, help="bytes of bf16 state for the weight_sync path (16 = Llama-3-8B)")
+    ap.add_argument("--sync-tensors", type=int, default=291, help="number of tensors the state is split into")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--repeat", type=int, default=5)
     args = ap.parse_args()

@@ -33,7 +33,7 @@ def main() -> None:
     ext = require_ext()
 
     # ---- symmetric heap + barrier -------------------------------------------------------------
-    mem = SymmetricMemory(1 << 22, device=dev)
+    mem = SymmetricMemory(1 << 23, device=dev)
     buf = mem.alloc((1024,), torch.float32)
     buf.local.fill_(float(rank + 1))
     mem.barrier()
@@ -52,6 +52,24 @@ def main() -> None:
     assert torch.equal(dst.local.float(), src.to(torch.bfloat16).float())
     mem.check()
     print(f"[{rank}] OK cast_broadcast", flush=True)
+
+    # ---- the weight-update protocol over symmetric memory, relay and direct -----------------------------
+    from rl_engine.executors.bridge import NVLinkBroadcastBridge
+
+    for relay in (True, False):
+        bridge = NVLinkBroadcastBridge(mem, 1 << 20, target_dtype=torch.bfloat16, relay=relay)
+        state = None
+        if rank == 0:
+            gs = torch.Generator(device=dev).manual_seed(8)
+            state = {"a.weight": torch.randn(300, 257, device=dev, generator=gs), "b.bias": torch.randn(19, device=dev, generator=gs),
+                     "steps": torch.tensor([3, 4, 5], device=dev)}
+        manifest, views = bridge.sync(state, weight_version=1)
+        want = torch.randn(300, 257, device=dev, generator=torch.Generator(device=dev).manual_seed(8)).to(torch.bfloat16)
+        assert torch.equal(views["a.weight"], want), f"weight sync (relay={relay}): wrong bytes on rank {rank}"
+        assert views["steps"].tolist() == [3, 4, 5] and bridge.active_weight_version == 1
+        assert manifest.metadata["weight_bridge"]["relay"] == (relay and world > 1)
+    mem.check()
+    print(f"[{rank}] OK weight sync bridge (relay + direct)", flush=True)
 
     # ---- vocab-parallel fused linear_logp -------------------------------------------------------
     g = torch.Generator(device=dev).manual_seed(5)  # same data on all ranks

@@ -47,6 +47,45 @@ def test_symmetric_memory_single_rank_and_timeout_error():
     mem.close()
 
 
+def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge():
+    """The weight-sync transport over symmetric memory on one rank: fp32 trainer weights land in the window as bf16
+    through the cast+broadcast kernel, the manifest validates, tampering is caught, a too-small window is refused."""
+    from rl_engine.executors.bridge import (
+        NVLinkBroadcastBridge, WeightBridgeUnavailableError, WeightManifestValidationError, make_weight_bridge,
+    )
+    from rl_engine.parallel.symmetric import SymmetricMemory
+
+    mem = SymmetricMemory(8 << 20)
+    bridge = make_weight_bridge("nvlink-broadcast", memory=mem, capacity_bytes=4 << 20, target_dtype=torch.bfloat16)
+    assert isinstance(bridge, NVLinkBroadcastBridge)
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(torch.nn.Linear(300, 257), torch.nn.Linear(257, 19, bias=False)).cuda()
+    model.register_buffer("step", torch.tensor([5], dtype=torch.int64, device="cuda"))
+    manifest, tensors = bridge.sync(model, weight_version=3)
+    mem.check()
+    assert manifest.transport == "nvlink-broadcast" and manifest.weight_version == 3
+    assert bridge.active_weight_version == 3 and bridge.update_status(manifest.update_id) == "acknowledged"
+    for name, want in model.state_dict().items():
+        got = tensors[name]
+        if want.is_floating_point():
+            assert got.dtype == torch.bfloat16 and torch.equal(got, want.to(torch.bfloat16)), name
+        else:
+            assert torch.equal(got, want), name
+        lo, hi = bridge.window.local.data_ptr(), bridge.window.local.data_ptr() + bridge.window.local.numel()
+        assert lo <= got.data_ptr() < hi and got.data_ptr() % 256 == 0       # a view of the window, 256-byte aligned
+    second = bridge.publish(model, weight_version=4)
+    view = bridge.import_update(second)
+    view["0.weight"].view(-1)[:8].add_(1.0)
+    with pytest.raises(WeightManifestValidationError, match="checksum"):
+        bridge.acknowledge(second.update_id)
+    assert bridge.active_weight_version == 3                                  # the previous version stays active
+    tiny = NVLinkBroadcastBridge(mem, 1024)
+    with pytest.raises(WeightBridgeUnavailableError):
+        tiny.publish(model, weight_version=1)
+    mem.check()
+    mem.close()
+
+
 @pytest.mark.parametrize("n,offset", [(8 * 4096, 0), (8 * 4096 + 5, 0), (3, 0), (8 * 1000 + 3, 1), (8 * 5000, 8)])
 def test_cast_broadcast_and_peer_sum_vector_and_scalar_paths(n, offset):
     """Sizes that are not multiples of 8 take a scalar tail; an element offset that leaves the pointer off a 16-byte boundary takes the
