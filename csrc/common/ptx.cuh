@@ -37,6 +37,11 @@ __device__ __forceinline__ void report_error(uint32_t* err, uint32_t code, uint3
   }
 }
 
+// Host side of the debug-bounds build: the error word of the current device, registered by the bindings
+// (defined in runtime/runtime.cpp; returns nullptr until a word was registered).
+uint32_t* debug_error_word();
+void bind_debug_error_word(int device, uint32_t* word);
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -46,11 +51,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Checked indexing for debug builds (-DRLK_DEBUG_BOUNDS=1, see setup.py): an index outside [0, limit)
 // records (kErrBadIndex, kernel id, block, site) in the error word and the macro evaluates to false so the
 // caller can skip the access.  Release builds compile the test away.
+// Kernels that do not otherwise take the error word get it as one extra trailing parameter in debug builds only:
+//   __global__ void k(..., int n RLK_DBG_PARAM) { ... RLK_INDEX_OK(i, n, RLK_DBG_ERR, id, site) ... }
+//   k<<<grid, block, 0, stream>>>(..., n RLK_DBG_ARG);
+// RLK_DBG_ARG reads the word that the bindings registered for the current device (debug_error_word()).
 #if defined(RLK_DEBUG_BOUNDS)
 #define RLK_INDEX_OK(idx, limit, err, kernel_id, site) \
   (((idx) >= 0 && (idx) < (limit)) ? true : (::rlk::report_error((err), ::rlk::kErrBadIndex, (kernel_id), (site)), false))
+#define RLK_DBG_PARAM , uint32_t* rlk_dbg_err
+#define RLK_DBG_ARG , ::rlk::debug_error_word()
+#define RLK_DBG_ERR rlk_dbg_err
 #else
 #define RLK_INDEX_OK(idx, limit, err, kernel_id, site) (true)
+#define RLK_DBG_PARAM
+#define RLK_DBG_ARG
+#define RLK_DBG_ERR (static_cast<uint32_t*>(nullptr))
 #endif
 
 constexpr uint64_t kWaitLimitNs = 4ull * 1000ull * 1000ull * 1000ull;  // 4 s

@@ -267,6 +267,41 @@ __global__ void cast_broadcast_kernel(const TS* __restrict__ src, PeerPtrs dsts,
   }
 }
 
+// Integrity digest of a byte range: sum over its 64-bit little-endian words w_i (the tail zero-padded) of
+// (w_i ^ (w_i >> 29)) * ((i + 1) * kDigestMul), all modulo 2^64, with an arithmetic shift.  Wrap-around integer
+// addition is associative and commutative, so any partition of the range over threads gives the same 64 bits.
+// One pass, 16-byte loads; the result is ADDED into *out (the caller zeroes it).
+constexpr unsigned long long kDigestMul = 0x9E3779B97F4A7C15ull;  // == -7046029254386353131 as a signed 64-bit value
+
+__device__ __forceinline__ unsigned long long digest_term(long long w, unsigned long long index) {
+  return static_cast<unsigned long long>(w ^ (w >> 29)) * ((index + 1ull) * kDigestMul);
+}
+
+__global__ void __launch_bounds__(256)
+digest64_kernel(const long long* __restrict__ words, long long n_words, const unsigned char* __restrict__ tail,
+                int tail_bytes, unsigned long long* __restrict__ out) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  unsigned long long acc = 0ull;
+  const long long pairs = n_words / 2;
+  for (long long i = tid; i < pairs; i += stride) {
+    const longlong2 w = reinterpret_cast<const longlong2*>(words)[i];
+    acc += digest_term(w.x, static_cast<unsigned long long>(2 * i));
+    acc += digest_term(w.y, static_cast<unsigned long long>(2 * i + 1));
+  }
+  if (tid == 0) {
+    if (n_words & 1) acc += digest_term(words[n_words - 1], static_cast<unsigned long long>(n_words - 1));
+    if (tail_bytes > 0) {
+      unsigned long long w = 0ull;
+      for (int b = 0; b < tail_bytes; ++b) w |= static_cast<unsigned long long>(tail[b]) << (8 * b);
+      acc += digest_term(static_cast<long long>(w), static_cast<unsigned long long>(n_words));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if ((threadIdx.x & 31) == 0 && acc != 0ull) atomicAdd(out, acc);
+}
+
 PeerPtrs make_ptrs(void* const* p, int world) {
   PeerPtrs out;
   for (int r = 0; r < 8; ++r) out.p[r] = r < world ? p[r] : nullptr;
@@ -311,6 +346,15 @@ void zero1_fused_step(void* const* grads, void* const* params, int rank, int wor
     default: RLK_ZERO1(0); break;
   }
 #undef RLK_ZERO1
+}
+
+void weight_digest64(const void* data, long long nbytes, unsigned long long* out, cudaStream_t stream) {
+  if (nbytes <= 0) return;
+  const long long n_words = nbytes / 8;
+  const int tail = static_cast<int>(nbytes % 8);
+  const int grid = capped_grid(n_words / 2 + 1, 256);
+  digest64_kernel<<<grid, 256, 0, stream>>>(static_cast<const long long*>(data), n_words,
+                                            static_cast<const unsigned char*>(data) + n_words * 8, tail, out);
 }
 
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream) {

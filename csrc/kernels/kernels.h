@@ -7,6 +7,11 @@
 #include <stdint.h>
 
 namespace rlk {
+// Debug-bounds builds (-DRLK_DEBUG_BOUNDS=1): the error word that checked index accesses report to, per device.  The
+// bindings register it; launchers read it (defined in runtime/runtime.cpp).
+uint32_t* debug_error_word();
+void bind_debug_error_word(int device, uint32_t* word);
+
 // Kernel attributes such as the opt-in shared-memory size belong to one device's context.  A function-local
 // ``static PerDeviceOnce flag;`` with ``if (flag.first()) { cudaFuncSetAttribute(...); }`` configures the kernel once
 // on every device that launches it, not once per process.
@@ -125,6 +130,7 @@ struct LogpRowsArgs {
   int V;
   void* out;  // [rows]
   int out_dtype;
+  long long total_rows;  // rows of ``logits`` (0: unknown); gathered row indices are checked against it in debug builds
 };
 void logp_rows(const LogpRowsArgs& args, cudaStream_t stream);
 
@@ -169,8 +175,9 @@ namespace rlk {
 
 // -------------------------------------------------------------------------------- RL losses
 // bounds == null -> uniform groups of `uniform` sequences.
+// n_rewards: length of ``rewards`` / ``adv`` (group bounds are checked against it in debug-bounds builds)
 void group_advantages(const float* rewards, const long long* bounds, int num_groups, long long uniform, float eps,
-                      float* adv, cudaStream_t stream);
+                      float* adv, long long n_rewards, cudaStream_t stream);
 
 struct SurrogateFwdArgs {
   const float* logp;      // [n] policy log-probs
@@ -221,13 +228,15 @@ void swiglu_packed_backward(const __nv_bfloat16* gu, long long ldgu, const __nv_
 // with l1 / l2 [Hkv, n * rep]; rows = n * rep.
 void attn_merge2(const void* o1, const float* l1, const void* o2, const float* l2, void* out, long long rows, int hkv,
                  int rep, cudaStream_t stream);
+// table_rows: rows of the cos / sin tables (positions are checked against it in debug-bounds builds)
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
-                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream);
+                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, long long table_rows,
+                cudaStream_t stream);
 void embedding_forward(const long long* ids, const void* table, long long ldw, int dtype, void* out, long long rows,
                        int D, long long vocab, cudaStream_t stream);
 void embedding_backward(const long long* seg_ids, const long long* seg_start, long long segments,
                         const long long* order, const void* dy, int dy_dtype, int D, void* dtable, bool table_fp32,
-                        long long ldw, cudaStream_t stream);
+                        long long ldw, long long dy_rows, long long table_rows, cudaStream_t stream);
 // master: fp32 master weights or nullptr.  residual: 16-bit residuals of a bf16 parameter (fp32 master = parameter
 // bits << 16 plus the sign-extended residual) or nullptr; at most one of the two.
 void adamw_step(void* p, int p_dtype, float* master, short* residual, const void* g, int g_dtype, float* m, float* v,
@@ -330,6 +339,8 @@ void zero1_fused_step(void* const* grads, void* const* params, int rank, int wor
                       float* v, float* master, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                       float grad_scale, const uint32_t* skip_if_set, int max_blocks, cudaStream_t stream);
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream);
+// 64-bit position-weighted digest of ``nbytes`` bytes at ``data`` (16-byte aligned), added into *out.
+void weight_digest64(const void* data, long long nbytes, unsigned long long* out, cudaStream_t stream);
 void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
                     cudaStream_t stream);
 

@@ -104,9 +104,12 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) logp_rows_kernel(const T* __restrict__ logits, long long ld,
                                                              const long long* __restrict__ ids,
                                                              const long long* __restrict__ row_indices, int V,
-                                                             void* __restrict__ out, int out_dtype, float inv_temp) {
+                                                             void* __restrict__ out, int out_dtype, float inv_temp,
+                                                             long long total_rows RLK_DBG_PARAM) {
   __shared__ MS red[kThreads / 32];
   const long long row = row_indices ? row_indices[blockIdx.x] : static_cast<long long>(blockIdx.x);
+  // a gathered row index outside the logits (debug-bounds builds report it and skip the row)
+  if (total_rows > 0 && !RLK_INDEX_OK(row, total_rows, RLK_DBG_ERR, 630u, 1)) return;
   const T* src = logits + row * ld;
   MS acc = stream_row(src, V);
   acc = block_merge(acc, red);
@@ -130,16 +133,18 @@ void logp_rows(const LogpRowsArgs& a, cudaStream_t stream) {
   switch (a.in_dtype) {
     case 0:
       logp_rows_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(a.logits), a.ld, a.ids,
-                                                             a.row_indices, a.V, a.out, a.out_dtype, 1.f);
+                                                             a.row_indices, a.V, a.out, a.out_dtype, 1.f,
+                                                             a.total_rows RLK_DBG_ARG);
       break;
     case 1:
       logp_rows_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.logits), a.ld,
                                                                      a.ids, a.row_indices, a.V, a.out, a.out_dtype,
-                                                                     1.f);
+                                                                     1.f, a.total_rows RLK_DBG_ARG);
       break;
     default:
       logp_rows_kernel<__half><<<grid, kThreads, 0, stream>>>(static_cast<const __half*>(a.logits), a.ld, a.ids,
-                                                              a.row_indices, a.V, a.out, a.out_dtype, 1.f);
+                                                              a.row_indices, a.V, a.out, a.out_dtype, 1.f,
+                                                              a.total_rows RLK_DBG_ARG);
       break;
   }
 }

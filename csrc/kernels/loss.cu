@@ -15,12 +15,17 @@ namespace {
 // ------------------------------------------------------------------------- group advantages
 // One warp per group (CSR bounds).  Population variance, clamped at eps^2 before the sqrt.
 __global__ void group_adv_kernel(const float* __restrict__ rewards, const long long* __restrict__ bounds,
-                                 int num_groups, long long uniform, float eps, float* __restrict__ adv) {
+                                 int num_groups, long long uniform, float eps, float* __restrict__ adv,
+                                 long long n_rewards RLK_DBG_PARAM) {
   const int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (g >= num_groups) return;
   const long long b0 = bounds ? bounds[g] : g * uniform;
   const long long b1 = bounds ? bounds[g + 1] : (g + 1) * uniform;
+  // CSR group bounds come from the caller: [b0, b1) must lie inside the reward vector
+  if (!RLK_INDEX_OK(b0, n_rewards + 1, RLK_DBG_ERR, 640u, 1) || !RLK_INDEX_OK(b1, n_rewards + 1, RLK_DBG_ERR, 640u, 2) ||
+      !RLK_INDEX_OK(b1 - b0, n_rewards + 1, RLK_DBG_ERR, 640u, 3))
+    return;
   float s = 0.f, q = 0.f;
   for (long long i = b0 + lane; i < b1; i += 32) {
     const float r = rewards[i];
@@ -171,11 +176,12 @@ __global__ void dpo_kernel(const float* __restrict__ pc, const float* __restrict
 }  // namespace
 
 void group_advantages(const float* rewards, const long long* bounds, int num_groups, long long uniform, float eps,
-                      float* adv, cudaStream_t stream) {
+                      float* adv, long long n_rewards, cudaStream_t stream) {
   if (num_groups <= 0) return;
   const int threads = 128;
   const int blocks = (num_groups * 32 + threads - 1) / threads;
-  group_adv_kernel<<<blocks, threads, 0, stream>>>(rewards, bounds, num_groups, uniform, eps, adv);
+  group_adv_kernel<<<blocks, threads, 0, stream>>>(rewards, bounds, num_groups, uniform, eps, adv,
+                                                   n_rewards RLK_DBG_ARG);
 }
 
 int surrogate_partial_floats() { return kLossBlocks * 3; }

@@ -335,7 +335,8 @@ __global__ void swiglu_packed_bwd_kernel(const __nv_bfloat16* __restrict__ gu, l
 template <typename T>
 __global__ void rope_kernel(const T* __restrict__ x, long long ldt, const long long* __restrict__ pos,
                             const float* __restrict__ cs, const float* __restrict__ sn, T* __restrict__ out,
-                            long long ldo, long long tokens, int heads, int D, float sign) {
+                            long long ldo, long long tokens, int heads, int D, float sign,
+                            long long table_rows RLK_DBG_PARAM) {
   const int half = D / 2;
   const long long total = tokens * heads * half;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
@@ -345,6 +346,7 @@ __global__ void rope_kernel(const T* __restrict__ x, long long ldt, const long l
     const int h = static_cast<int>(th % heads);
     const long long t = th / heads;
     const long long p = pos[t];
+    if (!RLK_INDEX_OK(p, table_rows, RLK_DBG_ERR, 610u, 1)) continue;  // position beyond the cos / sin table
     const float c = cs[p * half + j];
     const float s = sn[p * half + j] * sign;
     const long long base = t * ldt + static_cast<long long>(h) * D;
@@ -359,7 +361,7 @@ __global__ void rope_kernel(const T* __restrict__ x, long long ldt, const long l
 __global__ void rope_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, long long ldt, const long long* __restrict__ pos,
                                      const float* __restrict__ cs, const float* __restrict__ sn,
                                      __nv_bfloat16* __restrict__ out, long long ldo, long long tokens, int heads, int D,
-                                     float sign) {
+                                     float sign, long long table_rows RLK_DBG_PARAM) {
   const int half = D / 2;
   const int vec_per_head = half / 8;  // threads per (token, head)
   const long long total = tokens * heads * vec_per_head;
@@ -370,6 +372,7 @@ __global__ void rope_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, long l
     const int h = static_cast<int>(th % heads);
     const long long t = th / heads;
     const long long p = pos[t];
+    if (!RLK_INDEX_OK(p, table_rows, RLK_DBG_ERR, 611u, 1)) continue;  // position beyond the cos / sin table
     const float4* c4 = reinterpret_cast<const float4*>(cs + p * half + v * 8);
     const float4* s4 = reinterpret_cast<const float4*>(sn + p * half + v * 8);
     const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
@@ -398,9 +401,10 @@ __global__ void rope_bf16_vec_kernel(const __nv_bfloat16* __restrict__ x, long l
 // -------------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const T* __restrict__ table, long long ldw,
-                                     T* __restrict__ out, int D, long long vocab) {
+                                     T* __restrict__ out, int D, long long vocab RLK_DBG_PARAM) {
   const long long row = blockIdx.x;
   long long id = ids[row];
+  (void)RLK_INDEX_OK(id, vocab, RLK_DBG_ERR, 620u, 1);  // release builds read row 0 for an id outside the table
   if (id < 0 || id >= vocab) id = 0;
   const T* src = table + id * ldw;
   T* dst = out + row * static_cast<long long>(D);
@@ -419,13 +423,18 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const T*
 template <typename T, typename TG>
 __global__ void embedding_bwd_kernel(const long long* __restrict__ seg_ids, const long long* __restrict__ seg_start,
                                      const long long* __restrict__ order, const T* __restrict__ dy, int D,
-                                     TG* __restrict__ dtable, long long ldw) {
+                                     TG* __restrict__ dtable, long long ldw, long long dy_rows,
+                                     long long table_rows RLK_DBG_PARAM) {
   const long long s = blockIdx.x;
   const long long b0 = seg_start[s], b1 = seg_start[s + 1];
   const long long id = seg_ids[s];
+  if (!RLK_INDEX_OK(id, table_rows, RLK_DBG_ERR, 621u, 1)) return;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-    for (long long k = b0; k < b1; ++k) acc += ldf(dy, order[k] * static_cast<long long>(D) + i);
+    for (long long k = b0; k < b1; ++k) {
+      if (!RLK_INDEX_OK(order[k], dy_rows, RLK_DBG_ERR, 621u, 2)) continue;
+      acc += ldf(dy, order[k] * static_cast<long long>(D) + i);
+    }
     stf(dtable, id * ldw + i, acc);
   }
 }
@@ -720,7 +729,8 @@ void attn_merge2(const void* o1, const float* l1, const void* o2, const float* l
 }
 
 void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, const float* cos_t, const float* sin_t,
-                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, cudaStream_t stream) {
+                void* out, long long ldo, long long tokens, int heads, int D, bool inverse, long long table_rows,
+                cudaStream_t stream) {
   if (tokens <= 0) return;
   const int threads = 256;
   const bool vec_ok = dtype == 1 && D % 16 == 0 && ldt % 8 == 0 && ldo % 8 == 0 &&
@@ -729,13 +739,14 @@ void rope_apply(const void* x, long long ldt, int dtype, const long long* pos, c
   if (vec_ok) {
     rope_bf16_vec_kernel<<<grid_for(tokens * heads * (D / 16), threads), threads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), ldt, pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(out), ldo, tokens, heads, D,
-        inverse ? -1.f : 1.f);
+        inverse ? -1.f : 1.f, table_rows RLK_DBG_ARG);
     return;
   }
   const int grid = grid_for(tokens * heads * (D / 2), threads);
   RLK_DISPATCH_T(dtype, {
     rope_kernel<T><<<grid, threads, 0, stream>>>(static_cast<const T*>(x), ldt, pos, cos_t, sin_t,
-                                                 static_cast<T*>(out), ldo, tokens, heads, D, inverse ? -1.f : 1.f);
+                                                 static_cast<T*>(out), ldo, tokens, heads, D, inverse ? -1.f : 1.f,
+                                                 table_rows RLK_DBG_ARG);
   });
 }
 
@@ -744,22 +755,24 @@ void embedding_forward(const long long* ids, const void* table, long long ldw, i
   if (rows <= 0) return;
   RLK_DISPATCH_T(dtype, {
     embedding_fwd_kernel<T><<<rows, 128, 0, stream>>>(ids, static_cast<const T*>(table), ldw, static_cast<T*>(out), D,
-                                                      vocab);
+                                                      vocab RLK_DBG_ARG);
   });
 }
 
 void embedding_backward(const long long* seg_ids, const long long* seg_start, long long segments,
                         const long long* order, const void* dy, int dy_dtype, int D, void* dtable, bool table_fp32,
-                        long long ldw, cudaStream_t stream) {
+                        long long ldw, long long dy_rows, long long table_rows, cudaStream_t stream) {
   if (segments <= 0) return;
   RLK_DISPATCH_T(dy_dtype, {
     if (table_fp32)
       embedding_bwd_kernel<T, float><<<segments, 128, 0, stream>>>(seg_ids, seg_start, order,
                                                                    static_cast<const T*>(dy), D,
-                                                                   static_cast<float*>(dtable), ldw);
+                                                                   static_cast<float*>(dtable), ldw, dy_rows,
+                                                                   table_rows RLK_DBG_ARG);
     else
       embedding_bwd_kernel<T, T><<<segments, 128, 0, stream>>>(seg_ids, seg_start, order, static_cast<const T*>(dy), D,
-                                                               static_cast<T*>(dtable), ldw);
+                                                               static_cast<T*>(dtable), ldw, dy_rows,
+                                                               table_rows RLK_DBG_ARG);
   });
 }
 

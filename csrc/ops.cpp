@@ -37,15 +37,22 @@ void check_rowmajor(const Tensor& t, const char* name) {
   TORCH_CHECK(t.dim() == 2 && t.stride(1) == 1, "rl_engine: ", name, " must be 2-D with unit inner stride");
 }
 
-cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
-
 // One 4-word error record per device, allocated on first use.
 Tensor& error_word(int device) {
   static std::vector<Tensor> words(64);
   if (!words[device].defined()) {
     words[device] = torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+    // debug-bounds builds: kernels without an error-word parameter report checked indices here
+    rlk::bind_debug_error_word(device, reinterpret_cast<uint32_t*>(words[device].data_ptr<int>()));
   }
   return words[device];
+}
+
+cudaStream_t stream_of(const Tensor& t) {
+#if defined(RLK_DEBUG_BOUNDS)
+  error_word(t.get_device());  // make sure the word exists before any launch on this device
+#endif
+  return at::cuda::getCurrentCUDAStream(t.get_device()).stream();
 }
 uint32_t* err_ptr(const Tensor& like) { return reinterpret_cast<uint32_t*>(error_word(like.get_device()).data_ptr<int>()); }
 
@@ -590,6 +597,7 @@ void logp_rows(const Tensor& logits, const Tensor& ids, std::optional<Tensor> ro
     a.launch_rows = static_cast<int>(row_indices->numel());
   }
   a.V = static_cast<int>(logits.size(1));
+  a.total_rows = logits.size(0);
   a.out = out.data_ptr();
   a.out_dtype = dtype_code(out);
   if (a.launch_rows == 0) return;
@@ -684,7 +692,7 @@ Tensor group_advantages(const Tensor& rewards, std::optional<Tensor> bounds, int
   }
   if (groups > 0) {
     rlk::group_advantages(rewards.data_ptr<float>(), bptr, static_cast<int>(groups), uniform, static_cast<float>(eps),
-                          adv.data_ptr<float>(), stream_of(rewards));
+                          adv.data_ptr<float>(), rewards.numel(), stream_of(rewards));
     after_launch();
   }
   return adv;
@@ -901,7 +909,7 @@ Tensor rope(const Tensor& x, const Tensor& positions, const Tensor& cos_t, const
   if (x.numel()) {
     rlk::rope_apply(x.data_ptr(), x.stride(0), dtype_code(x), reinterpret_cast<const long long*>(positions.data_ptr<int64_t>()),
                     cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), out.data_ptr(), out.stride(0), x.size(0),
-                    static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), inverse, stream_of(x));
+                    static_cast<int>(x.size(1)), static_cast<int>(x.size(2)), inverse, cos_t.size(0), stream_of(x));
     after_launch();
   }
   return out;
@@ -957,7 +965,8 @@ void embedding_bwd(const Tensor& seg_ids, const Tensor& seg_start, const Tensor&
   rlk::embedding_backward(reinterpret_cast<const long long*>(seg_ids.data_ptr<int64_t>()),
                           reinterpret_cast<const long long*>(seg_start.data_ptr<int64_t>()), segs,
                           reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), dy.data_ptr(), dtype_code(dy),
-                          static_cast<int>(dy.size(1)), dtable.data_ptr(), tfp32, dtable.stride(0), stream_of(dy));
+                          static_cast<int>(dy.size(1)), dtable.data_ptr(), tfp32, dtable.stride(0), dy.size(0),
+                          dtable.size(0), stream_of(dy));
   after_launch();
 }
 

@@ -95,6 +95,18 @@ void py_cast_broadcast(const Tensor& src, std::vector<uint64_t> dsts, int64_t ds
                  static_cast<int>(d.size()), src.numel(), cur_stream(src.get_device()));
 }
 
+// digests[slot] += digest of the bytes of ``t`` (contiguous, 16-byte aligned); ``digests`` is int64 on the same device.
+void py_weight_digest(const Tensor& t, Tensor digests, int64_t slot) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "rl_engine.weight_digest: contiguous CUDA tensor expected");
+  TORCH_CHECK(digests.is_cuda() && digests.scalar_type() == torch::kInt64 && digests.is_contiguous() && slot >= 0 &&
+                  slot < digests.numel() && digests.get_device() == t.get_device(),
+              "rl_engine.weight_digest: digests must be a contiguous int64 tensor on the tensor's device");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "rl_engine.weight_digest: data must be 16-byte aligned");
+  const c10::cuda::CUDAGuard guard(t.device());
+  weight_digest64(t.data_ptr(), static_cast<long long>(t.numel()) * static_cast<long long>(t.element_size()),
+                  reinterpret_cast<unsigned long long*>(digests.data_ptr<int64_t>()) + slot, cur_stream(t.get_device()));
+}
+
 void check_rows(const Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && t.size(1) % 8 == 0 &&
                   t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
@@ -174,6 +186,7 @@ void bind_comm(pybind11::module_& m) {
   m.def("zero1_fused_step", counted("rlk::zero1_fused_step", &py_zero1_fused_step));
   m.def("peer_sum", counted("rlk::peer_sum", &py_peer_sum));
   m.def("cast_broadcast", counted("rlk::cast_broadcast", &py_cast_broadcast));
+  m.def("weight_digest", counted("rlk::weight_digest", &py_weight_digest));
 }
 
 }  // namespace rlk

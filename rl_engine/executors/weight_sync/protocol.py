@@ -111,25 +111,75 @@ def digest_policy() -> str:
     return os.environ.get("RL_KERNEL_WEIGHT_DIGEST", "auto").strip().lower()
 
 
+_DIGEST_MUL = -7046029254386353131  # 0x9E3779B97F4A7C15 as a signed 64-bit value
+
+
+def _dev64_reference(t: torch.Tensor) -> int:
+    """The ``dev64`` digest with plain tensor ops (any device): sum over the tensor's 64-bit words ``w_i`` (tail
+    zero-padded) of ``(w_i ^ (w_i >> 29)) * ((i + 1) * C)`` modulo 2^64.  The fused kernel computes the same bits in
+    one pass; this form is the fallback for unaligned views and the oracle of the kernel's test."""
+    flat = t.contiguous().view(-1).view(torch.uint8)
+    pad = (-flat.numel()) % 8
+    if pad:
+        flat = torch.cat([flat, flat.new_zeros(pad)])
+    words = flat.view(torch.int64)
+    total = 0
+    step = 1 << 24  # bounded temporaries: the weights of 16 M words at a time
+    for i0 in range(0, words.numel(), step):
+        w = words[i0 : i0 + step]
+        weights = torch.arange(i0 + 1, i0 + w.numel() + 1, device=w.device, dtype=torch.int64) * _DIGEST_MUL
+        total += int(((w ^ (w >> 29)) * weights).sum().item())
+    return total & 0xFFFFFFFFFFFFFFFF
+
+
+def _kernel_digest_ok(t: torch.Tensor) -> bool:
+    if not t.is_cuda or t.numel() == 0 or not t.is_contiguous() or t.data_ptr() % 16:
+        return False
+    from rl_engine.kernels.ops.base import _C, _EXT_AVAILABLE
+
+    return _EXT_AVAILABLE and hasattr(_C, "weight_digest")
+
+
+def tensor_digests(tensors: Mapping[str, torch.Tensor]) -> Dict[str, str]:
+    """Integrity digests of many tensors (the ``TensorDescriptor.sha256`` field; see the module docstring).  CUDA
+    tensors are digested by one kernel launch each into a shared result buffer that is read back ONCE, so a model
+    state of hundreds of tensors costs one host synchronisation, not one per tensor."""
+    policy = digest_policy()
+    out: Dict[str, str] = {}
+    if policy == "none":
+        return {name: "none" for name in tensors}
+    batched: Dict[torch.device, list] = {}
+    for name, tensor in tensors.items():
+        t = tensor.detach()
+        if t.is_cuda and policy != "sha256":
+            nbytes = t.numel() * t.element_size()
+            if _kernel_digest_ok(t):
+                batched.setdefault(t.device, []).append((name, t, nbytes))
+            else:
+                c = t.contiguous()
+                if c.numel() and _kernel_digest_ok(c):
+                    batched.setdefault(c.device, []).append((name, c, nbytes))
+                else:
+                    out[name] = f"dev64:{_dev64_reference(t):016x}:{(nbytes + 7) // 8 * 8}"
+            continue
+        data = t.contiguous().cpu()
+        raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
+        out[name] = hashlib.sha256(raw).hexdigest()
+    for device, items in batched.items():
+        from rl_engine.kernels.ops.base import require_ext
+
+        ext = require_ext()
+        results = torch.zeros(len(items), dtype=torch.int64, device=device)
+        for slot, (_name, t, _n) in enumerate(items):
+            ext.weight_digest(t, results, slot)
+        for (name, _t, nbytes), value in zip(items, results.cpu().tolist()):
+            out[name] = f"dev64:{value & 0xFFFFFFFFFFFFFFFF:016x}:{(nbytes + 7) // 8 * 8}"
+    return out
+
+
 def tensor_digest(tensor: torch.Tensor) -> str:
     """Integrity digest stored in ``TensorDescriptor.sha256`` (see the module docstring)."""
-    policy = digest_policy()
-    if policy == "none":
-        return "none"
-    t = tensor.detach()
-    if t.is_cuda and policy != "sha256":
-        flat = t.contiguous().view(-1).view(torch.uint8)
-        pad = (-flat.numel()) % 8
-        if pad:
-            flat = torch.cat([flat, flat.new_zeros(pad)])
-        words = flat.view(torch.int64)
-        # position-weighted wrap-around sum: cheap, order sensitive, computed entirely on the device
-        weights = torch.arange(1, words.numel() + 1, device=words.device, dtype=torch.int64) * -7046029254386353131
-        mixed = int(((words ^ (words >> 29)) * weights).sum().item()) & 0xFFFFFFFFFFFFFFFF
-        return f"dev64:{mixed:016x}:{flat.numel()}"
-    data = t.contiguous().cpu()
-    raw = data.view(torch.uint8).numpy().tobytes() if data.numel() else b""
-    return hashlib.sha256(raw).hexdigest()
+    return tensor_digests({"t": tensor})["t"]
 
 
 @dataclass(frozen=True)
@@ -144,7 +194,13 @@ class TensorDescriptor:
     sha256: str
 
     @classmethod
-    def from_tensor(cls, name: str, tensor: torch.Tensor) -> "TensorDescriptor":
+    def from_tensors(cls, tensors: Mapping[str, torch.Tensor]) -> Dict[str, "TensorDescriptor"]:
+        """Descriptors of a whole state; the digests are computed in one batch (see ``tensor_digests``)."""
+        digests = tensor_digests(tensors)
+        return {name: cls.from_tensor(name, t, digest=digests[name]) for name, t in tensors.items()}
+
+    @classmethod
+    def from_tensor(cls, name: str, tensor: torch.Tensor, digest: Optional[str] = None) -> "TensorDescriptor":
         return cls(
             name=name,
             shape=tuple(int(d) for d in tensor.shape),
@@ -153,7 +209,7 @@ class TensorDescriptor:
             device=str(tensor.device),
             numel=int(tensor.numel()),
             nbytes=int(tensor.numel() * tensor.element_size()),
-            sha256=tensor_digest(tensor),
+            sha256=tensor_digest(tensor) if digest is None else digest,
         )
 
     def to_json(self) -> Dict[str, Any]:
@@ -286,7 +342,7 @@ class BridgeStateMachine:
             meta[BRIDGE_METADATA_KEY] = block
         manifest = WeightUpdateManifest(
             update_id=update_id, source_worker=self.source_worker, source_rank=self.source_rank, weight_version=version,
-            transport=self.transport, tensors={n: TensorDescriptor.from_tensor(n, t) for n, t in stored.items()},
+            transport=self.transport, tensors=TensorDescriptor.from_tensors(stored),
             created_at=time.perf_counter(), metadata=meta,
         )
         self._updates[update_id] = UpdateRecord(manifest=manifest, tensors=stored, resources=resources)
@@ -383,7 +439,9 @@ class BridgeStateMachine:
                 raise WeightManifestValidationError(
                     f"tensor descriptor mismatch for {name}: expected {want}, got {got}"
                 )
-            now = TensorDescriptor.from_tensor(name, record.tensors[name])
+        current = TensorDescriptor.from_tensors({name: record.tensors[name] for name in expected.tensors})
+        for name, want in expected.tensors.items():
+            now = current[name]
             if now.sha256 != want.sha256:
                 raise WeightManifestValidationError(
                     f"tensor checksum mismatch for {name}: expected {want.sha256}, got {now.sha256}"

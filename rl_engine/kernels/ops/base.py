@@ -16,8 +16,15 @@ from rl_engine.utils.logger import logger
 _C: Any = None
 _EXT_ERROR: str = ""
 
+import os
+
 try:
-    from rl_engine import _C  # type: ignore[no-redef]
+    if os.environ.get("RLK_DEBUG_BOUNDS") == "1":
+        # the debug-bounds build: every index that comes from the caller (token ids, gathered rows, positions, group
+        # bounds, expert slots) is range-checked on the device and a bad one is reported in the error word
+        from rl_engine import _C_dbg as _C  # type: ignore[no-redef]
+    else:
+        from rl_engine import _C  # type: ignore[no-redef]
 
     _EXT_AVAILABLE = True
 except ImportError as exc:  # not built, or built for another torch
@@ -40,7 +47,7 @@ def check_device_errors(device: int = 0) -> None:
     code, kernel_id, block, site = require_ext().error_state(device)
     if code:
         require_ext().reset_error(device)
-        names = {1: "mbarrier wait timed out", 2: "peer wait timed out", 3: "bad argument"}
+        names = {1: "mbarrier wait timed out", 2: "peer wait timed out", 3: "bad argument", 4: "index out of range"}
         raise RuntimeError(
             f"rl_engine kernel error: {names.get(code, code)} (kernel {kernel_id}, block {block}, site {site})"
         )

@@ -196,6 +196,41 @@ class _FusedAttentionBlockPrefix(torch.autograd.Function):
         return dqkv, dk[:n], dv[:n], None, None, None, None, None, None, None
 
 
+class _FusedAttentionBlockCP(torch.autograd.Function):
+    """``_FusedAttentionBlock`` for a sequence that is sharded over the ranks of a context-parallel group: ``cp`` (a
+    ``rl_engine.parallel.context_parallel.ContextParallelAttention``) gathers every rank's rotated keys / values through
+    peer stores before the flash kernel runs on the local queries, and in backward sums the ranks' contributions to the
+    locally owned keys / values in rank order.  ``positions`` are the global positions of the local (zig-zag) rows."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_t, sin_t, cp, hq, hkv, scale):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+
+        ext = require_ext()
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        ext.rope(q, positions, cos_t, sin_t, False, q)
+        ext.rope(k, positions, cos_t, sin_t, False, k)
+        k_all, v_all = cp.gather_kv(k, v)
+        out, lse = packed_attention_forward(q, k_all, v_all, cp.layout(q.device), scale, True)
+        ctx.save_for_backward(qkv, out, lse, positions, cos_t, sin_t)
+        ctx.meta = (cp, hq, hkv, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from rl_engine.kernels.ops.sm100.attention_bwd_kernels import fused_backward
+
+        qkv, out, lse, positions, cos_t, sin_t = ctx.saved_tensors
+        cp, hq, hkv, scale = ctx.meta
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        k_all, v_all = cp.gather_kv(k, v)  # gathered again: cheaper than keeping the whole sequence's keys per layer
+        dq, dk_full, dv_full = fused_backward(q, k_all, v_all, out, lse, dout.contiguous(), cp.layout(q.device), scale)
+        dk, dv = cp.reduce_dkv(dk_full, dv_full)
+        dqkv = _unrotate_into(torch.empty_like(qkv), dq, dk, dv, positions, cos_t, sin_t, hq, hkv)
+        return dqkv, None, None, None, None, None, None, None
+
+
 class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
                  activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192) -> None:
@@ -318,6 +353,10 @@ class LlamaModel(nn.Module):
             qkv3 = torch.cat([qn.view(t, hq, -1), kn.view(t, hkv, -1), qkv3[:, hq + hkv :]], dim=1)
         if _fused_path(qkv) and cfg.head_dim == 128:
             tail = (positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale)
+            if hasattr(layout, "gather_kv"):  # a context-parallel group: ``layout`` is its attention object
+                if return_kv or k_prefix is not None:
+                    raise RuntimeError("context-parallel passes do not take or return a cached prefix")
+                return _FusedAttentionBlockCP.apply(qkv3, *tail).reshape(t, cfg.q_dim)
             if return_kv:
                 out, k_rot, v_rot = _FusedAttentionBlockKV.apply(qkv3, *tail)
                 return out.reshape(t, cfg.q_dim), k_rot, v_rot

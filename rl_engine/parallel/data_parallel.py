@@ -85,6 +85,7 @@ class ShardedFusedAdamW:
         self.master = self._gather_local(params.local).float() if master_weights else None
         self.steps = 0
         self.grad_scale = 1.0  # extra factor on the summed gradient (1 / number of accumulated prompt groups)
+        self.reduce = "mean"   # "mean": ranks hold gradients of different samples; "sum": of different tokens of one loss
         self.overlap = bool(overlap) and mem.world > 1
         self.overlap_blocks = int(overlap_blocks)
         self._side = torch.cuda.Stream(device=dev) if self.overlap else None
@@ -107,7 +108,7 @@ class ShardedFusedAdamW:
         require_ext().zero1_fused_step(
             self.grads.ptrs, self.params.ptrs, lo, hi, self.m[off : off + n], self.v[off : off + n], master, self.lr,
             self.betas[0], self.betas[1], self.eps, self.weight_decay, self.steps + 1,
-            float(self.grad_scale) / self.mem.world,
+            float(self.grad_scale) / (self.mem.world if self.reduce == "mean" else 1),
             self.mem.rank, self.mem.error_word, max_blocks,
         )
         self._launched[b] = True

@@ -26,8 +26,10 @@ NVCC_FLAGS = [
     "-Xfatbin",
     "-compress-all",
 ]
-if os.environ.get("RLK_DEBUG_BOUNDS") == "1":
-    NVCC_FLAGS.append("-DRLK_DEBUG_BOUNDS=1")
+# ``rl_engine._C_dbg`` is the same sources with -DRLK_DEBUG_BOUNDS=1 (checked index accesses that report to the
+# error word); it is loaded instead of ``_C`` when RLK_DEBUG_BOUNDS=1 is set at import time.  RLK_SKIP_DEBUG_EXT=1
+# skips building it.
+DEBUG_FLAG = "-DRLK_DEBUG_BOUNDS=1"
 if os.environ.get("RLK_ATTN_PROFILE") == "1":  # per-phase cycle counters in the attention forward kernel
     NVCC_FLAGS.append("-DRLK_ATTN_PROFILE=1")
     CXX_FLAGS.append("-DRLK_ATTN_PROFILE=1")
@@ -55,6 +57,13 @@ setup(
             include_dirs=[os.path.join(ROOT, "csrc")],
             extra_compile_args={"cxx": CXX_FLAGS, "nvcc": NVCC_FLAGS},
         )
-    ],
+    ] + ([] if os.environ.get("RLK_SKIP_DEBUG_EXT") == "1" else [
+        CUDAExtension(
+            name="rl_engine._C_dbg",
+            sources=sources(),
+            include_dirs=[os.path.join(ROOT, "csrc")],
+            extra_compile_args={"cxx": CXX_FLAGS + [DEBUG_FLAG], "nvcc": NVCC_FLAGS + [DEBUG_FLAG]},
+        )
+    ]),
     cmdclass={"build_ext": BuildExtension.with_options(use_ninja=True)},
 )

@@ -335,6 +335,42 @@ def main() -> None:
     check_device_errors(local)
     print(f"[{rank}] OK context-parallel attention", flush=True)
 
+    # ---- long-context GRPO step: sequences sharded over the ranks (context parallel) vs the single-GPU trainer ----
+    from rl_engine.parallel.long_context import ContextParallelGRPOTrainer
+
+    P_cp, L_cp = 128 * world, 128 * world * 3                 # S = 512 * world: chunks of 256 tokens
+    hb_cp = synthetic_batch(dcfg.vocab_size, prompt_len=P_cp, group=2, completion_len=L_cp, seed=9)
+    hb_cp.completion_mask[1, -37:] = False                    # a ragged completion
+    one = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=44, activation_checkpointing=False)
+    start_cp = one.flat.clone()
+    one_tr = GRPOTrainer(one, lr=1e-3, micro_group=None)
+    with torch.no_grad():
+        cur_cp = one_tr.policy_logps(hb_cp.to(dev)).float()
+    gcp = torch.Generator(device=dev).manual_seed(72)
+    hb_cp.old_logps = (cur_cp + 0.01 * torch.randn(cur_cp.shape, device=dev, generator=gcp)).cpu()
+    hb_cp.ref_logps = (cur_cp + 0.01 * torch.randn(cur_cp.shape, device=dev, generator=gcp)).cpu()
+    db_cp = hb_cp.to(dev)
+    cp_model = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=44, activation_checkpointing=False)
+    cp_tr = ContextParallelGRPOTrainer(cp_model, lr=1e-3, layers_per_bucket=1)
+    with torch.no_grad():
+        lp_cp = cp_tr.policy_logps(db_cp)
+    assert torch.allclose(lp_cp, cur_cp, atol=5e-2, rtol=5e-2), (lp_cp - cur_cp).abs().max()
+    loss_one = float(one_tr.step_device(db_cp))
+    loss_cp = float(cp_tr.step_device(db_cp))
+    cp_tr.check()
+    check_device_errors(local)
+    assert abs(loss_cp - loss_one) < 2e-2 * max(1.0, abs(loss_one)), (loss_cp, loss_one)
+    every = [torch.empty_like(cp_model.flat) for _ in range(world)]
+    dist.all_gather(every, cp_model.flat.contiguous())
+    assert all(torch.equal(every[0], e_) for e_ in every), "context parallel: parameters differ between ranks"
+    d_cp, d_one = cp_model.flat.float() - start_cp.float(), one.flat.float() - start_cp.float()
+    moved = d_one.abs() > 0
+    rel = ((d_cp - d_one).abs().mean() / d_one.abs().mean()).item()
+    agree = (torch.sign(d_cp[moved]) == torch.sign(d_one[moved])).float().mean().item()
+    assert rel < 0.25 and agree > 0.9, f"context-parallel step differs from the single-GPU step: {rel:.3f}, {agree:.3f}"
+    cp_tr.mem.close()
+    print(f"[{rank}] OK context-parallel GRPO step == single-GPU step (loss {loss_cp:.4f} vs {loss_one:.4f}, update diff {rel:.3f})", flush=True)
+
     # ---- tensor-parallel linears: all-gather -> GEMM and GEMM -> reduce-scatter in one kernel ---------
     from rl_engine.parallel.tp_linear import TensorParallelLinears
 

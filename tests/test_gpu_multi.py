@@ -47,6 +47,32 @@ def test_symmetric_memory_single_rank_and_timeout_error():
     mem.close()
 
 
+@pytest.mark.parametrize("dtype,numel", [(torch.bfloat16, 1), (torch.bfloat16, 3), (torch.float32, 5), (torch.uint8, 23),
+                                         (torch.bfloat16, 8 * 1000 + 4), (torch.float32, 1 << 20), (torch.int64, 7)])
+def test_weight_digest_kernel_matches_the_tensor_op_form(dtype, numel):
+    """The one-pass digest kernel and the plain tensor-op formula give the same 64 bits, for tails of 1..7 bytes, an
+    odd word count, and a size that spans many blocks; a single flipped bit or two swapped words change the digest."""
+    from rl_engine.executors.weight_sync.protocol import _dev64_reference, tensor_digest, tensor_digests
+
+    g = torch.Generator(device="cuda").manual_seed(numel)
+    raw = torch.randint(0, 256, (numel * torch.empty((), dtype=dtype).element_size(),), device="cuda", generator=g,
+                        dtype=torch.uint8)
+    t = raw.view(dtype)
+    want = _dev64_reference(t)
+    got = tensor_digest(t)
+    assert got == f"dev64:{want:016x}:{(raw.numel() + 7) // 8 * 8}"
+    flipped = raw.clone()
+    flipped[raw.numel() // 2] ^= 1
+    assert tensor_digest(flipped.view(dtype)) != got
+    if raw.numel() >= 24:
+        swapped = raw.clone()
+        swapped[:8], swapped[8:16] = raw[8:16], raw[:8]
+        if not torch.equal(raw[:8], raw[8:16]):
+            assert tensor_digest(swapped.view(dtype)) != got
+    many = tensor_digests({"a": t, "b": flipped.view(dtype), "c": t[: max(1, numel // 2)]})   # one read-back for all
+    assert many["a"] == got and many["b"] != got
+
+
 def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge():
     """The weight-sync transport over symmetric memory on one rank: fp32 trainer weights land in the window as bf16
     through the cast+broadcast kernel, the manifest validates, tampering is caught, a too-small window is refused."""
