@@ -1,8 +1,10 @@
 // Temperature / top-k / top-p sampling, one CTA per row of logits.
 //
-//   1. radix select on order-preserving 32-bit keys (integer histograms in shared memory: counts are exact, so
-//      the threshold is deterministic) with a 12-bit first digit; the search stops as soon as the elements at or
-//      above the threshold bin fit into the candidate buffer, normally after ONE pass over the row;
+//   1. a candidate threshold from ONE vectorised pass over the row without atomics: every thread keeps the maximum of
+//      its elements, and the k-th largest of the 1024 thread maxima (found by rank counting in shared memory) is a
+//      lower bound of the row's k-th largest value, so {x >= threshold} contains the top k and, for ordinary logits,
+//      only a few more.  If that set does not fit the candidate buffer (masses of ties), the exact radix select on
+//      order-preserving 32-bit keys (integer histograms in shared memory, 12-bit first digit) takes over;
 //   2. those candidates are gathered into shared memory and bitonic-sorted by (logit descending, index
 //      ascending) -- a total order, so the gather order does not matter -- and cut to the first k plus ties;
 //   3. softmax with temperature over the candidates, inclusive scan in a fixed tree, top-p cut
@@ -51,6 +53,26 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
   return c;
 }
 
+// Calls f(value, index) for every element of the row, thread t taking 16-byte vectors t, t + 1024, ... when the row
+// is 16-byte aligned (scalar otherwise).  The visiting order per thread is fixed, the union over threads is the row.
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_in_row(const T* __restrict__ z, int V, F&& f) {
+  constexpr int kVec = 16 / sizeof(T);
+  if ((reinterpret_cast<uintptr_t>(z) & 15u) == 0) {
+    const int body = V / kVec;
+    const uint4* p = reinterpret_cast<const uint4*>(z);
+    for (int v = threadIdx.x; v < body; v += kThreads) {
+      const uint4 q = p[v];
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) f(ldv(e, j), v * kVec + j);
+    }
+    for (int i = body * kVec + threadIdx.x; i < V; i += kThreads) f(ldv(z, i), i);
+  } else {
+    for (int i = threadIdx.x; i < V; i += kThreads) f(ldv(z, i), i);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int top_k, float top_p, float inv_temp,
@@ -80,11 +102,45 @@ sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int t
     s_remaining = static_cast<unsigned int>(k);
     s_above = 0;
     s_pop = static_cast<unsigned int>(V);
+    s_count = 0;
   }
+  // ---- 1a. threshold from the thread maxima (one pass, no atomics).  hist[] doubles as the key array.
+  {
+    uint32_t best = 0u;  // smaller than the key of any float
+    for_each_in_row(z, V, [&](float x, int) {
+      const uint32_t key = f2key(x);
+      best = key > best ? key : best;
+    });
+    hist[tid] = best;
+    __syncthreads();
+    // rank of this thread's maximum among the 1024 (ties broken by thread id): a total order, so exactly one thread
+    // has rank k - 1; its key is <= the k-th largest key of the row
+    unsigned int rank = 0;
+    for (int j = 0; j < kThreads; ++j) {
+      const uint32_t other = hist[j];
+      rank += (other > best || (other == best && j < tid)) ? 1u : 0u;
+    }
+    if (rank == static_cast<unsigned int>(k <= kThreads ? k - 1 : kThreads - 1)) s_prefix = best;
+    __syncthreads();
+    const uint32_t from = s_prefix;
+    if (k <= kThreads) {
+      for_each_in_row(z, V, [&](float x, int i) {
+        const uint32_t key = f2key(x);
+        if (key >= from) {
+          const unsigned int slot = atomicAdd(&s_count, 1u);
+          if (slot < kCap) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(i));
+        }
+      });
+    }
+    __syncthreads();
+  }
+  const bool gathered = k <= kThreads && s_count <= static_cast<unsigned int>(kCap);  // uniform over the block
+  __syncthreads();
+  if (!gathered && tid == 0) s_prefix = 0;
   __syncthreads();
   int shift = 32;
 #pragma unroll 1
-  for (int pass = 0; pass < 4; ++pass) {
+  for (int pass = 0; pass < 4 && !gathered; ++pass) {
     const int bits = pass == 0 ? 12 : (pass == 3 ? 4 : 8);
     if (s_above + s_pop <= static_cast<unsigned int>(kCap)) break;  // uniform: shared values behind a barrier
     const uint32_t himask = pass == 0 ? 0u : (0xffffffffu << shift);
@@ -143,24 +199,30 @@ sample_topk_topp_kernel(const T* __restrict__ logits, long long ld, int V, int t
   // keys >= gather_from are candidates: everything above the threshold bin plus the bin itself
   const uint32_t gather_from = s_prefix;
 
-  // ---- 2. gather the candidates, then sort (key desc, index asc)
-  if (tid == 0) s_count = 0;
-  __syncthreads();
-  for (int i = tid; i < V; i += kThreads) {
-    const uint32_t key = f2key(ldv(z, i));
-    if (key >= gather_from) {
-      const unsigned int slot = atomicAdd(&s_count, 1u);
-      if (slot < kCap) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(i));
+  // ---- 2. gather the candidates (unless 1a already did), then sort (key desc, index asc)
+  if (!gathered) {
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += kThreads) {
+      const uint32_t key = f2key(ldv(z, i));
+      if (key >= gather_from) {
+        const unsigned int slot = atomicAdd(&s_count, 1u);
+        if (slot < kCap) cand[slot] = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - static_cast<uint32_t>(i));
+      }
     }
+    __syncthreads();
   }
-  __syncthreads();
   int n = static_cast<int>(s_count < static_cast<unsigned int>(kCap) ? s_count : kCap);
-  for (int i = n + tid; i < kCap; i += kThreads) cand[i] = 0ull;
+  // sort only as many slots as the candidates need (a power of two >= n, at least 64): the usual few dozen
+  // candidates take 21 compare-exchange rounds instead of the 66 of the full buffer
+  int sort_n = 64;
+  while (sort_n < n) sort_n <<= 1;
+  for (int i = n + tid; i < sort_n; i += kThreads) cand[i] = 0ull;
   __syncthreads();
-  // bitonic sort, descending, kCap elements (2 per thread)
-  for (int size = 2; size <= kCap; size <<= 1) {
+  // bitonic sort, descending, sort_n elements
+  for (int size = 2; size <= sort_n; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int t = tid; t < kCap / 2; t += kThreads) {
+      for (int t = tid; t < sort_n / 2; t += kThreads) {
         const int lo = 2 * t - (t & (stride - 1));
         const int hi = lo + stride;
         const bool desc = ((lo & size) == 0);
