@@ -209,10 +209,13 @@ namespace rlk {
 // --------------------------------------------------------------------------- model-side ops
 void rmsnorm_forward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, void* y, long long ldy,
                      bool out_fp32, long long rows, int D, float eps, float* rstd, cudaStream_t stream);
-int rmsnorm_bwd_chunks(long long rows);
+// Rows that one CTA of the backward kernel walks (a function of the row count only) and the number of CTAs =
+// rows of the partial-sum scratch ``dw_part [chunks, D]``.  rows_per_cta <= 0 selects the default for ``rows``.
+int rmsnorm_bwd_rows_per_cta(long long rows);
+int rmsnorm_bwd_chunks(long long rows, int rows_per_cta = 0);
 void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, const void* dy,
                       long long lddy, const float* rstd, void* dx, long long lddx, long long rows, int D,
-                      float* dw_part, void* dw, cudaStream_t stream);
+                      float* dw_part, void* dw, cudaStream_t stream, int rows_per_cta = 0);
 // up == null -> plain SiLU
 void swiglu_forward(const void* gate, long long ldg, const void* up, long long ldu, int dtype, void* out, long long ldo,
                     bool out_fp32, long long rows, int F, cudaStream_t stream);

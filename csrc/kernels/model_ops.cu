@@ -64,17 +64,20 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict_
 }
 
 // dx = rstd * (w*dy - x * rstd^2 * mean(w*dy*x)); per-row-chunk partial dw written to dw_part[chunk, D].
-constexpr int kNormBwdRows = 64;  // rows per CTA for the dw partial
+// Rows per CTA: kNormBwdRowsMax for long inputs (few, large partial-sum chunks), fewer for short ones so that the grid
+// still covers the machine several times over (a CTA walks its rows one after the other).
+constexpr int kNormBwdRowsMax = 64;
+constexpr int kNormBwdRowsMin = 8;
 template <typename T, typename TW>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, const T* __restrict__ dy,
                    long long lddy, const float* __restrict__ rstd, T* __restrict__ dx, long long lddx, int rows, int D,
-                   float* __restrict__ dw_part) {
+                   float* __restrict__ dw_part, int rows_per_cta) {
   __shared__ float red[4];
   extern __shared__ float dw_acc[];  // [D]
   for (int i = threadIdx.x; i < D; i += kNormThreads) dw_acc[i] = 0.f;
-  const long long r0 = static_cast<long long>(blockIdx.x) * kNormBwdRows;
-  const long long r1 = r0 + kNormBwdRows < rows ? r0 + kNormBwdRows : rows;
+  const long long r0 = static_cast<long long>(blockIdx.x) * rows_per_cta;
+  const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
   for (long long row = r0; row < r1; ++row) {
     const T* xr = x + row * ldx;
     const T* gr = dy + row * lddy;
@@ -148,7 +151,8 @@ rmsnorm_fwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, cons
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
                         const __nv_bfloat16* __restrict__ dy, long long lddy, const float* __restrict__ rstd,
-                        __nv_bfloat16* __restrict__ dx, long long lddx, int rows, int D, float* __restrict__ dw_part) {
+                        __nv_bfloat16* __restrict__ dx, long long lddx, int rows, int D, float* __restrict__ dw_part,
+                        int rows_per_cta) {
   __shared__ float red[4];
   const int n8 = D / 8;
   float dwacc[kNormVecMax][8];
@@ -168,8 +172,8 @@ rmsnorm_bwd_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, cons
       dwacc[v][2 * j + 1] = 0.f;
     }
   }
-  const long long r0 = static_cast<long long>(blockIdx.x) * kNormBwdRows;
-  const long long r1 = r0 + kNormBwdRows < rows ? r0 + kNormBwdRows : rows;
+  const long long r0 = static_cast<long long>(blockIdx.x) * rows_per_cta;
+  const long long r1 = r0 + rows_per_cta < rows ? r0 + rows_per_cta : rows;
   for (long long row = r0; row < r1; ++row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + row * lddy);
@@ -647,19 +651,31 @@ void rmsnorm_forward(const void* x, long long ldx, int x_dtype, const void* w, i
   });
 }
 
-int rmsnorm_bwd_chunks(long long rows) { return static_cast<int>((rows + kNormBwdRows - 1) / kNormBwdRows); }
+int rmsnorm_bwd_rows_per_cta(long long rows) {
+  const long long target_ctas = 148LL * 8;
+  long long r = (rows + target_ctas - 1) / target_ctas;
+  if (r < kNormBwdRowsMin) r = kNormBwdRowsMin;
+  if (r > kNormBwdRowsMax) r = kNormBwdRowsMax;
+  return static_cast<int>(r);
+}
+
+int rmsnorm_bwd_chunks(long long rows, int rows_per_cta) {
+  if (rows_per_cta <= 0) rows_per_cta = rmsnorm_bwd_rows_per_cta(rows);
+  return static_cast<int>((rows + rows_per_cta - 1) / rows_per_cta);
+}
 
 void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, const void* dy,
                       long long lddy, const float* rstd, void* dx, long long lddx, long long rows, int D,
-                      float* dw_part, void* dw, cudaStream_t stream) {
+                      float* dw_part, void* dw, cudaStream_t stream, int rows_per_cta) {
   if (rows <= 0) return;
-  const int chunks = rmsnorm_bwd_chunks(rows);
+  if (rows_per_cta <= 0) rows_per_cta = rmsnorm_bwd_rows_per_cta(rows);
+  const int chunks = rmsnorm_bwd_chunks(rows, rows_per_cta);
   if (x_dtype == 1 && w_dtype == 1 && bf16_vec_ok(x, ldx, D) && bf16_vec_ok(dy, lddy, D) && bf16_vec_ok(dx, lddx, D) &&
       bf16_vec_ok(w, 8, D)) {
     rmsnorm_bwd_bf16_kernel<<<chunks, kNormThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
         static_cast<const __nv_bfloat16*>(dy), lddy, rstd, static_cast<__nv_bfloat16*>(dx), lddx,
-        static_cast<int>(rows), D, dw_part);
+        static_cast<int>(rows), D, dw_part, rows_per_cta);
     colsum_kernel<__nv_bfloat16><<<(D + 255) / 256, 256, 0, stream>>>(dw_part, chunks, D, static_cast<__nv_bfloat16*>(dw));
     return;
   }
@@ -672,7 +688,7 @@ void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, 
       k<<<chunks, kNormThreads, D * sizeof(float), stream>>>(static_cast<const TX*>(x), ldx, static_cast<const TW*>(w),
                                                             static_cast<const TX*>(dy), lddy, rstd,
                                                             static_cast<TX*>(dx), lddx, static_cast<int>(rows), D,
-                                                            dw_part);
+                                                            dw_part, rows_per_cta);
       colsum_kernel<TW><<<(D + 255) / 256, 256, 0, stream>>>(dw_part, chunks, D, static_cast<TW*>(dw));
     });
   });

@@ -14,6 +14,7 @@ namespace {
 static __device__ __align__(256) float g_noalloc_scratch[RLK_NOALLOC_SCRATCH_FLOATS];
 
 constexpr int kMaxDevices = 64;
+constexpr int kRowsPerCta = 64;  // fixed here (the regular entry point adapts it to the row count): scratch need = ceil(rows / 64) * dim
 float* g_scratch_ptr[kMaxDevices] = {};
 std::mutex g_setup_mutex;
 thread_local std::string g_last_error;
@@ -44,7 +45,7 @@ int scratch_for_current_device(float** out) {
 
 extern "C" long long rlk_rmsnorm_backward_noalloc_scratch_floats(long long rows, int dim) {
   if (rows <= 0 || dim <= 0) return 0;
-  return static_cast<long long>(rlk::rmsnorm_bwd_chunks(rows)) * dim;
+  return static_cast<long long>(rlk::rmsnorm_bwd_chunks(rows, kRowsPerCta)) * dim;
 }
 
 extern "C" const char* rlk_noalloc_last_error(void) { return g_last_error.c_str(); }
@@ -73,7 +74,8 @@ extern "C" int rlk_rmsnorm_backward_noalloc(const void* x, const void* weight, c
   // Drop a launch error that an earlier, unrelated call left behind, so that what is read after the launches below
   // belongs to them; then read AND clear the result, so that a failure here is not blamed on the host's next call.
   (void)cudaGetLastError();
-  rlk::rmsnorm_backward(x, ld, x_dtype, weight, w_dtype, dy, ld, rstd, dx, ld, rows, dim, scratch, dweight, stream);
+  rlk::rmsnorm_backward(x, ld, x_dtype, weight, w_dtype, dy, ld, rstd, dx, ld, rows, dim, scratch, dweight, stream,
+                        kRowsPerCta);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     g_last_error = std::string("launch failed: ") + cudaGetErrorString(e);

@@ -233,12 +233,20 @@ class _FusedAttentionBlockCP(torch.autograd.Function):
 
 class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
-                 activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192) -> None:
+                 activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192,
+                 expert_shard: Optional[Tuple[int, int]] = None) -> None:
         """``activation_checkpointing``: ``True`` recomputes every layer in the backward pass, ``False`` keeps every
         layer's activations, ``"auto"`` (default) keeps as many trailing layers as the free device memory allows at the
-        first training forward and recomputes the rest (``plan_checkpointing``)."""
+        first training forward and recomputes the rest (``plan_checkpointing``).
+
+        ``expert_shard = (rank, world)`` (mixture-of-experts models): this instance stores only experts
+        ``[rank * E / world, (rank + 1) * E / world)`` of every layer; the router still scores all ``E`` experts and
+        ``self.moe_op`` must be set to an expert-parallel operator (``rl_engine.parallel.expert_parallel``) that sends
+        every token to the ranks owning its experts.  All other parameters are replicated."""
         super().__init__()
         self.cfg = cfg
+        self.expert_shard = expert_shard
+        self.moe_op = None  # None: the single-GPU fused MoE from the registry
         self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)
         # Optional ``callable(layer_index)``: while it is set, every training forward registers gradient hooks that
         # call it from inside backward when the backward pass has left layer ``layer_index`` (``num_layers`` = the
@@ -249,13 +257,20 @@ class LlamaModel(nn.Module):
         qkv_rows = cfg.q_dim + 2 * cfg.kv_dim
         shapes: List[Tuple[str, Tuple[int, ...]]] = [("embed", (cfg.vocab_size, h))]
         e, fe = cfg.num_experts, cfg.moe_ffn_size
+        e_local = e
+        if expert_shard is not None:
+            shard_rank, shard_world = expert_shard
+            if not e or e % shard_world or not 0 <= shard_rank < shard_world:
+                raise ValueError(f"expert_shard={expert_shard} does not divide the {e} experts of this model")
+            e_local = e // shard_world
         for i in range(cfg.num_layers):
             shapes += [(f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h)), (f"l{i}.wo", (h, cfg.q_dim))]
             if cfg.qk_norm:
                 shapes += [(f"l{i}.q_norm", (cfg.head_dim,)), (f"l{i}.k_norm", (cfg.head_dim,))]
             shapes += [(f"l{i}.mlp_norm", (h,))]
             if e:  # mixture of experts: router + per-expert [gate | up] and down projections, stacked by expert
-                shapes += [(f"l{i}.router", (e, h)), (f"l{i}.w_gate_up", (e * 2 * fe, h)), (f"l{i}.w_down", (e * h, fe))]
+                shapes += [(f"l{i}.router", (e, h)), (f"l{i}.w_gate_up", (e_local * 2 * fe, h)),
+                           (f"l{i}.w_down", (e_local * h, fe))]
             else:
                 shapes += [(f"l{i}.w_gate_up", (2 * f, h)), (f"l{i}.w_down", (h, f))]
         shapes += [("final_norm", (h,)), ("lm_head", (cfg.vocab_size, h))]
@@ -403,7 +418,10 @@ class LlamaModel(nn.Module):
             from rl_engine.kernels.registry import kernel_registry
 
             h = rms_norm(x, p("mlp_norm"), cfg.rms_eps)
-            return x + kernel_registry.get_op("moe")(h, p("router"), p("w_gate_up"), p("w_down"), cfg.experts_per_token)
+            if self.expert_shard is not None and self.moe_op is None:
+                raise RuntimeError("a model built with expert_shard needs model.moe_op (an expert-parallel MoE operator)")
+            moe = self.moe_op if self.moe_op is not None else kernel_registry.get_op("moe")
+            return x + moe(h, p("router"), p("w_gate_up"), p("w_down"), cfg.experts_per_token)
         if lean:
             return x + swiglu_linear(norm_linear(x, p("mlp_norm"), p("w_gate_up"), cfg.rms_eps), p("w_down"))
         gu = linear(rms_norm(x, p("mlp_norm"), cfg.rms_eps), p("w_gate_up"))

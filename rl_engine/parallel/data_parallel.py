@@ -66,7 +66,7 @@ class ShardedFusedAdamW:
         self.model, self.mem, self.params, self.grads = model, mem, params, grads
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         n = model.flat.numel()
-        ranges, self.ready_at = layer_buckets(model, layers_per_bucket)
+        ranges, self.ready_at, self.local_ranges = self._plan_buckets(model, layers_per_bucket)
         # the symmetric buffers are padded to a multiple of 8 elements; the pad belongs to the last bucket
         ranges[-1] = (ranges[-1][0], params.local.numel())
         self.numel = n
@@ -92,6 +92,12 @@ class ShardedFusedAdamW:
         self._launched: List[bool] = [False] * len(self.slices)
         self._side_used = False
         self._armed = False
+
+    def _plan_buckets(self, model, layers_per_bucket):
+        """``(ranges, ready_at, local_ranges)``: the buckets of the cross-rank exchange (see ``layer_buckets``) and the
+        ranges of parameters that exist only on this rank and are stepped locally (none for a replicated model)."""
+        ranges, ready_at = layer_buckets(model, layers_per_bucket)
+        return ranges, ready_at, []
 
     def _gather_local(self, flat: torch.Tensor) -> torch.Tensor:
         return torch.cat([flat[lo:hi] for lo, hi, _ in self.slices]) if self.slices else flat[:0]
@@ -146,10 +152,14 @@ class ShardedFusedAdamW:
                 self._launch_bucket(b, 0, 0)
         if self._side_used:
             main.wait_stream(self._side)
+        self._step_local_ranges()
         self.steps += 1
         self._armed = False
         self._launched = [False] * len(self.slices)
         self.mem.barrier()  # every rank's parameter slices have landed everywhere
+
+    def _step_local_ranges(self) -> None:
+        """Hook for parameters that are not exchanged (see ``_plan_buckets``)."""
 
     # -- checkpoint ---------------------------------------------------------------------------------------
     def state_dict(self):
@@ -182,6 +192,8 @@ class ShardedFusedAdamW:
 class ShardedGRPOTrainer(GRPOTrainer):
     """``GRPOTrainer`` whose parameters/gradients live in symmetric memory and whose optimizer is fused."""
 
+    optimizer_class = ShardedFusedAdamW
+
     def __init__(self, model: LlamaModel, *, group=None, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
                  micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4) -> None:
@@ -197,9 +209,9 @@ class ShardedGRPOTrainer(GRPOTrainer):
         self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
         self.micro_group = micro_group
         self._micro_choice = {}
-        self.opt = ShardedFusedAdamW(model, self.mem, params, grads, lr=lr, weight_decay=weight_decay,
-                                     master_weights=master_weights, layers_per_bucket=layers_per_bucket,
-                                     overlap=overlap)
+        self.opt = self.optimizer_class(model, self.mem, params, grads, lr=lr, weight_decay=weight_decay,
+                                        master_weights=master_weights, layers_per_bucket=layers_per_bucket,
+                                        overlap=overlap)
         self._slice: Optional[slice] = None
         self.mem.barrier()
 

@@ -201,3 +201,104 @@ class ExpertParallelMoE:
         plan = ep.plan(idx)
         out = _EPExpertFFN.apply(x2, weights, local_gate_up, local_down, plan, ep)
         return out.reshape(x.shape)
+
+
+# ---------------------------------------------------------------------------------- whole-model training
+def moe_parameter_ranges(model):
+    """Splits the flat parameter vector of a mixture-of-experts ``LlamaModel`` into replicated and expert parts.
+
+    Returns ``(dense, ready_at, experts)``: ``dense`` are the ranges of the replicated parameters in flat order (the
+    embedding with layer 0's attention / norms / router, then every further layer's, then final norm + LM head),
+    ``ready_at[i]`` the layer whose backward completes range ``i`` (none for range 0), ``experts`` the per-layer ranges
+    of the stacked expert weights (``w_gate_up`` and ``w_down`` are adjacent)."""
+    off, cfg = model._offsets, model.cfg
+    total = model.flat.numel()
+    dense, experts, ready_at = [], [], {}
+    start = 0
+    for i in range(cfg.num_layers):
+        e0 = off[f"l{i}.w_gate_up"]
+        e1 = off[f"l{i + 1}.attn_norm"] if i + 1 < cfg.num_layers else off["final_norm"]
+        dense.append((start, e0))
+        if i > 0:
+            ready_at[len(dense) - 1] = i
+        experts.append((e0, e1))
+        start = e1
+    dense.append((start, total))
+    ready_at[len(dense) - 1] = cfg.num_layers
+    return dense, ready_at, experts
+
+
+def _expert_parallel_optimizer():
+    from rl_engine.parallel.data_parallel import ShardedFusedAdamW
+
+    class ExpertParallelAdamW(ShardedFusedAdamW):
+        """Replicated parameters: fused reduce-scatter + AdamW + all-gather over the ranks (state sharded 1 / W).
+        Expert parameters: they exist only here and their gradients already hold every rank's tokens (the dispatch
+        brought them), so they are stepped locally by the fused AdamW kernel with fp32 masters kept as 16-bit
+        residuals; the loss is the mean over the ranks, hence the 1 / W on their gradients."""
+
+        def _plan_buckets(self, model, layers_per_bucket):
+            dense, ready_at, experts = moe_parameter_ranges(model)
+            return dense, ready_at, experts
+
+        def _ensure_local_state(self) -> None:
+            if getattr(self, "_local", None) is not None:
+                return
+            dev = self.params.local.device
+            self._local = []
+            for lo, hi in self.local_ranges:
+                n = hi - lo
+                self._local.append((lo, hi, torch.zeros(n, dtype=torch.float32, device=dev),
+                                    torch.zeros(n, dtype=torch.float32, device=dev),
+                                    torch.zeros(n, dtype=torch.int16, device=dev) if self.master is not None else None))
+
+        def _step_local_ranges(self) -> None:
+            self._ensure_local_state()
+            ext = require_ext()
+            p, g = self.params.local, self.grads.local
+            for lo, hi, m, v, residual in self._local:
+                ext.adamw(p[lo:hi], residual, g[lo:hi], m, v, self.lr, self.betas[0], self.betas[1], self.eps,
+                          self.weight_decay, self.steps + 1, float(self.grad_scale) / self.mem.world)
+
+        def state_dict(self):
+            state = super().state_dict()
+            self._ensure_local_state()
+            state["expert_m"] = [m for _lo, _hi, m, _v, _r in self._local]
+            state["expert_v"] = [v for _lo, _hi, _m, v, _r in self._local]
+            state["expert_residual"] = [r for *_x, r in self._local]
+            return state
+
+        def load_state_dict(self, state) -> None:
+            super().load_state_dict(state)
+            self._ensure_local_state()
+            for (_lo, _hi, m, v, r), sm, sv, sr in zip(self._local, state["expert_m"], state["expert_v"],
+                                                        state["expert_residual"]):
+                m.copy_(sm)
+                v.copy_(sv)
+                if r is not None:
+                    r.copy_(sr) if sr is not None else r.zero_()
+
+    return ExpertParallelAdamW
+
+
+def expert_parallel_trainer(model, *, max_tokens: int, group=None, **kw):
+    """``ShardedGRPOTrainer`` for a mixture-of-experts ``LlamaModel`` built with ``expert_shard=(rank, world)``: every
+    rank trains on its own completions (data parallel), every MoE layer sends its tokens to the ranks that own the routed
+    experts (``ExpertParallelMoE``), and the optimiser treats replicated and expert parameters as ``ExpertParallelAdamW``
+    describes.  ``max_tokens``: the largest number of packed tokens one forward pass of a rank may hold."""
+    from rl_engine.parallel.data_parallel import ShardedGRPOTrainer
+
+    cfg = model.cfg
+    if not cfg.num_experts or model.expert_shard is None:
+        raise ValueError("expert_parallel_trainer needs a mixture-of-experts model built with expert_shard=(rank, world)")
+    optimizer = _expert_parallel_optimizer()
+
+    class ExpertParallelGRPOTrainer(ShardedGRPOTrainer):
+        optimizer_class = optimizer
+
+    trainer = ExpertParallelGRPOTrainer(model, group=group, **kw)
+    ctx = ExpertParallelContext(cfg.hidden_size, cfg.num_experts, cfg.experts_per_token, max_tokens=max_tokens,
+                                group=group, device=model.flat.device)
+    model.moe_op = ExpertParallelMoE(ctx)
+    trainer.expert_context = ctx
+    return trainer

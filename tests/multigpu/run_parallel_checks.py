@@ -335,6 +335,72 @@ def main() -> None:
     check_device_errors(local)
     print(f"[{rank}] OK context-parallel attention", flush=True)
 
+    # ---- mixture-of-experts model: data parallel + expert parallel GRPO step vs the single-GPU model with all experts ----
+    from rl_engine.parallel.expert_parallel import expert_parallel_trainer
+
+    ecfg = ModelConfig("ep-model", vocab_size=2048, hidden_size=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=128,
+                       ffn_size=512, rms_eps=1e-6, rope_theta=1e6, num_experts=4 * world, experts_per_token=2,
+                       moe_ffn_size=128, qk_norm=True)
+    full_moe = LlamaModel(ecfg, dtype=torch.bfloat16, device=dev, seed=55)
+    shard_moe = LlamaModel(ecfg, dtype=torch.bfloat16, device=dev, seed=55, expert_shard=(rank, world))
+    el_m, fe_m, hm = ecfg.num_experts // world, ecfg.moe_ffn_size, ecfg.hidden_size
+    with torch.no_grad():  # replicated parameters from the full model, experts: this rank's slice
+        for name, dst in shard_moe.named_views().items():
+            src = full_moe.view(name)
+            if name.endswith("w_gate_up"):
+                src = src.view(ecfg.num_experts, 2 * fe_m, hm)[rank * el_m:(rank + 1) * el_m].reshape(-1, hm)
+            elif name.endswith("w_down"):
+                src = src.view(ecfg.num_experts, hm, fe_m)[rank * el_m:(rank + 1) * el_m].reshape(-1, fe_m)
+            dst.copy_(src)
+    per_rank_m = 2
+    hb_m = synthetic_batch(ecfg.vocab_size, prompt_len=128, group=per_rank_m * world, completion_len=128, seed=6)
+    full_tr = GRPOTrainer(full_moe, lr=1e-3, micro_group=None)
+    with torch.no_grad():
+        cur_m = full_tr.policy_logps(hb_m.to(dev)).float()
+    gm = torch.Generator(device=dev).manual_seed(73)
+    hb_m.old_logps = (cur_m + 0.01 * torch.randn(cur_m.shape, device=dev, generator=gm)).cpu()
+    hb_m.ref_logps = (cur_m + 0.01 * torch.randn(cur_m.shape, device=dev, generator=gm)).cpu()
+    db_m = hb_m.to(dev)
+    start_m = {n: t.detach().clone() for n, t in shard_moe.named_views().items()}
+    ep_tr = expert_parallel_trainer(shard_moe, max_tokens=128 + per_rank_m * 128, lr=1e-3, micro_group=None)
+    sl_m = slice(rank * per_rank_m, (rank + 1) * per_rank_m)
+    ep_tr.set_group_slice(sl_m)
+    local_m = GRPOBatch(db_m.prompt_ids, db_m.completion_ids[sl_m].contiguous(), db_m.rewards, db_m.old_logps[sl_m].contiguous(),
+                        db_m.ref_logps[sl_m].contiguous(), db_m.completion_mask[sl_m].contiguous())
+    with torch.no_grad():
+        lp_ep = ep_tr.policy_logps(local_m).float()
+    assert torch.allclose(lp_ep, cur_m[sl_m], atol=5e-2, rtol=5e-2), (lp_ep - cur_m[sl_m]).abs().max()
+    loss_full = float(full_tr.step_device(db_m))
+    l_ep = ep_tr.step_device(local_m).float().reshape(1)
+    dist.all_reduce(l_ep, op=dist.ReduceOp.AVG)
+    ep_tr.check()
+    ep_tr.expert_context.mem.check()
+    check_device_errors(local)
+    assert abs(float(l_ep) - loss_full) < 2e-2 * max(1.0, abs(loss_full)), (float(l_ep), loss_full)
+
+    def update_matches(name, got_after, want_after, got_before):
+        d_got, d_want = got_after.float() - got_before.float(), want_after.float() - got_before.float()
+        moved_ = d_want.abs() > 0
+        if moved_.float().mean() < 0.2:
+            return  # a parameter that hardly receives gradient (e.g. rows of experts no token was routed to)
+        rel_ = ((d_got - d_want).abs().mean() / d_want.abs().mean().clamp_min(1e-12)).item()
+        assert rel_ < 0.35, f"expert-parallel step: update of {name} differs from the single-GPU step ({rel_:.3f})"
+
+    for name, after in shard_moe.named_views().items():
+        want = full_moe.view(name).detach()
+        if name.endswith("w_gate_up"):
+            want = want.view(ecfg.num_experts, 2 * fe_m, hm)[rank * el_m:(rank + 1) * el_m].reshape(-1, hm)
+        elif name.endswith("w_down"):
+            want = want.view(ecfg.num_experts, hm, fe_m)[rank * el_m:(rank + 1) * el_m].reshape(-1, fe_m)
+        update_matches(name, after.detach(), want, start_m[name])
+    dense_names = [n for n in shard_moe.named_views() if not n.endswith(("w_gate_up", "w_down"))]
+    blob = torch.cat([shard_moe.view(n).detach().reshape(-1) for n in dense_names])
+    every = [torch.empty_like(blob) for _ in range(world)]
+    dist.all_gather(every, blob)
+    assert all(torch.equal(every[0], e_) for e_ in every), "expert parallel: replicated parameters differ between ranks"
+    ep_tr.mem.close()
+    print(f"[{rank}] OK expert-parallel MoE GRPO step == single-GPU step (loss {float(l_ep):.4f} vs {loss_full:.4f})", flush=True)
+
     # ---- long-context GRPO step: sequences sharded over the ranks (context parallel) vs the single-GPU trainer ----
     from rl_engine.parallel.long_context import ContextParallelGRPOTrainer
 

@@ -120,3 +120,27 @@ def test_layer_grad_hook_reports_layers_from_last_to_first():
     trainer.step_device(batch)
     assert seen == [3, 2, 1, 0]
     assert model.layer_grad_hook is None
+
+
+def test_moe_parameter_ranges_split_replicated_and_expert_parameters():
+    from rl_engine.parallel.expert_parallel import moe_parameter_ranges
+
+    cfg = ModelConfig(name="tiny-moe", vocab_size=256, hidden_size=32, num_layers=3, num_heads=2, num_kv_heads=1,
+                      head_dim=16, ffn_size=48, num_experts=8, experts_per_token=2, moe_ffn_size=16, qk_norm=True)
+    full = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=0, max_positions=32)
+    shard = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=0, max_positions=32, expert_shard=(1, 4))
+    assert shard.view("l0.w_gate_up").shape[0] == full.view("l0.w_gate_up").shape[0] // 4
+    assert shard.view("l0.router").shape == full.view("l0.router").shape          # the router scores all experts
+    dense, ready_at, experts = moe_parameter_ranges(shard)
+    pieces = sorted(dense + experts)
+    assert pieces[0][0] == 0 and pieces[-1][1] == shard.flat.numel()
+    assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))                  # together they tile the flat vector
+    off = shard._offsets
+    assert experts[1] == (off["l1.w_gate_up"], off["l2.attn_norm"]) and dense[1] == (off["l1.attn_norm"], off["l1.w_gate_up"])
+    assert dense[-1][0] == off["final_norm"] and ready_at == {1: 1, 2: 2, 3: 3}
+    import pytest
+
+    with pytest.raises(ValueError):
+        LlamaModel(cfg, dtype=torch.float32, device="cpu", expert_shard=(0, 3))
+    with pytest.raises(RuntimeError, match="moe_op"):
+        shard._ffn(torch.zeros(4, 32), 0, False)

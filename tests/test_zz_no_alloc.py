@@ -35,6 +35,12 @@ def _lib():
 CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 
+def _close(got, want):
+    scale = want.float().abs().max().item() + 1e-6
+    tol = 2e-2 if got.dtype in (torch.bfloat16, torch.float16) else 1e-5
+    return (got.float() - want.float()).abs().max().item() / scale < tol
+
+
 def _call(lib, x, w, dy, rstd, dx, dw):
     stream = torch.cuda.current_stream().cuda_stream
     return lib.rlk_rmsnorm_backward_noalloc(
@@ -61,10 +67,11 @@ def test_noalloc_matches_regular_entry_point_twice(dtype):
         rc = _call(lib, x, w, dy, rstd, dx, dw)
         assert rc == 0, lib.rlk_noalloc_last_error()
         torch.cuda.synchronize()
-        # same kernels, same summation order: the results agree bitwise, which is well inside the
-        # tolerance the other RMSNorm tests use
+        # same kernels: dx is computed row by row and agrees bitwise; the weight gradient is a sum over rows that the
+        # two entry points cut into chunks of different length, so it agrees to rounding (the tolerance of the other
+        # RMSNorm tests)
         assert torch.equal(dx, want_dx)
-        assert torch.equal(dw, want_dw)
+        assert _close(dw, want_dw)
 
 
 @pytest.mark.parametrize("case", ["fp16", "fp32_wide_rows", "mixed_dtypes", "row_pitch"])
@@ -94,7 +101,7 @@ def test_noalloc_other_paths_match_regular_entry_point(case):
         assert rc == 0, lib.rlk_noalloc_last_error()
         torch.cuda.synchronize()
         assert torch.equal(dx, want_dx)
-        assert torch.equal(dw, want_dw)
+        assert _close(dw, want_dw)
 
 
 def test_noalloc_rejects_oversized_and_bad_arguments():
