@@ -340,7 +340,58 @@ def case_sampler():
     logits = rand((256, 151936)).float()
     ms = timed(lambda: sample_topk_topp(logits, top_k=50, top_p=0.9, temperature=0.7, seed=1, offset=0))
     return {"flops": 0.0, "bytes": 4.0 * 256 * 151936, "ms": ms, "shape": [256, 151936],
-            "note": "bytes = one pass over the logits; the kernel reads each row twice (histogram, gather)"}
+            "note": "bytes = one pass over the logits; the kernel reads each row twice (thread maxima from DRAM, gather "
+                    "from L2)"}
+
+
+def case_adamw():
+    """Fused AdamW on bf16 parameters with fp32 masters kept as 16-bit residuals (one GPU's optimiser step)."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    n = 1 << 28  # 0.27 G parameters: 0.5 GB of weights, 3.8 GB touched per step
+    p, g = rand((n,), 0.02), rand((n,), 1.0, 1)
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    residual = torch.zeros(n, dtype=torch.int16, device="cuda")
+    step = [0]
+
+    def run():
+        step[0] += 1
+        require_ext().adamw(p, residual, g, m, v, 1e-6, 0.9, 0.95, 1e-8, 0.0, step[0], 1.0)
+
+    ms = timed(run)
+    # read p, g, residual (2 B each) and m, v (4 B each); write p, residual, m, v
+    return {"flops": 0.0, "bytes": n * (2.0 + 2 + 2 + 4 + 4 + 2 + 2 + 4 + 4), "ms": ms, "shape": [n],
+            "note": "bf16 parameter + int16 residual = exact fp32 master; bytes = all reads and writes"}
+
+
+def case_weight_digest():
+    """One-pass integrity digest of a weight tensor (64-bit position-weighted sum)."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    n = 1 << 29  # 1 GB of bf16
+    t = rand((n,), 0.02)
+    out = torch.zeros(4, dtype=torch.int64, device="cuda")
+    ms = timed(lambda: require_ext().weight_digest(t, out, 0))
+    return {"flops": 0.0, "bytes": 2.0 * n, "ms": ms, "shape": [n]}
+
+
+def case_ratio_kl():
+    """Policy and reference logits streamed side by side (ratio / KL front end)."""
+    from rl_engine.kernels.registry import kernel_registry
+
+    b, t, v = 16, 512, 131072
+    pol, ref = rand((b, t, v)), rand((b, t, v), 1.0, 1)
+    ids = torch.randint(0, v, (b, t), device="cuda")
+    mask = torch.ones(b, t, dtype=torch.bool, device="cuda")
+    old = torch.zeros(b, t, device="cuda")
+    op = kernel_registry.get_op("ratio_kl")
+
+    def run():
+        with torch.no_grad():
+            op(pol, ref, ids, mask, old)
+
+    ms = timed(run)
+    return {"flops": 0.0, "bytes": 2.0 * 2 * b * t * v, "ms": ms, "shape": [b, t, v]}
 
 
 CASES = {name[5:]: fn for name, fn in globals().items() if name.startswith("case_")}
@@ -348,10 +399,14 @@ CASES = {name[5:]: fn for name, fn in globals().items() if name.startswith("case
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", choices=sorted(CASES) + ["all"], default="all")
+    ap.add_argument("--kernel", default="all", help="one name, a comma-separated list, or 'all' of: " + ", ".join(sorted(CASES)))
     args = ap.parse_args()
+    names = sorted(CASES) if args.kernel == "all" else [k.strip() for k in args.kernel.split(",") if k.strip()]
+    unknown = [k for k in names if k not in CASES]
+    if unknown:
+        ap.error(f"unknown kernels {unknown}; choose from {sorted(CASES)}")
     pk = peaks()
-    for name in (sorted(CASES) if args.kernel == "all" else [args.kernel]):
+    for name in names:
         r = CASES[name]()
         line = {"kernel": name, "ms": round(r["ms"], 4), "shape": r["shape"], "peaks": pk["source"]}
         if r["flops"]:

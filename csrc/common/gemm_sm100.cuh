@@ -249,16 +249,19 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
+      // Once a bounded wait has given up (abort flag), nothing more is issued: no further loads for the remaining
+      // items, so the teardown only has to outlast the copies that were already in flight.
+      for (int id = blockIdx.x; id < p.num_items && !*abort_flag; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
         if (item_skipped(p, w.m_tile)) continue;
         const ItemGeometry geo = item_geometry(p, w.m_tile);
         const int m0 = geo.a_m0;
         if (p.a_ready != nullptr) wait_a_ready(p, w.m_tile, abort_flag, err, kernel_id);
-        for (int nt = w.n_begin; nt < w.n_end; ++nt) {
+        for (int nt = w.n_begin; nt < w.n_end && !*abort_flag; ++nt) {
           const int n0 = nt * BN;
           for (int kb = 0; kb < geo.k_blocks; ++kb) {
             mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, err, kernel_id, 1);
+            if (*abort_flag) break;
             uint8_t* sa = smem + stage * L::kStageBytes;
             uint8_t* sb = sa + L::kABytes;
             mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
@@ -292,16 +295,18 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
-      for (int id = blockIdx.x; id < p.num_items; id += gridDim.x) {
+      for (int id = blockIdx.x; id < p.num_items && !*abort_flag; id += gridDim.x) {
         const WorkItem w = decode_item(p, id);
         if (item_skipped(p, w.m_tile)) continue;
         const int item_k_blocks = item_geometry(p, w.m_tile).k_blocks;
-        for (int nt = w.n_begin; nt < w.n_end; ++nt) {
+        for (int nt = w.n_begin; nt < w.n_end && !*abort_flag; ++nt) {
           mbar_wait(&tmem_empty[buf], buf_phase ^ 1, abort_flag, err, kernel_id, 2);
+          if (*abort_flag) break;  // no MMAs on operands that may never have arrived
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           for (int kb = 0; kb < item_k_blocks; ++kb) {
             mbar_wait(&full_bar[stage], phase, abort_flag, err, kernel_id, 3);
+            if (*abort_flag) break;
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
             const uint32_t sb = sa + L::kABytes;

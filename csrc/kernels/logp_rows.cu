@@ -79,6 +79,27 @@ __device__ __forceinline__ MS block_merge(MS v, MS* smem) {
   return r;
 }
 
+// One 16-byte vector into the running (max, sum): the vector's maximum is found first, so the running sum is rescaled
+// at most once per vector (rarely, after the first few vectors) and every element costs one fused multiply-add and one
+// exp2 -- no compare / select / branch per element, which is what limited this kernel before the tensor of exps did.
+template <int N>
+__device__ __forceinline__ void ms_push_vec(MS& a, const float (&z)[N]) {
+  float top = z[0];
+#pragma unroll
+  for (int j = 1; j < N; ++j) top = fmaxf(top, z[j]);
+  const float y = top * kLog2e;
+  if (y > a.m2) {
+    a.s *= fast_exp2(a.m2 - y);  // exp2(-inf) = 0 on the first vector
+    a.m2 = y;
+  }
+  if (a.m2 == -INFINITY) return;  // nothing but -inf so far: the sum stays 0
+  const float neg_m = -a.m2;
+  float part = 0.f;
+#pragma unroll
+  for (int j = 0; j < N; ++j) part += fast_exp2(fmaf(z[j], kLog2e, neg_m));
+  a.s += part;
+}
+
 template <typename T>
 __device__ __forceinline__ MS stream_row(const T* __restrict__ row, int V) {
   constexpr int kVec = 16 / sizeof(T);
@@ -89,15 +110,66 @@ __device__ __forceinline__ MS stream_row(const T* __restrict__ row, int V) {
   for (int i = threadIdx.x; i < head; i += kThreads) ms_push(acc, to_f(row[i]));
   const int body = (V - head) / kVec;
   const uint4* p = reinterpret_cast<const uint4*>(row + head);
-#pragma unroll 4
-  for (int i = threadIdx.x; i < body; i += kThreads) {
+  int i = threadIdx.x;
+  // two vectors per iteration: both loads are issued before either is consumed
+  for (; i + kThreads < body; i += 2 * kThreads) {
+    const uint4 q0 = __ldcs(p + i), q1 = __ldcs(p + i + kThreads);
+    const T* e0 = reinterpret_cast<const T*>(&q0);
+    const T* e1 = reinterpret_cast<const T*>(&q1);
+    float z0[kVec], z1[kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      z0[j] = to_f(e0[j]);
+      z1[j] = to_f(e1[j]);
+    }
+    ms_push_vec(acc, z0);
+    ms_push_vec(acc, z1);
+  }
+  for (; i < body; i += kThreads) {
     const uint4 q = __ldcs(p + i);
     const T* e = reinterpret_cast<const T*>(&q);
+    float z[kVec];
 #pragma unroll
-    for (int j = 0; j < kVec; ++j) ms_push(acc, to_f(e[j]));
+    for (int j = 0; j < kVec; ++j) z[j] = to_f(e[j]);
+    ms_push_vec(acc, z);
   }
-  for (int i = head + body * kVec + threadIdx.x; i < V; i += kThreads) ms_push(acc, to_f(row[i]));
+  for (int t = head + body * kVec + threadIdx.x; t < V; t += kThreads) ms_push(acc, to_f(row[t]));
   return acc;
+}
+
+// Two rows of the same length streamed side by side (policy and reference logits): both rows' loads are in flight
+// together and each element is visited once.  Falls back to two separate sweeps if the rows are not both 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void stream_two_rows(const T* __restrict__ a, const T* __restrict__ b, int V, MS& acc_a,
+                                                MS& acc_b) {
+  constexpr int kVec = 16 / sizeof(T);
+  if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15u) != 0) {
+    acc_a = stream_row(a, V);
+    acc_b = stream_row(b, V);
+    return;
+  }
+  acc_a = MS{-INFINITY, 0.f};
+  acc_b = MS{-INFINITY, 0.f};
+  const int body = V / kVec;
+  const uint4* pa = reinterpret_cast<const uint4*>(a);
+  const uint4* pb = reinterpret_cast<const uint4*>(b);
+  for (int i = threadIdx.x; i < body; i += kThreads) {
+    const uint4 qa = __ldcs(pa + i), qb = __ldcs(pb + i);
+    const T* ea = reinterpret_cast<const T*>(&qa);
+    const T* eb = reinterpret_cast<const T*>(&qb);
+    float za[kVec], zb[kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) {
+      za[j] = to_f(ea[j]);
+      zb[j] = to_f(eb[j]);
+    }
+    ms_push_vec(acc_a, za);
+    ms_push_vec(acc_b, zb);
+  }
+  for (int t = body * kVec + threadIdx.x; t < V; t += kThreads) {
+    ms_push(acc_a, to_f(a[t]));
+    ms_push(acc_b, to_f(b[t]));
+  }
 }
 
 template <typename T>
@@ -181,9 +253,15 @@ __global__ void __launch_bounds__(kThreads) ratio_kl_fwd_kernel(const T* __restr
   }
   const T* prow = pol + row * ld_p;
   const T* rrow = ref ? ref + row * ld_r : nullptr;  // null: reference == policy (d = 0, kl = 0)
-  MS a = block_merge(stream_row(prow, V), red);
-  MS b = a;
-  if (rrow) b = block_merge(stream_row(rrow, V), red);
+  MS a, b;
+  if (rrow) {
+    stream_two_rows(prow, rrow, V, a, b);
+    a = block_merge(a, red);
+    b = block_merge(b, red);
+  } else {
+    a = block_merge(stream_row(prow, V), red);
+    b = a;
+  }
   if (threadIdx.x == 0) {
     long long t = ids[row];
     if (t < 0 || t >= V) {

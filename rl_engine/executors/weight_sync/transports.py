@@ -500,9 +500,14 @@ class FileBlobBridge(BridgeStateMachine):
 
     transport = "file"
 
-    def __init__(self, directory: str, *, source_worker="local-training", source_rank=0) -> None:
+    def __init__(self, directory: str, *, source_worker="local-training", source_rank=0,
+                 delete_on_release: bool = True) -> None:
+        """``delete_on_release``: ``release(update_id)`` on the publishing side removes the update's blob and manifest
+        from disk, so a released update can no longer be imported by anyone (the behaviour of the in-memory transports).
+        Checkpoints are never released, so their files stay."""
         super().__init__(source_worker=source_worker, source_rank=source_rank)
         self.directory = directory
+        self.delete_on_release = delete_on_release
         os.makedirs(directory, exist_ok=True)
 
     def _paths(self, update_id: str) -> Tuple[str, str]:
@@ -543,6 +548,12 @@ class FileBlobBridge(BridgeStateMachine):
 
     def _dispose(self, record: UpdateRecord) -> None:
         record.tensors.clear()
+        if self.delete_on_release and record.resources.get("blob_path"):  # only the publisher's record owns the files
+            for path in self._paths(record.manifest.update_id):
+                try:
+                    os.unlink(path)
+                except FileNotFoundError:
+                    pass
 
 
 def read_blob(block: Mapping[str, Any], manifest: WeightUpdateManifest) -> Dict[str, torch.Tensor]:

@@ -88,6 +88,33 @@ def test_profiler_timing_uses_warmup_then_median(monkeypatch):
     assert result == 4 and len(calls) == 5 and latency_ms >= 0.0 and std_ms is not None
 
 
+# ------------------------------------------------------------------------------ weight-sync benchmark modes
+@pytest.mark.parametrize("mode", ["shared-memory", "file"])
+def test_weight_sync_benchmark_cross_process_modes(mode):
+    """The benchmark's consumer-process modes are integration tests of the transports: a separate process attaches to
+    the published update, validates it against the manifest and acknowledges; after the publisher's release a fresh
+    import is refused."""
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    done = subprocess.run([sys.executable, "benchmark_weight_sync_bridge.py", "--mode", mode, "--cross-process", "--smoke"],
+                          cwd=os.path.join(ROOT, "benchmarks"), env=env, text=True, capture_output=True, check=False, timeout=600)
+    assert done.returncode == 0, done.stderr
+    row = json.loads([ln for ln in done.stdout.splitlines() if ln.startswith("{")][-1])
+    assert row["status"] == "pass" and row["cross_process"] is True and row["verified"] is True
+    assert row["after_release"] == "stale import refused" and row["consumer_version"] == 1 and row["tensors"] == 8
+
+
+def test_weight_sync_benchmark_in_process_and_blockers():
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for mode in ("local", "rollout-update", "runtime-blockers"):
+        done = subprocess.run([sys.executable, "benchmark_weight_sync_bridge.py", "--mode", mode, "--smoke"],
+                              cwd=os.path.join(ROOT, "benchmarks"), env=env, text=True, capture_output=True, check=False,
+                              timeout=600)
+        assert done.returncode == 0, done.stderr
+        row = json.loads([ln for ln in done.stdout.splitlines() if ln.startswith("{")][-1])
+        assert row["status"] == "pass", row
+    assert "multi-node" in row and row["multi-node"].startswith("blocked")
+
+
 # ------------------------------------------------------------------------------ fixture
 def test_synthetic_batch_fixture_contract():
     from rl_engine.testing import make_synthetic_rl_kernel_batch
