@@ -52,6 +52,9 @@ def parse_args():
     # dp: completions split over the ranks, fused ZeRO-1 step (default, fastest for an 8B model on 180 GB GPUs);
     # tp: tensor + sequence parallel layers and vocabulary-parallel LM head, every rank sees the whole group
     ap.add_argument("--parallelism", choices=["dp", "tp"], default="dp")
+    # data parallel only: "auto" / "on" split the shared prompt's forward/backward pass over the ranks, "off" runs it on every rank
+    ap.add_argument("--prompt-shard", choices=["auto", "on", "off"], default="auto")
+    ap.add_argument("--skip-ops", action="store_true", help="leave out the per-operator measurements after the step")
     # development switches; any use marks the run as not comparable
     ap.add_argument("--dev-layers", type=int, default=0)
     ap.add_argument("--dev-group", type=int, default=0)
@@ -384,7 +387,8 @@ def main() -> None:
     elif world > 1:
         from rl_engine.parallel.data_parallel import ShardedGRPOTrainer
 
-        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro)
+        shard = {"auto": "auto", "on": True, "off": False}[args.prompt_shard]
+        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro, shard_prompt=shard)
         parallelism = f"dp{world}-zero1-fused"
     else:
         trainer = GRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro)
@@ -482,6 +486,8 @@ def main() -> None:
             "master_weights": master,
             "l2": "inputs larger than L2 (16 GB of weights streamed every step); no explicit flush",
             "activation_memory": activation_note,
+            "prompt_pass": ("split over the ranks (zig-zag context parallel), keys / values gathered by peer stores"
+                            if getattr(trainer, "_prompt_shards", None) else "once per rank"),
             "peak_torch_allocated_gb": round(peak_allocated / 2**30, 1),
             "device_memory_in_use_gb": round((mem_total - mem_free) / 2**30, 1),
             "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group),
@@ -505,12 +511,14 @@ def main() -> None:
     timer = threading.Timer(OPS_DEADLINE_S, watchdog)
     timer.daemon = True
     timer.start()
-    if (args.dev_layers or args.dev_group) and os.environ.get("RLK_BENCH_OPS") != "1":
+    if args.skip_ops:
+        ops["skipped"] = "--skip-ops"
+    elif (args.dev_layers or args.dev_group) and os.environ.get("RLK_BENCH_OPS") != "1":
         ops["skipped"] = "development overrides in use"
     else:
         if hasattr(trainer, "mem"):
             torch.cuda.synchronize()
-            trainer.mem.close()
+            trainer.close() if hasattr(trainer, "close") else trainer.mem.close()
         del trainer, dev_batch, host, full
         model = tp_model = None  # noqa: F841 - drop the last references to the parameters
         import gc

@@ -119,7 +119,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                 const __grid_constant__ CUtensorMap tmap_v, const SeqDesc* __restrict__ seqs,
                 const int2* __restrict__ tiles,  // (sequence, first query row within the sequence)
                 int num_heads_q, int q_per_kv, int causal, float scale_log2e, __nv_bfloat16* __restrict__ out,
-                long long ld_out, float* __restrict__ lse, long long lse_head_stride, uint32_t* __restrict__ err) {
+                long long ld_out, float* __restrict__ lse, long long lse_head_stride, uint32_t* __restrict__ err,
+                int num_seqs, int total_q, int total_kv) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
@@ -144,8 +145,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int head = blockIdx.x - tile_id * num_heads_q;
   const int kv_head = head / q_per_kv;
   const int2 tile = tiles[tile_id];
+  // The layout tables come from the caller.  Debug-bounds builds check them against the tensors before anything is
+  // read or written through them; the test is uniform over the CTA and precedes every barrier and the TMEM allocation.
+  if (!RLK_INDEX_OK(tile.x, num_seqs, err, 200u, 1)) return;
   const SeqDesc sd = seqs[tile.x];
   const int q0 = tile.y;
+  if (!RLK_INDEX_OK(q0, sd.q_len > 0 ? sd.q_len : 1, err, 200u, 2) ||
+      !RLK_INDEX_OK(sd.q_start, total_q - sd.q_len + 1, err, 200u, 3) ||
+      !RLK_INDEX_OK(sd.pk_start, total_kv - sd.pk_len + 1, err, 200u, 4) ||
+      !RLK_INDEX_OK(sd.sk_start, total_kv - sd.sk_len + 1, err, 200u, 5))
+    return;
 
   const int n_prefix = (sd.pk_len + kTileK - 1) / kTileK;
   int self_keys = sd.sk_len;
@@ -388,7 +397,7 @@ void attention_forward(const AttnFwdArgs& a, cudaStream_t stream) {
   attn_fwd_kernel<<<static_cast<unsigned int>(grid), kThreads, Smem::kDynamic, stream>>>(
       tq, tk, tv, reinterpret_cast<const SeqDesc*>(a.seqs), reinterpret_cast<const int2*>(a.tiles), a.heads_q,
       a.heads_q / a.heads_kv, a.causal ? 1 : 0, a.softmax_scale * kLog2e, a.out, a.ld_out, a.lse, a.lse_head_stride,
-      a.err);
+      a.err, a.num_seqs, static_cast<int>(a.total_q), static_cast<int>(a.total_kv));
 }
 
 }  // namespace rlk

@@ -277,6 +277,7 @@ struct AttnFwdArgs {
   long long total_q, total_kv;
   int heads_q, heads_kv;
   const int* seqs;
+  int num_seqs;  // rows of ``seqs`` (layout tables are checked against it and the token counts in debug-bounds builds)
   const int* tiles;
   int num_tiles;
   bool causal;

@@ -281,8 +281,8 @@ class _PromptPass:
     values through fp32 leaves, which collect their gradients; ``backward`` then back-propagates the sums through the
     prompt pass once."""
 
-    def __init__(self, model: LlamaModel, prompt_ids: torch.Tensor) -> None:
-        self.last_state, self.kv = model.prefix_states(prompt_ids)
+    def __init__(self, model: LlamaModel, prompt_ids: torch.Tensor, **sharding) -> None:
+        self.last_state, self.kv = model.prefix_states(prompt_ids, **sharding)
         leaf = lambda t: t.detach().float().requires_grad_(True)
         self.last_leaf = leaf(self.last_state)
         self.kv_leaves = [(leaf(k), leaf(v)) for k, v in self.kv]
@@ -363,7 +363,7 @@ class GRPOTrainer:
         """Accumulates the gradient of the group's token-mean loss into the flat gradient buffer; returns the loss."""
         g = batch.completion_ids.shape[0]
         m = self.completions_per_pass(batch)
-        if m >= g:
+        if m >= g and not self.force_prompt_pass(batch):
             with self.final_pass():
                 loss, _pl, _kl = self.loss(batch)
             loss.backward()
@@ -387,10 +387,17 @@ class GRPOTrainer:
 
     def prompt_pass(self, batch: GRPOBatch) -> Optional["_PromptPass"]:
         """Runs the shared prompt once for all micro-batches if the model supports prefix-cached passes."""
-        supported = getattr(self.model, "supports_prefix_cache", None)
-        if not self.cache_prompt or supported is None or not supported():
+        if not self.prompt_cacheable(batch):
             return None
         return _PromptPass(self.model, batch.prompt_ids)
+
+    def force_prompt_pass(self, batch: GRPOBatch) -> bool:
+        """True if the prompt-pass route is to be taken even though the whole group fits in one pass."""
+        return False
+
+    def prompt_cacheable(self, batch: GRPOBatch) -> bool:
+        supported = getattr(self.model, "supports_prefix_cache", None)
+        return bool(self.cache_prompt and supported is not None and supported())
 
     def final_pass(self):
         """Context manager around the FORWARD of the pass whose backward runs last in the step.  A trainer that

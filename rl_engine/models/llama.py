@@ -231,6 +231,45 @@ class _FusedAttentionBlockCP(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None
 
 
+class _FusedAttentionBlockCPKV(torch.autograd.Function):
+    """``_FusedAttentionBlockCP`` that also returns the gathered rotated keys / values ``[S, Hkv, 128]`` of the whole
+    sequence (natural order) as differentiable outputs: later passes attend to them as a cached prefix, and whatever
+    gradient reaches them on this rank is added to this rank's contribution before the ranks' contributions are
+    summed, so the owner of each chunk receives the gradient of every rank's later passes as well."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_t, sin_t, cp, hq, hkv, scale):
+        from rl_engine.kernels.ops.base import require_ext
+        from rl_engine.kernels.ops.sm100.attention import packed_attention_forward
+
+        ext = require_ext()
+        q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
+        ext.rope(q, positions, cos_t, sin_t, False, q)
+        ext.rope(k, positions, cos_t, sin_t, False, k)
+        k_all, v_all = cp.gather_kv(k, v)
+        k_all, v_all = k_all.clone(), v_all.clone()  # the symmetric buffers are reused by the next layer
+        out, lse = packed_attention_forward(q, k_all, v_all, cp.layout(q.device), scale, True)
+        ctx.save_for_backward(qkv, out, lse, positions, cos_t, sin_t, k_all, v_all)
+        ctx.meta = (cp, hq, hkv, scale)
+        return out, k_all, v_all
+
+    @staticmethod
+    def backward(ctx, dout, dk_later, dv_later):
+        from rl_engine.kernels.ops.sm100.attention_bwd_kernels import fused_backward
+
+        qkv, out, lse, positions, cos_t, sin_t, k_all, v_all = ctx.saved_tensors
+        cp, hq, hkv, scale = ctx.meta
+        q = qkv[:, :hq]
+        dq, dk_full, dv_full = fused_backward(q, k_all, v_all, out, lse, dout.contiguous(), cp.layout(q.device), scale)
+        if dk_later is not None:
+            dk_full = dk_full + dk_later.to(dk_full.dtype)
+        if dv_later is not None:
+            dv_full = dv_full + dv_later.to(dv_full.dtype)
+        dk, dv = cp.reduce_dkv(dk_full, dv_full)
+        dqkv = _unrotate_into(torch.empty_like(qkv), dq, dk, dv, positions, cos_t, sin_t, hq, hkv)
+        return dqkv, None, None, None, None, None, None, None
+
+
 class LlamaModel(nn.Module):
     def __init__(self, cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
                  activation_checkpointing: Union[bool, str] = "auto", max_positions: int = 8192,
@@ -369,8 +408,11 @@ class LlamaModel(nn.Module):
         if _fused_path(qkv) and cfg.head_dim == 128:
             tail = (positions, self.rope_cos, self.rope_sin, layout, cfg.num_heads, cfg.num_kv_heads, scale)
             if hasattr(layout, "gather_kv"):  # a context-parallel group: ``layout`` is its attention object
-                if return_kv or k_prefix is not None:
-                    raise RuntimeError("context-parallel passes do not take or return a cached prefix")
+                if k_prefix is not None:
+                    raise RuntimeError("context-parallel passes do not take a cached prefix")
+                if return_kv:
+                    out, k_all, v_all = _FusedAttentionBlockCPKV.apply(qkv3, *tail)
+                    return out.reshape(t, cfg.q_dim), k_all, v_all
                 return _FusedAttentionBlockCP.apply(qkv3, *tail).reshape(t, cfg.q_dim)
             if return_kv:
                 out, k_rot, v_rot = _FusedAttentionBlockKV.apply(qkv3, *tail)
@@ -490,16 +532,31 @@ class LlamaModel(nn.Module):
         cfg = self.cfg
         return (self.flat.is_cuda and self.flat.dtype == torch.bfloat16 and cfg.head_dim == 128 and not cfg.num_experts)
 
-    def prefix_states(self, prompt_ids: torch.Tensor):
+    def prefix_states(self, prompt_ids: torch.Tensor, cp=None, share_row=None):
         """One pass over the prompt alone: ``(final-norm hidden state of its last token [1, H], [(k, v)] per layer)``
         with the rotated keys / values ``[P, Hkv, 128]`` every later pass attends to.  All outputs carry the
-        autograd graph of the prompt pass."""
+        autograd graph of the prompt pass.
+
+        ``cp`` (a ``ContextParallelAttention`` for ``P`` tokens) shards the pass over the ranks of its group: every
+        rank runs only its zig-zag rows, the keys / values it returns are the gathered ones, and ``share_row`` (a
+        ``SharedRow`` of that group whose owner holds the last token) hands the last token's state to every rank.
+        Back-propagating through the outputs then sums the ranks' gradients onto the rows' owners; together with
+        the data-parallel gradient sum this equals every rank running the whole prompt."""
         from rl_engine.kernels.ops.sm100.attention import make_layout
         from rl_engine.kernels.registry import kernel_registry
 
         n = prompt_ids.numel()
         positions = torch.arange(n, device=prompt_ids.device)
-        layout = make_layout([(0, n, 0, 0, 0, n)], True, prompt_ids.device)
+        if cp is None:
+            layout = make_layout([(0, n, 0, 0, 0, n)], True, prompt_ids.device)
+        else:
+            from rl_engine.parallel.context_parallel import shard_sequence
+
+            if cp.seq_len != n or share_row is None:
+                raise ValueError("a sharded prompt pass needs a context-parallel object of the prompt's length and a shared row")
+            layout = cp
+            prompt_ids = shard_sequence(prompt_ids.reshape(-1), cp.rank, cp.world)
+            positions = shard_sequence(positions, cp.rank, cp.world)
         x = kernel_registry.get_op("embedding")(prompt_ids, self.view("embed"))
         kv = []
         for i in range(self.cfg.num_layers):
@@ -507,7 +564,8 @@ class LlamaModel(nn.Module):
             x, k_rot, v_rot = self._layer(x, i, positions, layout, return_kv=True)
             kv.append((k_rot, v_rot))
         self._watch(x, self.cfg.num_layers)
-        return rms_norm(x[-1:], self.view("final_norm"), self.cfg.rms_eps), kv
+        last = rms_norm(x[-1:], self.view("final_norm"), self.cfg.rms_eps)
+        return (last if cp is None else share_row(last)), kv
 
     def hidden_states_after_prefix(self, token_ids: torch.Tensor, positions: torch.Tensor, layout, kv) -> torch.Tensor:
         """Final-norm hidden states ``[T, H]`` of tokens that follow a prefix given by its per-layer ``kv``.

@@ -153,3 +153,47 @@ class _CPAttention(torch.autograd.Function):
         dq, dk_full, dv_full = fused_backward(q, k_all, v_all, out, lse, dout.contiguous(), cp.layout(q.device), ctx.scale)
         dk, dv = cp.reduce_dkv(dk_full, dv_full)
         return dq, dk, dv, None, None
+
+
+class SharedRow:
+    """``share(row [1, n])``: the ``owner`` rank's row on every rank of ``mem``'s group, differentiable.
+
+    Forward: the owner stores its row into every peer's buffer (one peer-store kernel); the other ranks' inputs are
+    ignored.  Backward: every rank publishes the gradient it holds, the owner sums them in rank order (``peer_sum``)
+    and the other ranks get zeros.  Calls must be issued by all ranks in the same order."""
+
+    def __init__(self, mem: SymmetricMemory, n: int, owner: int = 0) -> None:
+        self.mem, self.n, self.owner = mem, int(n), int(owner)
+        self.value = mem.alloc((self.n,), torch.bfloat16)
+        self.grad = mem.alloc((self.n,), torch.bfloat16)
+
+    def __call__(self, row: torch.Tensor) -> torch.Tensor:
+        if row.numel() != self.n or row.dtype != torch.bfloat16:
+            raise ValueError(f"expected a bfloat16 row of {self.n} elements")
+        return _ShareRow.apply(row, self)
+
+
+class _ShareRow(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, row, shared: SharedRow):
+        mem = shared.mem
+        mem.barrier()  # the previous value's readers are done
+        if mem.rank == shared.owner:
+            require_ext().cast_broadcast(row.contiguous().view(-1), list(shared.value.ptrs), 1)
+        mem.barrier()
+        ctx.shared = shared
+        return shared.value.local.clone().view_as(row)
+
+    @staticmethod
+    def backward(ctx, grad):
+        shared = ctx.shared
+        mem = shared.mem
+        mem.barrier()  # the previous reduction's readers are done
+        shared.grad.local.copy_(grad.reshape(-1))
+        mem.barrier()
+        if mem.rank == shared.owner:
+            out = torch.empty(shared.n, dtype=torch.bfloat16, device=grad.device)
+            require_ext().peer_sum(list(shared.grad.ptrs), shared.n, False, out)
+        else:
+            out = torch.zeros(shared.n, dtype=torch.bfloat16, device=grad.device)
+        return out.view_as(grad).to(grad.dtype), None

@@ -27,7 +27,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from rl_engine.kernels.ops.base import require_ext
-from rl_engine.models.grpo import GRPOBatch, GRPOTrainer
+from rl_engine.models.grpo import GRPOBatch, GRPOTrainer, _PromptPass
 from rl_engine.models.llama import LlamaModel
 from rl_engine.parallel.symmetric import SymmetricMemory
 
@@ -196,7 +196,14 @@ class ShardedGRPOTrainer(GRPOTrainer):
 
     def __init__(self, model: LlamaModel, *, group=None, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
-                 micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4) -> None:
+                 micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4, shard_prompt="auto") -> None:
+        """``shard_prompt``: the ranks split the shared prompt's forward/backward pass between them (zig-zag context
+        parallelism) instead of each running all of it.  That is only right when every rank trains on completions of
+        the SAME prompt, so ``"auto"`` (default) turns it on once ``set_group_slice`` has been called; ``True`` /
+        ``False`` force it.  Prompts whose length is not a multiple of ``32 * world`` run unsharded."""
+        self.shard_prompt = shard_prompt
+        self._group = group
+        self._prompt_shards = {}
         n = model.flat.numel()
         padded = (n + 7) // 8 * 8
         itemsize = model.flat.element_size()
@@ -223,6 +230,31 @@ class ShardedGRPOTrainer(GRPOTrainer):
         adv = super().advantages(batch)
         return adv if self._slice is None else adv[self._slice].contiguous()
 
+    def _prompt_sharding(self, batch: GRPOBatch):
+        """``{"cp": ..., "share_row": ...}`` for a prompt of this batch's length, or ``None`` if its pass is not sharded."""
+        on = self._slice is not None if self.shard_prompt == "auto" else bool(self.shard_prompt)
+        n = batch.prompt_ids.numel()
+        world = self.mem.world
+        if not on or world == 1 or n % (32 * world) or not self.prompt_cacheable(batch):
+            return None
+        if n not in self._prompt_shards:
+            from rl_engine.parallel.context_parallel import ContextParallelAttention, SharedRow
+
+            cfg = self.model.cfg
+            cp = ContextParallelAttention(n, cfg.num_kv_heads, cfg.head_dim, group=self._group,
+                                          device=self.model.flat.device)
+            self._prompt_shards[n] = {"cp": cp, "share_row": SharedRow(cp.mem, cfg.hidden_size, owner=0)}
+        return self._prompt_shards[n]
+
+    def force_prompt_pass(self, batch: GRPOBatch) -> bool:
+        return self._prompt_sharding(batch) is not None
+
+    def prompt_pass(self, batch: GRPOBatch):
+        sharding = self._prompt_sharding(batch)
+        if sharding is None:
+            return super().prompt_pass(batch)
+        return _PromptPass(self.model, batch.prompt_ids, **sharding)
+
     @contextlib.contextmanager
     def final_pass(self):
         """Wraps the forward of the pass that is back-propagated last: its layer hooks start the buckets."""
@@ -238,3 +270,12 @@ class ShardedGRPOTrainer(GRPOTrainer):
 
     def check(self) -> None:
         self.mem.check()
+        for shard in self._prompt_shards.values():
+            shard["cp"].mem.check()
+
+    def close(self) -> None:
+        """Unmaps the symmetric segments (collective: every rank calls it, with no kernel of the trainer in flight)."""
+        for shard in self._prompt_shards.values():
+            shard["cp"].mem.close()
+        self._prompt_shards = {}
+        self.mem.close()

@@ -3,9 +3,10 @@
 Each of the ``W`` ranks keeps ``E / W`` experts and its own tokens (data parallel activations).
 Dispatch and combine are not NCCL all-to-alls: the dispatch kernel stores every routed row straight
 into the owning rank's slot buffer over NVLink (``moe_scatter_rows_peer``) and the combine kernel reads
-the expert outputs back out of the peers' buffers (``moe_combine_peer``).  The only library collective
-is one tiny all-gather of the per-expert assignment counts, from which every rank derives the same slot
-layout:
+the expert outputs back out of the peers' buffers (``moe_combine_peer``).  The per-expert assignment
+counts travel the same way (every rank stores its ``E`` counts into row ``rank`` of a ``[W, E]`` table in
+each peer's segment, double-buffered, one device barrier), and from that table every rank derives the
+same slot layout; no library collective runs in the layer:
 
     owner(e) = e // (E / W)
     on the owner, expert e's block is padded to a multiple of 128 rows (at least 128) and holds the
@@ -97,23 +98,25 @@ class ExpertParallelContext:
         self.num_slots = (rows + BLOCK - 1) // BLOCK * BLOCK
         self.worst_case = factor >= self.world
         self.max_tokens = max_tokens
-        nbytes = 2 * self.num_slots * hidden * 2 + (1 << 20)
+        nbytes = 2 * self.num_slots * hidden * 2 + 2 * self.world * num_experts * 4 + (1 << 20)
         self.mem = mem if mem is not None else SymmetricMemory(nbytes, group=group, device=device)
         self.recv = self.mem.alloc((self.num_slots, hidden), torch.bfloat16)
         self.send = self.mem.alloc((self.num_slots, hidden), torch.bfloat16)
+        # int32 counts moved as raw 32-bit words (the copy kernel does no arithmetic when source and destination
+        # types match).  Two tables used alternately: a rank can be at most one exchange ahead of a peer, so the
+        # table it overwrites was read by everybody before the barrier of the exchange in between.
+        self._counts = [self.mem.alloc((self.world, num_experts), torch.float32) for _ in range(2)]
+        self._count_turn = 0
 
     # -- plan ---------------------------------------------------------------------------------------
     def plan(self, expert_idx: torch.Tensor) -> EPPlan:
-        import torch.distributed as dist
-
         if expert_idx.shape[0] > self.max_tokens:
             raise ValueError(f"{expert_idx.shape[0]} tokens exceed the context's max_tokens={self.max_tokens}")
         counts = torch.bincount(expert_idx.reshape(-1).long(), minlength=self.num_experts)
         if self.world == 1:
             all_counts = counts.unsqueeze(0)
         else:
-            all_counts = torch.empty(self.world, self.num_experts, dtype=counts.dtype, device=counts.device)
-            dist.all_gather_into_tensor(all_counts, counts, group=self.group)
+            all_counts = self.exchange_counts(counts)
         plan = build_ep_plan(expert_idx, all_counts, self.rank, self.world, self.num_slots)
         if not self.worst_case and int(plan.used_slots) > self.num_slots:
             raise RuntimeError(
@@ -121,6 +124,16 @@ class ExpertParallelContext:
                 "raise capacity_factor"
             )
         return plan
+
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """``counts`` ``[E]`` (integer) of this rank -> int64 ``[W, E]`` of all ranks, through peer stores."""
+        table = self._counts[self._count_turn]
+        self._count_turn ^= 1
+        words = counts.to(torch.int32).contiguous().view(torch.float32)
+        row = self.rank * self.num_experts * 4
+        require_ext().cast_broadcast(words, [p + row for p in table.ptrs], 0)
+        self.mem.barrier()
+        return table.local.view(torch.int32).to(torch.int64)
 
     # -- exchange -----------------------------------------------------------------------------------
     def dispatch(self, rows: torch.Tensor, plan: EPPlan, scale: Optional[torch.Tensor] = None) -> torch.Tensor:

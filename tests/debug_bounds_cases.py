@@ -76,6 +76,13 @@ FusedMoESM100Op()(xm, router, w1, w2, 2)
 from rl_engine.kernels.sampling import SamplerBackend  # noqa: E402
 
 SamplerBackend(seed=1).sample(torch.randn(4, 1000, device=dev, generator=g), top_k=20, top_p=0.9, temperature=0.8)
+from rl_engine.kernels.ops.sm100.attention import make_layout, packed_attention_forward  # noqa: E402
+
+qa = torch.randn(256, 4, 128, device=dev, generator=g).to(torch.bfloat16)
+ka = torch.randn(384, 2, 128, device=dev, generator=g).to(torch.bfloat16)
+va = torch.randn(384, 2, 128, device=dev, generator=g).to(torch.bfloat16)
+good_layout = make_layout([(0, 128, 0, 128, 128, 128), (128, 128, 0, 128, 256, 128)], True, dev)
+packed_attention_forward(qa, ka, va, good_layout, 128 ** -0.5, True)
 clean()
 
 # ---- part 2: one bad index per kernel; the checked access is skipped and reported --------------------------------
@@ -96,6 +103,10 @@ expect_bad_index({630})
 
 _C.group_advantages(rewards, torch.tensor([0, 3, 11], device=dev), 0, 1e-6)  # the last group ends past the rewards
 expect_bad_index({640})
+
+bad_layout = make_layout([(0, 128, 0, 128, 128, 128), (128, 128, 0, 128, 320, 128)], True, dev)  # keys 320..447 of 384
+packed_attention_forward(qa, ka, va, bad_layout, 128 ** -0.5, True)
+expect_bad_index({200})
 
 torch.cuda.synchronize()
 assert float(torch.ones(4, device=dev).sum()) == 4.0    # the context is intact

@@ -275,9 +275,11 @@ def main() -> None:
                           full_dev.old_logps[sl].contiguous(), full_dev.ref_logps[sl].contiguous(),
                           full_dev.completion_mask[sl].contiguous())
     results = {}
-    for name, kw in (("one pass, overlapped", dict(micro_group=None, overlap=True)),
-                     ("one pass, not overlapped", dict(micro_group=None, overlap=False)),
-                     ("prompt pass + micro-batches, overlapped", dict(micro_group=1, overlap=True))):
+    for name, kw in (("one pass, overlapped", dict(micro_group=None, overlap=True, shard_prompt=False)),
+                     ("one pass, not overlapped", dict(micro_group=None, overlap=False, shard_prompt=False)),
+                     ("prompt pass + micro-batches, overlapped", dict(micro_group=1, overlap=True, shard_prompt=False)),
+                     ("sharded prompt pass + one pass", dict(micro_group=None, overlap=True, shard_prompt=True)),
+                     ("sharded prompt pass + micro-batches", dict(micro_group=1, overlap=False))):
         model_dp = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=33, activation_checkpointing=False)
         assert torch.equal(model_dp.flat, start)
         dp_tr = ShardedGRPOTrainer(model_dp, lr=1e-3, layers_per_bucket=1, **kw)
@@ -302,7 +304,8 @@ def main() -> None:
         agree = (torch.sign(d_dp[moved]) == torch.sign(d_one[moved])).float().mean().item()
         assert rel < 0.25 and agree > 0.9, f"data parallel ({name}): update differs from the single-GPU step: {rel:.3f}, {agree:.3f}"
         results[name] = model_dp.flat.clone()
-        dp_tr.mem.close()
+        assert bool(dp_tr._prompt_shards) == ("sharded" in name), (name, "prompt sharding was not what the case asked for")
+        dp_tr.close()
     assert torch.equal(results["one pass, overlapped"], results["one pass, not overlapped"]), \
         "overlapping the gradient exchange with backward changed the result"
     print(f"[{rank}] OK data-parallel GRPO step == single-GPU step (loss {losses[0]:.4f} vs {loss_single[0]:.4f})", flush=True)
