@@ -16,12 +16,23 @@ namespace {
 constexpr int kBN = 256;
 constexpr int kStages = 4;
 
+// RLK_GEMM_GROUP_M=<n> fixes the number of M-tiles per rasterisation group on both tile engines (a tuning aid for
+// shape sweeps; unset or 0 = the L2-budget rule of raster_group_m).
+int group_m_override() {
+  static const int v = [] {
+    const char* env = std::getenv("RLK_GEMM_GROUP_M");
+    return env != nullptr ? std::atoi(env) : 0;
+  }();
+  return v;
+}
+
 template <bool A_MN, bool B_MN, class Epi>
 void launch(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t stream) {
   // Rasterise in groups of M-tiles so concurrently running CTAs share A and B tiles in L2 (at least 8; for
   // a plain GEMM as many as keep the group's A rows L2-resident, so that B streams from DRAM once per group).
   const int total_m = a.group_mode == 2 ? a.M * a.num_groups : a.M;
-  const int group_m = a.group_mode == 0 ? raster_group_m((total_m + kBM - 1) / kBM, a.K, 8) : 8;
+  int group_m = a.group_mode == 0 ? raster_group_m((total_m + kBM - 1) / kBM, a.K, 8) : 8;
+  if (a.group_mode == 0 && group_m_override() > 0) group_m = group_m_override();
   GemmProblem p = make_gemm_problem(total_m, a.N, a.K, kBN, 1, group_m);
   const int g = a.group_mode ? a.num_groups : 1;
   p.group_mode = a.group_mode;
@@ -65,6 +76,7 @@ void launch_pair(const GemmArgs& a, const typename Epi::Params& ep, cudaStream_t
   p.tiles_m = (a.M + kPairBM - 1) / kPairBM;
   p.num_items = p.tiles_m * p.items_per_m;
   p.group_m = raster_group_m(p.tiles_m, 2 * a.K, 4);
+  if (group_m_override() > 0) p.group_m = group_m_override() < p.tiles_m ? group_m_override() : p.tiles_m;
   const CUtensorMap ta = A_MN ? make_tmap_2d_bf16(a.A, a.K, a.M, a.lda, kBK, 64)
                               : make_tmap_2d_bf16(a.A, a.M, a.K, a.lda, kBM, kBK);
   const CUtensorMap tb = B_MN ? make_tmap_2d_bf16(a.B, a.K, a.N, a.ldb, kBK, 64)

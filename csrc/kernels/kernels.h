@@ -355,6 +355,8 @@ namespace rlk {
 // ---------------------------------------------------------------------------- mixture of experts
 // experts <= 512, k <= 32; hidden % 8 == 0 and 16-byte aligned rows for the row kernels.
 void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, float* weight, cudaStream_t stream);
+void moe_topk_backward(const int* idx, const float* weight, const float* dweight, int tokens, int experts, int k,
+                       float* dlogits, cudaStream_t stream);
 void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,
                      __nv_bfloat16* dst, long long ld_dst, int slots, int hidden, cudaStream_t stream,
                      long long src_rows = 0, uint32_t* err = nullptr);  // last two: checked indexing in debug builds

@@ -1,6 +1,7 @@
 // Mixture-of-experts support kernels (Qwen3-MoE style: softmax over all experts, top-k, renormalise):
 //   moe_topk           : per token, the k largest router probabilities (ties -> lower expert id) and their
 //                        renormalised weights; one warp per token, fixed-order reductions.
+//   moe_topk_backward  : gradient of those weights with respect to the logits (softmax over the selected logits).
 //   moe_gather_rows    : dst[slot] = scale[slot] * src[src_row[slot]]  (src_row < 0 -> zero row).  With peer
 //                        destination pointers this is the all-to-all DISPATCH: every rank stores the rows it
 //                        routes to expert e directly into the owning rank's expert-grouped buffer over NVLink.
@@ -75,6 +76,30 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, int tokens, in
     weight[static_cast<long long>(t) * k + lane] = my_w / picked_sum;
   }
   (void)sum;
+}
+
+// Gradient of the renormalised top-k weights with respect to the router logits.  The weights are a softmax over the
+// k selected logits, so d logit[e_i] = w_i * (dw_i - sum_j w_j dw_j) and every unselected logit gets zero.  One warp
+// per token writes the whole row (zeros and the k values).
+__global__ void moe_topk_bwd_kernel(const int* __restrict__ idx, const float* __restrict__ weight,
+                                    const float* __restrict__ dweight, int tokens, int experts, int k,
+                                    float* __restrict__ dlogits) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const long long base = static_cast<long long>(t) * k;
+  const float w = lane < k ? weight[base + lane] : 0.f;
+  const float dw = lane < k ? dweight[base + lane] : 0.f;
+  float dot = w * dw;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+  float* row = dlogits + static_cast<long long>(t) * experts;
+  for (int e = lane; e < experts; e += 32) row[e] = 0.f;
+  __syncwarp();
+  if (lane < k) {
+    const int e = idx[base + lane];
+    if (e >= 0 && e < experts) row[e] = w * (dw - dot);
+  }
 }
 
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src,
@@ -338,6 +363,14 @@ void moe_topk(const float* logits, int tokens, int experts, int k, int* idx, flo
   if (tokens <= 0) return;
   const int threads = 128;
   moe_topk_kernel<<<(tokens * 32 + threads - 1) / threads, threads, 0, stream>>>(logits, tokens, experts, k, idx, weight);
+}
+
+void moe_topk_backward(const int* idx, const float* weight, const float* dweight, int tokens, int experts, int k,
+                       float* dlogits, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  const int threads = 128;
+  moe_topk_bwd_kernel<<<(tokens * 32 + threads - 1) / threads, threads, 0, stream>>>(idx, weight, dweight, tokens, experts,
+                                                                                  k, dlogits);
 }
 
 void moe_gather_rows(const __nv_bfloat16* src, long long ld_src, const int* src_row, const float* scale,

@@ -349,6 +349,26 @@ std::vector<Tensor> moe_topk(const Tensor& logits, int64_t k) {
   return {idx, w};
 }
 
+// d logits [T, E] from the gradient of the renormalised top-k weights [T, k].
+Tensor moe_topk_bwd(const Tensor& idx, const Tensor& weight, const Tensor& dweight, int64_t experts) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == torch::kInt32 && idx.is_contiguous() && idx.dim() == 2,
+              "moe_topk_bwd: idx must be a contiguous int32 CUDA tensor [T, k]");
+  TORCH_CHECK(weight.scalar_type() == torch::kFloat32 && weight.is_contiguous() && weight.sizes() == idx.sizes() &&
+                  dweight.scalar_type() == torch::kFloat32 && dweight.is_contiguous() && dweight.sizes() == idx.sizes() &&
+                  weight.device() == idx.device() && dweight.device() == idx.device(),
+              "moe_topk_bwd: weight and dweight must be contiguous float32 tensors shaped like idx on its device");
+  TORCH_CHECK(idx.size(1) >= 1 && idx.size(1) <= 32 && experts >= idx.size(1), "moe_topk_bwd: 1 <= k <= min(32, experts)");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  Tensor dlogits = torch::empty({idx.size(0), experts}, weight.options());
+  if (idx.size(0)) {
+    rlk::moe_topk_backward(idx.data_ptr<int>(), weight.data_ptr<float>(), dweight.data_ptr<float>(),
+                           static_cast<int>(idx.size(0)), static_cast<int>(experts), static_cast<int>(idx.size(1)),
+                           dlogits.data_ptr<float>(), stream_of(idx));
+    after_launch();
+  }
+  return dlogits;
+}
+
 // (slot [T, k], src_row [S], tile_group [S / 128], offsets [E + 1], counts [E]) for expert ids `idx` int32 [T, k].
 std::vector<Tensor> moe_build_plan(const Tensor& idx, int64_t experts, int64_t num_slots, int64_t unused_group) {
   TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == torch::kInt32 && idx.is_contiguous() && idx.dim() == 2, "moe_build_plan: idx int32 [T, k]");
@@ -1208,6 +1228,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_ag_gemm", rlk::traced("rlk::tp_ag_gemm", &tp_ag_gemm));
   m.def("tp_gemm_rs", rlk::traced("rlk::tp_gemm_rs", &tp_gemm_rs));
   m.def("moe_topk", rlk::traced("rlk::moe_topk", &moe_topk));
+  m.def("moe_topk_bwd", rlk::traced("rlk::moe_topk_bwd", &moe_topk_bwd));
   m.def("moe_build_plan", rlk::traced("rlk::moe_build_plan", &moe_build_plan));
   m.def("moe_gather_rows", rlk::traced("rlk::moe_gather_rows", &moe_gather_rows), py::arg("src"), py::arg("src_row"), py::arg("scale") = py::none(),
         py::arg("dst_ptr") = 0, py::arg("dst_ld") = 0);

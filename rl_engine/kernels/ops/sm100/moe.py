@@ -30,18 +30,35 @@ from rl_engine.kernels.ops.base import require_ext
 BLOCK = 128
 
 
+class _RouteTopK(torch.autograd.Function):
+    """Softmax over all experts, top-k, renormalisation in ONE kernel; the backward kernel writes the logits' gradient
+    row (the renormalised weights are a softmax over the selected logits)."""
+
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, k: int):
+        idx, weights = require_ext().moe_topk(logits.contiguous(), int(k))
+        ctx.save_for_backward(idx, weights)
+        ctx.experts = logits.shape[1]
+        ctx.mark_non_differentiable(idx)
+        return idx, weights
+
+    @staticmethod
+    def backward(ctx, _didx, dweights):
+        idx, weights = ctx.saved_tensors
+        return require_ext().moe_topk_bwd(idx, weights, dweights.float().contiguous(), ctx.experts), None
+
+
 def route_topk(router_logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """(expert ids int32 [T, k], renormalised weights fp32 [T, k]); differentiable w.r.t. the logits.
 
-    Selection runs in the ``moe_topk`` kernel on the GPU (ties -> lower expert id); the weights are
-    re-derived from the logits with three small PyTorch ops so that autograd reaches the router."""
+    On the GPU selection and weights come from the ``moe_topk`` kernel (ties -> lower expert id) and the gradient from
+    ``moe_topk_bwd``; the portable path below spells the same function with PyTorch ops."""
     logits = router_logits.float()
     if logits.is_cuda:
-        idx, _ = require_ext().moe_topk(logits.detach().contiguous(), int(k))
-    else:
-        probs = torch.softmax(logits.detach(), dim=-1)
-        # stable descending sort reproduces the kernel's tie rule
-        idx = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :k].to(torch.int32)
+        return _RouteTopK.apply(logits, int(k))
+    probs = torch.softmax(logits.detach(), dim=-1)
+    # stable descending sort reproduces the kernel's tie rule
+    idx = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :k].to(torch.int32)
     probs = torch.softmax(logits, dim=-1)
     picked = probs.gather(1, idx.long())
     return idx, picked / picked.sum(dim=-1, keepdim=True)

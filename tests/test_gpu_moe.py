@@ -26,6 +26,29 @@ def test_topk_routing_matches_torch():
     assert torch.allclose(w, ref_w, atol=1e-6, rtol=1e-5)
 
 
+@pytest.mark.parametrize("experts,k", [(128, 8), (8, 2), (60, 4)])
+def test_router_weights_gradient_matches_torch(experts, k):
+    """``route_topk`` on the GPU (one forward kernel, one backward kernel) against softmax -> gather -> renormalise
+    spelled with PyTorch ops in fp32: same ids, same weights, same gradient for the logits."""
+    from rl_engine.kernels.ops.sm100.moe import route_topk
+
+    g = torch.Generator(device=DEV).manual_seed(3)
+    logits = torch.randn(777, experts, device=DEV, generator=g)
+    dw = torch.randn(777, k, device=DEV, generator=g)
+    a = logits.clone().requires_grad_(True)
+    idx, w = route_topk(a, k)
+    (w * dw).sum().backward()
+    b = logits.clone().requires_grad_(True)
+    probs = torch.softmax(b, dim=-1)
+    picked = probs.gather(1, idx.long())
+    w_ref = picked / picked.sum(-1, keepdim=True)
+    (w_ref * dw).sum().backward()
+    assert torch.equal(idx.long(), torch.sort(probs.detach(), dim=-1, descending=True, stable=True).indices[:, :k])
+    assert torch.allclose(w, w_ref, atol=1e-6, rtol=1e-5)
+    assert torch.allclose(a.grad, b.grad, atol=2e-6, rtol=1e-4)
+    assert not idx.requires_grad
+
+
 def test_grouped_gemm_modes():
     from rl_engine.kernels.ops.base import require_ext
     from rl_engine.kernels.ops.sm100.moe import build_dispatch_plan
