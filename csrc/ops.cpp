@@ -125,11 +125,11 @@ Tensor gemm(const Tensor& a, const Tensor& b, bool a_mn, bool b_mn, std::optiona
   g.alpha = static_cast<float>(alpha);
   g.sm_count = sm_count_of(a.get_device());
   g.err = err_ptr(a);
-  // Default engine: CTA pairs, except for a single 128-row tile (nothing to pair) and for A operands with a row
-  // pitch of 16 KB or more.  Measured in seconds-long loops under the power cap on B200 (T = 32768 tokens,
-  // Llama-3-8B linears, forward / dgrad / wgrad): pairs are 7-9 % faster on every shape whose A pitch is
-  // 4096-6144 elements and 4-12 % slower on the three shapes whose A pitch is 14336 or 28672 elements.
-  const bool pair_suits = M > 128 && a.stride(0) < 8192;
+  // Default engine: CTA pairs, except for a single 128-row tile (nothing to pair).  Measured in seconds-long loops
+  // under the power cap on B200 (T = 16384 and 32768 tokens, Llama-3-8B linears, forward / dgrad / wgrad): with
+  // rasterisation groups of at least eight 256-row tiles the pair engine is as fast or faster than the single-CTA
+  // engine on every shape (up to 12 % on the gate/up weight gradient), although it runs at a lower clock.
+  const bool pair_suits = M > 128;
   g.cta_pair = pair < 0 ? (gemm_pair_default() && pair_suits) : pair != 0;
   rlk::gemm_bf16(g, stream_of(a));
   after_launch();

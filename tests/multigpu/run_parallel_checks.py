@@ -279,7 +279,7 @@ def main() -> None:
                      ("one pass, not overlapped", dict(micro_group=None, overlap=False, shard_prompt=False)),
                      ("prompt pass + micro-batches, overlapped", dict(micro_group=1, overlap=True, shard_prompt=False)),
                      ("sharded prompt pass + one pass", dict(micro_group=None, overlap=True, shard_prompt=True)),
-                     ("sharded prompt pass + micro-batches", dict(micro_group=1, overlap=False))):
+                     ("sharded prompt pass + micro-batches", dict(micro_group=1, overlap=False, shard_prompt=True))):
         model_dp = LlamaModel(dcfg, dtype=torch.bfloat16, device=dev, seed=33, activation_checkpointing=False)
         assert torch.equal(model_dp.flat, start)
         dp_tr = ShardedGRPOTrainer(model_dp, lr=1e-3, layers_per_bucket=1, **kw)
