@@ -15,10 +15,14 @@
 // (4 x 128 columns).  Eight softmax warps share the 128 query rows TWO threads per row: warps 2..5 own keys
 // 0..63 of every tile and output columns 0..63, warps 6..9 own keys 64..127 and output columns 64..127.
 // Each thread pulls its half of the S row with two tcgen05.ld in flight, the two halves exchange their row
-// maximum through shared memory (one named barrier per tile), then each runs its half of the online softmax,
-// writes its 64-key atom of P as bf16 into the 128B-swizzled smem tile (the A operand of the second MMA) and
-// accumulates its half of O in registers as O = O * alpha + O_j.  Two warps per scheduler hide the
-// fixed-latency and TMEM-load stalls that one warp per scheduler exposes.
+// maximum through shared memory (one named barrier per tile), then each runs its half of the online softmax and
+// writes its 64-key atom of P as bf16 into the 128B-swizzled smem tile (the A operand of the second MMA).
+// O stays in TMEM: every P V product accumulates into the same 128 columns, and the softmax threads rescale them
+// (tcgen05.ld, multiply, tcgen05.st) only on tiles where some row's maximum grew by more than 2^8 over the value the
+// exponentials are taken against; until then that value lags the true maximum, which changes no result (numerator
+// and denominator carry the same factor, at most 2^8, far inside bf16 / fp32 range).  After the first tiles of a row
+// that is rare, so the per-tile accumulator traffic (128 fp32 per row in and out of registers) is gone.  Two warps
+// per scheduler hide the fixed-latency and TMEM-load stalls that one warp per scheduler exposes.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "kernels.h"
@@ -59,7 +63,7 @@ struct Smem {
   static constexpr int kP = kV + 2 * kTileBytes;   // 2 buffers
   static constexpr int kXmax = kP + 2 * kTileBytes;  // float [2 halves][128 rows]: row-maximum exchange
   static constexpr int kBars = kXmax + 2 * 128 * 4;
-  // q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_empty[2], v_full[2], v_empty[2]
+  // q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], (2 unused), v_full[2], v_empty[2]
   static constexpr int kNumBars = 19;
   static constexpr int kBytes = kBars + kNumBars * 8 + 16;
   static constexpr int kDynamic = kBytes + 1024;
@@ -134,8 +138,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* s_full = bars + 5;
   uint64_t* s_empty = bars + 7;
   uint64_t* p_full = bars + 9;
-  uint64_t* o_full = bars + 11;
-  uint64_t* o_empty = bars + 13;
+  uint64_t* o_full = bars + 11;  // P V of tile j has completed (commit per product; waited where O or P[b] is touched)
   float* xmax_s = reinterpret_cast<float*>(smem + Smem::kXmax);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -173,7 +176,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&s_empty[b], kSoftmaxThreads / 32);  // one arrival per softmax warp
       mbar_init(&p_full[b], kSoftmaxThreads / 32);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_empty[b], kSoftmaxThreads / 32);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -228,8 +230,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       auto issue_pv = [&](int j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        mbar_wait(&p_full[b], ph, abort_flag, err, 200, 3);
-        mbar_wait(&o_empty[b], ph ^ 1, abort_flag, err, 200, 4);
+        mbar_wait(&p_full[b], ph, abort_flag, err, 200, 3);  // also orders any rescale of O before this product
         mbar_wait(&v_full[b], ph, abort_flag, err, 200, 14);
         tc_fence_after();
         const uint32_t sp = smem_u32(smem + Smem::kP + b * kTileBytes);
@@ -239,7 +240,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           // A = P: K-major, K = keys; 4 k-steps per 64-key atom.  B = V: MN-major, 16 key rows = 2048 bytes.
           const uint64_t da = umma_smem_desc_sw128(sp + (k >> 2) * kAtomBytes + (k & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc_sw128(sv + k * 2048, kAtomBytes, 1024);
-          umma_bf16(tmem + 256 + b * 128, da, db, idesc_o, k != 0 ? 1u : 0u);
+          umma_bf16(tmem + 256, da, db, idesc_o, (j != 0 || k != 0) ? 1u : 0u);
         }
         umma_commit(&o_full[b]);
         umma_commit(&v_empty[b]);
@@ -271,31 +272,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int qi = q0 + r;             // query index within the sequence
     constexpr int kHalf = 64;
-    float o[kHalf];
-#pragma unroll
-    for (int i = 0; i < kHalf; ++i) o[i] = 0.f;
-    float m2 = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    constexpr float kLazy = 8.f;  // the exponent base follows the row maximum only in steps of more than 2^8
+    const uint32_t o_addr = tmem + 256 + half * kHalf + lane_addr;
+    float m_used = -INFINITY, l = 0.f;  // m_used: what the exponentials are taken against (log2 domain, scaled)
     PROF_DECL;
-
-    auto accumulate = [&](int j, float alpha) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      PROF(0);
-      mbar_wait(&o_full[b], ph, abort_flag, err, 200, 7);
-      PROF(6);
-      tc_fence_after();
-      uint32_t t0[32], t1[32];
-      tmem_ld_32x32b_x32(tmem + 256 + b * 128 + half * kHalf + lane_addr, t0);
-      tmem_ld_32x32b_x32(tmem + 256 + b * 128 + half * kHalf + 32 + lane_addr, t1);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(t0[i]));
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(t1[i]));
-      tc_fence_before();
-      mbar_arrive_warp(&o_empty[b]);
-      PROF(7);
-    };
 
     for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
@@ -328,22 +308,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mx = fmaxf(mx, xmax_s[(half ^ 1) * 128 + r]);
       asm volatile("bar.sync %0, 64;" ::"r"(5 + quad) : "memory");
       PROF(3);
-      const float new_m2 = fmaxf(m2, mx * scale_log2e);
-      const float m_safe = new_m2 == -INFINITY ? 0.f : new_m2;
-      const float alpha = fast_exp2(m2 - m_safe);  // m2 = -inf -> 0
+      // Both threads of a row hold the same mx, so both take the same branch and keep the same m_used.
+      const float cand = fmaxf(m_used, mx * scale_log2e);
+      if (j == 0) {
+        m_used = cand;  // nothing accumulated yet
+      } else if (__any_sync(0xffffffffu, cand - m_used > kLazy)) {  // (-inf) - (-inf) = NaN compares false
+        const float alpha = cand == -INFINITY ? 1.f : fast_exp2(m_used - cand);  // m_used = -inf -> 0
+        // O holds the products up to tile j - 1 once P V of that tile has completed; P V of tile j is issued only
+        // after every softmax warp has arrived on p_full below, i.e. after this rescale.
+        mbar_wait(&o_full[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 200, 7);
+        tc_fence_after();
+        uint32_t o0[32], o1[32];
+        tmem_ld_32x32b_x32(o_addr, o0);
+        tmem_ld_32x32b_x32(o_addr + 32, o1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+          o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+        }
+        tmem_st_32x32b_x32(o_addr, o0);
+        tmem_st_32x32b_x32(o_addr + 32, o1);
+        tmem_st_wait();
+        tc_fence_before();
+        l *= alpha;
+        m_used = cand;
+      }
+      const float m_safe = m_used == -INFINITY ? 0.f : m_used;
+      // P[b] was the A operand of P V of tile j - 2: that product must have finished reading it
+      if (j >= 2) mbar_wait(&o_full[b], ((j - 2) >> 1) & 1, abort_flag, err, 200, 4);
       // 64 keys of a row = one 128-byte swizzle row of atom `half`
       uint8_t* prow = smem + Smem::kP + b * kTileBytes + half * kAtomBytes + r * 128;
       const float sum = masked ? softmax_half_row<true>(t, limit, scale_log2e, m_safe, prow, r)
                                : softmax_half_row<false>(t, limit, scale_log2e, m_safe, prow, r);
-      l = fmaf(l, alpha, sum);  // this thread's share of the row sum; both halves use the same maximum
-      m2 = new_m2;
+      l += sum;  // this thread's share of the row sum; both halves use the same m_used
       fence_proxy_async_smem();
       mbar_arrive_warp(&p_full[b]);
       PROF(4);
-      if (j >= 1) accumulate(j - 1, alpha_prev);
-      alpha_prev = alpha;
     }
-    if (n_tiles >= 1) accumulate(n_tiles - 1, alpha_prev);
+
+    // this thread's 64 columns of O, once the last product has completed
+    uint32_t o[kHalf];  // fp32 bits
+    if (n_tiles >= 1) {
+      mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, err, 200, 9);
+      tc_fence_after();
+      tmem_ld_32x32b_x32(o_addr, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+      tmem_ld_32x32b_x32(o_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+      tmem_ld_wait();
+      tc_fence_before();
+    } else {
+#pragma unroll
+      for (int i = 0; i < kHalf; ++i) o[i] = 0u;
+    }
+    const float m2 = m_used;
 
     // total row sum = the two halves' shares (the exchange buffer is free: every reader passed barrier 2)
     xmax_s[half * 128 + r] = l;
@@ -358,7 +375,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 pk = __floats2bfloat162_rn(o[c8 * 8 + 2 * i] * inv, o[c8 * 8 + 2 * i + 1] * inv);
+          __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[c8 * 8 + 2 * i]) * inv,
+                                                    __uint_as_float(o[c8 * 8 + 2 * i + 1]) * inv);
           w[i] = *reinterpret_cast<uint32_t*>(&pk);
         }
         reinterpret_cast<uint4*>(dst)[c8] = make_uint4(w[0], w[1], w[2], w[3]);

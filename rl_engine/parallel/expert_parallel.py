@@ -45,6 +45,7 @@ class EPPlan:
     offsets: torch.Tensor      # int32 [El+1]  padded slot offsets of MY experts
     used_slots: torch.Tensor   # int64 []      slots in use on this rank (device scalar)
     top_k: int
+    rows: int = 0              # ``used_slots`` on the host (a multiple of 128) once ``ExpertParallelContext.plan`` read it
 
 
 def build_ep_plan(expert_idx: torch.Tensor, all_counts: torch.Tensor, rank: int, world: int, num_slots: int) -> EPPlan:
@@ -118,11 +119,17 @@ class ExpertParallelContext:
         else:
             all_counts = self.exchange_counts(counts)
         plan = build_ep_plan(expert_idx, all_counts, self.rank, self.world, self.num_slots)
-        if not self.worst_case and int(plan.used_slots) > self.num_slots:
+        # One host read per layer: the slot buffers are sized for the worst routing (every token of every rank to this
+        # rank's experts), W times the expected load.  Knowing the rows in use lets every later kernel (zero, copies,
+        # SwiGLU, the grouped GEMMs' outputs) touch only those instead of the whole buffer.
+        used = int(plan.used_slots)
+        if used > self.num_slots:
             raise RuntimeError(
-                f"expert-parallel slot buffer overflow on rank {self.rank}: {int(plan.used_slots)} > {self.num_slots}; "
+                f"expert-parallel slot buffer overflow on rank {self.rank}: {used} > {self.num_slots}; "
                 "raise capacity_factor"
             )
+        plan.rows = used
+        plan.tile_group = plan.tile_group[: used // BLOCK].contiguous()
         return plan
 
     def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
@@ -139,16 +146,17 @@ class ExpertParallelContext:
     def dispatch(self, rows: torch.Tensor, plan: EPPlan, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Send ``rows[token]`` (times ``scale``) of every assignment to its owner; returns MY received slots."""
         ext = require_ext()
-        self.recv.local.zero_()
+        mine = self.recv.local[: plan.rows]
+        mine.zero_()  # the padding rows between the experts' blocks feed the weight-gradient GEMMs: they must be zero
         self.mem.barrier()
         ext.moe_scatter_rows_peer(rows, plan.token, plan.dest_rank, plan.dest_slot, scale, self.recv.ptrs, self.hidden)
         self.mem.barrier()
-        return self.recv.local.clone()
+        return mine.clone()
 
     def collect(self, slots_out: torch.Tensor, plan: EPPlan) -> torch.Tensor:
         """Publish MY expert outputs and fetch, for every local assignment, its row: ``[T*k, H]``."""
         ext = require_ext()
-        self.send.local.copy_(slots_out)
+        self.send.local[: plan.rows].copy_(slots_out)
         self.mem.barrier()
         n = plan.dest_slot.numel()
         return ext.moe_combine_peer(self.send.ptrs, self.hidden, self.hidden, plan.dest_rank.view(n, 1),
