@@ -63,8 +63,8 @@ struct Smem {
   static constexpr int kP = kV + 2 * kTileBytes;   // 2 buffers
   static constexpr int kXmax = kP + 2 * kTileBytes;  // float [2 halves][128 rows]: row-maximum exchange
   static constexpr int kBars = kXmax + 2 * 128 * 4;
-  // q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], (2 unused), v_full[2], v_empty[2]
-  static constexpr int kNumBars = 19;
+  // q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], p_full[2], o_full[2], o_done, o_free, v_full[2], v_empty[2], q_empty
+  static constexpr int kNumBars = 20;
   static constexpr int kBytes = kBars + kNumBars * 8 + 16;
   static constexpr int kDynamic = kBytes + 1024;
 };
@@ -118,13 +118,53 @@ __device__ __forceinline__ float max_half_row(const uint32_t (&t)[64], int limit
   return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
+// One work item = one 128-query tile of one head; what every role needs to know about it.
+struct Item {
+  SeqDesc sd;
+  int q0, head, kv_head, n_prefix, n_tiles;
+  bool ok;
+};
+
+__device__ __forceinline__ Item decode_item(int w, const SeqDesc* __restrict__ seqs, const int2* __restrict__ tiles,
+                                            int num_heads_q, int q_per_kv, int causal, int num_seqs, int total_q,
+                                            int total_kv, uint32_t* err) {
+  Item it;
+  const int tile_id = w / num_heads_q;
+  it.head = w - tile_id * num_heads_q;
+  it.kv_head = it.head / q_per_kv;
+  const int2 tile = tiles[tile_id];
+  it.q0 = tile.y;
+  it.n_prefix = it.n_tiles = 0;
+  // The layout tables come from the caller.  Debug-bounds builds check them against the tensors before anything is
+  // read or written through them; every role of the CTA decodes the same item and takes the same decision.
+  it.ok = RLK_INDEX_OK(tile.x, num_seqs, err, 200u, 1);
+  if (!it.ok) return it;
+  it.sd = seqs[tile.x];
+  it.ok = RLK_INDEX_OK(it.q0, it.sd.q_len > 0 ? it.sd.q_len : 1, err, 200u, 2) &&
+          RLK_INDEX_OK(it.sd.q_start, total_q - it.sd.q_len + 1, err, 200u, 3) &&
+          RLK_INDEX_OK(it.sd.pk_start, total_kv - it.sd.pk_len + 1, err, 200u, 4) &&
+          RLK_INDEX_OK(it.sd.sk_start, total_kv - it.sd.sk_len + 1, err, 200u, 5);
+  if (!it.ok) return it;
+  it.n_prefix = (it.sd.pk_len + kTileK - 1) / kTileK;
+  int self_keys = it.sd.sk_len;
+  if (causal) self_keys = min(self_keys, it.q0 + kTileQ);
+  it.n_tiles = it.n_prefix + (self_keys + kTileK - 1) / kTileK;
+  return it;
+}
+
+// Persistent: CTA c handles work items total - 1 - c, total - 1 - c - gridDim.x, ... (the caller's tile list usually
+// ends with the sequences that see the most keys, so the heavy items go first and the light ones fill the tail).
+// The K / V rings, the S and P buffers and their barriers run on across items (`g`, the number of key tiles this CTA
+// has handled so far, selects buffer and phase), so the loader and the MMA warp start on the next item's Q, K and S
+// while the softmax warps still normalise and store the current item's output: the per-item set-up, the first loads
+// from DRAM and the output stores are hidden, which was about half of a CTA's lifetime when one CTA handled one item.
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const SeqDesc* __restrict__ seqs,
                 const int2* __restrict__ tiles,  // (sequence, first query row within the sequence)
-                int num_heads_q, int q_per_kv, int causal, float scale_log2e, __nv_bfloat16* __restrict__ out,
-                long long ld_out, float* __restrict__ lse, long long lse_head_stride, uint32_t* __restrict__ err,
-                int num_seqs, int total_q, int total_kv) {
+                int total_items, int num_heads_q, int q_per_kv, int causal, float scale_log2e,
+                __nv_bfloat16* __restrict__ out, long long ld_out, float* __restrict__ lse, long long lse_head_stride,
+                uint32_t* __restrict__ err, int num_seqs, int total_q, int total_kv) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
@@ -138,35 +178,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* s_full = bars + 5;
   uint64_t* s_empty = bars + 7;
   uint64_t* p_full = bars + 9;
-  uint64_t* o_full = bars + 11;  // P V of tile j has completed (commit per product; waited where O or P[b] is touched)
+  uint64_t* o_full = bars + 11;   // P V of a tile has completed (commit per product; waited where O or P[b] is touched)
+  uint64_t* o_done = bars + 13;   // per item: every product of the item has completed
+  uint64_t* o_free = bars + 14;   // per item: the softmax warps have pulled the item's O out of TMEM
+  uint64_t* q_empty = bars + 19;  // per item: every S product of the item has completed, Q may be overwritten
   float* xmax_s = reinterpret_cast<float*>(smem + Smem::kXmax);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_id = blockIdx.x / num_heads_q;
-  const int head = blockIdx.x - tile_id * num_heads_q;
-  const int kv_head = head / q_per_kv;
-  const int2 tile = tiles[tile_id];
-  // The layout tables come from the caller.  Debug-bounds builds check them against the tensors before anything is
-  // read or written through them; the test is uniform over the CTA and precedes every barrier and the TMEM allocation.
-  if (!RLK_INDEX_OK(tile.x, num_seqs, err, 200u, 1)) return;
-  const SeqDesc sd = seqs[tile.x];
-  const int q0 = tile.y;
-  if (!RLK_INDEX_OK(q0, sd.q_len > 0 ? sd.q_len : 1, err, 200u, 2) ||
-      !RLK_INDEX_OK(sd.q_start, total_q - sd.q_len + 1, err, 200u, 3) ||
-      !RLK_INDEX_OK(sd.pk_start, total_kv - sd.pk_len + 1, err, 200u, 4) ||
-      !RLK_INDEX_OK(sd.sk_start, total_kv - sd.sk_len + 1, err, 200u, 5))
-    return;
-
-  const int n_prefix = (sd.pk_len + kTileK - 1) / kTileK;
-  int self_keys = sd.sk_len;
-  if (causal) self_keys = min(self_keys, q0 + kTileQ);
-  const int n_self = (self_keys + kTileK - 1) / kTileK;
-  const int n_tiles = n_prefix + n_self;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(o_done, 1);
+    mbar_init(o_free, kSoftmaxThreads / 32);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&k_full[b], 1);
       mbar_init(&k_empty[b], 1);
@@ -191,34 +217,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int first = total_items - 1 - static_cast<int>(blockIdx.x), step = static_cast<int>(gridDim.x);
+#define RLK_ATTN_ITEM(w) decode_item(w, seqs, tiles, num_heads_q, q_per_kv, causal, num_seqs, total_q, total_kv, err)
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, kTileBytes);
-      tma_load_2d(smem + Smem::kQ, &tmap_q, q_full, head * kD, sd.q_start + q0);
-      tma_load_2d(smem + Smem::kQ + kAtomBytes, &tmap_q, q_full, head * kD + 64, sd.q_start + q0);
-      auto key_row = [&](int j) { return j < n_prefix ? sd.pk_start + j * kTileK : sd.sk_start + (j - n_prefix) * kTileK; };
-      auto load_k = [&](int j) {
-        const int b = j & 1;
-        mbar_wait(&k_empty[b], ((j >> 1) & 1) ^ 1, abort_flag, err, 200, 1);
-        mbar_arrive_expect_tx(&k_full[b], kTileBytes);
-        uint8_t* sk = smem + Smem::kK + b * kTileBytes;
-        tma_load_2d(sk, &tmap_k, &k_full[b], kv_head * kD, key_row(j));
-        tma_load_2d(sk + kAtomBytes, &tmap_k, &k_full[b], kv_head * kD + 64, key_row(j));
-      };
-      auto load_v = [&](int j) {
-        const int b = j & 1;
-        mbar_wait(&v_empty[b], ((j >> 1) & 1) ^ 1, abort_flag, err, 200, 13);
-        mbar_arrive_expect_tx(&v_full[b], kTileBytes);
-        uint8_t* sv = smem + Smem::kV + b * kTileBytes;
-        tma_load_2d(sv, &tmap_v, &v_full[b], kv_head * kD, key_row(j));
-        tma_load_2d(sv + kAtomBytes, &tmap_v, &v_full[b], kv_head * kD + 64, key_row(j));
-      };
-      // K runs one tile ahead of V in issue order: K(j + 1) only waits for S(j - 1), V(j) for P V of tile j - 2
-      if (n_tiles >= 1) load_k(0);
-      for (int j = 0; j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) load_k(j + 1);
-        load_v(j);
+      int g0 = 0, n_item = 0;  // key tiles and items (with at least one key tile) handled so far
+      // The next item's descriptor is fetched while the current one is worked on: its two dependent global loads
+      // (tile entry, then sequence entry) would otherwise sit on the critical path between two items.
+      Item next = RLK_ATTN_ITEM(first);
+      for (int w = first; w >= 0 && !*abort_flag; w -= step) {
+        const Item it = next;
+        if (w - step >= 0) next = RLK_ATTN_ITEM(w - step);
+        if (!it.ok || it.n_tiles == 0) continue;
+        mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, err, 200, 15);  // the previous item's S products are done with Q
+        mbar_arrive_expect_tx(q_full, kTileBytes);
+        tma_load_2d(smem + Smem::kQ, &tmap_q, q_full, it.head * kD, it.sd.q_start + it.q0);
+        tma_load_2d(smem + Smem::kQ + kAtomBytes, &tmap_q, q_full, it.head * kD + 64, it.sd.q_start + it.q0);
+        auto key_row = [&](int j) {
+          return j < it.n_prefix ? it.sd.pk_start + j * kTileK : it.sd.sk_start + (j - it.n_prefix) * kTileK;
+        };
+        auto load_k = [&](int j) {
+          const int g = g0 + j, b = g & 1;
+          mbar_wait(&k_empty[b], ((g >> 1) & 1) ^ 1, abort_flag, err, 200, 1);
+          mbar_arrive_expect_tx(&k_full[b], kTileBytes);
+          uint8_t* sk = smem + Smem::kK + b * kTileBytes;
+          tma_load_2d(sk, &tmap_k, &k_full[b], it.kv_head * kD, key_row(j));
+          tma_load_2d(sk + kAtomBytes, &tmap_k, &k_full[b], it.kv_head * kD + 64, key_row(j));
+        };
+        auto load_v = [&](int j) {
+          const int g = g0 + j, b = g & 1;
+          mbar_wait(&v_empty[b], ((g >> 1) & 1) ^ 1, abort_flag, err, 200, 13);
+          mbar_arrive_expect_tx(&v_full[b], kTileBytes);
+          uint8_t* sv = smem + Smem::kV + b * kTileBytes;
+          tma_load_2d(sv, &tmap_v, &v_full[b], it.kv_head * kD, key_row(j));
+          tma_load_2d(sv + kAtomBytes, &tmap_v, &v_full[b], it.kv_head * kD + 64, key_row(j));
+        };
+        // K runs one tile ahead of V in issue order: K(j + 1) only waits for S(j - 1), V(j) for P V of tile j - 2
+        load_k(0);
+        for (int j = 0; j < it.n_tiles; ++j) {
+          if (j + 1 < it.n_tiles) load_k(j + 1);
+          load_v(j);
+        }
+        g0 += it.n_tiles;
+        ++n_item;
       }
     }
   } else if (warp == 1) {
@@ -226,12 +268,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, false, false);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, false, true);   // P (K-major) x V (MN-major)
       const uint32_t sq = smem_u32(smem + Smem::kQ);
-      mbar_wait(q_full, 0, abort_flag, err, 200, 2);
-      auto issue_pv = [&](int j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+      int g0 = 0, n_item = 0;
+      // P V of a tile is issued one S product later than the tile's own S product, across item boundaries too: the
+      // first S tile of the next item is computed while the softmax warps finish the last tile of this one.
+      struct Pending {
+        int g, item;       // global key-tile index and item index of the product that is still to be issued
+        bool first, last;  // first / last key tile of its item
+      } pend{0, 0, false, false};
+      bool have_pend = false;
+      auto issue_pv = [&](const Pending& pv) {
+        const int b = pv.g & 1;
+        const uint32_t ph = (pv.g >> 1) & 1;
         mbar_wait(&p_full[b], ph, abort_flag, err, 200, 3);  // also orders any rescale of O before this product
         mbar_wait(&v_full[b], ph, abort_flag, err, 200, 14);
+        // the first product of an item overwrites O: the softmax warps must have read the previous item's
+        if (pv.first) mbar_wait(o_free, (pv.item & 1) ^ 1, abort_flag, err, 200, 16);
         tc_fence_after();
         const uint32_t sp = smem_u32(smem + Smem::kP + b * kTileBytes);
         const uint32_t sv = smem_u32(smem + Smem::kV + b * kTileBytes);
@@ -240,29 +291,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           // A = P: K-major, K = keys; 4 k-steps per 64-key atom.  B = V: MN-major, 16 key rows = 2048 bytes.
           const uint64_t da = umma_smem_desc_sw128(sp + (k >> 2) * kAtomBytes + (k & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc_sw128(sv + k * 2048, kAtomBytes, 1024);
-          umma_bf16(tmem + 256, da, db, idesc_o, (j != 0 || k != 0) ? 1u : 0u);
+          umma_bf16(tmem + 256, da, db, idesc_o, (!pv.first || k != 0) ? 1u : 0u);
         }
         umma_commit(&o_full[b]);
         umma_commit(&v_empty[b]);
+        if (pv.last) umma_commit(o_done);
       };
-      for (int j = 0; j < n_tiles; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        mbar_wait(&k_full[b], ph, abort_flag, err, 200, 5);
-        mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 200, 6);
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + Smem::kK + b * kTileBytes);
+      Item next = RLK_ATTN_ITEM(first);
+      for (int w = first; w >= 0 && !*abort_flag; w -= step) {
+        const Item it = next;
+        if (w - step >= 0) next = RLK_ATTN_ITEM(w - step);
+        if (!it.ok || it.n_tiles == 0) continue;
+        mbar_wait(q_full, n_item & 1, abort_flag, err, 200, 2);
+        for (int j = 0; j < it.n_tiles; ++j) {
+          const int g = g0 + j, b = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          mbar_wait(&k_full[b], ph, abort_flag, err, 200, 5);
+          mbar_wait(&s_empty[b], ph ^ 1, abort_flag, err, 200, 6);
+          tc_fence_after();
+          const uint32_t sk = smem_u32(smem + Smem::kK + b * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
-          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          umma_bf16(tmem + b * 128, umma_smem_desc_sw128(sq + off, 16, 1024), umma_smem_desc_sw128(sk + off, 16, 1024),
-                    idesc_s, k != 0 ? 1u : 0u);
+          for (int k = 0; k < kD / 16; ++k) {
+            const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+            umma_bf16(tmem + b * 128, umma_smem_desc_sw128(sq + off, 16, 1024), umma_smem_desc_sw128(sk + off, 16, 1024),
+                      idesc_s, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[b]);
+          umma_commit(&k_empty[b]);
+          if (j + 1 == it.n_tiles) umma_commit(q_empty);  // every S product of the item has been issued
+          if (have_pend) issue_pv(pend);
+          pend = Pending{g, n_item, j == 0, j + 1 == it.n_tiles};
+          have_pend = true;
         }
-        umma_commit(&s_full[b]);
-        umma_commit(&k_empty[b]);
-        if (j >= 1) issue_pv(j - 1);
+        g0 += it.n_tiles;
+        ++n_item;
       }
-      if (n_tiles >= 1) issue_pv(n_tiles - 1);
+      if (have_pend) issue_pv(pend);
     }
   } else {
     // ------------------------------ softmax / output warps ------------------------------
@@ -270,123 +334,140 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     const int half = (warp - 2) >> 2;  // 0: keys / output columns 0..63, 1: 64..127
     const int r = quad * 32 + lane;    // query row within the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int qi = q0 + r;             // query index within the sequence
     constexpr int kHalf = 64;
     constexpr float kLazy = 8.f;  // the exponent base follows the row maximum only in steps of more than 2^8
     const uint32_t o_addr = tmem + 256 + half * kHalf + lane_addr;
-    float m_used = -INFINITY, l = 0.f;  // m_used: what the exponentials are taken against (log2 domain, scaled)
+    int g0 = 0, n_item = 0;
     PROF_DECL;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int b = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      const bool is_self = j >= n_prefix;
-      const int key0 = is_self ? (j - n_prefix) * kTileK : j * kTileK;
-      const int range_len = is_self ? sd.sk_len : sd.pk_len;
-      int limit = range_len - key0;  // keys [0, limit) of this tile are in range
-      if (is_self && causal) limit = min(limit, qi - key0 + 1);
-      limit -= half * kHalf;         // in this thread's 64 columns
-      PROF(0);
-      mbar_wait(&s_full[b], ph, abort_flag, err, 200, 8);
-      PROF(1);
-      tc_fence_after();
-      // this thread's half of the S row: both loads in flight, one wait, then the TMEM buffer is released
-      uint32_t t[kHalf];
-      tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
-      tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive_warp(&s_empty[b]);
-      PROF(2);
-      // a tile is mask-free for the whole warp in all but the diagonal and the last tile of a range
-      const bool masked = __any_sync(0xffffffffu, limit < kHalf);
-      float mx = masked ? max_half_row<true>(t, limit) : max_half_row<false>(t, limit);
-      // exchange the half-row maxima through shared memory; the second barrier keeps the next tile's writes
-      // behind this tile's reads
-      xmax_s[half * 128 + r] = mx;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");  // only the two warps that share these 32 rows
-      mx = fmaxf(mx, xmax_s[(half ^ 1) * 128 + r]);
-      asm volatile("bar.sync %0, 64;" ::"r"(5 + quad) : "memory");
-      PROF(3);
-      // Both threads of a row hold the same mx, so both take the same branch and keep the same m_used.
-      const float cand = fmaxf(m_used, mx * scale_log2e);
-      if (j == 0) {
-        m_used = cand;  // nothing accumulated yet
-      } else if (__any_sync(0xffffffffu, cand - m_used > kLazy)) {  // (-inf) - (-inf) = NaN compares false
-        const float alpha = cand == -INFINITY ? 1.f : fast_exp2(m_used - cand);  // m_used = -inf -> 0
-        // O holds the products up to tile j - 1 once P V of that tile has completed; P V of tile j is issued only
-        // after every softmax warp has arrived on p_full below, i.e. after this rescale.
-        mbar_wait(&o_full[b ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 200, 7);
+    Item next = RLK_ATTN_ITEM(first);
+    for (int w = first; w >= 0 && !*abort_flag; w -= step) {
+      const Item it = next;
+      if (w - step >= 0) next = RLK_ATTN_ITEM(w - step);
+      if (!it.ok) continue;
+      const SeqDesc& sd = it.sd;
+      const int qi = it.q0 + r;  // query index within the sequence
+      float m_used = -INFINITY, l = 0.f;  // m_used: what the exponentials are taken against (log2 domain, scaled)
+
+      for (int j = 0; j < it.n_tiles; ++j) {
+        const int g = g0 + j, b = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        const bool is_self = j >= it.n_prefix;
+        const int key0 = is_self ? (j - it.n_prefix) * kTileK : j * kTileK;
+        const int range_len = is_self ? sd.sk_len : sd.pk_len;
+        int limit = range_len - key0;  // keys [0, limit) of this tile are in range
+        if (is_self && causal) limit = min(limit, qi - key0 + 1);
+        limit -= half * kHalf;         // in this thread's 64 columns
+        PROF(0);
+        mbar_wait(&s_full[b], ph, abort_flag, err, 200, 8);
+        PROF(1);
         tc_fence_after();
-        uint32_t o0[32], o1[32];
-        tmem_ld_32x32b_x32(o_addr, o0);
-        tmem_ld_32x32b_x32(o_addr + 32, o1);
+        // this thread's half of the S row: both loads in flight, one wait, then the TMEM buffer is released
+        uint32_t t[kHalf];
+        tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[0]));
+        tmem_ld_32x32b_x32(tmem + b * 128 + half * kHalf + 32 + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&t[32]));
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
-          o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
-        }
-        tmem_st_32x32b_x32(o_addr, o0);
-        tmem_st_32x32b_x32(o_addr + 32, o1);
-        tmem_st_wait();
         tc_fence_before();
-        l *= alpha;
-        m_used = cand;
-      }
-      const float m_safe = m_used == -INFINITY ? 0.f : m_used;
-      // P[b] was the A operand of P V of tile j - 2: that product must have finished reading it
-      if (j >= 2) mbar_wait(&o_full[b], ((j - 2) >> 1) & 1, abort_flag, err, 200, 4);
-      // 64 keys of a row = one 128-byte swizzle row of atom `half`
-      uint8_t* prow = smem + Smem::kP + b * kTileBytes + half * kAtomBytes + r * 128;
-      const float sum = masked ? softmax_half_row<true>(t, limit, scale_log2e, m_safe, prow, r)
-                               : softmax_half_row<false>(t, limit, scale_log2e, m_safe, prow, r);
-      l += sum;  // this thread's share of the row sum; both halves use the same m_used
-      fence_proxy_async_smem();
-      mbar_arrive_warp(&p_full[b]);
-      PROF(4);
-    }
-
-    // this thread's 64 columns of O, once the last product has completed
-    uint32_t o[kHalf];  // fp32 bits
-    if (n_tiles >= 1) {
-      mbar_wait(&o_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag, err, 200, 9);
-      tc_fence_after();
-      tmem_ld_32x32b_x32(o_addr, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
-      tmem_ld_32x32b_x32(o_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
-      tmem_ld_wait();
-      tc_fence_before();
-    } else {
+        mbar_arrive_warp(&s_empty[b]);
+        PROF(2);
+        // a tile is mask-free for the whole warp in all but the diagonal and the last tile of a range
+        const bool masked = __any_sync(0xffffffffu, limit < kHalf);
+        float mx = masked ? max_half_row<true>(t, limit) : max_half_row<false>(t, limit);
+        // exchange the half-row maxima through shared memory; the second barrier keeps the next tile's writes
+        // behind this tile's reads
+        xmax_s[half * 128 + r] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");  // only the two warps that share these 32 rows
+        mx = fmaxf(mx, xmax_s[(half ^ 1) * 128 + r]);
+        asm volatile("bar.sync %0, 64;" ::"r"(5 + quad) : "memory");
+        PROF(3);
+        // Both threads of a row hold the same mx, so both take the same branch and keep the same m_used.
+        const float cand = fmaxf(m_used, mx * scale_log2e);
+        if (j == 0) {
+          m_used = cand;  // nothing accumulated yet
+        } else if (__any_sync(0xffffffffu, cand - m_used > kLazy)) {  // (-inf) - (-inf) = NaN compares false
+          const float alpha = cand == -INFINITY ? 1.f : fast_exp2(m_used - cand);  // m_used = -inf -> 0
+          // O holds the products up to tile j - 1 once P V of that tile has completed; P V of tile j is issued only
+          // after every softmax warp has arrived on p_full below, i.e. after this rescale.
+          mbar_wait(&o_full[b ^ 1], ((g - 1) >> 1) & 1, abort_flag, err, 200, 7);
+          tc_fence_after();
+          uint32_t o0[32], o1[32];
+          tmem_ld_32x32b_x32(o_addr, o0);
+          tmem_ld_32x32b_x32(o_addr + 32, o1);
+          tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < kHalf; ++i) o[i] = 0u;
-    }
-    const float m2 = m_used;
-
-    // total row sum = the two halves' shares (the exchange buffer is free: every reader passed barrier 2)
-    xmax_s[half * 128 + r] = l;
-    asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
-    l += xmax_s[(half ^ 1) * 128 + r];
-
-    if (qi < sd.q_len) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + static_cast<long long>(sd.q_start + qi) * ld_out + head * kD + half * kHalf;
-#pragma unroll
-      for (int c8 = 0; c8 < kHalf / 8; ++c8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[c8 * 8 + 2 * i]) * inv,
-                                                    __uint_as_float(o[c8 * 8 + 2 * i + 1]) * inv);
-          w[i] = *reinterpret_cast<uint32_t*>(&pk);
+          for (int i = 0; i < 32; ++i) {
+            o0[i] = __float_as_uint(__uint_as_float(o0[i]) * alpha);
+            o1[i] = __float_as_uint(__uint_as_float(o1[i]) * alpha);
+          }
+          tmem_st_32x32b_x32(o_addr, o0);
+          tmem_st_32x32b_x32(o_addr + 32, o1);
+          tmem_st_wait();
+          tc_fence_before();
+          l *= alpha;
+          m_used = cand;
         }
-        reinterpret_cast<uint4*>(dst)[c8] = make_uint4(w[0], w[1], w[2], w[3]);
+        const float m_safe = m_used == -INFINITY ? 0.f : m_used;
+        // P[b] was the A operand of P V two tiles ago: that product must have finished reading it.  (For the first
+        // two tiles of an item that product belongs to the previous item, whose o_done this thread has waited for.)
+        if (j >= 2) mbar_wait(&o_full[b], ((g - 2) >> 1) & 1, abort_flag, err, 200, 4);
+        // 64 keys of a row = one 128-byte swizzle row of atom `half`
+        uint8_t* prow = smem + Smem::kP + b * kTileBytes + half * kAtomBytes + r * 128;
+        const float sum = masked ? softmax_half_row<true>(t, limit, scale_log2e, m_safe, prow, r)
+                                 : softmax_half_row<false>(t, limit, scale_log2e, m_safe, prow, r);
+        l += sum;  // this thread's share of the row sum; both halves use the same m_used
+        fence_proxy_async_smem();
+        mbar_arrive_warp(&p_full[b]);
+        PROF(4);
       }
-      if (lse != nullptr && half == 0) {
-        lse[static_cast<long long>(head) * lse_head_stride + sd.q_start + qi] =
-            l > 0.f ? (m2 + log2f(l)) * kLn2 : -INFINITY;
+
+      // this thread's 64 columns of O, once the item's last product has completed; then TMEM is handed back so that
+      // the next item's first product may overwrite it while this item is normalised and stored
+      uint32_t o[kHalf];  // fp32 bits
+      if (it.n_tiles >= 1) {
+        mbar_wait(o_done, n_item & 1, abort_flag, err, 200, 9);
+        tc_fence_after();
+        tmem_ld_32x32b_x32(o_addr, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+        tmem_ld_32x32b_x32(o_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive_warp(o_free);
+        g0 += it.n_tiles;
+        ++n_item;
+      } else {
+#pragma unroll
+        for (int i = 0; i < kHalf; ++i) o[i] = 0u;
+      }
+      const float m2 = m_used;
+
+      // total row sum = the two halves' shares (the exchange buffer is free: every reader passed barrier 5 + quad;
+      // the barrier after the read keeps the next item's first write behind it)
+      xmax_s[half * 128 + r] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      l += xmax_s[(half ^ 1) * 128 + r];
+      asm volatile("bar.sync %0, 64;" ::"r"(5 + quad) : "memory");
+
+      if (qi < sd.q_len) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* dst = out + static_cast<long long>(sd.q_start + qi) * ld_out + it.head * kD + half * kHalf;
+#pragma unroll
+        for (int c8 = 0; c8 < kHalf / 8; ++c8) {
+          uint32_t wd[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[c8 * 8 + 2 * i]) * inv,
+                                                      __uint_as_float(o[c8 * 8 + 2 * i + 1]) * inv);
+            wd[i] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+          reinterpret_cast<uint4*>(dst)[c8] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+        }
+        if (lse != nullptr && half == 0) {
+          lse[static_cast<long long>(it.head) * lse_head_stride + sd.q_start + qi] =
+              l > 0.f ? (m2 + log2f(l)) * kLn2 : -INFINITY;
+        }
       }
     }
   }
+#undef RLK_ATTN_ITEM
 
   if (*abort_flag) {
     const uint64_t t0 = global_timer_ns();
@@ -411,10 +492,11 @@ void attention_forward(const AttnFwdArgs& a, cudaStream_t stream) {
   if (configured.first()) {
     cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kDynamic);
   }
-  const long long grid = static_cast<long long>(a.num_tiles) * a.heads_q;
+  const long long items = static_cast<long long>(a.num_tiles) * a.heads_q;
+  const long long grid = items < a.sm_count ? items : a.sm_count;  // one persistent CTA per SM (227 KB of shared memory each)
   attn_fwd_kernel<<<static_cast<unsigned int>(grid), kThreads, Smem::kDynamic, stream>>>(
-      tq, tk, tv, reinterpret_cast<const SeqDesc*>(a.seqs), reinterpret_cast<const int2*>(a.tiles), a.heads_q,
-      a.heads_q / a.heads_kv, a.causal ? 1 : 0, a.softmax_scale * kLog2e, a.out, a.ld_out, a.lse, a.lse_head_stride,
+      tq, tk, tv, reinterpret_cast<const SeqDesc*>(a.seqs), reinterpret_cast<const int2*>(a.tiles),
+      static_cast<int>(items), a.heads_q, a.heads_q / a.heads_kv, a.causal ? 1 : 0, a.softmax_scale * kLog2e, a.out, a.ld_out, a.lse, a.lse_head_stride,
       a.err, a.num_seqs, static_cast<int>(a.total_q), static_cast<int>(a.total_kv));
 }
 

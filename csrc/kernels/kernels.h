@@ -287,6 +287,7 @@ struct AttnFwdArgs {
   float* lse;  // [heads_q, total_q] or null
   long long lse_head_stride;
   uint32_t* err;
+  int sm_count = 148;  // CTAs of the persistent grid
 };
 void attention_forward(const AttnFwdArgs& args, cudaStream_t stream);
 

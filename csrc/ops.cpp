@@ -1088,6 +1088,7 @@ std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor
   a.heads_kv = static_cast<int>(k.size(1));
   a.seqs = seqs.data_ptr<int>();
   a.num_seqs = static_cast<int>(seqs.size(0));
+  a.sm_count = sm_count_of(q.get_device());
   a.tiles = tiles.data_ptr<int>();
   a.num_tiles = static_cast<int>(tiles.size(0));
   a.causal = causal;
