@@ -10,19 +10,21 @@
 // LSE, no tails, D == 128 only) are special cases.  The log-sum-exp of every row is returned so a
 // backward pass or a cross-rank merge can follow.
 //
-// One CTA = one 128-query tile of one head.  Warp 0 loads Q once and K/V tiles through a 2-stage TMA
-// ring; warp 1 issues S = Q K^T and O_j = P_j V_j on tcgen05 with S, O_j double-buffered in TMEM
-// (4 x 128 columns).  Eight softmax warps share the 128 query rows TWO threads per row: warps 2..5 own keys
-// 0..63 of every tile and output columns 0..63, warps 6..9 own keys 64..127 and output columns 64..127.
-// Each thread pulls its half of the S row with two tcgen05.ld in flight, the two halves exchange their row
+// Persistent CTAs (one per SM) walk the list of work items, one item = one 128-query tile of one head.  Warp 0 loads
+// Q once per item and K/V tiles through 2-stage TMA rings; warp 1 issues S = Q K^T and O += P V on tcgen05 with S
+// double-buffered in TMEM.  Rings, buffers and barriers run on across items, so the next item's Q, K and first S tile
+// are in flight while the softmax warps still normalise and store the current item's output.
+// Eight softmax warps share the 128 query rows TWO threads per row: warps 2..5 own keys 0..63 of every tile and output
+// columns 0..63, warps 6..9 own keys 64..127 and output columns 64..127 (four threads per row, and two independent
+// groups alternating over the key tiles, were both measured slower: 0.61 and 0.63 ms against 0.55 ms on the GRPO
+// layout).  Each thread pulls its half of the S row with two tcgen05.ld in flight, the two halves exchange their row
 // maximum through shared memory (one named barrier per tile), then each runs its half of the online softmax and
 // writes its 64-key atom of P as bf16 into the 128B-swizzled smem tile (the A operand of the second MMA).
 // O stays in TMEM: every P V product accumulates into the same 128 columns, and the softmax threads rescale them
 // (tcgen05.ld, multiply, tcgen05.st) only on tiles where some row's maximum grew by more than 2^8 over the value the
 // exponentials are taken against; until then that value lags the true maximum, which changes no result (numerator
 // and denominator carry the same factor, at most 2^8, far inside bf16 / fp32 range).  After the first tiles of a row
-// that is rare, so the per-tile accumulator traffic (128 fp32 per row in and out of registers) is gone.  Two warps
-// per scheduler hide the fixed-latency and TMEM-load stalls that one warp per scheduler exposes.
+// that is rare, so the per-tile accumulator traffic (128 fp32 per row in and out of registers) is gone.
 #include "../common/ptx.cuh"
 #include "../common/tensormap.h"
 #include "kernels.h"
