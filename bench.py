@@ -52,12 +52,17 @@ def parse_args():
     # dp: completions split over the ranks, fused ZeRO-1 step (default, fastest for an 8B model on 180 GB GPUs);
     # tp: tensor + sequence parallel layers and vocabulary-parallel LM head, every rank sees the whole group
     ap.add_argument("--parallelism", choices=["dp", "tp"], default="dp")
-    # data parallel only: "auto" / "on" split the shared prompt's forward/backward pass over the ranks, "off" runs it on every rank
-    ap.add_argument("--prompt-shard", choices=["auto", "on", "off"], default="auto")
+    # data parallel only: "on" splits the shared prompt's forward/backward pass over the ranks, "off" (default, faster at
+    # this prompt length) runs it on every rank
+    ap.add_argument("--prompt-shard", choices=["on", "off"], default="off")
     ap.add_argument("--skip-ops", action="store_true", help="leave out the per-operator measurements after the step")
     # development switches; any use marks the run as not comparable
     ap.add_argument("--dev-layers", type=int, default=0)
     ap.add_argument("--dev-group", type=int, default=0)
+    ap.add_argument("--dev-no-overlap", action="store_true",
+                    help="development only: data-parallel optimiser step after the backward pass instead of overlapped with it")
+    ap.add_argument("--dev-layers-per-bucket", type=int, default=0,
+                    help="development only: layers per bucket of the data-parallel optimiser step (library default 4)")
     ap.add_argument("--dev-micro-group", type=int, default=0,
                     help="development only: fix the completions per forward/backward pass instead of planning them")
     return ap.parse_args()
@@ -387,8 +392,14 @@ def main() -> None:
     elif world > 1:
         from rl_engine.parallel.data_parallel import ShardedGRPOTrainer
 
-        shard = {"auto": "auto", "on": True, "off": False}[args.prompt_shard]
-        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro, shard_prompt=shard)
+        shard = args.prompt_shard == "on"
+        dev_kw = {}
+        if args.dev_no_overlap:
+            dev_kw["overlap"] = False
+        if args.dev_layers_per_bucket:
+            dev_kw["layers_per_bucket"] = args.dev_layers_per_bucket
+        trainer = ShardedGRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro, shard_prompt=shard,
+                                     **dev_kw)
         parallelism = f"dp{world}-zero1-fused"
     else:
         trainer = GRPOTrainer(model, lr=1e-6, clip_eps=0.2, beta=0.04, micro_group=micro)
@@ -490,7 +501,8 @@ def main() -> None:
                             if getattr(trainer, "_prompt_shards", None) else "once per rank"),
             "peak_torch_allocated_gb": round(peak_allocated / 2**30, 1),
             "device_memory_in_use_gb": round((mem_total - mem_free) / 2**30, 1),
-            "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group),
+            "dev_overrides": bool(args.dev_layers or args.dev_group or args.dev_micro_group or args.dev_no_overlap
+                                  or args.dev_layers_per_bucket),
         },
         "clocks": sampler.summary(),
         "e2e": {

@@ -196,12 +196,14 @@ class ShardedGRPOTrainer(GRPOTrainer):
 
     def __init__(self, model: LlamaModel, *, group=None, lr: float = 1e-6, clip_eps: float = 0.2, beta: float = 0.04,
                  adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True,
-                 micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4, shard_prompt="auto") -> None:
-        """``shard_prompt``: the ranks split the shared prompt's forward/backward pass between them (zig-zag context
+                 micro_group="auto", overlap: bool = True, layers_per_bucket: int = 4, shard_prompt: bool = False) -> None:
+        """``shard_prompt=True``: the ranks split the shared prompt's forward/backward pass between them (zig-zag context
         parallelism) instead of each running all of it.  That is only right when every rank trains on completions of
-        the SAME prompt, so ``"auto"`` (default) turns it on once ``set_group_slice`` has been called, and only from
-        four ranks up: on two ranks the shorter backward pass hides less of the overlapped optimiser step than the
-        split saves (measured: 3 287 ms against 3 232 ms per Llama-3-8B step).  ``True`` / ``False`` force it.
+        the SAME prompt (``set_group_slice``).  Off by default: measured on the Llama-3-8B step (1 024-token prompt,
+        256 completions) it is no faster on 2, 4 or 8 ranks (3 287 / 1 708 / 852 ms against 3 232 / 1 712 / 838 ms),
+        because the prompt's backward pass, the last one of the step, is also the window under which the bucketed
+        optimiser step runs, and a pass an eighth as long hides an eighth as much; with the prompt inside the only
+        pass the whole backward hides it.  It pays when the prompt is long against the completions.
         Prompts whose length is not a multiple of ``32 * world`` run unsharded."""
         self.shard_prompt = shard_prompt
         self._group = group
@@ -235,7 +237,7 @@ class ShardedGRPOTrainer(GRPOTrainer):
     def _prompt_sharding(self, batch: GRPOBatch):
         """``{"cp": ..., "share_row": ...}`` for a prompt of this batch's length, or ``None`` if its pass is not sharded."""
         world = self.mem.world
-        on = (self._slice is not None and world >= 4) if self.shard_prompt == "auto" else bool(self.shard_prompt)
+        on = bool(self.shard_prompt)
         n = batch.prompt_ids.numel()
         if not on or world == 1 or n % (32 * world) or not self.prompt_cacheable(batch):
             return None
