@@ -302,6 +302,90 @@ digest64_kernel(const long long* __restrict__ words, long long n_words, const un
   if ((threadIdx.x & 31) == 0 && acc != 0ull) atomicAdd(out, acc);
 }
 
+// ---- many tensors in one launch ---------------------------------------------------------------------------------
+// A weight update is hundreds of tensors; one launch per tensor costs more in launch and binding overhead than the
+// bytes cost in bandwidth (291 launches for 8 GB: 15.9 ms against 2.9 ms for one).  The segment kernels take a device
+// table with one row per tensor and cut the whole update into units of kSegUnit elements; block b handles units b,
+// b + gridDim.x, ... and finds a unit's tensor by binary search over the table's running unit count.
+struct Segment {
+  long long src;         // device address of the tensor's first element
+  long long dst;         // byte offset of its copy in the destination window (cast) / result slot (digest)
+  long long n;           // elements (cast) / bytes (digest)
+  long long first_unit;  // units of all earlier rows
+};
+constexpr long long kSegUnit = 1 << 15;
+
+__device__ __forceinline__ int find_segment(const Segment* __restrict__ segs, int count, long long unit) {
+  int lo = 0, hi = count - 1;
+  while (lo < hi) {  // last row whose first_unit <= unit
+    const int mid = (lo + hi + 1) >> 1;
+    if (segs[mid].first_unit <= unit) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// dst_base[seg.dst ...] = cast(src tensor) for every row of the table (one destination: this GPU's own window).
+template <typename TS, typename TD>
+__global__ void __launch_bounds__(256)
+cast_segments_kernel(const Segment* __restrict__ segs, int count, long long total_units, unsigned char* __restrict__ dst_base) {
+  for (long long unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+    const Segment sg = segs[find_segment(segs, count, unit)];
+    const long long e0 = (unit - sg.first_unit) * kSegUnit;
+    const long long len = min(kSegUnit, sg.n - e0);
+    const TS* src = reinterpret_cast<const TS*>(sg.src) + e0;
+    TD* dst = reinterpret_cast<TD*>(dst_base + sg.dst) + e0;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    const long long n8 = vec ? len / 8 : 0;
+    for (long long i = threadIdx.x; i < n8; i += 4 * blockDim.x) {
+      float f[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * blockDim.x < n8) load8(src + (i + u * blockDim.x) * 8, f[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * blockDim.x < n8) store8(dst + (i + u * blockDim.x) * 8, f[u]);
+    }
+    for (long long i = n8 * 8 + threadIdx.x; i < len; i += blockDim.x) store1(dst + i, load1(src + i));
+  }
+}
+
+// results[seg.dst] += digest of the tensor's bytes, for every row of the table (same function as digest64_kernel: the
+// terms carry their word index, so any partition into units gives the same 64 bits).
+__global__ void __launch_bounds__(256)
+digest_segments_kernel(const Segment* __restrict__ segs, int count, long long total_units,
+                       unsigned long long* __restrict__ results) {
+  constexpr long long kWordsPerUnit = kSegUnit;  // 64-bit words
+  for (long long unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+    const Segment sg = segs[find_segment(segs, count, unit)];
+    const long long n_words = sg.n / 8;
+    const int tail_bytes = static_cast<int>(sg.n - n_words * 8);
+    const long long w0 = (unit - sg.first_unit) * kWordsPerUnit;
+    const long long w1 = min(w0 + kWordsPerUnit, n_words);
+    const long long* words = reinterpret_cast<const long long*>(sg.src);
+    unsigned long long acc = 0ull;
+    // w0 is even, so pairs of words are 16-byte aligned whenever the tensor is
+    for (long long i = w0 + 2 * threadIdx.x; i + 1 < w1; i += 2 * blockDim.x) {
+      const longlong2 w = *reinterpret_cast<const longlong2*>(words + i);
+      acc += digest_term(w.x, static_cast<unsigned long long>(i));
+      acc += digest_term(w.y, static_cast<unsigned long long>(i + 1));
+    }
+    if (threadIdx.x == 0) {
+      if (((w1 - w0) & 1) && w1 > w0) acc += digest_term(words[w1 - 1], static_cast<unsigned long long>(w1 - 1));
+      const bool last_unit = w0 + kWordsPerUnit >= n_words;
+      if (last_unit && tail_bytes > 0) {
+        const unsigned char* tail = reinterpret_cast<const unsigned char*>(sg.src) + n_words * 8;
+        unsigned long long w = 0ull;
+        for (int b = 0; b < tail_bytes; ++b) w |= static_cast<unsigned long long>(tail[b]) << (8 * b);
+        acc += digest_term(static_cast<long long>(w), static_cast<unsigned long long>(n_words));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if ((threadIdx.x & 31) == 0 && acc != 0ull) atomicAdd(results + sg.dst, acc);
+  }
+}
+
 PeerPtrs make_ptrs(void* const* p, int world) {
   PeerPtrs out;
   for (int r = 0; r < 8; ++r) out.p[r] = r < world ? p[r] : nullptr;
@@ -393,6 +477,35 @@ void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_d
     else RLK_CB(__half, __half);
   }
 #undef RLK_CB
+}
+
+void cast_segments(const void* table, int count, long long total_units, int src_dtype, int dst_dtype, void* dst_base,
+                   cudaStream_t stream) {
+  if (count <= 0 || total_units <= 0) return;
+  const int grid = static_cast<int>(total_units < 148LL * 8 ? total_units : 148LL * 8);
+  const Segment* segs = static_cast<const Segment*>(table);
+  unsigned char* dst = static_cast<unsigned char*>(dst_base);
+#define RLK_CS(TS, TD) cast_segments_kernel<TS, TD><<<grid, 256, 0, stream>>>(segs, count, total_units, dst)
+  if (src_dtype == 0) {
+    if (dst_dtype == 0) RLK_CS(float, float);
+    else if (dst_dtype == 1) RLK_CS(float, __nv_bfloat16);
+    else RLK_CS(float, __half);
+  } else if (src_dtype == 1) {
+    if (dst_dtype == 0) RLK_CS(__nv_bfloat16, float);
+    else if (dst_dtype == 1) RLK_CS(__nv_bfloat16, __nv_bfloat16);
+    else RLK_CS(__nv_bfloat16, __half);
+  } else {
+    if (dst_dtype == 0) RLK_CS(__half, float);
+    else if (dst_dtype == 1) RLK_CS(__half, __nv_bfloat16);
+    else RLK_CS(__half, __half);
+  }
+#undef RLK_CS
+}
+
+void digest_segments(const void* table, int count, long long total_units, unsigned long long* results, cudaStream_t stream) {
+  if (count <= 0 || total_units <= 0) return;
+  const int grid = static_cast<int>(total_units < 148LL * 8 ? total_units : 148LL * 8);
+  digest_segments_kernel<<<grid, 256, 0, stream>>>(static_cast<const Segment*>(table), count, total_units, results);
 }
 
 }  // namespace rlk

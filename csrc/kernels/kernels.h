@@ -346,6 +346,11 @@ void zero1_fused_step(void* const* grads, void* const* params, int rank, int wor
 void peer_sum(void* const* srcs, int world, long long n, bool src_fp32, void* out, bool out_fp32, cudaStream_t stream);
 // 64-bit position-weighted digest of ``nbytes`` bytes at ``data`` (16-byte aligned), added into *out.
 void weight_digest64(const void* data, long long nbytes, unsigned long long* out, cudaStream_t stream);
+// Many tensors in one launch.  ``table``: device rows of four int64 (source address, destination byte offset or result
+// slot, elements or bytes, units of all earlier rows), a unit being 32768 elements (cast) or 64-bit words (digest).
+void cast_segments(const void* table, int count, long long total_units, int src_dtype, int dst_dtype, void* dst_base,
+                   cudaStream_t stream);
+void digest_segments(const void* table, int count, long long total_units, unsigned long long* results, cudaStream_t stream);
 void cast_broadcast(const void* src, int src_dtype, void* const* dsts, int dst_dtype, int world, long long n,
                     cudaStream_t stream);
 

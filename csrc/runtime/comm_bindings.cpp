@@ -107,6 +107,49 @@ void py_weight_digest(const Tensor& t, Tensor digests, int64_t slot) {
                   reinterpret_cast<unsigned long long*>(digests.data_ptr<int64_t>()) + slot, cur_stream(t.get_device()));
 }
 
+void check_segment_table(const Tensor& table, const char* who) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == torch::kInt64 && table.is_contiguous() && table.dim() == 2 &&
+                  table.size(1) == 4,
+              "rl_engine.", who, ": table must be a contiguous CUDA int64 tensor [tensors, 4]");
+}
+
+// One launch for a whole update: every row of ``table`` (source address, destination byte offset, elements, units of
+// the earlier rows; 32768 elements per unit) is cast from ``src_dtype`` to ``dst_dtype`` into ``dst_base + offset``.
+void py_cast_segments(const Tensor& table, int64_t total_units, int64_t src_dtype_code, int64_t dst_dtype_code,
+                      uint64_t dst_base) {
+  check_segment_table(table, "cast_segments");
+  TORCH_CHECK(src_dtype_code >= 0 && src_dtype_code <= 2 && dst_dtype_code >= 0 && dst_dtype_code <= 2,
+              "rl_engine.cast_segments: dtype codes are 0 (float32), 1 (bfloat16), 2 (float16)");
+  const c10::cuda::CUDAGuard guard(table.device());
+  cast_segments(table.data_ptr(), static_cast<int>(table.size(0)), total_units, static_cast<int>(src_dtype_code),
+                static_cast<int>(dst_dtype_code), reinterpret_cast<void*>(dst_base), cur_stream(table.get_device()));
+}
+
+// digests[row.slot] += digest of the row's bytes, for every row of ``table`` (source address, slot, bytes, units of the
+// earlier rows; 32768 64-bit words per unit).  Every source must be 16-byte aligned.
+void py_digest_segments(const Tensor& table, int64_t total_units, Tensor digests) {
+  check_segment_table(table, "digest_segments");
+  TORCH_CHECK(digests.is_cuda() && digests.scalar_type() == torch::kInt64 && digests.is_contiguous() &&
+                  digests.get_device() == table.get_device(),
+              "rl_engine.digest_segments: digests must be a contiguous int64 tensor on the table's device");
+  const c10::cuda::CUDAGuard guard(table.device());
+  digest_segments(table.data_ptr(), static_cast<int>(table.size(0)), total_units,
+                  reinterpret_cast<unsigned long long*>(digests.data_ptr<int64_t>()), cur_stream(table.get_device()));
+}
+
+// Copy-engine transfer of ``nbytes`` from ``src`` to a device address that may live on a peer GPU (a mapped window of
+// the symmetric heap), in stream order.  Plain bytes need no SM: the copy engines reach the NVLink rate where
+// store loops from the SMs measured 0.4 of it.
+void py_peer_copy(uint64_t dst, const Tensor& src, int64_t nbytes) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "rl_engine.peer_copy: src must be a contiguous CUDA tensor");
+  TORCH_CHECK(nbytes >= 0 && nbytes <= static_cast<int64_t>(src.numel()) * static_cast<int64_t>(src.element_size()),
+              "rl_engine.peer_copy: nbytes exceeds the source tensor");
+  if (nbytes == 0) return;
+  const c10::cuda::CUDAGuard guard(src.device());
+  C10_CUDA_CHECK(cudaMemcpyAsync(reinterpret_cast<void*>(dst), src.data_ptr(), static_cast<size_t>(nbytes),
+                                 cudaMemcpyDeviceToDevice, cur_stream(src.get_device())));
+}
+
 void check_rows(const Tensor& t, const char* n) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && t.size(1) % 8 == 0 &&
                   t.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0,
@@ -187,6 +230,9 @@ void bind_comm(pybind11::module_& m) {
   m.def("peer_sum", counted("rlk::peer_sum", &py_peer_sum));
   m.def("cast_broadcast", counted("rlk::cast_broadcast", &py_cast_broadcast));
   m.def("weight_digest", counted("rlk::weight_digest", &py_weight_digest));
+  m.def("cast_segments", counted("rlk::cast_segments", &py_cast_segments));
+  m.def("digest_segments", counted("rlk::digest_segments", &py_digest_segments));
+  m.def("peer_copy", &py_peer_copy);
 }
 
 }  // namespace rlk

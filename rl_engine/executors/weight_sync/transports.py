@@ -341,6 +341,9 @@ class IPCWeightBridge(BridgeStateMachine):
 
 
 # ----------------------------------------------------------------------------- NVLink broadcast
+_CAST_UNIT = 1 << 15  # elements per work unit of the table-driven cast kernel
+
+
 class NVLinkBroadcastBridge(BridgeStateMachine):
     """Trainer -> all rollout ranks of the node through symmetric memory, with the dtype cast fused in.
 
@@ -386,9 +389,13 @@ class NVLinkBroadcastBridge(BridgeStateMachine):
         ranks = list(ranks)
         if hi <= lo or not ranks:
             return
+        src = self.window.local[lo:hi]
+        if hasattr(ext, "peer_copy"):  # plain bytes: one copy-engine transfer per destination, no SM involved
+            for r in ranks:
+                ext.peer_copy(self.window.ptrs[r] + lo, src, hi - lo)
+            return
         n = (hi - lo + 3) // 4 * 4  # whole 32-bit words; the window is padded to 256 bytes
-        src = self.window.local[lo : lo + n].view(torch.float32)
-        ext.cast_broadcast(src, [self.window.ptrs[r] + lo for r in ranks], 0)
+        ext.cast_broadcast(self.window.local[lo : lo + n].view(torch.float32), [self.window.ptrs[r] + lo for r in ranks], 0)
 
     def _capture(self, tensors, update_id):
         from rl_engine.kernels.ops.base import require_ext
@@ -404,33 +411,50 @@ class NVLinkBroadcastBridge(BridgeStateMachine):
             )
         code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
         everyone = list(range(mem.world))
-        first_hop = [mem.rank] if self.relay else everyone  # relay: cast into the own window only
+        others = [r for r in everyone if r != mem.rank]
         mem.barrier()  # consumers are done with the previous contents of the window
-        stored = {}
+        # Step 1: cast everything into this rank's OWN window.  Floating-point tensors of one (source, target) type pair
+        # go through one table-driven launch; the others (integers, booleans) move as raw 32-bit words one by one.
+        stored, groups, keep = {}, {}, []
+        batched = hasattr(ext, "cast_segments")
         for name, t in tensors.items():
             e = entries[name]
             dst_dtype = out_dtype(t)
             src = t.detach().contiguous()
-            dsts = [self.window.ptrs[r] + e["offset"] for r in first_hop]
+            stored[name] = self._view(e, dst_dtype)
+            if src.numel() == 0:
+                continue
             if src.dtype in code and dst_dtype in code:
-                ext.cast_broadcast(src, dsts, code[dst_dtype])
+                if batched:
+                    keep.append(src)  # the table holds raw addresses: the tensors must outlive the launch call
+                    groups.setdefault((code[src.dtype], code[dst_dtype]), []).append((src.data_ptr(), e["offset"], src.numel()))
+                else:
+                    ext.cast_broadcast(src, [self.window.ptrs[mem.rank] + e["offset"]], code[dst_dtype])
             else:  # integer / bool tensors: move the raw bytes (bit-exact fp32 load/store, no arithmetic)
                 raw = src.view(-1).view(torch.uint8) if src.dtype != torch.bool else src.view(-1).to(torch.uint8)
                 pad = (-raw.numel()) % 4
                 if pad:
                     raw = torch.cat([raw, raw.new_zeros(pad)])
-                ext.cast_broadcast(raw.view(torch.float32), dsts, 0)
-            stored[name] = self._view(e, dst_dtype)
+                ext.cast_broadcast(raw.view(torch.float32), [self.window.ptrs[mem.rank] + e["offset"]], 0)
+        for (src_code, dst_code), segs in groups.items():
+            rows, units = [], 0
+            for ptr, offset, numel in segs:
+                rows.append((ptr, offset, numel, units))
+                units += (numel + _CAST_UNIT - 1) // _CAST_UNIT
+            table = torch.tensor(rows, dtype=torch.int64).to(self.window.local.device)
+            ext.cast_segments(table, units, src_code, dst_code, self.window.ptrs[mem.rank])
+        del keep
         self._publishes += 1
         if self.relay:
             slices = self._slices(total)
             self.header.local.copy_(torch.tensor([total, self._publishes, mem.rank, 0, 0, 0, 0, 0], dtype=torch.int64))
-            others = [r for r in everyone if r != mem.rank]
             ext.cast_broadcast(self.header.local.view(torch.float32), [self.header.ptrs[r] for r in others], 0)
             for r in others:  # hop 1: slice r goes to rank r only
                 self._raw_store(ext, *slices[r], [r])
             mem.barrier()  # every rank holds its slice (and the header)
             self._raw_store(ext, *slices[mem.rank], others)  # hop 2: the source forwards its own slice like everyone
+        else:
+            self._raw_store(ext, 0, total, others)  # the whole window to every peer
         mem.barrier()  # every rank's window is complete
         block = {"format": NVLINK_BROADCAST_FORMAT, "world_size": mem.world, "tensors": entries,
                  "requested_nbytes": total, "relay": bool(self.relay)}
