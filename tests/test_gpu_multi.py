@@ -73,6 +73,39 @@ def test_weight_digest_kernel_matches_the_tensor_op_form(dtype, numel):
     assert many["a"] == got and many["b"] != got
 
 
+@pytest.mark.parametrize("src_dtype,dst_dtype", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16),
+                                                 (torch.bfloat16, torch.float32), (torch.float16, torch.float32)])
+def test_table_driven_cast_matches_per_tensor_casts(src_dtype, dst_dtype):
+    """``cast_segments`` (one launch for many tensors) against ``Tensor.to``: sizes below, at and above one work unit,
+    a size that is not a multiple of eight, a source that is not 16-byte aligned; bytes between the tensors stay
+    untouched.  ``peer_copy`` moves plain bytes in stream order."""
+    from rl_engine.kernels.ops.base import require_ext
+
+    ext = require_ext()
+    code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+    sizes = [1, 7, 4096, 32768, 32769, 100003, 3 * 32768]
+    g = torch.Generator(device="cuda").manual_seed(5)
+    pool = torch.randn(sum(sizes) + 64, device="cuda", generator=g).to(src_dtype)
+    item = torch.empty((), dtype=dst_dtype).element_size()
+    window = torch.full((sum((n * item + 255) // 256 * 256 + 256 for n in sizes),), 0xAB, dtype=torch.uint8, device="cuda")
+    rows, units, cursor, start, expected = [], 0, 0, 1, []  # start = 1: the first source is deliberately misaligned
+    for n in sizes:
+        src = pool[start : start + n]
+        rows.append((src.data_ptr(), cursor, n, units))
+        expected.append((cursor, src.to(dst_dtype)))
+        units += (n + 32767) // 32768
+        cursor += (n * item + 255) // 256 * 256 + 256
+        start += n + (8 if n % 2 else 0)
+    ext.cast_segments(torch.tensor(rows, dtype=torch.int64).cuda(), units, code[src_dtype], code[dst_dtype], window.data_ptr())
+    for (offset, want), n in zip(expected, sizes):
+        got = window[offset : offset + n * item].view(dst_dtype)
+        assert torch.equal(got, want)
+        assert bool((window[offset + n * item : offset + n * item + 16] == 0xAB).all())  # nothing written past the tensor
+    copy = torch.zeros_like(window)
+    ext.peer_copy(copy.data_ptr() + 256, window[256:], window.numel() - 256)
+    assert torch.equal(copy[256:], window[256:]) and int(copy[:256].sum()) == 0
+
+
 def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge():
     """The weight-sync transport over symmetric memory on one rank: fp32 trainer weights land in the window as bf16
     through the cast+broadcast kernel, the manifest validates, tampering is caught, a too-small window is refused."""
