@@ -42,7 +42,7 @@ sys.path.insert(0, os.path.join(HERE, "_ref"))
 PROMPT_LEN, GROUP, COMPLETION_LEN = 1024, 256, 512
 # (gradient checkpointing, sequences per micro-batch), tried in this order; the first that fits runs
 MEMORY_PLANS = [(False, 8), (False, 4), (False, 2), (True, 8)]
-OPS_BUDGET_S = 150.0  # the operator measurements stop taking new samples after this many seconds
+OPS_TIME_LIMIT_S = 150.0  # the operator measurements stop taking new samples after this many seconds
 
 
 def unavailable(reason: str) -> None:
@@ -281,7 +281,7 @@ def measure_ops(torch, dist, kernel_registry, device, rank, world):
     """Same shapes, inputs, counting and memory accounting as ``measure_ops`` of ``bench.py``, through the
     reference's own ``kernel_registry`` / ``SamplerBackend``."""
     out = {}
-    deadline = time.perf_counter() + OPS_BUDGET_S
+    deadline = time.perf_counter() + OPS_TIME_LIMIT_S
     try:
         op = kernel_registry.get_op("linear_logp")
         d, v = 4096, 128256

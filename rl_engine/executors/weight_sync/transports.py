@@ -384,6 +384,16 @@ class NVLinkBroadcastBridge(BridgeStateMachine):
         per = ((total + world - 1) // world + 255) // 256 * 256
         return [(min(r * per, total), min((r + 1) * per, total)) for r in range(world)]
 
+    def _forward_order(self, source: int):
+        """Destinations of this rank's slice in hop 2: every rank but itself and the source (which has everything),
+        starting with its right-hand neighbour.  Every rank issues its transfers one after the other; if all of them
+        started with rank 0, then 1, ..., all of them would write into the same GPU at the same time and share its
+        ingress (measured on 8 ranks: 37 ms for 7 GB per rank); rotated, the k-th transfers of all ranks form a
+        permutation."""
+        mem = self.memory
+        order = [(mem.rank + k) % mem.world for k in range(1, mem.world)]
+        return [r for r in order if r != source or source == mem.rank]
+
     def _raw_store(self, ext, lo: int, hi: int, ranks) -> None:
         """Copies window bytes ``[lo, hi)`` of this rank into the same place of ``ranks``' windows, bit for bit."""
         ranks = list(ranks)
@@ -452,7 +462,7 @@ class NVLinkBroadcastBridge(BridgeStateMachine):
             for r in others:  # hop 1: slice r goes to rank r only
                 self._raw_store(ext, *slices[r], [r])
             mem.barrier()  # every rank holds its slice (and the header)
-            self._raw_store(ext, *slices[mem.rank], others)  # hop 2: the source forwards its own slice like everyone
+            self._raw_store(ext, *slices[mem.rank], self._forward_order(mem.rank))  # hop 2: the source forwards too
         else:
             self._raw_store(ext, 0, total, others)  # the whole window to every peer
         mem.barrier()  # every rank's window is complete
@@ -472,7 +482,7 @@ class NVLinkBroadcastBridge(BridgeStateMachine):
             mem.barrier()  # this rank's slice and the header have landed
             total, _count, source = (int(x) for x in self.header.local[:3].tolist())  # one small device -> host read
             lo, hi = self._slices(total)[mem.rank]
-            self._raw_store(require_ext(), lo, hi, [r for r in range(mem.world) if r not in (mem.rank, source)])
+            self._raw_store(require_ext(), lo, hi, self._forward_order(source))
         mem.barrier()  # window complete
 
     def sync(self, model, *, weight_version: int, source_rank: int = 0, group=None, metadata=None, dist=None):
