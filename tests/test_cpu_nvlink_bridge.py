@@ -149,6 +149,24 @@ def test_relay_mode_fills_every_window_with_less_traffic_from_the_source(fake_wo
     assert torch.equal(direct_world.windows[2][: total], windows[2])
 
 
+def test_hop_two_destinations_are_rotated_and_skip_the_source(fake_world):
+    """Every rank forwards its slice to all ranks that still miss it, starting with its right-hand neighbour, so that
+    the k-th transfers of the ranks do not all land on one GPU."""
+    world = 3
+    bridges = [NVLinkBroadcastBridge(fake_world.memory(r), 1 << 15) for r in range(world)]
+    source = 0
+    orders = [b._forward_order(source) for b in bridges]
+    assert orders[0] == [1, 2]                      # the source forwards its own slice to everybody else
+    assert orders[1] == [2] and orders[2] == [1]    # consumers skip themselves and the source
+    big = FakeWorld(8, 1 << 12)
+    eight = [NVLinkBroadcastBridge(big.memory(r), 1 << 10) for r in range(8)]
+    firsts = [b._forward_order(0)[0] for b in eight]
+    assert len(set(firsts)) >= 7                    # first transfers go to (almost) all different ranks
+    for r, b in enumerate(eight):
+        order = b._forward_order(0)
+        assert r not in order and len(order) == len(set(order)) == (7 if r == 0 else 6)
+
+
 def test_sync_is_one_collective_call(fake_world):
     bridges = [NVLinkBroadcastBridge(fake_world.memory(r), 1 << 15, relay=False) for r in range(3)]
     model = _model()
