@@ -216,6 +216,14 @@ int rmsnorm_bwd_chunks(long long rows, int rows_per_cta = 0);
 void rmsnorm_backward(const void* x, long long ldx, int x_dtype, const void* w, int w_dtype, const void* dy,
                       long long lddy, const float* rstd, void* dx, long long lddx, long long rows, int D,
                       float* dw_part, void* dw, cudaStream_t stream, int rows_per_cta = 0);
+// Per-head RMSNorm (head_dim 128) of the q and k heads inside a packed qkv buffer [tokens, (hq + 2 hkv) * 128]; v is copied.
+// Backward writes per-block partial weight gradients ``part [qk_norm_blocks(...)][2][128]`` (q, then k).
+int qk_norm_blocks(long long tokens, int heads);
+void qk_norm_forward(const __nv_bfloat16* qkv, long long ld, __nv_bfloat16* out, long long ldo, const __nv_bfloat16* wq,
+                     const __nv_bfloat16* wk, long long tokens, int hq, int hkv, float eps, cudaStream_t stream);
+void qk_norm_backward(const __nv_bfloat16* qkv, long long ld, const __nv_bfloat16* dout, long long ldg,
+                      __nv_bfloat16* dqkv, long long ldd, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
+                      long long tokens, int hq, int hkv, float eps, float* part, cudaStream_t stream);
 // up == null -> plain SiLU
 void swiglu_forward(const void* gate, long long ldg, const void* up, long long ldu, int dtype, void* out, long long ldo,
                     bool out_fp32, long long rows, int F, cudaStream_t stream);

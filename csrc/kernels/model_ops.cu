@@ -838,4 +838,160 @@ void adamw_step(void* p, int p_dtype, float* master, short* residual, const void
   });
 }
 
+
+// ---- per-head RMSNorm of q and k inside a packed qkv buffer (Qwen3-style q/k norm, head_dim 128) -------------------
+// qkv [T, (hq + 2 hkv) * 128] bf16.  Forward: out = qkv with every q head row normalised with w_q [128] and every k
+// head row with w_k [128]; v rows are copied.  One half-warp per (token, head) row: 16 lanes x 8 elements.  The
+// composition it replaces (two strided slices made contiguous, two generic RMSNorm launches, one concatenation) moves
+// the buffer about five times and runs the wide-row kernels on 128-element rows.
+namespace {
+
+constexpr int kQkHead = 128;
+
+// Sum over the 16 lanes of this thread's half of the warp.  The two halves of a warp work on different rows and may
+// take different branches, so the shuffle names only the lanes of its own half.
+__device__ __forceinline__ float half_warp_sum(float v) {
+  const unsigned int mask = 0xffffu << (threadIdx.x & 16);
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) v += __shfl_xor_sync(mask, v, off);
+  return v;
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+
+__global__ void __launch_bounds__(256)
+qk_norm_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat16* __restrict__ out, long long ldo,
+                   const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk, long long tokens, int hq,
+                   int hkv, float eps) {
+  const int heads = hq + 2 * hkv;
+  const long long rows = tokens * heads;
+  const int sub = threadIdx.x & 15;
+  const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
+  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  for (long long row = first; row < rows; row += stride) {  // uniform per half-warp
+    const long long t = row / heads;
+    const int h = static_cast<int>(row - t * heads);
+    const uint4 raw = *reinterpret_cast<const uint4*>(qkv + t * ld + h * kQkHead + sub * 8);
+    uint4 res = raw;
+    if (h < hq + hkv) {
+      float x[8];
+      unpack_bf16x8(raw, x);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+      ss = half_warp_sum(ss);
+      const float rstd = rsqrtf(ss * (1.f / kQkHead) + eps);
+      float w[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>((h < hq ? wq : wk) + sub * 8), w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = x[j] * rstd * w[j];
+      res = pack_bf16x8(x);
+    }
+    *reinterpret_cast<uint4*>(out + t * ldo + h * kQkHead + sub * 8) = res;
+  }
+}
+
+// dqkv from d(out); per-block partial weight gradients part[block][2][128] (q then k), summed later in block order.
+__global__ void __launch_bounds__(256)
+qk_norm_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const __nv_bfloat16* __restrict__ dout,
+                   long long ldg, __nv_bfloat16* __restrict__ dqkv, long long ldd, const __nv_bfloat16* __restrict__ wq,
+                   const __nv_bfloat16* __restrict__ wk, long long tokens, int hq, int hkv, float eps,
+                   float* __restrict__ part) {
+  __shared__ float red[16][2][kQkHead];  // one slab per half-warp of the block
+  const int heads = hq + 2 * hkv;
+  const long long rows = tokens * heads;
+  const int sub = threadIdx.x & 15, hw = threadIdx.x >> 4;
+  const long long first = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 4;
+  const long long stride = (static_cast<long long>(gridDim.x) * blockDim.x) >> 4;
+  float gq[8], gk[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) gq[j] = gk[j] = 0.f;
+  float wqf[8], wkf[8];
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(wq + sub * 8), wqf);
+  unpack_bf16x8(*reinterpret_cast<const uint4*>(wk + sub * 8), wkf);
+  for (long long row = first; row < rows; row += stride) {
+    const long long t = row / heads;
+    const int h = static_cast<int>(row - t * heads);
+    const uint4 graw = *reinterpret_cast<const uint4*>(dout + t * ldg + h * kQkHead + sub * 8);
+    uint4 res = graw;
+    if (h < hq + hkv) {
+      float x[8], dy[8];
+      unpack_bf16x8(*reinterpret_cast<const uint4*>(qkv + t * ld + h * kQkHead + sub * 8), x);
+      unpack_bf16x8(graw, dy);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(x[j], x[j], ss);
+      ss = half_warp_sum(ss);
+      const float rstd = rsqrtf(ss * (1.f / kQkHead) + eps);
+      const bool is_q = h < hq;
+      float dot = 0.f, xh[8], dyw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[j] = x[j] * rstd;
+        dyw[j] = dy[j] * (is_q ? wqf[j] : wkf[j]);
+        dot = fmaf(dyw[j], xh[j], dot);
+      }
+      dot = half_warp_sum(dot) * (1.f / kQkHead);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        x[j] = rstd * (dyw[j] - xh[j] * dot);
+        if (is_q) gq[j] = fmaf(dy[j], xh[j], gq[j]);
+        else gk[j] = fmaf(dy[j], xh[j], gk[j]);
+      }
+      res = pack_bf16x8(x);
+    }
+    *reinterpret_cast<uint4*>(dqkv + t * ldd + h * kQkHead + sub * 8) = res;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    red[hw][0][sub * 8 + j] = gq[j];
+    red[hw][1][sub * 8 + j] = gk[j];
+  }
+  __syncthreads();
+  // 256 threads = 2 x 128 columns: sum the 16 half-warp slabs in slab order
+  const int which = threadIdx.x >> 7, col = threadIdx.x & 127;
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc += red[i][which][col];
+  part[(static_cast<long long>(blockIdx.x) * 2 + which) * kQkHead + col] = acc;
+}
+
+}  // namespace
+
+int qk_norm_blocks(long long tokens, int heads) {
+  const long long half_warps = tokens * heads;
+  long long blocks = (half_warps + 15) / 16;
+  const long long cap = 148LL * 8;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+void qk_norm_forward(const __nv_bfloat16* qkv, long long ld, __nv_bfloat16* out, long long ldo, const __nv_bfloat16* wq,
+                     const __nv_bfloat16* wk, long long tokens, int hq, int hkv, float eps, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  qk_norm_fwd_kernel<<<qk_norm_blocks(tokens, hq + 2 * hkv), 256, 0, stream>>>(qkv, ld, out, ldo, wq, wk, tokens, hq, hkv, eps);
+}
+
+void qk_norm_backward(const __nv_bfloat16* qkv, long long ld, const __nv_bfloat16* dout, long long ldg,
+                      __nv_bfloat16* dqkv, long long ldd, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
+                      long long tokens, int hq, int hkv, float eps, float* part, cudaStream_t stream) {
+  if (tokens <= 0) return;
+  qk_norm_bwd_kernel<<<qk_norm_blocks(tokens, hq + 2 * hkv), 256, 0, stream>>>(qkv, ld, dout, ldg, dqkv, ldd, wq, wk, tokens,
+                                                                             hq, hkv, eps, part);
+}
+
 }  // namespace rlk

@@ -279,7 +279,7 @@ Tensor tp_gemm_rs(const Tensor& a_in, const Tensor& b, bool b_mn, int64_t rank, 
 //           [G * K, N] (b_mn = true, used for dX = dY * W_g), tile_group int32 [rows / 128]  -> out [rows, N]
 //   mode 2: a [rows, M], b [rows, N], group_offsets int32 [G + 1]  -> out [G * M, N] = per-group a^T b
 Tensor grouped_gemm(const Tensor& a, const Tensor& b, int64_t mode, const Tensor& table, int64_t num_groups, bool b_mn,
-                    bool out_fp32) {
+                    bool out_fp32, std::optional<Tensor> out) {
   check_rowmajor(a, "a");
   check_rowmajor(b, "b");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "grouped_gemm: bf16 operands only");
@@ -308,7 +308,14 @@ Tensor grouped_gemm(const Tensor& a, const Tensor& b, int64_t mode, const Tensor
     const int64_t N = b_mn ? b.size(1) : b.size(0) / num_groups;
     TORCH_CHECK(b_mn ? (b.size(0) == num_groups * K) : (b.size(1) == K && b.size(0) == num_groups * N), "grouped_gemm(1): b has the wrong shape");
     TORCH_CHECK(!b_mn || K % 64 == 0, "grouped_gemm(1): contraction size must be a multiple of 64 for stacked MN-major b");
-    d = torch::empty({a.size(0), N}, odt);
+    if (out.has_value()) {  // the caller's buffer (e.g. a window of symmetric memory that peers read afterwards)
+      d = *out;
+      TORCH_CHECK(d.is_cuda() && d.device() == a.device() && d.dim() == 2 && d.size(0) == a.size(0) && d.size(1) == N &&
+                      d.stride(1) == 1 && d.scalar_type() == odt.dtype().toScalarType(),
+                  "grouped_gemm(1): out must be [rows, N] of the output dtype on the operands' device");
+    } else {
+      d = torch::empty({a.size(0), N}, odt);
+    }
     g.M = static_cast<int>(a.size(0));
     g.N = static_cast<int>(N);
     g.K = static_cast<int>(K);
@@ -317,6 +324,7 @@ Tensor grouped_gemm(const Tensor& a, const Tensor& b, int64_t mode, const Tensor
     g.tile_group = table.data_ptr<int>();
   } else {
     TORCH_CHECK(mode == 2 && a.size(0) == b.size(0) && table.numel() == num_groups + 1, "grouped_gemm(2): bad operands");
+    TORCH_CHECK(!out.has_value(), "grouped_gemm(2): out is only supported for the grouped-M mode");
     TORCH_CHECK(a.size(1) % 128 == 0, "grouped_gemm(2): per-group output rows must be a multiple of 128");
     d = torch::empty({num_groups * a.size(1), b.size(1)}, odt);
     g.M = static_cast<int>(a.size(1));
@@ -815,6 +823,57 @@ std::vector<Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps, bo
   return {y, rstd};
 }
 
+void check_qk_norm(const Tensor& qkv, const Tensor& wq, const Tensor& wk, int64_t hq, int64_t hkv, const char* who) {
+  check_rowmajor(qkv, who);
+  TORCH_CHECK(qkv.scalar_type() == torch::kBFloat16 && hq >= 1 && hkv >= 1 && qkv.size(1) == (hq + 2 * hkv) * 128 &&
+                  qkv.stride(0) % 8 == 0 && reinterpret_cast<uintptr_t>(qkv.data_ptr()) % 16 == 0,
+              "qk_norm: ", who, " must be 16-byte aligned bf16 [tokens, (hq + 2 hkv) * 128]");
+  for (const Tensor* w : {&wq, &wk})
+    TORCH_CHECK(w->is_cuda() && w->scalar_type() == torch::kBFloat16 && w->is_contiguous() && w->numel() == 128 &&
+                    reinterpret_cast<uintptr_t>(w->data_ptr()) % 16 == 0 && w->device() == qkv.device(),
+                "qk_norm: the norm weights must be 16-byte aligned contiguous bf16 [128] on the buffer's device");
+}
+
+// Per-head RMSNorm of the q and k heads of a packed qkv buffer (head_dim 128), v copied: one launch.
+Tensor qk_norm_fwd(const Tensor& qkv, const Tensor& wq, const Tensor& wk, int64_t hq, int64_t hkv, double eps) {
+  check_qk_norm(qkv, wq, wk, hq, hkv, "qkv");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor out = torch::empty({qkv.size(0), qkv.size(1)}, qkv.options());
+  if (qkv.size(0)) {
+    rlk::qk_norm_forward(reinterpret_cast<const __nv_bfloat16*>(qkv.data_ptr()), qkv.stride(0),
+                         reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), out.stride(0),
+                         reinterpret_cast<const __nv_bfloat16*>(wq.data_ptr()),
+                         reinterpret_cast<const __nv_bfloat16*>(wk.data_ptr()), qkv.size(0), static_cast<int>(hq),
+                         static_cast<int>(hkv), static_cast<float>(eps), stream_of(qkv));
+    after_launch();
+  }
+  return out;
+}
+
+// (dqkv, dwq, dwk) from the gradient of qk_norm_fwd's output; the weight gradients are summed over the blocks' partial
+// sums in block order (fp32) and returned in bf16.
+std::vector<Tensor> qk_norm_bwd(const Tensor& qkv, const Tensor& dout, const Tensor& wq, const Tensor& wk, int64_t hq,
+                                int64_t hkv, double eps) {
+  check_qk_norm(qkv, wq, wk, hq, hkv, "qkv");
+  check_qk_norm(dout, wq, wk, hq, hkv, "dout");
+  TORCH_CHECK(dout.size(0) == qkv.size(0) && dout.device() == qkv.device(), "qk_norm_bwd: dout must match qkv");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor dqkv = torch::empty({qkv.size(0), qkv.size(1)}, qkv.options());
+  const int blocks = rlk::qk_norm_blocks(qkv.size(0), static_cast<int>(hq + 2 * hkv));
+  Tensor part = torch::zeros({blocks, 2, 128}, qkv.options().dtype(torch::kFloat32));
+  if (qkv.size(0)) {
+    rlk::qk_norm_backward(reinterpret_cast<const __nv_bfloat16*>(qkv.data_ptr()), qkv.stride(0),
+                          reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), dout.stride(0),
+                          reinterpret_cast<__nv_bfloat16*>(dqkv.data_ptr()), dqkv.stride(0),
+                          reinterpret_cast<const __nv_bfloat16*>(wq.data_ptr()),
+                          reinterpret_cast<const __nv_bfloat16*>(wk.data_ptr()), qkv.size(0), static_cast<int>(hq),
+                          static_cast<int>(hkv), static_cast<float>(eps), part.data_ptr<float>(), stream_of(qkv));
+    after_launch();
+  }
+  Tensor dw = part.sum(0);
+  return {dqkv, dw[0].to(torch::kBFloat16), dw[1].to(torch::kBFloat16)};
+}
+
 std::vector<Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy, const Tensor& rstd) {
   check_rowmajor(x, "x");
   check_rowmajor(dy, "dy");
@@ -1225,7 +1284,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", rlk::traced("rlk::gemm", &gemm), py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_fp32") = false, py::arg("accumulate") = false, py::arg("alpha") = 1.0,
         py::arg("pair") = -1);
-  m.def("grouped_gemm", rlk::traced("rlk::grouped_gemm", &grouped_gemm));
+  m.def("grouped_gemm", rlk::traced("rlk::grouped_gemm", &grouped_gemm), py::arg("a"), py::arg("b"), py::arg("mode"),
+        py::arg("table"), py::arg("num_groups"), py::arg("b_mn"), py::arg("out_fp32"), py::arg("out") = py::none());
   m.def("tp_ag_gemm", rlk::traced("rlk::tp_ag_gemm", &tp_ag_gemm));
   m.def("tp_gemm_rs", rlk::traced("rlk::tp_gemm_rs", &tp_gemm_rs));
   m.def("moe_topk", rlk::traced("rlk::moe_topk", &moe_topk));
@@ -1255,6 +1315,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale_b"), py::arg("pair") = -1);
   m.def("attn_merge2", rlk::traced("rlk::attn_merge2", &attn_merge2));
   m.def("rmsnorm_fwd", rlk::traced("rlk::rmsnorm_fwd", &rmsnorm_fwd));
+  m.def("qk_norm_fwd", rlk::traced("rlk::qk_norm_fwd", &qk_norm_fwd));
+  m.def("qk_norm_bwd", rlk::traced("rlk::qk_norm_bwd", &qk_norm_bwd));
   m.def("rmsnorm_bwd", rlk::traced("rlk::rmsnorm_bwd", &rmsnorm_bwd));
   m.def("swiglu_fwd", rlk::traced("rlk::swiglu_fwd", &swiglu_fwd));
   m.def("swiglu_bwd", rlk::traced("rlk::swiglu_bwd", &swiglu_bwd));

@@ -231,6 +231,30 @@ class _FusedAttentionBlockCP(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None
 
 
+class _QKHeadNorm(torch.autograd.Function):
+    """Per-head RMSNorm (head_dim 128) of the q and k heads of a packed ``qkv [T, (Hq + 2 Hkv) * 128]``; v is copied.
+    One kernel forward and one backward instead of two strided copies, two generic RMSNorm launches and a
+    concatenation (and their five backward kernels)."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_weight, k_weight, hq, hkv, eps):
+        from rl_engine.kernels.ops.base import require_ext
+
+        wq, wk = q_weight.contiguous(), k_weight.contiguous()
+        ctx.save_for_backward(qkv, wq, wk)
+        ctx.meta = (int(hq), int(hkv), float(eps))
+        return require_ext().qk_norm_fwd(qkv, wq, wk, int(hq), int(hkv), float(eps))
+
+    @staticmethod
+    def backward(ctx, dout):
+        from rl_engine.kernels.ops.base import require_ext
+
+        qkv, wq, wk = ctx.saved_tensors
+        hq, hkv, eps = ctx.meta
+        dqkv, dwq, dwk = require_ext().qk_norm_bwd(qkv, dout.contiguous(), wq, wk, hq, hkv, eps)
+        return dqkv, dwq, dwk, None, None, None
+
+
 class _FusedAttentionBlockCPKV(torch.autograd.Function):
     """``_FusedAttentionBlockCP`` that also returns the gathered rotated keys / values ``[S, Hkv, 128]`` of the whole
     sequence (natural order) as differentiable outputs: later passes attend to them as a cached prefix, and whatever
@@ -400,7 +424,12 @@ class LlamaModel(nn.Module):
         t = qkv.shape[0]
         qkv3 = qkv.view(t, cfg.num_heads + 2 * cfg.num_kv_heads, cfg.head_dim)
         scale = 1.0 / math.sqrt(cfg.head_dim)
-        if cfg.qk_norm:  # Qwen3: per-head RMSNorm on q and k before the rotary embedding
+        if cfg.qk_norm and _fused_path(qkv) and cfg.head_dim == 128 and qkv.stride(1) == 1 and qkv.stride(0) % 8 == 0 \
+                and qkv.data_ptr() % 16 == 0:
+            # Qwen3: per-head RMSNorm on q and k before the rotary embedding, one kernel over the packed buffer
+            qkv3 = _QKHeadNorm.apply(qkv, self.view(f"l{index}.q_norm"), self.view(f"l{index}.k_norm"), cfg.num_heads,
+                                     cfg.num_kv_heads, cfg.rms_eps).view(t, cfg.num_heads + 2 * cfg.num_kv_heads, cfg.head_dim)
+        elif cfg.qk_norm:  # the same with the generic ops
             hq, hkv = cfg.num_heads, cfg.num_kv_heads
             qn = rms_norm(qkv3[:, :hq].reshape(-1, cfg.head_dim), self.view(f"l{index}.q_norm"), cfg.rms_eps)
             kn = rms_norm(qkv3[:, hq : hq + hkv].reshape(-1, cfg.head_dim), self.view(f"l{index}.k_norm"), cfg.rms_eps)

@@ -153,10 +153,17 @@ class ExpertParallelContext:
         self.mem.barrier()
         return mine.clone()
 
+    def outbox(self, plan: EPPlan) -> torch.Tensor:
+        """The rows of the send window that ``collect`` publishes: the last expert GEMM writes its output here directly
+        (``grouped_gemm(..., out=...)``) instead of into a temporary that is copied afterwards.  Every reader of the
+        previous contents has passed the barriers of the dispatch in between."""
+        return self.send.local[: plan.rows]
+
     def collect(self, slots_out: torch.Tensor, plan: EPPlan) -> torch.Tensor:
         """Publish MY expert outputs and fetch, for every local assignment, its row: ``[T*k, H]``."""
         ext = require_ext()
-        self.send.local[: plan.rows].copy_(slots_out)
+        if slots_out.data_ptr() != self.send.local.data_ptr():
+            self.send.local[: plan.rows].copy_(slots_out)
         self.mem.barrier()
         n = plan.dest_slot.numel()
         return ext.moe_combine_peer(self.send.ptrs, self.hidden, self.hidden, plan.dest_rank.view(n, 1),
@@ -173,7 +180,7 @@ class _EPExpertFFN(torch.autograd.Function):
         xs = ep.dispatch(x, plan)
         h1 = ext.grouped_gemm(xs, w1, 1, plan.tile_group, el, False, False)
         act = ext.swiglu_packed_fwd(h1)
-        y = ext.grouped_gemm(act, w2, 1, plan.tile_group, el, False, False)
+        y = ext.grouped_gemm(act, w2, 1, plan.tile_group, el, False, False, out=ep.outbox(plan))
         rows = ep.collect(y, plan)                                       # [T*k, H] in assignment order
         t, k = weights.shape
         local_slot = torch.arange(t * k, dtype=torch.int32, device=x.device).view(t, k)
@@ -194,7 +201,7 @@ class _EPExpertFFN(torch.autograd.Function):
         dact = ext.grouped_gemm(dy, w2, 1, plan.tile_group, el, True, False)
         dw2 = ext.grouped_gemm(dy, act, 2, plan.offsets, el, True, False)
         dh1 = ext.swiglu_packed_bwd(h1, dact)
-        dxs = ext.grouped_gemm(dh1, w1, 1, plan.tile_group, el, True, False)
+        dxs = ext.grouped_gemm(dh1, w1, 1, plan.tile_group, el, True, False, out=ep.outbox(plan))
         dw1 = ext.grouped_gemm(dh1, xs, 2, plan.offsets, el, True, False)
         drows = ep.collect(dxs, plan)
         dx = ext.moe_combine(drows, 0, 0, 0, local_slot, None)

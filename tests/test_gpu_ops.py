@@ -720,3 +720,46 @@ def test_kv_cached_decode_matches_the_packed_forward_and_rollout_engine_runs():
     fp8 = NativeRolloutEngine(model, seed=5, fp8_linears=True).generate(prompt, num_generations=4, max_new_tokens=12, top_k=20)
     assert fp8["completion_ids"].shape == (4, 12) and torch.isfinite(fp8["rollout_logps"]).all()
     model.enable_fp8_inference(False)
+
+
+@pytest.mark.parametrize("tokens,hq,hkv", [(1, 4, 1), (37, 8, 2), (1000, 32, 4)])
+def test_fused_qk_head_norm_matches_the_generic_ops(tokens, hq, hkv):
+    """Per-head RMSNorm of q and k inside a packed qkv buffer (one kernel each way) against slices + generic RMSNorm +
+    concatenation in fp32: output, gradient of the buffer and of both weights; v passes through untouched; a buffer
+    with a row pitch larger than its width works; two runs give the same bits."""
+    from rl_engine.models.llama import _QKHeadNorm
+
+    g = torch.Generator(device=DEV).manual_seed(tokens)
+    width = (hq + 2 * hkv) * 128
+    wide = torch.randn(tokens, width + 64, device=DEV, generator=g).to(torch.bfloat16)
+    qkv = wide[:, :width]
+    wq = (1.0 + 0.1 * torch.randn(128, device=DEV, generator=g)).to(torch.bfloat16)
+    wk = (1.0 + 0.1 * torch.randn(128, device=DEV, generator=g)).to(torch.bfloat16)
+    dout = torch.randn(tokens, width, device=DEV, generator=g).to(torch.bfloat16)
+    eps = 1e-6
+
+    a, aq, ak = qkv.clone().requires_grad_(True), wq.clone().requires_grad_(True), wk.clone().requires_grad_(True)
+    x = a if tokens != 37 else None
+    if x is None:  # non-contiguous rows
+        holder = wide.clone().requires_grad_(True)
+        x, a = holder[:, :width], holder
+    out = _QKHeadNorm.apply(x, aq, ak, hq, hkv, eps)
+    out.backward(dout)
+
+    b, bq, bk = qkv.float().clone().requires_grad_(True), wq.float().clone().requires_grad_(True), wk.float().clone().requires_grad_(True)
+    b3 = b.view(tokens, hq + 2 * hkv, 128)
+
+    def norm(v, w):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    ref = torch.cat([norm(b3[:, :hq], bq), norm(b3[:, hq:hq + hkv], bk), b3[:, hq + hkv:]], dim=1).reshape(tokens, width)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.equal(out[:, (hq + hkv) * 128:], qkv[:, (hq + hkv) * 128:])
+    got_dx = a.grad[:, :width] if a.grad.shape[1] != width else a.grad
+    assert torch.allclose(got_dx.float(), b.grad, atol=3e-2, rtol=3e-2)
+    scale = max(1.0, float(bq.grad.abs().max()))
+    assert torch.allclose(aq.grad.float(), bq.grad, atol=2e-2 * scale, rtol=2e-2)
+    assert torch.allclose(ak.grad.float(), bk.grad, atol=2e-2 * max(1.0, float(bk.grad.abs().max())), rtol=2e-2)
+    again = _QKHeadNorm.apply(x.detach(), wq, wk, hq, hkv, eps)
+    assert torch.equal(again, out.detach())
