@@ -180,3 +180,67 @@ class LlamaPipelineStage:
         if self.stage == self.stages - 1:
             x = rms_norm(x, model.view("final_norm"), model.cfg.rms_eps)
         return x
+
+
+class PipelineGRPOTrainer:
+    """One GRPO step of a Llama model cut into pipeline stages: every rank of ``group`` holds one
+    ``LlamaPipelineStage`` and the whole prompt group (token ids, rewards, old / reference log-probs are small).
+
+    The group's completions are split into micro-batches of ``micro_group`` completions that each re-process the shared
+    prompt; every micro-batch's GRPO loss is weighted by its share of the unmasked tokens, so the step optimises the same
+    token-mean loss as ``GRPOTrainer`` on the unsplit model (checked on Gloo ranks).  Advantages come from the whole
+    group's rewards.  Every stage then steps its own parameters with the flat AdamW (fp32 masters by default).
+    ``step_device`` returns the loss on the last stage and ``None`` elsewhere."""
+
+    def __init__(self, stage: LlamaPipelineStage, *, micro_group: int, group=None, lr: float = 1e-6, clip_eps: float = 0.2,
+                 beta: float = 0.04, adv_eps: float = 1e-6, weight_decay: float = 0.0, master_weights: bool = True) -> None:
+        from rl_engine.models.grpo import FlatAdamW
+
+        if micro_group < 1:
+            raise ValueError("micro_group must be at least one completion")
+        self.stage, self.micro_group = stage, int(micro_group)
+        self.clip_eps, self.beta, self.adv_eps = clip_eps, beta, adv_eps
+        flat = stage.model.flat
+        self.schedule = PipelineSchedule(self._stage_fn, group=group, dtype=flat.dtype, device=flat.device)
+        self.opt = FlatAdamW(stage.model, lr=lr, weight_decay=weight_decay, master_weights=master_weights)
+        self._micro = []  # (batch part, layout, positions, rows, advantages) of the step in flight
+
+    def _stage_fn(self, x, index: int) -> torch.Tensor:
+        _part, layout, positions, _rows, _adv = self._micro[index]
+        return self.stage.forward(x, positions, layout)
+
+    def _loss_fn(self, hidden: torch.Tensor, index: int) -> torch.Tensor:
+        from rl_engine.kernels.registry import kernel_registry
+
+        part, _layout, _positions, rows, adv = self._micro[index]
+        picked = kernel_registry.get_op("embedding")(rows, hidden)
+        logp = kernel_registry.get_op("linear_logp")(picked, self.stage.model.lm_head_weight(), part.completion_ids.reshape(-1))
+        loss, _policy, _kl = kernel_registry.get_op("grpo_loss").apply_from_logps(
+            logp.reshape(part.completion_ids.shape), part.ref_logps, part.old_logps, adv, part.completion_mask,
+            clip_eps=self.clip_eps, beta=self.beta)
+        return loss
+
+    def step_device(self, batch) -> Optional[torch.Tensor]:
+        from rl_engine.kernels.registry import kernel_registry
+        from rl_engine.models.grpo import group_geometry
+
+        g = batch.completion_ids.shape[0]
+        device = batch.completion_ids.device
+        adv = kernel_registry.get_op("grpo_loss").group_advantages(batch.rewards.float(), samples_per_prompt=g, eps=self.adv_eps)
+        unmasked = float(batch.completion_mask.sum().clamp_min(1))
+        self._micro, inputs, weights = [], [], []
+        for i0 in range(0, g, self.micro_group):
+            part = batch.completions(i0, min(g, i0 + self.micro_group))
+            m, l = part.completion_ids.shape
+            layout, positions, rows = group_geometry(part.prompt_ids.numel(), m, l, device)
+            self._micro.append((part, layout, positions, rows, adv[i0 : i0 + m].contiguous()))
+            inputs.append(torch.cat([part.prompt_ids, part.completion_ids.reshape(-1)]))
+            weights.append(float(part.completion_mask.sum()) / unmasked)
+        self.opt.zero_grad()
+        last = self.schedule.stage == self.schedule.stages - 1
+        losses = self.schedule.run(inputs, self._loss_fn if last else None, weights)
+        self._micro = []
+        self.opt.step()
+        if not last:
+            return None
+        return sum(loss * w for loss, w in zip(losses, weights))
