@@ -259,7 +259,7 @@ def bench_weight_sync(args, rank, world):
     mem = SymmetricMemory((2 if world > 2 else 1) * (nbytes + 4096) + (1 << 20))  # one window per measured mode
     results = {}
     for relay in ((True, False) if world > 2 else (False,)):
-        bridge = NVLinkBroadcastBridge(mem, nbytes, relay=relay)
+        bridge = NVLinkBroadcastBridge(mem, nbytes, relay=relay, stores=args.sync_stores)
         state = None
         if rank == 0:
             flat = torch.empty(per * count, dtype=torch.bfloat16, device="cuda").normal_()
@@ -294,7 +294,7 @@ def bench_weight_sync(args, rank, world):
             # unique bytes must leave the source once (relay) or once per peer (direct); every peer must receive all
             roof = (size if relay else size * (world - 1)) / (NVLINK_GBS * 1e6) if world > 1 else size * 2 / (peaks()["hbm_gbs"] * 1e6)
             print(json.dumps({"path": "weight_sync_bridge", "mode": "relay" if relay else "direct", "world": world,
-                              "ms": round(ms, 3), "gbytes": round(size / 2**30, 2), "tensors": count,
+                              "stores": args.sync_stores, "ms": round(ms, 3), "gbytes": round(size / 2**30, 2), "tensors": count,
                               "delivered_gbs_per_rank": round(size / ms / 1e6, 1), "roofline_ms": round(roof, 3),
                               "frac_of_roofline": round(roof / ms, 3), "verified_identical_on_all_ranks": ok,
                               "note": "publish + manifest broadcast + import + device digest check + acknowledge"}), flush=True)
@@ -315,6 +315,8 @@ def main() -> None:
     ap.add_argument("--zero1-params", type=int, default=1 << 29)
     ap.add_argument("--broadcast-params", type=int, default=1 << 29)
     ap.add_argument("--sync-gb", type=float, default=1.0, help="bytes of bf16 state for the weight_sync path (16 = Llama-3-8B)")
+    ap.add_argument("--sync-stores", choices=["copy-engine", "kernel"], default="copy-engine",
+                    help="weight_sync path: table-driven cast + copy-engine transfers, or one fused cast + peer-store kernel per tensor")
     ap.add_argument("--sync-tensors", type=int, default=291, help="number of tensors the state is split into")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--repeat", type=int, default=5)

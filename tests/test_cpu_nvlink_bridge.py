@@ -149,6 +149,29 @@ def test_relay_mode_fills_every_window_with_less_traffic_from_the_source(fake_wo
     assert torch.equal(direct_world.windows[2][: total], windows[2])
 
 
+def test_kernel_store_mode_casts_straight_into_every_window(fake_world):
+    """``stores="kernel"``: one fused cast + peer-store launch per tensor writes all windows (direct mode), nothing is
+    staged; the resulting windows and manifests equal those of the copy-engine mode."""
+    model = _model()
+    fused = [NVLinkBroadcastBridge(fake_world.memory(r), 1 << 15, target_dtype=torch.bfloat16, relay=False, stores="kernel")
+             for r in range(3)]
+    manifest = fused[0].publish(model, weight_version=1)
+    for b in fused[1:]:
+        b.join_publish()
+    assert fake_world.launches == len(manifest.tensors) == 5
+    other = FakeWorld(3, 1 << 16)
+    import rl_engine.kernels.ops.base as base
+
+    base.require_ext = lambda: types.SimpleNamespace(cast_broadcast=other.cast_broadcast)
+    staged = [NVLinkBroadcastBridge(other.memory(r), 1 << 15, target_dtype=torch.bfloat16, relay=False) for r in range(3)]
+    staged[0].publish(model, weight_version=1)
+    total = manifest.metadata["weight_bridge"]["requested_nbytes"]
+    for r in range(3):
+        assert torch.equal(fake_world.windows[r][:total], other.windows[r][:total])
+    with pytest.raises(ValueError):
+        NVLinkBroadcastBridge(fake_world.memory(0), 1 << 10, stores="nccl")
+
+
 def test_hop_two_destinations_are_rotated_and_skip_the_source(fake_world):
     """Every rank forwards its slice to all ranks that still miss it, starting with its right-hand neighbour, so that
     the k-th transfers of the ranks do not all land on one GPU."""
