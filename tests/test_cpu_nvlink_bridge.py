@@ -168,6 +168,16 @@ def test_kernel_store_mode_casts_straight_into_every_window(fake_world):
     total = manifest.metadata["weight_bridge"]["requested_nbytes"]
     for r in range(3):
         assert torch.equal(fake_world.windows[r][:total], other.windows[r][:total])
+    # relay mode on the same engine: own window first, then slices and forwards by the same kernel
+    relay_world = FakeWorld(3, 1 << 16)
+    base.require_ext = lambda: types.SimpleNamespace(cast_broadcast=relay_world.cast_broadcast)
+    relayed = [NVLinkBroadcastBridge(relay_world.memory(r), 1 << 15, target_dtype=torch.bfloat16, relay=True, stores="kernel")
+               for r in range(3)]
+    relayed[0].publish(model, weight_version=1)
+    for b in relayed[1:]:
+        b.join_publish()
+    for r in range(3):
+        assert torch.equal(relay_world.windows[r][:total], other.windows[r][:total])
     with pytest.raises(ValueError):
         NVLinkBroadcastBridge(fake_world.memory(0), 1 << 10, stores="nccl")
 
