@@ -106,7 +106,8 @@ def test_table_driven_cast_matches_per_tensor_casts(src_dtype, dst_dtype):
     assert torch.equal(copy[256:], window[256:]) and int(copy[:256].sum()) == 0
 
 
-def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge():
+@pytest.mark.parametrize("stores", ["copy-engine", "kernel"])
+def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge(stores):
     """The weight-sync transport over symmetric memory on one rank: fp32 trainer weights land in the window as bf16
     through the cast+broadcast kernel, the manifest validates, tampering is caught, a too-small window is refused."""
     from rl_engine.executors.bridge import (
@@ -115,8 +116,9 @@ def test_nvlink_broadcast_bridge_single_rank_publish_import_acknowledge():
     from rl_engine.parallel.symmetric import SymmetricMemory
 
     mem = SymmetricMemory(8 << 20)
-    bridge = make_weight_bridge("nvlink-broadcast", memory=mem, capacity_bytes=4 << 20, target_dtype=torch.bfloat16)
-    assert isinstance(bridge, NVLinkBroadcastBridge)
+    bridge = make_weight_bridge("nvlink-broadcast", memory=mem, capacity_bytes=4 << 20, target_dtype=torch.bfloat16,
+                                stores=stores)
+    assert isinstance(bridge, NVLinkBroadcastBridge) and bridge.stores == stores
     torch.manual_seed(3)
     model = torch.nn.Sequential(torch.nn.Linear(300, 257), torch.nn.Linear(257, 19, bias=False)).cuda()
     model.register_buffer("step", torch.tensor([5], dtype=torch.int64, device="cuda"))
