@@ -130,7 +130,7 @@ def bench_linear_logp(args, rank, world):
 
 
 def bench_cp(args, rank, world):
-    from rl_engine.parallel.context_parallel import ContextParallelAttention, shard_sequence
+    from rl_engine.parallel.context_parallel import ContextParallelAttention
 
     hq, hkv = 32, 8
     s = args.cp_tokens // (256 * world) * 256 * world

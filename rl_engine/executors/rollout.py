@@ -13,7 +13,7 @@ log-probs produced by the same ``linear_logp`` kernel the trainer uses.
 
 from __future__ import annotations
 
-from typing import Any, Dict, Mapping, Optional, Sequence
+from typing import Any, Dict, Mapping, Optional
 
 import torch
 

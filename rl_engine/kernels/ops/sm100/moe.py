@@ -21,7 +21,7 @@ The reference has no MoE operator; ``NativeMoEOp`` below is the PyTorch oracle u
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 

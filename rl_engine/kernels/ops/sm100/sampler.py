@@ -59,8 +59,6 @@ def sample_reference(logits: torch.Tensor, top_k: int, top_p: float, temperature
 def nucleus_reference(logits: torch.Tensor, top_p: float, temperature: float, seed: int, offset: int):
     """CPU oracle of the full-vocabulary nucleus kernel: 40-bit fixed-point masses, cut = smallest value v such
     that the mass of tokens >= v reaches ``top_p`` of the total (ties kept), inverse CDF in index order."""
-    import math
-
     out = []
     z = logits.float().cpu()
     for row in range(z.shape[0]):

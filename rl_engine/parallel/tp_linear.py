@@ -27,7 +27,7 @@ The reference has no tensor-parallel linear layers (its TP support is the vocab-
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 

@@ -17,7 +17,6 @@ The reference has no tensor-parallel model; the oracle is ``LlamaModel`` + ``GRP
 
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Tuple, Union
 
 import torch
