@@ -14,8 +14,8 @@ the host between steps, with none of its kernels or collectives in flight:
 
 A rank that stops on purpose (an exception between steps, a preemption notice) calls ``leave(reason)``; the others
 learn of it at their next ``check`` without waiting (a check of a step that the leaver had still reported passes).
-A rank that dies without a word is found by its missing report after ``timeout_s``.  Nothing here touches a GPU, so failures are tested with CPU ranks.  The reference has no
-counterpart (no elasticity, heartbeats or retries).
+A rank that dies without a word is found by its missing report after ``timeout_s``.  Nothing here touches a GPU, so
+failures are tested with CPU ranks.  The reference has no counterpart (no elasticity, heartbeats or retries).
 """
 
 from __future__ import annotations

@@ -4,8 +4,8 @@ Covers: symmetric heap mapping + device barrier, vocab-parallel fused linear_log
 equal on all ranks and close to the single-GPU op, backward vs autograd), the fused
 reduce-scatter + AdamW + all-gather step vs a single-process AdamW, one data-parallel GRPO step (bucketed and
 overlapped with backward) vs the single-GPU trainer on the same batch, the weight broadcast+cast, the
-tensor-parallel linears fused with their all-gather / reduce-scatter, the context-parallel causal attention (zig-zag shards) against full-sequence attention, and the
-expert-parallel MoE (peer-store dispatch / peer-load combine) against the single-GPU fused MoE.
+tensor-parallel linears fused with their all-gather / reduce-scatter, the context-parallel causal attention
+(zig-zag shards) against full-sequence attention, and the expert-parallel MoE (peer-store dispatch / peer-load combine) against the single-GPU fused MoE.
 Every rank prints ``OK <name>`` lines; rank 0 prints ``ALL OK`` at the end.
 """
 
