@@ -307,6 +307,10 @@ class GRPOTrainer:
     unmasked tokens, so the step optimises the same token-mean loss as a single pass."""
 
     retry_on_out_of_memory = True
+    # Optional ``rl_engine.parallel.liveness.RankLiveness``: checked on the host at the start of every step, before
+    # anything is launched, so that a step whose peers have left raises ``RankLeftError`` instead of waiting on them.
+    liveness = None
+    _steps_started = 0
     cache_prompt = True  # micro-batches attend to the prompt's cached keys / values instead of re-processing it
     _last_group = True   # False while ``step_groups`` is accumulating a group that is not the step's last one
 
@@ -411,6 +415,9 @@ class GRPOTrainer:
         """Forward, backward and optimiser step.  If the kept activations do not fit after all (the plan of
         ``LlamaModel.plan_checkpointing`` is an estimate), the forward/backward is repeated with four more layers
         recomputed; nothing has been applied to the parameters at that point."""
+        if self.liveness is not None:
+            self.liveness.check(self._steps_started)
+        self._steps_started += 1
         while True:
             self.opt.zero_grad()
             try:

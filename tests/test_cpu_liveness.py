@@ -104,3 +104,30 @@ def test_departure_between_steps_across_processes():
     for rank in (0, 2):
         done, info = results[rank]
         assert done == 3 and isinstance(info, dict) and set(info) == {1} and "stopping after step 2" in info[1], results
+
+
+def test_trainer_checks_its_peers_before_launching_a_step():
+    """A trainer with a liveness object raises before any work of the step when a peer has left, and steps normally
+    while everybody reports."""
+    import torch
+
+    from rl_engine.models.config import tiny_llama
+    from rl_engine.models.grpo import GRPOTrainer, synthetic_batch
+    from rl_engine.models.llama import LlamaModel
+
+    store = dist.HashStore()
+    cfg = tiny_llama(head_dim=32)
+    model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=1, activation_checkpointing=False)
+    trainer = GRPOTrainer(model, lr=1e-3, micro_group=None)
+    trainer.liveness = RankLiveness(store, 0, 2, timeout_s=5.0)
+    peer = RankLiveness(store, 1, 2, timeout_s=5.0)
+    batch = synthetic_batch(cfg.vocab_size, prompt_len=4, group=2, completion_len=3, seed=2)
+    before = model.flat.clone()
+    peer.beat(0)
+    trainer.step_device(batch)                       # the peer reported step 0: the step runs
+    assert not torch.equal(model.flat, before)
+    after_first = model.flat.clone()
+    peer.leave("preempted")
+    with pytest.raises(RankLeftError):
+        trainer.step_device(batch)                   # step 1 never starts
+    assert torch.equal(model.flat, after_first)
