@@ -4,36 +4,17 @@ The implementation lives in ``rl_engine.executors.weight_sync`` (protocol / tran
 """
 
 from rl_engine.executors.weight_sync.protocol import (
-    BRIDGE_METADATA_KEY,
-    TensorDescriptor,
-    WeightBridge,
-    WeightBridgeError,
-    WeightBridgeUnavailableError,
-    WeightConsumer,
-    WeightInstallAdapter,
-    WeightLayout,
-    WeightManifestValidationError,
-    WeightPublisher,
-    WeightUpdateManifest,
+    BRIDGE_METADATA_KEY, TensorDescriptor, WeightBridge, WeightBridgeError, WeightBridgeUnavailableError, WeightConsumer,
+    WeightInstallAdapter, WeightLayout, WeightManifestValidationError, WeightPublisher, WeightUpdateManifest,
     WeightUpdateRejectedError,
 )
 from rl_engine.executors.weight_sync.transports import (
-    CUDAVMMTensorBridge,
-    FileBlobBridge,
-    IPCWeightBridge,
-    LocalTensorCopyBridge,
-    NVLinkBroadcastBridge,
-    SharedMemoryTensorBridge,
-    make_weight_bridge,
-    manifest_from_json,
-    manifest_to_json,
+    CUDAVMMTensorBridge, FileBlobBridge, IPCWeightBridge, LocalTensorCopyBridge, NVLinkBroadcastBridge,
+    SharedMemoryTensorBridge, make_weight_bridge, manifest_from_json, manifest_to_json,
 )
 from rl_engine.executors.weight_sync.vllm_adapters import (
-    VLLMCheckpointWeightReloadAdapter,
-    VLLMCUDAVMMExternalStorageAdapter,
-    VLLMInProcessWeightReloadAdapter,
-    VLLMIPCWeightUpdateRequestBuilder,
-    VLLMWeightInstallAdapter,
+    VLLMCheckpointWeightReloadAdapter, VLLMCUDAVMMExternalStorageAdapter, VLLMInProcessWeightReloadAdapter,
+    VLLMIPCWeightUpdateRequestBuilder, VLLMWeightInstallAdapter,
 )
 
 __all__ = [
