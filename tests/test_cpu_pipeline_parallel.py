@@ -89,7 +89,7 @@ def _worker(rank, world, store_path, layers, micro, queue):
         queue.put((rank, f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}", 0, None))
 
 
-@pytest.mark.parametrize("world,layers,micro", [(2, 4, 3), (3, 5, 4), (3, 3, 1)])
+@pytest.mark.parametrize("world,layers,micro", [(2, 4, 3), (3, 5, 2)])
 def test_1f1b_pipeline_matches_the_unsplit_model(world, layers, micro):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
