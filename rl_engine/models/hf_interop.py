@@ -1,0 +1,151 @@
+"""Hugging Face checkpoints <-> ``LlamaModel``.
+
+The reference has no model of its own: its executors and trainers run Hugging Face modules, and its weight bridge ships
+``state_dict`` keys ("checkpoint-format names") to vLLM (``rl_engine/executors/bridge.py:206,345``).  The native model of
+this library keeps packed parameters in one flat buffer (``wqkv`` = q, k and v rows stacked, ``w_gate_up`` = gate and up
+rows stacked, experts stacked by expert), so two things are needed to stand in for a Hugging Face module:
+
+* ``config_from_hf`` / ``load_hf_state_dict``: build the matching ``ModelConfig`` and copy a Llama-3 / Qwen3 /
+  Qwen3-MoE ``state_dict`` into the flat buffer (only the local experts of an expert-sharded model);
+* ``hf_state_dict_views``: the parameters under their Hugging Face names as zero-copy views (row ranges of the packed
+  matrices are contiguous), which is what a weight bridge publishes to a vLLM engine.
+
+Rotary embedding (half-split rotation), RMSNorm (plain weight, eps inside the root), attention scale and the Qwen3
+router (softmax over all experts, top-k, renormalised) follow the Hugging Face implementations, so logits agree (tested
+against ``transformers`` on CPU in fp32).
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, Iterator, List, Mapping, Tuple
+
+import torch
+
+from rl_engine.models.config import ModelConfig
+
+
+def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
+    """``ModelConfig`` of a Hugging Face Llama / Qwen3 / Qwen3-MoE configuration object (or mapping)."""
+    get = (lambda k, d=None: hf_config.get(k, d)) if isinstance(hf_config, Mapping) else (lambda k, d=None: getattr(hf_config, k, d))
+    hidden, heads = int(get("hidden_size")), int(get("num_attention_heads"))
+    head_dim = int(get("head_dim") or hidden // heads)
+    scaling = get("rope_scaling")
+    if scaling and (scaling.get("rope_type", scaling.get("type")) not in (None, "default")):
+        raise ValueError(f"rope scaling {scaling} is not supported (plain rotary embedding only)")
+    if get("attention_bias", False) or get("mlp_bias", False):
+        raise ValueError("projections with a bias are not supported")
+    experts = int(get("num_experts", 0) or get("num_local_experts", 0) or 0)
+    if experts and not get("norm_topk_prob", True):
+        raise ValueError("routers that do not renormalise the top-k weights are not supported")
+    if experts and (int(get("decoder_sparse_step", 1) or 1) != 1 or get("mlp_only_layers")):
+        raise ValueError("models that mix dense and mixture-of-experts layers are not supported")
+    model_type = str(get("model_type", "") or "")
+    rope_theta = get("rope_theta")
+    if rope_theta is None and isinstance(get("rope_parameters"), Mapping):
+        rope_theta = get("rope_parameters").get("rope_theta")
+    return ModelConfig(
+        name or model_type or "hf-model", int(get("vocab_size")), hidden, int(get("num_hidden_layers")), heads,
+        int(get("num_key_value_heads") or heads), head_dim, int(get("intermediate_size")),
+        rms_eps=float(get("rms_norm_eps", 1e-5)), rope_theta=float(rope_theta if rope_theta is not None else 10000.0),
+        num_experts=experts, experts_per_token=int(get("num_experts_per_tok", 0) or 0) if experts else 0,
+        moe_ffn_size=int(get("moe_intermediate_size", 0) or 0) if experts else 0,
+        qk_norm=model_type.startswith("qwen3"),
+    )
+
+
+def hf_parameter_map(model) -> Iterator[Tuple[str, List[Tuple[str, int, int]]]]:
+    """``(native name, [(hf name, first row, one past the last row)])`` for every parameter of ``model`` (a
+    ``LlamaModel``): which rows of the native tensor hold which Hugging Face tensor.  Vectors use element ranges."""
+    cfg = model.cfg
+    q, kv, f, h = cfg.q_dim, cfg.kv_dim, cfg.ffn_size, cfg.hidden_size
+    yield "embed", [("model.embed_tokens.weight", 0, cfg.vocab_size)]
+    shard_rank, shard_world = model.expert_shard if model.expert_shard is not None else (0, 1)
+    e_local = cfg.num_experts // shard_world if cfg.num_experts else 0
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        yield f"l{i}.attn_norm", [(p + "input_layernorm.weight", 0, h)]
+        yield f"l{i}.wqkv", [(p + "self_attn.q_proj.weight", 0, q), (p + "self_attn.k_proj.weight", q, q + kv),
+                             (p + "self_attn.v_proj.weight", q + kv, q + 2 * kv)]
+        yield f"l{i}.wo", [(p + "self_attn.o_proj.weight", 0, h)]
+        if cfg.qk_norm:
+            yield f"l{i}.q_norm", [(p + "self_attn.q_norm.weight", 0, cfg.head_dim)]
+            yield f"l{i}.k_norm", [(p + "self_attn.k_norm.weight", 0, cfg.head_dim)]
+        yield f"l{i}.mlp_norm", [(p + "post_attention_layernorm.weight", 0, h)]
+        if cfg.num_experts:
+            fe = cfg.moe_ffn_size
+            yield f"l{i}.router", [(p + "mlp.gate.weight", 0, cfg.num_experts)]
+            gate_up, down = [], []
+            for e in range(e_local):
+                ep = f"{p}mlp.experts.{shard_rank * e_local + e}."
+                gate_up += [(ep + "gate_proj.weight", e * 2 * fe, e * 2 * fe + fe),
+                            (ep + "up_proj.weight", e * 2 * fe + fe, (e + 1) * 2 * fe)]
+                down.append((ep + "down_proj.weight", e * h, (e + 1) * h))
+            yield f"l{i}.w_gate_up", gate_up
+            yield f"l{i}.w_down", down
+        else:
+            yield f"l{i}.w_gate_up", [(p + "mlp.gate_proj.weight", 0, f), (p + "mlp.up_proj.weight", f, 2 * f)]
+            yield f"l{i}.w_down", [(p + "mlp.down_proj.weight", 0, h)]
+    yield "final_norm", [("model.norm.weight", 0, h)]
+    yield "lm_head", [("lm_head.weight", 0, cfg.vocab_size)]
+
+
+def hf_state_dict_views(model) -> Dict[str, torch.Tensor]:
+    """The parameters of ``model`` under their Hugging Face names, as views of the flat buffer (no copies)."""
+    out: Dict[str, torch.Tensor] = {}
+    for native, pieces in hf_parameter_map(model):
+        tensor = model.view(native).detach()
+        for hf_name, lo, hi in pieces:
+            out[hf_name] = tensor[lo:hi]
+    return out
+
+
+@torch.no_grad()
+def load_hf_state_dict(model, state_dict: Mapping[str, torch.Tensor], *, strict: bool = True) -> List[str]:
+    """Copies a Hugging Face ``state_dict`` into ``model`` (cast to its dtype).  A missing ``lm_head.weight`` is taken from
+    the embedding (tied weights).  Returns the Hugging Face names that were not used (experts of other shards, buffers);
+    with ``strict`` a missing or mis-shaped tensor raises ``KeyError`` / ``ValueError``."""
+    used = set()
+    cfg = model.cfg
+    shard_rank, shard_world = model.expert_shard if model.expert_shard is not None else (0, 1)
+    e_local = cfg.num_experts // shard_world if cfg.num_experts else 0
+    for native, pieces in hf_parameter_map(model):
+        dst = model.view(native)
+        if cfg.num_experts and native.endswith((".w_gate_up", ".w_down")):
+            # newer ``transformers`` keep a layer's experts as two stacked tensors, ``experts.gate_up_proj [E, 2F, H]``
+            # and ``experts.down_proj [E, H, F]``: the native layout, expert by expert
+            layer = native.split(".")[0][1:]
+            fused = f"model.layers.{layer}.mlp.experts." + ("gate_up_proj" if native.endswith("w_gate_up") else "down_proj")
+            if fused in state_dict:
+                src = state_dict[fused][shard_rank * e_local : (shard_rank + 1) * e_local]
+                src = src.reshape(-1, src.shape[-1])
+                if tuple(src.shape) != tuple(dst.shape):
+                    raise ValueError(f"{fused} gives {tuple(src.shape)} for this shard, {native} needs {tuple(dst.shape)}")
+                dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+                used.add(fused)
+                continue
+        for hf_name, lo, hi in pieces:
+            src = state_dict.get(hf_name)
+            if src is None and hf_name == "lm_head.weight":
+                src = state_dict.get("model.embed_tokens.weight")
+            if src is None:
+                if strict:
+                    raise KeyError(f"{hf_name} is missing from the state dict (needed for {native})")
+                continue
+            part = dst[lo:hi]
+            if tuple(src.shape) != tuple(part.shape):
+                raise ValueError(f"{hf_name} has shape {tuple(src.shape)}, {native}[{lo}:{hi}] needs {tuple(part.shape)}")
+            part.copy_(src.to(device=part.device, dtype=part.dtype))
+            used.add(hf_name)
+    return sorted(k for k in state_dict if k not in used)
+
+
+def model_from_hf(hf_model, *, dtype: torch.dtype = torch.bfloat16, device="cuda", expert_shard=None, **model_kwargs):
+    """A ``LlamaModel`` with the architecture and the weights of a Hugging Face causal LM (``LlamaForCausalLM``,
+    ``Qwen3ForCausalLM``, ``Qwen3MoeForCausalLM``).  ``model_kwargs`` go to ``LlamaModel`` (``max_positions``, ...)."""
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = config_from_hf(hf_model.config)
+    model_kwargs.setdefault("max_positions", int(getattr(hf_model.config, "max_position_embeddings", 0) or 8192))
+    model = LlamaModel(cfg, dtype=dtype, device=device, expert_shard=expert_shard, **model_kwargs)
+    load_hf_state_dict(model, hf_model.state_dict())
+    return model

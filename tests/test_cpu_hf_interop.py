@@ -1,0 +1,162 @@
+"""Hugging Face checkpoints <-> the native model, on CPU in fp32: a tiny random ``LlamaForCausalLM`` (and, where this
+``transformers`` has them, ``Qwen3ForCausalLM`` and ``Qwen3MoeForCausalLM``) loaded into ``LlamaModel`` gives the same
+logits; the Hugging Face views of the native parameters are zero-copy and round-trip; expert shards take their experts."""
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _native_from(hf_model, **kw):
+    from rl_engine.models.hf_interop import config_from_hf, load_hf_state_dict
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = config_from_hf(hf_model.config)
+    model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=0, activation_checkpointing=False, max_positions=64, **kw)
+    unused = load_hf_state_dict(model, hf_model.state_dict())
+    return cfg, model, unused
+
+
+def _compare_logits(hf_model, model, vocab, atol=2e-4):
+    from rl_engine.models.causal_lm import PackedCausalLM
+
+    ids = torch.randint(0, vocab, (2, 9), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        want = hf_model(input_ids=ids, use_cache=False).logits.float()
+        got = PackedCausalLM(model)(ids).logits.float()
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, atol=atol, rtol=1e-3), float((got - want).abs().max())
+
+
+def test_llama_checkpoint_loads_and_matches_transformers():
+    from rl_engine.models.hf_interop import hf_state_dict_views
+
+    config = transformers.LlamaConfig(
+        vocab_size=97, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False,
+        attention_bias=False, mlp_bias=False)
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    cfg, model, unused = _native_from(hf)
+    assert (cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn_size) == (64, 2, 4, 2, 16, 112)
+    assert not cfg.qk_norm and not cfg.num_experts and unused == []
+    _compare_logits(hf, model, 97)
+    views = hf_state_dict_views(model)
+    theirs = hf.state_dict()
+    assert set(views) == set(theirs)
+    lo, hi = model.flat.data_ptr(), model.flat.data_ptr() + model.flat.numel() * 4
+    for name, want in theirs.items():
+        assert torch.equal(views[name], want), name
+        assert lo <= views[name].data_ptr() < hi and views[name].is_contiguous(), name     # a view, not a copy
+    with pytest.raises(KeyError):
+        from rl_engine.models.hf_interop import load_hf_state_dict
+
+        load_hf_state_dict(model, {k: v for k, v in theirs.items() if "k_proj" not in k})
+
+
+def test_tied_embeddings_and_unsupported_configurations():
+    from rl_engine.models.hf_interop import config_from_hf, load_hf_state_dict
+    from rl_engine.models.llama import LlamaModel
+
+    config = transformers.LlamaConfig(vocab_size=50, hidden_size=32, intermediate_size=48, num_hidden_layers=1,
+                                      num_attention_heads=2, num_key_value_heads=2, tie_word_embeddings=True)
+    torch.manual_seed(1)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    cfg = config_from_hf(hf.config)
+    model = LlamaModel(cfg, dtype=torch.float32, device="cpu", activation_checkpointing=False, max_positions=32)
+    state = {k: v for k, v in hf.state_dict().items() if k != "lm_head.weight"}
+    load_hf_state_dict(model, state)
+    assert torch.equal(model.view("lm_head"), hf.model.embed_tokens.weight)
+    _compare_logits(hf, model, 50)
+    with pytest.raises(ValueError):
+        config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
+                        "intermediate_size": 8, "rope_scaling": {"rope_type": "llama3", "factor": 8.0}})
+    with pytest.raises(ValueError):
+        config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
+                        "intermediate_size": 8, "attention_bias": True})
+
+
+def test_qwen3_dense_checkpoint_with_head_norms():
+    if not hasattr(transformers, "Qwen3ForCausalLM"):
+        pytest.skip("this transformers has no Qwen3")
+    config = transformers.Qwen3Config(
+        vocab_size=83, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=32, max_position_embeddings=64, rms_norm_eps=1e-6, rope_theta=10000.0,
+        tie_word_embeddings=False, attention_bias=False)
+    torch.manual_seed(2)
+    hf = transformers.Qwen3ForCausalLM(config).float().eval()
+    with torch.no_grad():  # make the head norms non-trivial
+        for layer in hf.model.layers:
+            layer.self_attn.q_norm.weight.uniform_(0.5, 1.5)
+            layer.self_attn.k_norm.weight.uniform_(0.5, 1.5)
+    cfg, model, unused = _native_from(hf)
+    assert cfg.qk_norm and cfg.head_dim == 32 and cfg.q_dim == 128 and unused == []
+    _compare_logits(hf, model, 83)
+
+
+def test_qwen3_moe_checkpoint_and_expert_shards():
+    if not hasattr(transformers, "Qwen3MoeForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-MoE")
+    from rl_engine.models.hf_interop import hf_state_dict_views
+
+    config = transformers.Qwen3MoeConfig(
+        vocab_size=71, hidden_size=64, intermediate_size=96, moe_intermediate_size=48, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2,
+        norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], max_position_embeddings=64, rms_norm_eps=1e-6,
+        rope_theta=10000.0, tie_word_embeddings=False, attention_bias=False, output_router_logits=False)
+    torch.manual_seed(3)
+    hf = transformers.Qwen3MoeForCausalLM(config).float().eval()
+    state = hf.state_dict()
+    stacked = "model.layers.0.mlp.experts.gate_up_proj" in state   # newer transformers: experts stacked per layer
+    cfg, model, unused = _native_from(hf)
+    assert cfg.num_experts == 4 and cfg.experts_per_token == 2 and cfg.moe_ffn_size == 48 and cfg.qk_norm and unused == []
+    _compare_logits(hf, model, 71, atol=5e-4)
+    # an expert shard takes its own experts (2 and 3 of 4); the per-expert checkpoint names come out as views
+    _cfg, shard, unused = _native_from(hf, expert_shard=(1, 2))
+    if not stacked:
+        assert all(".experts.0." in k or ".experts.1." in k for k in unused) and len(unused) == 2 * 2 * 3
+    views = hf_state_dict_views(shard)
+    assert "model.layers.0.mlp.experts.2.gate_proj.weight" in views and "model.layers.0.mlp.experts.0.gate_proj.weight" not in views
+    if stacked:
+        want_down = state["model.layers.1.mlp.experts.down_proj"][3]
+        want_gate = state["model.layers.0.mlp.experts.gate_up_proj"][2][:48]
+    else:
+        want_down = state["model.layers.1.mlp.experts.3.down_proj.weight"]
+        want_gate = state["model.layers.0.mlp.experts.2.gate_proj.weight"]
+    assert torch.equal(views["model.layers.1.mlp.experts.3.down_proj.weight"], want_down)
+    assert torch.equal(views["model.layers.0.mlp.experts.2.gate_proj.weight"], want_gate)
+    # a checkpoint with one tensor per expert (the on-disk format) loads to the same parameters
+    per_expert = {k: v for k, v in state.items() if ".mlp.experts." not in k}
+    full_views = hf_state_dict_views(model)
+    per_expert.update({k: v.clone() for k, v in full_views.items() if ".mlp.experts." in k})
+    from rl_engine.models.hf_interop import config_from_hf, load_hf_state_dict
+    from rl_engine.models.llama import LlamaModel
+
+    again = LlamaModel(config_from_hf(hf.config), dtype=torch.float32, device="cpu", seed=9, activation_checkpointing=False,
+                       max_positions=64)
+    assert load_hf_state_dict(again, per_expert) == []
+    assert torch.equal(again.flat, model.flat)
+
+
+def test_model_from_hf_and_publishing_checkpoint_names_through_a_bridge():
+    """``model_from_hf`` builds and loads in one call; a weight bridge that is handed the Hugging Face views ships the
+    checkpoint-format names an inference engine expects, and the consumer's tensors equal the Hugging Face weights."""
+    from rl_engine.executors.bridge import LocalTensorCopyBridge
+    from rl_engine.models.hf_interop import hf_state_dict_views, model_from_hf
+
+    config = transformers.LlamaConfig(vocab_size=61, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=48,
+                                      tie_word_embeddings=False)
+    torch.manual_seed(3)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    model = model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert model.cfg.num_layers == 2
+    _compare_logits(hf, model, 61)
+    bridge = LocalTensorCopyBridge()
+    manifest = bridge.publish(hf_state_dict_views(model), weight_version=1)
+    assert set(manifest.tensors) == set(hf.state_dict())
+    got = bridge.import_update(manifest)
+    for name, want in hf.state_dict().items():
+        assert torch.equal(got[name], want), name
+    bridge.acknowledge(manifest.update_id)
