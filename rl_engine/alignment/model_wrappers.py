@@ -21,37 +21,48 @@ import torch
 from rl_engine.testing import selected_logprobs_reference
 
 
-def _as_tensor(value: Any, where: str) -> torch.Tensor:
-    if not isinstance(value, torch.Tensor):
-        raise TypeError(f"{where} must be a torch.Tensor, got {type(value)!r}")
-    return value
+def _logits_field(output: Any) -> Any:
+    """The ``logits`` member of a mapping or an object, ``None`` when ``output`` has no such member."""
+    if isinstance(output, Mapping):
+        if "logits" not in output:
+            raise TypeError("model output mapping does not contain a 'logits' entry")
+        return output["logits"]
+    return getattr(output, "logits", None)
 
 
 def extract_logits(model_output: Any) -> torch.Tensor:
+    """The logits tensor inside whatever a model returned.  A worklist walk instead of recursion: containers are
+    opened in order, the first tensor with at least two dimensions found inside a container wins (so a scalar loss in
+    front of the logits is skipped), and a bare tensor or a ``logits`` member is taken as it is."""
     if isinstance(model_output, torch.Tensor):
         return model_output
-    if isinstance(model_output, Mapping):
-        if "logits" not in model_output:
-            raise TypeError("model output mapping does not contain a 'logits' entry")
-        return _as_tensor(model_output["logits"], "model output['logits']")
-    attr = getattr(model_output, "logits", None)
-    if attr is not None:
-        return _as_tensor(attr, "model output.logits")
-    if isinstance(model_output, (tuple, list)) and len(model_output):
-        why: Optional[Exception] = None
-        for pos, item in enumerate(model_output):
-            try:
-                found = extract_logits(item)
-            except TypeError as exc:
-                why = exc
-                continue
-            if found.ndim >= 2:
-                return found
-            why = TypeError(f"model output sequence item {pos} has too few dimensions for logits")
-        raise TypeError(
-            "model output sequence does not contain a logits tensor" + (f": {why}" if why else "")
-        )
-    raise TypeError(f"model output does not expose logits: {type(model_output)!r}")
+    pending, nested, problems = [model_output], False, []
+    while pending:
+        item = pending.pop(0)
+        if isinstance(item, torch.Tensor):
+            if not nested or item.ndim >= 2:
+                return item
+            problems.append(f"a {item.ndim}-d tensor has too few dimensions for logits")
+            continue
+        if isinstance(item, (tuple, list)):
+            pending[:0], nested = list(item), True
+            continue
+        try:
+            field = _logits_field(item)
+        except TypeError as exc:
+            if not nested:
+                raise
+            problems.append(str(exc))
+            continue
+        if field is None:
+            problems.append(f"{type(item)!r} does not expose logits")
+        elif not isinstance(field, torch.Tensor):
+            problems.append(f"the 'logits' member of {type(item)!r} must be a torch.Tensor, got {type(field)!r}")
+        elif nested and field.ndim < 2:
+            problems.append("a 'logits' member has too few dimensions")
+        else:
+            return field
+    raise TypeError("model output does not contain a logits tensor: " + ("; ".join(problems) or "it is empty"))
 
 
 def _window(logits: torch.Tensor, start: Optional[int], end: Optional[int]) -> torch.Tensor:
@@ -59,7 +70,7 @@ def _window(logits: torch.Tensor, start: Optional[int], end: Optional[int]) -> t
         return logits
     if logits.ndim < 2:
         raise ValueError("logits must have at least two dimensions to slice token positions")
-    return logits.narrow(-2, 0, logits.shape[-2])[..., slice(start, end), :]
+    return logits[..., slice(start, end), :]
 
 
 class PolicyModelWrapper(torch.nn.Module):
