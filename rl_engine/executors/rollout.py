@@ -70,6 +70,12 @@ class RolloutExecutor:
 
     @torch.no_grad()
     def _install_into_policy(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        if hasattr(self.policy_model, "named_views") and "model.embed_tokens.weight" in tensors:
+            # an update under Hugging Face checkpoint names (a trainer publishing for vLLM engines as well)
+            from rl_engine.models.hf_interop import load_hf_state_dict
+
+            load_hf_state_dict(self.policy_model, tensors)
+            return
         views = self.policy_model.named_views() if hasattr(self.policy_model, "named_views") else dict(
             self.policy_model.named_parameters())
         missing = sorted(set(views) - set(tensors))

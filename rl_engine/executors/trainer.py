@@ -52,6 +52,9 @@ class NativeTrainingConfig(TorchRLTrainingConfig):
     old_logp_offset: float = 0.01
     weight_transport: str = "local-clone"
     weight_decay: float = 0.0
+    # "native": this library's parameter names; "hf": the names of the Hugging Face checkpoint of the same
+    # architecture (what a vLLM engine's weight loader expects), as zero-copy views of the packed parameters
+    weight_names: str = "native"
 
 
 def safe_token_ids(token_ids: torch.Tensor, mask: Optional[torch.Tensor]) -> torch.Tensor:
@@ -154,7 +157,12 @@ class NativeTrainingWorker(RolloutBatchMixin):
             raise WeightManifestValidationError(
                 f"weight_version must increase monotonically (got {version}, latest {self._published_version})"
             )
-        source = self.model.state_dict_views() if hasattr(self.model, "state_dict_views") else self.model
+        if not hasattr(self.model, "state_dict_views"):
+            source = self.model
+        elif getattr(self.config, "weight_names", "native") == "hf":
+            source = self.model.state_dict_views(names="hf")
+        else:
+            source = self.model.state_dict_views()
         manifest = self.bridge.publish(source, weight_version=version, metadata=metadata)
         self._published_version = version
         return manifest

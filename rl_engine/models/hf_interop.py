@@ -149,3 +149,163 @@ def model_from_hf(hf_model, *, dtype: torch.dtype = torch.bfloat16, device="cuda
     model = LlamaModel(cfg, dtype=dtype, device=device, expert_shard=expert_shard, **model_kwargs)
     load_hf_state_dict(model, hf_model.state_dict())
     return model
+
+
+# ---- checkpoints on disk (``config.json`` + ``*.safetensors``, optionally sharded with an index) -------------------
+_INDEX_NAME = "model.safetensors.index.json"
+
+
+def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max_position_embeddings: int = 8192,
+                   tie_word_embeddings: bool = False) -> Dict[str, Any]:
+    """The ``config.json`` of ``cfg``: the inverse of ``config_from_hf`` (Llama, Qwen3 and Qwen3-MoE architectures)."""
+    moe, qwen = bool(cfg.num_experts), bool(cfg.qk_norm)
+    if moe and not qwen:
+        raise ValueError("mixture-of-experts checkpoints are written as Qwen3-MoE, which has per-head q/k norms")
+    arch, kind = (("Qwen3MoeForCausalLM", "qwen3_moe") if moe else ("Qwen3ForCausalLM", "qwen3") if qwen
+                  else ("LlamaForCausalLM", "llama"))
+    out: Dict[str, Any] = {
+        "architectures": [arch], "model_type": kind, "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
+        "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads,
+        "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn_size, "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta,
+        "hidden_act": "silu", "attention_bias": False, "max_position_embeddings": int(max_position_embeddings),
+        "tie_word_embeddings": bool(tie_word_embeddings), "torch_dtype": str(dtype).replace("torch.", ""),
+        "dtype": str(dtype).replace("torch.", ""),
+    }
+    if kind == "llama":
+        out["mlp_bias"] = False
+    if moe:
+        out.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token, moe_intermediate_size=cfg.moe_ffn_size,
+                   norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])
+    return out
+
+
+def save_hf_checkpoint(model, directory, *, max_shard_bytes: int = 5 << 30, tie_word_embeddings: bool = False,
+                       max_position_embeddings: int = 0) -> List[str]:
+    """Writes ``model`` (all experts local) as a Hugging Face checkpoint: ``config.json`` plus one or more
+    ``model-xxxxx-of-yyyyy.safetensors`` files cut at ``max_shard_bytes`` and the index that maps names to files.
+    Tensors are the zero-copy checkpoint-name views, so one shard at a time is staged on the host.  Returns the
+    file names written.  ``transformers`` and vLLM load the directory directly."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    if model.expert_shard is not None and model.expert_shard[1] > 1:
+        raise ValueError("an expert-sharded model holds only its own experts; gather them before saving")
+    os.makedirs(directory, exist_ok=True)
+    views = hf_state_dict_views(model)
+    if tie_word_embeddings:
+        views.pop("lm_head.weight")
+    shards: List[List[str]] = [[]]
+    used = 0
+    for name, t in views.items():
+        nbytes = t.numel() * t.element_size()
+        if shards[-1] and used + nbytes > max_shard_bytes:
+            shards.append([])
+            used = 0
+        shards[-1].append(name)
+        used += nbytes
+    files, weight_map, total = [], {}, 0
+    for i, names in enumerate(shards):
+        fname = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file({n: views[n].detach().to("cpu").contiguous() for n in names}, os.path.join(directory, fname),
+                  metadata={"format": "pt"})
+        files.append(fname)
+        for n in names:
+            weight_map[n] = fname
+            total += views[n].numel() * views[n].element_size()
+    if len(shards) > 1:
+        with open(os.path.join(directory, _INDEX_NAME), "w") as f:
+            json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=1, sort_keys=True)
+        files.append(_INDEX_NAME)
+    positions = max_position_embeddings or int(model.rope_cos.shape[0])
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(hf_config_dict(model.cfg, dtype=model.flat.dtype, max_position_embeddings=positions,
+                                 tie_word_embeddings=tie_word_embeddings), f, indent=1, sort_keys=True)
+    return files + ["config.json"]
+
+
+def checkpoint_files(directory) -> List[str]:
+    """The ``*.safetensors`` files of a checkpoint directory (from the index when there is one), sorted."""
+    import json
+    import os
+
+    index = os.path.join(directory, _INDEX_NAME)
+    if os.path.exists(index):
+        with open(index) as f:
+            return sorted(set(json.load(f)["weight_map"].values()))
+    found = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
+    if not found:
+        raise FileNotFoundError(f"no .safetensors file in {directory}")
+    return found
+
+
+@torch.no_grad()
+def load_hf_checkpoint(model, directory, *, strict: bool = True) -> List[str]:
+    """Streams a checkpoint directory into ``model`` one tensor at a time (memory-mapped safetensors, no full state
+    dict on the host): every name is routed to its rows of the flat buffer by ``hf_parameter_map``.  Handles tied
+    embeddings, per-expert and stacked expert tensors, and expert shards like ``load_hf_state_dict``.  Returns the names
+    that were not used; with ``strict`` a parameter that no file provides raises ``KeyError``."""
+    import os
+
+    from safetensors import safe_open
+
+    cfg = model.cfg
+    shard_rank, shard_world = model.expert_shard if model.expert_shard is not None else (0, 1)
+    e_local = cfg.num_experts // shard_world if cfg.num_experts else 0
+    route: Dict[str, Tuple[str, int, int]] = {}
+    for native, pieces in hf_parameter_map(model):
+        for hf_name, lo, hi in pieces:
+            route[hf_name] = (native, lo, hi)
+    stacked = {}
+    if cfg.num_experts:
+        for i in range(cfg.num_layers):
+            stacked[f"model.layers.{i}.mlp.experts.gate_up_proj"] = f"l{i}.w_gate_up"
+            stacked[f"model.layers.{i}.mlp.experts.down_proj"] = f"l{i}.w_down"
+    filled, unused, embed_seen = set(), [], False
+    for fname in checkpoint_files(directory):
+        with safe_open(os.path.join(directory, fname), framework="pt", device="cpu") as f:
+            for name in f.keys():
+                if name in stacked:
+                    dst = model.view(stacked[name])
+                    src = f.get_slice(name)[shard_rank * e_local : (shard_rank + 1) * e_local]
+                    src = src.reshape(-1, src.shape[-1])
+                    if tuple(src.shape) != tuple(dst.shape):
+                        raise ValueError(f"{name} gives {tuple(src.shape)} for this shard, {stacked[name]} needs {tuple(dst.shape)}")
+                    dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+                    filled.update(h for h, (nat, _lo, _hi) in route.items() if nat == stacked[name])
+                    continue
+                if name not in route:
+                    unused.append(name)
+                    continue
+                native, lo, hi = route[name]
+                part = model.view(native)[lo:hi]
+                src = f.get_tensor(name)
+                if tuple(src.shape) != tuple(part.shape):
+                    raise ValueError(f"{name} has shape {tuple(src.shape)}, {native}[{lo}:{hi}] needs {tuple(part.shape)}")
+                part.copy_(src.to(device=part.device, dtype=part.dtype))
+                filled.add(name)
+                embed_seen |= name == "model.embed_tokens.weight"
+    if "lm_head.weight" not in filled and embed_seen:          # tied embeddings: the head is the embedding
+        model.view("lm_head").copy_(model.view("embed"))
+        filled.add("lm_head.weight")
+    missing = sorted(set(route) - filled)
+    if missing and strict:
+        raise KeyError(f"the checkpoint in {directory} lacks {missing[:4]}{' ...' if len(missing) > 4 else ''}")
+    return sorted(unused)
+
+
+def model_from_hf_checkpoint(directory, *, dtype: torch.dtype = torch.bfloat16, device="cuda", expert_shard=None,
+                             **model_kwargs):
+    """A ``LlamaModel`` built from ``config.json`` and filled from the safetensors files of ``directory``."""
+    import json
+    import os
+
+    from rl_engine.models.llama import LlamaModel
+
+    with open(os.path.join(directory, "config.json")) as f:
+        raw = json.load(f)
+    model_kwargs.setdefault("max_positions", int(raw.get("max_position_embeddings", 0) or 8192))
+    model = LlamaModel(config_from_hf(raw), dtype=dtype, device=device, expert_shard=expert_shard, **model_kwargs)
+    load_hf_checkpoint(model, directory)
+    return model

@@ -413,8 +413,16 @@ class LlamaModel(nn.Module):
                 n = min(step, flat_dst.numel() - i)
                 flat_dst[i : i + n].copy_((torch.randn(n, generator=gen, device=dev) * 0.02).to(dst.dtype))
 
-    def state_dict_views(self) -> Dict[str, torch.Tensor]:
-        """Checkpoint-format names -> tensors (views of the flat buffer), for the weight bridge."""
+    def state_dict_views(self, names: str = "native") -> Dict[str, torch.Tensor]:
+        """Checkpoint-format names -> tensors (views of the flat buffer), for the weight bridge.  ``names="hf"``: the
+        names of the Hugging Face checkpoint of this architecture (``q_proj`` / ``k_proj`` / ``v_proj`` rows of the
+        packed ``wqkv`` and so on), still without a copy."""
+        if names == "hf":
+            from rl_engine.models.hf_interop import hf_state_dict_views
+
+            return hf_state_dict_views(self)
+        if names != "native":
+            raise ValueError(f"names must be 'native' or 'hf', got {names!r}")
         return {k: v.detach() for k, v in self.named_views().items()}
 
     # -- forward ----------------------------------------------------------------------------

@@ -160,3 +160,75 @@ def test_model_from_hf_and_publishing_checkpoint_names_through_a_bridge():
     for name, want in hf.state_dict().items():
         assert torch.equal(got[name], want), name
     bridge.acknowledge(manifest.update_id)
+
+
+def test_checkpoint_directory_round_trip_with_transformers(tmp_path):
+    """``save_hf_checkpoint`` writes a directory that ``transformers`` loads (same logits), sharded files carry an index,
+    and ``model_from_hf_checkpoint`` streams it back bit for bit; a tied checkpoint omits and restores the head."""
+    import json
+    import os
+
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.hf_interop import (
+        checkpoint_files, load_hf_checkpoint, model_from_hf_checkpoint, save_hf_checkpoint,
+    )
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("t", 71, 64, 2, 4, 2, 16, 112, rms_eps=1e-5, rope_theta=10000.0)
+    model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=5, activation_checkpointing=False, max_positions=64)
+    one = tmp_path / "one"
+    assert save_hf_checkpoint(model, one) == ["model.safetensors", "config.json"]
+    hf = transformers.AutoModelForCausalLM.from_pretrained(one, dtype=torch.float32).eval()
+    assert type(hf).__name__ == "LlamaForCausalLM" and hf.config.max_position_embeddings == 64
+    _compare_logits(hf, model, 71)
+    # sharded: several files and an index; streams back into a fresh model exactly
+    many = tmp_path / "many"
+    files = save_hf_checkpoint(model, many, max_shard_bytes=40_000)
+    assert "model.safetensors.index.json" in files and len(checkpoint_files(many)) >= 3
+    index = json.load(open(many / "model.safetensors.index.json"))
+    assert index["metadata"]["total_size"] == cfg.param_count() * 4
+    again = model_from_hf_checkpoint(many, dtype=torch.float32, device="cpu", seed=11, activation_checkpointing=False)
+    assert torch.equal(again.flat, model.flat) and again.rope_cos.shape[0] == 64
+    # tied: no head in the file, restored from the embedding on load
+    with torch.no_grad():
+        model.view("lm_head").copy_(model.view("embed"))
+    tied = tmp_path / "tied"
+    save_hf_checkpoint(model, tied, tie_word_embeddings=True)
+    from safetensors import safe_open
+
+    with safe_open(os.path.join(tied, "model.safetensors"), framework="pt") as f:
+        assert "lm_head.weight" not in f.keys()
+    fresh = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=3, activation_checkpointing=False, max_positions=64)
+    assert load_hf_checkpoint(fresh, tied) == [] and torch.equal(fresh.flat, model.flat)
+    # a checkpoint that lacks a tensor is an error, not a silently random parameter
+    from safetensors.torch import load_file, save_file
+
+    broken = tmp_path / "broken"
+    os.makedirs(broken)
+    state = load_file(os.path.join(one, "model.safetensors"))
+    state.pop("model.layers.1.mlp.down_proj.weight")
+    save_file(state, os.path.join(broken, "model.safetensors"))
+    with pytest.raises(KeyError, match="down_proj"):
+        load_hf_checkpoint(fresh, broken)
+
+
+def test_qwen3_moe_checkpoint_directory(tmp_path):
+    if not hasattr(transformers, "Qwen3MoeForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-MoE")
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.hf_interop import hf_config_dict, model_from_hf_checkpoint, save_hf_checkpoint
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("m", 67, 64, 2, 4, 2, 32, 96, rms_eps=1e-6, rope_theta=10000.0, num_experts=4, experts_per_token=2,
+                      moe_ffn_size=48, qk_norm=True)
+    assert hf_config_dict(cfg)["model_type"] == "qwen3_moe"
+    model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=6, activation_checkpointing=False, max_positions=64)
+    save_hf_checkpoint(model, tmp_path)                       # one tensor per expert: the on-disk convention
+    hf = transformers.AutoModelForCausalLM.from_pretrained(tmp_path, dtype=torch.float32).eval()
+    assert type(hf).__name__ == "Qwen3MoeForCausalLM"
+    _compare_logits(hf, model, 67, atol=5e-4)
+    shard = model_from_hf_checkpoint(tmp_path, dtype=torch.float32, device="cpu", expert_shard=(1, 2),
+                                     activation_checkpointing=False)
+    full_gate_up = model.view("l1.w_gate_up")
+    assert torch.equal(shard.view("l1.w_gate_up"), full_gate_up[full_gate_up.shape[0] // 2 :])
+    assert torch.equal(shard.view("l0.router"), model.view("l0.router"))

@@ -244,3 +244,20 @@ def test_cuda_home_discovery(tmp_path, monkeypatch):
     assert env["LD_LIBRARY_PATH"] == str(toolkit / "lib64") and ext.CUDA_HOME == str(toolkit)
     explicit = {"CUDA_HOME": "/opt/cuda-x"}
     assert ds.configure_cuda_home(explicit) == "/opt/cuda-x" and "PATH" not in explicit
+
+
+def test_worker_publishes_hugging_face_names_and_the_native_rollout_side_installs_them():
+    """``weight_names="hf"``: the manifest carries the names of the Hugging Face checkpoint of the architecture (what a
+    vLLM weight loader takes); the native rollout executor recognises them and fills its packed parameters."""
+    policy, rollout_copy = tiny(7), tiny(8)
+    bridge = make_weight_bridge("local-clone", source_worker="trainer")
+    worker = GRPOTrainingWorker(GRPOTrainingConfig(lr=1e-3, device="cpu", dtype=torch.float32, vocab_size=128,
+                                                   weight_names="hf"), model=policy, weight_bridge=bridge)
+    manifest = worker.publish_weights(0)
+    assert "model.layers.1.self_attn.k_proj.weight" in manifest.tensors and "l1.wqkv" not in manifest.tensors
+    assert manifest.tensors["model.layers.0.mlp.up_proj.weight"].shape == (48, 32)
+    executor = RolloutExecutor({"num_generations": 2}, weight_bridge=bridge, policy_model=rollout_copy)
+    executor.update_weights(manifest)
+    assert torch.equal(rollout_copy.flat, policy.flat) and executor.active_weight_version == 0
+    with pytest.raises(ValueError):
+        policy.state_dict_views(names="onnx")
