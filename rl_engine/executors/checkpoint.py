@@ -38,6 +38,66 @@ def _plain(value: Any) -> Any:
     raise TypeError(f"optimizer state holds a {type(value).__name__}, which a checkpoint cannot carry")
 
 
+class OptimizerShardReader:
+    """The flat optimizer vectors of a checkpoint, whatever number of ranks wrote it.
+
+    A job that lost a rank (or gained GPUs) resumes with another world size: the new ranks' slices of the flat
+    parameter vector are cut differently from the saved ones.  The reader maps every saved shard into the flat index
+    space (a shard of ``ShardedFusedAdamW`` carries its ``slices``; the state of ``FlatAdamW`` is one slice
+    ``[0, n)``) and hands out any range ``[lo, hi)`` of a vector by gathering from the shards that overlap it, so no
+    rank ever assembles a whole vector.  Shards are memory-mapped when the files allow it."""
+
+    def __init__(self, shards) -> None:
+        self._pieces = []                      # (lo, hi, offset into the shard's vectors, shard)
+        steps = set()
+        for shard in shards:
+            steps.add(int(shard["steps"]))
+            slices = shard.get("slices")
+            if slices is None:
+                slices = [[0, int(shard["m"].numel())]]
+            off = 0
+            for lo, hi in slices:
+                lo, hi = int(lo), int(hi)
+                if hi > lo:
+                    self._pieces.append((lo, hi, off, shard))
+                off += hi - lo
+        if len(steps) != 1:
+            raise ValueError(f"optimizer shards disagree on the step count: {sorted(steps)}")
+        self.steps = steps.pop()
+        self._pieces.sort(key=lambda piece: piece[0])
+        for (_, hi_a, _, _), (lo_b, _, _, _) in zip(self._pieces, self._pieces[1:]):
+            if lo_b < hi_a:
+                raise ValueError("optimizer shards overlap: not the shards of one checkpoint")
+        self.numel = self._pieces[-1][1] if self._pieces else 0
+
+    @classmethod
+    def from_directory(cls, directory: str, saved_world: int) -> "OptimizerShardReader":
+        shards = []
+        for r in range(max(1, int(saved_world))):
+            path = _optimizer_file(directory, r, saved_world)
+            if not os.path.exists(path):
+                raise FileNotFoundError(f"checkpoint has no optimizer state for rank {r} of {saved_world}: {path}")
+            try:
+                shards.append(torch.load(path, map_location="cpu", weights_only=True, mmap=True))
+            except (RuntimeError, ValueError):         # a file that cannot be mapped is read the plain way
+                shards.append(torch.load(path, map_location="cpu", weights_only=True))
+        return cls(shards)
+
+    def has(self, name: str) -> bool:
+        """Whether every shard holds vector ``name`` (``"m"``, ``"v"``, ``"master"``, ``"master_residual"``)."""
+        return bool(self._pieces) and all(shard.get(name) is not None for _, _, _, shard in self._pieces)
+
+    def read(self, name: str, lo: int, hi: int) -> torch.Tensor:
+        """Elements ``[lo, hi)`` of vector ``name`` on the CPU, zeros where no shard covers (padding past the end)."""
+        dtype = next((shard[name].dtype for _, _, _, shard in self._pieces if shard.get(name) is not None), torch.float32)
+        out = torch.zeros(max(0, hi - lo), dtype=dtype)
+        for p_lo, p_hi, off, shard in self._pieces:
+            a, b = max(lo, p_lo), min(hi, p_hi)
+            if b > a:
+                out[a - lo : b - lo] = shard[name][off + a - p_lo : off + b - p_lo]
+        return out
+
+
 def save_checkpoint(directory: str, model: Any, optimizer: Any = None, *, weight_version: int = 0,
                     sampler: Any = None, extra: Optional[Dict[str, Any]] = None, rank: int = 0,
                     world: int = 1) -> Optional[str]:
@@ -72,11 +132,18 @@ def load_checkpoint(directory: str, model: Any, optimizer: Any = None, *, sample
                     world: int = 1) -> Dict[str, Any]:
     """Restores weights (validated against the manifest), then the optimizer state of this ``rank`` (the optimizer's
     ``load_state_dict`` runs after the weights are in place, so it can re-derive master weights from them), then the
-    sampler's stream position.  Returns ``state.json``."""
+    sampler's stream position.  Returns ``state.json``.
+
+    ``world`` may differ from the number of ranks that saved (a job that resumes after losing a rank, or on more
+    GPUs): the weights are replicated, and an optimizer with ``accepts_resharded_state`` (``FlatAdamW``,
+    ``ShardedFusedAdamW``) gets an ``OptimizerShardReader`` over all saved shards and picks its new slices."""
     with open(os.path.join(directory, "state.json")) as f:
         state = json.load(f)
-    if int(state.get("world", 1)) != int(world):
-        raise ValueError(f"checkpoint was written by {state.get('world', 1)} rank(s), resuming with {world}")
+    saved_world = int(state.get("world", 1))
+    resharded = saved_world != int(world)
+    if resharded and optimizer is not None and not getattr(optimizer, "accepts_resharded_state", False):
+        raise ValueError(f"checkpoint was written by {saved_world} rank(s), resuming with {world}: "
+                         f"{type(optimizer).__name__} cannot take a re-cut optimizer state")
     bridge = FileBlobBridge(directory, source_worker="checkpoint")
     manifest = bridge.load_manifest(state["update_id"])
     tensors = bridge.import_update(manifest)
@@ -88,7 +155,10 @@ def load_checkpoint(directory: str, model: Any, optimizer: Any = None, *, sample
         dst.copy_(tensors[name].to(device=dst.device, dtype=dst.dtype))
     bridge.acknowledge(manifest.update_id)
     opt_path = _optimizer_file(directory, rank, world)
-    if optimizer is not None:
+    if optimizer is not None and resharded:
+        # another world size than the one that saved: every rank reads its new slices out of all the saved shards
+        optimizer.load_state_dict(OptimizerShardReader.from_directory(directory, saved_world))
+    elif optimizer is not None:
         if not os.path.exists(opt_path):
             raise FileNotFoundError(f"checkpoint has no optimizer state for rank {rank} of {world}: {opt_path}")
         optimizer.load_state_dict(torch.load(opt_path, map_location="cpu", weights_only=True))

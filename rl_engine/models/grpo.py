@@ -150,9 +150,20 @@ class FlatAdamW:
         ``master_residual`` (int16, to be joined with the saved bf16 parameters), so saving allocates nothing large."""
         return {"m": self.m, "v": self.v, "master": self.master, "master_residual": self.residual, "steps": self.steps}
 
-    def load_state_dict(self, state: Dict[str, object]) -> None:
+    accepts_resharded_state = True
+
+    def load_state_dict(self, state) -> None:
         """Call after the parameters have been restored.  A checkpoint without a master re-seeds the master from
-        the loaded parameters instead of keeping the values it had before."""
+        the loaded parameters instead of keeping the values it had before.  ``state`` may be an
+        ``OptimizerShardReader`` (a checkpoint written by several data-parallel ranks): the whole vectors are then
+        gathered from the shards."""
+        if hasattr(state, "read"):
+            n = self.param.numel()
+            if state.numel > (n + 7) // 8 * 8:
+                raise ValueError(f"the checkpoint's optimizer state covers {state.numel} elements, this model has {n}")
+            state = {"m": state.read("m", 0, n), "v": state.read("v", 0, n), "steps": state.steps,
+                     "master": state.read("master", 0, n) if state.has("master") else None,
+                     "master_residual": state.read("master_residual", 0, n) if state.has("master_residual") else None}
         self.m.copy_(state["m"])
         self.v.copy_(state["v"])
         self.steps = int(state["steps"])

@@ -167,10 +167,48 @@ class ShardedFusedAdamW:
         return {"m": self.m, "v": self.v, "master": self.master, "steps": self.steps, "rank": self.mem.rank,
                 "world": self.mem.world, "slices": [[lo, hi] for lo, hi, _ in self.slices]}
 
+    accepts_resharded_state = True
+
+    @torch.no_grad()
+    def _load_resharded(self, reader) -> None:
+        """This rank's slices out of a checkpoint written by any number of ranks (``reader``: an
+        ``OptimizerShardReader``).  Master weights come from the saved fp32 masters, else from saved bf16 residuals
+        joined with the restored parameters, else from the restored parameters."""
+        from rl_engine.models.grpo import join_master
+
+        if reader.numel > self.params.local.numel():
+            raise ValueError(f"the checkpoint's optimizer state covers {reader.numel} elements, this model has "
+                             f"{self.params.local.numel()}")
+        dev = self.m.device
+        for lo, hi, off in self.slices:
+            n = hi - lo
+            if n <= 0:
+                continue
+            self.m[off : off + n].copy_(reader.read("m", lo, hi).to(dev))
+            self.v[off : off + n].copy_(reader.read("v", lo, hi).to(dev))
+            if self.master is None:
+                continue
+            param = self.params.local[lo:hi]
+            if reader.has("master"):
+                master = reader.read("master", lo, hi).to(dev)
+                # padding past the checkpoint's end is not covered by any shard: keep the parameter there
+                if hi > reader.numel:
+                    master[max(0, reader.numel - lo):] = param[max(0, reader.numel - lo):].float()
+            elif reader.has("master_residual") and param.dtype == torch.bfloat16:
+                master = join_master(param, reader.read("master_residual", lo, hi).to(dev))
+            else:
+                master = param.float()
+            self.master[off : off + n].copy_(master)
+        self.steps = int(reader.steps)
+
     @torch.no_grad()
     def load_state_dict(self, state) -> None:
-        """Restores a shard saved by the same rank of the same world size and bucket layout.  Call after the
+        """Restores a shard saved by the same rank of the same world size and bucket layout, or (given an
+        ``OptimizerShardReader``) this rank's part of a checkpoint written with another world size.  Call after the
         parameters were restored; a checkpoint without master weights re-seeds them from the parameters."""
+        if hasattr(state, "read"):
+            self._load_resharded(state)
+            return
         mine = [[lo, hi] for lo, hi, _ in self.slices]
         theirs = [list(map(int, s)) for s in state.get("slices", [])]
         if theirs != mine or int(state.get("world", self.mem.world)) != self.mem.world \

@@ -80,14 +80,14 @@ def test_optimizer_file_is_loaded_without_unpickling_code(tmp_path):
         load_checkpoint(str(tmp_path), model, opt)
 
 
-def test_missing_optimizer_shard_and_world_mismatch_are_errors(tmp_path):
+def test_missing_optimizer_shard_is_an_error_and_weights_load_at_any_world_size(tmp_path):
     model = tiny()
     opt = FlatAdamW(model, lr=1e-3)
     save_checkpoint(str(tmp_path), model, None, weight_version=1)
     with pytest.raises(FileNotFoundError):
         load_checkpoint(str(tmp_path), model, opt)
-    with pytest.raises(ValueError):
-        load_checkpoint(str(tmp_path), model, None, world=2)
+    # the weights are replicated: loading them alone works for any number of ranks
+    assert load_checkpoint(str(tmp_path), model, None, world=2)["world"] == 1
 
 
 def _sharded(model, rank, world):
@@ -134,3 +134,64 @@ def test_sharded_optimizer_state_round_trip_per_rank(tmp_path):
     fresh.params.local.fill_(0.5)
     fresh.load_state_dict(state)
     assert torch.equal(fresh.master, torch.full_like(fresh.master, 0.5))
+
+
+def test_resume_with_another_world_size_recuts_the_optimizer_state(tmp_path):
+    """Saved by 3 ranks, resumed by 2 ranks, by 1 (``FlatAdamW``), and back from 1 to 3: every element of the moments
+    and the master weights lands at the same flat index."""
+    from rl_engine.executors.checkpoint import OptimizerShardReader
+
+    model = tiny()
+    n = model.flat.numel()
+    three = [_sharded(model, r, 3) for r in range(3)]
+    n_pad = three[0].params.local.numel()
+    truth = {k: torch.zeros(n_pad) for k in ("m", "v", "master")}
+    gen = torch.Generator().manual_seed(5)
+    for r, sh in enumerate(three):
+        sh.m.copy_(torch.rand(sh.m.shape, generator=gen) - 0.5)
+        sh.v.copy_(torch.rand(sh.v.shape, generator=gen))
+        sh.master.add_(torch.rand(sh.master.shape, generator=gen) * 1e-3)
+        sh.steps = 6
+        for lo, hi, off in sh.slices:
+            for k in truth:
+                truth[k][lo:hi] = getattr(sh, k)[off : off + hi - lo]
+        save_checkpoint(str(tmp_path / "w3"), model, sh, weight_version=3, rank=r, world=3)
+    reader = OptimizerShardReader.from_directory(str(tmp_path / "w3"), 3)
+    assert reader.steps == 6 and reader.numel == n_pad and reader.has("master") and not reader.has("master_residual")
+    assert torch.equal(reader.read("m", 5, 77), truth["m"][5:77])
+    # 3 -> 2
+    for r in range(2):
+        sh = _sharded(model, r, 2)
+        state = load_checkpoint(str(tmp_path / "w3"), model, sh, rank=r, world=2)
+        assert state["world"] == 3 and sh.steps == 6
+        for lo, hi, off in sh.slices:
+            for k in truth:
+                assert torch.equal(getattr(sh, k)[off : off + hi - lo], truth[k][lo:hi]), (k, r)
+    # 3 -> 1
+    flat = FlatAdamW(model, lr=1e-3)
+    load_checkpoint(str(tmp_path / "w3"), model, flat, world=1)
+    assert torch.equal(flat.m, truth["m"][:n]) and torch.equal(flat.v, truth["v"][:n]) and flat.steps == 6
+    # 1 -> 3: the flat state is one slice [0, n); padding past n keeps the parameter as its master
+    flat.m.mul_(2.0)
+    save_checkpoint(str(tmp_path / "w1"), model, flat, weight_version=4)
+    for r in range(3):
+        sh = _sharded(model, r, 3)
+        load_checkpoint(str(tmp_path / "w1"), model, sh, rank=r, world=3)
+        for lo, hi, off in sh.slices:
+            top = min(hi, n)
+            assert torch.equal(sh.m[off : off + top - lo], flat.m[lo:top])
+            if flat.master is not None:
+                assert torch.equal(sh.master[off : off + top - lo], flat.master[lo:top])
+    # shards of different checkpoints are refused
+    torch.save({"m": torch.zeros(4), "v": torch.zeros(4), "master": None, "steps": 1, "slices": [[0, 4]]}, tmp_path / "a.pt")
+    with pytest.raises(ValueError, match="step count"):
+        OptimizerShardReader([torch.load(tmp_path / "a.pt", weights_only=True),
+                              {"m": torch.zeros(4), "v": torch.zeros(4), "steps": 2, "slices": [[4, 8]]}])
+    with pytest.raises(ValueError, match="overlap"):
+        OptimizerShardReader([{"m": torch.zeros(4), "v": torch.zeros(4), "steps": 1, "slices": [[0, 4]]},
+                              {"m": torch.zeros(4), "v": torch.zeros(4), "steps": 1, "slices": [[2, 6]]}])
+    # an optimizer that cannot take a re-cut state still gets the explicit error
+    class Plain:
+        def load_state_dict(self, state): raise AssertionError("must not be called")
+    with pytest.raises(ValueError, match="written by 3"):
+        load_checkpoint(str(tmp_path / "w3"), model, Plain(), world=2)
