@@ -22,7 +22,6 @@ import torch
 from torch import nn
 from torch.utils.checkpoint import checkpoint
 
-from rl_engine.kernels.ops.pytorch.attention import NativeAttentionOp  # noqa: F401  (CPU oracle family)
 from rl_engine.kernels.ops.pytorch.linear.rope import rope_cos_sin
 from rl_engine.models.activation_plan import ActivationPlanner
 from rl_engine.models.config import ModelConfig
