@@ -184,31 +184,32 @@ class FusedRoPESM100Op:
         self._native = NativeRoPEOp()
         self._tables = {}
 
-    def tables(self, max_pos: int, head_dim: int, theta: float, device) -> tuple:
-        key = (int(max_pos), head_dim, float(theta), str(device))
+    def tables(self, max_pos: int, head_dim: int, theta: float, device, scaling=None) -> tuple:
+        key = (int(max_pos), head_dim, float(theta), str(device), scaling)
         hit = self._tables.get(key)
         if hit is None:
-            cos, sin = rope_cos_sin(torch.arange(max_pos, device=device), head_dim, theta)
+            cos, sin = rope_cos_sin(torch.arange(max_pos, device=device), head_dim, theta, scaling)
             hit = self._tables[key] = (cos.contiguous(), sin.contiguous())
         return hit
 
-    def __call__(self, x, positions, *, theta: float = 10000.0, tables=None):
-        return self.forward(x, positions, theta=theta, tables=tables)
+    def __call__(self, x, positions, *, theta: float = 10000.0, tables=None, scaling=None):
+        return self.forward(x, positions, theta=theta, tables=tables, scaling=scaling)
 
-    def forward(self, x, positions, *, theta: float = 10000.0, tables=None):
+    def forward(self, x, positions, *, theta: float = 10000.0, tables=None, scaling=None):
+        """``scaling``: context-extension rule of the rotary frequencies (``scaled_inv_freq``), ``None`` for none."""
         if not _ok(x):
-            return self._native.forward(x, positions, theta=theta)
+            return self._native.forward(x, positions, theta=theta, scaling=scaling)
         heads, d = x.shape[-2], x.shape[-1]
         x3 = x.reshape(-1, heads, d).contiguous()
         pos = positions.reshape(-1).to(torch.long).contiguous()
         if tables is None:
             # table length rounded up to a power of two so it is built at most log(max_pos) times
             need = int(pos.max()) + 1 if pos.numel() else 1
-            tables = self.tables(1 << max(need - 1, 1).bit_length(), d, theta, x.device)
+            tables = self.tables(1 << max(need - 1, 1).bit_length(), d, theta, x.device, scaling)
         return _RoPE.apply(x3, pos, tables[0], tables[1]).reshape(x.shape)
 
-    def forward_fp32(self, x, positions, *, theta: float = 10000.0):
-        return self._native.forward_fp32(x, positions, theta=theta)
+    def forward_fp32(self, x, positions, *, theta: float = 10000.0, scaling=None):
+        return self._native.forward_fp32(x, positions, theta=theta, scaling=scaling)
 
 
 # ---------------------------------------------------------------------------------- embedding

@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, replace
+from typing import Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -22,6 +23,9 @@ class ModelConfig:
     experts_per_token: int = 0
     moe_ffn_size: int = 0
     qk_norm: bool = False
+    # context extension of the rotary embedding: None, or (kind, factor, low_freq_factor, high_freq_factor,
+    # original_max_positions) with kind "linear" or "llama3" (see ``scaled_inv_freq``)
+    rope_scaling: Optional[Tuple[str, float, float, float, int]] = None
 
     @property
     def q_dim(self) -> int:
@@ -47,6 +51,26 @@ class ModelConfig:
 def llama3_8b() -> ModelConfig:
     """Llama-3-8B: 32 layers, hidden 4096, 32 q / 8 kv heads of 128, FFN 14336, vocab 128256."""
     return ModelConfig("llama3-8b", 128256, 4096, 32, 32, 8, 128, 14336, rms_eps=1e-5, rope_theta=500000.0)
+
+
+def llama31_8b() -> ModelConfig:
+    """Llama-3.1-8B: the Llama-3-8B architecture with the "llama3" rotary scaling (factor 8 over 8 192 positions)."""
+    return replace(llama3_8b(), name="llama3.1-8b", rope_scaling=("llama3", 8.0, 1.0, 4.0, 8192))
+
+
+def llama3_70b() -> ModelConfig:
+    """Llama-3-70B: 80 layers, hidden 8192, 64 q / 8 kv heads of 128, FFN 28672, vocab 128256."""
+    return ModelConfig("llama3-70b", 128256, 8192, 80, 64, 8, 128, 28672, rms_eps=1e-5, rope_theta=500000.0)
+
+
+def qwen3_8b() -> ModelConfig:
+    """Qwen3-8B (dense): 36 layers, hidden 4096, 32 q / 8 kv heads of 128 with per-head q/k norms, FFN 12288."""
+    return ModelConfig("qwen3-8b", 151936, 4096, 36, 32, 8, 128, 12288, rms_eps=1e-6, rope_theta=1000000.0, qk_norm=True)
+
+
+def qwen3_32b() -> ModelConfig:
+    """Qwen3-32B (dense): 64 layers, hidden 5120, 64 q / 8 kv heads of 128 with per-head q/k norms, FFN 25600."""
+    return ModelConfig("qwen3-32b", 151936, 5120, 64, 64, 8, 128, 25600, rms_eps=1e-6, rope_theta=1000000.0, qk_norm=True)
 
 
 def qwen3_30b_a3b() -> ModelConfig:

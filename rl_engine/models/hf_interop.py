@@ -29,9 +29,16 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
     get = (lambda k, d=None: hf_config.get(k, d)) if isinstance(hf_config, Mapping) else (lambda k, d=None: getattr(hf_config, k, d))
     hidden, heads = int(get("hidden_size")), int(get("num_attention_heads"))
     head_dim = int(get("head_dim") or hidden // heads)
-    scaling = get("rope_scaling")
-    if scaling and (scaling.get("rope_type", scaling.get("type")) not in (None, "default")):
-        raise ValueError(f"rope scaling {scaling} is not supported (plain rotary embedding only)")
+    scaling = get("rope_scaling") or (get("rope_parameters") if isinstance(get("rope_parameters"), Mapping) else None)
+    rope_scaling = None
+    kind = (scaling.get("rope_type", scaling.get("type")) if scaling else None) or "default"
+    if kind == "linear":
+        rope_scaling = ("linear", float(scaling["factor"]), 1.0, 1.0, 0)
+    elif kind == "llama3":
+        rope_scaling = ("llama3", float(scaling["factor"]), float(scaling.get("low_freq_factor", 1.0)),
+                        float(scaling.get("high_freq_factor", 4.0)), int(scaling["original_max_position_embeddings"]))
+    elif kind != "default":
+        raise ValueError(f"rope scaling {scaling} is not supported (known: default, linear, llama3)")
     if get("attention_bias", False) or get("mlp_bias", False):
         raise ValueError("projections with a bias are not supported")
     experts = int(get("num_experts", 0) or get("num_local_experts", 0) or 0)
@@ -49,7 +56,7 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
         rms_eps=float(get("rms_norm_eps", 1e-5)), rope_theta=float(rope_theta if rope_theta is not None else 10000.0),
         num_experts=experts, experts_per_token=int(get("num_experts_per_tok", 0) or 0) if experts else 0,
         moe_ffn_size=int(get("moe_intermediate_size", 0) or 0) if experts else 0,
-        qk_norm=model_type.startswith("qwen3"),
+        qk_norm=model_type.startswith("qwen3"), rope_scaling=rope_scaling,
     )
 
 
@@ -173,6 +180,13 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
     }
     if kind == "llama":
         out["mlp_bias"] = False
+    if cfg.rope_scaling is not None:
+        how, factor, low, high, original = cfg.rope_scaling
+        block = {"rope_type": how, "factor": factor}
+        if how == "llama3":
+            block.update(low_freq_factor=low, high_freq_factor=high, original_max_position_embeddings=original)
+        out["rope_scaling"] = dict(block)
+        out["rope_parameters"] = dict(block, rope_theta=cfg.rope_theta)      # the spelling of newer transformers
     if moe:
         out.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token, moe_intermediate_size=cfg.moe_ffn_size,
                    norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])

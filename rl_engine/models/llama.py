@@ -354,7 +354,7 @@ class LlamaModel(nn.Module):
         )
         self._index = {name: i for i, name in enumerate(self._names)}
         self.reset_parameters(seed)
-        cos, sin = rope_cos_sin(torch.arange(max_positions, device=device), cfg.head_dim, cfg.rope_theta)
+        cos, sin = rope_cos_sin(torch.arange(max_positions, device=device), cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
         self.register_buffer("rope_cos", cos.contiguous(), persistent=False)
         self.register_buffer("rope_sin", sin.contiguous(), persistent=False)
 
@@ -461,8 +461,9 @@ class LlamaModel(nn.Module):
         from rl_engine.kernels.registry import kernel_registry
 
         rope = kernel_registry.get_op("rope")
-        q = rope(qkv3[:, : cfg.num_heads], positions, theta=cfg.rope_theta)
-        k = rope(qkv3[:, cfg.num_heads : cfg.num_heads + cfg.num_kv_heads], positions, theta=cfg.rope_theta)
+        q = rope(qkv3[:, : cfg.num_heads], positions, theta=cfg.rope_theta, scaling=cfg.rope_scaling)
+        k = rope(qkv3[:, cfg.num_heads : cfg.num_heads + cfg.num_kv_heads], positions, theta=cfg.rope_theta,
+                 scaling=cfg.rope_scaling)
         v = qkv3[:, cfg.num_heads + cfg.num_kv_heads :]
         out = reference_packed_attention(q, k, v, layout.host_seqs, layout.causal, scale)
         return out.reshape(t, cfg.q_dim)

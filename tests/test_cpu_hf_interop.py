@@ -71,7 +71,7 @@ def test_tied_embeddings_and_unsupported_configurations():
     _compare_logits(hf, model, 50)
     with pytest.raises(ValueError):
         config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
-                        "intermediate_size": 8, "rope_scaling": {"rope_type": "llama3", "factor": 8.0}})
+                        "intermediate_size": 8, "rope_scaling": {"rope_type": "yarn", "factor": 8.0}})
     with pytest.raises(ValueError):
         config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
                         "intermediate_size": 8, "attention_bias": True})
@@ -232,3 +232,53 @@ def test_qwen3_moe_checkpoint_directory(tmp_path):
     full_gate_up = model.view("l1.w_gate_up")
     assert torch.equal(shard.view("l1.w_gate_up"), full_gate_up[full_gate_up.shape[0] // 2 :])
     assert torch.equal(shard.view("l0.router"), model.view("l0.router"))
+
+
+@pytest.mark.parametrize("scaling", [
+    {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 16},
+    {"rope_type": "linear", "factor": 2.0},
+])
+def test_rope_scaling_matches_transformers(scaling, tmp_path):
+    """Llama-3.1-style and linear context extension: with 16 original positions and head_dim 16 the eight rotary
+    frequencies fall into all three bands of the llama3 rule (kept, blended, divided), and 40 positions reach past the
+    original range; logits must agree with ``transformers``, and the configuration must survive a save / load."""
+    from rl_engine.models.hf_interop import config_from_hf, hf_config_dict, model_from_hf, save_hf_checkpoint
+
+    config = transformers.LlamaConfig(vocab_size=59, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                      num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=64,
+                                      rope_theta=10000.0, rope_scaling=dict(scaling), tie_word_embeddings=False)
+    torch.manual_seed(8)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    model = model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert model.cfg.rope_scaling is not None and model.cfg.rope_scaling[0] == scaling["rope_type"]
+    from rl_engine.models.causal_lm import PackedCausalLM
+
+    ids = torch.randint(0, 59, (2, 40), generator=torch.Generator().manual_seed(9))
+    with torch.no_grad():
+        want = hf(input_ids=ids, use_cache=False).logits.float()
+        got = PackedCausalLM(model)(ids).logits.float()
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
+    # the scaling changes the result (the test would pass vacuously otherwise) ...
+    from dataclasses import replace
+    from rl_engine.models.llama import LlamaModel
+
+    plain = LlamaModel(replace(model.cfg, rope_scaling=None), dtype=torch.float32, device="cpu", activation_checkpointing=False,
+                       max_positions=64)
+    plain.flat.data.copy_(model.flat.data)
+    with torch.no_grad():
+        assert float((PackedCausalLM(plain)(ids).logits.float() - want).abs().max()) > 1e-4
+    # ... and survives config.json
+    assert config_from_hf(hf_config_dict(model.cfg)).rope_scaling == model.cfg.rope_scaling
+    save_hf_checkpoint(model, tmp_path)
+    again = transformers.AutoModelForCausalLM.from_pretrained(tmp_path, dtype=torch.float32).eval()
+    with torch.no_grad():
+        assert torch.allclose(again(input_ids=ids, use_cache=False).logits.float(), want, atol=1e-5)
+
+
+def test_presets_describe_the_published_architectures():
+    from rl_engine.models import llama3_70b, llama3_8b, llama31_8b, qwen3_8b, qwen3_30b_a3b, qwen3_32b
+
+    billions = lambda cfg: cfg.param_count() / 1e9  # noqa: E731
+    assert 7.9 < billions(llama3_8b()) < 8.1 and 69 < billions(llama3_70b()) < 72
+    assert 8.0 < billions(qwen3_8b()) < 8.4 and 32 < billions(qwen3_32b()) < 33.5 and 30 < billions(qwen3_30b_a3b()) < 31
+    assert llama31_8b().rope_scaling == ("llama3", 8.0, 1.0, 4.0, 8192) and llama31_8b().param_count() == llama3_8b().param_count()
