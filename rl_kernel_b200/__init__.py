@@ -21,6 +21,8 @@ _ALIASES = {
     "executors": "rl_engine.executors",
     "testing": "rl_engine.testing",
     "platforms": "rl_engine.platforms",
+    "alignment": "rl_engine.alignment",
+    "integrations": "rl_engine.integrations",
 }
 
 
