@@ -26,6 +26,9 @@ class ModelConfig:
     # context extension of the rotary embedding: None, or (kind, factor, low_freq_factor, high_freq_factor,
     # original_max_positions) with kind "linear" or "llama3" (see ``scaled_inv_freq``)
     rope_scaling: Optional[Tuple[str, float, float, float, int]] = None
+    # the LM head is the embedding matrix (small Llama-3.2 / Qwen3 models).  The model still stores both; they start
+    # equal and the optimiser gives both the summed gradient, so they stay equal bit for bit.
+    tie_word_embeddings: bool = False
 
     @property
     def q_dim(self) -> int:
@@ -46,6 +49,14 @@ class ModelConfig:
             ffn = 3 * self.hidden_size * self.ffn_size
         per_layer = attn + ffn + 2 * self.hidden_size
         return self.num_layers * per_layer + 2 * self.vocab_size * self.hidden_size + self.hidden_size
+
+
+def require_untied(cfg: ModelConfig, what: str) -> None:
+    """Tied embeddings are kept equal by ``FlatAdamW`` (one GPU).  The sharded, tensor-parallel and pipeline trainers
+    step the embedding and the head in different buckets, ranks or stages and would let them drift apart."""
+    if cfg.tie_word_embeddings:
+        raise ValueError(f"{what} does not support tied embeddings: train this model with GRPOTrainer on one GPU, or "
+                         f"untie it (dataclasses.replace(cfg, tie_word_embeddings=False))")
 
 
 def llama3_8b() -> ModelConfig:

@@ -122,9 +122,21 @@ class FlatAdamW:
     def zero_grad(self) -> None:
         self.grad.zero_()
 
+    def _tie_gradients(self) -> None:
+        """Tied embeddings: the embedding and the LM head are one matrix, so each gets the sum of both gradients.
+        They start equal and see the same update from the same optimiser state, hence stay equal bit for bit."""
+        cfg = getattr(self.model, "cfg", None)
+        if cfg is None or not getattr(cfg, "tie_word_embeddings", False):
+            return
+        g_embed = self.model._slice(self.grad, "embed")
+        g_head = self.model._slice(self.grad, "lm_head")
+        g_embed.add_(g_head)
+        g_head.copy_(g_embed)
+
     @torch.no_grad()
     def step(self, grad_scale: Optional[float] = None) -> None:
         grad_scale = self.grad_scale if grad_scale is None else float(grad_scale)
+        self._tie_gradients()
         self.steps += 1
         p, g = self.param, self.grad
         if p.is_cuda:

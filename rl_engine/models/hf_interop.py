@@ -17,7 +17,7 @@ against ``transformers`` on CPU in fp32).
 
 from __future__ import annotations
 
-from typing import Any, Dict, Iterator, List, Mapping, Tuple
+from typing import Any, Dict, Iterator, List, Mapping, Optional, Tuple
 
 import torch
 
@@ -57,6 +57,7 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
         num_experts=experts, experts_per_token=int(get("num_experts_per_tok", 0) or 0) if experts else 0,
         moe_ffn_size=int(get("moe_intermediate_size", 0) or 0) if experts else 0,
         qk_norm=model_type.startswith("qwen3"), rope_scaling=rope_scaling,
+        tie_word_embeddings=bool(get("tie_word_embeddings", False)),
     )
 
 
@@ -163,8 +164,11 @@ _INDEX_NAME = "model.safetensors.index.json"
 
 
 def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max_position_embeddings: int = 8192,
-                   tie_word_embeddings: bool = False) -> Dict[str, Any]:
-    """The ``config.json`` of ``cfg``: the inverse of ``config_from_hf`` (Llama, Qwen3 and Qwen3-MoE architectures)."""
+                   tie_word_embeddings: Optional[bool] = None) -> Dict[str, Any]:
+    """The ``config.json`` of ``cfg``: the inverse of ``config_from_hf`` (Llama, Qwen3 and Qwen3-MoE architectures).
+    ``tie_word_embeddings`` defaults to the configuration's own flag."""
+    if tie_word_embeddings is None:
+        tie_word_embeddings = cfg.tie_word_embeddings
     moe, qwen = bool(cfg.num_experts), bool(cfg.qk_norm)
     if moe and not qwen:
         raise ValueError("mixture-of-experts checkpoints are written as Qwen3-MoE, which has per-head q/k norms")
@@ -193,7 +197,7 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
     return out
 
 
-def save_hf_checkpoint(model, directory, *, max_shard_bytes: int = 5 << 30, tie_word_embeddings: bool = False,
+def save_hf_checkpoint(model, directory, *, max_shard_bytes: int = 5 << 30, tie_word_embeddings: Optional[bool] = None,
                        max_position_embeddings: int = 0) -> List[str]:
     """Writes ``model`` (all experts local) as a Hugging Face checkpoint: ``config.json`` plus one or more
     ``model-xxxxx-of-yyyyy.safetensors`` files cut at ``max_shard_bytes`` and the index that maps names to files.
@@ -208,6 +212,8 @@ def save_hf_checkpoint(model, directory, *, max_shard_bytes: int = 5 << 30, tie_
         raise ValueError("an expert-sharded model holds only its own experts; gather them before saving")
     os.makedirs(directory, exist_ok=True)
     views = hf_state_dict_views(model)
+    if tie_word_embeddings is None:
+        tie_word_embeddings = model.cfg.tie_word_embeddings
     if tie_word_embeddings:
         views.pop("lm_head.weight")
     shards: List[List[str]] = [[]]

@@ -411,6 +411,8 @@ class LlamaModel(nn.Module):
             for i in range(0, flat_dst.numel(), step):
                 n = min(step, flat_dst.numel() - i)
                 flat_dst[i : i + n].copy_((torch.randn(n, generator=gen, device=dev) * 0.02).to(dst.dtype))
+        if self.cfg.tie_word_embeddings:
+            self._slice(self.flat, "lm_head").copy_(self._slice(self.flat, "embed"))
 
     def state_dict_views(self, names: str = "native") -> Dict[str, torch.Tensor]:
         """Checkpoint-format names -> tensors (views of the flat buffer), for the weight bridge.  ``names="hf"``: the

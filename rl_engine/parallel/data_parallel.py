@@ -28,6 +28,7 @@ import torch
 
 from rl_engine.kernels.ops.base import require_ext
 from rl_engine.models.grpo import GRPOBatch, GRPOTrainer, _PromptPass
+from rl_engine.models.config import require_untied
 from rl_engine.models.llama import LlamaModel
 from rl_engine.parallel.symmetric import SymmetricMemory
 
@@ -64,6 +65,7 @@ class ShardedFusedAdamW:
                  weight_decay=0.0, master_weights: bool = True, layers_per_bucket: int = 4, overlap: bool = True,
                  overlap_blocks: int = 148 * 2) -> None:
         self.model, self.mem, self.params, self.grads = model, mem, params, grads
+        require_untied(model.cfg, type(self).__name__)
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         n = model.flat.numel()
         ranges, self.ready_at, self.local_ranges = self._plan_buckets(model, layers_per_bucket)

@@ -151,8 +151,11 @@ class LlamaPipelineStage:
     ``[T, H]`` elsewhere; the last stage returns final-norm hidden states."""
 
     def __init__(self, cfg, stage: int, stages: int, *, dtype=torch.bfloat16, device="cpu", seed: int = 0, **model_kw) -> None:
+        from rl_engine.models.config import require_untied
         from rl_engine.models.llama import LlamaModel
 
+        if stages > 1:
+            require_untied(cfg, type(self).__name__)      # the embedding and the head live on different stages
         self.stage, self.stages = int(stage), int(stages)
         self.layers = stage_layers(cfg.num_layers, stages)[stage]
         self.model = LlamaModel(cfg.with_layers(len(self.layers)), dtype=dtype, device=device, seed=seed + stage, **model_kw)

@@ -282,3 +282,60 @@ def test_presets_describe_the_published_architectures():
     assert 7.9 < billions(llama3_8b()) < 8.1 and 69 < billions(llama3_70b()) < 72
     assert 8.0 < billions(qwen3_8b()) < 8.4 and 32 < billions(qwen3_32b()) < 33.5 and 30 < billions(qwen3_30b_a3b()) < 31
     assert llama31_8b().rope_scaling == ("llama3", 8.0, 1.0, 4.0, 8192) and llama31_8b().param_count() == llama3_8b().param_count()
+
+
+def test_tied_embeddings_stay_tied_through_training_and_round_trip(tmp_path):
+    """A tied Hugging Face model (small Llama-3.2 / Qwen3 style) keeps ``embed == lm_head`` bit for bit over optimiser
+    steps: both get the summed gradient.  The saved checkpoint omits the head and ``transformers`` ties it again."""
+    from dataclasses import replace
+
+    from rl_engine.models.grpo import GRPOBatch, GRPOTrainer
+    from rl_engine.models.hf_interop import model_from_hf, save_hf_checkpoint
+    from rl_engine.models.config import require_untied
+
+    config = transformers.LlamaConfig(vocab_size=53, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                      num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=48,
+                                      tie_word_embeddings=True)
+    torch.manual_seed(10)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    model = model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert model.cfg.tie_word_embeddings and torch.equal(model.view("embed"), model.view("lm_head"))
+    trainer = GRPOTrainer(model, lr=1e-2, micro_group=2)
+    gen = torch.Generator().manual_seed(11)
+    start = model.view("embed").detach().clone()
+    seen = {}
+    real_tie = trainer.opt._tie_gradients
+
+    def spy():
+        seen["embed"] = model._slice(trainer.opt.grad, "embed").clone()
+        seen["head"] = model._slice(trainer.opt.grad, "lm_head").clone()
+        real_tie()
+        seen["tied"] = model._slice(trainer.opt.grad, "embed").clone()
+
+    trainer.opt._tie_gradients = spy
+    for _ in range(3):
+        batch = GRPOBatch(prompt_ids=torch.randint(0, 53, (6,), generator=gen),
+                          completion_ids=torch.randint(0, 53, (4, 5), generator=gen),
+                          completion_mask=torch.ones(4, 5, dtype=torch.bool), rewards=torch.randn(4, generator=gen),
+                          old_logps=torch.full((4, 5), -4.0), ref_logps=torch.full((4, 5), -4.0))
+        trainer.step_device(batch)
+        assert torch.equal(model.view("embed"), model.view("lm_head"))
+    assert not torch.equal(model.view("embed"), start)
+    assert torch.equal(seen["tied"], seen["embed"] + seen["head"]) and float(seen["head"].abs().max()) > 0
+    # untied configuration of the same model: the two matrices drift apart (so the tie above is doing the work)
+    free = model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    free.cfg = replace(free.cfg, tie_word_embeddings=False)
+    other = GRPOTrainer(free, lr=1e-2, micro_group=2)
+    other.step_device(batch)
+    assert not torch.equal(free.view("embed"), free.view("lm_head"))
+    # checkpoint: head left out, transformers ties it again, logits agree
+    files = save_hf_checkpoint(model, tmp_path)
+    from safetensors import safe_open
+
+    with safe_open(str(tmp_path / files[0]), framework="pt") as f:
+        assert "lm_head.weight" not in f.keys()
+    again = transformers.AutoModelForCausalLM.from_pretrained(tmp_path, dtype=torch.float32).eval()
+    assert again.config.tie_word_embeddings
+    _compare_logits(again, model, 53)
+    with pytest.raises(ValueError, match="tied embeddings"):
+        require_untied(model.cfg, "ShardedFusedAdamW")
