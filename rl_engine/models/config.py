@@ -29,6 +29,8 @@ class ModelConfig:
     # the LM head is the embedding matrix (small Llama-3.2 / Qwen3 models).  The model still stores both; they start
     # equal and the optimiser gives both the summed gradient, so they stay equal bit for bit.
     tie_word_embeddings: bool = False
+    # Qwen2 / Qwen2.5: the q, k and v projections carry a bias (the output projection and the FFN do not)
+    qkv_bias: bool = False
 
     @property
     def q_dim(self) -> int:
@@ -43,12 +45,20 @@ class ModelConfig:
 
     def param_count(self) -> int:
         attn = self.hidden_size * (self.q_dim + 2 * self.kv_dim) + self.q_dim * self.hidden_size
+        if self.qkv_bias:
+            attn += self.q_dim + 2 * self.kv_dim
         if self.num_experts:
             ffn = self.num_experts * 3 * self.hidden_size * self.moe_ffn_size + self.hidden_size * self.num_experts
         else:
             ffn = 3 * self.hidden_size * self.ffn_size
         per_layer = attn + ffn + 2 * self.hidden_size
         return self.num_layers * per_layer + 2 * self.vocab_size * self.hidden_size + self.hidden_size
+
+
+def require_no_qkv_bias(cfg: ModelConfig, what: str) -> None:
+    if cfg.qkv_bias:
+        raise ValueError(f"{what} does not support biased q/k/v projections (Qwen2-style models run on LlamaModel with the "
+                         f"one-GPU, data-parallel, context-parallel and pipeline trainers)")
 
 
 def require_untied(cfg: ModelConfig, what: str) -> None:
@@ -72,6 +82,11 @@ def llama31_8b() -> ModelConfig:
 def llama3_70b() -> ModelConfig:
     """Llama-3-70B: 80 layers, hidden 8192, 64 q / 8 kv heads of 128, FFN 28672, vocab 128256."""
     return ModelConfig("llama3-70b", 128256, 8192, 80, 64, 8, 128, 28672, rms_eps=1e-5, rope_theta=500000.0)
+
+
+def qwen25_7b() -> ModelConfig:
+    """Qwen2.5-7B: 28 layers, hidden 3584, 28 q / 4 kv heads of 128 with biased q/k/v projections, FFN 18944."""
+    return ModelConfig("qwen2.5-7b", 152064, 3584, 28, 28, 4, 128, 18944, rms_eps=1e-6, rope_theta=1000000.0, qkv_bias=True)
 
 
 def qwen3_8b() -> ModelConfig:

@@ -39,14 +39,17 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
                         float(scaling.get("high_freq_factor", 4.0)), int(scaling["original_max_position_embeddings"]))
     elif kind != "default":
         raise ValueError(f"rope scaling {scaling} is not supported (known: default, linear, llama3)")
+    model_type = str(get("model_type", "") or "")
+    qkv_bias = model_type == "qwen2"          # Qwen2 / Qwen2.5: biased q, k, v; no bias on the output projection
     if get("attention_bias", False) or get("mlp_bias", False):
-        raise ValueError("projections with a bias are not supported")
+        raise ValueError("biases on the output projection or the FFN are not supported (Qwen2-style q/k/v biases are)")
+    if get("use_sliding_window", False):
+        raise ValueError("sliding-window attention is not supported")
     experts = int(get("num_experts", 0) or get("num_local_experts", 0) or 0)
     if experts and not get("norm_topk_prob", True):
         raise ValueError("routers that do not renormalise the top-k weights are not supported")
     if experts and (int(get("decoder_sparse_step", 1) or 1) != 1 or get("mlp_only_layers")):
         raise ValueError("models that mix dense and mixture-of-experts layers are not supported")
-    model_type = str(get("model_type", "") or "")
     rope_theta = get("rope_theta")
     if rope_theta is None and isinstance(get("rope_parameters"), Mapping):
         rope_theta = get("rope_parameters").get("rope_theta")
@@ -57,7 +60,7 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
         num_experts=experts, experts_per_token=int(get("num_experts_per_tok", 0) or 0) if experts else 0,
         moe_ffn_size=int(get("moe_intermediate_size", 0) or 0) if experts else 0,
         qk_norm=model_type.startswith("qwen3"), rope_scaling=rope_scaling,
-        tie_word_embeddings=bool(get("tie_word_embeddings", False)),
+        tie_word_embeddings=bool(get("tie_word_embeddings", False)), qkv_bias=qkv_bias,
     )
 
 
@@ -74,6 +77,9 @@ def hf_parameter_map(model) -> Iterator[Tuple[str, List[Tuple[str, int, int]]]]:
         yield f"l{i}.attn_norm", [(p + "input_layernorm.weight", 0, h)]
         yield f"l{i}.wqkv", [(p + "self_attn.q_proj.weight", 0, q), (p + "self_attn.k_proj.weight", q, q + kv),
                              (p + "self_attn.v_proj.weight", q + kv, q + 2 * kv)]
+        if cfg.qkv_bias:
+            yield f"l{i}.bqkv", [(p + "self_attn.q_proj.bias", 0, q), (p + "self_attn.k_proj.bias", q, q + kv),
+                                 (p + "self_attn.v_proj.bias", q + kv, q + 2 * kv)]
         yield f"l{i}.wo", [(p + "self_attn.o_proj.weight", 0, h)]
         if cfg.qk_norm:
             yield f"l{i}.q_norm", [(p + "self_attn.q_norm.weight", 0, cfg.head_dim)]
@@ -172,18 +178,26 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
     moe, qwen = bool(cfg.num_experts), bool(cfg.qk_norm)
     if moe and not qwen:
         raise ValueError("mixture-of-experts checkpoints are written as Qwen3-MoE, which has per-head q/k norms")
+    if cfg.qkv_bias and (moe or qwen or cfg.head_dim * cfg.num_heads != cfg.hidden_size):
+        raise ValueError("biased q/k/v projections are written as Qwen2, which has neither experts nor q/k norms and "
+                         "takes head_dim = hidden_size / heads")
     arch, kind = (("Qwen3MoeForCausalLM", "qwen3_moe") if moe else ("Qwen3ForCausalLM", "qwen3") if qwen
-                  else ("LlamaForCausalLM", "llama"))
+                  else ("Qwen2ForCausalLM", "qwen2") if cfg.qkv_bias else ("LlamaForCausalLM", "llama"))
     out: Dict[str, Any] = {
         "architectures": [arch], "model_type": kind, "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
         "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_heads, "num_key_value_heads": cfg.num_kv_heads,
         "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn_size, "rms_norm_eps": cfg.rms_eps, "rope_theta": cfg.rope_theta,
-        "hidden_act": "silu", "attention_bias": False, "max_position_embeddings": int(max_position_embeddings),
+        "hidden_act": "silu", "max_position_embeddings": int(max_position_embeddings),
         "tie_word_embeddings": bool(tie_word_embeddings), "torch_dtype": str(dtype).replace("torch.", ""),
         "dtype": str(dtype).replace("torch.", ""),
     }
     if kind == "llama":
         out["mlp_bias"] = False
+    if kind != "qwen2":
+        out["attention_bias"] = False
+    else:
+        out.pop("head_dim")
+        out["use_sliding_window"] = False
     if cfg.rope_scaling is not None:
         how, factor, low, high, original = cfg.rope_scaling
         block = {"rope_type": how, "factor": factor}

@@ -326,7 +326,10 @@ class LlamaModel(nn.Module):
                 raise ValueError(f"expert_shard={expert_shard} does not divide the {e} experts of this model")
             e_local = e // shard_world
         for i in range(cfg.num_layers):
-            shapes += [(f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h)), (f"l{i}.wo", (h, cfg.q_dim))]
+            shapes += [(f"l{i}.attn_norm", (h,)), (f"l{i}.wqkv", (qkv_rows, h))]
+            if cfg.qkv_bias:
+                shapes += [(f"l{i}.bqkv", (qkv_rows,))]
+            shapes += [(f"l{i}.wo", (h, cfg.q_dim))]
             if cfg.qk_norm:
                 shapes += [(f"l{i}.q_norm", (cfg.head_dim,)), (f"l{i}.k_norm", (cfg.head_dim,))]
             shapes += [(f"l{i}.mlp_norm", (h,))]
@@ -405,6 +408,8 @@ class LlamaModel(nn.Module):
             if name.endswith("norm"):
                 dst.fill_(1.0)
                 continue
+            if name.endswith("bqkv"):
+                continue                      # biases start at zero
             # chunked init (on the parameter's own device) keeps the fp32 temporary small
             flat_dst = dst.view(-1)
             step = 1 << 26
@@ -483,6 +488,8 @@ class LlamaModel(nn.Module):
             qkv = norm_linear(x, p("attn_norm"), p("wqkv"), cfg.rms_eps)
         else:
             qkv = linear(rms_norm(x, p("attn_norm"), cfg.rms_eps), p("wqkv"))
+        if cfg.qkv_bias:
+            qkv = qkv + p("bqkv")
         attn = self._attention(qkv, positions, layout, index, k_prefix, v_prefix, return_kv)
         if return_kv:
             attn, k_rot, v_rot = attn
@@ -655,7 +662,10 @@ class LlamaModel(nn.Module):
         x = kernel_registry.get_op("embedding")(token_ids, self.view("embed"))
         for i in range(cfg.num_layers):
             p = lambda name: self.view(f"l{i}.{name}")
-            qkv = self._project(rms_norm(x, p("attn_norm"), cfg.rms_eps), f"l{i}.wqkv").view(n, hq + 2 * hkv, cfg.head_dim)
+            qkv = self._project(rms_norm(x, p("attn_norm"), cfg.rms_eps), f"l{i}.wqkv")
+            if cfg.qkv_bias:
+                qkv = qkv + p("bqkv")
+            qkv = qkv.view(n, hq + 2 * hkv, cfg.head_dim)
             q, k, v = qkv[:, :hq], qkv[:, hq : hq + hkv], qkv[:, hq + hkv :]
             ext.rope(q, positions, self.rope_cos, self.rope_sin, False, q)
             ext.rope(k, positions, self.rope_cos, self.rope_sin, False, k)

@@ -23,7 +23,7 @@ import torch
 from torch.utils.checkpoint import checkpoint
 
 from rl_engine.models.activation_plan import ActivationPlanner
-from rl_engine.models.config import require_untied
+from rl_engine.models.config import require_no_qkv_bias, require_untied
 from rl_engine.models.grpo import GRPOBatch, GRPOTrainer, group_geometry
 from rl_engine.models.llama import LlamaModel, rms_norm
 from rl_engine.parallel.tp_linear import TensorParallelLinears
@@ -51,6 +51,7 @@ class TensorParallelLlama:
                  activation_checkpointing: Union[bool, str] = "auto") -> None:
         cfg = full.cfg
         require_untied(cfg, type(self).__name__)
+        require_no_qkv_bias(cfg, type(self).__name__)
         self.cfg, self.tp = cfg, tp
         self.rank, self.world = tp.rank, tp.world
         self._planner = ActivationPlanner(cfg.num_layers, activation_checkpointing)

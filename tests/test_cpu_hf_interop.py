@@ -339,3 +339,50 @@ def test_tied_embeddings_stay_tied_through_training_and_round_trip(tmp_path):
     _compare_logits(again, model, 53)
     with pytest.raises(ValueError, match="tied embeddings"):
         require_untied(model.cfg, "ShardedFusedAdamW")
+
+
+def test_qwen2_checkpoint_with_biased_qkv_projections(tmp_path):
+    """Qwen2 / Qwen2.5: q, k and v carry a bias.  Logits match ``transformers``, the bias trains (gradient = column sum
+    of the qkv gradient), the views and a saved directory carry the three HF bias tensors."""
+    if not hasattr(transformers, "Qwen2ForCausalLM"):
+        pytest.skip("this transformers has no Qwen2")
+    from rl_engine.models.hf_interop import hf_state_dict_views, model_from_hf, model_from_hf_checkpoint, save_hf_checkpoint
+    from rl_engine.models import qwen25_7b
+    from rl_engine.models.config import require_no_qkv_bias
+
+    config = transformers.Qwen2Config(vocab_size=67, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                      rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=False, use_sliding_window=False)
+    torch.manual_seed(12)
+    hf = transformers.Qwen2ForCausalLM(config).float().eval()
+    with torch.no_grad():
+        for layer in hf.model.layers:
+            for proj in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj):
+                proj.bias.uniform_(-0.5, 0.5)
+    model = model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert model.cfg.qkv_bias and not model.cfg.qk_norm and model.view("l1.bqkv").shape == (64 + 2 * 32,)
+    _compare_logits(hf, model, 67)
+    views = hf_state_dict_views(model)
+    assert torch.equal(views["model.layers.1.self_attn.k_proj.bias"], hf.model.layers[1].self_attn.k_proj.bias)
+    assert set(views) == set(hf.state_dict())
+    # gradients reach the bias
+    from rl_engine.models.causal_lm import PackedCausalLM
+
+    ids = torch.randint(0, 67, (2, 7), generator=torch.Generator().manual_seed(13))
+    model.ensure_flat_grad().zero_()
+    PackedCausalLM(model)(ids).logits.float().square().mean().backward()
+    hf.zero_grad()
+    hf(input_ids=ids, use_cache=False).logits.float().square().mean().backward()
+    want = torch.cat([hf.model.layers[0].self_attn.q_proj.bias.grad, hf.model.layers[0].self_attn.k_proj.bias.grad,
+                      hf.model.layers[0].self_attn.v_proj.bias.grad])
+    assert torch.allclose(model.view("l0.bqkv").grad, want, atol=1e-6) and float(want.abs().max()) > 0
+    # directory round trip, written as Qwen2
+    save_hf_checkpoint(model, tmp_path)
+    again = transformers.AutoModelForCausalLM.from_pretrained(tmp_path, dtype=torch.float32).eval()
+    assert type(again).__name__ == "Qwen2ForCausalLM"
+    _compare_logits(again, model, 67)
+    back = model_from_hf_checkpoint(tmp_path, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert torch.equal(back.flat, model.flat)
+    assert 7.5 < qwen25_7b().param_count() / 1e9 < 7.8
+    with pytest.raises(ValueError, match="biased q/k/v"):
+        require_no_qkv_bias(model.cfg, "TensorParallelLlama")
