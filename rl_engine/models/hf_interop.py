@@ -43,8 +43,9 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
     qkv_bias = model_type == "qwen2"          # Qwen2 / Qwen2.5: biased q, k, v; no bias on the output projection
     if get("attention_bias", False) or get("mlp_bias", False):
         raise ValueError("biases on the output projection or the FFN are not supported (Qwen2-style q/k/v biases are)")
-    if get("use_sliding_window", False):
-        raise ValueError("sliding-window attention is not supported")
+    window = get("sliding_window")
+    if get("use_sliding_window", model_type == "mistral") and window and int(window) < int(get("max_position_embeddings", 0) or 0):
+        raise ValueError(f"sliding-window attention (window {window}) is not supported")
     experts = int(get("num_experts", 0) or get("num_local_experts", 0) or 0)
     if experts and not get("norm_topk_prob", True):
         raise ValueError("routers that do not renormalise the top-k weights are not supported")

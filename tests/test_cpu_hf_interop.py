@@ -386,3 +386,22 @@ def test_qwen2_checkpoint_with_biased_qkv_projections(tmp_path):
     assert 7.5 < qwen25_7b().param_count() / 1e9 < 7.8
     with pytest.raises(ValueError, match="biased q/k/v"):
         require_no_qkv_bias(model.cfg, "TensorParallelLlama")
+
+
+def test_mistral_checkpoint_is_the_llama_architecture():
+    if not hasattr(transformers, "MistralForCausalLM"):
+        pytest.skip("this transformers has no Mistral")
+    from rl_engine.models.hf_interop import config_from_hf
+
+    config = transformers.MistralConfig(vocab_size=61, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                        num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                        rms_norm_eps=1e-5, rope_theta=10000.0, sliding_window=None, tie_word_embeddings=False)
+    torch.manual_seed(14)
+    hf = transformers.MistralForCausalLM(config).float().eval()
+    cfg, model, unused = _native_from(hf)
+    assert not cfg.qkv_bias and not cfg.qk_norm and unused == []
+    _compare_logits(hf, model, 61)
+    windowed = transformers.MistralConfig(vocab_size=61, hidden_size=64, intermediate_size=96, num_hidden_layers=1,
+                                          num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64, sliding_window=16)
+    with pytest.raises(ValueError, match="sliding-window"):
+        config_from_hf(windowed)
