@@ -59,6 +59,10 @@ class SamplerBackend(nn.Module):
 
     @staticmethod
     def _sample_torch(logits, top_k, top_p, temperature):
+        if top_k is not None and int(top_k) <= 0:       # 0 is the usual spelling of "no top-k", as in the fused kernel
+            top_k = None
+        if top_p is not None and float(top_p) >= 1.0:
+            top_p = None
         z = logits.float()
         if temperature != 1.0:
             z = z / temperature

@@ -173,6 +173,9 @@ def test_sampler_backend_cpu_paths_and_temperature_once():
     assert abs(freq - 0.75) < 0.02
     with pytest.raises(ValueError):
         s.sample(logits, temperature=0.0)
+    # top_k = 0 and top_p = 1 are the usual spellings of "off" (the fused kernel reads them that way too)
+    off = s.sample(two, top_k=0, top_p=1.0)
+    assert abs((off == 1).float().mean().item() - 0.9) < 0.02
     lp = s.compute_logp(torch.randn(3, 4, 9), torch.randint(0, 9, (3, 4)))
     assert lp.shape == (3, 4)
 

@@ -195,3 +195,18 @@ def test_stateless_executor_scores_a_real_hf_sequence_classifier():
     result = StatelessForwardExecutor(model, StatelessForwardConfig(mode="reward")).score(_inputs())
     assert result.rewards.shape == (2,) and result.rewards.requires_grad is False
     assert result.metrics["zero_kv_cache"] is True
+
+
+def test_rl_loop_example_learns_and_serves_the_trained_weights():
+    """``examples/rl_loop.py`` on CPU: rollout -> stateless reference scoring -> GRPO worker -> publish -> update, 18
+    times; the toy reward must climb and the rollout side must end on the last published version."""
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples", "rl_loop.py")
+    spec = importlib.util.spec_from_file_location("rl_loop_example", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    summary = module.main(["--iterations", "18"])
+    assert summary["final_weight_version"] == 18 and summary["training_backend"] == "GRPOTrainer"
+    assert summary["mean_reward_last3"] > summary["mean_reward_first3"] + 0.15
