@@ -106,6 +106,7 @@ def main(argv=None) -> dict:
     summary = {"mean_reward_first3": round(first, 4), "mean_reward_last3": round(last, 4),
                "final_weight_version": rollout.active_weight_version, "training_backend": result.metrics["training_backend"]}
     print(json.dumps(summary), flush=True)
+    rollout.release_weights()                                  # give the last update's segments back to the transport
     return summary
 
 
