@@ -44,6 +44,13 @@ class GRPOBatch:
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors())
 
+    def with_safe_ids(self) -> "GRPOBatch":
+        """Completion ids at masked positions replaced by 0.  Completion tokens are model inputs as well as targets, and
+        padding conventions put -100 or other out-of-vocabulary values there; their loss terms are masked anyway."""
+        keep = self.completion_mask.to(torch.bool)
+        ids = torch.where(keep, self.completion_ids, torch.zeros_like(self.completion_ids))
+        return GRPOBatch(self.prompt_ids, ids, self.rewards, self.old_logps, self.ref_logps, self.completion_mask)
+
     def completions(self, begin: int, end: int) -> "GRPOBatch":
         """The same prompt with completions ``[begin, end)`` (``rewards`` stay those of the whole group)."""
         return GRPOBatch(self.prompt_ids, self.completion_ids[begin:end].contiguous(), self.rewards,
@@ -441,6 +448,7 @@ class GRPOTrainer:
         if self.liveness is not None:
             self.liveness.check(self._steps_started)
         self._steps_started += 1
+        batch = batch.with_safe_ids()
         while True:
             self.opt.zero_grad()
             try:
@@ -460,7 +468,7 @@ class GRPOTrainer:
     def step_groups(self, batches) -> torch.Tensor:
         """One optimiser step on several prompt groups (a sequence of device ``GRPOBatch``): the gradient is the mean
         over the groups of each group's token-mean loss.  Returns that mean loss.  No out-of-memory retry here."""
-        batches = list(batches)
+        batches = [b.with_safe_ids() for b in batches]
         if not batches:
             raise ValueError("step_groups needs at least one prompt group")
         self.opt.zero_grad()

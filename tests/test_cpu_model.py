@@ -344,3 +344,36 @@ def test_micro_batched_step_matches_the_single_pass_step():
     assert choose_micro_group(256, 1024, 512, 32, kept) == 32
     assert choose_micro_group(32, 1024, 512, 32, kept) == 32
     assert choose_micro_group(6, 16, 12, 2, lambda tokens: 0) == 6  # short packed lengths are never split
+
+
+def test_trainer_ignores_garbage_ids_at_masked_positions_and_rejects_them_at_active_ones():
+    """Padding conventions put -100 or out-of-vocabulary ids at masked completion positions.  Completion tokens are model
+    inputs too, so the trainer replaces them before use: loss and parameters are bit-identical to a clean batch.  The
+    same values at ACTIVE positions are an error."""
+    from rl_engine.models.config import ModelConfig
+    from rl_engine.models.grpo import GRPOBatch, GRPOTrainer
+    from rl_engine.models.llama import LlamaModel
+
+    cfg = ModelConfig("t", 64, 32, 2, 2, 1, 16, 48)
+
+    def run(garbage, at_active=False):
+        model = LlamaModel(cfg, dtype=torch.float32, device="cpu", seed=1, max_positions=64)
+        trainer = GRPOTrainer(model, lr=1e-2, micro_group=2)
+        gen = torch.Generator().manual_seed(0)
+        comp = torch.randint(0, 64, (4, 6), generator=gen)
+        mask = torch.ones(4, 6, dtype=torch.bool)
+        mask[1, 3:] = False
+        mask[3, 1:] = False
+        if garbage is not None:
+            comp = torch.where(mask ^ at_active, comp, torch.full_like(comp, garbage))
+        batch = GRPOBatch(prompt_ids=torch.randint(0, 64, (5,), generator=gen), completion_ids=comp, completion_mask=mask,
+                          rewards=torch.tensor([1.0, 0.0, 0.5, -1.0]), old_logps=torch.full((4, 6), -4.0),
+                          ref_logps=torch.full((4, 6), -4.0))
+        return float(trainer.step_device(batch)), model.flat.clone()
+
+    clean = run(None)
+    for garbage in (-100, 9999):
+        loss, flat = run(garbage)
+        assert loss == clean[0] and torch.equal(flat, clean[1])
+    with pytest.raises((IndexError, ValueError, RuntimeError)):
+        run(9999, at_active=True)
