@@ -3,8 +3,8 @@
 Scoring executors, model wrappers and third-party loops call a policy the Hugging Face way:
 ``model(input_ids=[B, S], attention_mask=[B, S], use_cache=False, output_hidden_states=...)`` and read ``.logits`` or
 ``.last_hidden_state``.  ``LlamaModel`` works on ONE packed token axis with a layout that says who attends to whom.
-``PackedCausalLM`` bridges the two: every row becomes one causal sequence of the packed axis (right padding is dropped
-from the pack and comes back as zeros), the model runs once over all rows, and the outputs are scattered back to
+``PackedCausalLM`` bridges the two: every row becomes one causal sequence of the packed axis (padding on either side is
+dropped from the pack and comes back as zeros), the model runs once over all rows, and the outputs are scattered back to
 ``[B, S, ...]``.  Nothing is cached between calls (``use_cache=True`` is refused), which is what the stateless
 scoring executor wants (reference: ``rl_engine/executors/stateless_executor.py:93-209`` drives HF models this way).
 """
@@ -65,14 +65,17 @@ class PackedCausalLM(nn.Module):
         dev = self.model.flat.device
         ids = input_ids.to(dev).long()
         if attention_mask is None:
-            lengths = [s] * b
+            lengths, firsts = [s] * b, [0] * b
         else:
             mask = attention_mask.to(dev).bool()
             lengths = [int(n) for n in mask.long().sum(1).tolist()]
-            # only right padding can be dropped from a causal pack
-            expect = torch.arange(s, device=dev)[None, :] < torch.tensor(lengths, device=dev)[:, None]
-            if not torch.equal(mask, expect):
-                raise ValueError("attention_mask must be right-padded (ones followed by zeros in every row)")
+            # a row's tokens must be one contiguous run (right padding, left padding as batched generation produces
+            # it, or both); positions count from the first real token, as Hugging Face models do for padded rows
+            firsts = [int(f) for f in mask.long().argmax(1).tolist()]
+            column = torch.arange(s, device=dev)[None, :]
+            first_t, len_t = torch.tensor(firsts, device=dev)[:, None], torch.tensor(lengths, device=dev)[:, None]
+            if not torch.equal(mask, (column >= first_t) & (column < first_t + len_t)):
+                raise ValueError("attention_mask must select one contiguous run of tokens in every row")
         seqs, starts, cursor = [], [], 0
         for n in lengths:
             starts.append(cursor)
@@ -82,19 +85,19 @@ class PackedCausalLM(nn.Module):
         if cursor == 0:
             raise ValueError("attention_mask selects no token")
         layout = make_layout(seqs, True, dev)
-        packed = torch.cat([ids[r, :n] for r, n in enumerate(lengths) if n])
+        packed = torch.cat([ids[r, firsts[r] : firsts[r] + n] for r, n in enumerate(lengths) if n])
         positions = torch.cat([torch.arange(n, device=dev) for n in lengths if n])
         hidden = self.model.hidden_states(packed, positions, layout)            # [T, H], after the final norm
         out_hidden = hidden.new_zeros(b, s, hidden.shape[-1])
         for r, n in enumerate(lengths):
             if n:
-                out_hidden[r, :n] = hidden[starts[r] : starts[r] + n]
+                out_hidden[r, firsts[r] : firsts[r] + n] = hidden[starts[r] : starts[r] + n]
         logits = None
         if self.return_logits:
             flat_logits = linear(hidden, self.model.lm_head_weight())
             logits = flat_logits.new_zeros(b, s, flat_logits.shape[-1])
             for r, n in enumerate(lengths):
                 if n:
-                    logits[r, :n] = flat_logits[starts[r] : starts[r] + n]
+                    logits[r, firsts[r] : firsts[r] + n] = flat_logits[starts[r] : starts[r] + n]
         return CausalLMOutput(logits=logits, last_hidden_state=out_hidden,
                               hidden_states=(out_hidden,) if output_hidden_states else None)

@@ -405,3 +405,30 @@ def test_mistral_checkpoint_is_the_llama_architecture():
                                           num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64, sliding_window=16)
     with pytest.raises(ValueError, match="sliding-window"):
         config_from_hf(windowed)
+
+
+def test_padded_batches_match_transformers_for_right_and_left_padding():
+    """``PackedCausalLM`` drops padding from the pack: logits at the real tokens of right- and left-padded rows equal
+    what ``transformers`` computes with the same attention mask; padded slots come back as zeros; a mask with a hole is
+    refused."""
+    from rl_engine.models.causal_lm import PackedCausalLM
+    from rl_engine.models.hf_interop import model_from_hf
+
+    config = transformers.LlamaConfig(vocab_size=47, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                      num_attention_heads=2, num_key_value_heads=1, max_position_embeddings=32,
+                                      tie_word_embeddings=False)
+    torch.manual_seed(15)
+    hf = transformers.LlamaForCausalLM(config).float().eval()
+    lm = PackedCausalLM(model_from_hf(hf, dtype=torch.float32, device="cpu", activation_checkpointing=False))
+    ids = torch.randint(0, 47, (3, 8), generator=torch.Generator().manual_seed(16))
+    right = torch.tensor([[1] * 8, [1] * 5 + [0] * 3, [1] * 2 + [0] * 6])
+    left = torch.tensor([[1] * 8, [0] * 3 + [1] * 5, [0] * 6 + [1] * 2])
+    for mask in (right, left):
+        with torch.no_grad():
+            want = hf(input_ids=ids, attention_mask=mask, use_cache=False).logits.float()
+            got = lm(ids, attention_mask=mask).logits.float()
+        keep = mask.bool()
+        assert torch.allclose(got[keep], want[keep], atol=2e-4, rtol=1e-3), float((got[keep] - want[keep]).abs().max())
+        assert float(got[~keep].abs().max()) == 0.0
+    with pytest.raises(ValueError, match="contiguous run"):
+        lm(ids, attention_mask=torch.tensor([[1, 1, 0, 1, 1, 1, 1, 1]] * 3))
