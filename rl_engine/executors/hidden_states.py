@@ -91,3 +91,38 @@ def extract_hidden_states(model_output: Any, *, hidden_dim: Optional[int] = None
         return found
     want = "" if hidden_dim is None else f" with last dimension {hidden_dim}"
     raise TypeError(f"model output of type {type(model_output).__name__} exposes no hidden-state tensor{want}")
+
+
+def output_head(model: Any) -> Any:
+    """The module that maps hidden states to vocabulary logits: ``model.lm_head``, else what a Hugging Face model
+    returns from ``get_output_embeddings()``.  It must have a 2-D ``weight``."""
+    head = getattr(model, "lm_head", None)
+    if head is None and callable(getattr(model, "get_output_embeddings", None)):
+        head = model.get_output_embeddings()
+    if head is None or getattr(head, "weight", None) is None or head.weight.ndim != 2:
+        raise TypeError(f"{type(model).__name__} exposes no output projection (lm_head / get_output_embeddings())")
+    return head
+
+
+def backbone_hidden_states(model: Any, token_ids: torch.Tensor, *, hidden_dim: Optional[int] = None) -> torch.Tensor:
+    """Final hidden states of ``model`` for ``token_ids`` ``[B, S]`` without running its vocabulary projection where
+    that can be avoided.
+
+    * A Hugging Face ``...ForCausalLM`` keeps its decoder under ``base_model`` (``model.model``, ``model.transformer``):
+      that decoder is called directly (``use_cache=False``), so no ``[B, S, V]`` logits are ever built.
+    * Anything else is called as ``model(token_ids)`` and its output searched (``extract_hidden_states``); a model
+      that returns logits only is asked again with ``output_hidden_states=True``."""
+    base = getattr(model, "base_model", None)
+    if isinstance(base, torch.nn.Module) and base is not model and getattr(model, "lm_head", None) is not None:
+        try:
+            out = base(input_ids=token_ids, use_cache=False)
+        except TypeError:                      # an encoder-style backbone has no cache switch
+            out = base(input_ids=token_ids)
+        return extract_hidden_states(out, hidden_dim=hidden_dim)
+    out = model(token_ids)
+    try:
+        return extract_hidden_states(out, hidden_dim=hidden_dim)
+    except TypeError:
+        if not hasattr(getattr(model, "config", None), "output_hidden_states"):
+            raise
+    return extract_hidden_states(model(token_ids, output_hidden_states=True), hidden_dim=hidden_dim)

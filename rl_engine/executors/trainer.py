@@ -28,7 +28,7 @@ from rl_engine.executors.bridge import WeightBridge, WeightManifestValidationErr
 from rl_engine.executors.training_contract import (
     RolloutBatchMixin, RolloutStageResult, TorchRLTrainingConfig, TrainingStageResult, objective_reference_logps,
 )
-from rl_engine.executors.hidden_states import extract_hidden_states
+from rl_engine.executors.hidden_states import backbone_hidden_states, extract_hidden_states, output_head  # noqa: F401
 from rl_engine.testing import compute_policy_ratio, compute_reference_kl, masked_mean
 
 
@@ -110,9 +110,10 @@ class NativeTrainingWorker(RolloutBatchMixin):
 
     # -- one optimisation step ---------------------------------------------------------------------
     def _current_logps(self, batch) -> torch.Tensor:
-        head = self.model.lm_head
-        # whatever the backbone returns (tensor, ModelOutput, dict, tuple): take its final hidden states
-        hidden = extract_hidden_states(self.model(batch.token_ids.long()), hidden_dim=head.weight.shape[1])
+        head = output_head(self.model)
+        # whatever the backbone returns (tensor, ModelOutput, dict, tuple): take its final hidden states; a Hugging
+        # Face causal LM is entered below its vocabulary projection
+        hidden = backbone_hidden_states(self.model, batch.token_ids.long(), hidden_dim=head.weight.shape[1])
         targets = safe_token_ids(batch.token_ids.to(hidden.device), batch.completion_mask)
         logps = self._linear_logp(hidden, head.weight, targets, getattr(head, "bias", None))
         keep = batch.completion_mask.to(device=logps.device, dtype=torch.bool)
@@ -122,7 +123,7 @@ class NativeTrainingWorker(RolloutBatchMixin):
         t0 = time.perf_counter()
         cfg = self.config
         batch, payload_metrics = self._batch_from_rollout_or_synthetic(rollout)
-        validate_model_input_token_ids(batch.token_ids, vocab_size=self.model.lm_head.weight.shape[0])
+        validate_model_input_token_ids(batch.token_ids, vocab_size=output_head(self.model).weight.shape[0])
         self.optimizer.zero_grad(set_to_none=True)
         loss = clipped_ratio_objective(self._current_logps(batch), batch, cfg)
         loss.backward()

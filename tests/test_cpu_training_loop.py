@@ -261,3 +261,49 @@ def test_worker_publishes_hugging_face_names_and_the_native_rollout_side_install
     assert torch.equal(rollout_copy.flat, policy.flat) and executor.active_weight_version == 0
     with pytest.raises(ValueError):
         policy.state_dict_views(names="onnx")
+
+
+def test_native_worker_trains_hugging_face_causal_lms_below_their_vocabulary_projection():
+    """``NativeTrainingWorker(model=<HF ...ForCausalLM>)``: the decoder (``base_model``) is called directly, so the
+    LM head's ``forward`` never runs and no ``[B, S, V]`` logits exist; the step changes the head through ``linear_logp``
+    and the published names are the checkpoint's."""
+    transformers = pytest.importorskip("transformers")
+    from rl_engine.executors.hidden_states import backbone_hidden_states, output_head
+
+    cfg = NativeTrainingConfig(lr=1e-2, device="cpu", dtype=torch.float32, vocab_size=64, num_prompts=2, samples_per_prompt=3,
+                               prompt_len=4, completion_len=5)
+    llama = transformers.LlamaForCausalLM(transformers.LlamaConfig(
+        vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+        max_position_embeddings=64, tie_word_embeddings=False)).float()
+    gpt2 = transformers.GPT2LMHeadModel(transformers.GPT2Config(vocab_size=64, n_embd=32, n_layer=2, n_head=2, n_positions=64))
+    for model in (llama, gpt2):
+        head_calls = []
+        model.lm_head.register_forward_hook(lambda *_: head_calls.append(1))
+        worker = NativeTrainingWorker(cfg, model=model)
+        before = model.lm_head.weight.detach().clone()
+        result = worker.train(make_rollout_result(iteration=0, weight_version=0, payload=None))
+        assert result.metrics["current_logp_path"] == "linear_logp" and torch.isfinite(torch.tensor(result.metrics["loss"]))
+        assert not torch.equal(before, model.lm_head.weight) and head_calls == []
+        assert set(worker.publish_weights(1).tensors) == set(model.state_dict())
+    # a model that returns logits only is asked for its hidden states; one that cannot give any is an error
+    class LogitsOnly(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.config = types.SimpleNamespace(output_hidden_states=False)
+            self.embed, self.lm_head = torch.nn.Embedding(64, 16), torch.nn.Linear(16, 64, bias=False)
+
+        def forward(self, ids, output_hidden_states=False):
+            h = self.embed(ids)
+            out = {"logits": self.lm_head(h)}
+            if output_hidden_states:
+                out["hidden_states"] = (h, h * 2.0)
+            return out
+
+    m = LogitsOnly()
+    ids = torch.randint(0, 64, (2, 3))
+    assert torch.equal(backbone_hidden_states(m, ids, hidden_dim=16), m.embed(ids) * 2.0)
+    assert output_head(m) is m.lm_head
+    with pytest.raises(TypeError):
+        backbone_hidden_states(torch.nn.Embedding(64, 8), ids, hidden_dim=16)
+    with pytest.raises(TypeError):
+        output_head(torch.nn.Embedding(64, 8))
