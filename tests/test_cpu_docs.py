@@ -53,3 +53,37 @@ def test_relative_links_resolve():
             if not os.path.exists(path):
                 broken.append(f"{page} -> {target}")
     assert not broken, f"broken relative links: {broken}"
+
+
+def test_import_lines_in_code_blocks_resolve():
+    """Every ``from rl_engine... import name`` / ``import rl_engine...`` line inside a ``python`` block of the pages and
+    of the README names a module and attributes that exist, so a snippet cannot outlive the API it shows."""
+    import ast
+    import importlib
+
+    pages = [os.path.join(DOCS, page) for page in _pages()] + [os.path.join(ROOT, "README.md")]
+    problems, checked = [], 0
+    for path in pages:
+        with open(path) as f:
+            blocks = re.findall(r"```python\n(.*?)```", f.read(), re.S)
+        for block in blocks:
+            for line in block.splitlines():
+                line = line.split("#")[0].strip()
+                if not line.startswith(("from rl_engine", "import rl_engine")) or line.endswith("("):
+                    continue
+                node = ast.parse(line).body[0]
+                checked += 1
+                if isinstance(node, ast.Import):
+                    for alias in node.names:
+                        importlib.import_module(alias.name)
+                    continue
+                module = importlib.import_module(node.module)
+                for alias in node.names:
+                    if hasattr(module, alias.name):
+                        continue
+                    try:
+                        importlib.import_module(f"{node.module}.{alias.name}")
+                    except ImportError:
+                        problems.append(f"{os.path.relpath(path, ROOT)}: {node.module} has no {alias.name}")
+    assert not problems, problems
+    assert checked >= 10
