@@ -7,6 +7,8 @@ the same ``forward`` / ``forward_fp32`` contract as the other elementwise oracle
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 
@@ -24,7 +26,7 @@ def scaled_inv_freq(inv_freq: torch.Tensor, scaling) -> torch.Tensor:
     if kind == "linear":
         return inv_freq / float(factor)
     if kind != "llama3":
-        raise ValueError(f"rope scaling {kind!r} is not supported (known: 'linear', 'llama3')")
+        raise ValueError(f"rope scaling {kind!r} is not supported (known: 'linear', 'llama3', 'yarn')")
     wavelen = 2.0 * torch.pi / inv_freq
     scaled = torch.where(wavelen > original / low, inv_freq / factor, inv_freq)
     smooth = (original / wavelen - low) / (high - low)
@@ -33,11 +35,41 @@ def scaled_inv_freq(inv_freq: torch.Tensor, scaling) -> torch.Tensor:
     return torch.where(medium, blended, scaled)
 
 
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float = 10000.0, scaling=None):
+def yarn_inv_freq(head_dim: int, theta: float, factor: float, beta_fast: float, beta_slow: float, original: int, device=None):
+    """YaRN ("NTK by parts"): dimensions that turn more than ``beta_fast`` times over the original context keep their
+    frequency, those that turn fewer than ``beta_slow`` times are interpolated by ``factor``, a linear ramp in the
+    dimension index joins the two; cos and sin are scaled by ``0.1 ln(factor) + 1``.  Returns ``(inv_freq, scale)``."""
     half = head_dim // 2
-    inv_freq = theta ** (-torch.arange(half, dtype=torch.float32, device=positions.device) / half)
-    inv_freq = scaled_inv_freq(inv_freq, scaling)
+
+    def correction_dim(rotations: float) -> float:
+        return head_dim * math.log(original / (rotations * 2.0 * math.pi)) / (2.0 * math.log(theta))
+
+    low = max(math.floor(correction_dim(beta_fast)), 0)
+    high = min(math.ceil(correction_dim(beta_slow)), head_dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = ((torch.arange(half, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0.0, 1.0)
+    pos_freqs = theta ** (torch.arange(half, dtype=torch.float32, device=device) / half)
+    keep = 1.0 - ramp
+    inv_freq = (1.0 / (factor * pos_freqs)) * (1.0 - keep) + (1.0 / pos_freqs) * keep
+    return inv_freq, (1.0 if factor <= 1 else 0.1 * math.log(factor) + 1.0)
+
+
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float = 10000.0, scaling=None):
+    """cos / sin tables ``[..., head_dim / 2]`` for integer ``positions``.  ``scaling``: ``None`` or ``(kind, factor, a, b,
+    original_max_positions)`` with kind ``"linear"``, ``"llama3"`` (a, b = low / high frequency factors) or ``"yarn"``
+    (a, b = beta_fast, beta_slow)."""
+    half = head_dim // 2
+    scale = 1.0
+    if scaling is not None and scaling[0] == "yarn":
+        _, factor, beta_fast, beta_slow, original = scaling
+        inv_freq, scale = yarn_inv_freq(head_dim, theta, factor, beta_fast, beta_slow, original, positions.device)
+    else:
+        inv_freq = theta ** (-torch.arange(half, dtype=torch.float32, device=positions.device) / half)
+        inv_freq = scaled_inv_freq(inv_freq, scaling)
     ang = positions.to(torch.float32)[..., None] * inv_freq
+    if scale != 1.0:
+        return torch.cos(ang) * scale, torch.sin(ang) * scale
     return torch.cos(ang), torch.sin(ang)
 
 

@@ -23,8 +23,9 @@ class ModelConfig:
     experts_per_token: int = 0
     moe_ffn_size: int = 0
     qk_norm: bool = False
-    # context extension of the rotary embedding: None, or (kind, factor, low_freq_factor, high_freq_factor,
-    # original_max_positions) with kind "linear" or "llama3" (see ``scaled_inv_freq``)
+    # context extension of the rotary embedding: None, or (kind, factor, a, b, original_max_positions) with kind
+    # "linear", "llama3" (a, b = low / high frequency factors) or "yarn" (a, b = beta_fast, beta_slow); see
+    # ``rope_cos_sin``
     rope_scaling: Optional[Tuple[str, float, float, float, int]] = None
     # the LM head is the embedding matrix (small Llama-3.2 / Qwen3 models).  The model still stores both; they start
     # equal and the optimiser gives both the summed gradient, so they stay equal bit for bit.

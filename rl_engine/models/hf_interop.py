@@ -37,8 +37,14 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
     elif kind == "llama3":
         rope_scaling = ("llama3", float(scaling["factor"]), float(scaling.get("low_freq_factor", 1.0)),
                         float(scaling.get("high_freq_factor", 4.0)), int(scaling["original_max_position_embeddings"]))
+    elif kind == "yarn":
+        if any(scaling.get(k) is not None for k in ("attention_factor", "mscale", "mscale_all_dim")) or scaling.get("truncate") is False:
+            raise ValueError(f"YaRN with an explicit attention factor, mscale or without truncation is not supported: {scaling}")
+        rope_scaling = ("yarn", float(scaling["factor"]), float(scaling.get("beta_fast") or 32.0),
+                        float(scaling.get("beta_slow") or 1.0),
+                        int(scaling.get("original_max_position_embeddings") or get("max_position_embeddings")))
     elif kind != "default":
-        raise ValueError(f"rope scaling {scaling} is not supported (known: default, linear, llama3)")
+        raise ValueError(f"rope scaling {scaling} is not supported (known: default, linear, llama3, yarn)")
     model_type = str(get("model_type", "") or "")
     qkv_bias = model_type == "qwen2"          # Qwen2 / Qwen2.5: biased q, k, v; no bias on the output projection
     if get("attention_bias", False) or get("mlp_bias", False):
@@ -204,6 +210,8 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
         block = {"rope_type": how, "factor": factor}
         if how == "llama3":
             block.update(low_freq_factor=low, high_freq_factor=high, original_max_position_embeddings=original)
+        if how == "yarn":
+            block.update(beta_fast=low, beta_slow=high, original_max_position_embeddings=original)
         out["rope_scaling"] = dict(block)
         out["rope_parameters"] = dict(block, rope_theta=cfg.rope_theta)      # the spelling of newer transformers
     if moe:

@@ -71,7 +71,7 @@ def test_tied_embeddings_and_unsupported_configurations():
     _compare_logits(hf, model, 50)
     with pytest.raises(ValueError):
         config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
-                        "intermediate_size": 8, "rope_scaling": {"rope_type": "yarn", "factor": 8.0}})
+                        "intermediate_size": 8, "rope_scaling": {"rope_type": "longrope", "factor": 8.0}})
     with pytest.raises(ValueError):
         config_from_hf({"hidden_size": 32, "num_attention_heads": 2, "num_hidden_layers": 1, "vocab_size": 10,
                         "intermediate_size": 8, "attention_bias": True})
@@ -237,6 +237,7 @@ def test_qwen3_moe_checkpoint_directory(tmp_path):
 @pytest.mark.parametrize("scaling", [
     {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 16},
     {"rope_type": "linear", "factor": 2.0},
+    {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16, "beta_fast": 4.0, "beta_slow": 1.0},
 ])
 def test_rope_scaling_matches_transformers(scaling, tmp_path):
     """Llama-3.1-style and linear context extension: with 16 original positions and head_dim 16 the eight rotary
