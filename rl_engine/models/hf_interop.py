@@ -53,7 +53,8 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
     if get("use_sliding_window", model_type == "mistral") and window and int(window) < int(get("max_position_embeddings", 0) or 0):
         raise ValueError(f"sliding-window attention (window {window}) is not supported")
     experts = int(get("num_experts", 0) or get("num_local_experts", 0) or 0)
-    if experts and not get("norm_topk_prob", True):
+    renormalises = get("norm_topk_prob")
+    if experts and not (True if renormalises is None else renormalises):      # Mixtral has no switch: it always does
         raise ValueError("routers that do not renormalise the top-k weights are not supported")
     if experts and (int(get("decoder_sparse_step", 1) or 1) != 1 or get("mlp_only_layers")):
         raise ValueError("models that mix dense and mixture-of-experts layers are not supported")
@@ -65,7 +66,7 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
         int(get("num_key_value_heads") or heads), head_dim, int(get("intermediate_size")),
         rms_eps=float(get("rms_norm_eps", 1e-5)), rope_theta=float(rope_theta if rope_theta is not None else 10000.0),
         num_experts=experts, experts_per_token=int(get("num_experts_per_tok", 0) or 0) if experts else 0,
-        moe_ffn_size=int(get("moe_intermediate_size", 0) or 0) if experts else 0,
+        moe_ffn_size=int(get("moe_intermediate_size", 0) or get("intermediate_size")) if experts else 0,
         qk_norm=model_type.startswith("qwen3"), rope_scaling=rope_scaling,
         tie_word_embeddings=bool(get("tie_word_embeddings", False)), qkv_bias=qkv_bias,
     )
@@ -94,13 +95,16 @@ def hf_parameter_map(model) -> Iterator[Tuple[str, List[Tuple[str, int, int]]]]:
         yield f"l{i}.mlp_norm", [(p + "post_attention_layernorm.weight", 0, h)]
         if cfg.num_experts:
             fe = cfg.moe_ffn_size
-            yield f"l{i}.router", [(p + "mlp.gate.weight", 0, cfg.num_experts)]
+            # checkpoint names of the two MoE families: Qwen3-MoE (q/k norms) and Mixtral (none)
+            block, gate_n, up_n, down_n = (("mlp", "gate_proj", "up_proj", "down_proj") if cfg.qk_norm
+                                           else ("block_sparse_moe", "w1", "w3", "w2"))
+            yield f"l{i}.router", [(f"{p}{block}.gate.weight", 0, cfg.num_experts)]
             gate_up, down = [], []
             for e in range(e_local):
-                ep = f"{p}mlp.experts.{shard_rank * e_local + e}."
-                gate_up += [(ep + "gate_proj.weight", e * 2 * fe, e * 2 * fe + fe),
-                            (ep + "up_proj.weight", e * 2 * fe + fe, (e + 1) * 2 * fe)]
-                down.append((ep + "down_proj.weight", e * h, (e + 1) * h))
+                ep = f"{p}{block}.experts.{shard_rank * e_local + e}."
+                gate_up += [(ep + f"{gate_n}.weight", e * 2 * fe, e * 2 * fe + fe),
+                            (ep + f"{up_n}.weight", e * 2 * fe + fe, (e + 1) * 2 * fe)]
+                down.append((ep + f"{down_n}.weight", e * h, (e + 1) * h))
             yield f"l{i}.w_gate_up", gate_up
             yield f"l{i}.w_down", down
         else:
@@ -146,6 +150,9 @@ def load_hf_state_dict(model, state_dict: Mapping[str, torch.Tensor], *, strict:
                 continue
         for hf_name, lo, hi in pieces:
             src = state_dict.get(hf_name)
+            if src is None and ".block_sparse_moe.gate." in hf_name:     # newer transformers rename Mixtral's block
+                hf_name = hf_name.replace(".block_sparse_moe.", ".mlp.")
+                src = state_dict.get(hf_name)
             if src is None and hf_name == "lm_head.weight":
                 src = state_dict.get("model.embed_tokens.weight")
             if src is None:
@@ -183,12 +190,11 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
     if tie_word_embeddings is None:
         tie_word_embeddings = cfg.tie_word_embeddings
     moe, qwen = bool(cfg.num_experts), bool(cfg.qk_norm)
-    if moe and not qwen:
-        raise ValueError("mixture-of-experts checkpoints are written as Qwen3-MoE, which has per-head q/k norms")
     if cfg.qkv_bias and (moe or qwen or cfg.head_dim * cfg.num_heads != cfg.hidden_size):
         raise ValueError("biased q/k/v projections are written as Qwen2, which has neither experts nor q/k norms and "
                          "takes head_dim = hidden_size / heads")
-    arch, kind = (("Qwen3MoeForCausalLM", "qwen3_moe") if moe else ("Qwen3ForCausalLM", "qwen3") if qwen
+    arch, kind = (("Qwen3MoeForCausalLM", "qwen3_moe") if moe and qwen else ("MixtralForCausalLM", "mixtral") if moe
+                  else ("Qwen3ForCausalLM", "qwen3") if qwen
                   else ("Qwen2ForCausalLM", "qwen2") if cfg.qkv_bias else ("LlamaForCausalLM", "llama"))
     out: Dict[str, Any] = {
         "architectures": [arch], "model_type": kind, "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
@@ -214,9 +220,12 @@ def hf_config_dict(cfg: ModelConfig, *, dtype: torch.dtype = torch.bfloat16, max
             block.update(beta_fast=low, beta_slow=high, original_max_position_embeddings=original)
         out["rope_scaling"] = dict(block)
         out["rope_parameters"] = dict(block, rope_theta=cfg.rope_theta)      # the spelling of newer transformers
-    if moe:
+    if kind == "qwen3_moe":
         out.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token, moe_intermediate_size=cfg.moe_ffn_size,
                    norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])
+    if kind == "mixtral":
+        out.update(num_local_experts=cfg.num_experts, num_experts_per_tok=cfg.experts_per_token,
+                   intermediate_size=cfg.moe_ffn_size, sliding_window=None)
     return out
 
 
@@ -297,9 +306,12 @@ def load_hf_checkpoint(model, directory, *, strict: bool = True) -> List[str]:
     shard_rank, shard_world = model.expert_shard if model.expert_shard is not None else (0, 1)
     e_local = cfg.num_experts // shard_world if cfg.num_experts else 0
     route: Dict[str, Tuple[str, int, int]] = {}
+    alias: Dict[str, str] = {}                  # other spellings of a routed name -> the routed name
     for native, pieces in hf_parameter_map(model):
         for hf_name, lo, hi in pieces:
             route[hf_name] = (native, lo, hi)
+            if ".block_sparse_moe.gate." in hf_name:
+                alias[hf_name.replace(".block_sparse_moe.", ".mlp.")] = hf_name
     stacked = {}
     if cfg.num_experts:
         for i in range(cfg.num_layers):
@@ -318,12 +330,13 @@ def load_hf_checkpoint(model, directory, *, strict: bool = True) -> List[str]:
                     dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
                     filled.update(h for h, (nat, _lo, _hi) in route.items() if nat == stacked[name])
                     continue
+                src_name, name = name, alias.get(name, name)
                 if name not in route:
                     unused.append(name)
                     continue
                 native, lo, hi = route[name]
                 part = model.view(native)[lo:hi]
-                src = f.get_tensor(name)
+                src = f.get_tensor(src_name)
                 if tuple(src.shape) != tuple(part.shape):
                     raise ValueError(f"{name} has shape {tuple(src.shape)}, {native}[{lo}:{hi}] needs {tuple(part.shape)}")
                 part.copy_(src.to(device=part.device, dtype=part.dtype))

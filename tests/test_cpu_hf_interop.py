@@ -433,3 +433,31 @@ def test_padded_batches_match_transformers_for_right_and_left_padding():
         assert float(got[~keep].abs().max()) == 0.0
     with pytest.raises(ValueError, match="contiguous run"):
         lm(ids, attention_mask=torch.tensor([[1, 1, 0, 1, 1, 1, 1, 1]] * 3))
+
+
+def test_mixtral_checkpoint_names_and_logits(tmp_path):
+    """Mixtral: experts without q/k norms, ``block_sparse_moe`` / ``w1`` ``w3`` ``w2`` names on disk (newer
+    ``transformers`` hold them stacked under ``mlp`` in memory); both spellings load, logits match, a saved directory
+    loads back into ``transformers`` as ``MixtralForCausalLM``."""
+    if not hasattr(transformers, "MixtralForCausalLM"):
+        pytest.skip("this transformers has no Mixtral")
+    from rl_engine.models.hf_interop import hf_state_dict_views, model_from_hf_checkpoint, save_hf_checkpoint
+
+    config = transformers.MixtralConfig(vocab_size=67, hidden_size=64, intermediate_size=48, num_hidden_layers=2,
+                                        num_attention_heads=4, num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2,
+                                        max_position_embeddings=64, sliding_window=None, rms_norm_eps=1e-5, rope_theta=10000.0,
+                                        tie_word_embeddings=False)
+    torch.manual_seed(17)
+    hf = transformers.MixtralForCausalLM(config).float().eval()
+    cfg, model, unused = _native_from(hf)
+    assert cfg.num_experts == 4 and cfg.experts_per_token == 2 and cfg.moe_ffn_size == 48 and not cfg.qk_norm and unused == []
+    _compare_logits(hf, model, 67, atol=5e-4)
+    views = hf_state_dict_views(model)
+    assert "model.layers.1.block_sparse_moe.experts.3.w2.weight" in views and "model.layers.0.block_sparse_moe.gate.weight" in views
+    assert views["model.layers.0.block_sparse_moe.experts.0.w3.weight"].shape == (48, 64)
+    save_hf_checkpoint(model, tmp_path)
+    again = transformers.AutoModelForCausalLM.from_pretrained(tmp_path, dtype=torch.float32).eval()
+    assert type(again).__name__ == "MixtralForCausalLM"
+    _compare_logits(again, model, 67, atol=5e-4)
+    back = model_from_hf_checkpoint(tmp_path, dtype=torch.float32, device="cpu", activation_checkpointing=False)
+    assert torch.equal(back.flat, model.flat)
