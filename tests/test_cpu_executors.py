@@ -425,3 +425,43 @@ def test_importing_executors_does_not_import_heavy_runtimes():
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
     assert "BAD []" in out.stdout, out.stdout[-500:]
+
+
+def test_sampler_and_payload_parser_against_real_vllm_classes():
+    """With vLLM installed: the sampler builds a real ``vllm.SamplingParams`` from its configuration, and real
+    ``RequestOutput`` / ``CompletionOutput`` objects (returned by a stand-in engine, no GPU) are regrouped, normalised
+    and parsed by the training contract exactly like the fakes used elsewhere."""
+    try:
+        from vllm import SamplingParams
+        from vllm.outputs import CompletionOutput, RequestOutput
+    except Exception as exc:  # noqa: BLE001  (not installed, or not importable on this machine)
+        pytest.skip(f"vllm is not importable here: {type(exc).__name__}")
+    from rl_engine.executors.training_contract import extract_rollout_candidate_groups
+    from rl_engine.executors.vllm_sampler import VLLMSamplerConfig, VLLMSharedPrefixSampler
+
+    seen = {}
+
+    class Engine:
+        def generate(self, prompts, params):
+            seen["prompts"], seen["params"] = list(prompts), params
+            out = []
+            for i, prompt in enumerate(prompts):
+                done = CompletionOutput(index=0, text=f"t{i}", token_ids=[i + 1, i + 2], cumulative_logprob=-0.5 * (i + 1),
+                                        logprobs=None, finish_reason="length")
+                out.append(RequestOutput(request_id=f"r{i}", prompt=prompt if isinstance(prompt, str) else None,
+                                         prompt_token_ids=[7, 8, 9], prompt_logprobs=None, outputs=[done], finished=True))
+            return out
+
+    config = VLLMSamplerConfig.from_model_config({
+        "model": "unused", "num_generations": 3,
+        "sampling_params": {"temperature": 0.7, "top_p": 0.9, "top_k": 50, "max_tokens": 16, "seed": 1}})
+    sampler = VLLMSharedPrefixSampler(config, engine=Engine(), sampling_params_cls=SamplingParams, llm_cls=object)
+    result = sampler.generate(["alpha", "beta"])
+    assert isinstance(seen["params"], SamplingParams) and seen["params"].top_k == 50 and seen["params"].max_tokens == 16
+    assert seen["prompts"] == ["alpha"] * 3 + ["beta"] * 3                  # repeated back to back for the prefix cache
+    assert result["num_prompts"] == 2 and result["num_generations"] == 3
+    first = result["normalized_outputs"][1][2]
+    assert first.request_id == "r5" and first.token_ids == [6, 7] and first.finish_reason == "length"
+    assert first.prompt_token_ids == [7, 8, 9] and first.cumulative_logprob == -3.0 and first.text == "t5"
+    groups = extract_rollout_candidate_groups(result)
+    assert groups == [[[1, 2], [2, 3], [3, 4]], [[4, 5], [5, 6], [6, 7]]]
