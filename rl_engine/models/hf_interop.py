@@ -5,13 +5,16 @@ The reference has no model of its own: its executors and trainers run Hugging Fa
 this library keeps packed parameters in one flat buffer (``wqkv`` = q, k and v rows stacked, ``w_gate_up`` = gate and up
 rows stacked, experts stacked by expert), so two things are needed to stand in for a Hugging Face module:
 
-* ``config_from_hf`` / ``load_hf_state_dict``: build the matching ``ModelConfig`` and copy a Llama-3 / Qwen3 /
-  Qwen3-MoE ``state_dict`` into the flat buffer (only the local experts of an expert-sharded model);
+* ``config_from_hf`` / ``load_hf_state_dict``: build the matching ``ModelConfig`` and copy a Llama / Mistral / Mixtral /
+  Qwen2 / Qwen3 / Qwen3-MoE ``state_dict`` into the flat buffer (only the local experts of an expert-sharded model);
 * ``hf_state_dict_views``: the parameters under their Hugging Face names as zero-copy views (row ranges of the packed
-  matrices are contiguous), which is what a weight bridge publishes to a vLLM engine.
+  matrices are contiguous), which is what a weight bridge publishes to a vLLM engine;
+* ``save_hf_checkpoint`` / ``load_hf_checkpoint`` / ``model_from_hf_checkpoint``: the same for directories of
+  ``config.json`` + (sharded) safetensors files, streamed tensor by tensor.
 
-Rotary embedding (half-split rotation), RMSNorm (plain weight, eps inside the root), attention scale and the Qwen3
-router (softmax over all experts, top-k, renormalised) follow the Hugging Face implementations, so logits agree (tested
+Rotary embedding (half-split rotation; linear, llama3 and YaRN scaling), RMSNorm (plain weight, eps inside the root),
+attention scale, the Qwen2 q/k/v biases, the Qwen3 head norms and the router of both MoE families (softmax over all
+experts, top-k, renormalised) follow the Hugging Face implementations, so logits agree (tested
 against ``transformers`` on CPU in fp32).
 """
 
@@ -24,8 +27,15 @@ import torch
 from rl_engine.models.config import ModelConfig
 
 
+# a mapping without ``model_type`` is read as the Llama architecture
+_MODEL_TYPES = {"", "llama", "mistral", "mixtral", "qwen2", "qwen3", "qwen3_moe"}
+
+
 def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
-    """``ModelConfig`` of a Hugging Face Llama / Qwen3 / Qwen3-MoE configuration object (or mapping)."""
+    """``ModelConfig`` of a Hugging Face configuration object (or mapping) of one of the supported decoder families:
+    ``llama`` (Llama-2 / 3 / 3.x), ``mistral`` (no sliding window), ``mixtral``, ``qwen2`` (Qwen2 / 2.5), ``qwen3``,
+    ``qwen3_moe``.  Anything this model cannot reproduce exactly raises ``ValueError``: another ``model_type``, an
+    unknown rotary scaling, biases outside q/k/v, sliding windows, mixed dense / MoE stacks."""
     get = (lambda k, d=None: hf_config.get(k, d)) if isinstance(hf_config, Mapping) else (lambda k, d=None: getattr(hf_config, k, d))
     hidden, heads = int(get("hidden_size")), int(get("num_attention_heads"))
     head_dim = int(get("head_dim") or hidden // heads)
@@ -46,6 +56,8 @@ def config_from_hf(hf_config: Any, name: str = "") -> ModelConfig:
     elif kind != "default":
         raise ValueError(f"rope scaling {scaling} is not supported (known: default, linear, llama3, yarn)")
     model_type = str(get("model_type", "") or "")
+    if model_type not in _MODEL_TYPES:
+        raise ValueError(f"model_type {model_type!r} is not one of the supported decoder families {sorted(_MODEL_TYPES - {''})}")
     qkv_bias = model_type == "qwen2"          # Qwen2 / Qwen2.5: biased q, k, v; no bias on the output projection
     if get("attention_bias", False) or get("mlp_bias", False):
         raise ValueError("biases on the output projection or the FFN are not supported (Qwen2-style q/k/v biases are)")

@@ -406,6 +406,8 @@ def test_mistral_checkpoint_is_the_llama_architecture():
                                           num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64, sliding_window=16)
     with pytest.raises(ValueError, match="sliding-window"):
         config_from_hf(windowed)
+    with pytest.raises(ValueError, match="model_type 'gpt2'"):
+        config_from_hf(transformers.GPT2Config(vocab_size=10, n_embd=8, n_layer=1, n_head=1))
 
 
 def test_padded_batches_match_transformers_for_right_and_left_padding():
