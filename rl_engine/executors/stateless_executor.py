@@ -145,51 +145,79 @@ def _accepts(model: torch.nn.Module, keyword: str) -> bool:
 
 
 # ------------------------------------------------------------------------- model configuration
+_ABSENT = object()
+
+
+class _ConfigEdits:
+    """Applies the no-cache scoring policy to ``model.config`` / ``model.generation_config`` and remembers what was
+    there, so that a temporary application can be undone exactly (attributes that did not exist are removed again).
+
+    Hugging Face models pick their attention kernels from configuration attributes, not from forward arguments, so the
+    backend is written to ``attn_implementation`` and ``_attn_implementation`` of every configuration object, whether
+    or not it had them (reference: ``rl_engine/executors/stateless_executor.py:335-366,583-627``)."""
+
+    def __init__(self, model: torch.nn.Module, config: StatelessForwardConfig) -> None:
+        self._undo = []
+        cache_targets = backend_targets = 0
+        owners = []
+        for name in ("config", "generation_config"):
+            owner = getattr(model, name, None)
+            if owner is not None and all(owner is not seen for seen in owners):
+                owners.append(owner)
+        for owner in owners:
+            if hasattr(owner, "use_cache"):
+                self._set(owner, "use_cache", False)
+                cache_targets += 1
+            if config.attention_backend != "model_default":
+                try:
+                    self._set(owner, "attn_implementation", config.attention_backend)
+                    self._set(owner, "_attn_implementation", config.attention_backend)
+                    backend_targets += 1
+                except Exception:            # a configuration class that refuses the attribute: leave it alone
+                    pass
+        self.policy: Dict[str, Any] = {
+            "attention_backend": config.attention_backend,
+            "attention_backend_configured": backend_targets > 0,
+            "attention_backend_config_targets": backend_targets,
+            "model_config_use_cache_disabled": cache_targets > 0,
+            "model_config_use_cache_targets": cache_targets,
+            "reject_kv_cache_outputs": config.reject_kv_cache_outputs,
+        }
+
+    def _set(self, owner: Any, attr: str, value: Any) -> None:
+        before = getattr(owner, attr, _ABSENT)
+        setattr(owner, attr, value)
+        self._undo.append((owner, attr, before))
+
+    def undo(self) -> None:
+        for owner, attr, before in reversed(self._undo):
+            try:
+                if before is _ABSENT:
+                    if hasattr(owner, attr):
+                        delattr(owner, attr)
+                else:
+                    setattr(owner, attr, before)
+            except Exception:
+                pass
+        self._undo.clear()
+
+
 @contextmanager
 def _stateless_model_policy(model: torch.nn.Module, config: StatelessForwardConfig) -> Iterator[Dict[str, Any]]:
     """Temporarily force ``use_cache=False`` and the requested attention backend; restore on exit."""
-    touched = []
-    policy: Dict[str, Any] = {"attention_backend": config.attention_backend}
-    for owner_name in ("config", "generation_config"):
-        owner = getattr(model, owner_name, None)
-        if owner is None:
-            continue
-        if hasattr(owner, "use_cache"):
-            touched.append((owner, "use_cache", owner.use_cache))
-            owner.use_cache = False
-            policy[f"{owner_name}_use_cache_forced_false"] = True
-        if config.attention_backend != "model_default" and owner_name == "config":
-            for attr in ("_attn_implementation", "attn_implementation"):
-                if hasattr(owner, attr):
-                    touched.append((owner, attr, getattr(owner, attr)))
-                    try:
-                        setattr(owner, attr, config.attention_backend)
-                        policy["attention_backend_applied"] = True
-                    except Exception:
-                        touched.pop()
+    edits = _ConfigEdits(model, config)
     was_training = model.training
     model.eval()
     try:
-        yield policy
+        yield edits.policy
     finally:
-        for owner, attr, old in reversed(touched):
-            try:
-                setattr(owner, attr, old)
-            except Exception:
-                pass
+        edits.undo()
         model.train(was_training)
 
 
 def configure_stateless_model(model: torch.nn.Module, config: Optional[StatelessForwardConfig] = None) -> Dict[str, Any]:
     """Permanently apply the no-cache policy (same fields as the temporary context manager)."""
-    config = config or StatelessForwardConfig()
-    policy: Dict[str, Any] = {"attention_backend": config.attention_backend}
-    for owner_name in ("config", "generation_config"):
-        owner = getattr(model, owner_name, None)
-        if owner is not None and hasattr(owner, "use_cache"):
-            owner.use_cache = False
-            policy[f"{owner_name}_use_cache_forced_false"] = True
-    return policy
+    return _ConfigEdits(model, config or StatelessForwardConfig()).policy
 
 
 def _raised_inside_flash_attention(exc: BaseException) -> bool:
@@ -232,16 +260,27 @@ def _forward_no_cache(model: torch.nn.Module, inputs: StatelessForwardInputs):
 
 # ----------------------------------------------------------------------------------- scoring
 def _validate(inputs: StatelessForwardInputs, config: StatelessForwardConfig) -> None:
+    """Shape, device and mask rules of a scoring call (reference: ``rl_engine/executors/stateless_executor.py:440-471``)."""
     ids = inputs.input_ids
     if ids.ndim != 2:
         raise ValueError(f"input_ids must have shape [B, S], got {tuple(ids.shape)}")
-    for name in ("attention_mask", "completion_mask"):
-        if getattr(inputs, name).shape != ids.shape:
-            raise ValueError(f"{name} shape must match input_ids shape")
-    if inputs.labels is not None and inputs.labels.shape != ids.shape:
-        raise ValueError("labels shape must match input_ids shape")
+    companions = {"attention_mask": inputs.attention_mask, "completion_mask": inputs.completion_mask}
+    if inputs.labels is not None:
+        companions["labels"] = inputs.labels
+    for rule, bad in (("shape", lambda t: t.shape != ids.shape), ("device", lambda t: t.device != ids.device)):
+        for name, tensor in companions.items():
+            if bad(tensor):
+                raise ValueError(f"{name} {rule} must match input_ids {rule}")
     if config.max_batch_size is not None and ids.shape[0] > config.max_batch_size:
         raise ValueError(f"batch size {ids.shape[0]} exceeds max_batch_size {config.max_batch_size}")
+    keep = inputs.completion_mask.to(torch.bool)
+    if config.mode in ("reference", "both"):
+        if ids.shape[1] < 2:
+            raise ValueError("reference scoring requires sequence_len >= 2")
+        if bool(keep[:, 0].any()):
+            raise ValueError("completion_mask[:, 0] must be False; completions cannot start at position 0")
+    if not bool(keep.any()):
+        raise ValueError("completion_mask must contain at least one active token")
 
 
 def score_reference_logprobs(logits, inputs: StatelessForwardInputs, *, temperature: float = 1.0,
@@ -280,8 +319,10 @@ def default_reward_adapter(outputs: StatelessForwardOutputs, inputs: StatelessFo
         found = outputs.logits
     if found is None:
         raise ValueError("reward mode requires scalar logits or a reward_adapter")
-    while found.ndim > 1 and found.shape[-1] == 1:
-        found = found.squeeze(-1)
+    if found.ndim == 2 and found.shape[1] == 1:
+        found = found[:, 0]
+    if found.ndim != 1:
+        raise ValueError(f"reward tensor must have shape [B] or [B, 1], got {tuple(found.shape)}")
     return found
 
 
