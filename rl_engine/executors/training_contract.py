@@ -379,33 +379,73 @@ def build_stateless_inputs_from_rollout_payload(payload: Any, *, prompt_len: Opt
     return StatelessForwardInputs(input_ids=ids.to(dev), attention_mask=attn.to(dev), completion_mask=comp.to(dev))
 
 
-def _set(node: Any, key: str, value: Any) -> None:
-    if isinstance(node, dict):
-        node[key] = value
-    else:
-        try:
-            setattr(node, key, value)
-        except Exception:
-            pass
+def _candidate_copy(candidate: Any) -> Dict[str, Any]:
+    """A candidate as a fresh dict (mappings are copied, objects give their attributes), so that attaching scores never
+    writes into the rollout's own records."""
+    if isinstance(candidate, Mapping):
+        return dict(candidate)
+    try:
+        return dict(vars(candidate))
+    except TypeError:
+        return {"candidate": candidate}
+
+
+def _attach_per_candidate(scored: Dict[str, Any], values: List[Any], fields: Callable[[Any], Dict[str, Any]], what: str) -> None:
+    """Gives every candidate that carries token ids, in payload order, its entry of ``values``.  The grouped outputs are
+    rebuilt (``normalized_outputs`` first, else ``outputs``); a payload without such candidates is left alone; a count
+    that does not match is an error rather than a partial attachment."""
+    if not values:
+        return
+    for key in ("normalized_outputs", "outputs"):
+        grouped = scored.get(key)
+        if not _is_seq(grouped):
+            continue
+        cursor, rebuilt = 0, []
+        for group in grouped:
+            members = list(group) if _is_seq(group) and not isinstance(group, Mapping) else [group]
+            new_group = []
+            for cand in members:
+                if not _ints(_find_field(cand, _TOKEN_KEYS, nested_first=True)):
+                    new_group.append(cand)
+                    continue
+                if cursor >= len(values):
+                    raise ValueError(f"stateless {what} count must match rollout candidate count, got fewer "
+                                     f"{what} than candidates")
+                updated = _candidate_copy(cand)
+                updated.update(fields(values[cursor]))
+                new_group.append(updated)
+                cursor += 1
+            rebuilt.append(new_group)
+        if cursor == 0:
+            continue
+        if cursor != len(values):
+            raise ValueError(f"stateless {what} count must match rollout candidate count, got {len(values)} {what} "
+                             f"for {cursor} candidates")
+        scored[key] = rebuilt
+        return
 
 
 def attach_stateless_scores_to_payload(payload: Any, result: StatelessForwardResult, *,
                                        inputs: Optional[StatelessForwardInputs] = None) -> Dict[str, Any]:
+    """The rollout payload plus ``stateless_scores`` and, per candidate, ``reward`` / ``reference_logps`` with their
+    ``*_source`` set to ``"stateless_executor"`` (reference: ``rl_engine/executors/training_contract.py:351-374,
+    546-604``).  The input payload and its candidates are not modified."""
     scored = dict(payload) if isinstance(payload, Mapping) else {"raw_payload": payload}
     scored["stateless_scores"] = {
         "reference_logps": result.reference_logps, "rewards": result.rewards, "token_scores": result.token_scores,
         "metrics": dict(result.metrics),
     }
-    candidates = [c for group in _grouped_outputs(scored) for c in group
-                  if _ints(_find_field(c, _TOKEN_KEYS, nested_first=True))]
-    if result.rewards is not None and len(candidates) == int(result.rewards.shape[0]):
-        for cand, value in zip(candidates, result.rewards.detach().cpu().tolist()):
-            _set(cand, "reward", float(value))
-    if result.reference_logps is not None and inputs is not None and len(candidates) == int(inputs.input_ids.shape[0]):
+    if result.rewards is not None:
+        rewards = [float(v) for v in result.rewards.detach().cpu().reshape(-1).tolist()]
+        _attach_per_candidate(scored, rewards, lambda v: {"reward": v, "reward_source": "stateless_executor"}, "reward")
+    if result.reference_logps is not None and inputs is not None:
+        if result.reference_logps.shape != inputs.completion_mask.shape:
+            raise ValueError("reference_logps shape must match completion_mask shape")
         ref = result.reference_logps.detach().cpu()
         mask = inputs.completion_mask.detach().cpu().to(torch.bool)
-        for row, cand in enumerate(candidates):
-            _set(cand, "reference_logps", [float(v) for v in ref[row][mask[row]].tolist()])
+        rows = [[float(v) for v in ref[r][mask[r]].tolist()] for r in range(ref.shape[0])]
+        _attach_per_candidate(scored, rows, lambda v: {"reference_logps": v, "reference_logp_source": "stateless_executor"},
+                              "reference_logps row")
     return scored
 
 
