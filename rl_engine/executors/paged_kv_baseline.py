@@ -55,6 +55,8 @@ class PagedKVCacheReservation:
     value_cache: torch.Tensor
     block_tables: torch.Tensor
     sequence_lengths: torch.Tensor
+    blocks_per_sequence: torch.Tensor
+    block_size: int
     required_blocks: int
     reserved_blocks: int
     cache_bytes: int
@@ -91,8 +93,8 @@ def reserve_paged_kv_cache(inputs: StatelessForwardInputs, config: PagedKVScorin
     nbytes = lambda t: t.numel() * t.element_size()
     return PagedKVCacheReservation(
         key_cache=key_cache, value_cache=value_cache, block_tables=table, sequence_lengths=lengths,
-        required_blocks=required, reserved_blocks=reserved, cache_bytes=nbytes(key_cache) + nbytes(value_cache),
-        metadata_bytes=nbytes(table) + nbytes(lengths),
+        blocks_per_sequence=per_seq, block_size=int(config.block_size), required_blocks=required, reserved_blocks=reserved, cache_bytes=nbytes(key_cache) + nbytes(value_cache),
+        metadata_bytes=nbytes(table) + nbytes(lengths) + nbytes(per_seq),
     )
 
 

@@ -20,10 +20,16 @@ class RayUnavailableError(RuntimeError):
 
 @dataclass(frozen=True)
 class RayRuntimeConfig:
+    """``auto_init``: call ``ray.init`` when the runtime is not up yet (off: the caller has initialised Ray);
+    ``shutdown_ray_on_close``: ``ray.shutdown()`` after the actors were killed.  ``address`` / ``namespace`` are
+    shorthands for the same keys of ``init_kwargs``."""
+
+    auto_init: bool = True
+    init_kwargs: Mapping[str, Any] = field(default_factory=dict)
+    shutdown_ray_on_close: bool = False
     address: Optional[str] = None
     namespace: Optional[str] = None
     ignore_reinit_error: bool = True
-    init_kwargs: Mapping[str, Any] = field(default_factory=dict)
 
     def resolved_init_kwargs(self) -> Dict[str, Any]:
         out = dict(self.init_kwargs)
@@ -41,15 +47,19 @@ class RayActorOptions:
     num_cpus: Optional[float] = None
     num_gpus: Optional[float] = None
     resources: Mapping[str, float] = field(default_factory=dict)
-    max_restarts: int = 0
-    max_task_retries: int = 0
+    namespace: Optional[str] = None
+    max_restarts: Optional[int] = None
+    max_task_retries: Optional[int] = None
+    scheduling_strategy: Any = None
     lifetime: Optional[str] = None
     runtime_env: Optional[Mapping[str, Any]] = None
     extra: Mapping[str, Any] = field(default_factory=dict)
 
     def to_ray_options(self) -> Dict[str, Any]:
+        """Only what was set: Ray's own defaults apply to everything else."""
         out: Dict[str, Any] = dict(self.extra)
-        for key in ("name", "num_cpus", "num_gpus", "lifetime"):
+        for key in ("name", "namespace", "num_cpus", "num_gpus", "max_restarts", "max_task_retries",
+                    "scheduling_strategy", "lifetime"):
             value = getattr(self, key)
             if value is not None:
                 out[key] = value
@@ -57,8 +67,6 @@ class RayActorOptions:
             out["resources"] = dict(self.resources)
         if self.runtime_env is not None:
             out["runtime_env"] = dict(self.runtime_env)
-        out["max_restarts"] = int(self.max_restarts)
-        out["max_task_retries"] = int(self.max_task_retries)
         return out
 
 
@@ -67,7 +75,7 @@ class RayWorkerSpec:
     worker_factory: Any
     args: Tuple[Any, ...] = ()
     kwargs: Mapping[str, Any] = field(default_factory=dict)
-    options: RayActorOptions = field(default_factory=RayActorOptions)
+    actor_options: RayActorOptions = field(default_factory=RayActorOptions)
 
 
 class _RayWorkerActor:
@@ -91,7 +99,12 @@ class _RayWorkerActor:
 
     def update_weights(self, manifest: Any) -> Any:
         result = self._call(("update_weights",), manifest)
-        return {"weight_version": getattr(manifest, "weight_version", None), "tensors": len(result) if result is not None else 0}
+        # the worker's own answer goes back to the driver, except a mapping of imported tensors (what
+        # ``RolloutExecutor.update_weights`` returns): shipping the weights through the object store would defeat the
+        # bridge, so that becomes a summary
+        if isinstance(result, Mapping) and result and all(hasattr(v, "data_ptr") for v in result.values()):
+            return {"weight_version": getattr(manifest, "weight_version", None), "tensors": len(result)}
+        return result
 
     def publish_weights(self, weight_version: Optional[int] = None, metadata: Optional[Mapping[str, Any]] = None) -> Any:
         kwargs: Dict[str, Any] = {}
@@ -153,11 +166,14 @@ def _load_ray() -> Any:
 
 
 class RayActorManager:
-    def __init__(self, runtime: Optional[RayRuntimeConfig] = None, *, ray_module: Any = None) -> None:
-        self.runtime = runtime or RayRuntimeConfig()
+    def __init__(self, runtime_config: Optional[RayRuntimeConfig] = None, *, ray_module: Any = None) -> None:
+        self.runtime_config = runtime_config or RayRuntimeConfig()
         self._ray = ray_module
         self._actors: List[Any] = []
-        self._initialized = False
+
+    @property
+    def runtime(self) -> RayRuntimeConfig:
+        return self.runtime_config
 
     def __enter__(self) -> "RayActorManager":
         self.ensure_runtime()
@@ -169,17 +185,16 @@ class RayActorManager:
     def ensure_runtime(self) -> Any:
         if self._ray is None:
             self._ray = _load_ray()
-        if not self._initialized:
+        if self.runtime_config.auto_init:
             is_init = getattr(self._ray, "is_initialized", None)
             if not (callable(is_init) and is_init()):
-                self._ray.init(**self.runtime.resolved_init_kwargs())
-            self._initialized = True
+                self._ray.init(**self.runtime_config.resolved_init_kwargs())
         return self._ray
 
     def create_worker_actor(self, spec: RayWorkerSpec) -> Any:
         ray = self.ensure_runtime()
         remote_cls = ray.remote(_RayWorkerActor)
-        options = spec.options.to_ray_options()
+        options = spec.actor_options.to_ray_options()
         if options:
             remote_cls = remote_cls.options(**options)
         actor = remote_cls.remote(spec.worker_factory, *spec.args, **dict(spec.kwargs))
@@ -201,7 +216,9 @@ class RayActorManager:
             return
         for actor in reversed(self._actors):
             try:
-                self._ray.kill(actor)
+                self._ray.kill(actor, no_restart=True)      # a worker that is shut down must not come back
             except Exception:
                 pass
         self._actors.clear()
+        if self.runtime_config.shutdown_ray_on_close and hasattr(self._ray, "shutdown"):
+            self._ray.shutdown()

@@ -322,7 +322,8 @@ class FakeRay:
     def get(self, ref):
         return ref.value
 
-    def kill(self, actor):
+    def kill(self, actor, no_restart=True):          # the signature of ``ray.kill``
+        assert no_restart is True
         self.killed.append(actor)
 
 
@@ -338,8 +339,8 @@ def test_ray_actor_manager_with_fake_ray():
         assert ray.inited == [{"ignore_reinit_error": True, "address": "auto", "namespace": "rl"}]
         trainer = mgr.create_training_worker(RayWorkerSpec(
             NativeTrainingWorker, kwargs={"config": NativeTrainingConfig(vocab_size=32, hidden_dim=8)},
-            options=RayActorOptions(name="trainer", num_gpus=1, max_restarts=2)))
-        assert ray.options_seen[0] == {"name": "trainer", "num_gpus": 1, "max_restarts": 2, "max_task_retries": 0}
+            actor_options=RayActorOptions(name="trainer", num_gpus=1, max_restarts=2)))
+        assert ray.options_seen[0] == {"name": "trainer", "num_gpus": 1, "max_restarts": 2}   # only what was set
         result = trainer.train(make_rollout_result(iteration=0, weight_version=0, payload=None))
         assert result.published_weight_version == 1
         manifest = trainer.publish_weights(weight_version=1)
