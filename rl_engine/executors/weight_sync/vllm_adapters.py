@@ -18,6 +18,8 @@ None of these import vLLM; they look for capabilities on the engine object they 
 
 from __future__ import annotations
 
+import importlib
+
 from typing import Any, Callable, Dict, List, Mapping, Optional, Tuple
 
 import torch
@@ -107,10 +109,15 @@ class VLLMWeightInstallAdapter(_ActiveVersion):
 
 
 class VLLMIPCWeightUpdateRequestBuilder:
-    def __init__(self, *, is_checkpoint_format: bool = True, reduce_tensor=None, gpu_uuid_resolver=None) -> None:
+    def __init__(self, *, is_checkpoint_format: bool = True, reduce_tensor=None, gpu_uuid_resolver=None,
+                 reduce_tensor_fn=None, gpu_uuid: Optional[str] = None) -> None:
+        """``reduce_tensor`` / ``reduce_tensor_fn`` (the reference's spelling): the function that turns a CUDA tensor into
+        an IPC handle (default: torch's ``reduce_tensor``).  ``gpu_uuid``: a fixed UUID for the handle table;
+        ``gpu_uuid_resolver``: a callable asked when one is needed (default: the current device's)."""
         self.is_checkpoint_format = bool(is_checkpoint_format)
-        self._reduce_tensor = reduce_tensor
-        self._gpu_uuid_resolver = gpu_uuid_resolver
+        self._reduce_tensor = reduce_tensor if reduce_tensor is not None else reduce_tensor_fn
+        self._gpu_uuid_resolver = gpu_uuid_resolver if gpu_uuid_resolver is not None else (
+            None if gpu_uuid is None else (lambda: gpu_uuid))
         self._keepalive: Dict[str, List[Any]] = {}
 
     def __call__(self, manifest: WeightUpdateManifest, tensors: Mapping[str, Any]) -> Dict[str, Any]:
@@ -238,10 +245,14 @@ class VLLMInProcessWeightReloadAdapter(_ActiveVersion):
 
 class VLLMCheckpointWeightReloadAdapter(_ActiveVersion):
     def __init__(self, engine: Any, *, weights_path: Optional[str] = None, weights_path_resolver=None,
-                 is_checkpoint_format: bool = True) -> None:
+                 metadata_key: str = "vllm_weights_path", is_checkpoint_format: bool = True,
+                 synchronize_cuda: bool = True) -> None:
+        """The path comes from ``weights_path``, else ``weights_path_resolver(manifest)``, else
+        ``manifest.metadata[metadata_key]``."""
         self.engine = engine
         self._weights_path, self._resolver = weights_path, weights_path_resolver
-        self.is_checkpoint_format = bool(is_checkpoint_format)
+        self.metadata_key = metadata_key
+        self.is_checkpoint_format, self.synchronize_cuda = bool(is_checkpoint_format), bool(synchronize_cuda)
 
     def install(self, manifest: WeightUpdateManifest, tensors: Mapping[str, torch.Tensor]) -> None:
         WeightLayout.from_metadata(manifest.metadata).validate_supported()
@@ -254,6 +265,8 @@ class VLLMCheckpointWeightReloadAdapter(_ActiveVersion):
                 "checkpoint",
             )
             reload_fn(path)
+            if self.synchronize_cuda and torch.cuda.is_available():
+                torch.cuda.synchronize()
         except Exception:
             self.active_update_id = None
             raise
@@ -269,42 +282,82 @@ class VLLMCheckpointWeightReloadAdapter(_ActiveVersion):
             found = self._resolver(manifest)
             if found:
                 return str(found)
-        from_meta = manifest.metadata.get("vllm_weights_path")
+        from_meta = manifest.metadata.get(self.metadata_key)
         if from_meta:
             return str(from_meta)
         raise WeightBridgeUnavailableError(
-            "vLLM checkpoint reload needs a weights_path (argument, resolver, or metadata['vllm_weights_path'])."
+            f"vLLM checkpoint reload needs a weights_path (argument, resolver, or metadata[{self.metadata_key!r}])."
         )
 
 
-def rebind_parameters(model: torch.nn.Module, aliases: Mapping[str, torch.Tensor]) -> Dict[str, Any]:
-    """Point ``parameter.data`` at the aliasing tensors; undo everything if one entry does not fit."""
+def rebind_parameters(model: torch.nn.Module, aliases: Mapping[str, torch.Tensor], *, skip_unknown: bool = False,
+                      originals: Optional[Dict[str, torch.Tensor]] = None) -> List[str]:
+    """Point ``parameter.data`` of every parameter named in ``aliases`` at the aliasing tensor and return the names
+    that were rebound; undo all of them if one entry does not fit.  ``originals`` collects the storage each parameter
+    had before its FIRST rebinding.  Names the model does not have are an error unless ``skip_unknown``."""
     params = dict(model.named_parameters())
-    undo: List[Tuple[torch.nn.Parameter, torch.Tensor]] = []
+    originals = {} if originals is None else originals
+    done: List[Tuple[str, torch.Tensor, bool]] = []     # (name, data before this call, first rebinding?)
     try:
         for name, alias in aliases.items():
-            if name not in params:
+            p = params.get(name)
+            if p is None:
+                if skip_unknown:
+                    continue
                 raise WeightManifestValidationError(f"model has no parameter named {name}")
-            p = params[name]
-            if tuple(p.shape) != tuple(alias.shape) or p.dtype != alias.dtype:
+            if tuple(p.shape) != tuple(alias.shape):
                 raise WeightManifestValidationError(
-                    f"parameter {name} mismatch: model {tuple(p.shape)}/{p.dtype}, update {tuple(alias.shape)}/{alias.dtype}"
-                )
-            undo.append((p, p.data))
+                    f"parameter shape mismatch for {name}: model {tuple(p.shape)}, update {tuple(alias.shape)}")
+            if p.dtype != alias.dtype:
+                raise WeightManifestValidationError(
+                    f"parameter dtype mismatch for {name}: model {p.dtype}, update {alias.dtype}")
+            first = name not in originals
+            done.append((name, p.data, first))
+            originals.setdefault(name, p.data)
             p.data = alias
     except Exception:
-        for p, old in reversed(undo):
-            p.data = old
+        for name, before, first in reversed(done):
+            params[name].data = before
+            if first:
+                originals.pop(name, None)
         raise
-    return {"rebound": len(undo), "originals": undo}
+    return [name for name, _before, _first in done]
+
+
+class _WorkerBinding:
+    """What lives beside the model inside the worker process while its parameters alias an imported update: the
+    consumer bridge that keeps the mapping alive, the update's tensors and the storage to go back to."""
+
+    ATTRIBUTE = "_rl_engine_vmm_binding"
+
+    def __init__(self) -> None:
+        self.bridge: Any = None
+        self.update_id: Optional[str] = None
+        self.tensors: Dict[str, torch.Tensor] = {}
+        self.originals: Dict[str, torch.Tensor] = {}
 
 
 class VLLMCUDAVMMExternalStorageAdapter(_ActiveVersion):
-    def __init__(self, engine: Any, *, bridge_factory=None, apply_model: Optional[Callable] = None) -> None:
+    """Zero-copy install of a ``cuda-vmm`` update into vLLM workers (reference: ``rl_engine/executors/bridge.py:543-747``).
+
+    The function handed to ``engine.apply_model`` runs INSIDE every worker: it builds a consumer
+    ``CUDAVMMTensorBridge`` there, imports the manifest (mapping the publisher's allocation through the POSIX fd),
+    points the ``.data`` of every parameter whose name is in the update at the imported tensor, and acknowledges.  A
+    tensor that does not fit undoes the worker's rebinding and releases the import.  ``release`` goes the same way
+    back.  ``require_all_parameters``: every tensor of the manifest must have been bound on some worker.
+
+    ``bridge_factory`` (tests, other transports) replaces the construction of the consumer bridge; ``apply_model``
+    replaces ``engine.apply_model`` / ``engine.llm_engine.apply_model``."""
+
+    def __init__(self, engine: Any, *, device_index: int = 0, source_worker: str = "vllm-rollout", source_rank: int = 0,
+                 require_all_parameters: bool = False, synchronize_cuda: bool = True, bridge_factory=None,
+                 apply_model: Optional[Callable] = None) -> None:
         self.engine = engine
+        self.device_index, self.source_worker, self.source_rank = int(device_index), source_worker, int(source_rank)
+        self.require_all_parameters, self.synchronize_cuda = bool(require_all_parameters), bool(synchronize_cuda)
         self._bridge_factory = bridge_factory
         self._apply_model = apply_model
-        self._originals: Dict[str, Any] = {}
+        self.last_result: List[Dict[str, Any]] = []
 
     def _apply(self) -> Callable[[Callable], Any]:
         if self._apply_model is not None:
@@ -317,32 +370,68 @@ class VLLMCUDAVMMExternalStorageAdapter(_ActiveVersion):
             "vLLM external-storage install needs engine.apply_model(fn) (or an explicit apply_model=)."
         )
 
+    def _consumer_bridge(self) -> Any:
+        if self._bridge_factory is not None:
+            return self._bridge_factory()
+        # looked up through the public module at call time, inside the worker
+        bridge_module = importlib.import_module("rl_engine.executors.bridge")
+        return bridge_module.CUDAVMMTensorBridge(source_worker=self.source_worker, source_rank=self.source_rank,
+                                                 device_index=self.device_index)
+
     def install(self, manifest: WeightUpdateManifest, tensors: Mapping[str, torch.Tensor]) -> None:
-        block = manifest.metadata.get(BRIDGE_METADATA_KEY)
-        if not isinstance(block, Mapping) or block.get("format") != CUDA_VMM_FORMAT:
-            raise WeightBridgeUnavailableError("external-storage install needs a cuda-vmm weight update")
-        if set(tensors) != set(manifest.tensors):
-            raise WeightManifestValidationError("external-storage tensor set does not match the manifest")
-        aliases = dict(tensors)
+        del tensors                       # the workers import the update themselves
+        WeightLayout.from_metadata(manifest.metadata).validate_supported()
+        if manifest.transport != "cuda-vmm":
+            raise WeightBridgeUnavailableError(
+                f"external-storage install needs a cuda-vmm weight update, got transport {manifest.transport!r}")
+        apply = self._apply()
+        synchronize = self.synchronize_cuda
 
-        def on_worker(model: torch.nn.Module) -> Dict[str, Any]:
-            local = aliases
-            if self._bridge_factory is not None:  # worker in another process: map the update there
-                local = dict(self._bridge_factory().import_update(manifest))
-            result = rebind_parameters(model, local)
-            self._originals[manifest.update_id] = result.pop("originals")
-            return result
+        def bind(model: torch.nn.Module) -> Dict[str, Any]:
+            binding = getattr(model, _WorkerBinding.ATTRIBUTE, None) or _WorkerBinding()
+            bridge = self._consumer_bridge()
+            imported = dict(bridge.import_update(manifest))
+            try:
+                with torch.no_grad():
+                    rebound = rebind_parameters(model, imported, skip_unknown=True, originals=binding.originals)
+                bridge.acknowledge(manifest.update_id)
+            except Exception:
+                imported.clear()
+                bridge.release(manifest.update_id)
+                raise
+            if synchronize and torch.cuda.is_available():
+                torch.cuda.synchronize()
+            binding.bridge, binding.update_id, binding.tensors = bridge, manifest.update_id, imported
+            setattr(model, _WorkerBinding.ATTRIBUTE, binding)
+            return {"update_id": manifest.update_id, "weight_version": manifest.weight_version, "rebound": rebound,
+                    "tensor_count": len(imported), "zero_copy": True}
 
-        self._apply()(on_worker)
+        results = apply(bind)
+        results = [dict(r or {}) for r in (results if isinstance(results, list) else [results])]
+        bound = set().union(*(set(r.get("rebound", [])) for r in results)) if results else set()
+        missing = sorted(set(manifest.tensors) - bound)
+        if self.require_all_parameters and missing:
+            self.release(manifest.update_id)
+            raise WeightManifestValidationError(f"vLLM CUDA VMM install did not bind every manifest tensor: missing={missing}")
+        self.last_result = results
         self._activate(manifest)
 
     def release(self, update_id: str) -> None:
-        originals = self._originals.pop(update_id, None)
-        if originals:
-            def restore(_model: torch.nn.Module) -> Dict[str, Any]:
-                for p, old in reversed(originals):
-                    p.data = old
-                return {"restored": len(originals)}
+        def unbind(model: torch.nn.Module) -> Dict[str, Any]:
+            binding = getattr(model, _WorkerBinding.ATTRIBUTE, None)
+            if binding is None or binding.update_id != update_id:
+                return {"released": False, "update_id": update_id}
+            params = dict(model.named_parameters())
+            with torch.no_grad():
+                for name, original in binding.originals.items():
+                    if name in params:
+                        params[name].data = original
+            binding.tensors.clear()
+            try:
+                binding.bridge.release(update_id)
+            finally:
+                delattr(model, _WorkerBinding.ATTRIBUTE)
+            return {"released": True, "update_id": update_id}
 
-            self._apply()(restore)
+        self._apply()(unbind)
         self._deactivate(update_id)

@@ -368,28 +368,71 @@ def test_reload_adapters_in_process_and_checkpoint():
 
 
 def test_external_storage_adapter_rebinds_and_rolls_back():
+    """The function run on the worker imports the update through its own consumer bridge, rebinds the parameters it
+    knows, acknowledges; release restores the original storage; a tensor that does not fit undoes the rebinding and
+    releases the import; ``require_all_parameters`` insists on every tensor."""
     model = _model(3)
     publisher = CUDAVMMTensorBridge(backend_factory=_FakeSegment, device_index=0)
     manifest = publisher.publish(_model(4), weight_version=1)
-    aliases = publisher.import_update(manifest)
+    aliases = dict(publisher.import_update(manifest))
     originals = {n: p.data_ptr() for n, p in model.named_parameters()}
-    adapter = VLLMCUDAVMMExternalStorageAdapter(object(), apply_model=lambda fn: fn(model))
-    adapter.install(manifest, aliases)
+    calls = []
+
+    class Consumer:
+        def __init__(self, tensors):
+            self.tensors = tensors
+
+        def import_update(self, m):
+            calls.append(("import", m.update_id))
+            return self.tensors
+
+        def acknowledge(self, update_id):
+            calls.append(("ack", update_id))
+
+        def release(self, update_id):
+            calls.append(("release", update_id))
+
+    adapter = VLLMCUDAVMMExternalStorageAdapter(object(), apply_model=lambda fn: fn(model), synchronize_cuda=False,
+                                                bridge_factory=lambda: Consumer(aliases))
+    adapter.install(manifest, {})
+    assert adapter.active_weight_version == 1 and adapter.last_result[0]["zero_copy"] is True
+    assert sorted(adapter.last_result[0]["rebound"]) == sorted(aliases)
     for name, p in model.named_parameters():
         assert p.data_ptr() == aliases[name].data_ptr()  # parameters now alias the published memory
     adapter.release(manifest.update_id)
     assert {n: p.data_ptr() for n, p in model.named_parameters()} == originals
+    assert calls == [("import", manifest.update_id), ("ack", manifest.update_id), ("release", manifest.update_id)]
+    assert adapter.active_update_id is None
+    # not a cuda-vmm update
+    local = LocalTensorCopyBridge().publish(_model(), weight_version=1)
+    with pytest.raises(WeightBridgeUnavailableError, match="cuda-vmm"):
+        adapter.install(local, {})
+    # a tensor that does not fit: nothing stays rebound, the import is released, nothing is acknowledged
+    calls.clear()
     broken = dict(aliases)
     broken["1.weight"] = torch.zeros(7, 7)
-    local = LocalTensorCopyBridge().publish(_model(), weight_version=1)
-    with pytest.raises(WeightBridgeUnavailableError):
-        adapter.install(local, aliases)  # not a cuda-vmm update
+    bad = VLLMCUDAVMMExternalStorageAdapter(object(), apply_model=lambda fn: fn(model), synchronize_cuda=False,
+                                            bridge_factory=lambda: Consumer(broken))
+    with pytest.raises(WeightManifestValidationError, match="shape mismatch"):
+        bad.install(manifest, {})
+    assert {n: p.data_ptr() for n, p in model.named_parameters()} == originals
+    assert ("release", manifest.update_id) in calls and ("ack", manifest.update_id) not in calls
+    # a worker whose model lacks a parameter: fine by default, an error when every tensor is required
+    partial = dict(aliases)
+    partial["extra.weight"] = torch.zeros(2)
     import dataclasses
 
-    wrong = dataclasses.replace(manifest, update_id="other")
-    with pytest.raises(WeightManifestValidationError):
-        adapter.install(wrong, broken)
-    assert {n: p.data_ptr() for n, p in model.named_parameters()} == originals  # partial rebind undone
+    wider = dataclasses.replace(manifest, tensors={**manifest.tensors, "extra.weight": manifest.tensors["1.weight"]})
+    lenient = VLLMCUDAVMMExternalStorageAdapter(object(), apply_model=lambda fn: [fn(model)], synchronize_cuda=False,
+                                                bridge_factory=lambda: Consumer(partial))
+    lenient.install(wider, {})
+    assert "extra.weight" not in lenient.last_result[0]["rebound"]
+    lenient.release(wider.update_id)
+    strict = VLLMCUDAVMMExternalStorageAdapter(object(), apply_model=lambda fn: [fn(model)], synchronize_cuda=False,
+                                               bridge_factory=lambda: Consumer(partial), require_all_parameters=True)
+    with pytest.raises(WeightManifestValidationError, match="extra.weight"):
+        strict.install(wider, {})
+    assert {n: p.data_ptr() for n, p in model.named_parameters()} == originals
     publisher.release(manifest.update_id)
     with pytest.raises(WeightBridgeUnavailableError):
         VLLMCUDAVMMExternalStorageAdapter(object()).install(manifest, aliases)
