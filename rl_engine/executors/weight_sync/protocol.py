@@ -317,6 +317,7 @@ class BridgeStateMachine:
 
     transport = "abstract"
     allow_multi_rank = False
+    writes_transport_block = True       # transports that put their own block under ``metadata["weight_bridge"]``
 
     def __init__(self, *, source_worker: str = "local-training", source_rank: int = 0) -> None:
         self.source_worker = source_worker
@@ -343,6 +344,9 @@ class BridgeStateMachine:
 
     # -- publisher -----------------------------------------------------------------------------
     def publish(self, model: Any, *, weight_version: int, metadata: Optional[Mapping[str, Any]] = None):
+        if metadata is not None and BRIDGE_METADATA_KEY in metadata and self.writes_transport_block:
+            raise WeightManifestValidationError(
+                f"metadata key {BRIDGE_METADATA_KEY!r} is reserved for the transport's own description of the update")
         meta = validated_metadata(metadata, allow_multi_rank=self.allow_multi_rank)
         version = int(weight_version)
         if version <= self._latest_published_weight_version:

@@ -59,6 +59,7 @@ def pack_layout(tensors: Mapping[str, torch.Tensor], alignment: int = TENSOR_ALI
 # ---------------------------------------------------------------------------------- local clone
 class LocalTensorCopyBridge(BridgeStateMachine):
     transport = "local-clone"
+    writes_transport_block = False
 
     def _capture(self, tensors, update_id):
         return {n: _clone(t) for n, t in tensors.items()}, None, {}
@@ -130,10 +131,14 @@ class SharedMemoryTensorBridge(BridgeStateMachine):
         block = manifest.metadata.get(BRIDGE_METADATA_KEY)
         if not isinstance(block, Mapping) or block.get("format") != SHARED_MEMORY_FORMAT:
             raise WeightUpdateRejectedError(f"unknown weight update {manifest.update_id}")
+        entries = block.get("tensors")
+        if not isinstance(entries, Mapping) or set(entries) != set(manifest.tensors):
+            raise WeightManifestValidationError(
+                "shared-memory handle mismatch: the transport block and the manifest name different tensors")
         views, segments = {}, {}
         try:
             for name, desc in manifest.tensors.items():
-                info = block["tensors"][name]
+                info = entries[name]
                 dtype = _DTYPES[desc.dtype]
                 if not info["name"]:
                     views[name] = torch.empty(desc.shape, dtype=dtype)
@@ -179,29 +184,42 @@ def _serve_fd_forever(server: socket.socket, fd: int, stop: threading.Event) -> 
 
 
 class CUDAVMMTensorBridge(BridgeStateMachine):
-    """One VMM allocation per update, shared by POSIX fd.  ``backend_factory`` is injectable for tests."""
+    """One VMM allocation per update, shared by POSIX fd.
+
+    Two injection points: ``backend_factory()`` returns the driver backend, an object with
+    ``segment(device, nbytes, fd)`` (default: the C++ extension's ``VmmSegment``; the reference injects its ctypes
+    driver wrapper the same way, ``rl_engine/executors/bridge.py:2016``) and is only called once the tensors have been
+    found to live on a GPU; ``segment_factory(device, nbytes, fd)`` replaces segment creation itself and lifts the
+    GPU requirement (host-memory stand-ins in tests)."""
 
     transport = "cuda-vmm"
 
     def __init__(self, *, source_worker="local-training", source_rank=0, device_index: Optional[int] = None,
-                 backend_factory=None) -> None:
+                 backend_factory=None, segment_factory=None) -> None:
         super().__init__(source_worker=source_worker, source_rank=source_rank)
         self.device_index = device_index
         self._backend_factory = backend_factory
+        self._segment_factory = segment_factory
+        self._backend = None
 
     def _segment(self, device: int, nbytes: int, fd: int = -1):
+        if self._segment_factory is not None:
+            return self._segment_factory(device, nbytes, fd)
         if self._backend_factory is not None:
-            return self._backend_factory(device, nbytes, fd)
+            if self._backend is None:
+                self._backend = self._backend_factory()
+            return self._backend.segment(device, nbytes, fd)
         from rl_engine.kernels.ops.base import require_ext
 
         return require_ext().VmmSegment(device, nbytes, fd)
 
     def _capture(self, tensors, update_id):
-        if not torch.cuda.is_available() and self._backend_factory is None:
-            raise WeightBridgeUnavailableError("CUDAVMMTensorBridge requires a CUDA device")
-        for name, t in tensors.items():
-            if t.device.type != "cuda" and self._backend_factory is None:
-                raise WeightBridgeUnavailableError(f"CUDAVMMTensorBridge needs CUDA tensors; {name} is on {t.device}")
+        if self._segment_factory is None:
+            for name, t in tensors.items():
+                if t.device.type != "cuda":
+                    raise WeightBridgeUnavailableError(f"CUDAVMMTensorBridge requires CUDA tensors; {name} is on {t.device}")
+            if not torch.cuda.is_available():
+                raise WeightBridgeUnavailableError("CUDAVMMTensorBridge requires a CUDA device")
         device = self.device_index if self.device_index is not None else (
             next(iter(tensors.values())).device.index or 0)
         entries, total = pack_layout(tensors)
@@ -213,7 +231,7 @@ class CUDAVMMTensorBridge(BridgeStateMachine):
             dst.copy_(t.detach())
             stored[name] = dst
         event_handle = None
-        if torch.cuda.is_available() and self._backend_factory is None:
+        if torch.cuda.is_available() and self._segment_factory is None:
             ev = torch.cuda.Event(interprocess=True)
             ev.record(torch.cuda.current_stream(device))
             event_handle = ev.ipc_handle()
@@ -305,7 +323,17 @@ class IPCWeightBridge(BridgeStateMachine):
             return "cpu"
         return str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
 
+    def _require_cuda(self, tensors) -> None:
+        """CUDA IPC handles exist for device memory only (an injected ``reduce_tensor`` lifts the check: tests)."""
+        if self._reduce_tensor is not None:
+            return
+        for name, t in tensors.items():
+            if not getattr(t, "is_cuda", False):
+                raise WeightBridgeUnavailableError(
+                    f"CUDA IPC weight transport requires CUDA tensors; {name} is on {getattr(t, 'device', 'cpu')}")
+
     def _capture(self, tensors, update_id):
+        self._require_cuda(tensors)
         stored = {n: t.detach().contiguous() for n, t in tensors.items()}
         reduce = self._reduce()
         handles = {n: {"handle": reduce(t)} for n, t in stored.items()}
@@ -332,6 +360,7 @@ class IPCWeightBridge(BridgeStateMachine):
 
     # legacy entry points used by the reference's perf script (scripts/run_perf.py:65-69)
     def export_model_handles(self, model) -> Mapping[str, Any]:
+        self._require_cuda(model.state_dict())
         reduce = self._reduce()
         self._legacy_keepalive = {n: t.detach().contiguous() for n, t in model.state_dict().items()}
         return {n: reduce(t) for n, t in self._legacy_keepalive.items()}

@@ -131,7 +131,7 @@ class VLLMIPCWeightUpdateRequestBuilder:
             device = getattr(t, "device", None)
             if getattr(device, "type", "cuda") != "cuda" and not getattr(t, "is_cuda", False):
                 raise WeightBridgeUnavailableError(
-                    f"vLLM IPC weight updates need CUDA tensors; {name} is on {device}"
+                    f"vLLM IPC weight update requires CUDA tensors; {name} is on {device}"
                 )
             if tuple(int(d) for d in t.shape) != tuple(desc.shape):
                 raise WeightManifestValidationError(f"vLLM IPC tensor shape mismatch for {name}")
@@ -258,7 +258,7 @@ class VLLMCheckpointWeightReloadAdapter(_ActiveVersion):
         WeightLayout.from_metadata(manifest.metadata).validate_supported()
         if set(tensors) != set(manifest.tensors):
             raise WeightManifestValidationError("vLLM checkpoint reload tensor set does not match the manifest")
-        path = self._path_for(manifest)
+        path = self._path_for(manifest, tensors)
         try:
             reload_fn = _resolve_reload(
                 self.engine, lambda p: {"weights_path": p, "is_checkpoint_format": self.is_checkpoint_format},
@@ -275,11 +275,14 @@ class VLLMCheckpointWeightReloadAdapter(_ActiveVersion):
     def release(self, update_id: str) -> None:
         self._deactivate(update_id)
 
-    def _path_for(self, manifest: WeightUpdateManifest) -> str:
+    def _path_for(self, manifest: WeightUpdateManifest, tensors: Optional[Mapping[str, torch.Tensor]] = None) -> str:
         if self._weights_path:
             return str(self._weights_path)
         if self._resolver is not None:
-            found = self._resolver(manifest)
+            try:
+                found = self._resolver(manifest, tensors)        # the reference's resolvers take (manifest, tensors)
+            except TypeError:
+                found = self._resolver(manifest)
             if found:
                 return str(found)
         from_meta = manifest.metadata.get(self.metadata_key)

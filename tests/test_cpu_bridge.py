@@ -210,13 +210,13 @@ class _FakeSegment:
 
 
 def test_cuda_vmm_bridge_protocol_with_injected_backend():
-    publisher = CUDAVMMTensorBridge(backend_factory=_FakeSegment, device_index=0)
+    publisher = CUDAVMMTensorBridge(segment_factory=_FakeSegment, device_index=0)
     model = _model()
     manifest = publisher.publish(model, weight_version=1)
     block = manifest.metadata["weight_bridge"]
     assert block["format"] == "cuda-vmm-posix-fd-v1" and os.path.exists(block["socket_path"])
     assert all(e["offset"] % 256 == 0 for e in block["tensors"].values())
-    consumer = CUDAVMMTensorBridge(backend_factory=_FakeSegment)
+    consumer = CUDAVMMTensorBridge(segment_factory=_FakeSegment)
     tensors = consumer.import_update(manifest)  # fd arrives over the unix socket
     for name, p in model.state_dict().items():
         assert torch.equal(tensors[name], p)
@@ -226,7 +226,7 @@ def test_cuda_vmm_bridge_protocol_with_injected_backend():
     publisher.release(manifest.update_id)
     assert not os.path.exists(block["socket_path"])
     with pytest.raises(WeightUpdateRejectedError):
-        CUDAVMMTensorBridge(backend_factory=_FakeSegment).import_update(manifest)  # publisher is gone
+        CUDAVMMTensorBridge(segment_factory=_FakeSegment).import_update(manifest)  # publisher is gone
 
 
 # ------------------------------------------------------------------------- rollout executor
@@ -372,7 +372,7 @@ def test_external_storage_adapter_rebinds_and_rolls_back():
     knows, acknowledges; release restores the original storage; a tensor that does not fit undoes the rebinding and
     releases the import; ``require_all_parameters`` insists on every tensor."""
     model = _model(3)
-    publisher = CUDAVMMTensorBridge(backend_factory=_FakeSegment, device_index=0)
+    publisher = CUDAVMMTensorBridge(segment_factory=_FakeSegment, device_index=0)
     manifest = publisher.publish(_model(4), weight_version=1)
     aliases = dict(publisher.import_update(manifest))
     originals = {n: p.data_ptr() for n, p in model.named_parameters()}
