@@ -77,7 +77,7 @@ class GPUProfiler:
     @staticmethod
     def get_target_info(device_index: int = 0) -> GPUTargetInfo:
         if not torch.cuda.is_available():
-            return GPUTargetInfo("cpu", "cpu", 0.0, "n/a", "cpu", None, device_index)
+            return GPUTargetInfo("CPU", "unknown", 0.0, "N/A", "cpu", None, -1)
         props = torch.cuda.get_device_properties(device_index)
         major, minor = props.major, props.minor
         arch = {10: "blackwell", 9: "hopper", 8: "ampere"}.get(major, f"sm_{major}{minor}")
@@ -101,6 +101,18 @@ class PerformanceProfiler:
         self.gpu_info = GPUProfiler.get_target_info(self.device.index or 0)
         self._metrics: List[BenchmarkMetrics] = []
         self._flush = None
+
+    # -- FLOP models of the report (the reference's: ``benchmarks/profiler.py:226-245``) -------------------
+    @staticmethod
+    def estimate_logp_tflops(batch_size: int, seq_len: int, vocab_size: int) -> float:
+        """TFLOP of one selected-token log-prob pass over ``[B, S, V]`` logits: about five operations per element
+        (subtract the maximum, exponentiate, sum, divide, take the logarithm)."""
+        return 5.0 * batch_size * seq_len * vocab_size / 1e12
+
+    @staticmethod
+    def estimate_sampling_tflops(batch_size: int, vocab_size: int) -> float:
+        """TFLOP of one sampling step over ``[B, V]`` logits (the softmax dominates)."""
+        return 5.0 * batch_size * vocab_size / 1e12
 
     # -- timing -------------------------------------------------------------------------------------
     def _flush_l2(self) -> None:
