@@ -25,8 +25,10 @@ from typing import Any, Dict, List, Mapping, Optional
 import torch
 
 from rl_engine.executors.bridge import WeightBridgeUnavailableError
+from rl_engine.executors.hidden_states import extract_hidden_states
 from rl_engine.executors.trainer import (
-    NativeTrainingConfig, NativeTrainingWorker, advantage_metrics, clipped_ratio_objective, validate_model_input_token_ids,
+    NativeTrainingConfig, NativeTrainingWorker, advantage_metrics, clipped_ratio_objective, safe_token_ids,
+    validate_model_input_token_ids,
 )
 from rl_engine.executors.training_contract import RolloutStageResult, TrainingStageResult
 
@@ -166,6 +168,17 @@ class DeepSpeedTrainingWorker(NativeTrainingWorker):
         head = self.model.lm_head
         params = [head.weight] + ([head.bias] if getattr(head, "bias", None) is not None else [])
         return gather(params, modifier_rank=None)
+
+    def _current_logps(self, batch) -> torch.Tensor:
+        """The forward pass goes through the ENGINE (``engine(token_ids)``), not the bare module: DeepSpeed's
+        ``backward`` / ``step`` book-keeping and the ZeRO-3 parameter hooks hang on the engine's forward
+        (reference: ``rl_engine/executors/deepspeed_trainer.py:146-151,618-641``)."""
+        head = self.model.lm_head
+        hidden = extract_hidden_states(self.engine(batch.token_ids.long()), hidden_dim=head.weight.shape[1])
+        targets = safe_token_ids(batch.token_ids.to(hidden.device), batch.completion_mask)
+        logps = self._linear_logp(hidden, head.weight, targets, getattr(head, "bias", None))
+        keep = batch.completion_mask.to(device=logps.device, dtype=torch.bool)
+        return torch.where(keep, logps, torch.zeros_like(logps)).float()
 
     def train(self, rollout: RolloutStageResult) -> TrainingStageResult:
         t0 = time.perf_counter()

@@ -35,10 +35,10 @@ from rl_engine.testing import compute_policy_ratio, compute_reference_kl, masked
 class TinyPolicy(nn.Module):
     """``Embedding -> Linear`` toy policy: ``forward`` returns hidden states; ``lm_head`` is the projection."""
 
-    def __init__(self, vocab_size: int, hidden_dim: int) -> None:
+    def __init__(self, vocab_size: int, hidden_dim: int, *, bias: bool = True) -> None:
         super().__init__()
         self.embed = nn.Embedding(vocab_size, hidden_dim)
-        self.lm_head = nn.Linear(hidden_dim, vocab_size, bias=False)
+        self.lm_head = nn.Linear(hidden_dim, vocab_size, bias=bias)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return self.embed(token_ids)
@@ -66,8 +66,9 @@ def safe_token_ids(token_ids: torch.Tensor, mask: Optional[torch.Tensor]) -> tor
 def validate_model_input_token_ids(token_ids: torch.Tensor, *, vocab_size: int) -> None:
     if token_ids.numel() and (int(token_ids.min()) < 0 or int(token_ids.max()) >= vocab_size):
         raise ValueError(
-            f"training token ids must be in [0, {vocab_size}); got "
-            f"[{int(token_ids.min())}, {int(token_ids.max())}]"
+            f"training token ids must be in [0, {vocab_size}); got [{int(token_ids.min())}, {int(token_ids.max())}]. "
+            "Token ids are model inputs here: replace ignore-index / padding values (such as -100) before training; "
+            "masking only protects the loss"
         )
 
 
@@ -148,7 +149,12 @@ class NativeTrainingWorker(RolloutBatchMixin):
         )
 
     def _next_published_weight_version(self, consumed: int) -> int:
-        return max(int(consumed), self._published_version) + 1
+        """The version the weights of this step will be published under: above the consumed one, above everything
+        published, and above every version already promised to an earlier step (two steps on the same rollout version
+        get two different numbers)."""
+        promised = max(int(consumed), self._published_version, getattr(self, "_promised_version", -1)) + 1
+        self._promised_version = promised
+        return promised
 
     # -- weights ---------------------------------------------------------------------------------
     def publish_weights(self, weight_version: Optional[int] = None,

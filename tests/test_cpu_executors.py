@@ -360,7 +360,11 @@ def test_ray_actor_manager_with_fake_ray():
 
 class FakeDeepSpeedEngine:
     def __init__(self, model, optimizer):
-        self.module, self.optimizer, self.steps, self.backwards = model, optimizer, 0, 0
+        self.module, self.optimizer, self.steps, self.backwards, self.forwards = model, optimizer, 0, 0, 0
+
+    def __call__(self, *args, **kwargs):          # DeepSpeedEngine.forward runs the wrapped module
+        self.forwards += 1
+        return self.module(*args, **kwargs)
 
     def zero_grad(self):
         self.optimizer.zero_grad()
@@ -402,7 +406,8 @@ def test_deepspeed_worker_with_fake_module_and_zero3_gather():
     assert ds_cfg["zero_optimization"] == {"stage": 3, "overlap_comm": True} and ds_cfg["bf16"] == {"enabled": False}
     res = worker.train(make_rollout_result(iteration=0, weight_version=0, payload=None))
     assert res.metrics["training_backend"] == "deepspeed" and res.metrics["deepspeed_zero_stage"] == 3
-    assert worker.engine.steps == 1 and worker.engine.backwards == 1 and ("gather", 1, None) in record
+    assert worker.engine.steps == 1 and worker.engine.backwards == 1 and worker.engine.forwards == 1   # through the engine
+    assert ("gather", 2, None) in record                     # lm_head weight and bias, gathered around forward + backward
     manifest = worker.publish_weights()
     assert manifest.metadata["layout"]["zero_stage"] == 3 and record[-1][0] == "gather"
     try:

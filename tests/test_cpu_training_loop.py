@@ -168,6 +168,9 @@ class _FakeEngine:
     def __init__(self, model, rank, world):
         self.module, self.global_rank, self.world_size = model, rank, world
 
+    def __call__(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
     def backward(self, loss):
         loss.backward()
 
@@ -205,8 +208,8 @@ def test_deepspeed_zero3_publishes_a_rank0_gathered_clone():
     layout = manifest.metadata["layout"]
     assert layout["kind"] == "full-state" and layout["zero_stage"] == 3 and layout["world_size"] == 2 and layout["rank"] == 0
     export = manifest.metadata["deepspeed_zero3_full_state_export"]
-    assert export["method"] == "deepspeed.zero.GatheredParameters" and export["tensor_count"] == len(manifest.tensors) == 2
-    assert log[0] == ("enter", 2, 0) and log[1] == ("exit",)          # cloned inside the gather context, modifier rank 0
+    assert export["method"] == "deepspeed.zero.GatheredParameters" and export["tensor_count"] == len(manifest.tensors) == 3   # embedding, head weight, head bias
+    assert log[0] == ("enter", 3, 0) and log[1] == ("exit",)          # cloned inside the gather context, modifier rank 0
     # the published tensors are a clone: later training does not change what the consumer imports
     imported = worker.bridge.import_update(manifest)
     snapshot = {k: v.clone() for k, v in imported.items()}
