@@ -80,15 +80,20 @@ def _open_segment(name: Optional[str], size: int = 0, create: bool = False) -> s
         pass
     if create:
         return shared_memory.SharedMemory(create=True, size=max(size, 1))
-    seg = shared_memory.SharedMemory(name=name, **kwargs)
-    if "track" not in kwargs:
-        try:  # older pythons register attachments too; undo that so only the creator unlinks
-            from multiprocessing import resource_tracker
+    if "track" in kwargs:
+        return shared_memory.SharedMemory(name=name, **kwargs)
+    # Older pythons register every attachment with the resource tracker, which then unlinks the creator's segment when
+    # the attaching process exits.  Undoing the registration afterwards is no cure: a child that shares its parent's
+    # tracker would erase the PARENT's registration (the tracker then complains when the parent unlinks).  So the
+    # attachment is made with registration switched off, which is what ``track=False`` does on newer pythons.
+    from multiprocessing import resource_tracker
 
-            resource_tracker.unregister(seg._name, "shared_memory")  # type: ignore[attr-defined]
-        except Exception:
-            pass
-    return seg
+    register = resource_tracker.register
+    resource_tracker.register = lambda *args, **kwargs: None
+    try:
+        return shared_memory.SharedMemory(name=name)
+    finally:
+        resource_tracker.register = register
 
 
 class SharedMemoryTensorBridge(BridgeStateMachine):
