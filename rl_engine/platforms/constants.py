@@ -61,17 +61,20 @@ ActivationFunction = _enum(
     "ActivationFunction", RELU="relu", GELU="gelu", SILU="silu", TANH="tanh", SIGMOID="sigmoid"
 )
 
-constants = SimpleNamespace(
-    DeviceType=DeviceType,
-    BackendLib=BackendLib,
-    PrecisionType=PrecisionType,
-    SamplingMethod=SamplingMethod,
-    MemoryFormat=MemoryFormat,
-    OperatorFusionLevel=OperatorFusionLevel,
-    KernelOptimizationLevel=KernelOptimizationLevel,
-    LoggingLevel=LoggingLevel,
-    ProfilingMode=ProfilingMode,
-    DistributedStrategy=DistributedStrategy,
-    CheckpointFormat=CheckpointFormat,
-    ActivationFunction=ActivationFunction,
+_GROUPS = dict(
+    DeviceType=DeviceType, BackendLib=BackendLib, PrecisionType=PrecisionType, SamplingMethod=SamplingMethod,
+    MemoryFormat=MemoryFormat, OperatorFusionLevel=OperatorFusionLevel, KernelOptimizationLevel=KernelOptimizationLevel,
+    LoggingLevel=LoggingLevel, ProfilingMode=ProfilingMode, DistributedStrategy=DistributedStrategy,
+    CheckpointFormat=CheckpointFormat, ActivationFunction=ActivationFunction,
 )
+
+
+class Constants(SimpleNamespace):
+    """All enum groups as attributes of one object (``constants.DeviceType.CUDA``); the reference exposes the class as
+    well as the instance (``rl_engine/platforms/constants.py:96-112``)."""
+
+    def __init__(self) -> None:
+        super().__init__(**_GROUPS)
+
+
+constants = Constants()
