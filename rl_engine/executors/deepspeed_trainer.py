@@ -52,6 +52,7 @@ class DeepSpeedTrainingConfig(NativeTrainingConfig):
     zero_stage: int = 0
     train_micro_batch_size_per_gpu: int = 1
     deepspeed_config: Mapping[str, Any] = field(default_factory=dict)
+    initialize_kwargs: Mapping[str, Any] = field(default_factory=dict)     # extra keywords for ``deepspeed.initialize``
 
     def resolved_deepspeed_config(self) -> Dict[str, Any]:
         defaults = {
@@ -146,14 +147,20 @@ class FullStateSnapshot(torch.nn.Module):
 
 class DeepSpeedTrainingWorker(NativeTrainingWorker):
     def __init__(self, config: Optional[DeepSpeedTrainingConfig] = None, *, model=None, weight_bridge=None,
-                 deepspeed_module: Any = None) -> None:
-        super().__init__(config or DeepSpeedTrainingConfig(), model=model, weight_bridge=weight_bridge,
-                         source_worker="deepspeed-training")
+                 weight_transport: Optional[str] = None, deepspeed_module: Any = None) -> None:
+        """``weight_transport``: name for ``make_weight_bridge`` when no ``weight_bridge`` is given (default: the
+        configuration's)."""
+        config = config or DeepSpeedTrainingConfig()
+        if weight_bridge is None and weight_transport is not None:
+            from rl_engine.executors.bridge import make_weight_bridge
+
+            weight_bridge = make_weight_bridge(weight_transport, source_worker="deepspeed-training")
+        super().__init__(config, model=model, weight_bridge=weight_bridge, source_worker="deepspeed-training")
         self._deepspeed = _load_deepspeed(deepspeed_module)
         ds_config = self.config.resolved_deepspeed_config()
         self._zero_stage = int(ds_config.get("zero_optimization", {}).get("stage", 0))
         self.engine, self.optimizer, _, _ = self._deepspeed.initialize(
-            model=self.model, optimizer=self.optimizer, config=ds_config
+            model=self.model, optimizer=self.optimizer, config=ds_config, **dict(self.config.initialize_kwargs)
         )
 
     def _gathered(self):

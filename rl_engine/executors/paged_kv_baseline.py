@@ -61,10 +61,11 @@ class PagedKVCacheReservation:
     reserved_blocks: int
     cache_bytes: int
     metadata_bytes: int
+    reserved_bytes: int = -1          # cache + metadata when not given
 
-    @property
-    def reserved_bytes(self) -> int:
-        return self.cache_bytes + self.metadata_bytes
+    def __post_init__(self) -> None:
+        if self.reserved_bytes < 0:
+            object.__setattr__(self, "reserved_bytes", int(self.cache_bytes) + int(self.metadata_bytes))
 
     @property
     def reserved_mb(self) -> float:

@@ -88,9 +88,9 @@ RewardAdapter = Callable[[StatelessForwardOutputs, StatelessForwardInputs], torc
 
 
 # ---------------------------------------------------------------------------------- tree helpers
-def summarize_tensor_tree(tree: Any) -> TensorTreeSummary:
+def summarize_tensor_tree(value: Any) -> TensorTreeSummary:
     count = total = 0
-    stack = [tree]
+    stack = [value]
     while stack:
         node = stack.pop()
         if isinstance(node, torch.Tensor):
@@ -107,7 +107,8 @@ def summarize_tensor_tree(tree: Any) -> TensorTreeSummary:
     return TensorTreeSummary(count, total)
 
 
-def extract_kv_cache_outputs(raw: Any) -> Optional[Any]:
+def extract_kv_cache_outputs(raw_outputs: Any) -> Optional[Any]:
+    raw = raw_outputs
     for key in _KV_KEYS:
         value = raw.get(key) if isinstance(raw, Mapping) else getattr(raw, key, None)
         if value is not None and summarize_tensor_tree(value).tensor_count > 0:

@@ -112,10 +112,10 @@ def normalize_output_candidate(raw_output: Any, *, prompt_index: int, candidate_
     )
 
 
-def normalize_grouped_outputs(grouped: Sequence[Sequence[Any]]) -> List[List[NormalizedRolloutCandidate]]:
+def normalize_grouped_outputs(grouped_outputs: Sequence[Sequence[Any]]) -> List[List[NormalizedRolloutCandidate]]:
     return [
         [normalize_output_candidate(out, prompt_index=p, candidate_index=c) for c, out in enumerate(group)]
-        for p, group in enumerate(grouped)
+        for p, group in enumerate(grouped_outputs)
     ]
 
 

@@ -311,9 +311,10 @@ class IPCWeightBridge(BridgeStateMachine):
 
     transport = "cuda-ipc"
 
-    def __init__(self, *, source_worker="local-training", source_rank=0, reduce_tensor=None) -> None:
+    def __init__(self, *, source_worker="local-training", source_rank=0, reduce_tensor=None, reduce_tensor_fn=None) -> None:
+        """``reduce_tensor`` / ``reduce_tensor_fn`` (the reference's spelling): tensor -> IPC handle, injectable."""
         super().__init__(source_worker=source_worker, source_rank=source_rank)
-        self._reduce_tensor = reduce_tensor
+        self._reduce_tensor = reduce_tensor if reduce_tensor is not None else reduce_tensor_fn
 
     def _reduce(self):
         if self._reduce_tensor is not None:
@@ -370,8 +371,8 @@ class IPCWeightBridge(BridgeStateMachine):
         self._legacy_keepalive = {n: t.detach().contiguous() for n, t in model.state_dict().items()}
         return {n: reduce(t) for n, t in self._legacy_keepalive.items()}
 
-    def import_model_weights(self, handles: Mapping[str, Any]) -> Dict[str, torch.Tensor]:
-        return {n: rebuild(*args) for n, (rebuild, args) in handles.items()}
+    def import_model_weights(self, ipc_handles: Mapping[str, Any]) -> Dict[str, torch.Tensor]:
+        return {n: rebuild(*args) for n, (rebuild, args) in ipc_handles.items()}
 
 
 # ----------------------------------------------------------------------------- NVLink broadcast
