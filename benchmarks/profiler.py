@@ -171,6 +171,24 @@ class PerformanceProfiler:
         self._metrics.append(m)
         return m
 
+    # -- one-call profiling of a user's callable (the reference's ``profile_logp`` / ``profile_sampling``) ------
+    def profile_logp(self, candidate_fn: Callable[[], Any], batch_size: int, seq_len: int, vocab_size: int,
+                     benchmark_name: str = "logp_forward", native_fn: Optional[Callable[[], Any]] = None) -> BenchmarkMetrics:
+        """Times ``candidate_fn`` (a selected-token log-prob over ``[B, S, V]`` logits), measures its peak memory and,
+        when ``native_fn`` is given, how much less memory it needs than that baseline."""
+        _, ms, std = self.time_fn(candidate_fn)
+        peak = self.peak_memory_gb(candidate_fn)
+        saved = None if native_fn is None else self.peak_memory_gb(native_fn) - peak
+        return self.record(benchmark_name, batch_size, seq_len, vocab_size, ms, std,
+                           self.estimate_logp_tflops(batch_size, seq_len, vocab_size) * 1e12, peak, reduction_gb=saved)
+
+    def profile_sampling(self, candidate_fn: Callable[[], Any], batch_size: int, vocab_size: int, seq_len: int = 1,
+                         benchmark_name: str = "sampling_step") -> BenchmarkMetrics:
+        """Times one sampling step over ``[B, V]`` logits and records it."""
+        _, ms, std = self.time_fn(candidate_fn)
+        return self.record(benchmark_name, batch_size, seq_len, vocab_size, ms, std,
+                           self.estimate_sampling_tflops(batch_size, vocab_size) * 1e12, self.peak_memory_gb(candidate_fn))
+
     def blocked(self, name: str, batch: int, seq: int, vocab: int, exc: Exception) -> BenchmarkMetrics:
         first = (str(exc).splitlines() or [type(exc).__name__])[0]
         return self.record(name, batch, seq, vocab, float("inf"), None, status="blocked", notes=first)

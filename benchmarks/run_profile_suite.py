@@ -16,12 +16,17 @@ sys.path.insert(0, str(Path(__file__).resolve().parent))
 import profiler as prof  # noqa: E402
 
 
-def main() -> None:
+def build_script_parser():
+    """The profiler's own command line plus the flags that say where the two report files go."""
     parser = prof.build_arg_parser()
     parser.add_argument("--output-dir", type=Path, default=Path("profile_reports"))
     parser.add_argument("--prefix", default=None, help="report file stem (default: profile_<UTC timestamp>)")
     parser.add_argument("--fail-on-blocked", action="store_true", help="exit 1 when any workload was blocked")
-    args = parser.parse_args()
+    return parser
+
+
+def main() -> None:
+    args = build_script_parser().parse_args()
     if args.smoke:
         args.dtype, args.warmup, args.repeat, args.hidden = "float32", 0, 1, 16
     stem = args.prefix or datetime.now(timezone.utc).strftime("profile_%Y%m%dT%H%M%SZ")
